@@ -1,0 +1,161 @@
+/*
+ * C ABI of the B200 (sm_100a) Qwen3-0.6B greedy-decode engine.
+ *
+ * The first four entry points have exactly the signatures the reference's torch
+ * binding declares and calls (Tools/megakernel/qwen_ops.cpp:9-39), so that file
+ * links against this library unchanged.  The qmk_* entry points are additions
+ * (status codes, configuration, diagnostics) with no counterpart in the
+ * reference.
+ *
+ * Conventions: all weight/cache/scratch pointers are DEVICE pointers owned by
+ * the caller; `token_ids` of launch_ldg_prefill is a HOST pointer; every call
+ * acts on the CUDA device that is current on the calling thread and on the
+ * stream passed in.  The library keeps a small per-device scratch area of its
+ * own (inter-CTA exchange words + status), allocated on first use.
+ * The library is not re-entrant per device: one call at a time per GPU, as in
+ * the reference (process-global launcher state, megakernel_5090.cu:722-742).
+ */
+#ifndef QWEN_MEGAKERNEL_H_
+#define QWEN_MEGAKERNEL_H_
+
+#include <cuda_runtime_api.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Per-layer weight pointer record: 12 x 8 bytes, 16-byte aligned.  Same field
+ * order and size as the reference's struct (megakernel_5090.cu:91-104) and as
+ * the int64 table packed by Model/Qwen06B_architecture.py:166-185.
+ * All matrices are fp16 row-major [out, in]. */
+struct LDGLayerWeight;
+
+/* One decode step; the greedy token is written to *output_token_id (device).
+ * Does not synchronise.  Replaces megakernel_5090.cu:1175-1218
+ * (declared at qwen_ops.cpp:9-17). */
+void launch_ldg_decode_direct(
+    int input_token_id, int *output_token_id, const void *embed_weight,
+    const struct LDGLayerWeight *layer_weights, const void *final_norm_weight,
+    const void *lm_head_weight, const void *cos_table, const void *sin_table,
+    void *k_cache, void *v_cache, void *hidden_buffer, void *g_activations,
+    void *g_residual, void *g_q, void *g_k, void *g_v, void *g_attn_out,
+    void *g_mlp_intermediate, void *g_normalized, void *block_max_vals,
+    void *block_max_idxs, int num_layers, int position, int max_seq_len,
+    float attn_scale, cudaStream_t stream);
+
+/* Same contract as launch_ldg_decode_direct.  Replaces
+ * megakernel_5090.cu:1220-1272 (exported there, not bound by qwen_ops.cpp). */
+void launch_ldg_decode_persistent(
+    int input_token_id, int *output_token_id, const void *embed_weight,
+    const struct LDGLayerWeight *layer_weights, const void *final_norm_weight,
+    const void *lm_head_weight, const void *cos_table, const void *sin_table,
+    void *k_cache, void *v_cache, void *hidden_buffer, void *g_activations,
+    void *g_residual, void *g_q, void *g_k, void *g_v, void *g_attn_out,
+    void *g_mlp_intermediate, void *g_normalized, void *block_max_vals,
+    void *block_max_idxs, int num_layers, int position, int max_seq_len,
+    float attn_scale, cudaStream_t stream);
+
+/* num_steps greedy tokens from first_token_id at start_position; token i is
+ * written to output_log[i]; the EOS token is logged and ends the run; entries
+ * after it are left untouched.  Blocks until the stream is idle.  Replaces
+ * megakernel_5090.cu:1357-1436 (declared at qwen_ops.cpp:19-29). */
+void launch_ldg_generate_nosync(
+    int first_token_id, int num_steps, const void *embed_weight,
+    const struct LDGLayerWeight *layer_weights, const void *final_norm_weight,
+    const void *lm_head_weight, const void *cos_table, const void *sin_table,
+    void *k_cache, void *v_cache, void *hidden_buffer, void *g_activations,
+    void *g_residual, void *g_q, void *g_k, void *g_v, void *g_attn_out,
+    void *g_mlp_intermediate, void *g_normalized, void *block_max_vals,
+    void *block_max_idxs, int *output_log, int num_layers, int start_position,
+    int max_seq_len, float attn_scale, int eos_token_id, cudaStream_t stream);
+
+/* Fills the KV cache for num_tokens prompt tokens (HOST int32 array) at
+ * positions start_position .. start_position+num_tokens-1; no LM head.
+ * Blocks until done.  Replaces megakernel_5090.cu:1276-1355
+ * (declared at qwen_ops.cpp:31-39). */
+void launch_ldg_prefill(
+    const int *token_ids, int num_tokens, const void *embed_weight,
+    const struct LDGLayerWeight *layer_weights, const void *final_norm_weight,
+    const void *lm_head_weight, const void *cos_table, const void *sin_table,
+    void *k_cache, void *v_cache, void *hidden_buffer, void *g_activations,
+    void *g_residual, void *g_q, void *g_k, void *g_v, void *g_attn_out,
+    void *g_mlp_intermediate, void *g_normalized, void *block_max_vals,
+    void *block_max_idxs, int num_layers, int start_position, int max_seq_len,
+    float attn_scale, cudaStream_t stream);
+
+/* ---- additions (no counterpart in the reference) ------------------------- */
+
+/* Status codes returned by qmk_* and kept by the void entry points above. */
+enum {
+  QMK_OK = 0,
+  QMK_ERR_CUDA = 1,          /* a CUDA runtime call failed (see qmk_last_error) */
+  QMK_ERR_BAD_ARGUMENT = 2,  /* null/misaligned pointer, bad sizes */
+  QMK_ERR_POSITION = 3,      /* start_position + steps exceeds max_seq_len */
+  QMK_ERR_WAIT_TIMEOUT = 4,  /* a bounded device-side wait ran out */
+  QMK_ERR_BAD_TOKEN = 5,     /* token id outside [0, vocab) reached the kernel */
+  QMK_ERR_NOT_RESIDENT = 6   /* the persistent grid cannot be co-resident */
+};
+
+/* Layout version of LDGLayerWeight / the op surface; equals the reference's
+ * abi_version() (qwen_ops.cpp:42-44). */
+int qmk_abi_version(void);
+
+/* Engine options for the current device; pass a negative value to keep one.
+ *  vocab_size       rows of the tied LM head (default 151936, the reference's
+ *                   compile-time LDG_VOCAB_SIZE, megakernel_5090.cu:85)
+ *  rope_from_table  1: rotate with the caller's fp16 cos/sin tables as the
+ *                   reference does (megakernel_5090.cu:351-352); 0 (default):
+ *                   fp32 angles position * inv_freq computed in the kernel, valid
+ *                   for any position
+ *  split_len        target KV positions per attention work item (default 128)
+ *  max_ctas         cap on the persistent grid (default: one CTA per SM)
+ *  timeout_ms       budget of every device-side wait (default 2000) */
+int qmk_configure(int vocab_size, int rope_from_table, int split_len, int max_ctas, int timeout_ms);
+
+/* 64 fp32 inverse frequencies theta^(-2i/128) used when rope_from_table == 0
+ * (HOST pointer).  Default: theta = 1e6. */
+int qmk_set_inv_freq(const float *inv_freq64);
+
+/* Debug: when non-null, decode steps also write every logit to
+ * logits_out[step * vocab_size + row] (DEVICE fp32).  Null switches it off. */
+int qmk_set_logits_dump(float *logits_out);
+
+/* Status-returning twins of the three void launchers. */
+int qmk_decode(
+    int input_token_id, int *output_token_id, const void *embed_weight,
+    const struct LDGLayerWeight *layer_weights, const void *final_norm_weight,
+    const void *lm_head_weight, const void *cos_table, const void *sin_table,
+    void *k_cache, void *v_cache, void *hidden_buffer, void *g_normalized,
+    void *block_max_vals, void *block_max_idxs, int num_layers, int position,
+    int max_seq_len, float attn_scale, cudaStream_t stream);
+int qmk_generate(
+    int first_token_id, int num_steps, const void *embed_weight,
+    const struct LDGLayerWeight *layer_weights, const void *final_norm_weight,
+    const void *lm_head_weight, const void *cos_table, const void *sin_table,
+    void *k_cache, void *v_cache, void *hidden_buffer, void *g_normalized,
+    void *block_max_vals, void *block_max_idxs, int *output_log, int num_layers,
+    int start_position, int max_seq_len, float attn_scale, int eos_token_id,
+    int synchronize, cudaStream_t stream);
+int qmk_prefill(
+    const int *token_ids_host, int num_tokens, const void *embed_weight,
+    const struct LDGLayerWeight *layer_weights, const void *final_norm_weight,
+    const void *cos_table, const void *sin_table, void *k_cache, void *v_cache,
+    int num_layers, int start_position, int max_seq_len, float attn_scale,
+    cudaStream_t stream);
+
+/* Synchronises the device and returns the status word of the last launch
+ * (QMK_OK, or the first error a CTA recorded). */
+int qmk_sync_status(void);
+/* Text of the last error on this thread's device ("" if none). */
+const char *qmk_last_error(void);
+/* Persistent grid size (CTAs) and bytes of library-owned device scratch. */
+int qmk_num_ctas(void);
+long long qmk_scratch_bytes(void);
+/* Runs one bounded wait on a word nothing ever sets, with budget_us
+ * microseconds; returns QMK_ERR_WAIT_TIMEOUT when the wait gave up as designed. */
+int qmk_selftest_wait_timeout(int budget_us);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QWEN_MEGAKERNEL_H_ */

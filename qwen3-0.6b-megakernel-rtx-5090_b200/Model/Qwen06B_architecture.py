@@ -1,0 +1,285 @@
+"""Host side of the B200 Qwen3-0.6B decode engine: weight layout and the ``Decoder`` API.
+
+Mirrors the public surface of the reference module of the same name
+(``Model/Qwen06B_architecture.py``): module constants, ``load_weights``,
+``_pack_layer_weights``, ``Decoder`` (``step`` / ``reset`` / ``position`` /
+``generate``) and the module-level ``generate``.  A program written against the
+reference imports this file unchanged.  What differs underneath:
+
+* the ops come from the sm_100a C-ABI library through ``qwen_megakernel_C`` and a
+  whole request (all decode steps, LM head, argmax, token feedback) is one launch;
+* ``max_seq_len`` is a constructor argument (the reference fixes 2048,
+  ``Model/Qwen06B_architecture.py:21``); RoPE angles are computed in the kernel in
+  fp32 for any position, the fp16 tables are still built and passed for
+  signature compatibility (and are used when ``rope_from_table=True``);
+* the scratch tensors of the reference signature are allocated at their reference
+  sizes but only ``hidden``, ``norm_out`` and the argmax partials are written;
+* ``prefill_ids`` / ``generate_ids`` expose the token-ID level under ``generate``.
+"""
+
+from __future__ import annotations
+
+import math
+import os
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+try:  # same lookup order as the reference (Model/Qwen06B_architecture.py:7-10, 31-38)
+    import qwen_megakernel_C
+except ImportError:  # pragma: no cover - exercised only without a built library
+    qwen_megakernel_C = None
+
+EXTENSION_ABI_VERSION = 2
+
+NUM_LAYERS = 28
+NUM_KV_HEADS = 8
+HEAD_DIM = 128
+HIDDEN_SIZE = 1024
+INTERMEDIATE_SIZE = 3072
+Q_SIZE = 16 * HEAD_DIM
+KV_SIZE = 8 * HEAD_DIM
+MAX_SEQ_LEN = 2048
+VOCAB_SIZE = 151936
+# Size of the caller-side argmax partial buffers in the reference signature
+# (Model/Qwen06B_architecture.py:26); this engine fills one entry per CTA (<= 256).
+LDG_LM_NUM_BLOCKS = 680
+ROPE_THETA = 1_000_000.0
+FIELDS_PER_LAYER = 11
+_FIELD_NAMES = ("input_layernorm", "q_proj", "k_proj", "v_proj", "q_norm", "k_norm", "o_proj",
+                "post_attn_norm", "gate_proj", "up_proj", "down_proj")
+
+
+def _require_megakernel_op(op_name: str):
+    """The named op, or ``RuntimeError`` saying the native library is not loaded."""
+    if qwen_megakernel_C is not None and hasattr(qwen_megakernel_C, op_name):
+        return getattr(qwen_megakernel_C, op_name)
+    ns = getattr(torch.ops, "qwen_megakernel_C", None)
+    if ns is not None and hasattr(ns, op_name):
+        return getattr(ns, op_name)
+    have = [n for n in ("decode", "generate_nosync", "prefill")
+            if qwen_megakernel_C is not None and hasattr(qwen_megakernel_C, n)]
+    raise RuntimeError(
+        f"qwen_megakernel_C op '{op_name}' is unavailable. The CUDA library is not built/loaded "
+        f"(run build.py; torch {torch.__version__}). Available ops: {', '.join(have) or 'none'}.")
+
+
+def _assert_extension_compatibility() -> None:
+    """ABI handshake with the native library (reference: Model/Qwen06B_architecture.py:62-89)."""
+    if qwen_megakernel_C is None:
+        return
+    try:
+        got = int(qwen_megakernel_C.abi_version())
+    except Exception:
+        got = None
+    if got != EXTENSION_ABI_VERSION:
+        raise RuntimeError(
+            f"Incompatible qwen_megakernel_C binary: expected ABI {EXTENSION_ABI_VERSION}, got {got}. "
+            "The packed layer-pointer layout of Python and CUDA sides must match; rebuild the library.")
+
+
+_assert_extension_compatibility()
+_decode = _require_megakernel_op("decode")
+
+
+def rope_inv_freq(theta: float = ROPE_THETA) -> torch.Tensor:
+    return 1.0 / (theta ** (torch.arange(0, HEAD_DIM, 2, dtype=torch.float32) / HEAD_DIM))
+
+
+def build_rope_tables(max_seq_len: int, device="cuda", theta: float = ROPE_THETA):
+    """fp16 ``[max_seq_len, 128]`` cos/sin tables with duplicated halves
+    (layout of Model/Qwen06B_architecture.py:126-132)."""
+    ang = torch.outer(torch.arange(max_seq_len, dtype=torch.float32), rope_inv_freq(theta))
+    cos = torch.cos(ang).repeat(1, 2).to(torch.float16).to(device).contiguous()
+    sin = torch.sin(ang).repeat(1, 2).to(torch.float16).to(device).contiguous()
+    return cos, sin
+
+
+def load_weights(model_name: str = "Qwen/Qwen3-0.6B", verbose: bool = True, max_seq_len: int = MAX_SEQ_LEN):
+    """HF checkpoint -> (weights dict, tokenizer) in the reference layout
+    (Model/Qwen06B_architecture.py:96-163).  Needs the checkpoint on disk or a network."""
+    if not verbose:
+        os.environ.setdefault("HF_HUB_DISABLE_PROGRESS_BARS", "1")
+        os.environ.setdefault("TRANSFORMERS_NO_ADVISORY_WARNINGS", "1")
+    from transformers import AutoModelForCausalLM, AutoTokenizer
+
+    if verbose:
+        print(f"Loading {model_name}...")
+    model = AutoModelForCausalLM.from_pretrained(model_name, dtype=torch.float16, device_map="cuda")
+    tokenizer = AutoTokenizer.from_pretrained(model_name)
+    sd = model.state_dict()
+    hf_names = ("input_layernorm", "self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj",
+                "self_attn.q_norm", "self_attn.k_norm", "self_attn.o_proj", "post_attention_layernorm",
+                "mlp.gate_proj", "mlp.up_proj", "mlp.down_proj")
+    n_layers = model.config.num_hidden_layers
+    layer_weights = [sd[f"model.layers.{li}.{n}.weight"].contiguous() for li in range(n_layers) for n in hf_names]
+    embed = sd["model.embed_tokens.weight"].contiguous()
+    cos, sin = build_rope_tables(max_seq_len)
+    weights = dict(embed_weight=embed, layer_weights=layer_weights,
+                   final_norm_weight=sd["model.norm.weight"].contiguous(), lm_head_weight=embed,
+                   cos_table=cos, sin_table=sin)
+    del model
+    torch.cuda.empty_cache()
+    return weights, tokenizer
+
+
+def _pack_layer_weights(layer_weights: Sequence[torch.Tensor]) -> torch.Tensor:
+    """int64 device table, 12 pointers per layer (11 + zero pad), 16-byte aligned
+    (layout of Model/Qwen06B_architecture.py:166-185 / megakernel_5090.cu:91-104)."""
+    n_layers, rem = divmod(len(layer_weights), FIELDS_PER_LAYER)
+    assert rem == 0, "layer_weights must hold 11 tensors per layer"
+    table = torch.zeros(n_layers, FIELDS_PER_LAYER + 1, dtype=torch.int64)
+    for li in range(n_layers):
+        for j in range(FIELDS_PER_LAYER):
+            table[li, j] = layer_weights[li * FIELDS_PER_LAYER + j].data_ptr()
+    device = layer_weights[0].device
+    raw = torch.zeros(table.numel() + 2, dtype=torch.int64, device=device)
+    shift = ((16 - raw.data_ptr() % 16) % 16) // 8
+    view = raw[shift:shift + table.numel()]
+    view.copy_(table.flatten())
+    assert view.data_ptr() % 16 == 0
+    return view
+
+
+class Decoder:
+    """Stateful greedy decoder on one B200 (API of Model/Qwen06B_architecture.py:188-448)."""
+
+    def __init__(self, weights=None, tokenizer=None, model_name: str = "Qwen/Qwen3-0.6B", verbose: bool = True,
+                 max_seq_len: int = MAX_SEQ_LEN, rope_from_table: bool = False, device: str = "cuda"):
+        if not torch.cuda.is_available():
+            raise RuntimeError("Decoder needs a CUDA device (sm_100a); there is no CPU path")
+        if weights is None:
+            weights, tokenizer = load_weights(model_name, verbose=verbose, max_seq_len=max_seq_len)
+        self.tokenizer = tokenizer
+        self.max_seq_len = int(max_seq_len)
+        self._position = 0
+        self._weights = weights
+        self._embed_weight = weights["embed_weight"]
+        self._final_norm_weight = weights["final_norm_weight"]
+        self._lm_head_weight = weights["lm_head_weight"]
+        dev = self._embed_weight.device
+        self.num_layers = len(weights["layer_weights"]) // FIELDS_PER_LAYER
+        self.vocab_size = int(self._embed_weight.shape[0])
+        cos, sin = weights.get("cos_table"), weights.get("sin_table")
+        if cos is None or cos.shape[0] < self.max_seq_len or cos.device != dev:
+            cos, sin = build_rope_tables(self.max_seq_len, device=dev)
+        self._cos_table, self._sin_table = cos, sin
+        self._layer_weights_packed = _pack_layer_weights(weights["layer_weights"])
+        self._check_weight_alignment(weights["layer_weights"], verbose)
+        self._attn_scale = 1.0 / math.sqrt(HEAD_DIM)
+
+        self._k_cache = torch.zeros(self.num_layers, NUM_KV_HEADS, self.max_seq_len, HEAD_DIM,
+                                    dtype=torch.float16, device=dev)
+        self._v_cache = torch.zeros_like(self._k_cache)
+        self._kv_high_water = 0
+
+        f16 = dict(dtype=torch.float16, device=dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+        self._hidden = torch.zeros(HIDDEN_SIZE, **f16)
+        self._act = torch.zeros(HIDDEN_SIZE, **f32)
+        self._res = torch.zeros(HIDDEN_SIZE, **f32)
+        self._q = torch.zeros(Q_SIZE, **f16)
+        self._k = torch.zeros(KV_SIZE, **f16)
+        self._v = torch.zeros(KV_SIZE, **f16)
+        self._attn_out = torch.zeros(Q_SIZE, **f16)
+        self._mlp_inter = torch.zeros(INTERMEDIATE_SIZE, **f32)
+        self._norm_out = torch.zeros(HIDDEN_SIZE, **f32)
+        self._fmax_vals = torch.zeros(LDG_LM_NUM_BLOCKS, **f32)
+        self._fmax_idxs = torch.zeros(LDG_LM_NUM_BLOCKS, dtype=torch.int32, device=dev)
+        # token log: device tensor for the kernel, pinned host twin for the single DtoH copy
+        self._output_log = torch.full((self.max_seq_len,), -1, dtype=torch.int32, device=dev)
+        self._output_log_cpu = torch.empty(self.max_seq_len, dtype=torch.int32).pin_memory()
+
+        self._gen = _require_megakernel_op("generate_nosync")
+        self._prefill_op = _require_megakernel_op("prefill")
+        if qwen_megakernel_C is not None and hasattr(qwen_megakernel_C, "configure"):
+            qwen_megakernel_C.configure(vocab_size=self.vocab_size, rope_from_table=int(bool(rope_from_table)))
+            qwen_megakernel_C.set_inv_freq(rope_inv_freq())
+
+    # ------------------------------------------------------------------ argument packing
+    def _common(self):
+        return (self._embed_weight, self._layer_weights_packed, self._final_norm_weight, self._lm_head_weight,
+                self._cos_table, self._sin_table, self._k_cache, self._v_cache, self._hidden, self._act,
+                self._res, self._q, self._k, self._v, self._attn_out, self._mlp_inter, self._norm_out,
+                self._fmax_vals, self._fmax_idxs)
+
+    def _eos(self) -> int:
+        eos = getattr(self.tokenizer, "eos_token_id", None)
+        return -1 if eos is None else int(eos)
+
+    def _check_weight_alignment(self, layer_weights, verbose=True) -> None:
+        bad = [f"layer {i // FIELDS_PER_LAYER} [{_FIELD_NAMES[i % FIELDS_PER_LAYER]}]"
+               for i, t in enumerate(layer_weights) if t.data_ptr() % 16]
+        if bad:
+            raise RuntimeError("weight tensors not 16-byte aligned: " + ", ".join(bad[:8]))
+        if verbose:
+            print("All weight pointers 16-byte aligned OK")
+
+    # ------------------------------------------------------------------ reference API
+    @property
+    def position(self) -> int:
+        return self._position
+
+    def reset(self) -> None:
+        """Back to position 0.  Cache rows are not cleared: every row below the current
+        length is rewritten before it is read."""
+        self._position = 0
+        self._kv_high_water = 0
+
+    def step(self, input_token_id: int) -> int:
+        """One decode step through the ``decode`` op (Model/Qwen06B_architecture.py:351-380)."""
+        out = _decode(int(input_token_id), *self._common(), self.num_layers, self._position,
+                      self.max_seq_len, self._attn_scale)
+        tok = int(out.item())
+        self._position += 1
+        self._kv_high_water = max(self._kv_high_water, self._position)
+        return tok
+
+    def prefill_ids(self, ids: Sequence[int]) -> None:
+        """KV cache for ``ids`` at the current position through the ``prefill`` op."""
+        if len(ids) == 0:
+            return
+        t = torch.tensor(list(ids), dtype=torch.int32)
+        self._prefill_op(t, *self._common(), self.num_layers, self._position, self.max_seq_len, self._attn_scale)
+        self._position += len(ids)
+        self._kv_high_water = max(self._kv_high_water, self._position)
+
+    def generate_ids(self, prompt_ids: Sequence[int], max_tokens: int, reset: bool = True) -> List[int]:
+        """Token-ID form of ``generate``: prefill ``ids[:-1]``, decode from ``ids[-1]``, one DtoH copy
+        of the token log, trim at the first unwritten entry or EOS."""
+        ids = list(prompt_ids)
+        if not ids:
+            raise ValueError("empty prompt")
+        if reset:
+            self.reset()
+        self.prefill_ids(ids[:-1])
+        max_tokens = int(max_tokens)
+        if max_tokens <= 0:
+            return []
+        log = self._output_log[:max_tokens]
+        log.fill_(-1)
+        eos = self._eos()
+        self._gen(ids[-1], max_tokens, *self._common(), log, self.num_layers, self._position,
+                  self.max_seq_len, self._attn_scale, eos)
+        host = self._output_log_cpu[:max_tokens]
+        host.copy_(log)                       # stream is idle: the op synchronised
+        out: List[int] = []
+        for tok in host.tolist():
+            if tok == -1 or tok == eos:
+                break
+            out.append(tok)
+        self._position += len(out)
+        self._kv_high_water = max(self._kv_high_water, self._position)
+        return out
+
+    def generate(self, prompt: str, max_tokens: int = 100) -> Tuple[str, int, int]:
+        """``(text, n_prompt_tokens, n_output_tokens)`` (Model/Qwen06B_architecture.py:398-448)."""
+        ids = self.tokenizer.encode(prompt, add_special_tokens=False)
+        out = self.generate_ids(ids, max_tokens)
+        return self.tokenizer.decode(out, skip_special_tokens=True), len(ids), len(out)
+
+
+def generate(prompt: str, max_tokens: int = 50, verbose: bool = True) -> str:
+    """Load the model, generate once, return the text."""
+    text, _, _ = Decoder(verbose=verbose).generate(prompt, max_tokens)
+    return text

@@ -1,0 +1,214 @@
+"""Op surface ``qwen_megakernel_C`` over the sm_100a C-ABI library (ctypes, no libtorch).
+
+Same module name, op names, argument order and error behaviour as the reference's
+pybind module (``Tools/megakernel/qwen_ops.cpp:46-267``): ``decode``,
+``generate_nosync``, ``prefill``, ``abi_version``.  Argument checks that the
+reference does with ``TORCH_CHECK`` raise ``RuntimeError`` here too.  Tensors are
+only unwrapped to raw pointers; all arithmetic happens in the CUDA library.
+
+There is no CPU fallback: importing this module without the built library raises
+``ImportError``, and calling an op without a CUDA device raises ``RuntimeError``.
+
+Additions with no counterpart in the reference are grouped at the bottom
+(``configure``, ``set_inv_freq``, ``set_logits_dump``, ``sync_status``, ...).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIBRARY_PATH = os.environ.get("QWEN_MEGAKERNEL_LIB", os.path.join(_HERE, "libqwen_megakernel.so"))
+
+if not os.path.exists(LIBRARY_PATH):
+    raise ImportError(
+        f"qwen_megakernel_C: {LIBRARY_PATH} is not built. Run `python build.py` in {_HERE} "
+        "(nvcc, sm_100a). There is no CPU or PyTorch fallback for the decode ops.")
+
+_lib = ctypes.CDLL(LIBRARY_PATH)
+
+_P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+_PTRS19 = [_P] * 19  # embed .. block_max_idxs, in the reference's order (qwen_ops.cpp:9-17)
+
+_lib.launch_ldg_decode_direct.argtypes = [_I, _P, *_PTRS19, _I, _I, _I, _F, _P]
+_lib.launch_ldg_decode_direct.restype = None
+_lib.launch_ldg_decode_persistent.argtypes = [_I, _P, *_PTRS19, _I, _I, _I, _F, _P]
+_lib.launch_ldg_decode_persistent.restype = None
+_lib.launch_ldg_generate_nosync.argtypes = [_I, _I, *_PTRS19, _P, _I, _I, _I, _F, _I, _P]
+_lib.launch_ldg_generate_nosync.restype = None
+_lib.launch_ldg_prefill.argtypes = [_P, _I, *_PTRS19, _I, _I, _I, _F, _P]
+_lib.launch_ldg_prefill.restype = None
+_lib.qmk_abi_version.restype = _I
+_lib.qmk_configure.argtypes = [_I, _I, _I, _I, _I]
+_lib.qmk_configure.restype = _I
+_lib.qmk_set_inv_freq.argtypes = [_P]
+_lib.qmk_set_inv_freq.restype = _I
+_lib.qmk_set_logits_dump.argtypes = [_P]
+_lib.qmk_set_logits_dump.restype = _I
+_lib.qmk_decode.argtypes = [_I, _P, *([_P] * 12), _I, _I, _I, _F, _P]
+_lib.qmk_decode.restype = _I
+_lib.qmk_generate.argtypes = [_I, _I, *([_P] * 12), _P, _I, _I, _I, _F, _I, _I, _P]
+_lib.qmk_generate.restype = _I
+_lib.qmk_prefill.argtypes = [_P, _I, *([_P] * 7), _I, _I, _I, _F, _P]
+_lib.qmk_prefill.restype = _I
+_lib.qmk_sync_status.restype = _I
+_lib.qmk_last_error.restype = ctypes.c_char_p
+_lib.qmk_num_ctas.restype = _I
+_lib.qmk_scratch_bytes.restype = ctypes.c_longlong
+_lib.qmk_selftest_wait_timeout.argtypes = [_I]
+_lib.qmk_selftest_wait_timeout.restype = _I
+
+EXPORTED_SYMBOLS = (
+    "launch_ldg_decode_direct", "launch_ldg_decode_persistent", "launch_ldg_generate_nosync",
+    "launch_ldg_prefill", "qmk_abi_version", "qmk_configure", "qmk_set_inv_freq", "qmk_set_logits_dump",
+    "qmk_decode", "qmk_generate", "qmk_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
+    "qmk_scratch_bytes", "qmk_selftest_wait_timeout",
+)
+
+
+def _check(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _require_cuda() -> None:
+    _check(torch.cuda.is_available(),
+           "qwen_megakernel_C: no CUDA device; the decode ops have no CPU fallback")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _check_table(layer_weights_packed: torch.Tensor, who: str) -> None:
+    # qwen_ops.cpp:75-78, 155-157, 226-228
+    _check(layer_weights_packed.data_ptr() % 16 == 0,
+           f"{who}: layer_weights_packed must be 16-byte aligned "
+           f"(address ends in {layer_weights_packed.data_ptr() % 16})")
+
+
+def _raise_if_failed(who: str) -> None:
+    msg = _lib.qmk_last_error().decode()
+    if msg:
+        raise RuntimeError(f"{who}: {msg}")
+
+
+def abi_version() -> int:
+    """Layout version of the packed layer table (qwen_ops.cpp:42-44)."""
+    return int(_lib.qmk_abi_version())
+
+
+def decode(input_token_id, embed_weight, layer_weights_packed, final_norm_weight, lm_head_weight,
+           cos_table, sin_table, k_cache, v_cache, hidden, act, res, q, k, v, attn_out, mlp_inter,
+           norm_out, bmax_vals, bmax_idxs, num_layers, position, max_seq_len, attn_scale):
+    """One greedy step; returns an int32[1] CUDA tensor, does not synchronise (qwen_ops.cpp:46-110)."""
+    _require_cuda()
+    _check_table(layer_weights_packed, "decode")
+    out = torch.zeros(1, dtype=torch.int32, device=embed_weight.device)
+    _lib.launch_ldg_decode_direct(
+        int(input_token_id), out.data_ptr(), _ptr(embed_weight), _ptr(layer_weights_packed),
+        _ptr(final_norm_weight), _ptr(lm_head_weight), _ptr(cos_table), _ptr(sin_table), _ptr(k_cache),
+        _ptr(v_cache), _ptr(hidden), _ptr(act), _ptr(res), _ptr(q), _ptr(k), _ptr(v), _ptr(attn_out),
+        _ptr(mlp_inter), _ptr(norm_out), _ptr(bmax_vals), _ptr(bmax_idxs),
+        int(num_layers), int(position), int(max_seq_len), float(attn_scale), _stream())
+    _raise_if_failed("decode")
+    return out
+
+
+def generate_nosync(first_token_id, num_steps, embed_weight, layer_weights_packed, final_norm_weight,
+                    lm_head_weight, cos_table, sin_table, k_cache, v_cache, hidden, act, res, q, k, v,
+                    attn_out, mlp_inter, norm_out, bmax_vals, bmax_idxs, output_log, num_layers,
+                    start_position, max_seq_len, attn_scale, eos_token_id=151645):
+    """``num_steps`` greedy tokens into ``output_log``; blocks; returns ``output_log`` (qwen_ops.cpp:112-191)."""
+    _require_cuda()
+    _check(output_log.dtype == torch.int32,
+           f"generate_nosync: output_log must be dtype int32, got {output_log.dtype}")
+    _check(output_log.is_cuda, "generate_nosync: output_log must be on CUDA")
+    _check(output_log.is_contiguous(), "generate_nosync: output_log must be contiguous")
+    _check(output_log.numel() >= num_steps,
+           f"generate_nosync: output_log.numel() ({output_log.numel()}) < num_steps ({num_steps})")
+    _check_table(layer_weights_packed, "generate_nosync")
+    _lib.launch_ldg_generate_nosync(
+        int(first_token_id), int(num_steps), _ptr(embed_weight), _ptr(layer_weights_packed),
+        _ptr(final_norm_weight), _ptr(lm_head_weight), _ptr(cos_table), _ptr(sin_table), _ptr(k_cache),
+        _ptr(v_cache), _ptr(hidden), _ptr(act), _ptr(res), _ptr(q), _ptr(k), _ptr(v), _ptr(attn_out),
+        _ptr(mlp_inter), _ptr(norm_out), _ptr(bmax_vals), _ptr(bmax_idxs), output_log.data_ptr(),
+        int(num_layers), int(start_position), int(max_seq_len), float(attn_scale),
+        -1 if eos_token_id is None else int(eos_token_id), _stream())
+    _raise_if_failed("generate_nosync")
+    return output_log
+
+
+def prefill(token_ids, embed_weight, layer_weights_packed, final_norm_weight, lm_head_weight, cos_table,
+            sin_table, k_cache, v_cache, hidden, act, res, q, k, v, attn_out, mlp_inter, norm_out,
+            bmax_vals, bmax_idxs, num_layers, start_position, max_seq_len, attn_scale):
+    """Fills the KV cache for a CPU int32 token tensor; blocks (qwen_ops.cpp:193-260)."""
+    _check(token_ids.dtype == torch.int32, "token_ids must be int32")
+    _check(token_ids.device.type == "cpu", "token_ids must be on CPU")
+    _check(token_ids.is_contiguous(), "token_ids must be contiguous")
+    n = int(token_ids.shape[0])
+    if n == 0:
+        return None
+    _require_cuda()
+    _check_table(layer_weights_packed, "prefill")
+    _lib.launch_ldg_prefill(
+        token_ids.data_ptr(), n, _ptr(embed_weight), _ptr(layer_weights_packed), _ptr(final_norm_weight),
+        _ptr(lm_head_weight), _ptr(cos_table), _ptr(sin_table), _ptr(k_cache), _ptr(v_cache), _ptr(hidden),
+        _ptr(act), _ptr(res), _ptr(q), _ptr(k), _ptr(v), _ptr(attn_out), _ptr(mlp_inter), _ptr(norm_out),
+        _ptr(bmax_vals), _ptr(bmax_idxs), int(num_layers), int(start_position), int(max_seq_len),
+        float(attn_scale), _stream())
+    _raise_if_failed("prefill")
+    return None
+
+
+# ---------------------------------------------------------------- additions
+def configure(vocab_size=-1, rope_from_table=-1, split_len=-1, max_ctas=-1, timeout_ms=-1) -> None:
+    """Engine options of the current device; negative keeps the present value."""
+    rc = _lib.qmk_configure(int(vocab_size), int(rope_from_table), int(split_len), int(max_ctas), int(timeout_ms))
+    _check(rc == 0, f"configure failed with status {rc}")
+
+
+def set_inv_freq(inv_freq: torch.Tensor) -> None:
+    """64 fp32 RoPE inverse frequencies (CPU tensor) used for in-kernel angles."""
+    _require_cuda()
+    t = inv_freq.detach().to("cpu", torch.float32).contiguous()
+    _check(t.numel() == 64, "inv_freq must have 64 elements")
+    rc = _lib.qmk_set_inv_freq(t.data_ptr())
+    _check(rc == 0, f"set_inv_freq failed with status {rc}")
+
+
+def set_logits_dump(buf) -> None:
+    """fp32 CUDA tensor ``[steps, vocab]`` that decode steps fill with all logits, or None."""
+    if buf is not None:
+        _check(buf.is_cuda and buf.dtype == torch.float32 and buf.is_contiguous(),
+               "logits dump must be a contiguous fp32 CUDA tensor")
+    _lib.qmk_set_logits_dump(_ptr(buf))
+
+
+def sync_status() -> int:
+    return int(_lib.qmk_sync_status())
+
+
+def last_error() -> str:
+    return _lib.qmk_last_error().decode()
+
+
+def num_ctas() -> int:
+    _require_cuda()
+    return int(_lib.qmk_num_ctas())
+
+
+def scratch_bytes() -> int:
+    return int(_lib.qmk_scratch_bytes())
+
+
+def selftest_wait_timeout(budget_us: int = 200) -> int:
+    _require_cuda()
+    return int(_lib.qmk_selftest_wait_timeout(int(budget_us)))

@@ -1,0 +1,83 @@
+"""CPU tests of the boundary: the C-ABI library builds, loads and exports every symbol the header
+declares; the op module validates arguments like the reference binding; nothing computes here."""
+
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol(built_library):
+    header = open(os.path.join(ROOT, "include", "qwen_megakernel.h")).read()
+    declared = set(re.findall(r"\b((?:launch_ldg|qmk)_\w+)\s*\(", header))
+    assert {"launch_ldg_decode_direct", "launch_ldg_decode_persistent", "launch_ldg_generate_nosync",
+            "launch_ldg_prefill"} <= declared
+    lib = ctypes.CDLL(built_library)
+    for name in sorted(declared):
+        assert hasattr(lib, name), f"{name} declared in the header but not exported"
+    import qwen_megakernel_C as C
+    assert declared == set(C.EXPORTED_SYMBOLS)
+
+
+def test_abi_version_handshake(built_library):
+    import qwen_megakernel_C as C
+    from Model import Qwen06B_architecture as A
+    assert C.abi_version() == 2 == A.EXTENSION_ABI_VERSION
+    assert C.scratch_bytes() < 1 << 20
+
+
+def test_reference_constants_and_surface(built_library):
+    from Model import Qwen06B_architecture as A
+    assert (A.NUM_LAYERS, A.NUM_KV_HEADS, A.HEAD_DIM, A.HIDDEN_SIZE, A.INTERMEDIATE_SIZE) == (28, 8, 128, 1024, 3072)
+    assert (A.Q_SIZE, A.KV_SIZE, A.MAX_SEQ_LEN, A.VOCAB_SIZE, A.ROPE_THETA) == (2048, 1024, 2048, 151936, 1e6)
+    for name in ("load_weights", "_pack_layer_weights", "Decoder", "generate", "_require_megakernel_op"):
+        assert hasattr(A, name)
+    for name in ("step", "reset", "position", "generate"):
+        assert hasattr(A.Decoder, name)
+    with pytest.raises(RuntimeError, match="unavailable"):
+        A._require_megakernel_op("no_such_op")
+
+
+def test_pack_layer_weights_layout(built_library):
+    from Model.Qwen06B_architecture import _pack_layer_weights
+    import synthetic as S
+    w = S.make_weights(seed=1, num_layers=2, vocab_size=64)
+    t = _pack_layer_weights(w["layer_weights"])
+    assert t.dtype == torch.int64 and t.numel() == 2 * 12 and t.data_ptr() % 16 == 0
+    tab = t.view(2, 12)
+    for li in range(2):
+        for j in range(11):
+            assert tab[li, j].item() == w["layer_weights"][li * 11 + j].data_ptr()
+        assert tab[li, 11].item() == 0
+
+
+def test_argument_validation_matches_reference_binding(built_library):
+    """dtype / device / contiguity / size checks raise RuntimeError before any launch
+    (reference: qwen_ops.cpp:142-150, 219-221)."""
+    import qwen_megakernel_C as C
+    dummy = [torch.zeros(4)] * 19
+    with pytest.raises(RuntimeError, match="int32"):
+        C.prefill(torch.zeros(3, dtype=torch.int64), *dummy, 1, 0, 16, 0.1)
+    with pytest.raises(RuntimeError, match="contiguous"):
+        C.prefill(torch.zeros(6, dtype=torch.int32)[::2], *dummy, 1, 0, 16, 0.1)
+    assert C.prefill(torch.zeros(0, dtype=torch.int32), *dummy, 1, 0, 16, 0.1) is None
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError, match="no CUDA device"):
+            C.generate_nosync(1, 2, *dummy, torch.zeros(4, dtype=torch.int32), 1, 0, 16, 0.1)
+        with pytest.raises(RuntimeError, match="no CUDA device"):
+            C.decode(1, *dummy, 1, 0, 16, 0.1)
+        with pytest.raises(RuntimeError, match="CUDA device"):
+            from Model.Qwen06B_architecture import Decoder
+            Decoder(weights={})
+
+
+def test_stub_tokenizer_roundtrip():
+    import synthetic as S
+    tok = S.StubTokenizer(eos_token_id=7, vocab_size=100)
+    assert tok.encode("5 17 230") == [5, 17, 30]
+    assert tok.decode([5, 17]) == "5 17"
+    assert tok.apply_chat_template([{"role": "user", "content": "1 2"}]) == "1 2"
