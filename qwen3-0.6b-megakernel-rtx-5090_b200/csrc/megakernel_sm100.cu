@@ -559,6 +559,9 @@ __device__ void attention_phase(const Params &P, Ctx &c, const LayerW &lw, int l
     a1[i] = 0.f;
   }
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  // Row groups of one warp can run different trip counts: shuffles inside the loop name only
+  // the 8 lanes of the group.
+  const uint32_t grp_mask = 0xffu << (grp * 8);
   const __half *kb = P.k_cache + head_base + seg * 16;
   const __half *vb = P.v_cache + head_base + seg * 16;
   for (int p = p0 + c.warp * 4 + grp; p < p1; p += CONS_WARPS * 4) {
@@ -570,8 +573,8 @@ __device__ void attention_phase(const Params &P, Ctx &c, const LayerW &lw, int l
     d1 = dot8(k1, q1 + 8, d1);
 #pragma unroll
     for (int o = 1; o < 8; o <<= 1) {
-      d0 += __shfl_xor_sync(0xffffffffu, d0, o);
-      d1 += __shfl_xor_sync(0xffffffffu, d1, o);
+      d0 += __shfl_xor_sync(grp_mask, d0, o);
+      d1 += __shfl_xor_sync(grp_mask, d1, o);
     }
     d0 *= sc_log2;
     d1 *= sc_log2;
@@ -598,6 +601,7 @@ __device__ void attention_phase(const Params &P, Ctx &c, const LayerW &lw, int l
     }
   }
   // (3) merge the 4 row groups of the warp (rows differ, dims match for equal `seg`)
+  __syncwarp();
 #pragma unroll
   for (int o = 8; o <= 16; o <<= 1) {
     const float om0 = __shfl_xor_sync(0xffffffffu, m0, o), om1 = __shfl_xor_sync(0xffffffffu, m1, o);
@@ -724,6 +728,7 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
 
   if (c.warp == CONS_WARPS) {
     if (c.lane == 0) producer_main(P, c);
+    __syncwarp();   // the warp meets the block barrier below as a whole
   } else {
     const int S_max = min(MAX_SPLITS, max(1, c.ncta / NKV));
     int token = P.prefill ? P.token_ids[0] : P.first_token;
@@ -875,8 +880,10 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
   __syncthreads();
   // Bulk copies issued but never consumed (early stop, abort) must land before the CTA exits.
   if (c.tid == CONS_THREADS) {
-    const uint32_t issued = static_cast<uint32_t>(c.s_flags[2]), consumed = static_cast<uint32_t>(c.s_flags[3]);
-    for (uint32_t i = consumed; i < issued; ++i) {
+    // Every slot's latest fill is checked (already-landed phases answer at once), so this also
+    // covers chunks the consumers skipped after an abort.
+    const uint32_t issued = static_cast<uint32_t>(c.s_flags[2]);
+    for (uint32_t i = (issued > NSLOTS ? issued - NSLOTS : 0u); i < issued; ++i) {
       uint64_t *bar = c.full + (i % NSLOTS);
       const uint32_t parity = (i / NSLOTS) & 1u;
       const unsigned long long t0 = now_ns();
