@@ -120,6 +120,20 @@ int qmk_set_inv_freq(const float *inv_freq64);
  * logits_out[step * vocab_size + row] (DEVICE fp32).  Null switches it off. */
 int qmk_set_logits_dump(float *logits_out);
 
+/* Performance knobs; negative keeps a value.  spin_sleep_ns: nanosleep between
+ * polls of an exchange word (default 0).  l2_evict_first: 1 (default) streams
+ * weights with an evict-first L2 policy, 0 uses the default policy. */
+int qmk_set_tuning(int spin_sleep_ns, int l2_evict_first);
+
+/* Debug: when non-null, every CTA writes globaltimer stamps (ns) of the phase
+ * boundaries of the LAST step of each launch to timestamps[cta * 768 + slot]
+ * (DEVICE, >= grid * 768 words): slot layer*12 + k, k = 0 layer start, 1 QKV done,
+ * 2 attention done, 3 merge done, 4 attention output received, 5 O-proj done,
+ * 6 residual received, 7 gate/up done, 8 MLP activations received, 9 down-proj
+ * done, 10 layer output received; slots num_layers*12 + {0,1,2}: LM head start,
+ * LM head rows done, next token known.  Null switches it off. */
+int qmk_set_profile_buffer(unsigned long long *timestamps);
+
 /* Status-returning twins of the three void launchers. */
 int qmk_decode(
     int input_token_id, int *output_token_id, const void *embed_weight,

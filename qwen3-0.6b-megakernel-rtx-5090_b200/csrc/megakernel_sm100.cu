@@ -48,15 +48,24 @@ constexpr int KVS = NKV * D;     // 1024
 constexpr int QKV_ROWS = QS + 2 * KVS;  // 4096
 constexpr float RMS_EPS = 1e-6f;
 
-constexpr int CONS_WARPS = 16;
+#ifndef QMK_CONS_WARPS
+#define QMK_CONS_WARPS 12
+#endif
+// Math warps per CTA, a multiple of 4 (rows-per-chunk divides it).  12 + the producer warp puts at
+// most 4 warps on each SM sub-partition, which allows 128 registers per thread and a spill-free
+// kernel; 16 + 1 caps registers at 96 and spills.
+constexpr int CONS_WARPS = QMK_CONS_WARPS;
 constexpr int CONS_THREADS = CONS_WARPS * 32;   // 512 math threads
 constexpr int THREADS = CONS_THREADS + 32;      // + 1 producer warp
 constexpr int SLOT_BYTES = 8192;
 constexpr int NSLOTS = 22;
 static_assert(NSLOTS >= CONS_WARPS, "a group of chunks (up to one per warp) must fit in the ring");
+constexpr int EMPTY_UNITS = 4;   // arrival units that free a ring slot (rows-per-chunk is 4, 2 or 1)
 constexpr int MAX_SPLITS = 24;   // attention work items per kv head (<= grid / 8)
 constexpr int MAX_CTAS = 256;
+constexpr int MAX_LAYERS = 48;
 constexpr int PART_STRIDE = D + 2;  // acc[128], max, sum
+constexpr int PROF_STRIDE = 768;    // timestamp slots per CTA: 12 per layer + 8 for the LM head
 
 // Exchange buffers, in 8-byte words.
 constexpr int LL_QKV = 0;
@@ -81,6 +90,7 @@ struct Params {
   const __half *final_norm;
   const __half *lm_head;
   const __half *cos_table, *sin_table;
+  const float *rope;             // fp32 [position][cos 64 | sin 64], built by rope_table_kernel
   __half *k_cache, *v_cache;
   unsigned long long *ll;
   unsigned int *status;          // [0] code, [1] where, [2] cta
@@ -92,11 +102,14 @@ struct Params {
   float *bmax_vals;              // per-CTA argmax partials (may be null)
   int *bmax_idxs;
   float *logits_out;             // debug dump (may be null)
+  unsigned long long *prof;      // debug: per-CTA phase timestamps of the last step (may be null)
   unsigned long long timeout_ns;
   int first_token, num_steps, num_layers, start_position, max_seq_len, vocab;
   int eos, prefill, rope_from_table, split_len;
   unsigned int seq_base;
   float attn_scale;
+  int spin_sleep_ns;             // back-off between polls of an exchange word (0 = none)
+  int l2_evict_first;            // weight stream L2 policy: 1 evict_first, 0 default
 };
 
 __constant__ float c_inv_freq[D / 2];
@@ -110,6 +123,9 @@ __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_n(uint64_t *bar, uint32_t n) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(n) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
@@ -129,6 +145,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 __device__ __forceinline__ uint64_t l2_evict_first_policy() {
   uint64_t pol;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_evict_normal_policy() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pol));
   return pol;
 }
 // Bulk (non-tensor, non-multicast) TMA copy global -> this CTA's shared memory.
@@ -185,186 +206,216 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
-// ----------------------------------------------------------------------------- per-CTA context
+// ----------------------------------------------------------------------------- per-CTA state
+// Everything below is force-inlined into the one kernel and keeps its state in registers or in
+// shared memory at fixed offsets.  The kernel must compile to a ZERO-byte stack frame: with 222 KB
+// of shared memory carved out, L1 is ~30 KB for 544 threads, so any per-thread local memory
+// (escaping structs, dynamically indexed local arrays, spills) turns every touch into an L2
+// round trip on the critical path.  build.py fails the build if ptxas reports a stack frame.
+
+constexpr size_t SMEM_RING = static_cast<size_t>(NSLOTS) * SLOT_BYTES;
+// fp32 regions (offsets in floats from the end of the ring)
+constexpr int F_X = 0;                       // residual stream / layer input      [1024]
+constexpr int F_X1 = F_X + H;                // residual after attention           [1024]
+constexpr int F_VEC = F_X1 + H;              // attention output / MLP activations [3072]
+constexpr int F_RED = F_VEC + I;             // block reduction scratch            [32]
+constexpr int F_Q = F_RED + 32;              // rotated query heads                [2][128]
+constexpr int F_KNEW = F_Q + 2 * D;          // new K row (fp16-rounded)           [128]
+constexpr int F_VNEW = F_KNEW + D;           // new V row (fp16-rounded)           [128]
+constexpr int F_WPART = F_VNEW + D;          // per-warp attention partials        [16][2][130]
+constexpr int F_CS = F_WPART + CONS_WARPS * 2 * PART_STRIDE;  // cos[64], sin[64] of this position
+constexpr int F_AMAX = F_CS + 2 * (D / 2);   // argmax partials of all CTAs        [2*256]
+constexpr int F_MISC = F_AMAX + 2 * MAX_CTAS;  // [0,1] new-row scores, [16] token, [32..47]/[48..63] warp argmax
+constexpr int F_END = F_MISC + 64;
+constexpr size_t OFF_FULL = SMEM_RING + static_cast<size_t>(F_END) * 4;   // mbarriers: full[NSLOTS]
+constexpr size_t OFF_EMPTY = OFF_FULL + NSLOTS * 8;                       //            empty[NSLOTS]
+constexpr size_t OFF_FLAGS = OFF_EMPTY + NSLOTS * 8;   // int[4]: abort, stop, issued chunks, consumed chunks
+constexpr size_t OFF_LAYERS = OFF_FLAGS + 64;          // copy of the layer pointer table, 12 x u64 per layer
+constexpr size_t OFF_SEGS = OFF_LAYERS + MAX_LAYERS * sizeof(LayerW);
+constexpr int NKIND = 5;
+enum Kind { K_QKV = 0, K_O = 1, K_GU = 2, K_DOWN = 3, K_LM = 4 };
+// Row slices this CTA owns in every phase, computed once per launch (shared memory).
+struct SegTab {
+  int nseg[NKIND];
+  int tsel[NKIND][3];    // pointer slot within the 12-pointer layer record (K_LM: unused)
+  int row0[NKIND][3];    // first row within that tensor
+  int nrows[NKIND][3];
+  int out0[NKIND][3];    // index of the first output element
+  int e0, e1;            // attention outputs this CTA merges when KV is split
+};
+constexpr size_t SMEM_BYTES = OFF_SEGS + ((sizeof(SegTab) + 63) / 64) * 64;
+static_assert(SMEM_BYTES <= 232448, "over the 227 KB shared-memory limit of one CTA");
+static_assert(OFF_FULL % 8 == 0 && OFF_LAYERS % 16 == 0, "shared-memory alignment");
+
 struct Ctx {
-  unsigned char *ring;
-  uint64_t *full, *empty;
-  float *s_x, *s_x1, *s_vec, *s_red, *s_q, *s_knew, *s_vnew, *s_wpart, *s_cs, *s_misc;
-  volatile int *s_flags;  // [0] abort, [1] stop, [2] issued chunks, [3] consumed chunks
-  unsigned int *status;
-  unsigned long long timeout_ns;
+  unsigned char *smem;
   int tid, warp, lane, cta, ncta;
-  uint32_t chunk;  // consumer-side running chunk index (uniform over consumer threads)
+  uint32_t chunk;   // consumer-side running chunk index (uniform over consumer threads)
+  __device__ __forceinline__ float *f(int off) const { return reinterpret_cast<float *>(smem + SMEM_RING) + off; }
+  __device__ __forceinline__ uint64_t *full(uint32_t slot) const { return reinterpret_cast<uint64_t *>(smem + OFF_FULL) + slot; }
+  __device__ __forceinline__ uint64_t *empty(uint32_t slot) const { return reinterpret_cast<uint64_t *>(smem + OFF_EMPTY) + slot; }
+  __device__ __forceinline__ volatile int *flags() const { return reinterpret_cast<volatile int *>(smem + OFF_FLAGS); }
+  __device__ __forceinline__ const unsigned long long *layer_rec(int l) const {
+    return reinterpret_cast<const unsigned long long *>(smem + OFF_LAYERS) + l * 12;
+  }
+  __device__ __forceinline__ const SegTab *segs() const { return reinterpret_cast<const SegTab *>(smem + OFF_SEGS); }
+  __device__ __forceinline__ unsigned char *slot(uint32_t idx) const { return smem + static_cast<size_t>(idx % NSLOTS) * SLOT_BYTES; }
 };
 
 enum { WHERE_LL = 1, WHERE_FULL = 2, WHERE_EMPTY = 3, WHERE_DRAIN = 4, WHERE_TOKEN = 5 };
+// pointer slots of the layer record (megakernel_5090.cu:91-104)
+enum { REC_IN_LN = 0, REC_WQ = 1, REC_WK = 2, REC_WV = 3, REC_QNORM = 4, REC_KNORM = 5, REC_WO = 6, REC_POST_LN = 7,
+       REC_GATE = 8, REC_UP = 9, REC_DOWN = 10 };
 
-__device__ __noinline__ void raise_error(Ctx &c, int code, int where) {
-  if (atomicCAS(c.status, 0u, static_cast<unsigned>(code)) == 0u) {
-    c.status[1] = static_cast<unsigned>(where);
-    c.status[2] = static_cast<unsigned>(c.cta);
+__device__ __forceinline__ void raise_error(const Params &P, const Ctx &c, int code, int where) {
+  if (atomicCAS(P.status, 0u, static_cast<unsigned>(code)) == 0u) {
+    P.status[1] = static_cast<unsigned>(where);
+    P.status[2] = static_cast<unsigned>(c.cta);
   }
-  c.s_flags[0] = 1;
+  c.flags()[0] = 1;
 }
 
-// Slow path of an exchange-word wait: spin until the tag shows up, another CTA reported
-// an error, or the time budget is gone.  Returns the word (garbage after an abort).
-__device__ __noinline__ unsigned long long ll_spin(const unsigned long long *p, uint32_t tag, Ctx &c) {
-  const unsigned long long t0 = now_ns();
+// Wait for an exchange word to carry `tag`.  The fast path is one load; the spin looks at the abort
+// flag, the global status and the clock only every 256 polls.  Returns garbage after an abort.
+__device__ __forceinline__ unsigned long long ll_spin(const Params &P, const Ctx &c, const unsigned long long *p, uint32_t tag) {
+  unsigned long long t0 = 0;
   uint32_t it = 0;
   for (;;) {
-    unsigned long long w = ll_load(p);
+    const unsigned long long w = ll_load(p);
     if (static_cast<uint32_t>(w >> 32) == tag) return w;
-    if ((++it & 63u) == 0u) {
-      if (c.s_flags[0]) return 0ull;
-      if (ld_relaxed_u32(c.status) != 0u) { c.s_flags[0] = 1; return 0ull; }
-      if (now_ns() - t0 > c.timeout_ns) { raise_error(c, QMK_ERR_WAIT_TIMEOUT, WHERE_LL); return 0ull; }
+    if (P.spin_sleep_ns) __nanosleep(P.spin_sleep_ns);
+    if ((++it & 255u) == 0u) {
+      if (c.flags()[0]) return 0ull;
+      if (ld_relaxed_u32(P.status) != 0u) { c.flags()[0] = 1; return 0ull; }
+      const unsigned long long t = now_ns();
+      if (t0 == 0) t0 = t;
+      if (t - t0 > P.timeout_ns) { raise_error(P, c, QMK_ERR_WAIT_TIMEOUT, WHERE_LL); return 0ull; }
     }
   }
 }
-__device__ __forceinline__ float ll_wait(const unsigned long long *p, uint32_t tag, Ctx &c) {
+__device__ __forceinline__ float ll_wait(const Params &P, const Ctx &c, const unsigned long long *p, uint32_t tag) {
   unsigned long long w = ll_load(p);
-  if (static_cast<uint32_t>(w >> 32) != tag) w = ll_spin(p, tag, c);
+  if (static_cast<uint32_t>(w >> 32) != tag) w = ll_spin(P, c, p, tag);
   return __uint_as_float(static_cast<uint32_t>(w));
 }
 
-// Wait on an mbarrier phase with the same bounds.  Returns false after an abort.
-__device__ __noinline__ bool mbar_spin(uint64_t *bar, uint32_t parity, Ctx &c, int where, bool watch_stop) {
-  const unsigned long long t0 = now_ns();
+// Wait on an mbarrier phase with the same bounds.  Returns false after an abort (or, for the
+// producer, after the consumers said stop).
+__device__ __forceinline__ bool mbar_wait(const Params &P, const Ctx &c, uint64_t *bar, uint32_t parity, int where, bool producer) {
+  if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0 = 0;
   uint32_t it = 0;
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++it & 15u) == 0u) {
-      if (c.s_flags[0]) return false;
-      if (watch_stop && c.s_flags[1]) return false;
-      if (ld_relaxed_u32(c.status) != 0u) { c.s_flags[0] = 1; return false; }
+    if ((++it & 31u) == 0u) {
+      if (c.flags()[0]) return false;
+      if (producer && c.flags()[1]) return false;
+      if (ld_relaxed_u32(P.status) != 0u) { c.flags()[0] = 1; return false; }
+      const unsigned long long t = now_ns();
+      if (t0 == 0) t0 = t;
       // the producer may legitimately wait as long as any consumer does: 4x budget
-      if (now_ns() - t0 > (watch_stop ? 4 * c.timeout_ns : c.timeout_ns)) {
-        raise_error(c, QMK_ERR_WAIT_TIMEOUT, where);
-        return false;
-      }
+      if (t - t0 > (producer ? 4 * P.timeout_ns : P.timeout_ns)) { raise_error(P, c, QMK_ERR_WAIT_TIMEOUT, where); return false; }
     }
   }
 }
-__device__ __forceinline__ bool wait_full(Ctx &c, uint32_t idx) {
-  uint64_t *bar = c.full + (idx % NSLOTS);
-  uint32_t parity = (idx / NSLOTS) & 1u;
-  bool ok = mbar_try_wait(bar, parity);
-  if (!ok) ok = mbar_spin(bar, parity, c, WHERE_FULL, false);
-  return __all_sync(0xffffffffu, ok);   // the whole warp takes the same branch (shuffles follow)
+// The whole warp takes the same branch afterwards (shuffles follow).
+__device__ __forceinline__ bool wait_full(const Params &P, const Ctx &c, uint32_t idx) {
+  const bool ok = mbar_wait(P, c, c.full(idx % NSLOTS), (idx / NSLOTS) & 1u, WHERE_FULL, false);
+  return __all_sync(0xffffffffu, ok);
 }
 
-// Rows [r0, r1) of an n-row matrix owned by this CTA.
+// Rows [r0, r1) of an n-row matrix owned by CTA `cta` of `ncta` (launch-time only: 64-bit divisions).
 __device__ __forceinline__ void split_rows(int n, int ncta, int cta, int &r0, int &r1) {
   r0 = static_cast<int>((static_cast<long long>(n) * cta) / ncta);
   r1 = static_cast<int>((static_cast<long long>(n) * (cta + 1)) / ncta);
 }
+__device__ __forceinline__ constexpr int kind_row_bytes(int kind) { return kind == K_O ? QS * 2 : kind == K_DOWN ? I * 2 : H * 2; }
+__device__ __forceinline__ constexpr int kind_rpc(int kind) { return (kind == K_QKV || kind == K_LM) ? 4 : kind == K_DOWN ? 1 : 2; }
 
-// A contiguous run of weight rows one CTA streams and multiplies.
-struct Seg {
-  const unsigned char *src;   // first row
-  const unsigned char *src2;  // second matrix (up_proj rows) for the gate/up phase, else null
-  int nrows;
-  int out0;                   // index of the first output element
-};
-
-enum Phase { PH_QKV = 0, PH_O = 1, PH_GU = 2, PH_DOWN = 3, PH_LM = 4 };
-template <int PH> struct PhaseCfg;
-template <> struct PhaseCfg<PH_QKV> { static constexpr int K = H, RPC = 4; };
-template <> struct PhaseCfg<PH_O> { static constexpr int K = QS, RPC = 2; };
-template <> struct PhaseCfg<PH_GU> { static constexpr int K = H, RPC = 2; };   // 2 gate + 2 up rows
-template <> struct PhaseCfg<PH_DOWN> { static constexpr int K = I, RPC = 1; };
-template <> struct PhaseCfg<PH_LM> { static constexpr int K = H, RPC = 4; };
-
-// Row slices of one phase for this CTA.  Used verbatim by the producer and the consumers,
-// which is what keeps their chunk sequences identical.
-template <int PH>
-__device__ __forceinline__ int phase_segs(const LayerW &lw, const __half *lm_head, int vocab, int cta, int ncta,
-                                          Seg segs[3]) {
-  int r0, r1, n = 0;
-  if (PH == PH_QKV) {
-    split_rows(QKV_ROWS, ncta, cta, r0, r1);
-    const __half *base[3] = {lw.wq, lw.wk, lw.wv};
-    const int lo[3] = {0, QS, QS + KVS}, hi[3] = {QS, QS + KVS, QKV_ROWS};
-#pragma unroll
-    for (int t = 0; t < 3; ++t) {
-      int a = max(r0, lo[t]), b = min(r1, hi[t]);
-      if (a < b) {
-        segs[n].src = reinterpret_cast<const unsigned char *>(base[t] + static_cast<size_t>(a - lo[t]) * H);
-        segs[n].src2 = nullptr;
-        segs[n].nrows = b - a;
-        segs[n].out0 = a;
-        ++n;
-      }
+// Thread 0, once per launch.
+__device__ void build_segtab(SegTab *t, int cta, int ncta, int vocab) {
+  int r0, r1;
+  for (int k = 0; k < NKIND; ++k) t->nseg[k] = 0;
+  split_rows(QKV_ROWS, ncta, cta, r0, r1);
+  const int lo[3] = {0, QS, QS + KVS}, hi[3] = {QS, QS + KVS, QKV_ROWS};
+  for (int i = 0; i < 3; ++i) {
+    const int a = max(r0, lo[i]), b = min(r1, hi[i]);
+    if (a < b) {
+      const int n = t->nseg[K_QKV]++;
+      t->tsel[K_QKV][n] = REC_WQ + i; t->row0[K_QKV][n] = a - lo[i]; t->nrows[K_QKV][n] = b - a; t->out0[K_QKV][n] = a;
     }
-  } else if (PH == PH_O) {
-    split_rows(H, ncta, cta, r0, r1);
-    if (r0 < r1) { segs[0] = {reinterpret_cast<const unsigned char *>(lw.wo + static_cast<size_t>(r0) * QS), nullptr, r1 - r0, r0}; n = 1; }
-  } else if (PH == PH_GU) {
-    split_rows(I, ncta, cta, r0, r1);
-    if (r0 < r1) {
-      segs[0] = {reinterpret_cast<const unsigned char *>(lw.w_gate + static_cast<size_t>(r0) * H),
-                 reinterpret_cast<const unsigned char *>(lw.w_up + static_cast<size_t>(r0) * H), r1 - r0, r0};
-      n = 1;
-    }
-  } else if (PH == PH_DOWN) {
-    split_rows(H, ncta, cta, r0, r1);
-    if (r0 < r1) { segs[0] = {reinterpret_cast<const unsigned char *>(lw.w_down + static_cast<size_t>(r0) * I), nullptr, r1 - r0, r0}; n = 1; }
-  } else {
-    split_rows(vocab, ncta, cta, r0, r1);
-    if (r0 < r1) { segs[0] = {reinterpret_cast<const unsigned char *>(lm_head + static_cast<size_t>(r0) * H), nullptr, r1 - r0, r0}; n = 1; }
   }
-  return n;
+  const int rows[NKIND] = {0, H, I, H, vocab};
+  const int rec[NKIND] = {0, REC_WO, REC_GATE, REC_DOWN, 0};
+  for (int k = K_O; k <= K_LM; ++k) {
+    split_rows(rows[k], ncta, cta, r0, r1);
+    if (r0 < r1) { t->nseg[k] = 1; t->tsel[k][0] = rec[k]; t->row0[k][0] = r0; t->nrows[k][0] = r1 - r0; t->out0[k][0] = r0; }
+  }
+  split_rows(QS, ncta, cta, t->e0, t->e1);
 }
 
-// ----------------------------------------------------------------------------- producer
-struct Producer {
-  Ctx &c;
-  uint64_t pol;
-  uint32_t idx;
-  __device__ bool issue(const unsigned char *src, const unsigned char *src2, uint32_t bytes) {
-    const uint32_t slot = idx % NSLOTS;
-    if (c.s_flags[0] | c.s_flags[1]) return false;
-    if (idx >= NSLOTS) {
-      const uint32_t parity = ((idx / NSLOTS) - 1u) & 1u;
-      if (!mbar_try_wait(c.empty + slot, parity) && !mbar_spin(c.empty + slot, parity, c, WHERE_EMPTY, true)) return false;
-    }
-    unsigned char *dst = c.ring + static_cast<size_t>(slot) * SLOT_BYTES;
-    mbar_arrive_expect_tx(c.full + slot, src2 ? 2 * bytes : bytes);
-    bulk_g2s(dst, src, bytes, c.full + slot, pol);
-    if (src2) bulk_g2s(dst + SLOT_BYTES / 2, src2, bytes, c.full + slot, pol);
-    ++idx;
-    return true;
-  }
-  template <int PH>
-  __device__ bool phase(const LayerW &lw, const __half *lm_head, int vocab) {
-    constexpr int RB = PhaseCfg<PH>::K * 2, RPC = PhaseCfg<PH>::RPC;
-    Seg segs[3];
-    const int n = phase_segs<PH>(lw, lm_head, vocab, c.cta, c.ncta, segs);
-    for (int s = 0; s < n; ++s)
-      for (int r = 0; r < segs[s].nrows; r += RPC) {
-        const int nr = min(RPC, segs[s].nrows - r);
-        if (!issue(segs[s].src + static_cast<size_t>(r) * RB, segs[s].src2 ? segs[s].src2 + static_cast<size_t>(r) * RB : nullptr,
-                   static_cast<uint32_t>(nr) * RB))
-          return false;
-      }
-    return true;
-  }
-};
+// Weight rows of segment s of phase `kind` (layer record `rec` in shared memory, or the LM head).
+__device__ __forceinline__ const unsigned char *seg_src(const SegTab *t, int kind, int s, const unsigned long long *rec,
+                                                        const __half *lm_head, int which_up) {
+  const unsigned long long base = (kind == K_LM) ? reinterpret_cast<unsigned long long>(lm_head)
+                                                 : rec[t->tsel[kind][s] + which_up];
+  return reinterpret_cast<const unsigned char *>(base) + static_cast<size_t>(t->row0[kind][s]) * kind_row_bytes(kind);
+}
 
-__device__ void producer_main(const Params &P, Ctx &c) {
-  Producer pr{c, l2_evict_first_policy(), 0u};
-  LayerW none{};
-  bool ok = true;
-  for (int step = 0; ok && step < P.num_steps; ++step) {
-    for (int l = 0; ok && l < P.num_layers; ++l) {
-      const LayerW lw = P.layers[l];
-      ok = pr.phase<PH_QKV>(lw, nullptr, 0) && pr.phase<PH_O>(lw, nullptr, 0) && pr.phase<PH_GU>(lw, nullptr, 0) &&
-           pr.phase<PH_DOWN>(lw, nullptr, 0);
+// ----------------------------------------------------------------------------- producer (one thread)
+__device__ __forceinline__ bool produce_chunk(const Params &P, const Ctx &c, uint32_t &idx, uint64_t pol,
+                                              const unsigned char *src, const unsigned char *src2, uint32_t bytes) {
+  const uint32_t slot = idx % NSLOTS;
+  if (c.flags()[0] | c.flags()[1]) return false;
+  if (idx >= NSLOTS && !mbar_wait(P, c, c.empty(slot), ((idx / NSLOTS) - 1u) & 1u, WHERE_EMPTY, true)) return false;
+  unsigned char *dst = c.slot(idx);
+  mbar_arrive_expect_tx(c.full(slot), src2 ? 2 * bytes : bytes);
+  bulk_g2s(dst, src, bytes, c.full(slot), pol);
+  if (src2) bulk_g2s(dst + SLOT_BYTES / 2, src2, bytes, c.full(slot), pol);
+  ++idx;
+  return true;
+}
+
+__device__ __forceinline__ bool produce_phase(const Params &P, const Ctx &c, uint32_t &idx, uint64_t pol, int kind,
+                                              const unsigned long long *rec) {
+  const SegTab *t = c.segs();
+  const int rb = kind_row_bytes(kind), rpc = kind_rpc(kind);
+  const int n = t->nseg[kind];
+  for (int s = 0; s < n; ++s) {
+    const unsigned char *src = seg_src(t, kind, s, rec, P.lm_head, 0);
+    const unsigned char *src2 = (kind == K_GU) ? seg_src(t, kind, s, rec, P.lm_head, 1) : nullptr;
+    const int nrows = t->nrows[kind][s];
+#pragma unroll 1
+    for (int r = 0; r < nrows; r += rpc) {
+      const int nr = min(rpc, nrows - r);
+      const size_t off = static_cast<size_t>(r) * rb;
+      if (!produce_chunk(P, c, idx, pol, src + off, src2 ? src2 + off : nullptr, static_cast<uint32_t>(nr * rb))) return false;
     }
-    if (ok && !P.prefill) ok = pr.phase<PH_LM>(none, P.lm_head, P.vocab);
   }
-  c.s_flags[2] = static_cast<int>(pr.idx);
+  return true;
+}
+
+__device__ __forceinline__ void producer_main(const Params &P, const Ctx &c) {
+  const uint64_t pol = P.l2_evict_first ? l2_evict_first_policy() : l2_evict_normal_policy();
+  uint32_t idx = 0;
+  bool ok = true;
+#pragma unroll 1
+  for (int step = 0; ok && step < P.num_steps; ++step) {
+#pragma unroll 1
+    for (int l = 0; ok && l < P.num_layers; ++l) {
+      const unsigned long long *rec = c.layer_rec(l);
+      if (c.cta < 4) {  // pull the small norm vectors of this layer into L2 ahead of the math
+        const int which = c.cta == 0 ? REC_IN_LN : c.cta == 1 ? REC_POST_LN : c.cta == 2 ? REC_QNORM : REC_KNORM;
+        const unsigned char *v = reinterpret_cast<const unsigned char *>(rec[which]);
+        const int bytes = c.cta < 2 ? H * 2 : D * 2;
+        for (int b = 0; b < bytes; b += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(v + b));
+      }
+#pragma unroll 1
+      for (int kind = K_QKV; ok && kind <= K_DOWN; ++kind) ok = produce_phase(P, c, idx, pol, kind, rec);
+    }
+    if (ok && !P.prefill) ok = produce_phase(P, c, idx, pol, K_LM, nullptr);
+  }
+  c.flags()[2] = static_cast<int>(idx);
 }
 
 // ----------------------------------------------------------------------------- consumer math
@@ -404,84 +455,110 @@ __device__ __forceinline__ float row_dot_smem(const unsigned char *row, const fl
 }
 
 // sum over the 512 consumer threads; contains one consumer barrier
-__device__ __forceinline__ float block_sum(Ctx &c, float v) {
+__device__ __forceinline__ float block_sum(const Ctx &c, float v) {
   v = warp_sum(v);
-  if (c.lane == 0) c.s_red[c.warp] = v;
+  float *red = c.f(F_RED);
+  if (c.lane == 0) red[c.warp] = v;
   cons_sync();
   float t = 0.f;
 #pragma unroll
-  for (int i = 0; i < CONS_WARPS; ++i) t += c.s_red[i];
+  for (int i = 0; i < CONS_WARPS; ++i) t += red[i];
   return t;
 }
 
 // Polls N exchange words into shared memory as fp32; returns this thread's sum of squares.
+// All loads are issued before the first one is looked at.
 template <int N>
-__device__ __forceinline__ float poll_vec(const unsigned long long *buf, uint32_t tag, float *dst, Ctx &c) {
-  constexpr int PT = N / CONS_THREADS;
+__device__ __forceinline__ float poll_vec(const Params &P, const Ctx &c, const unsigned long long *buf, uint32_t tag, float *dst) {
+  constexpr int PT = (N + CONS_THREADS - 1) / CONS_THREADS;
   unsigned long long w[PT];
 #pragma unroll
-  for (int j = 0; j < PT; ++j) w[j] = ll_load(buf + c.tid + j * CONS_THREADS);
+  for (int j = 0; j < PT; ++j)
+    if (N % CONS_THREADS == 0 || c.tid + j * CONS_THREADS < N) w[j] = ll_load(buf + c.tid + j * CONS_THREADS);
   float ss = 0.f;
 #pragma unroll
-  for (int j = 0; j < PT; ++j) {
-    if (static_cast<uint32_t>(w[j] >> 32) != tag) w[j] = ll_spin(buf + c.tid + j * CONS_THREADS, tag, c);
-    const float v = __uint_as_float(static_cast<uint32_t>(w[j]));
-    dst[c.tid + j * CONS_THREADS] = v;
-    ss = fmaf(v, v, ss);
-  }
+  for (int j = 0; j < PT; ++j)
+    if (N % CONS_THREADS == 0 || c.tid + j * CONS_THREADS < N) {
+      if (static_cast<uint32_t>(w[j] >> 32) != tag) w[j] = ll_spin(P, c, buf + c.tid + j * CONS_THREADS, tag);
+      const float v = __uint_as_float(static_cast<uint32_t>(w[j]));
+      dst[c.tid + j * CONS_THREADS] = v;
+      ss = fmaf(v, v, ss);
+    }
   return ss;
 }
 
-// RMSNorm of the vector in `src` (sum of squares `ss` per thread) into per-lane registers.
-__device__ __forceinline__ void norm_to_regs(Ctx &c, const float *src, float ss, const uint4 (&wn)[4], float (&a)[32]) {
-  const float tot = block_sum(c, ss);  // barrier inside also publishes `src`
+// RMSNorm of the fp32 vector x in shared memory (`ss` = this thread's share of sum x^2) into
+// per-lane registers: a[j*8+i] = x[k] * rstd * w[k], k = j*256 + lane*8 + i.
+__device__ __forceinline__ void norm_to_regs(const Ctx &c, const float *x, float ss, const __half *norm_w, float (&a)[32]) {
+  uint4 wn[4];
+  const float tot = block_sum(c, ss);  // the barrier inside also publishes x
+  // The norm weights are loaded after the barrier on purpose: issued before it (while the CTA is
+  // still polling exchange words) the same loads measured ~100 us/token slower.
+#pragma unroll
+  for (int j = 0; j < 4; ++j) wn[j] = __ldg(reinterpret_cast<const uint4 *>(norm_w + j * 256 + c.lane * 8));
   const float rstd = 1.0f / sqrtf(tot * (1.0f / H) + RMS_EPS);
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int k = j * 256 + c.lane * 8;
-    const float4 x0 = *reinterpret_cast<const float4 *>(src + k);
-    const float4 x1 = *reinterpret_cast<const float4 *>(src + k + 4);
-    const float x[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+    const float4 x0 = *reinterpret_cast<const float4 *>(x + k);
+    const float4 x1 = *reinterpret_cast<const float4 *>(x + k + 4);
+    const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
     const __half2 *h = reinterpret_cast<const __half2 *>(&wn[j]);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float2 wf = __half22float2(h[i]);
-      a[j * 8 + 2 * i] = x[2 * i] * rstd * wf.x;
-      a[j * 8 + 2 * i + 1] = x[2 * i + 1] * rstd * wf.y;
+      a[j * 8 + 2 * i] = xs[2 * i] * rstd * wf.x;
+      a[j * 8 + 2 * i + 1] = xs[2 * i + 1] * rstd * wf.y;
     }
   }
 }
-__device__ __forceinline__ void load_norm_w(const __half *w, int lane, uint4 (&wn)[4]) {
-#pragma unroll
-  for (int j = 0; j < 4; ++j) wn[j] = __ldg(reinterpret_cast<const uint4 *>(w + j * 256 + lane * 8));
-}
 
-// Walks this CTA's chunks of one phase.  Warp w takes row (w % RPC) of chunk (w / RPC) of each
-// group of 16/RPC chunks; `fn(row_ptr, row_ptr2, out_index)` runs on the whole warp.
-// Every warp releases every chunk of the group (the empty barriers count 16 arrivals).
-template <int PH, typename Fn>
-__device__ __forceinline__ void consume_phase(Ctx &c, const LayerW &lw, const __half *lm_head, int vocab, Fn fn) {
-  constexpr int RB = PhaseCfg<PH>::K * 2, RPC = PhaseCfg<PH>::RPC, G = CONS_WARPS / RPC;
-  Seg segs[3];
-  const int n = phase_segs<PH>(lw, lm_head, vocab, c.cta, c.ncta, segs);
+// This CTA's rows of one projection, streamed through the ring.  Warp w takes row (w % RPC) of
+// chunk (w / RPC) of each group of 16/RPC chunks and hands the slot back when its row is done.
+//   K_QKV : out[row] = W.a                       K_GU  : out[row] = silu(Wg.a) * (Wu.a)
+//   K_O / K_DOWN : out[row] = W.act + resid[row] (activations in shared memory)
+//   K_LM  : running (max, argmax) in best / best_i, optional logits dump
+template <int KIND>
+__device__ __forceinline__ void gemv_rows(const Params &P, Ctx &c, const float (&a)[32], const float *act, const float *resid,
+                                          unsigned long long *out, uint32_t tag, float &best, int &best_i, float *dump) {
+  constexpr int RB = kind_row_bytes(KIND), RPC = kind_rpc(KIND), G = CONS_WARPS / RPC;
+  const SegTab *t = c.segs();
+  const int sub = c.warp % RPC, wch = c.warp / RPC;
+  const int n = t->nseg[KIND];
   for (int s = 0; s < n; ++s) {
-    const int nrows = segs[s].nrows;
+    const int nrows = t->nrows[KIND][s];
+    const int out0 = t->out0[KIND][s];
     const int nchunks = (nrows + RPC - 1) / RPC;
+#pragma unroll 1
     for (int c0 = 0; c0 < nchunks; c0 += G) {
-      const int ch = c0 + c.warp / RPC;
-      const int row = ch * RPC + (c.warp % RPC);
+      const int ch = c0 + wch;
+      const int row = ch * RPC + sub;
       if (ch < nchunks && row < nrows) {
         const uint32_t idx = c.chunk + static_cast<uint32_t>(ch);
-        if (wait_full(c, idx)) {
-          const unsigned char *p = c.ring + static_cast<size_t>(idx % NSLOTS) * SLOT_BYTES + (c.warp % RPC) * RB;
-          fn(p, p + SLOT_BYTES / 2, segs[s].out0 + row);
+        if (wait_full(P, c, idx)) {
+          const unsigned char *p = c.slot(idx) + sub * RB;
+          const int o = out0 + row;
+          float v;
+          if constexpr (KIND == K_O) v = row_dot_smem<QS>(p, act, c.lane) + resid[o];
+          else if constexpr (KIND == K_DOWN) v = row_dot_smem<I>(p, act, c.lane) + resid[o];
+          else v = row_dot_regs(p, a, c.lane);
+          if constexpr (KIND == K_GU) {
+            const float u = row_dot_regs(p + SLOT_BYTES / 2, a, c.lane);
+            v = v / (1.0f + expf(-v)) * u;   // SiLU(gate) * up in fp32 (megakernel_5090.cu:681-684 does it in fp16)
+          }
+          if constexpr (KIND == K_LM) {
+            if (v > best || (v == best && o < best_i)) { best = v; best_i = o; }
+            if (dump && c.lane == 0) dump[o] = v;
+          } else {
+            if (c.lane == 0) ll_store(out + o, v, tag);
+          }
         }
       }
+      // Release: the RPC warps mapped to a chunk each hand back EMPTY_UNITS/RPC units, whether or not
+      // their row exists (a short last chunk), so every chunk collects exactly EMPTY_UNITS.
       __syncwarp();
-      if (c.lane == 0) {
-        const int last = min(G, nchunks - c0);
-        for (int j = 0; j < last; ++j) mbar_arrive(c.empty + ((c.chunk + static_cast<uint32_t>(c0 + j)) % NSLOTS));
-      }
+      if (c.lane == 0 && ch < nchunks)
+        mbar_arrive_n(c.empty((c.chunk + static_cast<uint32_t>(ch)) % NSLOTS), EMPTY_UNITS / RPC);
     }
     c.chunk += static_cast<uint32_t>(nchunks);
   }
@@ -491,13 +568,17 @@ __device__ __forceinline__ void consume_phase(Ctx &c, const LayerW &lw, const __
 // Work item (kv head g, split s) on CTA g + 8*s: old cache rows [p0, p1); the last split also
 // normalises/rotates/stores the new K,V row and folds it in.  Writes either the final head
 // outputs (one split) or unnormalised partials.
-__device__ void attention_phase(const Params &P, Ctx &c, const LayerW &lw, int layer, int pos, int S, uint32_t tag) {
+__device__ __forceinline__ void attention_phase(const Params &P, const Ctx &c, const unsigned long long *rec, int layer, int pos,
+                                                int S, uint32_t tag) {
+  float *s_q = c.f(F_Q), *s_knew = c.f(F_KNEW), *s_vnew = c.f(F_VNEW), *s_wpart = c.f(F_WPART), *s_misc = c.f(F_MISC);
+  const float *s_cs = c.f(F_CS);
   const unsigned long long *qkv = P.ll + LL_QKV;
   if (c.cta >= NKV * S) return;
   const int g = c.cta % NKV, s = c.cta / NKV;
   const bool owner = (s == S - 1);
-  const int p0 = static_cast<int>((static_cast<long long>(pos) * s) / S);
-  const int p1 = static_cast<int>((static_cast<long long>(pos) * (s + 1)) / S);
+  // old rows [p0, p1) of [0, pos); pos * S < 2^31, 32-bit division
+  const int p0 = static_cast<int>(static_cast<unsigned>(pos * s) / static_cast<unsigned>(S));
+  const int p1 = static_cast<int>(static_cast<unsigned>(pos * (s + 1)) / static_cast<unsigned>(S));
   const size_t head_base = (static_cast<size_t>(layer) * NKV + g) * static_cast<size_t>(P.max_seq_len) * D;
 
   // (1) head preparation: warps 0,1 = the two query heads; owner: warp 2 = K, warp 3 = V
@@ -506,13 +587,13 @@ __device__ void attention_phase(const Params &P, Ctx &c, const LayerW &lw, int l
     const unsigned long long *src = (w < 2) ? qkv + (2 * g + w) * D : (w == 2) ? qkv + QS + g * D : qkv + QS + KVS + g * D;
     float nw[4] = {1.f, 1.f, 1.f, 1.f};
     if (w < 3) {
-      const __half *nwp = (w < 2) ? lw.q_norm : lw.k_norm;
+      const __half *nwp = reinterpret_cast<const __half *>(rec[(w < 2) ? REC_QNORM : REC_KNORM]);
 #pragma unroll
       for (int i = 0; i < 4; ++i) nw[i] = __half2float(__ldg(nwp + lane + 32 * i));
     }
     float v[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] = ll_wait(src + lane + 32 * i, tag, c);
+    for (int i = 0; i < 4; ++i) v[i] = ll_wait(P, c, src + lane + 32 * i, tag);
     if (w < 3) {
       float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
       ss = warp_sum(ss);
@@ -520,18 +601,18 @@ __device__ void attention_phase(const Params &P, Ctx &c, const LayerW &lw, int l
 #pragma unroll
       for (int i = 0; i < 4; ++i) v[i] = v[i] * rstd * nw[i];
       // rotate-half: element i pairs with i+64 and both use frequency i (i < 64)
-      const float c0 = c.s_cs[lane], s0 = c.s_cs[64 + lane];
-      const float c1 = c.s_cs[lane + 32], s1 = c.s_cs[64 + lane + 32];
+      const float c0 = s_cs[lane], s0 = s_cs[64 + lane];
+      const float c1 = s_cs[lane + 32], s1 = s_cs[64 + lane + 32];
       const float r0 = v[0] * c0 - v[2] * s0, r2 = v[0] * s0 + v[2] * c0;
       const float r1 = v[1] * c1 - v[3] * s1, r3 = v[1] * s1 + v[3] * c1;
       v[0] = r0; v[1] = r1; v[2] = r2; v[3] = r3;
     }
     if (w < 2) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) c.s_q[w * D + lane + 32 * i] = v[i];
+      for (int i = 0; i < 4; ++i) s_q[w * D + lane + 32 * i] = v[i];
     } else {
       // the new row takes part in this step's attention as the fp16 value the cache will hold
-      float *snew = (w == 2) ? c.s_knew : c.s_vnew;
+      float *snew = (w == 2) ? s_knew : s_vnew;
 #pragma unroll
       for (int i = 0; i < 4; ++i) snew[lane + 32 * i] = __half2float(__float2half_rn(v[i]));
     }
@@ -543,36 +624,35 @@ __device__ void attention_phase(const Params &P, Ctx &c, const LayerW &lw, int l
   if (owner && c.warp < 2) {
     float d = 0.f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) d = fmaf(c.s_q[c.warp * D + c.lane + 32 * i], c.s_knew[c.lane + 32 * i], d);
+    for (int i = 0; i < 4; ++i) d = fmaf(s_q[c.warp * D + c.lane + 32 * i], s_knew[c.lane + 32 * i], d);
     d = warp_sum(d);
-    if (c.lane == 0) c.s_misc[c.warp] = d * sc_log2;
+    if (c.lane == 0) s_misc[c.warp] = d * sc_log2;
   }
 
-  // (2) stream old rows: 8 lanes per row (16 dims each), 4 rows per warp pass, 64 rows per CTA pass
-  const int grp = c.lane >> 3, seg = c.lane & 7;
-  float q0[16], q1[16], a0[16], a1[16];
+  // (2) stream old rows: 16 lanes per row (8 dims each), 2 rows per warp pass, 32 rows per CTA pass.
+  // (8 lanes x 16 dims needs 32 more registers and spilled; spills cost an L2 round trip here.)
+  const int grp = c.lane >> 4, seg = c.lane & 15;
+  float q0[8], q1[8], a0[8], a1[8];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    q0[i] = c.s_q[seg * 16 + i];
-    q1[i] = c.s_q[D + seg * 16 + i];
+  for (int i = 0; i < 8; ++i) {
+    q0[i] = s_q[seg * 8 + i];
+    q1[i] = s_q[D + seg * 8 + i];
     a0[i] = 0.f;
     a1[i] = 0.f;
   }
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-  // Row groups of one warp can run different trip counts: shuffles inside the loop name only
-  // the 8 lanes of the group.
-  const uint32_t grp_mask = 0xffu << (grp * 8);
-  const __half *kb = P.k_cache + head_base + seg * 16;
-  const __half *vb = P.v_cache + head_base + seg * 16;
-  for (int p = p0 + c.warp * 4 + grp; p < p1; p += CONS_WARPS * 4) {
-    const uint4 *kp = reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(p) * D);
-    const uint4 *vp = reinterpret_cast<const uint4 *>(vb + static_cast<size_t>(p) * D);
-    const uint4 k0 = __ldcg(kp), k1 = __ldcg(kp + 1), v0 = __ldcg(vp), v1 = __ldcg(vp + 1);
+  // The two row groups of a warp can run different trip counts: shuffles inside the loop name
+  // only the 16 lanes of the group.
+  const uint32_t grp_mask = 0xffffu << (grp * 16);
+  const __half *kb = P.k_cache + head_base + seg * 8;
+  const __half *vb = P.v_cache + head_base + seg * 8;
+#pragma unroll 2
+  for (int p = p0 + c.warp * 2 + grp; p < p1; p += CONS_WARPS * 2) {
+    const uint4 k0 = __ldcg(reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(p) * D));
+    const uint4 v0 = __ldcg(reinterpret_cast<const uint4 *>(vb + static_cast<size_t>(p) * D));
     float d0 = dot8(k0, q0, 0.f), d1 = dot8(k0, q1, 0.f);
-    d0 = dot8(k1, q0 + 8, d0);
-    d1 = dot8(k1, q1 + 8, d1);
 #pragma unroll
-    for (int o = 1; o < 8; o <<= 1) {
+    for (int o = 1; o < 16; o <<= 1) {
       d0 += __shfl_xor_sync(grp_mask, d0, o);
       d1 += __shfl_xor_sync(grp_mask, d1, o);
     }
@@ -584,26 +664,20 @@ __device__ void attention_phase(const Params &P, Ctx &c, const LayerW &lw, int l
     m0 = n0; m1 = n1;
     l0 = fmaf(l0, cr0, e0);
     l1 = fmaf(l1, cr1, e1);
-    float vf[16];
-    {
-      const __half2 *h = reinterpret_cast<const __half2 *>(&v0);
-      const __half2 *h2 = reinterpret_cast<const __half2 *>(&v1);
+    const __half2 *h = reinterpret_cast<const __half2 *>(&v0);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 f = __half22float2(h[i]), f2 = __half22float2(h2[i]);
-        vf[2 * i] = f.x; vf[2 * i + 1] = f.y; vf[8 + 2 * i] = f2.x; vf[8 + 2 * i + 1] = f2.y;
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      a0[i] = fmaf(a0[i], cr0, e0 * vf[i]);
-      a1[i] = fmaf(a1[i], cr1, e1 * vf[i]);
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(h[i]);
+      a0[2 * i] = fmaf(a0[2 * i], cr0, e0 * f.x);
+      a0[2 * i + 1] = fmaf(a0[2 * i + 1], cr0, e0 * f.y);
+      a1[2 * i] = fmaf(a1[2 * i], cr1, e1 * f.x);
+      a1[2 * i + 1] = fmaf(a1[2 * i + 1], cr1, e1 * f.y);
     }
   }
-  // (3) merge the 4 row groups of the warp (rows differ, dims match for equal `seg`)
+  // (3) merge the 2 row groups of the warp (rows differ, dims match for equal `seg`)
   __syncwarp();
-#pragma unroll
-  for (int o = 8; o <= 16; o <<= 1) {
+  {
+    const int o = 16;
     const float om0 = __shfl_xor_sync(0xffffffffu, m0, o), om1 = __shfl_xor_sync(0xffffffffu, m1, o);
     const float ol0 = __shfl_xor_sync(0xffffffffu, l0, o), ol1 = __shfl_xor_sync(0xffffffffu, l1, o);
     const float n0 = fmaxf(m0, om0), n1 = fmaxf(m1, om1);
@@ -612,7 +686,7 @@ __device__ void attention_phase(const Params &P, Ctx &c, const LayerW &lw, int l
     l0 = l0 * sa0 + ol0 * sb0;
     l1 = l1 * sa1 + ol1 * sb1;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
+    for (int i = 0; i < 8; ++i) {
       const float oa0 = __shfl_xor_sync(0xffffffffu, a0[i], o), oa1 = __shfl_xor_sync(0xffffffffu, a1[i], o);
       a0[i] = a0[i] * sa0 + oa0 * sb0;
       a1[i] = a1[i] * sa1 + oa1 * sb1;
@@ -620,30 +694,30 @@ __device__ void attention_phase(const Params &P, Ctx &c, const LayerW &lw, int l
     m0 = n0; m1 = n1;
   }
   if (grp == 0) {
-    float *w0 = c.s_wpart + (c.warp * 2 + 0) * PART_STRIDE, *w1 = c.s_wpart + (c.warp * 2 + 1) * PART_STRIDE;
+    float *w0 = s_wpart + (c.warp * 2 + 0) * PART_STRIDE, *w1 = s_wpart + (c.warp * 2 + 1) * PART_STRIDE;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) { w0[seg * 16 + i] = a0[i]; w1[seg * 16 + i] = a1[i]; }
+    for (int i = 0; i < 8; ++i) { w0[seg * 8 + i] = a0[i]; w1[seg * 8 + i] = a1[i]; }
     if (seg == 0) { w0[D] = m0; w0[D + 1] = l0; w1[D] = m1; w1[D + 1] = l1; }
   }
   cons_sync();
   // (4) merge the 16 warps (+ the new row) per (head, dim)
   if (c.tid < 2 * D) {
     const int h = c.tid >> 7, d = c.tid & (D - 1);
-    float M = owner ? c.s_misc[h] : -INFINITY;
-    for (int w = 0; w < CONS_WARPS; ++w) M = fmaxf(M, c.s_wpart[(w * 2 + h) * PART_STRIDE + D]);
+    float M = owner ? s_misc[h] : -INFINITY;
+    for (int w = 0; w < CONS_WARPS; ++w) M = fmaxf(M, s_wpart[(w * 2 + h) * PART_STRIDE + D]);
     float L = 0.f, A = 0.f;
     if (M != -INFINITY) {
       for (int w = 0; w < CONS_WARPS; ++w) {
-        const float *wp = c.s_wpart + (w * 2 + h) * PART_STRIDE;
+        const float *wp = s_wpart + (w * 2 + h) * PART_STRIDE;
         const float mw = wp[D];
         const float sc = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
         L = fmaf(wp[D + 1], sc, L);
         A = fmaf(wp[d], sc, A);
       }
       if (owner) {
-        const float sc = exp2f(c.s_misc[h] - M);
+        const float sc = exp2f(s_misc[h] - M);
         L += sc;
-        A = fmaf(c.s_vnew[d], sc, A);
+        A = fmaf(s_vnew[d], sc, A);
       }
     }
     const int hq = 2 * g + h;
@@ -659,7 +733,7 @@ __device__ void attention_phase(const Params &P, Ctx &c, const LayerW &lw, int l
   // the row before the exchange words this CTA publishes later; readers fence once per step.
   if (owner && (c.warp == 2 || c.warp == 3)) {
     __half *cache = ((c.warp == 2) ? P.k_cache : P.v_cache) + head_base + static_cast<size_t>(pos) * D;
-    const float *snew = (c.warp == 2) ? c.s_knew : c.s_vnew;
+    const float *snew = (c.warp == 2) ? s_knew : s_vnew;
 #pragma unroll
     for (int i = 0; i < 4; ++i) cache[c.lane + 32 * i] = __float2half_rn(snew[c.lane + 32 * i]);
     __threadfence();
@@ -667,17 +741,17 @@ __device__ void attention_phase(const Params &P, Ctx &c, const LayerW &lw, int l
 }
 
 // Combines the S partials of each attention output element this CTA owns (S > 1 only).
-__device__ void attention_merge(const Params &P, Ctx &c, int S, uint32_t tag) {
-  int e0, e1;
-  split_rows(QS, c.ncta, c.cta, e0, e1);
+__device__ __forceinline__ void attention_merge(const Params &P, const Ctx &c, int S, uint32_t tag) {
+  const int e0 = c.segs()->e0, e1 = c.segs()->e1;
+#pragma unroll 1
   for (int e = e0 + c.warp; e < e1; e += CONS_WARPS) {
     const int hq = e >> 7, d = e & (D - 1);
     float a = 0.f, m = -INFINITY, l = 0.f;
     if (c.lane < S) {
       const unsigned long long *part = P.ll + LL_PART + static_cast<size_t>(hq * MAX_SPLITS + c.lane) * PART_STRIDE;
-      a = ll_wait(part + d, tag, c);
-      m = ll_wait(part + D, tag, c);
-      l = ll_wait(part + D + 1, tag, c);
+      a = ll_wait(P, c, part + d, tag);
+      m = ll_wait(P, c, part + D, tag);
+      l = ll_wait(P, c, part + D + 1, tag);
     }
     const float M = warp_max(m);
     const float sc = (m == -INFINITY) ? 0.f : exp2f(m - M);
@@ -687,31 +761,16 @@ __device__ void attention_merge(const Params &P, Ctx &c, int S, uint32_t tag) {
 }
 
 // ----------------------------------------------------------------------------- the kernel
-constexpr size_t SMEM_RING = static_cast<size_t>(NSLOTS) * SLOT_BYTES;
-constexpr size_t SMEM_FLOATS = H + H + I + 32 + 2 * D + D + D + CONS_WARPS * 2 * PART_STRIDE + 2 * (D / 2) + 2 * MAX_CTAS + 64;
-constexpr size_t SMEM_BYTES = SMEM_RING + SMEM_FLOATS * 4 + 2 * NSLOTS * 8 + 64;
+#define QMK_STAMP(slot)                                                                           \
+  do {                                                                                            \
+    if (P.prof && c.tid == 0 && step == P.num_steps - 1)                                          \
+      P.prof[static_cast<size_t>(c.cta) * PROF_STRIDE + (slot)] = now_ns();                       \
+  } while (0)
 
 __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __grid_constant__ Params P) {
   extern __shared__ __align__(128) unsigned char smem[];
   Ctx c;
-  c.ring = smem;
-  float *f = reinterpret_cast<float *>(smem + SMEM_RING);
-  c.s_x = f;            f += H;
-  c.s_x1 = f;           f += H;
-  c.s_vec = f;          f += I;
-  c.s_red = f;          f += 32;
-  c.s_q = f;            f += 2 * D;
-  c.s_knew = f;         f += D;
-  c.s_vnew = f;         f += D;
-  c.s_wpart = f;        f += CONS_WARPS * 2 * PART_STRIDE;
-  c.s_cs = f;           f += 2 * (D / 2);
-  float *s_amax = f;    f += 2 * MAX_CTAS;
-  c.s_misc = f;         f += 64;   // [0,1] new-row scores, [16] token, [32..47]/[48..63] warp argmax
-  c.full = reinterpret_cast<uint64_t *>(f);
-  c.empty = c.full + NSLOTS;
-  c.s_flags = reinterpret_cast<volatile int *>(c.empty + NSLOTS);
-  c.status = P.status;
-  c.timeout_ns = P.timeout_ns;
+  c.smem = smem;
   c.tid = threadIdx.x;
   c.warp = threadIdx.x >> 5;
   c.lane = threadIdx.x & 31;
@@ -720,9 +779,16 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
   c.chunk = 0;
 
   if (c.tid == 0) {
-    for (int i = 0; i < NSLOTS; ++i) { mbar_init(c.full + i, 1); mbar_init(c.empty + i, CONS_WARPS); }
-    c.s_flags[0] = 0; c.s_flags[1] = 0; c.s_flags[2] = 0; c.s_flags[3] = 0;
+    for (int i = 0; i < NSLOTS; ++i) { mbar_init(c.full(i), 1); mbar_init(c.empty(i), EMPTY_UNITS); }
+    volatile int *fl = c.flags();
+    fl[0] = 0; fl[1] = 0; fl[2] = 0; fl[3] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (c.tid == 32) build_segtab(reinterpret_cast<SegTab *>(smem + OFF_SEGS), c.cta, c.ncta, P.vocab);
+  {  // layer pointer table -> shared memory (12 pointers per layer)
+    const unsigned long long *src = reinterpret_cast<const unsigned long long *>(P.layers);
+    unsigned long long *dst = reinterpret_cast<unsigned long long *>(smem + OFF_LAYERS);
+    for (int i = c.tid; i < P.num_layers * 12; i += THREADS) dst[i] = src[i];
   }
   __syncthreads();
 
@@ -730,24 +796,29 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
     if (c.lane == 0) producer_main(P, c);
     __syncwarp();   // the warp meets the block barrier below as a whole
   } else {
+    float *s_x = c.f(F_X), *s_x1 = c.f(F_X1), *s_vec = c.f(F_VEC), *s_misc = c.f(F_MISC), *s_amax = c.f(F_AMAX);
     const int S_max = min(MAX_SPLITS, max(1, c.ncta / NKV));
     int token = P.prefill ? P.token_ids[0] : P.first_token;
-    LayerW none{};
+    float a[32];
+    float best = 0.f;
+    int best_i = 0;
+#pragma unroll 1
     for (int step = 0; step < P.num_steps; ++step) {
       const int pos = P.start_position + step;
       const uint32_t tag_base = (P.seq_base + static_cast<uint32_t>(step)) * 64u;
-      if (token < 0 || token >= P.vocab) { if (c.tid == 0) raise_error(c, QMK_ERR_BAD_TOKEN, WHERE_TOKEN); token = 0; }
+      if (token < 0 || token >= P.vocab) { if (c.tid == 0) raise_error(P, c, QMK_ERR_BAD_TOKEN, WHERE_TOKEN); token = 0; }
       // cos/sin of this position (fp32 angles, or the caller's fp16 table row)
       if (c.tid < D / 2) {
         float cs, sn;
         if (P.rope_from_table) {
           cs = __half2float(P.cos_table[static_cast<size_t>(pos) * D + c.tid]);
           sn = __half2float(P.sin_table[static_cast<size_t>(pos) * D + c.tid]);
-        } else {
-          sincosf(static_cast<float>(pos) * c_inv_freq[c.tid], &sn, &cs);
+        } else {   // fp32 table (sincosf's large-argument path would put a stack frame into this kernel)
+          cs = __ldg(P.rope + static_cast<size_t>(pos) * D + c.tid);
+          sn = __ldg(P.rope + static_cast<size_t>(pos) * D + 64 + c.tid);
         }
-        c.s_cs[c.tid] = cs;
-        c.s_cs[64 + c.tid] = sn;
+        c.f(F_CS)[c.tid] = cs;
+        c.f(F_CS)[64 + c.tid] = sn;
       }
       __threadfence();  // acquire side of the KV-row ordering (rows written in earlier steps)
       int S = pos / max(1, P.split_len);
@@ -757,154 +828,161 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
       {
         const __half *row = P.embed + static_cast<size_t>(token) * H;
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const float v = __half2float(__ldg(row + c.tid + j * CONS_THREADS));
-          c.s_x[c.tid + j * CONS_THREADS] = v;
-          ss = fmaf(v, v, ss);
-        }
+        for (int j = 0; j < (H + CONS_THREADS - 1) / CONS_THREADS; ++j)
+          if (c.tid + j * CONS_THREADS < H) {
+            const float v = __half2float(__ldg(row + c.tid + j * CONS_THREADS));
+            s_x[c.tid + j * CONS_THREADS] = v;
+            ss = fmaf(v, v, ss);
+          }
       }
+#pragma unroll 1
       for (int layer = 0; layer < P.num_layers; ++layer) {
-        const LayerW lw = P.layers[layer];
+        const unsigned long long *rec = c.layer_rec(layer);
         const uint32_t tag = tag_base + static_cast<uint32_t>(layer) + 1u;
-        uint4 wn[4];
-        float a[32];
         // P1: input RMSNorm + fused QKV rows
-        load_norm_w(lw.in_ln, c.lane, wn);
-        norm_to_regs(c, c.s_x, ss, wn, a);
-        consume_phase<PH_QKV>(c, lw, nullptr, 0, [&](const unsigned char *row, const unsigned char *, int out) {
-          const float v = row_dot_regs(row, a, c.lane);
-          if (c.lane == 0) ll_store(P.ll + LL_QKV + out, v, tag);
-        });
+        QMK_STAMP(layer * 12 + 0);
+        norm_to_regs(c, s_x, ss, reinterpret_cast<const __half *>(rec[REC_IN_LN]), a);
+        gemv_rows<K_QKV>(P, c, a, nullptr, nullptr, P.ll + LL_QKV, tag, best, best_i, nullptr);
         // P2/P3: attention work items, then merge of split partials
-        attention_phase(P, c, lw, layer, pos, S, tag);
+        QMK_STAMP(layer * 12 + 1);
+        attention_phase(P, c, rec, layer, pos, S, tag);
+        QMK_STAMP(layer * 12 + 2);
         if (S > 1) attention_merge(P, c, S, tag);
+        QMK_STAMP(layer * 12 + 3);
         // P4: O-proj + residual
-        poll_vec<QS>(P.ll + LL_ATTN, tag, c.s_vec, c);
-        load_norm_w(lw.post_ln, c.lane, wn);
+        poll_vec<QS>(P, c, P.ll + LL_ATTN, tag, s_vec);
+        QMK_STAMP(layer * 12 + 4);
         cons_sync();
-        consume_phase<PH_O>(c, lw, nullptr, 0, [&](const unsigned char *row, const unsigned char *, int out) {
-          const float v = row_dot_smem<QS>(row, c.s_vec, c.lane) + c.s_x[out];
-          if (c.lane == 0) ll_store(P.ll + LL_X1 + out, v, tag);
-        });
+        gemv_rows<K_O>(P, c, a, s_vec, s_x, P.ll + LL_X1, tag, best, best_i, nullptr);
         // P5: post-attention RMSNorm + gate/up + SwiGLU
-        ss = poll_vec<H>(P.ll + LL_X1, tag, c.s_x1, c);
-        norm_to_regs(c, c.s_x1, ss, wn, a);
-        consume_phase<PH_GU>(c, lw, nullptr, 0, [&](const unsigned char *grow, const unsigned char *urow, int out) {
-          const float gv = row_dot_regs(grow, a, c.lane);
-          const float uv = row_dot_regs(urow, a, c.lane);
-          if (c.lane == 0) ll_store(P.ll + LL_INTER + out, gv / (1.0f + expf(-gv)) * uv, tag);
-        });
+        QMK_STAMP(layer * 12 + 5);
+        ss = poll_vec<H>(P, c, P.ll + LL_X1, tag, s_x1);
+        QMK_STAMP(layer * 12 + 6);
+        norm_to_regs(c, s_x1, ss, reinterpret_cast<const __half *>(rec[REC_POST_LN]), a);
+        gemv_rows<K_GU>(P, c, a, nullptr, nullptr, P.ll + LL_INTER, tag, best, best_i, nullptr);
         // P6: down-proj + residual
-        poll_vec<I>(P.ll + LL_INTER, tag, c.s_vec, c);
+        QMK_STAMP(layer * 12 + 7);
+        poll_vec<I>(P, c, P.ll + LL_INTER, tag, s_vec);
+        QMK_STAMP(layer * 12 + 8);
         cons_sync();
-        consume_phase<PH_DOWN>(c, lw, nullptr, 0, [&](const unsigned char *row, const unsigned char *, int out) {
-          const float v = row_dot_smem<I>(row, c.s_vec, c.lane) + c.s_x1[out];
-          if (c.lane == 0) ll_store(P.ll + LL_X2 + out, v, tag);
-        });
+        gemv_rows<K_DOWN>(P, c, a, s_vec, s_x1, P.ll + LL_X2, tag, best, best_i, nullptr);
         // next layer's input (in prefill mode the last layer's output is not needed)
-        if (!(P.prefill && layer == P.num_layers - 1)) ss = poll_vec<H>(P.ll + LL_X2, tag, c.s_x, c);
-        if (cons_any(c.s_flags[0] != 0)) break;
+        QMK_STAMP(layer * 12 + 9);
+        if (!(P.prefill && layer == P.num_layers - 1)) ss = poll_vec<H>(P, c, P.ll + LL_X2, tag, s_x);
+        QMK_STAMP(layer * 12 + 10);
+        if (cons_any(c.flags()[0] != 0)) break;
       }
-      if (cons_any(c.s_flags[0] != 0)) break;
+      if (cons_any(c.flags()[0] != 0)) break;
       if (P.prefill) {
         if (step + 1 < P.num_steps) token = P.token_ids[step + 1];
         continue;
       }
       // final RMSNorm + tied LM head + argmax (megakernel_5090.cu:921-947, 1024-1167)
-      {
-        uint4 wn[4];
-        float a[32];
-        load_norm_w(P.final_norm, c.lane, wn);
-        norm_to_regs(c, c.s_x, ss, wn, a);
-        if (c.cta == 0 && c.warp == 0) {
+      QMK_STAMP(P.num_layers * 12 + 0);
+      norm_to_regs(c, s_x, ss, P.final_norm, a);
+      if (c.cta == 0 && c.warp == 0 && (P.normalized_out || P.hidden_out)) {  // reference-signature output buffers
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < 4; ++j)
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              if (P.normalized_out) P.normalized_out[j * 256 + c.lane * 8 + i] = a[j * 8 + i];
-              if (P.hidden_out) P.hidden_out[j * 256 + c.lane * 8 + i] = __float2half_rn(c.s_x[j * 256 + c.lane * 8 + i]);
-            }
-        }
-        float best = -INFINITY;
-        int best_i = 0x7fffffff;
-        float *dump = P.logits_out ? P.logits_out + static_cast<size_t>(step) * P.vocab : nullptr;
-        consume_phase<PH_LM>(c, none, P.lm_head, P.vocab, [&](const unsigned char *row, const unsigned char *, int out) {
-          const float v = row_dot_regs(row, a, c.lane);
-          if (v > best || (v == best && out < best_i)) { best = v; best_i = out; }
-          if (dump && c.lane == 0) dump[out] = v;
-        });
-        if (c.lane == 0) { c.s_misc[32 + c.warp] = best; c.s_misc[48 + c.warp] = __int_as_float(best_i); }
-        cons_sync();
-        const uint32_t atag = tag_base + 63u;
-        if (c.tid == 0) {
-          for (int w = 1; w < CONS_WARPS; ++w) {
-            const float v = c.s_misc[32 + w];
-            const int vi = __float_as_int(c.s_misc[48 + w]);
-            if (v > best || (v == best && vi < best_i)) { best = v; best_i = vi; }
+          for (int i = 0; i < 8; ++i) {
+            const int k = j * 256 + c.lane * 8 + i;
+            if (P.normalized_out) P.normalized_out[k] = a[j * 8 + i];
+            if (P.hidden_out) P.hidden_out[k] = __float2half_rn(s_x[k]);
           }
-          ll_store(P.ll + LL_AMAX + 2 * c.cta, best, atag);
-          ll_store(P.ll + LL_AMAX + 2 * c.cta + 1, __int_as_float(best_i), atag);
-          if (P.bmax_vals) P.bmax_vals[c.cta] = best;
-          if (P.bmax_idxs) P.bmax_idxs[c.cta] = best_i;
-        }
-        if (c.tid < 2 * c.ncta) s_amax[c.tid] = ll_wait(P.ll + LL_AMAX + c.tid, atag, c);
-        cons_sync();
-        if (c.warp == 0) {
-          float bv = -INFINITY;
-          int bi = 0x7fffffff;
-          for (int k = c.lane; k < c.ncta; k += 32) {
-            const float v = s_amax[2 * k];
-            const int vi = __float_as_int(s_amax[2 * k + 1]);
-            if (v > bv || (v == bv && vi < bi)) { bv = v; bi = vi; }
-          }
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-          }
-          if (c.lane == 0) c.s_misc[16] = __int_as_float(bi);
-        }
-        const bool aborted = cons_any(c.s_flags[0] != 0);
-        token = __float_as_int(c.s_misc[16]);
-        if (aborted) break;
-        if (c.cta == 0 && c.tid == 0) {
-          if (P.output_log) P.output_log[step] = token;   // the EOS token is logged too (megakernel_5090.cu:785-787)
-          if (P.output_token) *P.output_token = token;
-        }
-        if (token == P.eos) break;
       }
+      best = -INFINITY;
+      best_i = 0x7fffffff;
+      gemv_rows<K_LM>(P, c, a, nullptr, nullptr, nullptr, 0u, best, best_i,
+                      P.logits_out ? P.logits_out + static_cast<size_t>(step) * P.vocab : nullptr);
+      QMK_STAMP(P.num_layers * 12 + 1);
+      if (c.lane == 0) { s_misc[32 + c.warp] = best; s_misc[48 + c.warp] = __int_as_float(best_i); }
+      cons_sync();
+      const uint32_t atag = tag_base + 63u;
+      if (c.tid == 0) {
+#pragma unroll 1
+        for (int w = 1; w < CONS_WARPS; ++w) {
+          const float v = s_misc[32 + w];
+          const int vi = __float_as_int(s_misc[48 + w]);
+          if (v > best || (v == best && vi < best_i)) { best = v; best_i = vi; }
+        }
+        ll_store(P.ll + LL_AMAX + 2 * c.cta, best, atag);
+        ll_store(P.ll + LL_AMAX + 2 * c.cta + 1, __int_as_float(best_i), atag);
+        if (P.bmax_vals) P.bmax_vals[c.cta] = best;
+        if (P.bmax_idxs) P.bmax_idxs[c.cta] = best_i;
+      }
+#pragma unroll 1
+      for (int i = c.tid; i < 2 * c.ncta; i += CONS_THREADS) s_amax[i] = ll_wait(P, c, P.ll + LL_AMAX + i, atag);
+      cons_sync();
+      if (c.warp == 0) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+#pragma unroll 1
+        for (int k = c.lane; k < c.ncta; k += 32) {
+          const float v = s_amax[2 * k];
+          const int vi = __float_as_int(s_amax[2 * k + 1]);
+          if (v > bv || (v == bv && vi < bi)) { bv = v; bi = vi; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+          const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+          if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (c.lane == 0) s_misc[16] = __int_as_float(bi);
+      }
+      const bool aborted = cons_any(c.flags()[0] != 0);
+      QMK_STAMP(P.num_layers * 12 + 2);
+      token = __float_as_int(s_misc[16]);
+      if (aborted) break;
+      if (c.cta == 0 && c.tid == 0) {
+        if (P.output_log) P.output_log[step] = token;   // the EOS token is logged too (megakernel_5090.cu:785-787)
+        if (P.output_token) *P.output_token = token;
+      }
+      if (token == P.eos) break;
     }
-    if (c.tid == 0) { c.s_flags[3] = static_cast<int>(c.chunk); c.s_flags[1] = 1; }
+    if (c.tid == 0) { c.flags()[3] = static_cast<int>(c.chunk); c.flags()[1] = 1; }
   }
   __syncthreads();
   // Bulk copies issued but never consumed (early stop, abort) must land before the CTA exits.
   if (c.tid == CONS_THREADS) {
     // Every slot's latest fill is checked (already-landed phases answer at once), so this also
     // covers chunks the consumers skipped after an abort.
-    const uint32_t issued = static_cast<uint32_t>(c.s_flags[2]);
+    const uint32_t issued = static_cast<uint32_t>(c.flags()[2]);
+#pragma unroll 1
     for (uint32_t i = (issued > NSLOTS ? issued - NSLOTS : 0u); i < issued; ++i) {
-      uint64_t *bar = c.full + (i % NSLOTS);
+      uint64_t *bar = c.full(i % NSLOTS);
       const uint32_t parity = (i / NSLOTS) & 1u;
       const unsigned long long t0 = now_ns();
       while (!mbar_try_wait(bar, parity)) {
-        if (now_ns() - t0 > c.timeout_ns) { raise_error(c, QMK_ERR_WAIT_TIMEOUT, WHERE_DRAIN); break; }
+        if (now_ns() - t0 > P.timeout_ns) { raise_error(P, c, QMK_ERR_WAIT_TIMEOUT, WHERE_DRAIN); break; }
       }
     }
   }
 }
 
+// fp32 rotary factors for positions [0, n): angle = float(pos) * inv_freq[i], as the oracle computes them.
+__global__ void rope_table_kernel(float *table, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n * (D / 2)) return;
+  const int pos = i / (D / 2), f = i % (D / 2);
+  float sn, cs;
+  sincosf(static_cast<float>(pos) * c_inv_freq[f], &sn, &cs);
+  table[static_cast<size_t>(pos) * D + f] = cs;
+  table[static_cast<size_t>(pos) * D + 64 + f] = sn;
+}
+
 // Bounded-wait self test: waits for a tag nothing writes.
-__global__ void wait_timeout_probe(unsigned long long *word, unsigned int *status, unsigned long long budget_ns) {
-  __shared__ int flags[4];
+__global__ void wait_timeout_probe(const __grid_constant__ Params P, unsigned long long *word) {
+  extern __shared__ __align__(128) unsigned char smem[];
   if (threadIdx.x == 0) {
-    flags[0] = 0;
-    Ctx c{};
-    c.s_flags = flags;
-    c.status = status;
-    c.timeout_ns = budget_ns;
+    Ctx c;
+    c.smem = smem;
+    c.tid = c.warp = c.lane = 0;
     c.cta = blockIdx.x;
-    ll_wait(word, 0xfffffff0u, c);
+    c.ncta = gridDim.x;
+    c.chunk = 0;
+    c.flags()[0] = 0;
+    ll_wait(P, c, word, 0xfffffff0u);
   }
 }
 
@@ -925,6 +1003,8 @@ struct Engine {
   unsigned int *status_host = nullptr;  // pinned
   int *tok_dev = nullptr;
   int tok_cap = 0;
+  float *rope = nullptr;   // fp32 rotary table for positions [0, rope_cap)
+  int rope_cap = 0;
   uint32_t seq = 0;
   int last_status = 0;
   std::string last_error;
@@ -935,6 +1015,9 @@ struct Engine {
   int max_ctas = 0;
   int timeout_ms = 2000;
   float *logits_out = nullptr;
+  unsigned long long *prof = nullptr;
+  int spin_sleep_ns = 0;
+  int l2_evict_first = 1;
   bool inv_freq_set = false;
 };
 
@@ -976,6 +1059,8 @@ int ensure_ready(Engine *e) {
   e->num_sms = prop.multiProcessorCount;
   QMK_CUDA(e, cudaFuncSetAttribute(qmk::qwen3_decode_megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(qmk::SMEM_BYTES)));
+  QMK_CUDA(e, cudaFuncSetAttribute(qmk::wait_timeout_probe, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(qmk::SMEM_BYTES)));
   int per_sm = 0;
   QMK_CUDA(e, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, qmk::qwen3_decode_megakernel, qmk::THREADS,
                                                             qmk::SMEM_BYTES));
@@ -1014,7 +1099,8 @@ int launch(Engine *e, Params &P, cudaStream_t stream, bool synchronize) {
   if (!aligned16(P.embed) || !aligned16(P.layers) || !aligned16(P.k_cache) || !aligned16(P.v_cache) ||
       (P.lm_head && !aligned16(P.lm_head)))
     return fail(e, QMK_ERR_BAD_ARGUMENT, "weight, cache and layer-table pointers must be 16-byte aligned");
-  if (P.num_layers < 1 || P.num_layers > 60) return fail(e, QMK_ERR_BAD_ARGUMENT, "num_layers must be in [1, 60]");
+  if (P.num_layers < 1 || P.num_layers > qmk::MAX_LAYERS)
+    return fail(e, QMK_ERR_BAD_ARGUMENT, "num_layers must be in [1, 48]");
   if (P.start_position < 0 || P.start_position + P.num_steps > P.max_seq_len)
     return fail(e, QMK_ERR_POSITION, "start_position + steps exceeds max_seq_len");
   if (e->rope_from_table && (!P.cos_table || !P.sin_table))
@@ -1027,6 +1113,18 @@ int launch(Engine *e, Params &P, cudaStream_t stream, bool synchronize) {
     QMK_CUDA(e, cudaMemsetAsync(e->ll, 0, sizeof(unsigned long long) * qmk::LL_WORDS, stream));
     e->seq = 0;
   }
+  if (!e->rope_from_table && P.max_seq_len > e->rope_cap) {   // grow-only, like the token staging buffer
+    if (e->rope) cudaFree(e->rope);
+    e->rope = nullptr;
+    e->rope_cap = 0;
+    int cap = 2048;
+    while (cap < P.max_seq_len) cap *= 2;
+    QMK_CUDA(e, cudaMalloc(&e->rope, sizeof(float) * qmk::D * cap));
+    qmk::rope_table_kernel<<<(cap * (qmk::D / 2) + 255) / 256, 256, 0, stream>>>(e->rope, cap);
+    QMK_CUDA(e, cudaGetLastError());
+    e->rope_cap = cap;
+  }
+  P.rope = e->rope;
   QMK_CUDA(e, cudaMemsetAsync(e->status, 0, 16, stream));
   P.ll = e->ll;
   P.status = e->status;
@@ -1036,6 +1134,9 @@ int launch(Engine *e, Params &P, cudaStream_t stream, bool synchronize) {
   P.split_len = e->split_len;
   P.timeout_ns = static_cast<unsigned long long>(e->timeout_ms) * 1000000ull;
   P.logits_out = P.prefill ? nullptr : e->logits_out;
+  P.prof = e->prof;
+  P.spin_sleep_ns = e->spin_sleep_ns;
+  P.l2_evict_first = e->l2_evict_first;
   e->seq += static_cast<uint32_t>(P.num_steps);
 
   void *args[] = {&P};
@@ -1105,8 +1206,10 @@ int qmk_set_inv_freq(const float *inv_freq64) {
   std::lock_guard<std::mutex> lock(g_mutex);
   Engine *e = current_engine_unlocked();
   if (!e || !inv_freq64) return QMK_ERR_BAD_ARGUMENT;
+  QMK_CUDA(e, cudaDeviceSynchronize());   // no launch may still be reading the old table
   QMK_CUDA(e, cudaMemcpyToSymbol(qmk::c_inv_freq, inv_freq64, sizeof(float) * (qmk::D / 2)));
   e->inv_freq_set = true;
+  e->rope_cap = 0;   // rebuilt with the new frequencies at the next launch
   return QMK_OK;
 }
 
@@ -1115,6 +1218,23 @@ int qmk_set_logits_dump(float *logits_out) {
   Engine *e = current_engine_unlocked();
   if (!e) return QMK_ERR_CUDA;
   e->logits_out = logits_out;
+  return QMK_OK;
+}
+
+int qmk_set_tuning(int spin_sleep_ns, int l2_evict_first) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  Engine *e = current_engine_unlocked();
+  if (!e) return QMK_ERR_CUDA;
+  if (spin_sleep_ns >= 0) e->spin_sleep_ns = spin_sleep_ns > 10000 ? 10000 : spin_sleep_ns;
+  if (l2_evict_first >= 0) e->l2_evict_first = l2_evict_first ? 1 : 0;
+  return QMK_OK;
+}
+
+int qmk_set_profile_buffer(unsigned long long *timestamps) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  Engine *e = current_engine_unlocked();
+  if (!e) return QMK_ERR_CUDA;
+  e->prof = timestamps;
   return QMK_OK;
 }
 
@@ -1232,7 +1352,11 @@ int qmk_selftest_wait_timeout(int budget_us) {
   if (rc != QMK_OK) return rc;
   if (budget_us < 1 || budget_us > 1000000) return fail(e, QMK_ERR_BAD_ARGUMENT, "budget_us must be in [1, 1e6]");
   QMK_CUDA(e, cudaMemset(e->status, 0, 16));
-  qmk::wait_timeout_probe<<<1, 32>>>(e->ll + qmk::LL_AMAX, e->status, static_cast<unsigned long long>(budget_us) * 1000ull);
+  Params P;
+  memset(&P, 0, sizeof(P));
+  P.status = e->status;
+  P.timeout_ns = static_cast<unsigned long long>(budget_us) * 1000ull;
+  qmk::wait_timeout_probe<<<1, 32, qmk::SMEM_BYTES>>>(P, e->ll + qmk::LL_AMAX);
   QMK_CUDA(e, cudaGetLastError());
   QMK_CUDA(e, cudaDeviceSynchronize());
   QMK_CUDA(e, cudaMemcpy(e->status_host, e->status, 16, cudaMemcpyDeviceToHost));

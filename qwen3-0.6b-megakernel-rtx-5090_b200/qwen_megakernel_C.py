@@ -48,6 +48,10 @@ _lib.qmk_set_inv_freq.argtypes = [_P]
 _lib.qmk_set_inv_freq.restype = _I
 _lib.qmk_set_logits_dump.argtypes = [_P]
 _lib.qmk_set_logits_dump.restype = _I
+_lib.qmk_set_tuning.argtypes = [_I, _I]
+_lib.qmk_set_tuning.restype = _I
+_lib.qmk_set_profile_buffer.argtypes = [_P]
+_lib.qmk_set_profile_buffer.restype = _I
 _lib.qmk_decode.argtypes = [_I, _P, *([_P] * 12), _I, _I, _I, _F, _P]
 _lib.qmk_decode.restype = _I
 _lib.qmk_generate.argtypes = [_I, _I, *([_P] * 12), _P, _I, _I, _I, _F, _I, _I, _P]
@@ -64,7 +68,7 @@ _lib.qmk_selftest_wait_timeout.restype = _I
 EXPORTED_SYMBOLS = (
     "launch_ldg_decode_direct", "launch_ldg_decode_persistent", "launch_ldg_generate_nosync",
     "launch_ldg_prefill", "qmk_abi_version", "qmk_configure", "qmk_set_inv_freq", "qmk_set_logits_dump",
-    "qmk_decode", "qmk_generate", "qmk_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
+    "qmk_set_tuning", "qmk_set_profile_buffer", "qmk_decode", "qmk_generate", "qmk_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
     "qmk_scratch_bytes", "qmk_selftest_wait_timeout",
 )
 
@@ -190,6 +194,23 @@ def set_logits_dump(buf) -> None:
         _check(buf.is_cuda and buf.dtype == torch.float32 and buf.is_contiguous(),
                "logits dump must be a contiguous fp32 CUDA tensor")
     _lib.qmk_set_logits_dump(_ptr(buf))
+
+
+def set_tuning(spin_sleep_ns=-1, l2_evict_first=-1) -> None:
+    """Performance knobs (see include/qwen_megakernel.h); negative keeps a value."""
+    _check(_lib.qmk_set_tuning(int(spin_sleep_ns), int(l2_evict_first)) == 0, "set_tuning failed")
+
+
+PROFILE_STRIDE = 768
+
+
+def set_profile_buffer(buf) -> None:
+    """int64 CUDA tensor ``[grid, 768]`` receiving per-CTA phase timestamps (ns) of the last step
+    of each launch (slot map: include/qwen_megakernel.h), or None."""
+    if buf is not None:
+        _check(buf.is_cuda and buf.dtype == torch.int64 and buf.is_contiguous(),
+               "profile buffer must be a contiguous int64 CUDA tensor")
+    _lib.qmk_set_profile_buffer(_ptr(buf))
 
 
 def sync_status() -> int:
