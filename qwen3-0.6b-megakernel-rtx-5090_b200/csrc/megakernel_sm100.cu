@@ -362,6 +362,24 @@ __device__ __forceinline__ const unsigned char *seg_src(const SegTab *t, int kin
   return reinterpret_cast<const unsigned char *>(base) + static_cast<size_t>(t->row0[kind][s]) * kind_row_bytes(kind);
 }
 
+// Attention work item of this CTA at position `pos`: kv head g, split s of S, old cache rows [p0, p1).
+// Both the producer (to stream the rows) and the consumers (to use them) call this.
+constexpr int KV_ROWS_PER_CHUNK = 16;   // 16 K rows (4 KB) + 16 V rows (4 KB) per ring slot
+struct AttnItem { int S, g, s, p0, p1, nchunks; bool active; };
+__device__ __forceinline__ AttnItem attn_item(const Params &P, const Ctx &c, int pos) {
+  AttnItem it;
+  const int S_max = min(MAX_SPLITS, max(1, c.ncta / NKV));
+  it.S = max(1, min(pos / max(1, P.split_len), S_max));
+  it.active = c.cta < NKV * it.S;
+  it.g = c.cta % NKV;
+  it.s = c.cta / NKV;
+  // old rows [p0, p1) of [0, pos); pos * S < 2^31, 32-bit division
+  it.p0 = it.active ? static_cast<int>(static_cast<unsigned>(pos * it.s) / static_cast<unsigned>(it.S)) : 0;
+  it.p1 = it.active ? static_cast<int>(static_cast<unsigned>(pos * (it.s + 1)) / static_cast<unsigned>(it.S)) : 0;
+  it.nchunks = (it.p1 - it.p0 + KV_ROWS_PER_CHUNK - 1) / KV_ROWS_PER_CHUNK;
+  return it;
+}
+
 // ----------------------------------------------------------------------------- producer (one thread)
 __device__ __forceinline__ bool produce_chunk(const Params &P, const Ctx &c, uint32_t &idx, uint64_t pol,
                                               const unsigned char *src, const unsigned char *src2, uint32_t bytes) {
@@ -411,7 +429,20 @@ __device__ __forceinline__ void producer_main(const Params &P, const Ctx &c) {
         for (int b = 0; b < bytes; b += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(v + b));
       }
 #pragma unroll 1
-      for (int kind = K_QKV; ok && kind <= K_DOWN; ++kind) ok = produce_phase(P, c, idx, pol, kind, rec);
+      ok = produce_phase(P, c, idx, pol, K_QKV, rec);
+      {  // this CTA's range of old K/V rows for the attention phase of this layer
+        const AttnItem it = attn_item(P, c, P.start_position + step);
+        const size_t head_base = (static_cast<size_t>(l) * NKV + it.g) * static_cast<size_t>(P.max_seq_len) * D;
+#pragma unroll 1
+        for (int r = it.p0; ok && r < it.p1; r += KV_ROWS_PER_CHUNK) {
+          const uint32_t bytes = static_cast<uint32_t>(min(KV_ROWS_PER_CHUNK, it.p1 - r)) * D * 2;
+          const size_t off = (head_base + static_cast<size_t>(r) * D) * 2;
+          ok = produce_chunk(P, c, idx, pol, reinterpret_cast<const unsigned char *>(P.k_cache) + off,
+                             reinterpret_cast<const unsigned char *>(P.v_cache) + off, bytes);
+        }
+      }
+#pragma unroll 1
+      for (int kind = K_O; ok && kind <= K_DOWN; ++kind) ok = produce_phase(P, c, idx, pol, kind, rec);
     }
     if (ok && !P.prefill) ok = produce_phase(P, c, idx, pol, K_LM, nullptr);
   }
@@ -568,17 +599,15 @@ __device__ __forceinline__ void gemv_rows(const Params &P, Ctx &c, const float (
 // Work item (kv head g, split s) on CTA g + 8*s: old cache rows [p0, p1); the last split also
 // normalises/rotates/stores the new K,V row and folds it in.  Writes either the final head
 // outputs (one split) or unnormalised partials.
-__device__ __forceinline__ void attention_phase(const Params &P, const Ctx &c, const unsigned long long *rec, int layer, int pos,
-                                                int S, uint32_t tag) {
+__device__ __forceinline__ void attention_phase(const Params &P, Ctx &c, const unsigned long long *rec, int layer, int pos,
+                                                const AttnItem &it, uint32_t tag) {
   float *s_q = c.f(F_Q), *s_knew = c.f(F_KNEW), *s_vnew = c.f(F_VNEW), *s_wpart = c.f(F_WPART), *s_misc = c.f(F_MISC);
   const float *s_cs = c.f(F_CS);
   const unsigned long long *qkv = P.ll + LL_QKV;
-  if (c.cta >= NKV * S) return;
-  const int g = c.cta % NKV, s = c.cta / NKV;
+  if (!it.active) return;
+  const int S = it.S, g = it.g, s = it.s;
   const bool owner = (s == S - 1);
-  // old rows [p0, p1) of [0, pos); pos * S < 2^31, 32-bit division
-  const int p0 = static_cast<int>(static_cast<unsigned>(pos * s) / static_cast<unsigned>(S));
-  const int p1 = static_cast<int>(static_cast<unsigned>(pos * (s + 1)) / static_cast<unsigned>(S));
+  const int p0 = it.p0, p1 = it.p1;
   const size_t head_base = (static_cast<size_t>(layer) * NKV + g) * static_cast<size_t>(P.max_seq_len) * D;
 
   // (1) head preparation: warps 0,1 = the two query heads; owner: warp 2 = K, warp 3 = V
@@ -644,36 +673,47 @@ __device__ __forceinline__ void attention_phase(const Params &P, const Ctx &c, c
   // The two row groups of a warp can run different trip counts: shuffles inside the loop name
   // only the 16 lanes of the group.
   const uint32_t grp_mask = 0xffffu << (grp * 16);
-  const __half *kb = P.k_cache + head_base + seg * 8;
-  const __half *vb = P.v_cache + head_base + seg * 8;
+  // Old rows arrive through the ring in chunks of 16 K rows + 16 V rows; warp w takes chunks
+  // w, w + CONS_WARPS, ... and hands each slot back when done.
+#pragma unroll 1
+  for (int j = c.warp; j < it.nchunks; j += CONS_WARPS) {
+    const uint32_t idx = c.chunk + static_cast<uint32_t>(j);
+    const int nrow = min(KV_ROWS_PER_CHUNK, (p1 - p0) - j * KV_ROWS_PER_CHUNK);
+    if (wait_full(P, c, idx)) {
+      const unsigned char *kslot = c.slot(idx) + seg * 16;
 #pragma unroll 2
-  for (int p = p0 + c.warp * 2 + grp; p < p1; p += CONS_WARPS * 2) {
-    const uint4 k0 = __ldcg(reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(p) * D));
-    const uint4 v0 = __ldcg(reinterpret_cast<const uint4 *>(vb + static_cast<size_t>(p) * D));
-    float d0 = dot8(k0, q0, 0.f), d1 = dot8(k0, q1, 0.f);
+      for (int r = grp; r < nrow; r += 2) {
+        const uint4 k0 = *reinterpret_cast<const uint4 *>(kslot + r * (D * 2));
+        const uint4 v0 = *reinterpret_cast<const uint4 *>(kslot + SLOT_BYTES / 2 + r * (D * 2));
+        float d0 = dot8(k0, q0, 0.f), d1 = dot8(k0, q1, 0.f);
 #pragma unroll
-    for (int o = 1; o < 16; o <<= 1) {
-      d0 += __shfl_xor_sync(grp_mask, d0, o);
-      d1 += __shfl_xor_sync(grp_mask, d1, o);
-    }
-    d0 *= sc_log2;
-    d1 *= sc_log2;
-    const float n0 = fmaxf(m0, d0), n1 = fmaxf(m1, d1);
-    const float cr0 = exp2f(m0 - n0), cr1 = exp2f(m1 - n1);
-    const float e0 = exp2f(d0 - n0), e1 = exp2f(d1 - n1);
-    m0 = n0; m1 = n1;
-    l0 = fmaf(l0, cr0, e0);
-    l1 = fmaf(l1, cr1, e1);
-    const __half2 *h = reinterpret_cast<const __half2 *>(&v0);
+        for (int o = 1; o < 16; o <<= 1) {
+          d0 += __shfl_xor_sync(grp_mask, d0, o);
+          d1 += __shfl_xor_sync(grp_mask, d1, o);
+        }
+        d0 *= sc_log2;
+        d1 *= sc_log2;
+        const float n0 = fmaxf(m0, d0), n1 = fmaxf(m1, d1);
+        const float cr0 = exp2f(m0 - n0), cr1 = exp2f(m1 - n1);
+        const float e0 = exp2f(d0 - n0), e1 = exp2f(d1 - n1);
+        m0 = n0; m1 = n1;
+        l0 = fmaf(l0, cr0, e0);
+        l1 = fmaf(l1, cr1, e1);
+        const __half2 *h = reinterpret_cast<const __half2 *>(&v0);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 f = __half22float2(h[i]);
-      a0[2 * i] = fmaf(a0[2 * i], cr0, e0 * f.x);
-      a0[2 * i + 1] = fmaf(a0[2 * i + 1], cr0, e0 * f.y);
-      a1[2 * i] = fmaf(a1[2 * i], cr1, e1 * f.x);
-      a1[2 * i + 1] = fmaf(a1[2 * i + 1], cr1, e1 * f.y);
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __half22float2(h[i]);
+          a0[2 * i] = fmaf(a0[2 * i], cr0, e0 * f.x);
+          a0[2 * i + 1] = fmaf(a0[2 * i + 1], cr0, e0 * f.y);
+          a1[2 * i] = fmaf(a1[2 * i], cr1, e1 * f.x);
+          a1[2 * i + 1] = fmaf(a1[2 * i + 1], cr1, e1 * f.y);
+        }
+      }
     }
+    __syncwarp();
+    if (c.lane == 0) mbar_arrive_n(c.empty(idx % NSLOTS), EMPTY_UNITS);
   }
+  c.chunk += static_cast<uint32_t>(it.nchunks);
   // (3) merge the 2 row groups of the warp (rows differ, dims match for equal `seg`)
   __syncwarp();
   {
@@ -797,7 +837,6 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
     __syncwarp();   // the warp meets the block barrier below as a whole
   } else {
     float *s_x = c.f(F_X), *s_x1 = c.f(F_X1), *s_vec = c.f(F_VEC), *s_misc = c.f(F_MISC), *s_amax = c.f(F_AMAX);
-    const int S_max = min(MAX_SPLITS, max(1, c.ncta / NKV));
     int token = P.prefill ? P.token_ids[0] : P.first_token;
     float a[32];
     float best = 0.f;
@@ -821,8 +860,7 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
         c.f(F_CS)[64 + c.tid] = sn;
       }
       __threadfence();  // acquire side of the KV-row ordering (rows written in earlier steps)
-      int S = pos / max(1, P.split_len);
-      S = max(1, min(S, S_max));
+      const AttnItem item = attn_item(P, c, pos);
       // embedding row -> fp32 residual stream (megakernel_5090.cu:825-830)
       float ss = 0.f;
       {
@@ -845,9 +883,9 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
         gemv_rows<K_QKV>(P, c, a, nullptr, nullptr, P.ll + LL_QKV, tag, best, best_i, nullptr);
         // P2/P3: attention work items, then merge of split partials
         QMK_STAMP(layer * 12 + 1);
-        attention_phase(P, c, rec, layer, pos, S, tag);
+        attention_phase(P, c, rec, layer, pos, item, tag);
         QMK_STAMP(layer * 12 + 2);
-        if (S > 1) attention_merge(P, c, S, tag);
+        if (item.S > 1) attention_merge(P, c, item.S, tag);
         QMK_STAMP(layer * 12 + 3);
         // P4: O-proj + residual
         poll_vec<QS>(P, c, P.ll + LL_ATTN, tag, s_vec);
