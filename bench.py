@@ -52,9 +52,9 @@ def measured_peak_gbs():
         return 6650.0, "fallback"
 
 
-def step_bytes() -> int:
-    """Algorithmic HBM bytes of one step: sum over its 256 tokens of weights + KV read + KV write."""
-    return sum(S.decode_step_bytes(PROMPT_LEN + i) for i in range(DECODE_TOKENS))
+def step_bytes(prompt_len: int = PROMPT_LEN, decode_tokens: int = DECODE_TOKENS) -> int:
+    """Algorithmic HBM bytes of one step: sum over its tokens of weights + KV read + KV write."""
+    return sum(S.decode_step_bytes(prompt_len + i) for i in range(decode_tokens))
 
 
 class ClockSampler:
@@ -215,6 +215,8 @@ def run_ours(args):
     import qwen_megakernel_C as C
     from Model.Qwen06B_architecture import Decoder
 
+    PROMPT_LEN, DECODE_TOKENS = args.prompt_len, args.decode_tokens   # defaults: the benchmark configuration
+    MAX_SEQ_LEN = PROMPT_LEN + DECODE_TOKENS
     weights = S.weights_to(S.make_weights(seed=0, max_seq_len=16), str(device))
     eng = Decoder(weights=weights, tokenizer=S.StubTokenizer(-1), verbose=False, max_seq_len=MAX_SEQ_LEN,
                   device=str(device))
@@ -277,11 +279,13 @@ def run_ours(args):
 
     peak, peak_kind = measured_peak_gbs()
     avg_launch_s = statistics.mean(launch_ms) / 1e3
-    achieved = step_bytes() / avg_launch_s / 1e9
-    traffic = None
+    achieved = step_bytes(PROMPT_LEN, DECODE_TOKENS) / avg_launch_s / 1e9
+    traffic = None   # DRAM bytes per launch from the committed ncu capture, scaled by tokens per launch
     try:
         with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
-            traffic = json.load(f).get("qwen3_decode_megakernel_bytes_per_launch")
+            per_token = json.load(f).get("qwen3_decode_megakernel_dram_bytes_per_token")
+        if per_token:
+            traffic = per_token * DECODE_TOKENS
     except Exception:
         pass
 
@@ -290,12 +294,14 @@ def run_ours(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": 1e3 * total_s / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "tokens_per_step": DECODE_TOKENS, "replicas": world,
+            "config": {"workload": WORKLOAD if (PROMPT_LEN, DECODE_TOKENS) == (4096, 256) else
+                       f"profiling case: {PROMPT_LEN} prompt tokens, {DECODE_TOKENS} decode tokens per step",
+                       "tokens_per_step": DECODE_TOKENS, "replicas": world,
                        "l2": "no flush needed: each token streams 1.19 GB of weights + 0.47 GB of KV, > 126 MB L2",
                        "grid_ctas": C.num_ctas()},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic, "peak_kind": f"of {peak_kind}",
-                         "bytes_per_launch": step_bytes(), "launch_ms": statistics.mean(launch_ms),
+                         "bytes_per_launch": step_bytes(PROMPT_LEN, DECODE_TOKENS), "launch_ms": statistics.mean(launch_ms),
                          "frac_of_nominal_8TBs": achieved / 8000.0},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4,
                     "d2h_bytes_per_step": 4 * DECODE_TOKENS},
@@ -324,6 +330,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle leg (profiling runs)")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prefilled context (default: benchmark config)")
+    ap.add_argument("--decode-tokens", type=int, default=DECODE_TOKENS,
+                    help="greedy tokens per step (default: benchmark config; smaller for ncu captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
