@@ -157,6 +157,30 @@ int qmk_prefill(
     int num_layers, int start_position, int max_seq_len, float attn_scale,
     cudaStream_t stream);
 
+/* qmk_generate for callers that cannot allocate device memory while running -
+ * for example a server that handed all free HBM to its own cache pool when it
+ * started, or a loop that must not hit cudaMalloc's device-wide
+ * synchronisation.  It has no counterpart in the reference.  It runs the same
+ * kernel and gives the same tokens, but its scratch (exchange words, fp32
+ * rotary table, status) is a fixed 1,542,208-byte device array inside the
+ * library, held on every GPU the process uses until exit; the call and
+ * everything under it make no cudaMalloc / cudaFree / cudaHostAlloc.
+ * Limits: max_seq_len <= 2048 (the rotary table's size; a larger value is
+ * refused with QMK_ERR_BAD_ARGUMENT and a message), num_layers <= 48.
+ * The first call on a device looks up the array's device address and sets the
+ * kernel's shared-memory attribute: make that call before any stream capture.
+ * All calls on a device share the array, which keeps the previous call's
+ * contents (status and rotary table are rewritten per call, exchange words
+ * are distinguished by tags): calls that overlap on the GPU race.  Blocks
+ * until the stream is idle; vocab/split/time-out options come from
+ * qmk_configure; RoPE always uses in-kernel fp32 angles. */
+int qmk_generate_static(
+    int first_token_id, int num_steps, const void *embed_weight,
+    const struct LDGLayerWeight *layer_weights, const void *final_norm_weight,
+    const void *lm_head_weight, void *k_cache, void *v_cache, void *g_normalized,
+    int *output_log, int num_layers, int start_position, int max_seq_len,
+    float attn_scale, int eos_token_id, cudaStream_t stream);
+
 /* Synchronises the device and returns the status word of the last launch
  * (QMK_OK, or the first error a CTA recorded). */
 int qmk_sync_status(void);

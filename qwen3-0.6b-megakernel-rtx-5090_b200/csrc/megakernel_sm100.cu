@@ -1024,6 +1024,18 @@ __global__ void wait_timeout_probe(const __grid_constant__ Params P, unsigned lo
   }
 }
 
+// ---- scratch for the allocation-free entry point (qmk_generate_static) ----------------------
+// Some callers cannot allocate device memory once they are running: a serving process that gave all
+// free HBM to its own cache pool at start-up (a later cudaMalloc simply fails), or a loop that cannot
+// afford cudaMalloc's device-wide synchronisation.  For them the megakernel's scratch lives in this
+// fixed array, which every process that loads the library holds on every GPU it touches until exit:
+// the exchange words, an fp32 rotary table for STATIC_MAX_POSITIONS positions, and the status words.
+constexpr int STATIC_MAX_POSITIONS = 2048;
+constexpr size_t STATIC_LL_BYTES = sizeof(unsigned long long) * LL_WORDS;
+constexpr size_t STATIC_ROPE_BYTES = sizeof(float) * D * STATIC_MAX_POSITIONS;
+constexpr size_t STATIC_SCRATCH_BYTES = STATIC_LL_BYTES + STATIC_ROPE_BYTES + 64;   // 1,542,208 B
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+
 }  // namespace qmk
 
 // ============================================================================= host side
@@ -1401,6 +1413,123 @@ int qmk_selftest_wait_timeout(int budget_us) {
   const int code = static_cast<int>(e->status_host[0]);
   QMK_CUDA(e, cudaMemset(e->status, 0, 16));
   return code;
+}
+
+// ---- allocation-free variant ------------------------------------------------------------------
+// Same kernel and same results as qmk_generate, but nothing here (or below it) calls cudaMalloc,
+// cudaFree, cudaHostAlloc or any other allocating routine: the scratch is qmk::g_static_scratch.
+// In host code that name is only a stand-in for the device array, not an address a kernel can use,
+// so the first call on each device (with that device current) asks the runtime for the real device
+// address with cudaGetSymbolAddress and keeps it.  That first call also opts the kernel into its
+// shared-memory size; make it before any stream capture starts.
+// All calls on a device share the one array and it keeps what the previous call left in it: the
+// status words are cleared and the rotary table is rebuilt at the start of every call, the exchange
+// words are told apart by their tags (and cleared when the tag sequence restarts).  Two calls that
+// overlap on the GPU (two qmk_generate_static calls on different streams of one device) would race on
+// the array; keep them on one stream.  (qmk_generate has its own, allocated, scratch.)
+struct StaticState {
+  bool ready = false;
+  unsigned char *base = nullptr;   // device address of qmk::g_static_scratch on this device
+  int grid = 0;
+  uint32_t seq = 0;
+};
+StaticState g_static[MAX_DEVICES];
+
+int qmk_generate_static(int first_token_id, int num_steps, const void *embed_weight,
+                        const LDGLayerWeight *layer_weights, const void *final_norm_weight,
+                        const void *lm_head_weight, void *k_cache, void *v_cache, void *g_normalized,
+                        int *output_log, int num_layers, int start_position, int max_seq_len, float attn_scale,
+                        int eos_token_id, cudaStream_t stream) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  Engine *e = current_engine_unlocked();
+  if (!e) return QMK_ERR_CUDA;
+  clear_error(e);
+  if (num_steps <= 0) return QMK_OK;
+  if (!output_log || !embed_weight || !layer_weights || !final_norm_weight || !lm_head_weight || !k_cache || !v_cache)
+    return fail(e, QMK_ERR_BAD_ARGUMENT, "qmk_generate_static: null pointer argument");
+  if (!aligned16(embed_weight) || !aligned16(layer_weights) || !aligned16(lm_head_weight) || !aligned16(k_cache) ||
+      !aligned16(v_cache))
+    return fail(e, QMK_ERR_BAD_ARGUMENT, "weight, cache and layer-table pointers must be 16-byte aligned");
+  if (num_layers < 1 || num_layers > qmk::MAX_LAYERS)
+    return fail(e, QMK_ERR_BAD_ARGUMENT, "num_layers must be in [1, 48]");
+  if (max_seq_len > qmk::STATIC_MAX_POSITIONS) {
+    char buf[160];
+    snprintf(buf, sizeof(buf), "qmk_generate_static: max_seq_len %d exceeds the static scratch limit of %d positions",
+             max_seq_len, qmk::STATIC_MAX_POSITIONS);
+    return fail(e, QMK_ERR_BAD_ARGUMENT, buf);
+  }
+  if (start_position < 0 || start_position + num_steps > max_seq_len)
+    return fail(e, QMK_ERR_POSITION, "start_position + steps exceeds max_seq_len");
+
+  StaticState &st = g_static[e->device];
+  if (!st.ready) {   // once per device, with that device current
+    cudaDeviceProp prop;
+    QMK_CUDA(e, cudaGetDeviceProperties(&prop, e->device));
+    if (prop.major < 10) return fail(e, QMK_ERR_CUDA, "this library is built for sm_100a only");
+    QMK_CUDA(e, cudaFuncSetAttribute(qmk::qwen3_decode_megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(qmk::SMEM_BYTES)));
+    void *dev_ptr = nullptr;
+    QMK_CUDA(e, cudaGetSymbolAddress(&dev_ptr, qmk::g_static_scratch));
+    st.base = static_cast<unsigned char *>(dev_ptr);
+    st.grid = prop.multiProcessorCount < qmk::MAX_CTAS ? prop.multiProcessorCount : qmk::MAX_CTAS;
+    if (!e->inv_freq_set && !e->ready) {   // same default frequencies as the allocating path (theta = 1e6)
+      float inv[qmk::D / 2];
+      for (int i = 0; i < qmk::D / 2; ++i) inv[i] = static_cast<float>(1.0 / pow(1.0e6, (2.0 * i) / qmk::D));
+      QMK_CUDA(e, cudaMemcpyToSymbol(qmk::c_inv_freq, inv, sizeof(inv)));
+    }
+    QMK_CUDA(e, cudaMemsetAsync(st.base, 0, qmk::STATIC_SCRATCH_BYTES, stream));
+    st.seq = 0;
+    st.ready = true;
+  }
+  unsigned long long *ll = reinterpret_cast<unsigned long long *>(st.base);
+  float *rope = reinterpret_cast<float *>(st.base + qmk::STATIC_LL_BYTES);
+  unsigned int *status = reinterpret_cast<unsigned int *>(st.base + qmk::STATIC_LL_BYTES + qmk::STATIC_ROPE_BYTES);
+  if (static_cast<unsigned long long>(st.seq) + static_cast<unsigned long long>(num_steps) >= (1ull << 26)) {
+    QMK_CUDA(e, cudaMemsetAsync(ll, 0, qmk::STATIC_LL_BYTES, stream));   // tags restart from zero
+    st.seq = 0;
+  }
+  QMK_CUDA(e, cudaMemsetAsync(status, 0, 16, stream));
+  // rebuilt every call: picks up a qmk_set_inv_freq made since the last one
+  qmk::rope_table_kernel<<<(qmk::STATIC_MAX_POSITIONS * (qmk::D / 2) + 255) / 256, 256, 0, stream>>>(
+      rope, qmk::STATIC_MAX_POSITIONS);
+  QMK_CUDA(e, cudaGetLastError());
+
+  Params P = base_params(embed_weight, layer_weights, final_norm_weight, lm_head_weight, nullptr, nullptr, k_cache,
+                         v_cache, num_layers, start_position, max_seq_len, attn_scale);
+  P.first_token = first_token_id;
+  P.num_steps = num_steps;
+  P.output_log = output_log;
+  P.eos = eos_token_id;
+  P.normalized_out = static_cast<float *>(g_normalized);
+  P.ll = ll;
+  P.rope = rope;
+  P.status = status;
+  P.seq_base = st.seq;
+  P.vocab = e->vocab;
+  P.rope_from_table = 0;
+  P.split_len = e->split_len;
+  P.timeout_ns = static_cast<unsigned long long>(e->timeout_ms) * 1000000ull;
+  P.logits_out = e->logits_out;
+  P.spin_sleep_ns = e->spin_sleep_ns;
+  P.l2_evict_first = e->l2_evict_first;
+  st.seq += static_cast<uint32_t>(num_steps);
+  int grid = st.grid;
+  if (e->max_ctas > 0 && e->max_ctas < grid) grid = e->max_ctas;
+  void *args[] = {&P};
+  cudaError_t err = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(qmk::qwen3_decode_megakernel), dim3(grid),
+                                                dim3(qmk::THREADS), args, qmk::SMEM_BYTES, stream);
+  if (err == cudaErrorCooperativeLaunchTooLarge)
+    return fail(e, QMK_ERR_NOT_RESIDENT, "persistent grid cannot be co-resident on this device");
+  if (err != cudaSuccess) return fail(e, QMK_ERR_CUDA, std::string("cudaLaunchCooperativeKernel: ") + cudaGetErrorString(err));
+  unsigned int host_status[4] = {0, 0, 0, 0};   // plain host memory: no pinned allocation on this path
+  QMK_CUDA(e, cudaMemcpyAsync(host_status, status, 16, cudaMemcpyDeviceToHost, stream));
+  QMK_CUDA(e, cudaStreamSynchronize(stream));
+  if (host_status[0] != 0) {
+    char buf[160];
+    snprintf(buf, sizeof(buf), "device status %u (where %u, cta %u)", host_status[0], host_status[1], host_status[2]);
+    return fail(e, static_cast<int>(host_status[0]), buf);
+  }
+  return QMK_OK;
 }
 
 // ---- reference-signature entry points (qwen_ops.cpp:9-39) ------------------------------------

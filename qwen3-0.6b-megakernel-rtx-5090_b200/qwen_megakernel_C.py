@@ -58,6 +58,8 @@ _lib.qmk_generate.argtypes = [_I, _I, *([_P] * 12), _P, _I, _I, _I, _F, _I, _I, 
 _lib.qmk_generate.restype = _I
 _lib.qmk_prefill.argtypes = [_P, _I, *([_P] * 7), _I, _I, _I, _F, _P]
 _lib.qmk_prefill.restype = _I
+_lib.qmk_generate_static.argtypes = [_I, _I, *([_P] * 7), _P, _I, _I, _I, _F, _I, _P]
+_lib.qmk_generate_static.restype = _I
 _lib.qmk_sync_status.restype = _I
 _lib.qmk_last_error.restype = ctypes.c_char_p
 _lib.qmk_num_ctas.restype = _I
@@ -68,7 +70,7 @@ _lib.qmk_selftest_wait_timeout.restype = _I
 EXPORTED_SYMBOLS = (
     "launch_ldg_decode_direct", "launch_ldg_decode_persistent", "launch_ldg_generate_nosync",
     "launch_ldg_prefill", "qmk_abi_version", "qmk_configure", "qmk_set_inv_freq", "qmk_set_logits_dump",
-    "qmk_set_tuning", "qmk_set_profile_buffer", "qmk_decode", "qmk_generate", "qmk_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
+    "qmk_set_tuning", "qmk_set_profile_buffer", "qmk_decode", "qmk_generate", "qmk_generate_static", "qmk_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
     "qmk_scratch_bytes", "qmk_selftest_wait_timeout",
 )
 
@@ -211,6 +213,28 @@ def set_profile_buffer(buf) -> None:
         _check(buf.is_cuda and buf.dtype == torch.int64 and buf.is_contiguous(),
                "profile buffer must be a contiguous int64 CUDA tensor")
     _lib.qmk_set_profile_buffer(_ptr(buf))
+
+
+def generate_static(first_token_id, num_steps, embed_weight, layer_weights_packed, final_norm_weight,
+                    lm_head_weight, k_cache, v_cache, norm_out, output_log, num_layers, start_position,
+                    max_seq_len, attn_scale, eos_token_id=-1):
+    """``generate_nosync`` for callers that cannot allocate device memory while running (a server whose
+    cache pool already owns all free HBM, a loop that cannot take cudaMalloc's device-wide sync): same
+    kernel, same tokens, scratch in a fixed array inside the library.  ``max_seq_len`` <= 2048.
+    Blocks; raises ``RuntimeError`` on any reported error; returns ``output_log``."""
+    _require_cuda()
+    _check(output_log.dtype == torch.int32 and output_log.is_cuda and output_log.is_contiguous(),
+           "generate_static: output_log must be a contiguous int32 CUDA tensor")
+    _check(output_log.numel() >= num_steps, "generate_static: output_log is shorter than num_steps")
+    _check_table(layer_weights_packed, "generate_static")
+    rc = _lib.qmk_generate_static(
+        int(first_token_id), int(num_steps), _ptr(embed_weight), _ptr(layer_weights_packed),
+        _ptr(final_norm_weight), _ptr(lm_head_weight), _ptr(k_cache), _ptr(v_cache), _ptr(norm_out),
+        output_log.data_ptr(), int(num_layers), int(start_position), int(max_seq_len), float(attn_scale),
+        -1 if eos_token_id is None else int(eos_token_id), _stream())
+    if rc != 0:
+        raise RuntimeError(f"generate_static: {_lib.qmk_last_error().decode()} (status {rc})")
+    return output_log
 
 
 def sync_status() -> int:
