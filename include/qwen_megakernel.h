@@ -124,6 +124,11 @@ int qmk_set_logits_dump(float *logits_out);
  * polls of an exchange word (default 0).  l2_evict_first: 1 (default) streams
  * weights with an evict-first L2 policy, 0 uses the default policy. */
 int qmk_set_tuning(int spin_sleep_ns, int l2_evict_first);
+/* More knobs; negative keeps a value.  repl (1, 2 or 4): copies of the exchange
+ * area; producers publish every word to all copies and CTA i polls copy i % repl,
+ * which divides the number of pollers per cache line (default 4).  stream_inflight: cap on
+ * weight/KV chunks in flight per SM during the layer phases (0 = ring depth). */
+int qmk_set_tuning2(int repl, int stream_inflight);
 
 /* Debug: when non-null, every CTA writes globaltimer stamps (ns) of the phase
  * boundaries of the LAST step of each launch to timestamps[cta * 768 + slot]

@@ -76,6 +76,7 @@ constexpr int LL_X2 = LL_INTER + I;
 constexpr int LL_AMAX = LL_X2 + H;
 constexpr int LL_PART = LL_AMAX + 2 * MAX_CTAS;
 constexpr int LL_WORDS = LL_PART + NQ * MAX_SPLITS * PART_STRIDE;
+constexpr int MAX_REPL = 4;      // the allocated exchange area holds up to 4 copies
 
 // Same binary layout as the reference's per-layer pointer record
 // (megakernel_5090.cu:91-104): 11 fp16 pointers + 1 pad = 96 bytes.
@@ -110,6 +111,8 @@ struct Params {
   float attn_scale;
   int spin_sleep_ns;             // back-off between polls of an exchange word (0 = none)
   int l2_evict_first;            // weight stream L2 policy: 1 evict_first, 0 default
+  int repl;                      // copies of the exchange area (1, 2 or 4); CTA i polls copy i % repl
+  int stream_inflight;           // max weight chunks in flight during layer phases (0 = ring depth)
 };
 
 __constant__ float c_inv_freq[D / 2];
@@ -184,6 +187,14 @@ __device__ __forceinline__ void ll_store(unsigned long long *p, float v, uint32_
   unsigned long long w = (static_cast<unsigned long long>(tag) << 32) | __float_as_uint(v);
   asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
+// Publishes one exchange word to all `repl` copies of the area (copy stride LL_WORDS).
+__device__ __forceinline__ void ll_publish(unsigned long long *p, float v, uint32_t tag, int repl) {
+  ll_store(p, v, tag);
+  if (repl > 1) {
+    ll_store(p + LL_WORDS, v, tag);
+    if (repl > 2) { ll_store(p + 2 * LL_WORDS, v, tag); ll_store(p + 3 * LL_WORDS, v, tag); }
+  }
+}
 __device__ __forceinline__ unsigned long long ll_load(const unsigned long long *p) {
   unsigned long long w;
   asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
@@ -248,6 +259,7 @@ static_assert(SMEM_BYTES <= 232448, "over the 227 KB shared-memory limit of one 
 static_assert(OFF_FULL % 8 == 0 && OFF_LAYERS % 16 == 0, "shared-memory alignment");
 
 struct Ctx {
+  const unsigned long long *llr;   // the copy of the exchange area this CTA polls
   unsigned char *smem;
   int tid, warp, lane, cta, ncta;
   uint32_t chunk;   // consumer-side running chunk index (uniform over consumer threads)
@@ -297,6 +309,41 @@ __device__ __forceinline__ float ll_wait(const Params &P, const Ctx &c, const un
   unsigned long long w = ll_load(p);
   if (static_cast<uint32_t>(w >> 32) != tag) w = ll_spin(P, c, p, tag);
   return __uint_as_float(static_cast<uint32_t>(w));
+}
+
+// Waits for NW exchange words at once: every pass re-loads ALL words still missing before looking at
+// any of them, so the whole set completes one L2 round trip after its last word lands (polling them
+// one after the other costs a round trip per word that was stale in the first pass).
+// `valid` masks the words this thread really owns.  Values are garbage after an abort.
+template <int NW>
+__device__ __forceinline__ void ll_wait_many(const Params &P, const Ctx &c, const unsigned long long *const (&p)[NW],
+                                             uint32_t valid, uint32_t tag, float (&out)[NW]) {
+  unsigned long long w[NW];
+#pragma unroll
+  for (int j = 0; j < NW; ++j)
+    if (valid & (1u << j)) w[j] = ll_load(p[j]);
+  uint32_t pending = valid;
+  unsigned long long t0 = 0;
+  uint32_t it = 0;
+  for (;;) {
+#pragma unroll
+    for (int j = 0; j < NW; ++j)
+      if ((pending & (1u << j)) && static_cast<uint32_t>(w[j] >> 32) == tag) pending &= ~(1u << j);
+    if (pending == 0u) break;
+    if (P.spin_sleep_ns) __nanosleep(P.spin_sleep_ns);
+#pragma unroll
+    for (int j = 0; j < NW; ++j)
+      if (pending & (1u << j)) w[j] = ll_load(p[j]);
+    if ((++it & 255u) == 0u) {
+      if (c.flags()[0]) break;
+      if (ld_relaxed_u32(P.status) != 0u) { c.flags()[0] = 1; break; }
+      const unsigned long long t = now_ns();
+      if (t0 == 0) t0 = t;
+      if (t - t0 > P.timeout_ns) { raise_error(P, c, QMK_ERR_WAIT_TIMEOUT, WHERE_LL); break; }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < NW; ++j) out[j] = __uint_as_float(static_cast<uint32_t>(w[j]));
 }
 
 // Wait on an mbarrier phase with the same bounds.  Returns false after an abort (or, for the
@@ -382,10 +429,15 @@ __device__ __forceinline__ AttnItem attn_item(const Params &P, const Ctx &c, int
 
 // ----------------------------------------------------------------------------- producer (one thread)
 __device__ __forceinline__ bool produce_chunk(const Params &P, const Ctx &c, uint32_t &idx, uint64_t pol,
-                                              const unsigned char *src, const unsigned char *src2, uint32_t bytes) {
+                                              const unsigned char *src, const unsigned char *src2, uint32_t bytes,
+                                              int inflight) {
   const uint32_t slot = idx % NSLOTS;
   if (c.flags()[0] | c.flags()[1]) return false;
   if (idx >= NSLOTS && !mbar_wait(P, c, c.empty(slot), ((idx / NSLOTS) - 1u) & 1u, WHERE_EMPTY, true)) return false;
+  if (inflight > 0 && idx >= static_cast<uint32_t>(inflight)) {   // pacing: chunk idx - inflight must have landed
+    const uint32_t prev = idx - static_cast<uint32_t>(inflight);
+    if (!mbar_wait(P, c, c.full(prev % NSLOTS), (prev / NSLOTS) & 1u, WHERE_EMPTY, true)) return false;
+  }
   unsigned char *dst = c.slot(idx);
   mbar_arrive_expect_tx(c.full(slot), src2 ? 2 * bytes : bytes);
   bulk_g2s(dst, src, bytes, c.full(slot), pol);
@@ -407,7 +459,9 @@ __device__ __forceinline__ bool produce_phase(const Params &P, const Ctx &c, uin
     for (int r = 0; r < nrows; r += rpc) {
       const int nr = min(rpc, nrows - r);
       const size_t off = static_cast<size_t>(r) * rb;
-      if (!produce_chunk(P, c, idx, pol, src + off, src2 ? src2 + off : nullptr, static_cast<uint32_t>(nr * rb))) return false;
+      if (!produce_chunk(P, c, idx, pol, src + off, src2 ? src2 + off : nullptr, static_cast<uint32_t>(nr * rb),
+                         kind == K_LM ? 0 : P.stream_inflight))
+        return false;
     }
   }
   return true;
@@ -438,7 +492,7 @@ __device__ __forceinline__ void producer_main(const Params &P, const Ctx &c) {
           const uint32_t bytes = static_cast<uint32_t>(min(KV_ROWS_PER_CHUNK, it.p1 - r)) * D * 2;
           const size_t off = (head_base + static_cast<size_t>(r) * D) * 2;
           ok = produce_chunk(P, c, idx, pol, reinterpret_cast<const unsigned char *>(P.k_cache) + off,
-                             reinterpret_cast<const unsigned char *>(P.v_cache) + off, bytes);
+                             reinterpret_cast<const unsigned char *>(P.v_cache) + off, bytes, P.stream_inflight);
         }
       }
 #pragma unroll 1
@@ -502,18 +556,21 @@ __device__ __forceinline__ float block_sum(const Ctx &c, float v) {
 template <int N>
 __device__ __forceinline__ float poll_vec(const Params &P, const Ctx &c, const unsigned long long *buf, uint32_t tag, float *dst) {
   constexpr int PT = (N + CONS_THREADS - 1) / CONS_THREADS;
-  unsigned long long w[PT];
+  const unsigned long long *p[PT];
+  uint32_t valid = 0;
 #pragma unroll
-  for (int j = 0; j < PT; ++j)
-    if (N % CONS_THREADS == 0 || c.tid + j * CONS_THREADS < N) w[j] = ll_load(buf + c.tid + j * CONS_THREADS);
+  for (int j = 0; j < PT; ++j) {
+    p[j] = buf + c.tid + j * CONS_THREADS;
+    if (N % CONS_THREADS == 0 || c.tid + j * CONS_THREADS < N) valid |= 1u << j;
+  }
+  float v[PT];
+  ll_wait_many<PT>(P, c, p, valid, tag, v);
   float ss = 0.f;
 #pragma unroll
   for (int j = 0; j < PT; ++j)
-    if (N % CONS_THREADS == 0 || c.tid + j * CONS_THREADS < N) {
-      if (static_cast<uint32_t>(w[j] >> 32) != tag) w[j] = ll_spin(P, c, buf + c.tid + j * CONS_THREADS, tag);
-      const float v = __uint_as_float(static_cast<uint32_t>(w[j]));
-      dst[c.tid + j * CONS_THREADS] = v;
-      ss = fmaf(v, v, ss);
+    if (valid & (1u << j)) {
+      dst[c.tid + j * CONS_THREADS] = v[j];
+      ss = fmaf(v[j], v[j], ss);
     }
   return ss;
 }
@@ -581,7 +638,7 @@ __device__ __forceinline__ void gemv_rows(const Params &P, Ctx &c, const float (
             if (v > best || (v == best && o < best_i)) { best = v; best_i = o; }
             if (dump && c.lane == 0) dump[o] = v;
           } else {
-            if (c.lane == 0) ll_store(out + o, v, tag);
+            if (c.lane == 0) ll_publish(out + o, v, tag, P.repl);
           }
         }
       }
@@ -603,7 +660,7 @@ __device__ __forceinline__ void attention_phase(const Params &P, Ctx &c, const u
                                                 const AttnItem &it, uint32_t tag) {
   float *s_q = c.f(F_Q), *s_knew = c.f(F_KNEW), *s_vnew = c.f(F_VNEW), *s_wpart = c.f(F_WPART), *s_misc = c.f(F_MISC);
   const float *s_cs = c.f(F_CS);
-  const unsigned long long *qkv = P.ll + LL_QKV;
+  const unsigned long long *qkv = c.llr + LL_QKV;
   if (!it.active) return;
   const int S = it.S, g = it.g, s = it.s;
   const bool owner = (s == S - 1);
@@ -621,8 +678,10 @@ __device__ __forceinline__ void attention_phase(const Params &P, Ctx &c, const u
       for (int i = 0; i < 4; ++i) nw[i] = __half2float(__ldg(nwp + lane + 32 * i));
     }
     float v[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] = ll_wait(P, c, src + lane + 32 * i, tag);
+    {
+      const unsigned long long *wp[4] = {src + lane, src + lane + 32, src + lane + 64, src + lane + 96};
+      ll_wait_many<4>(P, c, wp, 0xfu, tag, v);
+    }
     if (w < 3) {
       float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
       ss = warp_sum(ss);
@@ -762,11 +821,11 @@ __device__ __forceinline__ void attention_phase(const Params &P, Ctx &c, const u
     }
     const int hq = 2 * g + h;
     if (S == 1) {
-      ll_store(P.ll + LL_ATTN + hq * D + d, A / L, tag);
+      ll_publish(P.ll + LL_ATTN + hq * D + d, A / L, tag, P.repl);
     } else {
       unsigned long long *part = P.ll + LL_PART + static_cast<size_t>(hq * MAX_SPLITS + s) * PART_STRIDE;
-      ll_store(part + d, A, tag);
-      if (d == 0) { ll_store(part + D, M, tag); ll_store(part + D + 1, L, tag); }
+      ll_publish(part + d, A, tag, P.repl);
+      if (d == 0) { ll_publish(part + D, M, tag, P.repl); ll_publish(part + D + 1, L, tag, P.repl); }
     }
   }
   // New K,V row -> cache (megakernel_5090.cu:392-397), off the critical path.  The fence orders
@@ -788,15 +847,16 @@ __device__ __forceinline__ void attention_merge(const Params &P, const Ctx &c, i
     const int hq = e >> 7, d = e & (D - 1);
     float a = 0.f, m = -INFINITY, l = 0.f;
     if (c.lane < S) {
-      const unsigned long long *part = P.ll + LL_PART + static_cast<size_t>(hq * MAX_SPLITS + c.lane) * PART_STRIDE;
-      a = ll_wait(P, c, part + d, tag);
-      m = ll_wait(P, c, part + D, tag);
-      l = ll_wait(P, c, part + D + 1, tag);
+      const unsigned long long *part = c.llr + LL_PART + static_cast<size_t>(hq * MAX_SPLITS + c.lane) * PART_STRIDE;
+      const unsigned long long *wp[3] = {part + d, part + D, part + D + 1};
+      float v3[3];
+      ll_wait_many<3>(P, c, wp, 0x7u, tag, v3);
+      a = v3[0]; m = v3[1]; l = v3[2];
     }
     const float M = warp_max(m);
     const float sc = (m == -INFINITY) ? 0.f : exp2f(m - M);
     const float L = warp_sum(l * sc), A = warp_sum(a * sc);
-    if (c.lane == 0) ll_store(P.ll + LL_ATTN + e, A / L, tag);
+    if (c.lane == 0) ll_publish(P.ll + LL_ATTN + e, A / L, tag, P.repl);
   }
 }
 
@@ -817,6 +877,7 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
   c.cta = blockIdx.x;
   c.ncta = gridDim.x;
   c.chunk = 0;
+  c.llr = P.ll + static_cast<size_t>(c.cta % max(1, P.repl)) * LL_WORDS;
 
   if (c.tid == 0) {
     for (int i = 0; i < NSLOTS; ++i) { mbar_init(c.full(i), 1); mbar_init(c.empty(i), EMPTY_UNITS); }
@@ -888,25 +949,25 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
         if (item.S > 1) attention_merge(P, c, item.S, tag);
         QMK_STAMP(layer * 12 + 3);
         // P4: O-proj + residual
-        poll_vec<QS>(P, c, P.ll + LL_ATTN, tag, s_vec);
+        poll_vec<QS>(P, c, c.llr + LL_ATTN, tag, s_vec);
         QMK_STAMP(layer * 12 + 4);
         cons_sync();
         gemv_rows<K_O>(P, c, a, s_vec, s_x, P.ll + LL_X1, tag, best, best_i, nullptr);
         // P5: post-attention RMSNorm + gate/up + SwiGLU
         QMK_STAMP(layer * 12 + 5);
-        ss = poll_vec<H>(P, c, P.ll + LL_X1, tag, s_x1);
+        ss = poll_vec<H>(P, c, c.llr + LL_X1, tag, s_x1);
         QMK_STAMP(layer * 12 + 6);
         norm_to_regs(c, s_x1, ss, reinterpret_cast<const __half *>(rec[REC_POST_LN]), a);
         gemv_rows<K_GU>(P, c, a, nullptr, nullptr, P.ll + LL_INTER, tag, best, best_i, nullptr);
         // P6: down-proj + residual
         QMK_STAMP(layer * 12 + 7);
-        poll_vec<I>(P, c, P.ll + LL_INTER, tag, s_vec);
+        poll_vec<I>(P, c, c.llr + LL_INTER, tag, s_vec);
         QMK_STAMP(layer * 12 + 8);
         cons_sync();
         gemv_rows<K_DOWN>(P, c, a, s_vec, s_x1, P.ll + LL_X2, tag, best, best_i, nullptr);
         // next layer's input (in prefill mode the last layer's output is not needed)
         QMK_STAMP(layer * 12 + 9);
-        if (!(P.prefill && layer == P.num_layers - 1)) ss = poll_vec<H>(P, c, P.ll + LL_X2, tag, s_x);
+        if (!(P.prefill && layer == P.num_layers - 1)) ss = poll_vec<H>(P, c, c.llr + LL_X2, tag, s_x);
         QMK_STAMP(layer * 12 + 10);
         if (cons_any(c.flags()[0] != 0)) break;
       }
@@ -943,13 +1004,13 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
           const int vi = __float_as_int(s_misc[48 + w]);
           if (v > best || (v == best && vi < best_i)) { best = v; best_i = vi; }
         }
-        ll_store(P.ll + LL_AMAX + 2 * c.cta, best, atag);
-        ll_store(P.ll + LL_AMAX + 2 * c.cta + 1, __int_as_float(best_i), atag);
+        ll_publish(P.ll + LL_AMAX + 2 * c.cta, best, atag, P.repl);
+        ll_publish(P.ll + LL_AMAX + 2 * c.cta + 1, __int_as_float(best_i), atag, P.repl);
         if (P.bmax_vals) P.bmax_vals[c.cta] = best;
         if (P.bmax_idxs) P.bmax_idxs[c.cta] = best_i;
       }
 #pragma unroll 1
-      for (int i = c.tid; i < 2 * c.ncta; i += CONS_THREADS) s_amax[i] = ll_wait(P, c, P.ll + LL_AMAX + i, atag);
+      for (int i = c.tid; i < 2 * c.ncta; i += CONS_THREADS) s_amax[i] = ll_wait(P, c, c.llr + LL_AMAX + i, atag);
       cons_sync();
       if (c.warp == 0) {
         float bv = -INFINITY;
@@ -1019,6 +1080,7 @@ __global__ void wait_timeout_probe(const __grid_constant__ Params P, unsigned lo
     c.cta = blockIdx.x;
     c.ncta = gridDim.x;
     c.chunk = 0;
+    c.llr = word;
     c.flags()[0] = 0;
     ll_wait(P, c, word, 0xfffffff0u);
   }
@@ -1068,6 +1130,8 @@ struct Engine {
   unsigned long long *prof = nullptr;
   int spin_sleep_ns = 0;
   int l2_evict_first = 1;
+  int repl = 4;              // measured: 835 -> 752 us/token at short context, 1152 -> 1061 at 4096
+  int stream_inflight = 0;   // measured: pacing the stream changes nothing
   bool inv_freq_set = false;
 };
 
@@ -1117,8 +1181,8 @@ int ensure_ready(Engine *e) {
   if (per_sm < 1) return fail(e, QMK_ERR_NOT_RESIDENT, "megakernel does not fit on an SM");
   e->grid = e->num_sms;
   if (e->grid > qmk::MAX_CTAS) e->grid = qmk::MAX_CTAS;
-  QMK_CUDA(e, cudaMalloc(&e->ll, sizeof(unsigned long long) * qmk::LL_WORDS));
-  QMK_CUDA(e, cudaMemset(e->ll, 0, sizeof(unsigned long long) * qmk::LL_WORDS));
+  QMK_CUDA(e, cudaMalloc(&e->ll, sizeof(unsigned long long) * qmk::LL_WORDS * qmk::MAX_REPL));
+  QMK_CUDA(e, cudaMemset(e->ll, 0, sizeof(unsigned long long) * qmk::LL_WORDS * qmk::MAX_REPL));
   QMK_CUDA(e, cudaMalloc(&e->status, 16));
   QMK_CUDA(e, cudaMemset(e->status, 0, 16));
   QMK_CUDA(e, cudaHostAlloc(&e->status_host, 16, cudaHostAllocDefault));
@@ -1160,7 +1224,7 @@ int launch(Engine *e, Params &P, cudaStream_t stream, bool synchronize) {
 
   // Tags are (sequence number * 64 + layer); restart the sequence before it can wrap.
   if (static_cast<unsigned long long>(e->seq) + static_cast<unsigned long long>(P.num_steps) >= (1ull << 26)) {
-    QMK_CUDA(e, cudaMemsetAsync(e->ll, 0, sizeof(unsigned long long) * qmk::LL_WORDS, stream));
+    QMK_CUDA(e, cudaMemsetAsync(e->ll, 0, sizeof(unsigned long long) * qmk::LL_WORDS * qmk::MAX_REPL, stream));
     e->seq = 0;
   }
   if (!e->rope_from_table && P.max_seq_len > e->rope_cap) {   // grow-only, like the token staging buffer
@@ -1187,6 +1251,8 @@ int launch(Engine *e, Params &P, cudaStream_t stream, bool synchronize) {
   P.prof = e->prof;
   P.spin_sleep_ns = e->spin_sleep_ns;
   P.l2_evict_first = e->l2_evict_first;
+  P.repl = e->repl;
+  P.stream_inflight = e->stream_inflight;
   e->seq += static_cast<uint32_t>(P.num_steps);
 
   void *args[] = {&P};
@@ -1268,6 +1334,16 @@ int qmk_set_logits_dump(float *logits_out) {
   Engine *e = current_engine_unlocked();
   if (!e) return QMK_ERR_CUDA;
   e->logits_out = logits_out;
+  return QMK_OK;
+}
+
+int qmk_set_tuning2(int repl, int stream_inflight) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  Engine *e = current_engine_unlocked();
+  if (!e) return QMK_ERR_CUDA;
+  if (repl == 1 || repl == 2 || repl == 4) e->repl = repl;
+  else if (repl >= 0) return fail(e, QMK_ERR_BAD_ARGUMENT, "repl must be 1, 2 or 4");
+  if (stream_inflight >= 0) e->stream_inflight = stream_inflight > qmk::NSLOTS ? qmk::NSLOTS : stream_inflight;
   return QMK_OK;
 }
 
@@ -1392,7 +1468,9 @@ int qmk_num_ctas(void) {
   return grid_for(e);
 }
 
-long long qmk_scratch_bytes(void) { return static_cast<long long>(sizeof(unsigned long long)) * qmk::LL_WORDS + 16; }
+long long qmk_scratch_bytes(void) {
+  return static_cast<long long>(sizeof(unsigned long long)) * qmk::LL_WORDS * qmk::MAX_REPL + 16;
+}
 
 int qmk_selftest_wait_timeout(int budget_us) {
   std::lock_guard<std::mutex> lock(g_mutex);
@@ -1512,6 +1590,8 @@ int qmk_generate_static(int first_token_id, int num_steps, const void *embed_wei
   P.logits_out = e->logits_out;
   P.spin_sleep_ns = e->spin_sleep_ns;
   P.l2_evict_first = e->l2_evict_first;
+  P.repl = 1;                 // the fixed array holds one copy of the exchange area
+  P.stream_inflight = e->stream_inflight;
   st.seq += static_cast<uint32_t>(num_steps);
   int grid = st.grid;
   if (e->max_ctas > 0 && e->max_ctas < grid) grid = e->max_ctas;

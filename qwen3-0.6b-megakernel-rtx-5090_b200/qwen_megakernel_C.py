@@ -50,6 +50,8 @@ _lib.qmk_set_logits_dump.argtypes = [_P]
 _lib.qmk_set_logits_dump.restype = _I
 _lib.qmk_set_tuning.argtypes = [_I, _I]
 _lib.qmk_set_tuning.restype = _I
+_lib.qmk_set_tuning2.argtypes = [_I, _I]
+_lib.qmk_set_tuning2.restype = _I
 _lib.qmk_set_profile_buffer.argtypes = [_P]
 _lib.qmk_set_profile_buffer.restype = _I
 _lib.qmk_decode.argtypes = [_I, _P, *([_P] * 12), _I, _I, _I, _F, _P]
@@ -70,7 +72,7 @@ _lib.qmk_selftest_wait_timeout.restype = _I
 EXPORTED_SYMBOLS = (
     "launch_ldg_decode_direct", "launch_ldg_decode_persistent", "launch_ldg_generate_nosync",
     "launch_ldg_prefill", "qmk_abi_version", "qmk_configure", "qmk_set_inv_freq", "qmk_set_logits_dump",
-    "qmk_set_tuning", "qmk_set_profile_buffer", "qmk_decode", "qmk_generate", "qmk_generate_static", "qmk_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
+    "qmk_set_tuning", "qmk_set_tuning2", "qmk_set_profile_buffer", "qmk_decode", "qmk_generate", "qmk_generate_static", "qmk_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
     "qmk_scratch_bytes", "qmk_selftest_wait_timeout",
 )
 
@@ -198,9 +200,10 @@ def set_logits_dump(buf) -> None:
     _lib.qmk_set_logits_dump(_ptr(buf))
 
 
-def set_tuning(spin_sleep_ns=-1, l2_evict_first=-1) -> None:
+def set_tuning(spin_sleep_ns=-1, l2_evict_first=-1, repl=-1, stream_inflight=-1) -> None:
     """Performance knobs (see include/qwen_megakernel.h); negative keeps a value."""
     _check(_lib.qmk_set_tuning(int(spin_sleep_ns), int(l2_evict_first)) == 0, "set_tuning failed")
+    _check(_lib.qmk_set_tuning2(int(repl), int(stream_inflight)) == 0, "set_tuning failed")
 
 
 PROFILE_STRIDE = 768
