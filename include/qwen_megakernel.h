@@ -121,7 +121,7 @@ int qmk_set_inv_freq(const float *inv_freq64);
 int qmk_set_logits_dump(float *logits_out);
 
 /* Performance knobs; negative keeps a value.  spin_sleep_ns: nanosleep between
- * polls of an exchange word (default 0).  l2_evict_first: 1 (default) streams
+ * polls of an exchange word (default 600).  l2_evict_first: 1 (default) streams
  * weights with an evict-first L2 policy, 0 uses the default policy. */
 int qmk_set_tuning(int spin_sleep_ns, int l2_evict_first);
 /* More knobs; negative keeps a value.  repl (1, 2 or 4): copies of the exchange

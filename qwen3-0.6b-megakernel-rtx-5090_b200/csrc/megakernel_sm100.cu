@@ -58,7 +58,7 @@ constexpr int CONS_WARPS = QMK_CONS_WARPS;
 constexpr int CONS_THREADS = CONS_WARPS * 32;   // 512 math threads
 constexpr int THREADS = CONS_THREADS + 32;      // + 1 producer warp
 constexpr int SLOT_BYTES = 8192;
-constexpr int NSLOTS = 22;
+constexpr int NSLOTS = 21;
 static_assert(NSLOTS >= CONS_WARPS, "a group of chunks (up to one per warp) must fit in the ring");
 constexpr int EMPTY_UNITS = 4;   // arrival units that free a ring slot (rows-per-chunk is 4, 2 or 1)
 constexpr int MAX_SPLITS = 24;   // attention work items per kv head (<= grid / 8)
@@ -240,9 +240,15 @@ constexpr int F_MISC = F_AMAX + 2 * MAX_CTAS;  // [0,1] new-row scores, [16] tok
 constexpr int F_END = F_MISC + 64;
 constexpr size_t OFF_FULL = SMEM_RING + static_cast<size_t>(F_END) * 4;   // mbarriers: full[NSLOTS]
 constexpr size_t OFF_EMPTY = OFF_FULL + NSLOTS * 8;                       //            empty[NSLOTS]
-constexpr size_t OFF_FLAGS = OFF_EMPTY + NSLOTS * 8;   // int[4]: abort, stop, issued chunks, consumed chunks
+constexpr size_t OFF_NFULL = OFF_EMPTY + NSLOTS * 8;   // mbarriers of the two norm-vector buffers
+constexpr size_t OFF_FLAGS = OFF_NFULL + 16;           // int[4]: abort, stop, issued chunks, consumed chunks
 constexpr size_t OFF_LAYERS = OFF_FLAGS + 64;          // copy of the layer pointer table, 12 x u64 per layer
-constexpr size_t OFF_SEGS = OFF_LAYERS + MAX_LAYERS * sizeof(LayerW);
+// Norm vectors of a layer (fp16): in_ln[1024] | post_ln[1024] | q_norm[128] | k_norm[128]; two buffers,
+// layer parity selects one.  The producer copies them in when it starts a layer's weights.
+constexpr int NORM_HALVES = 2 * H + 2 * D;
+constexpr int NB_IN_LN = 0, NB_POST_LN = H, NB_QNORM = 2 * H, NB_KNORM = 2 * H + D;
+constexpr size_t OFF_NORMS = OFF_LAYERS + MAX_LAYERS * sizeof(LayerW);
+constexpr size_t OFF_SEGS = OFF_NORMS + 2 * NORM_HALVES * 2;
 constexpr int NKIND = 5;
 enum Kind { K_QKV = 0, K_O = 1, K_GU = 2, K_DOWN = 3, K_LM = 4 };
 // Row slices this CTA owns in every phase, computed once per launch (shared memory).
@@ -255,8 +261,9 @@ struct SegTab {
   int e0, e1;            // attention outputs this CTA merges when KV is split
 };
 constexpr size_t SMEM_BYTES = OFF_SEGS + ((sizeof(SegTab) + 63) / 64) * 64;
+static_assert((I + CONS_THREADS - 1) / CONS_THREADS <= 8, "poll_vec handles at most 8 words per thread");
 static_assert(SMEM_BYTES <= 232448, "over the 227 KB shared-memory limit of one CTA");
-static_assert(OFF_FULL % 8 == 0 && OFF_LAYERS % 16 == 0, "shared-memory alignment");
+static_assert(OFF_FULL % 8 == 0 && OFF_LAYERS % 16 == 0 && OFF_NORMS % 16 == 0, "shared-memory alignment");
 
 struct Ctx {
   const unsigned long long *llr;   // the copy of the exchange area this CTA polls
@@ -266,6 +273,8 @@ struct Ctx {
   __device__ __forceinline__ float *f(int off) const { return reinterpret_cast<float *>(smem + SMEM_RING) + off; }
   __device__ __forceinline__ uint64_t *full(uint32_t slot) const { return reinterpret_cast<uint64_t *>(smem + OFF_FULL) + slot; }
   __device__ __forceinline__ uint64_t *empty(uint32_t slot) const { return reinterpret_cast<uint64_t *>(smem + OFF_EMPTY) + slot; }
+  __device__ __forceinline__ uint64_t *nfull(uint32_t b) const { return reinterpret_cast<uint64_t *>(smem + OFF_NFULL) + b; }
+  __device__ __forceinline__ __half *norms(uint32_t b) const { return reinterpret_cast<__half *>(smem + OFF_NORMS) + b * NORM_HALVES; }
   __device__ __forceinline__ volatile int *flags() const { return reinterpret_cast<volatile int *>(smem + OFF_FLAGS); }
   __device__ __forceinline__ const unsigned long long *layer_rec(int l) const {
     return reinterpret_cast<const unsigned long long *>(smem + OFF_LAYERS) + l * 12;
@@ -411,8 +420,8 @@ __device__ __forceinline__ const unsigned char *seg_src(const SegTab *t, int kin
 
 // Attention work item of this CTA at position `pos`: kv head g, split s of S, old cache rows [p0, p1).
 // Both the producer (to stream the rows) and the consumers (to use them) call this.
-constexpr int KV_ROWS_PER_CHUNK = 16;   // 16 K rows (4 KB) + 16 V rows (4 KB) per ring slot
-struct AttnItem { int S, g, s, p0, p1, nchunks; bool active; };
+constexpr int KV_ROWS_PER_CHUNK = 16;   // at most 16 K rows (4 KB) + 16 V rows (4 KB) per ring slot
+struct AttnItem { int S, g, s, p0, p1, nchunks, rpc; bool active; };
 __device__ __forceinline__ AttnItem attn_item(const Params &P, const Ctx &c, int pos) {
   AttnItem it;
   const int S_max = min(MAX_SPLITS, max(1, c.ncta / NKV));
@@ -423,7 +432,12 @@ __device__ __forceinline__ AttnItem attn_item(const Params &P, const Ctx &c, int
   // old rows [p0, p1) of [0, pos); pos * S < 2^31, 32-bit division
   it.p0 = it.active ? static_cast<int>(static_cast<unsigned>(pos * it.s) / static_cast<unsigned>(it.S)) : 0;
   it.p1 = it.active ? static_cast<int>(static_cast<unsigned>(pos * (it.s + 1)) / static_cast<unsigned>(it.S)) : 0;
-  it.nchunks = (it.p1 - it.p0 + KV_ROWS_PER_CHUNK - 1) / KV_ROWS_PER_CHUNK;
+  // Rows per chunk chosen so that every warp gets the same number of (equally long) chunks: with a fixed
+  // 16 rows per chunk, 15 chunks over 12 warps left three warps with twice the work of the others.
+  const int rows = it.p1 - it.p0;
+  const int rounds = max(1, (rows + CONS_WARPS * KV_ROWS_PER_CHUNK - 1) / (CONS_WARPS * KV_ROWS_PER_CHUNK));
+  it.rpc = max(1, (rows + CONS_WARPS * rounds - 1) / (CONS_WARPS * rounds));
+  it.nchunks = (rows + it.rpc - 1) / it.rpc;
   return it;
 }
 
@@ -476,20 +490,25 @@ __device__ __forceinline__ void producer_main(const Params &P, const Ctx &c) {
 #pragma unroll 1
     for (int l = 0; ok && l < P.num_layers; ++l) {
       const unsigned long long *rec = c.layer_rec(l);
-      if (c.cta < 4) {  // pull the small norm vectors of this layer into L2 ahead of the math
-        const int which = c.cta == 0 ? REC_IN_LN : c.cta == 1 ? REC_POST_LN : c.cta == 2 ? REC_QNORM : REC_KNORM;
-        const unsigned char *v = reinterpret_cast<const unsigned char *>(rec[which]);
-        const int bytes = c.cta < 2 ? H * 2 : D * 2;
-        for (int b = 0; b < bytes; b += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(v + b));
+      {  // this layer's norm vectors -> shared memory.  The buffer of layer L-2 is free: the ring holds fewer
+         // chunks than one layer has, so the math is at least in layer L-1 when this point is reached.
+        const uint32_t L = static_cast<uint32_t>(step) * static_cast<uint32_t>(P.num_layers) + static_cast<uint32_t>(l);
+        const uint32_t b = L & 1u;
+        __half *dst = c.norms(b);
+        c.flags()[4 + b] = static_cast<int>(L + 1u);   // for the exit drain
+        mbar_arrive_expect_tx(c.nfull(b), NORM_HALVES * 2);
+        bulk_g2s(dst + NB_IN_LN, reinterpret_cast<const void *>(rec[REC_IN_LN]), H * 2, c.nfull(b), l2_evict_normal_policy());
+        bulk_g2s(dst + NB_POST_LN, reinterpret_cast<const void *>(rec[REC_POST_LN]), H * 2, c.nfull(b), l2_evict_normal_policy());
+        bulk_g2s(dst + NB_QNORM, reinterpret_cast<const void *>(rec[REC_QNORM]), D * 2, c.nfull(b), l2_evict_normal_policy());
+        bulk_g2s(dst + NB_KNORM, reinterpret_cast<const void *>(rec[REC_KNORM]), D * 2, c.nfull(b), l2_evict_normal_policy());
       }
-#pragma unroll 1
       ok = produce_phase(P, c, idx, pol, K_QKV, rec);
       {  // this CTA's range of old K/V rows for the attention phase of this layer
         const AttnItem it = attn_item(P, c, P.start_position + step);
         const size_t head_base = (static_cast<size_t>(l) * NKV + it.g) * static_cast<size_t>(P.max_seq_len) * D;
 #pragma unroll 1
-        for (int r = it.p0; ok && r < it.p1; r += KV_ROWS_PER_CHUNK) {
-          const uint32_t bytes = static_cast<uint32_t>(min(KV_ROWS_PER_CHUNK, it.p1 - r)) * D * 2;
+        for (int r = it.p0; ok && r < it.p1; r += it.rpc) {
+          const uint32_t bytes = static_cast<uint32_t>(min(it.rpc, it.p1 - r)) * D * 2;
           const size_t off = (head_base + static_cast<size_t>(r) * D) * 2;
           ok = produce_chunk(P, c, idx, pol, reinterpret_cast<const unsigned char *>(P.k_cache) + off,
                              reinterpret_cast<const unsigned char *>(P.v_cache) + off, bytes, P.stream_inflight);
@@ -514,31 +533,6 @@ __device__ __forceinline__ float dot8(const uint4 w, const float *a, float acc) 
   }
   return acc;
 }
-// Row of K=1024 fp16 weights in shared memory times activations held in registers
-// (lane owns k = j*256 + lane*8 + i).
-__device__ __forceinline__ float row_dot_regs(const unsigned char *row, const float (&a)[32], int lane) {
-  const uint4 *w = reinterpret_cast<const uint4 *>(row);
-  float acc[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) acc[j] = dot8(w[j * 32 + lane], &a[j * 8], 0.f);
-  return warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
-}
-// Row of K fp16 weights in shared memory times fp32 activations in shared memory.
-template <int K>
-__device__ __forceinline__ float row_dot_smem(const unsigned char *row, const float *act, int lane) {
-  const uint4 *w = reinterpret_cast<const uint4 *>(row);
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-  for (int j = 0; j < K / 256; ++j) {
-    const int k = j * 256 + lane * 8;
-    const float4 a0 = *reinterpret_cast<const float4 *>(act + k);
-    const float4 a1 = *reinterpret_cast<const float4 *>(act + k + 4);
-    const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-    acc[j & 3] = dot8(w[j * 32 + lane], a, acc[j & 3]);
-  }
-  return warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
-}
-
 // sum over the 512 consumer threads; contains one consumer barrier
 __device__ __forceinline__ float block_sum(const Ctx &c, float v) {
   v = warp_sum(v);
@@ -553,15 +547,18 @@ __device__ __forceinline__ float block_sum(const Ctx &c, float v) {
 
 // Polls N exchange words into shared memory as fp32; returns this thread's sum of squares.
 // All loads are issued before the first one is looked at.
-template <int N>
-__device__ __forceinline__ float poll_vec(const Params &P, const Ctx &c, const unsigned long long *buf, uint32_t tag, float *dst) {
-  constexpr int PT = (N + CONS_THREADS - 1) / CONS_THREADS;
+// One shared (non-inlined) copy: the kernel's per-layer code has to stay small enough for the
+// instruction cache, and this routine has five call sites.  Arguments are scalars / by value, so it
+// needs no stack.  n <= 8 * CONS_THREADS.
+__device__ __noinline__ float poll_vec(const Params &P, const Ctx c, const unsigned long long *buf, int n, uint32_t tag,
+                                       float *dst) {
+  constexpr int PT = 8;
   const unsigned long long *p[PT];
   uint32_t valid = 0;
 #pragma unroll
   for (int j = 0; j < PT; ++j) {
     p[j] = buf + c.tid + j * CONS_THREADS;
-    if (N % CONS_THREADS == 0 || c.tid + j * CONS_THREADS < N) valid |= 1u << j;
+    if (c.tid + j * CONS_THREADS < n) valid |= 1u << j;
   }
   float v[PT];
   ll_wait_many<PT>(P, c, p, valid, tag, v);
@@ -583,7 +580,7 @@ __device__ __forceinline__ void norm_to_regs(const Ctx &c, const float *x, float
   // The norm weights are loaded after the barrier on purpose: issued before it (while the CTA is
   // still polling exchange words) the same loads measured ~100 us/token slower.
 #pragma unroll
-  for (int j = 0; j < 4; ++j) wn[j] = __ldg(reinterpret_cast<const uint4 *>(norm_w + j * 256 + c.lane * 8));
+  for (int j = 0; j < 4; ++j) wn[j] = *reinterpret_cast<const uint4 *>(norm_w + j * 256 + c.lane * 8);
   const float rstd = 1.0f / sqrtf(tot * (1.0f / H) + RMS_EPS);
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
@@ -601,62 +598,157 @@ __device__ __forceinline__ void norm_to_regs(const Ctx &c, const float *x, float
   }
 }
 
-// This CTA's rows of one projection, streamed through the ring.  Warp w takes row (w % RPC) of
-// chunk (w / RPC) of each group of 16/RPC chunks and hands the slot back when its row is done.
+// This CTA's rows of one projection, streamed through the ring.  Warp w takes row (w % RPC) of chunk
+// (w / RPC) of each group of CONS_WARPS/RPC chunks; NB groups are handled per pass so that a warp
+// loads, multiplies and reduces all its rows of a layer phase together (one pass per layer phase), and
+// hands each slot back when its row is done.
 //   K_QKV : out[row] = W.a                       K_GU  : out[row] = silu(Wg.a) * (Wu.a)
 //   K_O / K_DOWN : out[row] = W.act + resid[row] (activations in shared memory)
 //   K_LM  : running (max, argmax) in best / best_i, optional logits dump
-template <int KIND>
-__device__ __forceinline__ void gemv_rows(const Params &P, Ctx &c, const float (&a)[32], const float *act, const float *resid,
-                                          unsigned long long *out, uint32_t tag, float &best, int &best_i, float *dump) {
-  constexpr int RB = kind_row_bytes(KIND), RPC = kind_rpc(KIND), G = CONS_WARPS / RPC;
+__device__ __forceinline__ float row_partial_regs(const unsigned char *row, const float (&a)[32], int lane) {
+  const uint4 *w = reinterpret_cast<const uint4 *>(row);
+  float acc[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) acc[j] = dot8(w[j * 32 + lane], &a[j * 8], 0.f);
+  return (acc[0] + acc[1]) + (acc[2] + acc[3]);
+}
+// K = 1024 phases (fused QKV, gate/up, LM head): RMSNorm of x into registers, then this CTA's rows.
+// One shared non-inlined copy (runtime `kind`); returns the advanced chunk counter.  For K_LM each warp
+// leaves its running (max, argmax) in s_misc[32 + warp] / s_misc[48 + warp].
+__device__ __noinline__ uint32_t gemv_k1024(const Params &P, Ctx c, int kind, const float *x, float ss,
+                                            const __half *norm_w, unsigned long long *out, uint32_t tag, float *dump) {
+  float a[32];
+  norm_to_regs(c, x, ss, norm_w, a);
+  if (kind == K_LM && c.cta == 0 && c.warp == 0 && (P.normalized_out || P.hidden_out)) {  // reference-signature outputs
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int k = j * 256 + c.lane * 8 + i;
+        if (P.normalized_out) P.normalized_out[k] = a[j * 8 + i];
+        if (P.hidden_out) P.hidden_out[k] = __float2half_rn(x[k]);
+      }
+  }
+  constexpr int NB = 3;
+  const int RPC = kind == K_GU ? 2 : 4, G = CONS_WARPS / RPC;
   const SegTab *t = c.segs();
   const int sub = c.warp % RPC, wch = c.warp / RPC;
-  const int n = t->nseg[KIND];
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  const int n = t->nseg[kind];
   for (int s = 0; s < n; ++s) {
-    const int nrows = t->nrows[KIND][s];
-    const int out0 = t->out0[KIND][s];
+    const int nrows = t->nrows[kind][s];
+    const int out0 = t->out0[kind][s];
+    const int nchunks = (nrows + RPC - 1) / RPC;
+#pragma unroll 1
+    for (int c0 = 0; c0 < nchunks; c0 += NB * G) {
+      float v[NB], u[NB];
+      bool have[NB];
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        const int ch = c0 + b * G + wch;
+        const int row = ch * RPC + sub;
+        have[b] = false;
+        v[b] = 0.f;
+        u[b] = 0.f;
+        if (ch < nchunks && row < nrows) {          // warp-uniform
+          const uint32_t idx = c.chunk + static_cast<uint32_t>(ch);
+          if (wait_full(P, c, idx)) {
+            have[b] = true;
+            const unsigned char *p = c.slot(idx) + sub * (H * 2);
+            v[b] = row_partial_regs(p, a, c.lane);
+            if (kind == K_GU) u[b] = row_partial_regs(p + SLOT_BYTES / 2, a, c.lane);
+          }
+        }
+      }
+      // all reductions of the pass interleaved (fixed butterfly order: deterministic)
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          v[b] += __shfl_xor_sync(0xffffffffu, v[b], o);
+          u[b] += __shfl_xor_sync(0xffffffffu, u[b], o);
+        }
+      }
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        const int ch = c0 + b * G + wch;
+        if (have[b]) {
+          const int o = out0 + ch * RPC + sub;
+          float r = v[b];
+          if (kind == K_GU) r = r / (1.0f + expf(-r)) * u[b];   // SiLU(gate) * up in fp32 (megakernel_5090.cu:681-684 does it in fp16)
+          if (kind == K_LM) {
+            if (r > best || (r == best && o < best_i)) { best = r; best_i = o; }
+            if (dump && c.lane == 0) dump[o] = r;
+          } else {
+            if (c.lane == 0) ll_publish(out + o, r, tag, P.repl);
+          }
+        }
+        // Release: the RPC warps mapped to a chunk each hand back EMPTY_UNITS/RPC units, whether or not
+        // their row exists (a short last chunk), so every chunk collects exactly EMPTY_UNITS.
+        __syncwarp();
+        if (c.lane == 0 && ch < nchunks)
+          mbar_arrive_n(c.empty((c.chunk + static_cast<uint32_t>(ch)) % NSLOTS), EMPTY_UNITS / RPC);
+      }
+    }
+    c.chunk += static_cast<uint32_t>(nchunks);
+  }
+  if (kind == K_LM && c.lane == 0) { c.f(F_MISC)[32 + c.warp] = best; c.f(F_MISC)[48 + c.warp] = __int_as_float(best_i); }
+  return c.chunk;
+}
+
+// O (K = 2048) and down (K = 3072) projections: out[row] = W.act + resid[row], activations and residual
+// in shared memory.  One shared non-inlined copy; returns the advanced chunk counter.
+__device__ __noinline__ uint32_t gemv_wide(const Params &P, Ctx c, int kind, const float *act, const float *resid,
+                                           unsigned long long *out, uint32_t tag) {
+  const int RPC = kind == K_O ? 2 : 1, G = CONS_WARPS / RPC, rb = kind == K_O ? QS * 2 : I * 2;
+  const int kiters = rb / 512;   // 256 weights per warp pass: 8 or 12
+  const SegTab *t = c.segs();
+  const int sub = c.warp % RPC, wch = c.warp / RPC;
+  const int n = t->nseg[kind];
+  for (int s = 0; s < n; ++s) {
+    const int nrows = t->nrows[kind][s];
+    const int out0 = t->out0[kind][s];
     const int nchunks = (nrows + RPC - 1) / RPC;
 #pragma unroll 1
     for (int c0 = 0; c0 < nchunks; c0 += G) {
       const int ch = c0 + wch;
       const int row = ch * RPC + sub;
-      if (ch < nchunks && row < nrows) {
+      if (ch < nchunks && row < nrows) {            // warp-uniform
         const uint32_t idx = c.chunk + static_cast<uint32_t>(ch);
         if (wait_full(P, c, idx)) {
-          const unsigned char *p = c.slot(idx) + sub * RB;
+          const uint4 *w = reinterpret_cast<const uint4 *>(c.slot(idx) + sub * rb);
+          float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+          for (int j = 0; j < kiters; j += 4) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int k = (j + q) * 256 + c.lane * 8;
+              const float4 a0 = *reinterpret_cast<const float4 *>(act + k);
+              const float4 a1 = *reinterpret_cast<const float4 *>(act + k + 4);
+              const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+              acc[q] = dot8(w[(j + q) * 32 + c.lane], av, acc[q]);
+            }
+          }
           const int o = out0 + row;
-          float v;
-          if constexpr (KIND == K_O) v = row_dot_smem<QS>(p, act, c.lane) + resid[o];
-          else if constexpr (KIND == K_DOWN) v = row_dot_smem<I>(p, act, c.lane) + resid[o];
-          else v = row_dot_regs(p, a, c.lane);
-          if constexpr (KIND == K_GU) {
-            const float u = row_dot_regs(p + SLOT_BYTES / 2, a, c.lane);
-            v = v / (1.0f + expf(-v)) * u;   // SiLU(gate) * up in fp32 (megakernel_5090.cu:681-684 does it in fp16)
-          }
-          if constexpr (KIND == K_LM) {
-            if (v > best || (v == best && o < best_i)) { best = v; best_i = o; }
-            if (dump && c.lane == 0) dump[o] = v;
-          } else {
-            if (c.lane == 0) ll_publish(out + o, v, tag, P.repl);
-          }
+          const float r = warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3])) + resid[o];
+          if (c.lane == 0) ll_publish(out + o, r, tag, P.repl);
         }
       }
-      // Release: the RPC warps mapped to a chunk each hand back EMPTY_UNITS/RPC units, whether or not
-      // their row exists (a short last chunk), so every chunk collects exactly EMPTY_UNITS.
       __syncwarp();
       if (c.lane == 0 && ch < nchunks)
         mbar_arrive_n(c.empty((c.chunk + static_cast<uint32_t>(ch)) % NSLOTS), EMPTY_UNITS / RPC);
     }
     c.chunk += static_cast<uint32_t>(nchunks);
   }
+  return c.chunk;
 }
 
 // ----------------------------------------------------------------------------- attention
 // Work item (kv head g, split s) on CTA g + 8*s: old cache rows [p0, p1); the last split also
 // normalises/rotates/stores the new K,V row and folds it in.  Writes either the final head
 // outputs (one split) or unnormalised partials.
-__device__ __forceinline__ void attention_phase(const Params &P, Ctx &c, const unsigned long long *rec, int layer, int pos,
+__device__ __forceinline__ void attention_phase(const Params &P, Ctx &c, const __half *nv, int layer, int pos,
                                                 const AttnItem &it, uint32_t tag) {
   float *s_q = c.f(F_Q), *s_knew = c.f(F_KNEW), *s_vnew = c.f(F_VNEW), *s_wpart = c.f(F_WPART), *s_misc = c.f(F_MISC);
   const float *s_cs = c.f(F_CS);
@@ -673,9 +765,9 @@ __device__ __forceinline__ void attention_phase(const Params &P, Ctx &c, const u
     const unsigned long long *src = (w < 2) ? qkv + (2 * g + w) * D : (w == 2) ? qkv + QS + g * D : qkv + QS + KVS + g * D;
     float nw[4] = {1.f, 1.f, 1.f, 1.f};
     if (w < 3) {
-      const __half *nwp = reinterpret_cast<const __half *>(rec[(w < 2) ? REC_QNORM : REC_KNORM]);
+      const __half *nwp = nv + ((w < 2) ? NB_QNORM : NB_KNORM);   // shared memory
 #pragma unroll
-      for (int i = 0; i < 4; ++i) nw[i] = __half2float(__ldg(nwp + lane + 32 * i));
+      for (int i = 0; i < 4; ++i) nw[i] = __half2float(nwp[lane + 32 * i]);
     }
     float v[4];
     {
@@ -737,7 +829,7 @@ __device__ __forceinline__ void attention_phase(const Params &P, Ctx &c, const u
 #pragma unroll 1
   for (int j = c.warp; j < it.nchunks; j += CONS_WARPS) {
     const uint32_t idx = c.chunk + static_cast<uint32_t>(j);
-    const int nrow = min(KV_ROWS_PER_CHUNK, (p1 - p0) - j * KV_ROWS_PER_CHUNK);
+    const int nrow = min(it.rpc, (p1 - p0) - j * it.rpc);
     if (wait_full(P, c, idx)) {
       const unsigned char *kslot = c.slot(idx) + seg * 16;
 #pragma unroll 2
@@ -881,8 +973,10 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
 
   if (c.tid == 0) {
     for (int i = 0; i < NSLOTS; ++i) { mbar_init(c.full(i), 1); mbar_init(c.empty(i), EMPTY_UNITS); }
+    mbar_init(c.nfull(0), 1);
+    mbar_init(c.nfull(1), 1);
     volatile int *fl = c.flags();
-    fl[0] = 0; fl[1] = 0; fl[2] = 0; fl[3] = 0;
+    fl[0] = 0; fl[1] = 0; fl[2] = 0; fl[3] = 0; fl[4] = 0; fl[5] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (c.tid == 32) build_segtab(reinterpret_cast<SegTab *>(smem + OFF_SEGS), c.cta, c.ncta, P.vocab);
@@ -899,9 +993,6 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
   } else {
     float *s_x = c.f(F_X), *s_x1 = c.f(F_X1), *s_vec = c.f(F_VEC), *s_misc = c.f(F_MISC), *s_amax = c.f(F_AMAX);
     int token = P.prefill ? P.token_ids[0] : P.first_token;
-    float a[32];
-    float best = 0.f;
-    int best_i = 0;
 #pragma unroll 1
     for (int step = 0; step < P.num_steps; ++step) {
       const int pos = P.start_position + step;
@@ -938,36 +1029,37 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
       for (int layer = 0; layer < P.num_layers; ++layer) {
         const unsigned long long *rec = c.layer_rec(layer);
         const uint32_t tag = tag_base + static_cast<uint32_t>(layer) + 1u;
+        const uint32_t Lg = static_cast<uint32_t>(step) * static_cast<uint32_t>(P.num_layers) + static_cast<uint32_t>(layer);
+        const __half *nv = c.norms(Lg & 1u);
+        mbar_wait(P, c, c.nfull(Lg & 1u), (Lg >> 1) & 1u, WHERE_FULL, false);
         // P1: input RMSNorm + fused QKV rows
         QMK_STAMP(layer * 12 + 0);
-        norm_to_regs(c, s_x, ss, reinterpret_cast<const __half *>(rec[REC_IN_LN]), a);
-        gemv_rows<K_QKV>(P, c, a, nullptr, nullptr, P.ll + LL_QKV, tag, best, best_i, nullptr);
+        c.chunk = gemv_k1024(P, c, K_QKV, s_x, ss, nv + NB_IN_LN, P.ll + LL_QKV, tag, nullptr);
         // P2/P3: attention work items, then merge of split partials
         QMK_STAMP(layer * 12 + 1);
-        attention_phase(P, c, rec, layer, pos, item, tag);
+        attention_phase(P, c, nv, layer, pos, item, tag);
         QMK_STAMP(layer * 12 + 2);
         if (item.S > 1) attention_merge(P, c, item.S, tag);
         QMK_STAMP(layer * 12 + 3);
         // P4: O-proj + residual
-        poll_vec<QS>(P, c, c.llr + LL_ATTN, tag, s_vec);
+        poll_vec(P, c, c.llr + LL_ATTN, QS, tag, s_vec);
         QMK_STAMP(layer * 12 + 4);
         cons_sync();
-        gemv_rows<K_O>(P, c, a, s_vec, s_x, P.ll + LL_X1, tag, best, best_i, nullptr);
+        c.chunk = gemv_wide(P, c, K_O, s_vec, s_x, P.ll + LL_X1, tag);
         // P5: post-attention RMSNorm + gate/up + SwiGLU
         QMK_STAMP(layer * 12 + 5);
-        ss = poll_vec<H>(P, c, c.llr + LL_X1, tag, s_x1);
+        ss = poll_vec(P, c, c.llr + LL_X1, H, tag, s_x1);
         QMK_STAMP(layer * 12 + 6);
-        norm_to_regs(c, s_x1, ss, reinterpret_cast<const __half *>(rec[REC_POST_LN]), a);
-        gemv_rows<K_GU>(P, c, a, nullptr, nullptr, P.ll + LL_INTER, tag, best, best_i, nullptr);
+        c.chunk = gemv_k1024(P, c, K_GU, s_x1, ss, nv + NB_POST_LN, P.ll + LL_INTER, tag, nullptr);
         // P6: down-proj + residual
         QMK_STAMP(layer * 12 + 7);
-        poll_vec<I>(P, c, c.llr + LL_INTER, tag, s_vec);
+        poll_vec(P, c, c.llr + LL_INTER, I, tag, s_vec);
         QMK_STAMP(layer * 12 + 8);
         cons_sync();
-        gemv_rows<K_DOWN>(P, c, a, s_vec, s_x1, P.ll + LL_X2, tag, best, best_i, nullptr);
+        c.chunk = gemv_wide(P, c, K_DOWN, s_vec, s_x1, P.ll + LL_X2, tag);
         // next layer's input (in prefill mode the last layer's output is not needed)
         QMK_STAMP(layer * 12 + 9);
-        if (!(P.prefill && layer == P.num_layers - 1)) ss = poll_vec<H>(P, c, c.llr + LL_X2, tag, s_x);
+        if (!(P.prefill && layer == P.num_layers - 1)) ss = poll_vec(P, c, c.llr + LL_X2, H, tag, s_x);
         QMK_STAMP(layer * 12 + 10);
         if (cons_any(c.flags()[0] != 0)) break;
       }
@@ -978,26 +1070,14 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
       }
       // final RMSNorm + tied LM head + argmax (megakernel_5090.cu:921-947, 1024-1167)
       QMK_STAMP(P.num_layers * 12 + 0);
-      norm_to_regs(c, s_x, ss, P.final_norm, a);
-      if (c.cta == 0 && c.warp == 0 && (P.normalized_out || P.hidden_out)) {  // reference-signature output buffers
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int k = j * 256 + c.lane * 8 + i;
-            if (P.normalized_out) P.normalized_out[k] = a[j * 8 + i];
-            if (P.hidden_out) P.hidden_out[k] = __float2half_rn(s_x[k]);
-          }
-      }
-      best = -INFINITY;
-      best_i = 0x7fffffff;
-      gemv_rows<K_LM>(P, c, a, nullptr, nullptr, nullptr, 0u, best, best_i,
-                      P.logits_out ? P.logits_out + static_cast<size_t>(step) * P.vocab : nullptr);
+      c.chunk = gemv_k1024(P, c, K_LM, s_x, ss, P.final_norm, nullptr, 0u,
+                           P.logits_out ? P.logits_out + static_cast<size_t>(step) * P.vocab : nullptr);
       QMK_STAMP(P.num_layers * 12 + 1);
-      if (c.lane == 0) { s_misc[32 + c.warp] = best; s_misc[48 + c.warp] = __int_as_float(best_i); }
       cons_sync();
       const uint32_t atag = tag_base + 63u;
       if (c.tid == 0) {
+        float best = s_misc[32];
+        int best_i = __float_as_int(s_misc[48]);
 #pragma unroll 1
         for (int w = 1; w < CONS_WARPS; ++w) {
           const float v = s_misc[32 + w];
@@ -1053,6 +1133,15 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
       const uint32_t parity = (i / NSLOTS) & 1u;
       const unsigned long long t0 = now_ns();
       while (!mbar_try_wait(bar, parity)) {
+        if (now_ns() - t0 > P.timeout_ns) { raise_error(P, c, QMK_ERR_WAIT_TIMEOUT, WHERE_DRAIN); break; }
+      }
+    }
+    for (uint32_t b = 0; b < 2; ++b) {   // norm-vector copies
+      const int v = c.flags()[4 + b];
+      if (v == 0) continue;
+      const uint32_t parity = ((static_cast<uint32_t>(v) - 1u) >> 1) & 1u;
+      const unsigned long long t0 = now_ns();
+      while (!mbar_try_wait(c.nfull(b), parity)) {
         if (now_ns() - t0 > P.timeout_ns) { raise_error(P, c, QMK_ERR_WAIT_TIMEOUT, WHERE_DRAIN); break; }
       }
     }
@@ -1128,7 +1217,7 @@ struct Engine {
   int timeout_ms = 2000;
   float *logits_out = nullptr;
   unsigned long long *prof = nullptr;
-  int spin_sleep_ns = 0;
+  int spin_sleep_ns = 600;   // measured: 745 -> 695 us/token; without a pause the polls delay the stores they wait for
   int l2_evict_first = 1;
   int repl = 4;              // measured: 835 -> 752 us/token at short context, 1152 -> 1061 at 4096
   int stream_inflight = 0;   // measured: pacing the stream changes nothing
