@@ -138,7 +138,8 @@ class StubTokenizer:
         self.vocab_size = vocab_size
 
     def encode(self, text, add_special_tokens=False):
-        return [int(t) % self.vocab_size for t in text.split()]
+        # anything that is not a decimal number (chat-template markup, think tags) is dropped
+        return [int(t) % self.vocab_size for t in text.split() if t.isdigit()]
 
     def decode(self, ids, skip_special_tokens=True):
         return " ".join(str(int(i)) for i in ids)
