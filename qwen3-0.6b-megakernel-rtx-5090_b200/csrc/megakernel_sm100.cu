@@ -266,6 +266,7 @@ static_assert(SMEM_BYTES <= 232448, "over the 227 KB shared-memory limit of one 
 static_assert(OFF_FULL % 8 == 0 && OFF_LAYERS % 16 == 0 && OFF_NORMS % 16 == 0, "shared-memory alignment");
 
 struct Ctx {
+  int repl;                        // copies of the exchange area (kept in a register for the publish path)
   const unsigned long long *llr;   // the copy of the exchange area this CTA polls
   unsigned char *smem;
   int tid, warp, lane, cta, ncta;
@@ -533,6 +534,26 @@ __device__ __forceinline__ float dot8(const uint4 w, const float *a, float acc) 
   }
   return acc;
 }
+// Sums four per-lane values over the warp with 6 shuffles instead of 20: lanes trade halves of their
+// value set (xor 16, xor 8) and then finish one value each (xor 4, 2, 1).  Afterwards every lane with
+// (lane >> 3) == r holds the complete sum of value r.  The tree is fixed, so results are deterministic.
+__device__ __forceinline__ float warp_reduce_scatter4(float v0, float v1, float v2, float v3, int lane) {
+  const bool hi16 = (lane & 16) != 0;
+  // keep values {0,1} in lanes 0..15 and {2,3} in lanes 16..31
+  float k0 = hi16 ? v2 : v0, k1 = hi16 ? v3 : v1;
+  const float s0 = hi16 ? v0 : v2, s1 = hi16 ? v1 : v3;
+  k0 += __shfl_xor_sync(0xffffffffu, s0, 16);
+  k1 += __shfl_xor_sync(0xffffffffu, s1, 16);
+  const bool hi8 = (lane & 8) != 0;
+  float k = hi8 ? k1 : k0;
+  const float sd = hi8 ? k0 : k1;
+  k += __shfl_xor_sync(0xffffffffu, sd, 8);
+  k += __shfl_xor_sync(0xffffffffu, k, 4);
+  k += __shfl_xor_sync(0xffffffffu, k, 2);
+  k += __shfl_xor_sync(0xffffffffu, k, 1);
+  return k;
+}
+
 // sum over the 512 consumer threads; contains one consumer barrier
 __device__ __forceinline__ float block_sum(const Ctx &c, float v) {
   v = warp_sum(v);
@@ -629,71 +650,85 @@ __device__ __noinline__ uint32_t gemv_k1024(const Params &P, Ctx c, int kind, co
         if (P.hidden_out) P.hidden_out[k] = __float2half_rn(x[k]);
       }
   }
-  constexpr int NB = 3;
-  const int RPC = kind == K_GU ? 2 : 4, G = CONS_WARPS / RPC;
+  constexpr int NB = 3;                                 // rows per warp and pass (warp_reduce_scatter4 takes up to 4)
+  const int rsh = kind == K_GU ? 1 : 2;                 // log2(rows per chunk)
+  const int RPC = 1 << rsh, G = CONS_WARPS >> rsh;
   const SegTab *t = c.segs();
-  const int sub = c.warp % RPC, wch = c.warp / RPC;
+  const int sub = c.warp & (RPC - 1), wch = c.warp >> rsh;
   float best = -INFINITY;
   int best_i = 0x7fffffff;
   const int n = t->nseg[kind];
   for (int s = 0; s < n; ++s) {
     const int nrows = t->nrows[kind][s];
     const int out0 = t->out0[kind][s];
-    const int nchunks = (nrows + RPC - 1) / RPC;
+    const int nchunks = (nrows + RPC - 1) >> rsh;
 #pragma unroll 1
     for (int c0 = 0; c0 < nchunks; c0 += NB * G) {
       float v[NB], u[NB];
-      bool have[NB];
+      bool valid[NB];
+      bool ok = true;
+      // one combined wait for the (up to) NB chunks of this warp, then all the math
 #pragma unroll
       for (int b = 0; b < NB; ++b) {
         const int ch = c0 + b * G + wch;
-        const int row = ch * RPC + sub;
-        have[b] = false;
+        valid[b] = ch < nchunks && ((ch << rsh) + sub) < nrows;          // warp-uniform
+        if (valid[b]) {
+          const uint32_t idx = c.chunk + static_cast<uint32_t>(ch);
+          ok &= mbar_wait(P, c, c.full(idx % NSLOTS), (idx / NSLOTS) & 1u, WHERE_FULL, false);
+        }
+      }
+      ok = __all_sync(0xffffffffu, ok);   // the whole warp takes the same branch (shuffles follow)
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
         v[b] = 0.f;
         u[b] = 0.f;
-        if (ch < nchunks && row < nrows) {          // warp-uniform
-          const uint32_t idx = c.chunk + static_cast<uint32_t>(ch);
-          if (wait_full(P, c, idx)) {
-            have[b] = true;
-            const unsigned char *p = c.slot(idx) + sub * (H * 2);
-            v[b] = row_partial_regs(p, a, c.lane);
-            if (kind == K_GU) u[b] = row_partial_regs(p + SLOT_BYTES / 2, a, c.lane);
-          }
+        if (valid[b] && ok) {
+          const uint32_t idx = c.chunk + static_cast<uint32_t>(c0 + b * G + wch);
+          const unsigned char *p = c.slot(idx) + sub * (H * 2);
+          v[b] = row_partial_regs(p, a, c.lane);
+          if (kind == K_GU) u[b] = row_partial_regs(p + SLOT_BYTES / 2, a, c.lane);
         }
       }
-      // all reductions of the pass interleaved (fixed butterfly order: deterministic)
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
+      // The rows are in registers now: hand the slots back BEFORE publishing (mbarrier.arrive has
+      // release semantics and would otherwise wait for the global stores).  The RPC warps mapped to a
+      // chunk each return EMPTY_UNITS/RPC units, whether or not their row exists (a short last chunk).
+      __syncwarp();
+      if (c.lane == 0) {
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
-          v[b] += __shfl_xor_sync(0xffffffffu, v[b], o);
-          u[b] += __shfl_xor_sync(0xffffffffu, u[b], o);
+          const int ch = c0 + b * G + wch;
+          if (ch < nchunks) mbar_arrive_n(c.empty((c.chunk + static_cast<uint32_t>(ch)) % NSLOTS), EMPTY_UNITS >> rsh);
         }
       }
-#pragma unroll
-      for (int b = 0; b < NB; ++b) {
-        const int ch = c0 + b * G + wch;
-        if (have[b]) {
-          const int o = out0 + ch * RPC + sub;
-          float r = v[b];
-          if (kind == K_GU) r = r / (1.0f + expf(-r)) * u[b];   // SiLU(gate) * up in fp32 (megakernel_5090.cu:681-684 does it in fp16)
-          if (kind == K_LM) {
-            if (r > best || (r == best && o < best_i)) { best = r; best_i = o; }
-            if (dump && c.lane == 0) dump[o] = r;
-          } else {
-            if (c.lane == 0) ll_publish(out + o, r, tag, P.repl);
-          }
+      // lanes 0-7 end up with row b = 0, lanes 8-15 with b = 1, lanes 16-23 with b = 2
+      float r = warp_reduce_scatter4(v[0], v[1], v[2], 0.f, c.lane);
+      if (kind == K_GU) {
+        const float ur = warp_reduce_scatter4(u[0], u[1], u[2], 0.f, c.lane);
+        r = r / (1.0f + expf(-r)) * ur;   // SiLU(gate) * up in fp32 (megakernel_5090.cu:681-684 does it in fp16)
+      }
+      const int mb = c.lane >> 3;                                   // which of the NB rows this lane holds
+      const bool mine = ok && (c.lane & 7) == 0 && mb < NB && ((mb == 0 && valid[0]) || (mb == 1 && valid[1]) || (mb == 2 && valid[2]));
+      if (mine) {
+        const int o = out0 + ((c0 + mb * G + wch) << rsh) + sub;
+        if (kind == K_LM) {
+          if (r > best || (r == best && o < best_i)) { best = r; best_i = o; }
+          if (dump) dump[o] = r;
+        } else {
+          ll_publish(out + o, r, tag, c.repl);                      // one store instruction covers the NB rows
         }
-        // Release: the RPC warps mapped to a chunk each hand back EMPTY_UNITS/RPC units, whether or not
-        // their row exists (a short last chunk), so every chunk collects exactly EMPTY_UNITS.
-        __syncwarp();
-        if (c.lane == 0 && ch < nchunks)
-          mbar_arrive_n(c.empty((c.chunk + static_cast<uint32_t>(ch)) % NSLOTS), EMPTY_UNITS / RPC);
       }
     }
     c.chunk += static_cast<uint32_t>(nchunks);
   }
-  if (kind == K_LM && c.lane == 0) { c.f(F_MISC)[32 + c.warp] = best; c.f(F_MISC)[48 + c.warp] = __int_as_float(best_i); }
+  if (kind == K_LM) {   // lanes 0, 8 and 16 each tracked their own rows
+#pragma unroll
+    for (int o = 16; o >= 8; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    if (c.lane == 0) { c.f(F_MISC)[32 + c.warp] = best; c.f(F_MISC)[48 + c.warp] = __int_as_float(best_i); }
+  }
   return c.chunk;
 }
 
@@ -701,19 +736,22 @@ __device__ __noinline__ uint32_t gemv_k1024(const Params &P, Ctx c, int kind, co
 // in shared memory.  One shared non-inlined copy; returns the advanced chunk counter.
 __device__ __noinline__ uint32_t gemv_wide(const Params &P, Ctx c, int kind, const float *act, const float *resid,
                                            unsigned long long *out, uint32_t tag) {
-  const int RPC = kind == K_O ? 2 : 1, G = CONS_WARPS / RPC, rb = kind == K_O ? QS * 2 : I * 2;
+  const int rsh = kind == K_O ? 1 : 0;
+  const int RPC = 1 << rsh, G = CONS_WARPS >> rsh, rb = kind == K_O ? QS * 2 : I * 2;
   const int kiters = rb / 512;   // 256 weights per warp pass: 8 or 12
   const SegTab *t = c.segs();
-  const int sub = c.warp % RPC, wch = c.warp / RPC;
+  const int sub = c.warp & (RPC - 1), wch = c.warp >> rsh;
   const int n = t->nseg[kind];
   for (int s = 0; s < n; ++s) {
     const int nrows = t->nrows[kind][s];
     const int out0 = t->out0[kind][s];
-    const int nchunks = (nrows + RPC - 1) / RPC;
+    const int nchunks = (nrows + RPC - 1) >> rsh;
 #pragma unroll 1
     for (int c0 = 0; c0 < nchunks; c0 += G) {
       const int ch = c0 + wch;
-      const int row = ch * RPC + sub;
+      const int row = (ch << rsh) + sub;
+      float part = 0.f;
+      bool have = false;
       if (ch < nchunks && row < nrows) {            // warp-uniform
         const uint32_t idx = c.chunk + static_cast<uint32_t>(ch);
         if (wait_full(P, c, idx)) {
@@ -730,14 +768,18 @@ __device__ __noinline__ uint32_t gemv_wide(const Params &P, Ctx c, int kind, con
               acc[q] = dot8(w[(j + q) * 32 + c.lane], av, acc[q]);
             }
           }
-          const int o = out0 + row;
-          const float r = warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3])) + resid[o];
-          if (c.lane == 0) ll_publish(out + o, r, tag, P.repl);
+          part = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+          have = true;
         }
       }
-      __syncwarp();
+      __syncwarp();   // slot first, then the stores (see gemv_k1024)
       if (c.lane == 0 && ch < nchunks)
-        mbar_arrive_n(c.empty((c.chunk + static_cast<uint32_t>(ch)) % NSLOTS), EMPTY_UNITS / RPC);
+        mbar_arrive_n(c.empty((c.chunk + static_cast<uint32_t>(ch)) % NSLOTS), EMPTY_UNITS >> rsh);
+      if (have) {
+        const int o = out0 + row;
+        const float r = warp_sum(part) + resid[o];
+        if (c.lane == 0) ll_publish(out + o, r, tag, c.repl);
+      }
     }
     c.chunk += static_cast<uint32_t>(nchunks);
   }
@@ -913,11 +955,11 @@ __device__ __forceinline__ void attention_phase(const Params &P, Ctx &c, const _
     }
     const int hq = 2 * g + h;
     if (S == 1) {
-      ll_publish(P.ll + LL_ATTN + hq * D + d, A / L, tag, P.repl);
+      ll_publish(P.ll + LL_ATTN + hq * D + d, A / L, tag, c.repl);
     } else {
       unsigned long long *part = P.ll + LL_PART + static_cast<size_t>(hq * MAX_SPLITS + s) * PART_STRIDE;
-      ll_publish(part + d, A, tag, P.repl);
-      if (d == 0) { ll_publish(part + D, M, tag, P.repl); ll_publish(part + D + 1, L, tag, P.repl); }
+      ll_publish(part + d, A, tag, c.repl);
+      if (d == 0) { ll_publish(part + D, M, tag, c.repl); ll_publish(part + D + 1, L, tag, c.repl); }
     }
   }
   // New K,V row -> cache (megakernel_5090.cu:392-397), off the critical path.  The fence orders
@@ -948,7 +990,7 @@ __device__ __forceinline__ void attention_merge(const Params &P, const Ctx &c, i
     const float M = warp_max(m);
     const float sc = (m == -INFINITY) ? 0.f : exp2f(m - M);
     const float L = warp_sum(l * sc), A = warp_sum(a * sc);
-    if (c.lane == 0) ll_publish(P.ll + LL_ATTN + e, A / L, tag, P.repl);
+    if (c.lane == 0) ll_publish(P.ll + LL_ATTN + e, A / L, tag, c.repl);
   }
 }
 
@@ -969,7 +1011,8 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
   c.cta = blockIdx.x;
   c.ncta = gridDim.x;
   c.chunk = 0;
-  c.llr = P.ll + static_cast<size_t>(c.cta % max(1, P.repl)) * LL_WORDS;
+  c.repl = max(1, P.repl);
+  c.llr = P.ll + static_cast<size_t>(c.cta % c.repl) * LL_WORDS;
 
   if (c.tid == 0) {
     for (int i = 0; i < NSLOTS; ++i) { mbar_init(c.full(i), 1); mbar_init(c.empty(i), EMPTY_UNITS); }
@@ -1084,8 +1127,8 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
           const int vi = __float_as_int(s_misc[48 + w]);
           if (v > best || (v == best && vi < best_i)) { best = v; best_i = vi; }
         }
-        ll_publish(P.ll + LL_AMAX + 2 * c.cta, best, atag, P.repl);
-        ll_publish(P.ll + LL_AMAX + 2 * c.cta + 1, __int_as_float(best_i), atag, P.repl);
+        ll_publish(P.ll + LL_AMAX + 2 * c.cta, best, atag, c.repl);
+        ll_publish(P.ll + LL_AMAX + 2 * c.cta + 1, __int_as_float(best_i), atag, c.repl);
         if (P.bmax_vals) P.bmax_vals[c.cta] = best;
         if (P.bmax_idxs) P.bmax_idxs[c.cta] = best_i;
       }
@@ -1169,6 +1212,7 @@ __global__ void wait_timeout_probe(const __grid_constant__ Params P, unsigned lo
     c.cta = blockIdx.x;
     c.ncta = gridDim.x;
     c.chunk = 0;
+    c.repl = 1;
     c.llr = word;
     c.flags()[0] = 0;
     ll_wait(P, c, word, 0xfffffff0u);
