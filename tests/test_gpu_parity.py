@@ -144,6 +144,47 @@ def test_split_kv_attention_long_context(C):
     assert (eng._k_cache[:, :, :n].float().cpu() - o.k_cache[:, :, :n].float()).abs().max() < 8e-3
 
 
+def test_context_beyond_2048_all_splits(C):
+    """3000-token context: positions past the reference's 2048-row RoPE table, KV split over every
+    available work item per head, uneven last split, chunks spanning several ring rounds."""
+    w = S.make_weights(seed=6, num_layers=2, vocab_size=2048, norm_std=0.1, max_seq_len=16)
+    ids = S.make_prompt(3000, seed=13, vocab_size=2048)
+    o = OracleDecoder(w, max_seq_len=3072)
+    want, logits = o.generate_ids(ids, 5, keep_logits=True)
+    eng = _engine(w, 3072)
+    dump = torch.zeros(5, 2048, device="cuda")
+    C.set_logits_dump(dump)
+    try:
+        got = eng.generate_ids(ids, 5)
+    finally:
+        C.set_logits_dump(None)
+    err = float((dump.cpu() - logits).abs().max())
+    print(f"ctx 3000: max |logit - oracle| = {err:.3e}")
+    assert got == want and err < LOGIT_TOL
+
+
+def test_reduced_grid_gives_same_tokens(C, tiny_cfg):
+    """A smaller persistent grid changes every CTA's row ranges and the number of KV splits; tokens and
+    logits must not change beyond round-off."""
+    g = np.load(os.path.join(GOLDEN, "tiny_l2_v4096.npz"))
+    w = _tiny_weights(tiny_cfg)
+    ids = g["prompt"].tolist()
+    eng = _engine(w, tiny_cfg["max_seq_len"])
+    try:
+        for ctas in (8, 40, 97):
+            C.configure(max_ctas=ctas)
+            assert C.num_ctas() == ctas
+            dump = torch.zeros(tiny_cfg["steps"], tiny_cfg["vocab_size"], device="cuda")
+            C.set_logits_dump(dump)
+            try:
+                assert eng.generate_ids(ids, tiny_cfg["steps"]) == g["tokens"].tolist(), ctas
+            finally:
+                C.set_logits_dump(None)
+            assert (dump.cpu() - torch.from_numpy(g["logits"])).abs().max() < LOGIT_TOL
+    finally:
+        C.configure(max_ctas=0)
+
+
 def test_errors_are_reported_not_ignored(C, tiny_cfg):
     w = _tiny_weights(tiny_cfg)
     eng = _engine(w, tiny_cfg["max_seq_len"])
