@@ -52,9 +52,13 @@ def measured_peak_gbs():
         return 6650.0, "fallback"
 
 
-def step_bytes(prompt_len: int = PROMPT_LEN, decode_tokens: int = DECODE_TOKENS) -> int:
+def step_bytes(prompt_len: int = PROMPT_LEN, decode_tokens: int = DECODE_TOKENS, weights: str = "fp16") -> int:
     """Algorithmic HBM bytes of one step: sum over its tokens of weights + KV read + KV write."""
-    return sum(S.decode_step_bytes(prompt_len + i) for i in range(decode_tokens))
+    total = sum(S.decode_step_bytes(prompt_len + i) for i in range(decode_tokens))
+    if weights == "fp8":
+        import quantize
+        total += decode_tokens * (quantize.weight_bytes_fp8() - S.weight_bytes_fp16())
+    return total
 
 
 class ClockSampler:
@@ -217,9 +221,13 @@ def run_ours(args):
 
     PROMPT_LEN, DECODE_TOKENS = args.prompt_len, args.decode_tokens   # defaults: the benchmark configuration
     MAX_SEQ_LEN = PROMPT_LEN + DECODE_TOKENS
-    weights = S.weights_to(S.make_weights(seed=0, max_seq_len=16), str(device))
+    host_weights = S.make_weights(seed=0, max_seq_len=16)
+    if args.weights == "fp8":     # BASELINE.json configs[2] weight format at batch 1 (not the headline line)
+        import quantize
+        host_weights, _ = quantize.quantize_weights_fp8(host_weights)
+    weights = S.weights_to(host_weights, str(device))
     eng = Decoder(weights=weights, tokenizer=S.StubTokenizer(-1), verbose=False, max_seq_len=MAX_SEQ_LEN,
-                  device=str(device))
+                  device=str(device), weight_format=args.weights)
     prompt = S.make_prompt(PROMPT_LEN, seed=rank)   # each replica serves its own stream
     eng.reset()
     eng.prefill_ids(prompt[:-1])                    # untimed; fills 4095 cache rows
@@ -279,12 +287,12 @@ def run_ours(args):
 
     peak, peak_kind = measured_peak_gbs()
     avg_launch_s = statistics.mean(launch_ms) / 1e3
-    achieved = step_bytes(PROMPT_LEN, DECODE_TOKENS) / avg_launch_s / 1e9
+    achieved = step_bytes(PROMPT_LEN, DECODE_TOKENS, args.weights) / avg_launch_s / 1e9
     traffic = None   # DRAM bytes per launch from the committed ncu capture, scaled by tokens per launch
     try:
         with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
             per_token = json.load(f).get("qwen3_decode_megakernel_dram_bytes_per_token")
-        if per_token:
+        if per_token and args.weights == "fp16":
             traffic = per_token * DECODE_TOKENS
     except Exception:
         pass
@@ -293,15 +301,16 @@ def run_ours(args):
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": 1e3 * total_s / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
-            "config": {"workload": WORKLOAD if (PROMPT_LEN, DECODE_TOKENS) == (4096, 256) else
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp16" if args.weights == "fp16" else "fp8-e4m3 weights, fp32 math",
+            "data": "synthetic",
+            "config": {"weights": args.weights, "workload": WORKLOAD if (PROMPT_LEN, DECODE_TOKENS) == (4096, 256) else
                        f"profiling case: {PROMPT_LEN} prompt tokens, {DECODE_TOKENS} decode tokens per step",
                        "tokens_per_step": DECODE_TOKENS, "replicas": world,
                        "l2": "no flush needed: each token streams 1.19 GB of weights + 0.47 GB of KV, > 126 MB L2",
                        "grid_ctas": C.num_ctas()},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic, "peak_kind": f"of {peak_kind}",
-                         "bytes_per_launch": step_bytes(PROMPT_LEN, DECODE_TOKENS), "launch_ms": statistics.mean(launch_ms),
+                         "bytes_per_launch": step_bytes(PROMPT_LEN, DECODE_TOKENS, args.weights), "launch_ms": statistics.mean(launch_ms),
                          "frac_of_nominal_8TBs": achieved / 8000.0},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4,
                     "d2h_bytes_per_step": 4 * DECODE_TOKENS},
@@ -330,6 +339,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle leg (profiling runs)")
+    ap.add_argument("--weights", choices=["fp16", "fp8"], default="fp16",
+                    help="weight format (default fp16 = the benchmark configuration)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prefilled context (default: benchmark config)")
     ap.add_argument("--decode-tokens", type=int, default=DECODE_TOKENS,
                     help="greedy tokens per step (default: benchmark config; smaller for ncu captures)")

@@ -120,6 +120,13 @@ int qmk_set_inv_freq(const float *inv_freq64);
  * logits_out[step * vocab_size + row] (DEVICE fp32).  Null switches it off. */
 int qmk_set_logits_dump(float *logits_out);
 
+/* Weight format of ALL matrices reached through the layer table, the embedding
+ * and the LM head (norm vectors stay fp16).  0 (default): fp16 row-major [out,in].
+ * 1: FP8-E4M3 rows - each row is `in` e4m3 bytes followed by a 16-byte trailer
+ * whose first 4 bytes are the row's fp32 scale (w = scale * e4m3); row stride
+ * in + 16 bytes.  Activations, accumulation and the KV cache are unchanged. */
+int qmk_set_weight_format(int format);
+
 /* Performance knobs; negative keeps a value.  spin_sleep_ns: nanosleep between
  * polls of an exchange word (default 600).  l2_evict_first: 1 (default) streams
  * weights with an evict-first L2 policy, 0 uses the default policy. */

@@ -145,7 +145,8 @@ class Decoder:
     """Stateful greedy decoder on one B200 (API of Model/Qwen06B_architecture.py:188-448)."""
 
     def __init__(self, weights=None, tokenizer=None, model_name: str = "Qwen/Qwen3-0.6B", verbose: bool = True,
-                 max_seq_len: int = MAX_SEQ_LEN, rope_from_table: bool = False, device: str = "cuda"):
+                 max_seq_len: int = MAX_SEQ_LEN, rope_from_table: bool = False, device: str = "cuda",
+                 weight_format: str = "fp16"):
         if not torch.cuda.is_available():
             raise RuntimeError("Decoder needs a CUDA device (sm_100a); there is no CPU path")
         if weights is None:
@@ -160,6 +161,7 @@ class Decoder:
         dev = self._embed_weight.device
         self.num_layers = len(weights["layer_weights"]) // FIELDS_PER_LAYER
         self.vocab_size = int(self._embed_weight.shape[0])
+        self.weight_format = weight_format   # "fp16", or "fp8" (matrices packed by quantize.quantize_weights_fp8)
         cos, sin = weights.get("cos_table"), weights.get("sin_table")
         if cos is None or cos.shape[0] < self.max_seq_len or cos.device != dev:
             cos, sin = build_rope_tables(self.max_seq_len, device=dev)
@@ -194,6 +196,7 @@ class Decoder:
         self._prefill_op = _require_megakernel_op("prefill")
         if qwen_megakernel_C is not None and hasattr(qwen_megakernel_C, "configure"):
             qwen_megakernel_C.configure(vocab_size=self.vocab_size, rope_from_table=int(bool(rope_from_table)))
+            qwen_megakernel_C.set_weight_format(weight_format)
             qwen_megakernel_C.set_inv_freq(rope_inv_freq())
 
     # ------------------------------------------------------------------ argument packing

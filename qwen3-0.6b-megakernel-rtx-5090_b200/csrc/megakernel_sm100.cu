@@ -26,6 +26,7 @@
 //    drain, in-flight bulk copies are awaited, and the launch returns normally.
 
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -111,6 +112,7 @@ struct Params {
   float attn_scale;
   int spin_sleep_ns;             // back-off between polls of an exchange word (0 = none)
   int l2_evict_first;            // weight stream L2 policy: 1 evict_first, 0 default
+  int wfmt;                      // weight format of all matrices: 0 fp16 rows, 1 fp8-e4m3 rows + 16-byte scale trailer
   int repl;                      // copies of the exchange area (1, 2 or 4); CTA i polls copy i % repl
   int stream_inflight;           // max weight chunks in flight during layer phases (0 = ring depth)
 };
@@ -386,7 +388,14 @@ __device__ __forceinline__ void split_rows(int n, int ncta, int cta, int &r0, in
   r0 = static_cast<int>((static_cast<long long>(n) * cta) / ncta);
   r1 = static_cast<int>((static_cast<long long>(n) * (cta + 1)) / ncta);
 }
-__device__ __forceinline__ constexpr int kind_row_bytes(int kind) { return kind == K_O ? QS * 2 : kind == K_DOWN ? I * 2 : H * 2; }
+__device__ __forceinline__ constexpr int kind_k(int kind) { return kind == K_O ? QS : kind == K_DOWN ? I : H; }
+// Bytes of one weight row.  fp16: K halves.  fp8: K e4m3 bytes followed by a 16-byte trailer whose first
+// four bytes are the row's fp32 scale (the trailer keeps rows 16-byte aligned for bulk copies and brings
+// the scale into shared memory with the row).
+constexpr int FP8_TRAILER = 16;
+__device__ __forceinline__ constexpr int kind_row_bytes(int kind, int wfmt) {
+  return wfmt ? kind_k(kind) + FP8_TRAILER : kind_k(kind) * 2;
+}
 __device__ __forceinline__ constexpr int kind_rpc(int kind) { return (kind == K_QKV || kind == K_LM) ? 4 : kind == K_DOWN ? 1 : 2; }
 
 // Thread 0, once per launch.
@@ -413,10 +422,10 @@ __device__ void build_segtab(SegTab *t, int cta, int ncta, int vocab) {
 
 // Weight rows of segment s of phase `kind` (layer record `rec` in shared memory, or the LM head).
 __device__ __forceinline__ const unsigned char *seg_src(const SegTab *t, int kind, int s, const unsigned long long *rec,
-                                                        const __half *lm_head, int which_up) {
+                                                        const __half *lm_head, int which_up, int wfmt) {
   const unsigned long long base = (kind == K_LM) ? reinterpret_cast<unsigned long long>(lm_head)
                                                  : rec[t->tsel[kind][s] + which_up];
-  return reinterpret_cast<const unsigned char *>(base) + static_cast<size_t>(t->row0[kind][s]) * kind_row_bytes(kind);
+  return reinterpret_cast<const unsigned char *>(base) + static_cast<size_t>(t->row0[kind][s]) * kind_row_bytes(kind, wfmt);
 }
 
 // Attention work item of this CTA at position `pos`: kv head g, split s of S, old cache rows [p0, p1).
@@ -464,11 +473,11 @@ __device__ __forceinline__ bool produce_chunk(const Params &P, const Ctx &c, uin
 __device__ __forceinline__ bool produce_phase(const Params &P, const Ctx &c, uint32_t &idx, uint64_t pol, int kind,
                                               const unsigned long long *rec) {
   const SegTab *t = c.segs();
-  const int rb = kind_row_bytes(kind), rpc = kind_rpc(kind);
+  const int rb = kind_row_bytes(kind, P.wfmt), rpc = kind_rpc(kind);
   const int n = t->nseg[kind];
   for (int s = 0; s < n; ++s) {
-    const unsigned char *src = seg_src(t, kind, s, rec, P.lm_head, 0);
-    const unsigned char *src2 = (kind == K_GU) ? seg_src(t, kind, s, rec, P.lm_head, 1) : nullptr;
+    const unsigned char *src = seg_src(t, kind, s, rec, P.lm_head, 0, P.wfmt);
+    const unsigned char *src2 = (kind == K_GU) ? seg_src(t, kind, s, rec, P.lm_head, 1, P.wfmt) : nullptr;
     const int nrows = t->nrows[kind][s];
 #pragma unroll 1
     for (int r = 0; r < nrows; r += rpc) {
@@ -524,6 +533,38 @@ __device__ __forceinline__ void producer_main(const Params &P, const Ctx &c) {
 }
 
 // ----------------------------------------------------------------------------- consumer math
+// Eight consecutive weights of a row in shared memory as fp32: `idx8` counts groups of eight.
+__device__ __forceinline__ void load_w8(const unsigned char *row, int idx8, int wfmt, float (&w)[8]) {
+  if (wfmt == 0) {
+    const uint4 v = reinterpret_cast<const uint4 *>(row)[idx8];
+    const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(h[i]);
+      w[2 * i] = f.x;
+      w[2 * i + 1] = f.y;
+    }
+  } else {
+    const uint2 v = reinterpret_cast<const uint2 *>(row)[idx8];
+    const unsigned short *p = reinterpret_cast<const unsigned short *>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(p[i]), __NV_E4M3);
+      const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&hr));
+      w[2 * i] = f.x;
+      w[2 * i + 1] = f.y;
+    }
+  }
+}
+__device__ __forceinline__ float dot8f(const float (&w)[8], const float *a, float acc) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc = fmaf(w[i], a[i], acc);
+  return acc;
+}
+// fp32 scale of an fp8 row (1 for fp16 rows): first word of the trailer behind the K weights
+__device__ __forceinline__ float row_scale(const unsigned char *row, int k, int wfmt) {
+  return wfmt ? *reinterpret_cast<const float *>(row + k) : 1.0f;
+}
 __device__ __forceinline__ float dot8(const uint4 w, const float *a, float acc) {
   const __half2 *h = reinterpret_cast<const __half2 *>(&w);
 #pragma unroll
@@ -626,18 +667,23 @@ __device__ __forceinline__ void norm_to_regs(const Ctx &c, const float *x, float
 //   K_QKV : out[row] = W.a                       K_GU  : out[row] = silu(Wg.a) * (Wu.a)
 //   K_O / K_DOWN : out[row] = W.act + resid[row] (activations in shared memory)
 //   K_LM  : running (max, argmax) in best / best_i, optional logits dump
-__device__ __forceinline__ float row_partial_regs(const unsigned char *row, const float (&a)[32], int lane) {
-  const uint4 *w = reinterpret_cast<const uint4 *>(row);
+__device__ __forceinline__ float row_partial_regs(const unsigned char *row, const float (&a)[32], int lane, int wfmt) {
   float acc[4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) acc[j] = dot8(w[j * 32 + lane], &a[j * 8], 0.f);
-  return (acc[0] + acc[1]) + (acc[2] + acc[3]);
+  for (int j = 0; j < 4; ++j) {
+    float w[8];
+    load_w8(row, j * 32 + lane, wfmt, w);
+    acc[j] = dot8f(w, &a[j * 8], 0.f);
+  }
+  // every lane multiplies its partial by the row scale (1 for fp16): the sum over lanes is scaled once
+  return ((acc[0] + acc[1]) + (acc[2] + acc[3])) * row_scale(row, H, wfmt);
 }
 // K = 1024 phases (fused QKV, gate/up, LM head): RMSNorm of x into registers, then this CTA's rows.
 // One shared non-inlined copy (runtime `kind`); returns the advanced chunk counter.  For K_LM each warp
 // leaves its running (max, argmax) in s_misc[32 + warp] / s_misc[48 + warp].
 __device__ __noinline__ uint32_t gemv_k1024(const Params &P, Ctx c, int kind, const float *x, float ss,
                                             const __half *norm_w, unsigned long long *out, uint32_t tag, float *dump) {
+  const int wfmt = P.wfmt;
   float a[32];
   norm_to_regs(c, x, ss, norm_w, a);
   if (kind == K_LM && c.cta == 0 && c.warp == 0 && (P.normalized_out || P.hidden_out)) {  // reference-signature outputs
@@ -684,9 +730,9 @@ __device__ __noinline__ uint32_t gemv_k1024(const Params &P, Ctx c, int kind, co
         u[b] = 0.f;
         if (valid[b] && ok) {
           const uint32_t idx = c.chunk + static_cast<uint32_t>(c0 + b * G + wch);
-          const unsigned char *p = c.slot(idx) + sub * (H * 2);
-          v[b] = row_partial_regs(p, a, c.lane);
-          if (kind == K_GU) u[b] = row_partial_regs(p + SLOT_BYTES / 2, a, c.lane);
+          const unsigned char *p = c.slot(idx) + sub * kind_row_bytes(K_QKV, wfmt);
+          v[b] = row_partial_regs(p, a, c.lane, wfmt);
+          if (kind == K_GU) u[b] = row_partial_regs(p + SLOT_BYTES / 2, a, c.lane, wfmt);
         }
       }
       // The rows are in registers now: hand the slots back BEFORE publishing (mbarrier.arrive has
@@ -737,8 +783,9 @@ __device__ __noinline__ uint32_t gemv_k1024(const Params &P, Ctx c, int kind, co
 __device__ __noinline__ uint32_t gemv_wide(const Params &P, Ctx c, int kind, const float *act, const float *resid,
                                            unsigned long long *out, uint32_t tag) {
   const int rsh = kind == K_O ? 1 : 0;
-  const int RPC = 1 << rsh, G = CONS_WARPS >> rsh, rb = kind == K_O ? QS * 2 : I * 2;
-  const int kiters = rb / 512;   // 256 weights per warp pass: 8 or 12
+  const int wfmt = P.wfmt;
+  const int RPC = 1 << rsh, G = CONS_WARPS >> rsh, K = kind == K_O ? QS : I, rb = kind_row_bytes(kind, wfmt);
+  const int kiters = K / 256;    // 256 weights per warp pass: 8 or 12
   const SegTab *t = c.segs();
   const int sub = c.warp & (RPC - 1), wch = c.warp >> rsh;
   const int n = t->nseg[kind];
@@ -755,7 +802,7 @@ __device__ __noinline__ uint32_t gemv_wide(const Params &P, Ctx c, int kind, con
       if (ch < nchunks && row < nrows) {            // warp-uniform
         const uint32_t idx = c.chunk + static_cast<uint32_t>(ch);
         if (wait_full(P, c, idx)) {
-          const uint4 *w = reinterpret_cast<const uint4 *>(c.slot(idx) + sub * rb);
+          const unsigned char *wrow = c.slot(idx) + sub * rb;
           float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
           for (int j = 0; j < kiters; j += 4) {
@@ -765,10 +812,12 @@ __device__ __noinline__ uint32_t gemv_wide(const Params &P, Ctx c, int kind, con
               const float4 a0 = *reinterpret_cast<const float4 *>(act + k);
               const float4 a1 = *reinterpret_cast<const float4 *>(act + k + 4);
               const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-              acc[q] = dot8(w[(j + q) * 32 + c.lane], av, acc[q]);
+              float wv[8];
+              load_w8(wrow, (j + q) * 32 + c.lane, wfmt, wv);
+              acc[q] = dot8f(wv, av, acc[q]);
             }
           }
-          part = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+          part = ((acc[0] + acc[1]) + (acc[2] + acc[3])) * row_scale(wrow, K, wfmt);
           have = true;
         }
       }
@@ -790,12 +839,13 @@ __device__ __noinline__ uint32_t gemv_wide(const Params &P, Ctx c, int kind, con
 // Work item (kv head g, split s) on CTA g + 8*s: old cache rows [p0, p1); the last split also
 // normalises/rotates/stores the new K,V row and folds it in.  Writes either the final head
 // outputs (one split) or unnormalised partials.
-__device__ __forceinline__ void attention_phase(const Params &P, Ctx &c, const __half *nv, int layer, int pos,
-                                                const AttnItem &it, uint32_t tag) {
+__device__ __noinline__ uint32_t attention_phase(const Params &P, Ctx c, const __half *nv, int layer, int pos,
+                                                 uint32_t tag) {
+  const AttnItem it = attn_item(P, c, pos);
   float *s_q = c.f(F_Q), *s_knew = c.f(F_KNEW), *s_vnew = c.f(F_VNEW), *s_wpart = c.f(F_WPART), *s_misc = c.f(F_MISC);
   const float *s_cs = c.f(F_CS);
   const unsigned long long *qkv = c.llr + LL_QKV;
-  if (!it.active) return;
+  if (!it.active) return c.chunk;
   const int S = it.S, g = it.g, s = it.s;
   const bool owner = (s == S - 1);
   const int p0 = it.p0, p1 = it.p1;
@@ -971,10 +1021,11 @@ __device__ __forceinline__ void attention_phase(const Params &P, Ctx &c, const _
     for (int i = 0; i < 4; ++i) cache[c.lane + 32 * i] = __float2half_rn(snew[c.lane + 32 * i]);
     __threadfence();
   }
+  return c.chunk;
 }
 
 // Combines the S partials of each attention output element this CTA owns (S > 1 only).
-__device__ __forceinline__ void attention_merge(const Params &P, const Ctx &c, int S, uint32_t tag) {
+__device__ __noinline__ void attention_merge(const Params &P, const Ctx c, int S, uint32_t tag) {
   const int e0 = c.segs()->e0, e1 = c.segs()->e1;
 #pragma unroll 1
   for (int e = e0 + c.warp; e < e1; e += CONS_WARPS) {
@@ -1055,15 +1106,24 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
         c.f(F_CS)[64 + c.tid] = sn;
       }
       __threadfence();  // acquire side of the KV-row ordering (rows written in earlier steps)
-      const AttnItem item = attn_item(P, c, pos);
+      const int S_step = max(1, min(pos / max(1, P.split_len), min(MAX_SPLITS, max(1, c.ncta / NKV))));  // as attn_item
       // embedding row -> fp32 residual stream (megakernel_5090.cu:825-830)
       float ss = 0.f;
       {
-        const __half *row = P.embed + static_cast<size_t>(token) * H;
+        const unsigned char *erow = reinterpret_cast<const unsigned char *>(P.embed) +
+                                    static_cast<size_t>(token) * kind_row_bytes(K_LM, P.wfmt);
+        const float escale = P.wfmt ? __ldg(reinterpret_cast<const float *>(erow + H)) : 1.0f;
 #pragma unroll
         for (int j = 0; j < (H + CONS_THREADS - 1) / CONS_THREADS; ++j)
           if (c.tid + j * CONS_THREADS < H) {
-            const float v = __half2float(__ldg(row + c.tid + j * CONS_THREADS));
+            const int k = c.tid + j * CONS_THREADS;
+            float v;
+            if (P.wfmt) {
+              const __half_raw hr = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(__ldg(erow + k)), __NV_E4M3);
+              v = __half2float(*reinterpret_cast<const __half *>(&hr)) * escale;
+            } else {
+              v = __half2float(__ldg(reinterpret_cast<const __half *>(erow) + k));
+            }
             s_x[c.tid + j * CONS_THREADS] = v;
             ss = fmaf(v, v, ss);
           }
@@ -1080,9 +1140,9 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
         c.chunk = gemv_k1024(P, c, K_QKV, s_x, ss, nv + NB_IN_LN, P.ll + LL_QKV, tag, nullptr);
         // P2/P3: attention work items, then merge of split partials
         QMK_STAMP(layer * 12 + 1);
-        attention_phase(P, c, nv, layer, pos, item, tag);
+        c.chunk = attention_phase(P, c, nv, layer, pos, tag);
         QMK_STAMP(layer * 12 + 2);
-        if (item.S > 1) attention_merge(P, c, item.S, tag);
+        if (S_step > 1) attention_merge(P, c, S_step, tag);
         QMK_STAMP(layer * 12 + 3);
         // P4: O-proj + residual
         poll_vec(P, c, c.llr + LL_ATTN, QS, tag, s_vec);
@@ -1263,6 +1323,7 @@ struct Engine {
   unsigned long long *prof = nullptr;
   int spin_sleep_ns = 600;   // measured: 745 -> 695 us/token; without a pause the polls delay the stores they wait for
   int l2_evict_first = 1;
+  int wfmt = 0;              // 0 fp16, 1 fp8-e4m3 rows with scale trailer
   int repl = 4;              // measured: 835 -> 752 us/token at short context, 1152 -> 1061 at 4096
   int stream_inflight = 0;   // measured: pacing the stream changes nothing
   bool inv_freq_set = false;
@@ -1385,6 +1446,7 @@ int launch(Engine *e, Params &P, cudaStream_t stream, bool synchronize) {
   P.spin_sleep_ns = e->spin_sleep_ns;
   P.l2_evict_first = e->l2_evict_first;
   P.repl = e->repl;
+  P.wfmt = e->wfmt;
   P.stream_inflight = e->stream_inflight;
   e->seq += static_cast<uint32_t>(P.num_steps);
 
@@ -1467,6 +1529,15 @@ int qmk_set_logits_dump(float *logits_out) {
   Engine *e = current_engine_unlocked();
   if (!e) return QMK_ERR_CUDA;
   e->logits_out = logits_out;
+  return QMK_OK;
+}
+
+int qmk_set_weight_format(int format) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  Engine *e = current_engine_unlocked();
+  if (!e) return QMK_ERR_CUDA;
+  if (format != 0 && format != 1) return fail(e, QMK_ERR_BAD_ARGUMENT, "weight format must be 0 (fp16) or 1 (fp8-e4m3 rows)");
+  e->wfmt = format;
   return QMK_OK;
 }
 
@@ -1724,6 +1795,7 @@ int qmk_generate_static(int first_token_id, int num_steps, const void *embed_wei
   P.spin_sleep_ns = e->spin_sleep_ns;
   P.l2_evict_first = e->l2_evict_first;
   P.repl = 1;                 // the fixed array holds one copy of the exchange area
+  P.wfmt = e->wfmt;
   P.stream_inflight = e->stream_inflight;
   st.seq += static_cast<uint32_t>(num_steps);
   int grid = st.grid;

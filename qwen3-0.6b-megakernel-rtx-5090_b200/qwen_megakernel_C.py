@@ -50,6 +50,8 @@ _lib.qmk_set_logits_dump.argtypes = [_P]
 _lib.qmk_set_logits_dump.restype = _I
 _lib.qmk_set_tuning.argtypes = [_I, _I]
 _lib.qmk_set_tuning.restype = _I
+_lib.qmk_set_weight_format.argtypes = [_I]
+_lib.qmk_set_weight_format.restype = _I
 _lib.qmk_set_tuning2.argtypes = [_I, _I]
 _lib.qmk_set_tuning2.restype = _I
 _lib.qmk_set_profile_buffer.argtypes = [_P]
@@ -72,7 +74,7 @@ _lib.qmk_selftest_wait_timeout.restype = _I
 EXPORTED_SYMBOLS = (
     "launch_ldg_decode_direct", "launch_ldg_decode_persistent", "launch_ldg_generate_nosync",
     "launch_ldg_prefill", "qmk_abi_version", "qmk_configure", "qmk_set_inv_freq", "qmk_set_logits_dump",
-    "qmk_set_tuning", "qmk_set_tuning2", "qmk_set_profile_buffer", "qmk_decode", "qmk_generate", "qmk_generate_static", "qmk_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
+    "qmk_set_weight_format", "qmk_set_tuning", "qmk_set_tuning2", "qmk_set_profile_buffer", "qmk_decode", "qmk_generate", "qmk_generate_static", "qmk_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
     "qmk_scratch_bytes", "qmk_selftest_wait_timeout",
 )
 
@@ -204,6 +206,15 @@ def set_tuning(spin_sleep_ns=-1, l2_evict_first=-1, repl=-1, stream_inflight=-1)
     """Performance knobs (see include/qwen_megakernel.h); negative keeps a value."""
     _check(_lib.qmk_set_tuning(int(spin_sleep_ns), int(l2_evict_first)) == 0, "set_tuning failed")
     _check(_lib.qmk_set_tuning2(int(repl), int(stream_inflight)) == 0, "set_tuning failed")
+
+
+WEIGHT_FORMATS = {"fp16": 0, "fp8": 1}
+
+
+def set_weight_format(fmt) -> None:
+    """"fp16" (default) or "fp8" (e4m3 rows with a 16-byte scale trailer, see include/qwen_megakernel.h)."""
+    code = WEIGHT_FORMATS[fmt] if isinstance(fmt, str) else int(fmt)
+    _check(_lib.qmk_set_weight_format(code) == 0, f"set_weight_format({fmt!r}) failed")
 
 
 PROFILE_STRIDE = 768

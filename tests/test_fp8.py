@@ -1,0 +1,99 @@
+"""FP8-E4M3 weight variant: quantiser (CPU) and engine parity against the oracle run on the dequantised
+weights (GPU).  Tolerance: identical greedy tokens; logits within max-abs 3e-2 of the oracle on the SAME
+quantised weights (the engine and the oracle then differ only in summation order); the distance to the
+fp16 model is printed, not asserted - it is a property of the quantisation, not of the engine."""
+
+import pytest
+import torch
+
+import quantize as Q
+import synthetic as S
+from oracle.decoder_ref import Decoder as OracleDecoder
+
+
+def test_quantiser_scheme_and_row_format():
+    g = torch.Generator("cpu").manual_seed(0)
+    w = (torch.randn(6, 64, generator=g) * 0.02).to(torch.float16)
+    w[3] = 0                                                  # an all-zero row must not divide by zero
+    q, s = Q.quantize_rows_fp8(w)
+    assert q.dtype == torch.float8_e4m3fn and s.dtype == torch.float32 and s.shape == (6,)
+    assert torch.allclose(s[:3], w[:3].float().abs().amax(1) / 448.0) and s[3] == 1.0
+    deq = Q.dequantize_rows_fp8(q, s)
+    # e4m3 has 3 mantissa bits: relative error <= 2^-4 for normal values, absolute error bounded by the scale
+    assert ((deq - w.float()).abs() <= w.float().abs() * 2 ** -4 + s[:, None] * 2 ** -9 + 1e-12).all()
+    assert deq[3].abs().max() == 0
+    assert (deq.abs().amax(1)[:3] - w[:3].float().abs().amax(1)).abs().max() < 1e-6   # the row maximum is exact
+    packed = Q.pack_rows_fp8(q, s)
+    assert packed.shape == (6, 64 + 16) and packed.dtype == torch.uint8
+    assert torch.equal(packed[:, :64], q.view(torch.uint8))
+    assert torch.equal(packed[:, 64:68].contiguous().view(torch.float32).flatten(), s)
+    assert packed[:, 68:].abs().max() == 0
+
+
+def test_quantised_weight_dicts_and_byte_count():
+    w = S.make_weights(seed=2, num_layers=1, vocab_size=128)
+    eng, ora = Q.quantize_weights_fp8(w)
+    assert eng["lm_head_weight"] is eng["embed_weight"] and ora["lm_head_weight"] is ora["embed_weight"]
+    assert eng["embed_weight"].shape == (128, 1024 + 16)
+    shapes = [tuple(t.shape) for t in eng["layer_weights"]]
+    assert shapes[1] == (2048, 1040) and shapes[6] == (1024, 2064) and shapes[10] == (1024, 3088)
+    assert eng["layer_weights"][0].dtype == torch.float16          # norm vectors untouched
+    assert ora["layer_weights"][1].dtype == torch.float32
+    # ~598 MB per decode step for the full model (BASELINE.md gives 598.1 M with bare fp32 scales)
+    assert 0.595e9 < Q.weight_bytes_fp8() < 0.610e9
+
+
+@pytest.mark.gpu
+def test_fp8_engine_matches_oracle_on_dequantised_weights(built_library):
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import qwen_megakernel_C as C
+    from Model.Qwen06B_architecture import Decoder
+    vocab, steps = 4096, 8
+    w = S.make_weights(seed=3, num_layers=2, vocab_size=vocab, norm_std=0.1, max_seq_len=64)
+    ids = S.make_prompt(12, seed=5, vocab_size=vocab)
+    eng_w, ora_w = Q.quantize_weights_fp8(w)
+    want, logits = OracleDecoder(ora_w, max_seq_len=64).generate_ids(ids, steps, keep_logits=True)
+    _, logits16 = OracleDecoder(w, max_seq_len=64).generate_ids(ids, steps, keep_logits=True)
+    eng = Decoder(weights=S.weights_to(eng_w, "cuda"), verbose=False, max_seq_len=64, weight_format="fp8")
+    dump = torch.zeros(steps, vocab, device="cuda")
+    C.set_logits_dump(dump)
+    try:
+        got = eng.generate_ids(ids, steps)
+        again = eng.generate_ids(ids, steps)
+    finally:
+        C.set_logits_dump(None)
+        C.set_weight_format("fp16")
+    err = float((dump.cpu() - logits).abs().max())
+    dq = float((logits - logits16).abs().max())
+    print(f"fp8: max |logit - oracle(fp8 weights)| = {err:.3e}; quantisation moved the logits by up to {dq:.3e}")
+    assert got == want and again == want
+    assert err < 3e-2
+
+
+@pytest.mark.gpu
+def test_fp8_full_model_greedy_tokens(built_library):
+    """Full Qwen3-0.6B shape, fp8 weights, 32-token prompt, 16 greedy steps against the oracle on the
+    dequantised weights."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import qwen_megakernel_C as C
+    from Model.Qwen06B_architecture import Decoder
+    w = S.make_weights(seed=0, max_seq_len=128)
+    ids = S.make_prompt(32, seed=0)
+    eng_w, ora_w = Q.quantize_weights_fp8(w)
+    want, logits = OracleDecoder(ora_w, max_seq_len=128).generate_ids(ids, 16, keep_logits=True)
+    margins = torch.topk(logits, 2, dim=-1).values
+    min_margin = float((margins[:, 0] - margins[:, 1]).min())
+    eng = Decoder(weights=S.weights_to(eng_w, "cuda"), verbose=False, max_seq_len=128, weight_format="fp8")
+    dump = torch.zeros(16, S.VOCAB_SIZE, device="cuda")
+    C.set_logits_dump(dump)
+    try:
+        got = eng.generate_ids(ids, 16)
+    finally:
+        C.set_logits_dump(None)
+        C.set_weight_format("fp16")
+    err = float((dump.cpu() - logits).abs().max())
+    print(f"fp8 full: max |logit - oracle| = {err:.3e}; min greedy margin {min_margin:.3e}")
+    assert err < 3e-2
+    assert got == want
