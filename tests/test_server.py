@@ -103,3 +103,29 @@ def test_load_generator_against_the_app(client):
     assert all(r["output_tokens"] <= 3 for r in rep["results"])
     bad = loadgen.run(lambda body: (_ for _ in ()).throw(RuntimeError("down")), prompts[:2], "m", 3)
     assert bad["summary"]["num_failed"] == 2 and bad["summary"]["avg_latency_s"] == 0.0
+
+
+@pytest.mark.gpu
+def test_server_end_to_end_on_the_engine(built_library):
+    """The real Decoder (tiny seeded model, stub tokenizer) behind the HTTP surface: the answer is the oracle's
+    greedy continuation of the prompt's ids."""
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from Model.Qwen06B_architecture import Decoder
+    from oracle.decoder_ref import Decoder as Oracle
+    w = S.make_weights(seed=3, num_layers=2, vocab_size=4096, norm_std=0.1, max_seq_len=64)
+    ids = S.make_prompt(12, seed=5, vocab_size=4096)
+    want, _ = Oracle(w, max_seq_len=64).generate_ids(ids, 6)
+    dec = Decoder(weights=S.weights_to(w, "cuda"), tokenizer=S.StubTokenizer(-1, 4096), verbose=False, max_seq_len=64)
+    with TestClient(server.create_app(decoder=dec, model_name="tiny")) as c:
+        r = c.post("/v1/chat/completions", json={"model": "tiny", "max_tokens": 6,
+                                                 "messages": [{"role": "user", "content": " ".join(map(str, ids))}]})
+        assert r.status_code == 200, r.text
+        body = r.json()
+        assert body["choices"][0]["message"]["content"] == " ".join(map(str, want))
+        assert body["choices"][0]["finish_reason"] == "length"
+        assert body["usage"] == {"prompt_tokens": 12, "completion_tokens": 6, "total_tokens": 18}
+        rep = loadgen.run(lambda b: c.post("/v1/chat/completions", json=b).json(),
+                          loadgen.synthetic_prompts(4, 8, seed=2, vocab=4096), "tiny", 4)
+        assert rep["summary"]["num_failed"] == 0 and rep["summary"]["tokens_per_s"] > 0
