@@ -15,7 +15,8 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 SOURCES = [os.path.join(HERE, "csrc", "megakernel_sm100.cu")]
-HEADERS = [os.path.join(os.path.dirname(HERE), "include", "qwen_megakernel.h")]
+HEADERS = [os.path.join(os.path.dirname(HERE), "include", "qwen_megakernel.h"),
+           os.path.join(HERE, "csrc", "megakernel_device.cuh"), os.path.join(HERE, "csrc", "megakernel_params.h")]
 LIB_PATH = os.path.join(HERE, "libqwen_megakernel.so")
 
 NVCC_FLAGS = [
