@@ -226,36 +226,69 @@ def run_ours(args):
         import quantize
         host_weights, _ = quantize.quantize_weights_fp8(host_weights)
     weights = S.weights_to(host_weights, str(device))
-    eng = Decoder(weights=weights, tokenizer=S.StubTokenizer(-1), verbose=False, max_seq_len=MAX_SEQ_LEN,
-                  device=str(device), weight_format=args.weights)
-    prompt = S.make_prompt(PROMPT_LEN, seed=rank)   # each replica serves its own stream
-    eng.reset()
-    eng.prefill_ids(prompt[:-1])                    # untimed; fills 4095 cache rows
-    start_pos = eng.position
-    first = prompt[-1]
-    log = eng._output_log[:DECODE_TOKENS]
-    host_log = eng._output_log_cpu[:DECODE_TOKENS]
+    B = args.batch
+    if B == 1:
+        eng = Decoder(weights=weights, tokenizer=S.StubTokenizer(-1), verbose=False, max_seq_len=MAX_SEQ_LEN,
+                      device=str(device), weight_format=args.weights)
+        prompt = S.make_prompt(PROMPT_LEN, seed=rank)   # each replica serves its own stream
+        eng.reset()
+        eng.prefill_ids(prompt[:-1])                    # untimed; fills 4095 cache rows
+        start_pos = eng.position
+        first = prompt[-1]
+        log = eng._output_log[:DECODE_TOKENS]
+        host_log = eng._output_log_cpu[:DECODE_TOKENS]
 
-    def op_call():
-        eng._gen(first, DECODE_TOKENS, *eng._common(), log, eng.num_layers, start_pos, eng.max_seq_len,
-                 eng._attn_scale, -1)
+        def op_call():
+            eng._gen(first, DECODE_TOKENS, *eng._common(), log, eng.num_layers, start_pos, eng.max_seq_len,
+                     eng._attn_scale, -1)
 
-    def api_call():
-        # what Decoder.generate_ids does after prefill, with host buffers on both sides
-        log.fill_(-1)
-        op_call()
-        host_log.copy_(log)
-        out = []
-        for t in host_log.tolist():
-            if t == -1:
-                break
-            out.append(t)
-        return out
+        def api_call():
+            # what Decoder.generate_ids does after prefill, with host buffers on both sides
+            log.fill_(-1)
+            op_call()
+            host_log.copy_(log)
+            out = []
+            for t in host_log.tolist():
+                if t == -1:
+                    break
+                out.append(t)
+            return out
+    else:
+        # B sequences per launch (multi-sequence kernel), every one at the benchmark context length
+        from Model.Qwen06B_architecture import BatchDecoder
+        eng = BatchDecoder(weights=weights, tokenizer=S.StubTokenizer(-1), num_sequences=B, max_seq_len=MAX_SEQ_LEN,
+                           device=str(device), weight_format=args.weights)
+        prompts = [S.make_prompt(PROMPT_LEN, seed=rank * 16 + b) for b in range(B)]
+        for b in range(B):
+            eng._prefill_slot(b, prompts[b][:-1])       # untimed
+        firsts = [p[-1] for p in prompts]
+        starts = list(eng.positions)
+        logs = [eng._logs[b][:DECODE_TOKENS] for b in range(B)]
+        host_logs = eng._logs_cpu[:, :DECODE_TOKENS]
+        base = eng._base
+
+        def op_call():
+            eng._gen_batch(firsts, starts, DECODE_TOKENS, base._embed_weight, base._layer_weights_packed,
+                           base._final_norm_weight, base._lm_head_weight, base._cos_table, base._sin_table,
+                           eng._k_caches, eng._v_caches, logs, base.num_layers, eng.max_seq_len, base._attn_scale)
+
+        def api_call():
+            out = []
+            for b in range(B):
+                logs[b].fill_(-1)
+            op_call()
+            for b in range(B):
+                host_logs[b].copy_(logs[b])
+                for t in host_logs[b].tolist():
+                    if t == -1:
+                        break
+                    out.append(t)
+            return out
 
     for _ in range(max(args.warmup, 0)):
         op_call()
     ref_tokens = api_call()
-    assert len(ref_tokens) == DECODE_TOKENS
+    assert len(ref_tokens) == DECODE_TOKENS * B
 
     # ---- device-timed region: K steps, one launch each
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
@@ -273,7 +306,7 @@ def run_ours(args):
     total_s = t_begin.elapsed_time(t_end) / 1e3
     launch_ms = [a.elapsed_time(b) for a, b in ev]
     total_s = max_over_ranks(total_s, world, device)
-    value = aggregate(args.steps * DECODE_TOKENS, total_s, world)
+    value = aggregate(args.steps * DECODE_TOKENS * B, total_s, world)
 
     # ---- end-to-end region through the host API
     barrier(world)
@@ -283,37 +316,40 @@ def run_ours(args):
     torch.cuda.synchronize()
     e2e_s = max_over_ranks(time.perf_counter() - t0, world, device)
     assert out == ref_tokens, "decode is not reproducible run to run"
-    e2e_value = aggregate(args.steps * DECODE_TOKENS, e2e_s, world)
+    e2e_value = aggregate(args.steps * DECODE_TOKENS * B, e2e_s, world)
 
     peak, peak_kind = measured_peak_gbs()
     avg_launch_s = statistics.mean(launch_ms) / 1e3
-    achieved = step_bytes(PROMPT_LEN, DECODE_TOKENS, args.weights) / avg_launch_s / 1e9
+    # algorithmic bytes of a launch: weights once per step, KV of every sequence
+    kv_only = step_bytes(PROMPT_LEN, DECODE_TOKENS, "fp16") - DECODE_TOKENS * S.weight_bytes_fp16()
+    launch_bytes = step_bytes(PROMPT_LEN, DECODE_TOKENS, args.weights) + (B - 1) * kv_only
+    achieved = launch_bytes / avg_launch_s / 1e9
     traffic = None   # DRAM bytes per launch from the committed ncu capture, scaled by tokens per launch
     try:
         with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
             per_token = json.load(f).get("qwen3_decode_megakernel_dram_bytes_per_token")
-        if per_token and args.weights == "fp16":
+        if per_token and args.weights == "fp16" and B == 1:
             traffic = per_token * DECODE_TOKENS
     except Exception:
         pass
 
     if rank == 0:
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "metric": METRIC if B == 1 else f"batch-{B} decode tok/s (all sequences)", "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": 1e3 * total_s / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "fp16" if args.weights == "fp16" else "fp8-e4m3 weights, fp32 math",
             "data": "synthetic",
             "config": {"weights": args.weights, "workload": WORKLOAD if (PROMPT_LEN, DECODE_TOKENS) == (4096, 256) else
                        f"profiling case: {PROMPT_LEN} prompt tokens, {DECODE_TOKENS} decode tokens per step",
-                       "tokens_per_step": DECODE_TOKENS, "replicas": world,
+                       "tokens_per_step": DECODE_TOKENS * B, "sequences_per_launch": B, "replicas": world,
                        "l2": "no flush needed: each token streams 1.19 GB of weights + 0.47 GB of KV, > 126 MB L2",
                        "grid_ctas": C.num_ctas()},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic, "peak_kind": f"of {peak_kind}",
-                         "bytes_per_launch": step_bytes(PROMPT_LEN, DECODE_TOKENS, args.weights), "launch_ms": statistics.mean(launch_ms),
+                         "bytes_per_launch": launch_bytes, "launch_ms": statistics.mean(launch_ms),
                          "frac_of_nominal_8TBs": achieved / 8000.0},
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4,
-                    "d2h_bytes_per_step": 4 * DECODE_TOKENS},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * B,
+                    "d2h_bytes_per_step": 4 * DECODE_TOKENS * B},
             "gpu_launches": args.steps,
             "clocks": clocks.summary(),
         }
@@ -341,6 +377,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle leg (profiling runs)")
     ap.add_argument("--weights", choices=["fp16", "fp8"], default="fp16",
                     help="weight format (default fp16 = the benchmark configuration)")
+    ap.add_argument("--batch", type=int, default=1, choices=[1, 2, 3, 4],
+                    help="sequences per launch and GPU (default 1: the headline batch-1 configuration)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prefilled context (default: benchmark config)")
     ap.add_argument("--decode-tokens", type=int, default=DECODE_TOKENS,
                     help="greedy tokens per step (default: benchmark config; smaller for ncu captures)")

@@ -169,6 +169,28 @@ int qmk_prefill(
     int num_layers, int start_position, int max_seq_len, float attn_scale,
     cudaStream_t stream);
 
+/* Greedy decode of up to four independent sequences in ONE persistent launch:
+ * every weight row is streamed from HBM once per step and used by all
+ * sequences; the math warps of each CTA are split into one group per sequence.
+ * The reference decodes one sequence per launch (megakernel_5090.cu:1216-1260
+ * launch_ldg_generate_nosync); this is its multi-sequence form, the building
+ * block for the batched configurations.  Host arrays of num_sequences entries:
+ * first_token_ids, start_positions (each sequence's own cache length), and the
+ * DEVICE pointers k_caches / v_caches (one cache pair per sequence, same
+ * [layer][8][max_seq_len][128] fp16 shape, filled by qmk_prefill) and
+ * output_logs (num_steps ints each).  All sequences run num_steps steps; there
+ * is no EOS stop (cut the logs on the host).  With a logits dump set
+ * (qmk_set_logits_dump) the buffer is [sequence][step][vocab].  num_sequences
+ * is 1, 2, 3 or 4; two sequences may not share a cache or a log. */
+int qmk_generate_batch(
+    int num_sequences, const int *first_token_ids, const int *start_positions,
+    int num_steps, const void *embed_weight,
+    const struct LDGLayerWeight *layer_weights, const void *final_norm_weight,
+    const void *lm_head_weight, const void *cos_table, const void *sin_table,
+    void *const *k_caches, void *const *v_caches, int *const *output_logs,
+    int num_layers, int max_seq_len, float attn_scale, int synchronize,
+    cudaStream_t stream);
+
 /* qmk_generate for callers that cannot allocate device memory while running -
  * for example a server that handed all free HBM to its own cache pool when it
  * started, or a loop that must not hit cudaMalloc's device-wide

@@ -282,6 +282,91 @@ class Decoder:
         return self.tokenizer.decode(out, skip_special_tokens=True), len(ids), len(out)
 
 
+class BatchDecoder:
+    """Greedy decode of up to four independent sequences per launch.
+
+    The reference decodes one sequence per persistent launch
+    (Model/Qwen06B_architecture.py:398-448); this wraps the multi-sequence form of the same kernel
+    (``generate_batch`` op): weights are streamed once per step and shared by all sequences, each
+    sequence has its own KV cache and position.  Prompts are prefilled one after the other through
+    the ``prefill`` op, then all sequences decode together.
+    """
+
+    MAX_SEQUENCES = 4
+
+    def __init__(self, weights=None, tokenizer=None, num_sequences: int = 4, max_seq_len: int = MAX_SEQ_LEN,
+                 verbose: bool = False, **decoder_kw):
+        if not 1 <= int(num_sequences) <= self.MAX_SEQUENCES:
+            raise ValueError("num_sequences must be 1..4")
+        self.num_sequences = int(num_sequences)
+        # slot 0 owns the weights, tables and the first cache; the other slots only add caches
+        self._base = Decoder(weights=weights, tokenizer=tokenizer, max_seq_len=max_seq_len, verbose=verbose,
+                             **decoder_kw)
+        self.tokenizer = self._base.tokenizer
+        self.max_seq_len = self._base.max_seq_len
+        dev = self._base._embed_weight.device
+        self._k_caches = [self._base._k_cache] + [torch.zeros_like(self._base._k_cache)
+                                                   for _ in range(self.num_sequences - 1)]
+        self._v_caches = [self._base._v_cache] + [torch.zeros_like(self._base._v_cache)
+                                                   for _ in range(self.num_sequences - 1)]
+        self._logs = [torch.full((self.max_seq_len,), -1, dtype=torch.int32, device=dev)
+                      for _ in range(self.num_sequences)]
+        self._logs_cpu = torch.empty(self.num_sequences, self.max_seq_len, dtype=torch.int32).pin_memory()
+        self.positions = [0] * self.num_sequences
+        self._gen_batch = _require_megakernel_op("generate_batch")
+
+    def _prefill_slot(self, b: int, ids: Sequence[int]) -> None:
+        base = self._base
+        base._k_cache, base._v_cache = self._k_caches[b], self._v_caches[b]
+        try:
+            base._position = 0
+            base.prefill_ids(ids)
+        finally:
+            base._k_cache, base._v_cache = self._k_caches[0], self._v_caches[0]
+        self.positions[b] = len(ids)
+
+    def generate_ids(self, prompts: Sequence[Sequence[int]], max_tokens: int) -> List[List[int]]:
+        """One list of new token IDs per prompt (cut at EOS, which is not returned).  ``len(prompts)``
+        may be below ``num_sequences``; the launch then carries fewer sequences."""
+        n = len(prompts)
+        if not 1 <= n <= self.num_sequences:
+            raise ValueError(f"between 1 and {self.num_sequences} prompts per call")
+        max_tokens = int(max_tokens)
+        firsts = []
+        for b, ids in enumerate(prompts):
+            ids = list(ids)
+            if not ids:
+                raise ValueError("empty prompt")
+            if len(ids) - 1 + max_tokens > self.max_seq_len:
+                raise ValueError("prompt + max_tokens exceeds max_seq_len")
+            self._prefill_slot(b, ids[:-1])
+            firsts.append(ids[-1])
+        if max_tokens <= 0:
+            return [[] for _ in range(n)]
+        base = self._base
+        logs = [self._logs[b][:max_tokens] for b in range(n)]
+        for log in logs:
+            log.fill_(-1)
+        self._gen_batch(firsts, self.positions[:n], max_tokens, base._embed_weight, base._layer_weights_packed,
+                        base._final_norm_weight, base._lm_head_weight, base._cos_table, base._sin_table,
+                        self._k_caches[:n], self._v_caches[:n], logs, base.num_layers, self.max_seq_len,
+                        base._attn_scale)
+        eos = base._eos()
+        outs: List[List[int]] = []
+        for b in range(n):
+            host = self._logs_cpu[b, :max_tokens]
+            host.copy_(logs[b])
+            out: List[int] = []
+            for tok in host.tolist():
+                if tok == -1 or tok == eos:
+                    break
+                out.append(tok)
+            outs.append(out)
+            # cache rows past an EOS were written but are never read: the position counts what was returned
+            self.positions[b] += len(out)
+        return outs
+
+
 def generate(prompt: str, max_tokens: int = 50, verbose: bool = True) -> str:
     """Load the model, generate once, return the text."""
     text, _, _ = Decoder(verbose=verbose).generate(prompt, max_tokens)

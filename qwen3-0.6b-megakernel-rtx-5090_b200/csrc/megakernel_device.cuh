@@ -33,9 +33,13 @@ constexpr int CONS_WARPS = QMK_CONS_WARPS;
 constexpr int CONS_THREADS = CONS_WARPS * 32;   // 512 math threads
 constexpr int THREADS = CONS_THREADS + 32;      // + 1 producer warp
 constexpr int SLOT_BYTES = 8192;
+#if QMK_MAX_SEQ == 1
 constexpr int NSLOTS = 21;
+#else
+constexpr int NSLOTS = 13;       // every sequence keeps its own activations in shared memory: a shorter ring
+#endif
 static_assert(NSLOTS >= CONS_WARPS, "a group of chunks (up to one per warp) must fit in the ring");
-constexpr int EMPTY_UNITS = 4;   // arrival units that free a ring slot (rows-per-chunk is 4, 2 or 1)
+constexpr int EMPTY_UNITS = 4;   // single-sequence build: arrival units that free a ring slot (rows-per-chunk is 4, 2 or 1)
 constexpr int MAX_SPLITS = 24;   // attention work items per kv head (<= grid / 8)
 constexpr int MAX_CTAS = 256;
 constexpr int MAX_LAYERS = 48;
@@ -52,6 +56,8 @@ constexpr int LL_AMAX = LL_X2 + H;
 constexpr int LL_PART = LL_AMAX + 2 * MAX_CTAS;
 constexpr int LL_WORDS = LL_PART + NQ * MAX_SPLITS * PART_STRIDE;
 constexpr int MAX_REPL = 4;      // the allocated exchange area holds up to 4 copies
+// Exchange area layout: [copy][sequence][LL_WORDS]; the single-sequence build has one sequence per copy.
+constexpr int LL_REPL_STRIDE = QMK_MAX_SEQ * LL_WORDS;
 
 __constant__ float c_inv_freq[D / 2];
 
@@ -125,12 +131,12 @@ __device__ __forceinline__ void ll_store(unsigned long long *p, float v, uint32_
   unsigned long long w = (static_cast<unsigned long long>(tag) << 32) | __float_as_uint(v);
   asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
-// Publishes one exchange word to all `repl` copies of the area (copy stride LL_WORDS).
+// Publishes one exchange word to all `repl` copies of the area.
 __device__ __forceinline__ void ll_publish(unsigned long long *p, float v, uint32_t tag, int repl) {
   ll_store(p, v, tag);
   if (repl > 1) {
-    ll_store(p + LL_WORDS, v, tag);
-    if (repl > 2) { ll_store(p + 2 * LL_WORDS, v, tag); ll_store(p + 3 * LL_WORDS, v, tag); }
+    ll_store(p + LL_REPL_STRIDE, v, tag);
+    if (repl > 2) { ll_store(p + 2 * LL_REPL_STRIDE, v, tag); ll_store(p + 3 * LL_REPL_STRIDE, v, tag); }
   }
 }
 __device__ __forceinline__ unsigned long long ll_load(const unsigned long long *p) {
@@ -164,6 +170,7 @@ __device__ __forceinline__ float warp_max(float v) {
 
 constexpr size_t SMEM_RING = static_cast<size_t>(NSLOTS) * SLOT_BYTES;
 // fp32 regions (offsets in floats from the end of the ring)
+#if QMK_MAX_SEQ == 1
 constexpr int F_X = 0;                       // residual stream / layer input      [1024]
 constexpr int F_X1 = F_X + H;                // residual after attention           [1024]
 constexpr int F_VEC = F_X1 + H;              // attention output / MLP activations [3072]
@@ -176,6 +183,24 @@ constexpr int F_CS = F_WPART + CONS_WARPS * 2 * PART_STRIDE;  // cos[64], sin[64
 constexpr int F_AMAX = F_CS + 2 * (D / 2);   // argmax partials of all CTAs        [2*256]
 constexpr int F_MISC = F_AMAX + 2 * MAX_CTAS;  // [0,1] new-row scores, [16] token, [32..47]/[48..63] warp argmax
 constexpr int F_END = F_MISC + 64;
+#else
+// Multi-sequence build: one block of G_END floats per sequence (= per warp group), then the per-warp
+// attention partials of all twelve math warps.
+constexpr int G_X = 0;                       // residual stream / layer input      [1024]
+constexpr int G_X1 = G_X + H;                // residual after attention           [1024]
+constexpr int G_VEC = G_X1 + H;              // attention output / MLP activations [3072]
+constexpr int G_AMAX = G_VEC;                // argmax partials of all CTAs [2*256]: the LM head does not use G_VEC
+constexpr int G_RED = G_VEC + I;             // group reduction scratch            [32]
+constexpr int G_Q = G_RED + 32;              // rotated query heads                [2][128]
+constexpr int G_KNEW = G_Q + 2 * D;          // new K row (fp16-rounded)           [128]
+constexpr int G_VNEW = G_KNEW + D;           // new V row (fp16-rounded)           [128]
+constexpr int G_CS = G_VNEW + D;             // cos[64], sin[64] of this sequence's position
+constexpr int G_MISC = G_CS + 2 * (D / 2);   // [0,1] new-row scores, [16] token, [32..47]/[48..63] warp argmax
+constexpr int G_END = G_MISC + 64;
+constexpr int F_WPART = QMK_MAX_SEQ * G_END; // per-warp attention partials        [12][2][130]
+constexpr int F_END = F_WPART + CONS_WARPS * 2 * PART_STRIDE;
+static_assert(2 * MAX_CTAS <= I, "argmax partials alias the activation vector");
+#endif
 constexpr size_t OFF_FULL = SMEM_RING + static_cast<size_t>(F_END) * 4;   // mbarriers: full[NSLOTS]
 constexpr size_t OFF_EMPTY = OFF_FULL + NSLOTS * 8;                       //            empty[NSLOTS]
 constexpr size_t OFF_NFULL = OFF_EMPTY + NSLOTS * 8;   // mbarriers of the two norm-vector buffers
@@ -209,6 +234,15 @@ struct Ctx {
   unsigned char *smem;
   int tid, warp, lane, cta, ncta;
   uint32_t chunk;   // consumer-side running chunk index (uniform over consumer threads)
+#if QMK_MAX_SEQ > 1
+  // Multi-sequence build: the math warps are split into one group per sequence.
+  int seq;                         // sequence (= group) of this warp
+  int gw, gwarp, gtid, gthreads;   // warps per group; this warp / thread within its group; threads per group
+  unsigned long long *llw;         // copy 0 of this sequence's exchange area (publish target)
+  __device__ __forceinline__ float *g(int off) const {
+    return reinterpret_cast<float *>(smem + SMEM_RING) + seq * G_END + off;
+  }
+#endif
   __device__ __forceinline__ float *f(int off) const { return reinterpret_cast<float *>(smem + SMEM_RING) + off; }
   __device__ __forceinline__ uint64_t *full(uint32_t slot) const { return reinterpret_cast<uint64_t *>(smem + OFF_FULL) + slot; }
   __device__ __forceinline__ uint64_t *empty(uint32_t slot) const { return reinterpret_cast<uint64_t *>(smem + OFF_EMPTY) + slot; }
@@ -368,21 +402,35 @@ __device__ __forceinline__ const unsigned char *seg_src(const SegTab *t, int kin
 // Both the producer (to stream the rows) and the consumers (to use them) call this.
 constexpr int KV_ROWS_PER_CHUNK = 16;   // at most 16 K rows (4 KB) + 16 V rows (4 KB) per ring slot
 struct AttnItem { int S, g, s, p0, p1, nchunks, rpc; bool active; };
-__device__ __forceinline__ AttnItem attn_item(const Params &P, const Ctx &c, int pos) {
+// Entry b of a per-sequence launch-parameter array.  Written as selects on purpose: indexing a kernel
+// parameter array with a run-time value makes the compiler copy the array to the thread's stack.
+template <typename T>
+__device__ __forceinline__ T per_seq(const T (&arr)[qmkp::MAX_SEQ], int b) {
+  static_assert(qmkp::MAX_SEQ == 4, "written out for four entries");
+  return b == 0 ? arr[0] : b == 1 ? arr[1] : b == 2 ? arr[2] : arr[3];
+}
+// `b` of `nseq` sequences: each sequence's items start at a different CTA so that short contexts (few
+// items per sequence) land on different SMs.  `gw` = math warps that share the item's rows.
+__device__ __forceinline__ AttnItem attn_item(const Params &P, const Ctx &c, int b, int nseq, int gw, int pos) {
   AttnItem it;
   const int S_max = min(MAX_SPLITS, max(1, c.ncta / NKV));
   it.S = max(1, min(pos / max(1, P.split_len), S_max));
-  it.active = c.cta < NKV * it.S;
-  it.g = c.cta % NKV;
-  it.s = c.cta / NKV;
+  int local = c.cta;
+  if (nseq > 1) {
+    local -= (b * c.ncta) / nseq;
+    if (local < 0) local += c.ncta;
+  }
+  it.active = local < NKV * it.S;
+  it.g = local % NKV;
+  it.s = local / NKV;
   // old rows [p0, p1) of [0, pos); pos * S < 2^31, 32-bit division
   it.p0 = it.active ? static_cast<int>(static_cast<unsigned>(pos * it.s) / static_cast<unsigned>(it.S)) : 0;
   it.p1 = it.active ? static_cast<int>(static_cast<unsigned>(pos * (it.s + 1)) / static_cast<unsigned>(it.S)) : 0;
   // Rows per chunk chosen so that every warp gets the same number of (equally long) chunks: with a fixed
   // 16 rows per chunk, 15 chunks over 12 warps left three warps with twice the work of the others.
   const int rows = it.p1 - it.p0;
-  const int rounds = max(1, (rows + CONS_WARPS * KV_ROWS_PER_CHUNK - 1) / (CONS_WARPS * KV_ROWS_PER_CHUNK));
-  it.rpc = max(1, (rows + CONS_WARPS * rounds - 1) / (CONS_WARPS * rounds));
+  const int rounds = max(1, (rows + gw * KV_ROWS_PER_CHUNK - 1) / (gw * KV_ROWS_PER_CHUNK));
+  it.rpc = min(KV_ROWS_PER_CHUNK, max(1, (rows + gw * rounds - 1) / (gw * rounds)));
   it.nchunks = (rows + it.rpc - 1) / it.rpc;
   return it;
 }
@@ -431,6 +479,7 @@ __device__ __forceinline__ void producer_main(const Params &P, const Ctx &c) {
   const uint64_t pol = P.l2_evict_first ? l2_evict_first_policy() : l2_evict_normal_policy();
   uint32_t idx = 0;
   bool ok = true;
+  const int nseq = (QMK_MAX_SEQ > 1) ? P.nseq : 1;
 #pragma unroll 1
   for (int step = 0; ok && step < P.num_steps; ++step) {
 #pragma unroll 1
@@ -449,15 +498,16 @@ __device__ __forceinline__ void producer_main(const Params &P, const Ctx &c) {
         bulk_g2s(dst + NB_KNORM, reinterpret_cast<const void *>(rec[REC_KNORM]), D * 2, c.nfull(b), l2_evict_normal_policy());
       }
       ok = produce_phase(P, c, idx, pol, K_QKV, rec);
-      {  // this CTA's range of old K/V rows for the attention phase of this layer
-        const AttnItem it = attn_item(P, c, P.start_position + step);
+#pragma unroll 1
+      for (int b = 0; ok && b < nseq; ++b) {  // this CTA's range of old K/V rows of each sequence's attention item
+        const AttnItem it = attn_item(P, c, b, nseq, CONS_WARPS / nseq, per_seq(P.start_positions, b) + step);
         const size_t head_base = (static_cast<size_t>(l) * NKV + it.g) * static_cast<size_t>(P.max_seq_len) * D;
 #pragma unroll 1
         for (int r = it.p0; ok && r < it.p1; r += it.rpc) {
           const uint32_t bytes = static_cast<uint32_t>(min(it.rpc, it.p1 - r)) * D * 2;
           const size_t off = (head_base + static_cast<size_t>(r) * D) * 2;
-          ok = produce_chunk(P, c, idx, pol, reinterpret_cast<const unsigned char *>(P.k_cache) + off,
-                             reinterpret_cast<const unsigned char *>(P.v_cache) + off, bytes, P.stream_inflight);
+          ok = produce_chunk(P, c, idx, pol, reinterpret_cast<const unsigned char *>(per_seq(P.k_caches, b)) + off,
+                             reinterpret_cast<const unsigned char *>(per_seq(P.v_caches, b)) + off, bytes, P.stream_inflight);
         }
       }
 #pragma unroll 1
@@ -531,6 +581,51 @@ __device__ __forceinline__ float warp_reduce_scatter4(float v0, float v1, float 
   return k;
 }
 
+// RMSNorm of the fp32 vector x in shared memory (`ss` = this thread's share of sum x^2) into
+// per-lane registers: a[j*8+i] = x[k] * rstd * w[k], k = j*256 + lane*8 + i.
+__device__ __forceinline__ void norm_apply(const Ctx &c, const float *x, float tot, const __half *norm_w, float (&a)[32]) {
+  uint4 wn[4];
+  // The norm weights are loaded after the barrier of the sum on purpose: issued before it (while the
+  // CTA is still polling exchange words) the same loads measured ~100 us/token slower.
+#pragma unroll
+  for (int j = 0; j < 4; ++j) wn[j] = *reinterpret_cast<const uint4 *>(norm_w + j * 256 + c.lane * 8);
+  const float rstd = 1.0f / sqrtf(tot * (1.0f / H) + RMS_EPS);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int k = j * 256 + c.lane * 8;
+    const float4 x0 = *reinterpret_cast<const float4 *>(x + k);
+    const float4 x1 = *reinterpret_cast<const float4 *>(x + k + 4);
+    const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+    const __half2 *h = reinterpret_cast<const __half2 *>(&wn[j]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 wf = __half22float2(h[i]);
+      a[j * 8 + 2 * i] = xs[2 * i] * rstd * wf.x;
+      a[j * 8 + 2 * i + 1] = xs[2 * i + 1] * rstd * wf.y;
+    }
+  }
+}
+
+// This CTA's rows of one projection, streamed through the ring.  Warp w takes row (w % RPC) of chunk
+// (w / RPC) of each group of CONS_WARPS/RPC chunks; NB groups are handled per pass so that a warp
+// loads, multiplies and reduces all its rows of a layer phase together (one pass per layer phase), and
+// hands each slot back when its row is done.
+//   K_QKV : out[row] = W.a                       K_GU  : out[row] = silu(Wg.a) * (Wu.a)
+//   K_O / K_DOWN : out[row] = W.act + resid[row] (activations in shared memory)
+//   K_LM  : running (max, argmax) in best / best_i, optional logits dump
+__device__ __forceinline__ float row_partial_regs(const unsigned char *row, const float (&a)[32], int lane, int wfmt) {
+  float acc[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float w[8];
+    load_w8(row, j * 32 + lane, wfmt, w);
+    acc[j] = dot8f(w, &a[j * 8], 0.f);
+  }
+  // every lane multiplies its partial by the row scale (1 for fp16): the sum over lanes is scaled once
+  return ((acc[0] + acc[1]) + (acc[2] + acc[3])) * row_scale(row, H, wfmt);
+}
+#if QMK_MAX_SEQ == 1
+// ----------------------------------------------------------------------------- single-sequence math
 // sum over the 512 consumer threads; contains one consumer barrier
 __device__ __forceinline__ float block_sum(const Ctx &c, float v) {
   v = warp_sum(v);
@@ -570,50 +665,11 @@ __device__ __noinline__ float poll_vec(const Params &P, const Ctx c, const unsig
   return ss;
 }
 
-// RMSNorm of the fp32 vector x in shared memory (`ss` = this thread's share of sum x^2) into
-// per-lane registers: a[j*8+i] = x[k] * rstd * w[k], k = j*256 + lane*8 + i.
 __device__ __forceinline__ void norm_to_regs(const Ctx &c, const float *x, float ss, const __half *norm_w, float (&a)[32]) {
-  uint4 wn[4];
   const float tot = block_sum(c, ss);  // the barrier inside also publishes x
-  // The norm weights are loaded after the barrier on purpose: issued before it (while the CTA is
-  // still polling exchange words) the same loads measured ~100 us/token slower.
-#pragma unroll
-  for (int j = 0; j < 4; ++j) wn[j] = *reinterpret_cast<const uint4 *>(norm_w + j * 256 + c.lane * 8);
-  const float rstd = 1.0f / sqrtf(tot * (1.0f / H) + RMS_EPS);
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int k = j * 256 + c.lane * 8;
-    const float4 x0 = *reinterpret_cast<const float4 *>(x + k);
-    const float4 x1 = *reinterpret_cast<const float4 *>(x + k + 4);
-    const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-    const __half2 *h = reinterpret_cast<const __half2 *>(&wn[j]);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 wf = __half22float2(h[i]);
-      a[j * 8 + 2 * i] = xs[2 * i] * rstd * wf.x;
-      a[j * 8 + 2 * i + 1] = xs[2 * i + 1] * rstd * wf.y;
-    }
-  }
+  norm_apply(c, x, tot, norm_w, a);
 }
 
-// This CTA's rows of one projection, streamed through the ring.  Warp w takes row (w % RPC) of chunk
-// (w / RPC) of each group of CONS_WARPS/RPC chunks; NB groups are handled per pass so that a warp
-// loads, multiplies and reduces all its rows of a layer phase together (one pass per layer phase), and
-// hands each slot back when its row is done.
-//   K_QKV : out[row] = W.a                       K_GU  : out[row] = silu(Wg.a) * (Wu.a)
-//   K_O / K_DOWN : out[row] = W.act + resid[row] (activations in shared memory)
-//   K_LM  : running (max, argmax) in best / best_i, optional logits dump
-__device__ __forceinline__ float row_partial_regs(const unsigned char *row, const float (&a)[32], int lane, int wfmt) {
-  float acc[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    float w[8];
-    load_w8(row, j * 32 + lane, wfmt, w);
-    acc[j] = dot8f(w, &a[j * 8], 0.f);
-  }
-  // every lane multiplies its partial by the row scale (1 for fp16): the sum over lanes is scaled once
-  return ((acc[0] + acc[1]) + (acc[2] + acc[3])) * row_scale(row, H, wfmt);
-}
 // K = 1024 phases (fused QKV, gate/up, LM head): RMSNorm of x into registers, then this CTA's rows.
 // One shared non-inlined copy (runtime `kind`); returns the advanced chunk counter.  For K_LM each warp
 // leaves its running (max, argmax) in s_misc[32 + warp] / s_misc[48 + warp].
@@ -777,7 +833,7 @@ __device__ __noinline__ uint32_t gemv_wide(const Params &P, Ctx c, int kind, con
 // outputs (one split) or unnormalised partials.
 __device__ __noinline__ uint32_t attention_phase(const Params &P, Ctx c, const __half *nv, int layer, int pos,
                                                  uint32_t tag) {
-  const AttnItem it = attn_item(P, c, pos);
+  const AttnItem it = attn_item(P, c, 0, 1, CONS_WARPS, pos);
   float *s_q = c.f(F_Q), *s_knew = c.f(F_KNEW), *s_vnew = c.f(F_VNEW), *s_wpart = c.f(F_WPART), *s_misc = c.f(F_MISC);
   const float *s_cs = c.f(F_CS);
   const unsigned long long *qkv = c.llr + LL_QKV;
@@ -999,7 +1055,7 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
   c.ncta = gridDim.x;
   c.chunk = 0;
   c.repl = max(1, P.repl);
-  c.llr = P.ll + static_cast<size_t>(c.cta % c.repl) * LL_WORDS;
+  c.llr = P.ll + static_cast<size_t>(c.cta % c.repl) * LL_REPL_STRIDE;
 
   if (c.tid == 0) {
     for (int i = 0; i < NSLOTS; ++i) { mbar_init(c.full(i), 1); mbar_init(c.empty(i), EMPTY_UNITS); }
@@ -1186,5 +1242,7 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
     }
   }
 }
+
+#endif  // QMK_MAX_SEQ == 1
 
 }  // namespace QMK_NS

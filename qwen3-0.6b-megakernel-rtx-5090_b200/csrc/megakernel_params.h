@@ -14,6 +14,8 @@ struct __align__(16) LayerW {
   const void *pad;
 };
 
+constexpr int MAX_SEQ = 4;       // sequences one launch of the multi-sequence build can carry
+
 struct Params {
   const __half *embed;
   const LayerW *layers;
@@ -43,6 +45,13 @@ struct Params {
   int wfmt;                      // weight format of all matrices: 0 fp16 rows, 1 fp8-e4m3 rows + 16-byte scale trailer
   int repl;                      // copies of the exchange area (1, 2 or 4); CTA i polls copy i % repl
   int stream_inflight;           // max weight chunks in flight during layer phases (0 = ring depth)
+  // Sequences interleaved in one launch (multi-sequence build only; the single-sequence kernel reads
+  // the scalar fields above and the host mirrors them into entry 0 for the shared producer code).
+  int nseq;                      // 1 .. MAX_SEQ
+  int first_tokens[MAX_SEQ];
+  int start_positions[MAX_SEQ];
+  __half *k_caches[MAX_SEQ], *v_caches[MAX_SEQ];
+  int *output_logs[MAX_SEQ];     // decode: token per step of each sequence
 };
 
 }  // namespace qmkp

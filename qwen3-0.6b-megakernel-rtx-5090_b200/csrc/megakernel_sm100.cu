@@ -42,6 +42,7 @@
 #define QMK_NS qmk
 #define QMK_MAX_SEQ 1
 #include "megakernel_device.cuh"
+#include "megakernel_batch.h"
 
 namespace qmk {
 
@@ -153,6 +154,13 @@ int fail(Engine *e, int code, const std::string &msg) {
       return fail(e, QMK_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(err__));        \
   } while (0)
 
+// One allocation serves both builds of the kernel: [copy][sequence][LL_WORDS] words.
+size_t exchange_bytes() {
+  size_t words = static_cast<size_t>(qmk::LL_WORDS) * qmk::MAX_REPL;
+  if (qmk_batch::exchange_words() > words) words = qmk_batch::exchange_words();
+  return words * sizeof(unsigned long long);
+}
+
 int ensure_ready(Engine *e) {
   if (e->ready) return QMK_OK;
   cudaDeviceProp prop;
@@ -169,8 +177,10 @@ int ensure_ready(Engine *e) {
   if (per_sm < 1) return fail(e, QMK_ERR_NOT_RESIDENT, "megakernel does not fit on an SM");
   e->grid = e->num_sms;
   if (e->grid > qmk::MAX_CTAS) e->grid = qmk::MAX_CTAS;
-  QMK_CUDA(e, cudaMalloc(&e->ll, sizeof(unsigned long long) * qmk::LL_WORDS * qmk::MAX_REPL));
-  QMK_CUDA(e, cudaMemset(e->ll, 0, sizeof(unsigned long long) * qmk::LL_WORDS * qmk::MAX_REPL));
+  QMK_CUDA(e, cudaFuncSetAttribute(qmk_batch::kernel(), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(qmk_batch::smem_bytes())));
+  QMK_CUDA(e, cudaMalloc(&e->ll, exchange_bytes()));
+  QMK_CUDA(e, cudaMemset(e->ll, 0, exchange_bytes()));
   QMK_CUDA(e, cudaMalloc(&e->status, 16));
   QMK_CUDA(e, cudaMemset(e->status, 0, 16));
   QMK_CUDA(e, cudaHostAlloc(&e->status_host, 16, cudaHostAllocDefault));
@@ -193,18 +203,34 @@ int grid_for(const Engine *e) {
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Common launch path.  `P` arrives with the per-call fields set.
-int launch(Engine *e, Params &P, cudaStream_t stream, bool synchronize) {
+// The producer code shared by both builds reads per-sequence entries: entry 0 mirrors the scalar fields.
+void mirror_sequence0(Params &P) {
+  P.nseq = 1;
+  P.first_tokens[0] = P.first_token;
+  P.start_positions[0] = P.start_position;
+  P.k_caches[0] = P.k_cache;
+  P.v_caches[0] = P.v_cache;
+  P.output_logs[0] = P.output_log;
+}
+
+// Common launch path.  `P` arrives with the per-call fields set; `batch` selects the multi-sequence
+// build (per-sequence entries filled by the caller) instead of the single-sequence kernel.
+int launch(Engine *e, Params &P, cudaStream_t stream, bool synchronize, bool batch = false) {
   if (P.num_steps <= 0) return QMK_OK;
-  if (!P.embed || !P.layers || !P.k_cache || !P.v_cache || (!P.prefill && (!P.final_norm || !P.lm_head)))
+  if (!batch) mirror_sequence0(P);
+  if (!P.embed || !P.layers || (!P.prefill && (!P.final_norm || !P.lm_head)))
     return fail(e, QMK_ERR_BAD_ARGUMENT, "null weight or cache pointer");
-  if (!aligned16(P.embed) || !aligned16(P.layers) || !aligned16(P.k_cache) || !aligned16(P.v_cache) ||
-      (P.lm_head && !aligned16(P.lm_head)))
+  if (!aligned16(P.embed) || !aligned16(P.layers) || (P.lm_head && !aligned16(P.lm_head)))
     return fail(e, QMK_ERR_BAD_ARGUMENT, "weight, cache and layer-table pointers must be 16-byte aligned");
   if (P.num_layers < 1 || P.num_layers > qmk::MAX_LAYERS)
     return fail(e, QMK_ERR_BAD_ARGUMENT, "num_layers must be in [1, 48]");
-  if (P.start_position < 0 || P.start_position + P.num_steps > P.max_seq_len)
-    return fail(e, QMK_ERR_POSITION, "start_position + steps exceeds max_seq_len");
+  for (int b = 0; b < P.nseq; ++b) {
+    if (!P.k_caches[b] || !P.v_caches[b]) return fail(e, QMK_ERR_BAD_ARGUMENT, "null weight or cache pointer");
+    if (!aligned16(P.k_caches[b]) || !aligned16(P.v_caches[b]))
+      return fail(e, QMK_ERR_BAD_ARGUMENT, "weight, cache and layer-table pointers must be 16-byte aligned");
+    if (P.start_positions[b] < 0 || P.start_positions[b] + P.num_steps > P.max_seq_len)
+      return fail(e, QMK_ERR_POSITION, "start_position + steps exceeds max_seq_len");
+  }
   if (e->rope_from_table && (!P.cos_table || !P.sin_table))
     return fail(e, QMK_ERR_BAD_ARGUMENT, "rope_from_table needs cos/sin tables");
   int rc = ensure_ready(e);
@@ -212,7 +238,7 @@ int launch(Engine *e, Params &P, cudaStream_t stream, bool synchronize) {
 
   // Tags are (sequence number * 64 + layer); restart the sequence before it can wrap.
   if (static_cast<unsigned long long>(e->seq) + static_cast<unsigned long long>(P.num_steps) >= (1ull << 26)) {
-    QMK_CUDA(e, cudaMemsetAsync(e->ll, 0, sizeof(unsigned long long) * qmk::LL_WORDS * qmk::MAX_REPL, stream));
+    QMK_CUDA(e, cudaMemsetAsync(e->ll, 0, exchange_bytes(), stream));
     e->seq = 0;
   }
   if (!e->rope_from_table && P.max_seq_len > e->rope_cap) {   // grow-only, like the token staging buffer
@@ -246,8 +272,11 @@ int launch(Engine *e, Params &P, cudaStream_t stream, bool synchronize) {
 
   void *args[] = {&P};
   const int grid = grid_for(e);
-  cudaError_t err = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(qmk::qwen3_decode_megakernel), dim3(grid),
-                                                dim3(qmk::THREADS), args, qmk::SMEM_BYTES, stream);
+  cudaError_t err =
+      batch ? cudaLaunchCooperativeKernel(qmk_batch::kernel(), dim3(grid), dim3(qmk_batch::threads()), args,
+                                          qmk_batch::smem_bytes(), stream)
+            : cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(qmk::qwen3_decode_megakernel), dim3(grid),
+                                          dim3(qmk::THREADS), args, qmk::SMEM_BYTES, stream);
   if (err == cudaErrorCooperativeLaunchTooLarge)
     return fail(e, QMK_ERR_NOT_RESIDENT, "persistent grid cannot be co-resident on this device");
   if (err != cudaSuccess) return fail(e, QMK_ERR_CUDA, std::string("cudaLaunchCooperativeKernel: ") + cudaGetErrorString(err));
@@ -406,6 +435,46 @@ int qmk_generate(int first_token_id, int num_steps, const void *embed_weight, co
   return launch(e, P, stream, synchronize != 0);
 }
 
+int qmk_generate_batch(int num_sequences, const int *first_token_ids, const int *start_positions, int num_steps,
+                       const void *embed_weight, const LDGLayerWeight *layer_weights, const void *final_norm_weight,
+                       const void *lm_head_weight, const void *cos_table, const void *sin_table, void *const *k_caches,
+                       void *const *v_caches, int *const *output_logs, int num_layers, int max_seq_len, float attn_scale,
+                       int synchronize, cudaStream_t stream) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  Engine *e = current_engine_unlocked();
+  if (!e) return QMK_ERR_CUDA;
+  clear_error(e);
+  if (num_sequences < 1 || num_sequences > qmkp::MAX_SEQ)
+    return fail(e, QMK_ERR_BAD_ARGUMENT, "qmk_generate_batch: num_sequences must be 1, 2, 3 or 4");
+  if (!first_token_ids || !start_positions || !k_caches || !v_caches || !output_logs)
+    return fail(e, QMK_ERR_BAD_ARGUMENT, "qmk_generate_batch: null array argument");
+  Params P = base_params(embed_weight, layer_weights, final_norm_weight, lm_head_weight, cos_table, sin_table, nullptr,
+                         nullptr, num_layers, 0, max_seq_len, attn_scale);
+  P.num_steps = num_steps;
+  P.nseq = num_sequences;
+  for (int b = 0; b < num_sequences; ++b) {
+    if (num_steps > 0 && !output_logs[b]) return fail(e, QMK_ERR_BAD_ARGUMENT, "output_log is null");
+    if (first_token_ids[b] < 0 || first_token_ids[b] >= e->vocab)
+      return fail(e, QMK_ERR_BAD_TOKEN, "first token outside [0, vocab)");
+    for (int a = 0; a < b; ++a)
+      if (k_caches[a] == k_caches[b] || v_caches[a] == v_caches[b] || output_logs[a] == output_logs[b])
+        return fail(e, QMK_ERR_BAD_ARGUMENT, "qmk_generate_batch: two sequences share a cache or an output log");
+    P.first_tokens[b] = first_token_ids[b];
+    P.start_positions[b] = start_positions[b];
+    P.k_caches[b] = static_cast<__half *>(k_caches[b]);
+    P.v_caches[b] = static_cast<__half *>(v_caches[b]);
+    P.output_logs[b] = output_logs[b];
+  }
+  for (int b = num_sequences; b < qmkp::MAX_SEQ; ++b) {   // unused entries repeat entry 0 (never dereferenced)
+    P.first_tokens[b] = P.first_tokens[0];
+    P.start_positions[b] = P.start_positions[0];
+    P.k_caches[b] = P.k_caches[0];
+    P.v_caches[b] = P.v_caches[0];
+    P.output_logs[b] = P.output_logs[0];
+  }
+  return launch(e, P, stream, synchronize != 0, true);
+}
+
 int qmk_prefill(const int *token_ids_host, int num_tokens, const void *embed_weight,
                 const LDGLayerWeight *layer_weights, const void *final_norm_weight, const void *cos_table,
                 const void *sin_table, void *k_cache, void *v_cache, int num_layers, int start_position,
@@ -467,7 +536,7 @@ int qmk_num_ctas(void) {
 }
 
 long long qmk_scratch_bytes(void) {
-  return static_cast<long long>(sizeof(unsigned long long)) * qmk::LL_WORDS * qmk::MAX_REPL + 16;
+  return static_cast<long long>(exchange_bytes()) + 16;
 }
 
 int qmk_selftest_wait_timeout(int budget_us) {
@@ -589,6 +658,7 @@ int qmk_generate_static(int first_token_id, int num_steps, const void *embed_wei
   P.spin_sleep_ns = e->spin_sleep_ns;
   P.l2_evict_first = e->l2_evict_first;
   P.repl = 1;                 // the fixed array holds one copy of the exchange area
+  mirror_sequence0(P);
   P.wfmt = e->wfmt;
   P.stream_inflight = e->stream_inflight;
   st.seq += static_cast<uint32_t>(num_steps);
