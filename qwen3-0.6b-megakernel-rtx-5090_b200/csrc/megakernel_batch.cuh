@@ -602,7 +602,7 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_batch_megakernel(cons
     mbar_init(c.nfull(0), 1);
     mbar_init(c.nfull(1), 1);
     volatile int *fl = c.flags();
-    fl[0] = 0; fl[1] = 0; fl[2] = 0; fl[3] = 0; fl[4] = 0; fl[5] = 0;
+    fl[0] = 0; fl[1] = 0; fl[2] = 0; fl[3] = 0; fl[4] = 0; fl[5] = 0; fl[6] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (tid == 32) build_segtab(reinterpret_cast<SegTab *>(smem + OFF_SEGS), blockIdx.x, gridDim.x, P.vocab);

@@ -204,7 +204,8 @@ static_assert(2 * MAX_CTAS <= I, "argmax partials alias the activation vector");
 constexpr size_t OFF_FULL = SMEM_RING + static_cast<size_t>(F_END) * 4;   // mbarriers: full[NSLOTS]
 constexpr size_t OFF_EMPTY = OFF_FULL + NSLOTS * 8;                       //            empty[NSLOTS]
 constexpr size_t OFF_NFULL = OFF_EMPTY + NSLOTS * 8;   // mbarriers of the two norm-vector buffers
-constexpr size_t OFF_FLAGS = OFF_NFULL + 16;           // int[4]: abort, stop, issued chunks, consumed chunks
+constexpr size_t OFF_FLAGS = OFF_NFULL + 16;           // int[16]: 0 abort, 1 stop, 2 issued chunks (at exit), 3 consumed chunks,
+                                                       // 4/5 norm-buffer fills, 6 issued chunks (running)
 constexpr size_t OFF_LAYERS = OFF_FLAGS + 64;          // copy of the layer pointer table, 12 x u64 per layer
 // Norm vectors of a layer (fp16): in_ln[1024] | post_ln[1024] | q_norm[128] | k_norm[128]; two buffers,
 // layer parity selects one.  The producer copies them in when it starts a layer's weights.
@@ -347,10 +348,32 @@ __device__ __forceinline__ bool mbar_wait(const Params &P, const Ctx &c, uint64_
     }
   }
 }
+// Waits until ring chunk `idx` has landed in its slot.  A parity wait can only tell two consecutive
+// uses of a slot apart: asked about use n while use n-1 is still in flight, it answers for use n-2 and
+// says "complete".  So the wait first makes sure the producer has issued chunk `idx` (flags()[6] counts
+// issued chunks): from then on the slot's barrier is in use n and the parity is unambiguous.  Warps
+// that jump ahead in the ring (a group skipping another sequence's cache rows) depend on this.
+__device__ __forceinline__ bool chunk_wait(const Params &P, const Ctx &c, uint32_t idx) {
+  volatile int *fl = c.flags();
+  if (static_cast<uint32_t>(fl[6]) <= idx) {
+    unsigned long long t0 = 0;
+    uint32_t it = 0;
+    for (;;) {
+      if (static_cast<uint32_t>(fl[6]) > idx) break;
+      if ((++it & 31u) == 0u) {
+        if (fl[0]) return false;
+        if (ld_relaxed_u32(P.status) != 0u) { fl[0] = 1; return false; }
+        const unsigned long long t = now_ns();
+        if (t0 == 0) t0 = t;
+        if (t - t0 > P.timeout_ns) { raise_error(P, c, QMK_ERR_WAIT_TIMEOUT, WHERE_FULL); return false; }
+      }
+    }
+  }
+  return mbar_wait(P, c, c.full(idx % NSLOTS), (idx / NSLOTS) & 1u, WHERE_FULL, false);
+}
 // The whole warp takes the same branch afterwards (shuffles follow).
 __device__ __forceinline__ bool wait_full(const Params &P, const Ctx &c, uint32_t idx) {
-  const bool ok = mbar_wait(P, c, c.full(idx % NSLOTS), (idx / NSLOTS) & 1u, WHERE_FULL, false);
-  return __all_sync(0xffffffffu, ok);
+  return __all_sync(0xffffffffu, chunk_wait(P, c, idx));
 }
 
 // Rows [r0, r1) of an n-row matrix owned by CTA `cta` of `ncta` (launch-time only: 64-bit divisions).
@@ -451,6 +474,8 @@ __device__ __forceinline__ bool produce_chunk(const Params &P, const Ctx &c, uin
   bulk_g2s(dst, src, bytes, c.full(slot), pol);
   if (src2) bulk_g2s(dst + SLOT_BYTES / 2, src2, bytes, c.full(slot), pol);
   ++idx;
+  __threadfence_block();          // the barrier's new use is visible before the count that announces it
+  c.flags()[6] = static_cast<int>(idx);
   return true;
 }
 
@@ -712,7 +737,7 @@ __device__ __noinline__ uint32_t gemv_k1024(const Params &P, Ctx c, int kind, co
         valid[b] = ch < nchunks && ((ch << rsh) + sub) < nrows;          // warp-uniform
         if (valid[b]) {
           const uint32_t idx = c.chunk + static_cast<uint32_t>(ch);
-          ok &= mbar_wait(P, c, c.full(idx % NSLOTS), (idx / NSLOTS) & 1u, WHERE_FULL, false);
+          ok &= chunk_wait(P, c, idx);
         }
       }
       ok = __all_sync(0xffffffffu, ok);   // the whole warp takes the same branch (shuffles follow)
@@ -1062,7 +1087,7 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
     mbar_init(c.nfull(0), 1);
     mbar_init(c.nfull(1), 1);
     volatile int *fl = c.flags();
-    fl[0] = 0; fl[1] = 0; fl[2] = 0; fl[3] = 0; fl[4] = 0; fl[5] = 0;
+    fl[0] = 0; fl[1] = 0; fl[2] = 0; fl[3] = 0; fl[4] = 0; fl[5] = 0; fl[6] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (c.tid == 32) build_segtab(reinterpret_cast<SegTab *>(smem + OFF_SEGS), c.cta, c.ncta, P.vocab);

@@ -95,6 +95,26 @@ def test_mixed_context_lengths_split_and_unsplit(C):
     assert (eng._v_caches[0][:, :, :n].float().cpu() - o.v_cache[:, :, :n].float()).abs().max() < 8e-3
 
 
+def test_long_contexts_jump_several_ring_laps(C):
+    """Four contexts above 2000 tokens: every sequence's attention item brings about nine cache chunks
+    into the 13-slot ring, so the later groups jump more than two ring laps ahead when they skip the
+    other sequences' chunks (the case the issued-chunk check in front of the parity wait exists for)."""
+    w = S.make_weights(seed=8, num_layers=2, vocab_size=2048, norm_std=0.1, max_seq_len=16)
+    lens = [2300, 2200, 2100, 2050]
+    prompts = [S.make_prompt(L, seed=80 + i, vocab_size=2048) for i, L in enumerate(lens)]
+    steps = 4
+    want, logits = _oracle(w, 2560, prompts, steps)
+    eng = _batch_engine(w, 4, 2560)
+    got, dump = _run_with_dump(C, eng, prompts, steps, 2048)
+    for b in range(4):
+        err = float((dump[b] - logits[b]).abs().max())
+        print(f"long contexts, sequence {b} (len {lens[b]}): max |logit - oracle| = {err:.3e}")
+        assert got[b] == want[b]
+        assert err < LOGIT_TOL
+    eng2 = _batch_engine(w, 2, 2560)
+    assert eng2.generate_ids(prompts[:2], steps) == want[:2]
+
+
 def test_full_model_four_sequences_match_single_sequence_and_golden(C, full_cfg):
     """Qwen3-0.6B shape.  Sequence 0 is the golden prompt (token IDs from the committed oracle run);
     all four must equal what the single-sequence engine produces for the same prompts."""
