@@ -592,6 +592,18 @@ __device__ __noinline__ bool grp_aborted(const Params &P) {
   return grp_any(c, c.flags()[0] != 0);
 }
 
+// Debug timestamps: thread 0 of every group, last step only, to prof[(seq * grid + cta) * PROF_STRIDE + slot]
+// (same slot numbering as the single-sequence kernel).
+#define QMKB_STAMP(slot)                                                                              \
+  do {                                                                                                \
+    if (P.prof && step == P.num_steps - 1 && (threadIdx.x & 31) == 0) grp_stamp(P, (slot));            \
+  } while (0)
+__device__ __noinline__ void grp_stamp(const Params &P, int slot) {
+  const Ctx c = make_ctx(P, 0u);
+  if (c.gtid == 0)
+    P.prof[(static_cast<size_t>(c.seq) * c.ncta + c.cta) * PROF_STRIDE + slot] = now_ns();
+}
+
 // ----------------------------------------------------------------------------- the kernel
 __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_batch_megakernel(const __grid_constant__ Params P) {
   unsigned char *smem = batch_smem;
@@ -625,21 +637,35 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_batch_megakernel(cons
       bool aborted = false;
 #pragma unroll 1
       for (int layer = 0; layer < P.num_layers && !aborted; ++layer) {
+        QMKB_STAMP(layer * 12 + 0);
         chunk = grp_gemv_k1024(P, chunk, K_QKV, layer, step, ss);    // input RMSNorm + fused QKV rows
+        QMKB_STAMP(layer * 12 + 1);
         chunk = grp_attention(P, chunk, layer, step);                // this sequence's attention work item
+        QMKB_STAMP(layer * 12 + 2);
         grp_attention_merge(P, layer, step);                         // merge of split partials
+        QMKB_STAMP(layer * 12 + 3);
         grp_poll_vec(P, LL_ATTN, layer, step);
+        QMKB_STAMP(layer * 12 + 4);
         chunk = grp_gemv_wide(P, chunk, K_O, layer, step);           // O-proj + residual
+        QMKB_STAMP(layer * 12 + 5);
         ss = grp_poll_vec(P, LL_X1, layer, step);
+        QMKB_STAMP(layer * 12 + 6);
         chunk = grp_gemv_k1024(P, chunk, K_GU, layer, step, ss);     // post-attention RMSNorm + gate/up + SwiGLU
+        QMKB_STAMP(layer * 12 + 7);
         grp_poll_vec(P, LL_INTER, layer, step);
+        QMKB_STAMP(layer * 12 + 8);
         chunk = grp_gemv_wide(P, chunk, K_DOWN, layer, step);        // down-proj + residual
+        QMKB_STAMP(layer * 12 + 9);
         ss = grp_poll_vec(P, LL_X2, layer, step);                    // next layer's input
+        QMKB_STAMP(layer * 12 + 10);
         aborted = grp_aborted(P);
       }
       if (aborted) break;
+      QMKB_STAMP(P.num_layers * 12 + 0);
       chunk = grp_gemv_k1024(P, chunk, K_LM, 0, step, ss);           // final RMSNorm + tied LM head
+      QMKB_STAMP(P.num_layers * 12 + 1);
       token = grp_argmax(P, step);
+      QMKB_STAMP(P.num_layers * 12 + 2);
       if (token < 0) break;
     }
     const Ctx c = make_ctx(P, chunk);

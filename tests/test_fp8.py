@@ -97,3 +97,33 @@ def test_fp8_full_model_greedy_tokens(built_library):
     print(f"fp8 full: max |logit - oracle| = {err:.3e}; min greedy margin {min_margin:.3e}")
     assert err < 3e-2
     assert got == want
+
+
+@pytest.mark.gpu
+def test_fp8_four_sequences_per_launch(built_library):
+    """FP8 weights through the multi-sequence launch (the B = 4 shape of the FP8 configuration): every
+    sequence against the oracle on the dequantised weights."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import qwen_megakernel_C as C
+    from Model.Qwen06B_architecture import BatchDecoder
+    vocab, steps = 4096, 6
+    w = S.make_weights(seed=3, num_layers=2, vocab_size=vocab, norm_std=0.1, max_seq_len=16)
+    eng_w, ora_w = Q.quantize_weights_fp8(w)
+    lens = [40, 300, 9, 150]
+    prompts = [S.make_prompt(L, seed=70 + i, vocab_size=vocab) for i, L in enumerate(lens)]
+    eng = BatchDecoder(weights=S.weights_to(eng_w, "cuda"), tokenizer=S.StubTokenizer(-1, vocab), num_sequences=4,
+                       max_seq_len=384, weight_format="fp8")
+    dump = torch.zeros(4, steps, vocab, device="cuda")
+    C.set_logits_dump(dump)
+    try:
+        got = eng.generate_ids(prompts, steps)
+    finally:
+        C.set_logits_dump(None)
+        C.set_weight_format("fp16")
+    for b in range(4):
+        want, logits = OracleDecoder(ora_w, max_seq_len=384).generate_ids(prompts[b], steps, keep_logits=True)
+        err = float((dump[b].cpu() - logits).abs().max())
+        print(f"fp8 batch 4, sequence {b}: max |logit - oracle(fp8 weights)| = {err:.3e}")
+        assert got[b] == want
+        assert err < 3e-2
