@@ -368,6 +368,68 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_continuous(args):
+    """Continuous-batching job (the multi-replica serving configuration, scaled by --continuous): N requests
+    per GPU, prompt lengths uniform in [64, 2048], 128 greedy tokens each, up to --batch live sequences.
+    Wall-clock of the whole job, prefill included; one JSON line with its own metric name."""
+    rank, world, local = dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the engine has no CPU path")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    import build
+    build.build()
+    from Model.Qwen06B_architecture import BatchDecoder
+    from scheduler import ContinuousBatcher
+    slots = max(args.batch, 2)
+    new_tokens = 128
+    weights = S.weights_to(S.make_weights(seed=0, max_seq_len=16), str(device))
+    eng = BatchDecoder(weights=weights, tokenizer=S.StubTokenizer(-1), num_sequences=slots, max_seq_len=2048 + new_tokens,
+                       device=str(device))
+    gen = torch.Generator("cpu").manual_seed(rank)             # a different request stream per replica
+    lens = torch.randint(64, 2049, (args.continuous,), generator=gen).tolist()
+    prompts = [S.make_prompt(L, seed=1000 * rank + i) for i, L in enumerate(lens)]
+    prefill_s = [0.0]
+    inner = eng.prefill_slot
+
+    def timed_prefill(b, ids):
+        t = time.perf_counter()
+        inner(b, ids)
+        prefill_s[0] += time.perf_counter() - t
+    eng.prefill_slot = timed_prefill
+    sch = ContinuousBatcher(eng, eos_token_id=None, quantum=32)
+    sch.submit(prompts[0][:64], 8)                             # warm-up: both kernels, all buffers
+    sch.run_until_idle()
+    prefill_s[0] = 0.0
+    launches0 = sch.launches
+    barrier(world)
+    with ClockSampler(local) as clocks:
+        t0 = time.perf_counter()
+        futs = [sch.submit(p, new_tokens) for p in prompts]
+        sch.run_until_idle()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+    n_out = sum(len(f.result().tokens) for f in futs)
+    assert n_out == args.continuous * new_tokens
+    wall = max_over_ranks(wall, world, device)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "continuous-batching generated tok/s (prefill included)", "value": world * n_out / wall,
+            "unit": UNIT, "n_gpus": world, "requests_per_gpu": args.continuous, "live_sequences": slots,
+            "new_tokens_per_request": new_tokens, "prompt_tokens": sum(lens), "wall_s": wall,
+            "prefill_s": prefill_s[0], "decode_s": wall - prefill_s[0],
+            "decode_only_tok_s": n_out / max(wall - prefill_s[0], 1e-9), "launches": sch.launches - launches0,
+            "scaling": "weak", "data": "synthetic", "dtype": "fp16", "clocks": clocks.summary(),
+            "note": "rank 0's own prefill/decode split; value uses the slowest replica's wall time"}))
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -379,12 +441,17 @@ def main():
                     help="weight format (default fp16 = the benchmark configuration)")
     ap.add_argument("--batch", type=int, default=1, choices=[1, 2, 3, 4],
                     help="sequences per launch and GPU (default 1: the headline batch-1 configuration)")
+    ap.add_argument("--continuous", type=int, default=0, metavar="N",
+                    help="instead of the headline workload: N requests per GPU through the continuous-batching "
+                         "scheduler (prompt lengths 64..2048, 128 new tokens each, --batch live sequences)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prefilled context (default: benchmark config)")
     ap.add_argument("--decode-tokens", type=int, default=DECODE_TOKENS,
                     help="greedy tokens per step (default: benchmark config; smaller for ncu captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.continuous > 0:
+        run_continuous(args)
     else:
         run_ours(args)
 

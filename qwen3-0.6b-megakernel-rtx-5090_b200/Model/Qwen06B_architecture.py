@@ -315,7 +315,12 @@ class BatchDecoder:
         self.positions = [0] * self.num_sequences
         self._gen_batch = _require_megakernel_op("generate_batch")
 
-    def _prefill_slot(self, b: int, ids: Sequence[int]) -> None:
+    def prefill_slot(self, b: int, ids: Sequence[int]) -> None:
+        """Fill slot ``b``'s KV cache with ``ids`` from position 0 (the ``prefill`` op)."""
+        if not 0 <= b < self.num_sequences:
+            raise ValueError("slot out of range")
+        if len(ids) > self.max_seq_len:
+            raise ValueError("prompt exceeds max_seq_len")
         base = self._base
         base._k_cache, base._v_cache = self._k_caches[b], self._v_caches[b]
         try:
@@ -324,6 +329,36 @@ class BatchDecoder:
         finally:
             base._k_cache, base._v_cache = self._k_caches[0], self._v_caches[0]
         self.positions[b] = len(ids)
+
+    _prefill_slot = prefill_slot
+
+    def decode_slots(self, slots: Sequence[int], first_tokens: Sequence[int], steps: int) -> List[List[int]]:
+        """One launch: ``steps`` greedy tokens for every slot in ``slots`` (any subset, each from its own
+        position and ``first_tokens`` entry).  Returns the raw token lists (no EOS cut) and advances
+        the slots' positions by ``steps``."""
+        slots = [int(b) for b in slots]
+        steps = int(steps)
+        if len(set(slots)) != len(slots) or not all(0 <= b < self.num_sequences for b in slots):
+            raise ValueError("slots must be distinct and in range")
+        if steps <= 0 or not slots:
+            return [[] for _ in slots]
+        for b in slots:
+            if self.positions[b] + steps > self.max_seq_len:
+                raise ValueError(f"slot {b}: position + steps exceeds max_seq_len")
+        base = self._base
+        logs = [self._logs[b][:steps] for b in slots]
+        self._gen_batch(list(first_tokens), [self.positions[b] for b in slots], steps, base._embed_weight,
+                        base._layer_weights_packed, base._final_norm_weight, base._lm_head_weight,
+                        base._cos_table, base._sin_table, [self._k_caches[b] for b in slots],
+                        [self._v_caches[b] for b in slots], logs, base.num_layers, self.max_seq_len,
+                        base._attn_scale)
+        out = []
+        for i, b in enumerate(slots):
+            host = self._logs_cpu[b, :steps]
+            host.copy_(logs[i])
+            out.append(host.tolist())
+            self.positions[b] += steps
+        return out
 
     def generate_ids(self, prompts: Sequence[Sequence[int]], max_tokens: int) -> List[List[int]]:
         """One list of new token IDs per prompt (cut at EOS, which is not returned).  ``len(prompts)``

@@ -1,0 +1,184 @@
+"""Continuous batching over the multi-sequence decode launch.
+
+The reference serves one request at a time (a one-worker executor in ``megakernel.py:39``); its
+benchmark configurations also name a continuous-batching mode.  This scheduler keeps up to
+``engine.num_sequences`` requests live on one GPU.  Each round it
+
+1. admits waiting requests into free slots in arrival order (the slot's KV cache is filled by the
+   ``prefill`` op),
+2. runs ONE persistent launch that advances every live sequence by ``q`` tokens, where ``q`` is the
+   smaller of ``quantum`` and the fewest tokens any live sequence still needs (so no sequence runs past
+   its budget and every launch ends on a point where a slot may free up),
+3. cuts each sequence at EOS or at its budget, completes it and frees its slot.
+
+The engine is any object with ``num_sequences``, ``max_seq_len``, ``prefill_slot(slot, ids)`` and
+``decode_slots(slots, first_tokens, steps) -> list of token lists`` (``BatchDecoder`` provides them);
+tests drive the scheduler with a fake engine on the CPU.
+"""
+
+from __future__ import annotations
+
+import threading
+from collections import deque
+from concurrent.futures import Future
+from dataclasses import dataclass, field
+from typing import Deque, Dict, List, Optional, Sequence
+
+
+@dataclass
+class Request:
+    rid: int
+    prompt_ids: List[int]
+    max_tokens: int
+    future: Future = field(default_factory=Future, repr=False)
+    # filled while the request is live
+    slot: int = -1
+    next_token: int = -1           # input token of the next decode step
+    out: List[int] = field(default_factory=list)
+
+
+@dataclass
+class Result:
+    rid: int
+    tokens: List[int]
+    prompt_tokens: int
+    finish_reason: str             # "stop" (EOS) or "length"
+
+
+class ContinuousBatcher:
+    def __init__(self, engine, eos_token_id: Optional[int] = None, quantum: int = 16):
+        if quantum < 1:
+            raise ValueError("quantum must be >= 1")
+        self.engine = engine
+        self.eos = -1 if eos_token_id is None else int(eos_token_id)
+        self.quantum = int(quantum)
+        self.num_slots = int(engine.num_sequences)
+        self._waiting: Deque[Request] = deque()
+        self._live: Dict[int, Request] = {}           # slot -> request
+        self._free: List[int] = list(range(self.num_slots))
+        self._lock = threading.Lock()
+        self._wake = threading.Condition(self._lock)
+        self._next_id = 0
+        self._thread: Optional[threading.Thread] = None
+        self._stop = False
+        # counters for tests and reports
+        self.launches = 0
+        self.decoded_tokens = 0        # tokens produced by launches, including ones cut after EOS
+        self.max_live = 0
+
+    # ------------------------------------------------------------------ submission
+    def submit(self, prompt_ids: Sequence[int], max_tokens: int) -> Future:
+        """Queue a request; the future resolves to a ``Result`` (or raises what the engine raised)."""
+        ids = [int(t) for t in prompt_ids]
+        req = Request(rid=-1, prompt_ids=ids, max_tokens=int(max_tokens))
+        if not ids:
+            req.future.set_exception(ValueError("empty prompt"))
+            return req.future
+        if len(ids) - 1 + max(req.max_tokens, 0) > self.engine.max_seq_len:
+            req.future.set_exception(ValueError("prompt + max_tokens exceeds max_seq_len"))
+            return req.future
+        with self._wake:
+            req.rid = self._next_id
+            self._next_id += 1
+            if req.max_tokens <= 0:
+                req.future.set_result(Result(req.rid, [], len(ids), "length"))
+                return req.future
+            self._waiting.append(req)
+            self._wake.notify_all()
+        return req.future
+
+    # ------------------------------------------------------------------ one scheduling round
+    def _admit(self) -> None:
+        while True:
+            with self._lock:
+                if not self._waiting or not self._free:
+                    return
+                req = self._waiting.popleft()
+                slot = self._free.pop(0)
+            try:
+                self.engine.prefill_slot(slot, req.prompt_ids[:-1])
+            except Exception as exc:           # a bad prompt fails its own request only
+                with self._lock:
+                    self._free.append(slot)
+                    self._free.sort()
+                req.future.set_exception(exc)
+                continue
+            req.slot = slot
+            req.next_token = req.prompt_ids[-1]
+            with self._lock:
+                self._live[slot] = req
+                self.max_live = max(self.max_live, len(self._live))
+
+    def step(self) -> bool:
+        """One round (admit, launch, retire).  Returns False when there was nothing to do."""
+        self._admit()
+        with self._lock:
+            live = [self._live[s] for s in sorted(self._live)]
+        if not live:
+            return False
+        q = min(self.quantum, min(r.max_tokens - len(r.out) for r in live))
+        slots = [r.slot for r in live]
+        try:
+            produced = self.engine.decode_slots(slots, [r.next_token for r in live], q)
+        except Exception as exc:               # an engine failure ends every live request
+            with self._lock:
+                for r in live:
+                    del self._live[r.slot]
+                    self._free.append(r.slot)
+                self._free.sort()
+            for r in live:
+                r.future.set_exception(exc)
+            return True
+        self.launches += 1
+        self.decoded_tokens += q * len(live)
+        for r, toks in zip(live, produced):
+            finish = None
+            for t in toks:
+                if t == self.eos:
+                    finish = "stop"
+                    break
+                r.out.append(int(t))
+            if finish is None and len(r.out) >= r.max_tokens:
+                finish = "length"
+            if finish is None:
+                r.next_token = int(toks[-1])
+                continue
+            with self._lock:
+                del self._live[r.slot]
+                self._free.append(r.slot)
+                self._free.sort()
+            r.future.set_result(Result(r.rid, r.out, len(r.prompt_ids), finish))
+        return True
+
+    def run_until_idle(self) -> None:
+        """Synchronous driver: rounds until no request is waiting or live."""
+        while self.step():
+            pass
+
+    # ------------------------------------------------------------------ background driver
+    def start(self) -> None:
+        if self._thread is not None:
+            return
+        self._stop = False
+        self._thread = threading.Thread(target=self._loop, name="continuous-batcher", daemon=True)
+        self._thread.start()
+
+    def stop(self) -> None:
+        with self._wake:
+            self._stop = True
+            self._wake.notify_all()
+        if self._thread is not None:
+            self._thread.join()
+            self._thread = None
+
+    def _loop(self) -> None:
+        while True:
+            if not self.step():
+                with self._wake:
+                    if self._stop:
+                        return
+                    if not self._waiting and not self._live:
+                        self._wake.wait(timeout=0.5)
+            with self._lock:
+                if self._stop and not self._waiting and not self._live:
+                    return

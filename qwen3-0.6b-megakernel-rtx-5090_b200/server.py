@@ -72,22 +72,38 @@ def build_prompt(tokenizer, messages: List[Message]) -> str:
 
 
 def _load_decoder(model_name: str):
-    from Model.Qwen06B_architecture import Decoder
+    """``BATCH_SLOTS`` > 1 (up to 4) loads the multi-sequence engine: requests are then served
+    concurrently by the continuous-batching scheduler instead of one at a time."""
+    from Model.Qwen06B_architecture import BatchDecoder, Decoder, load_weights
+    slots = int(os.getenv("BATCH_SLOTS", "1"))
     if os.getenv("SYNTHETIC", "0") == "1":
         import synthetic as S
         layers = int(os.getenv("SYNTHETIC_LAYERS", "28"))
         w = S.weights_to(S.make_weights(seed=0, num_layers=layers), "cuda")
         tok = S.StubTokenizer(eos_token_id=-1)
-        return Decoder(weights=w, tokenizer=tok, verbose=False)
-    return Decoder(model_name=model_name, verbose=True)
+    elif slots > 1:
+        w, tok = load_weights(model_name, verbose=True)
+    else:
+        return Decoder(model_name=model_name, verbose=True)
+    if slots > 1:
+        return BatchDecoder(weights=w, tokenizer=tok, num_sequences=slots, verbose=False)
+    return Decoder(weights=w, tokenizer=tok, verbose=False)
 
 
 def create_app(decoder=None, model_name: Optional[str] = None, default_max_tokens: Optional[int] = None) -> FastAPI:
     model_name = model_name or os.getenv("MODEL", "Qwen/Qwen3-0.6B")
     default_max_tokens = default_max_tokens or int(os.getenv("MAX_TOKENS", "128"))
-    state = {"decoder": decoder}
-    worker = ThreadPoolExecutor(max_workers=1)      # the engine serves one request at a time per GPU
+    state = {"decoder": decoder, "batcher": None}
+    worker = ThreadPoolExecutor(max_workers=1)      # single-sequence engine: one request at a time per GPU
     ids = itertools.count(1)
+
+    def start_batcher():
+        dec = state["decoder"]
+        if state["batcher"] is None and hasattr(dec, "decode_slots"):   # multi-sequence engine
+            from scheduler import ContinuousBatcher
+            eos = getattr(dec.tokenizer, "eos_token_id", None)
+            state["batcher"] = ContinuousBatcher(dec, eos_token_id=eos, quantum=int(os.getenv("BATCH_QUANTUM", "16")))
+            state["batcher"].start()
 
     @asynccontextmanager
     async def lifespan(app: FastAPI):
@@ -96,7 +112,10 @@ def create_app(decoder=None, model_name: Optional[str] = None, default_max_token
             print(f"[server] loading {model_name} ...", flush=True)
             state["decoder"] = _load_decoder(model_name)
             print(f"[server] ready in {time.time() - t0:.1f}s", flush=True)
+        start_batcher()
         yield
+        if state["batcher"] is not None:
+            state["batcher"].stop()
         worker.shutdown(wait=False)
 
     app = FastAPI(title="Qwen3-0.6B B200 megakernel server", lifespan=lifespan)
@@ -121,8 +140,16 @@ def create_app(decoder=None, model_name: Optional[str] = None, default_max_token
         if state["decoder"] is None:
             raise HTTPException(status_code=503, detail="Model not loaded yet")
         budget = req.max_tokens or default_max_tokens
+        finish = None
         try:
-            text, n_in, n_out = await asyncio.get_running_loop().run_in_executor(worker, run, req.messages, budget)
+            if state["batcher"] is not None:
+                dec = state["decoder"]
+                prompt_ids = dec.tokenizer.encode(build_prompt(dec.tokenizer, req.messages), add_special_tokens=False)
+                res = await asyncio.wrap_future(state["batcher"].submit(prompt_ids, budget))
+                text = dec.tokenizer.decode(res.tokens, skip_special_tokens=True)
+                n_in, n_out, finish = res.prompt_tokens, len(res.tokens), res.finish_reason
+            else:
+                text, n_in, n_out = await asyncio.get_running_loop().run_in_executor(worker, run, req.messages, budget)
         except Exception as exc:  # engine errors surface as HTTP 500 with the engine's message
             raise HTTPException(status_code=500, detail=str(exc))
         return {
@@ -131,7 +158,7 @@ def create_app(decoder=None, model_name: Optional[str] = None, default_max_token
             "created": int(time.time()),
             "model": model_name,
             "choices": [{"index": 0, "message": {"role": "assistant", "content": text},
-                         "finish_reason": "length" if n_out >= budget else "stop"}],
+                         "finish_reason": finish or ("length" if n_out >= budget else "stop")}],
             "usage": {"prompt_tokens": n_in, "completion_tokens": n_out, "total_tokens": n_in + n_out},
         }
 

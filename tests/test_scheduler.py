@@ -1,0 +1,147 @@
+"""Continuous batching scheduler: host logic against a fake engine (CPU), and end to end on the GPU
+against the single-sequence engine."""
+
+import pytest
+import torch
+
+import synthetic as S
+from scheduler import ContinuousBatcher
+
+
+class FakeEngine:
+    """Deterministic stand-in: the token after ``t`` at cache position ``p`` is ``(7 t + 3 p + 1) % 97``.
+    Records what the scheduler asked for."""
+
+    def __init__(self, num_sequences=4, max_seq_len=64):
+        self.num_sequences, self.max_seq_len = num_sequences, max_seq_len
+        self.positions = [0] * num_sequences
+        self.launch_log = []
+
+    @staticmethod
+    def nxt(t, p):
+        return (7 * t + 3 * p + 1) % 97
+
+    def prefill_slot(self, b, ids):
+        if any(t < 0 for t in ids):
+            raise RuntimeError("bad token")
+        self.positions[b] = len(ids)
+
+    def decode_slots(self, slots, firsts, steps):
+        self.launch_log.append((tuple(slots), steps))
+        out = []
+        for b, t in zip(slots, firsts):
+            toks = []
+            for _ in range(steps):
+                t = self.nxt(t, self.positions[b])
+                self.positions[b] += 1
+                toks.append(t)
+            out.append(toks)
+        return out
+
+    @classmethod
+    def reference(cls, ids, n, eos=-1):
+        t, p, out = ids[-1], len(ids) - 1, []
+        for _ in range(n):
+            t = cls.nxt(t, p)
+            p += 1
+            if t == eos:
+                return out, "stop"
+            out.append(t)
+        return out, "length"
+
+
+def test_every_request_matches_its_own_sequential_run():
+    eng = FakeEngine(num_sequences=3)
+    sch = ContinuousBatcher(eng, eos_token_id=None, quantum=5)
+    reqs = [(S.make_prompt(1 + (i * 5) % 11, seed=i, vocab_size=97), 1 + (i * 7) % 23) for i in range(17)]
+    futs = [sch.submit(ids, n) for ids, n in reqs]
+    sch.run_until_idle()
+    for (ids, n), f in zip(reqs, futs):
+        r = f.result(timeout=0)
+        want, why = FakeEngine.reference(ids, n)
+        assert r.tokens == want and r.finish_reason == why == "length" and r.prompt_tokens == len(ids)
+    assert sch.max_live == 3                                   # the slots were actually shared
+    assert all(len(s) <= 3 and 1 <= q <= 5 for s, q in eng.launch_log)
+    assert sch.launches == len(eng.launch_log) < sum(n for _, n in reqs)   # fewer launches than tokens
+    # arrival order is admission order: request ids are handed out in submit order
+    assert [f.result().rid for f in futs] == list(range(17))
+
+
+def test_eos_frees_the_slot_and_is_not_returned():
+    ids, n = [5, 9, 2], 30
+    full, _ = FakeEngine.reference(ids, n)
+    eos = full[4]
+    eng = FakeEngine(num_sequences=2)
+    sch = ContinuousBatcher(eng, eos_token_id=eos, quantum=3)
+    f1 = sch.submit(ids, n)
+    f2 = sch.submit([1, 2, 3, 4], 9)
+    f3 = sch.submit([8], 4)                                    # waits for a slot
+    sch.run_until_idle()
+    want, why = FakeEngine.reference(ids, n, eos)
+    assert why == "stop" and f1.result().tokens == want == full[:full.index(eos)]
+    assert f1.result().finish_reason == "stop"
+    for f, (i, k) in ((f2, ([1, 2, 3, 4], 9)), (f3, ([8], 4))):
+        w, y = FakeEngine.reference(i, k, eos)
+        assert f.result().tokens == w and f.result().finish_reason == y
+
+
+def test_quantum_never_overruns_a_budget_and_bad_requests_fail_alone():
+    eng = FakeEngine(num_sequences=2, max_seq_len=16)
+    sch = ContinuousBatcher(eng, quantum=8)
+    ok = sch.submit([3, 4], 3)
+    too_long = sch.submit(list(range(10)), 10)                 # 9 + 10 > 16
+    empty = sch.submit([], 4)
+    zero = sch.submit([1, 2], 0)
+    bad = sch.submit([5, -1, 7], 2)                            # the engine refuses the prompt
+    later = sch.submit([6], 11)
+    sch.run_until_idle()
+    assert ok.result().tokens == FakeEngine.reference([3, 4], 3)[0]
+    assert later.result().tokens == FakeEngine.reference([6], 11)[0]
+    assert zero.result().tokens == []
+    with pytest.raises(ValueError):
+        too_long.result()
+    with pytest.raises(ValueError):
+        empty.result()
+    with pytest.raises(RuntimeError):
+        bad.result()
+    # the first launch carried both live requests and stopped at the shorter budget
+    assert eng.launch_log[0] == ((0, 1), 3)
+    for b in range(2):
+        assert eng.positions[b] <= 16
+
+
+def test_background_thread_serves_submissions():
+    eng = FakeEngine(num_sequences=4)
+    sch = ContinuousBatcher(eng, quantum=4)
+    sch.start()
+    try:
+        futs = [(ids, n, sch.submit(ids, n)) for ids, n in (([2, 3], 6), ([9], 13), ([4, 4, 4], 2))]
+        for ids, n, f in futs:
+            assert f.result(timeout=10).tokens == FakeEngine.reference(ids, n)[0]
+    finally:
+        sch.stop()
+
+
+@pytest.mark.gpu
+def test_gpu_continuous_batching_equals_single_sequence_engine(built_library, tiny_cfg):
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from Model.Qwen06B_architecture import BatchDecoder, Decoder
+    vocab = tiny_cfg["vocab_size"]
+    w = S.weights_to(S.make_weights(seed=tiny_cfg["seed"], num_layers=tiny_cfg["num_layers"], vocab_size=vocab,
+                                    norm_std=tiny_cfg["norm_std"], max_seq_len=16), "cuda")
+    tok = S.StubTokenizer(-1, vocab)
+    eng = BatchDecoder(weights=w, tokenizer=tok, num_sequences=4, max_seq_len=256)
+    reqs = [(S.make_prompt(3 + (i * 13) % 60, seed=100 + i, vocab_size=vocab), 4 + (i * 5) % 29) for i in range(11)]
+    single = Decoder(weights=w, tokenizer=tok, verbose=False, max_seq_len=256)
+    want = [single.generate_ids(ids, n) for ids, n in reqs]
+    eos = want[2][3]                                           # a token that really occurs
+    sch = ContinuousBatcher(eng, eos_token_id=eos, quantum=8)
+    futs = [sch.submit(ids, n) for ids, n in reqs]
+    sch.run_until_idle()
+    for w_, f, (ids, n) in zip(want, futs, reqs):
+        r = f.result(timeout=0)
+        cut = w_[:w_.index(eos)] if eos in w_ else w_
+        assert r.tokens == cut
+        assert r.finish_reason == ("stop" if eos in w_ else "length")
+    assert sch.max_live == 4 and sch.launches < sum(n for _, n in reqs)

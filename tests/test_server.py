@@ -129,3 +129,32 @@ def test_server_end_to_end_on_the_engine(built_library):
         rep = loadgen.run(lambda b: c.post("/v1/chat/completions", json=b).json(),
                           loadgen.synthetic_prompts(4, 8, seed=2, vocab=4096), "tiny", 4)
         assert rep["summary"]["num_failed"] == 0 and rep["summary"]["tokens_per_s"] > 0
+
+
+def test_batching_mode_serves_concurrent_requests_with_real_finish_reason():
+    """A multi-sequence engine behind the app: requests go through the continuous-batching scheduler,
+    several are live at once, and finish_reason says whether EOS or the budget ended the answer."""
+    from concurrent.futures import ThreadPoolExecutor
+    from test_scheduler import FakeEngine
+
+    eng = FakeEngine(num_sequences=3, max_seq_len=128)
+    ids, budget = [5, 9, 2], 12
+    full, _ = FakeEngine.reference(ids, budget)
+    eng.tokenizer = S.StubTokenizer(eos_token_id=full[6], vocab_size=97)
+    app = server.create_app(decoder=eng, model_name="stub-batch", default_max_tokens=4)
+    with TestClient(app) as c:
+        def ask(content, max_tokens):
+            return c.post("/v1/chat/completions", json={"model": "x", "messages": [{"role": "user", "content": content}],
+                                                        "max_tokens": max_tokens}).json()
+        with ThreadPoolExecutor(6) as pool:
+            futs = [pool.submit(ask, "5 9 2", budget)] + [pool.submit(ask, f"{i} {i + 1}", 3 + i) for i in range(5)]
+            bodies = [f.result() for f in futs]
+        stop = bodies[0]
+        assert stop["choices"][0]["finish_reason"] == "stop"
+        assert stop["choices"][0]["message"]["content"] == " ".join(map(str, full[:6]))
+        assert stop["usage"] == {"prompt_tokens": 3, "completion_tokens": 6, "total_tokens": 9}
+        for i, b in enumerate(bodies[1:]):
+            want, why = FakeEngine.reference([i, i + 1], 3 + i, full[6])
+            assert b["choices"][0]["message"]["content"] == " ".join(map(str, want))
+            assert b["choices"][0]["finish_reason"] == why
+        assert app.state.engine["batcher"].launches > 0
