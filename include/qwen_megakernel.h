@@ -215,6 +215,13 @@ int qmk_generate_static(
     int *output_log, int num_layers, int start_position, int max_seq_len,
     float attn_scale, int eos_token_id, cudaStream_t stream);
 
+/* C[m x n] (fp32, row-major, DEVICE) = A[m x k] * B[n x k]^T with fp16 row-major DEVICE operands, on the
+ * tcgen05 tensor cores (TMA-fed, accumulator in TMEM).  m and n multiples of 128, k a multiple of 64,
+ * operands 16-byte aligned.  This is the GEMM the chunked prefill is built from; the reference has no
+ * counterpart (its prefill repeats the decode kernels once per prompt token, megakernel_5090.cu:1324-1350).
+ * Blocks until done. */
+int qmk_gemm_f16_tn(const void *a, const void *b, float *c, int m, int n, int k, cudaStream_t stream);
+
 /* Synchronises the device and returns the status word of the last launch
  * (QMK_OK, or the first error a CTA recorded). */
 int qmk_sync_status(void);

@@ -1,0 +1,218 @@
+// C[M x N] (fp32) = A[M x K] (fp16, row-major) * B[N x K]^T (fp16, row-major) on the sm_100a tensor cores.
+//
+// One CTA per 128 x 128 output tile, warp-specialised:
+//   warp 0   : one thread streams 128 x 64 tiles of A and of B with tiled TMA loads (128-byte swizzle)
+//              into a 4-stage shared-memory ring (full/empty mbarriers);
+//   warp 1   : allocates 128 TMEM columns, then one thread issues tcgen05.mma (M 128, N 128, K 16; four per
+//              64-wide K block) with shared-memory matrix descriptors, commits each stage back to the
+//              producer and finally commits the accumulator to the epilogue;
+//   warps 2-5: read the fp32 accumulator from TMEM (tcgen05.ld, each warp its own 32-lane quarter) and store
+//              it to global memory.
+// Every mbarrier wait is bounded by a clock budget; a wait that runs out sets *status = 4 and all roles
+// leave their loops (outstanding copies are given the same budget to land, TMEM is freed) so that the
+// context survives.  No cluster multicast anywhere.
+//
+// Shapes: M, N multiples of 128, K a multiple of 64 (the callers pad the token dimension).
+#ifndef QMK_GEMM_TCGEN05_CUH_
+#define QMK_GEMM_TCGEN05_CUH_
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace qmk_gemm {
+
+constexpr int BM = 128, BN = 128, BK = 64;       // BK * 2 bytes = one 128-byte swizzle row
+constexpr int STAGES = 4;
+constexpr int THREADS = 192;
+constexpr uint32_t TILE_A_BYTES = BM * BK * 2;   // 16 KB
+constexpr uint32_t TILE_B_BYTES = BN * BK * 2;   // 16 KB
+constexpr uint32_t STAGE_BYTES = TILE_A_BYTES + TILE_B_BYTES;
+constexpr uint32_t TMEM_COLS = 128;              // fp32 accumulator: 128 lanes x 128 columns
+constexpr size_t SMEM_BYTES = 1024 /* alignment slack */ + static_cast<size_t>(STAGES) * STAGE_BYTES + 256;
+
+__device__ __forceinline__ uint32_t s32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void bar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool bar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the budget ran out or another role already gave up.
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned int *status,
+                                         unsigned long long budget_ns) {
+  if (bar_try(bar, parity)) return true;
+  const unsigned long long t0 = gtime();
+  uint32_t it = 0;
+  for (;;) {
+    if (bar_try(bar, parity)) return true;
+    if ((++it & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (gtime() - t0 > budget_ns) {
+        *abort_flag = 1;
+        atomicCAS(status, 0u, 4u);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the 128-byte swizzle:
+// 8-row groups are 1024 bytes apart (stride byte offset), version 1 (sm_100), layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: fp32 accumulator, fp16 A and B, both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+constexpr uint32_t IDESC = (1u << 4) | (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+
+__device__ __forceinline__ void mma_f16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t"
+      "}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(IDESC), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, float *C, int M,
+                   int N, int K, unsigned int *status, unsigned long long budget_ns) {
+  extern __shared__ unsigned char gemm_smem_raw[];
+  const uint32_t raw = s32(gemm_smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;                 // swizzled tiles need 1024-byte alignment
+  unsigned char *aligned = gemm_smem_raw + (base - raw);
+  const uint32_t bars = base + STAGES * STAGE_BYTES;            // full[STAGES], empty[STAGES], acc_full, then scratch
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(aligned + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 1));
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  const int kblocks = K / BK;
+  auto full = [&](int s) { return bars + 8u * s; };
+  auto empty = [&](int s) { return bars + 8u * (STAGES + s); };
+  const uint32_t acc_full = bars + 8u * (2 * STAGES);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { bar_init(full(s), 1); bar_init(empty(s), 1); }
+    bar_init(acc_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {   // the whole warp allocates; the address lands in shared memory
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {                       // ---- producer
+      int issued = 0;
+      for (int kb = 0; kb < kblocks; ++kb) {
+        const int s = kb % STAGES;
+        if (kb >= STAGES && !bar_wait(empty(s), ((kb / STAGES) - 1) & 1, abort_flag, status, budget_ns)) break;
+        if (*abort_flag) break;
+        bar_expect_tx(full(s), STAGE_BYTES);
+        tma_load_2d(base + s * STAGE_BYTES, &map_a, kb * BK, m0, full(s));
+        tma_load_2d(base + s * STAGE_BYTES + TILE_A_BYTES, &map_b, kb * BK, n0, full(s));
+        issued = kb + 1;
+      }
+      // after an abort the copies already issued must land before the CTA can exit
+      if (*abort_flag) {
+        for (int kb = (issued > STAGES ? issued - STAGES : 0); kb < issued; ++kb) {
+          const unsigned long long t0 = gtime();
+          while (!bar_try(full(kb % STAGES), (kb / STAGES) & 1)) {
+            if (gtime() - t0 > budget_ns) break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {                       // ---- MMA issuer
+      bool ok = true;
+      for (int kb = 0; kb < kblocks && ok; ++kb) {
+        const int s = kb % STAGES;
+        ok = bar_wait(full(s), (kb / STAGES) & 1, abort_flag, status, budget_ns);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint64_t da = smem_desc_sw128(base + s * STAGE_BYTES);
+        const uint64_t db = smem_desc_sw128(base + s * STAGE_BYTES + TILE_A_BYTES);
+#pragma unroll
+        for (int j = 0; j < BK / 16; ++j)   // 16 halves = 32 bytes = 2 descriptor address units per K step
+          mma_f16_ss(tmem_base, da + 2u * j, db + 2u * j, (kb > 0 || j > 0) ? 1u : 0u);
+        mma_commit(empty(s));               // the stage is free once these MMAs have read it
+      }
+      if (ok) mma_commit(acc_full);         // accumulator complete
+    }
+  } else {                                 // ---- epilogue: warps 2..5 own TMEM lanes 32 * (warp % 4) ..
+    const int quarter = warp & 3;
+    // warp-uniform outcome: the TMEM loads below are warp-wide instructions
+    const bool ok = __all_sync(0xffffffffu, bar_wait(acc_full, 0, abort_flag, status, budget_ns));
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      const int row = m0 + quarter * 32 + lane;
+      float *crow = C + static_cast<size_t>(row) * N + n0;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(c * 32);
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+              "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+              "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+              "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(taddr)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row < M) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            *reinterpret_cast<float4 *>(crow + c * 32 + i) =
+                make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
+                            __uint_as_float(r[i + 3]));
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+}  // namespace qmk_gemm
+#endif  // QMK_GEMM_TCGEN05_CUH_

@@ -1,0 +1,16 @@
+// Internal interface of the tensor-core side (prefill_sm100.cu).
+#ifndef QMK_PREFILL_SM100_H_
+#define QMK_PREFILL_SM100_H_
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string>
+
+namespace qmk_tc {
+int make_map_f16(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t cols, uint32_t box_rows, std::string *err);
+int launch_gemm(const CUtensorMap &map_a, const CUtensorMap &map_b, float *C, int M, int N, int K, unsigned int *status,
+                int timeout_ms, cudaStream_t stream, std::string *err);
+}  // namespace qmk_tc
+
+#endif  // QMK_PREFILL_SM100_H_

@@ -66,6 +66,8 @@ _lib.qmk_generate_static.argtypes = [_I, _I, *([_P] * 7), _P, _I, _I, _I, _F, _I
 _lib.qmk_generate_static.restype = _I
 _lib.qmk_generate_batch.argtypes = [_I, _P, _P, _I, *([_P] * 6), _P, _P, _P, _I, _I, _F, _I, _P]
 _lib.qmk_generate_batch.restype = _I
+_lib.qmk_gemm_f16_tn.argtypes = [_P, _P, _P, _I, _I, _I, _P]
+_lib.qmk_gemm_f16_tn.restype = _I
 _lib.qmk_sync_status.restype = _I
 _lib.qmk_last_error.restype = ctypes.c_char_p
 _lib.qmk_num_ctas.restype = _I
@@ -76,7 +78,7 @@ _lib.qmk_selftest_wait_timeout.restype = _I
 EXPORTED_SYMBOLS = (
     "launch_ldg_decode_direct", "launch_ldg_decode_persistent", "launch_ldg_generate_nosync",
     "launch_ldg_prefill", "qmk_abi_version", "qmk_configure", "qmk_set_inv_freq", "qmk_set_logits_dump",
-    "qmk_set_weight_format", "qmk_set_tuning", "qmk_set_tuning2", "qmk_set_profile_buffer", "qmk_decode", "qmk_generate", "qmk_generate_static", "qmk_generate_batch", "qmk_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
+    "qmk_set_weight_format", "qmk_set_tuning", "qmk_set_tuning2", "qmk_set_profile_buffer", "qmk_decode", "qmk_generate", "qmk_generate_static", "qmk_generate_batch", "qmk_gemm_f16_tn", "qmk_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
     "qmk_scratch_bytes", "qmk_selftest_wait_timeout",
 )
 
@@ -284,6 +286,25 @@ def generate_batch(first_token_ids, start_positions, num_steps, embed_weight, la
     if rc != 0:
         raise RuntimeError(f"generate_batch: {_lib.qmk_last_error().decode()} (status {rc})")
     return output_logs
+
+
+def gemm_f16_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
+    """``a @ b.T`` in fp32 for fp16 CUDA matrices ``a [m, k]`` and ``b [n, k]`` on the tcgen05 tensor cores
+    (m, n multiples of 128; k a multiple of 64)."""
+    _require_cuda()
+    _check(a.is_cuda and b.is_cuda and a.dtype == torch.float16 and b.dtype == torch.float16 and
+           a.is_contiguous() and b.is_contiguous() and a.dim() == 2 and b.dim() == 2 and a.shape[1] == b.shape[1],
+           "gemm_f16_tn: contiguous fp16 CUDA matrices [m, k] and [n, k] expected")
+    m, k = a.shape
+    n = b.shape[0]
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.float32, device=a.device)
+    _check(out.is_cuda and out.dtype == torch.float32 and out.is_contiguous() and tuple(out.shape) == (m, n),
+           "gemm_f16_tn: out must be a contiguous fp32 CUDA matrix [m, n]")
+    rc = _lib.qmk_gemm_f16_tn(_ptr(a), _ptr(b), _ptr(out), int(m), int(n), int(k), _stream())
+    if rc != 0:
+        raise RuntimeError(f"gemm_f16_tn failed with status {rc}")
+    return out
 
 
 def sync_status() -> int:
