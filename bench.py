@@ -388,7 +388,7 @@ def run_continuous(args):
     new_tokens = 128
     weights = S.weights_to(S.make_weights(seed=0, max_seq_len=16), str(device))
     eng = BatchDecoder(weights=weights, tokenizer=S.StubTokenizer(-1), num_sequences=slots, max_seq_len=2048 + new_tokens,
-                       device=str(device))
+                       device=str(device), prefill_mode=args.prefill)
     gen = torch.Generator("cpu").manual_seed(rank)             # a different request stream per replica
     lens = torch.randint(64, 2049, (args.continuous,), generator=gen).tolist()
     prompts = [S.make_prompt(L, seed=1000 * rank + i) for i, L in enumerate(lens)]
@@ -422,6 +422,7 @@ def run_continuous(args):
             "new_tokens_per_request": new_tokens, "prompt_tokens": sum(lens), "wall_s": wall,
             "prefill_s": prefill_s[0], "decode_s": wall - prefill_s[0],
             "decode_only_tok_s": n_out / max(wall - prefill_s[0], 1e-9), "launches": sch.launches - launches0,
+            "prefill": args.prefill, "prompt_tok_s": sum(lens) / max(prefill_s[0], 1e-9),
             "scaling": "weak", "data": "synthetic", "dtype": "fp16", "clocks": clocks.summary(),
             "note": "rank 0's own prefill/decode split; value uses the slowest replica's wall time"}))
     if world > 1:
@@ -444,6 +445,8 @@ def main():
     ap.add_argument("--continuous", type=int, default=0, metavar="N",
                     help="instead of the headline workload: N requests per GPU through the continuous-batching "
                          "scheduler (prompt lengths 64..2048, 128 new tokens each, --batch live sequences)")
+    ap.add_argument("--prefill", choices=["serial", "tensor"], default="tensor",
+                    help="--continuous only: token-serial prefill op or the tensor-core chunked prefill")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prefilled context (default: benchmark config)")
     ap.add_argument("--decode-tokens", type=int, default=DECODE_TOKENS,
                     help="greedy tokens per step (default: benchmark config; smaller for ncu captures)")

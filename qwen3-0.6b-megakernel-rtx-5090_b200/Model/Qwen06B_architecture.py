@@ -146,7 +146,7 @@ class Decoder:
 
     def __init__(self, weights=None, tokenizer=None, model_name: str = "Qwen/Qwen3-0.6B", verbose: bool = True,
                  max_seq_len: int = MAX_SEQ_LEN, rope_from_table: bool = False, device: str = "cuda",
-                 weight_format: str = "fp16"):
+                 weight_format: str = "fp16", prefill_mode: str = "serial"):
         if not torch.cuda.is_available():
             raise RuntimeError("Decoder needs a CUDA device (sm_100a); there is no CPU path")
         if weights is None:
@@ -162,6 +162,13 @@ class Decoder:
         self.num_layers = len(weights["layer_weights"]) // FIELDS_PER_LAYER
         self.vocab_size = int(self._embed_weight.shape[0])
         self.weight_format = weight_format   # "fp16", or "fp8" (matrices packed by quantize.quantize_weights_fp8)
+        # "serial": the reference's token-by-token prefill (fp32 activations, bit-identical to decoding the
+        # prompt); "tensor": chunked prefill on the tensor cores (fp16 GEMM operands, fp16 weights only)
+        if prefill_mode not in ("serial", "tensor"):
+            raise ValueError("prefill_mode must be 'serial' or 'tensor'")
+        if prefill_mode == "tensor" and weight_format != "fp16":
+            raise ValueError("tensor-core prefill needs fp16 weights")
+        self.prefill_mode = prefill_mode
         cos, sin = weights.get("cos_table"), weights.get("sin_table")
         if cos is None or cos.shape[0] < self.max_seq_len or cos.device != dev:
             cos, sin = build_rope_tables(self.max_seq_len, device=dev)
@@ -243,7 +250,13 @@ class Decoder:
         if len(ids) == 0:
             return
         t = torch.tensor(list(ids), dtype=torch.int32)
-        self._prefill_op(t, *self._common(), self.num_layers, self._position, self.max_seq_len, self._attn_scale)
+        if self.prefill_mode == "tensor":
+            _require_megakernel_op("prefill_chunked")(
+                t, self._embed_weight, self._layer_weights_packed, self._cos_table, self._sin_table,
+                self._k_cache, self._v_cache, self.num_layers, self._position, self.max_seq_len, self._attn_scale)
+        else:
+            self._prefill_op(t, *self._common(), self.num_layers, self._position, self.max_seq_len,
+                             self._attn_scale)
         self._position += len(ids)
         self._kv_high_water = max(self._kv_high_water, self._position)
 

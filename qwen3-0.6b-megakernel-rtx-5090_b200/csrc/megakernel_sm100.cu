@@ -43,6 +43,7 @@
 #define QMK_MAX_SEQ 1
 #include "megakernel_device.cuh"
 #include "megakernel_batch.h"
+#include "engine_internal.h"
 
 namespace qmk {
 
@@ -203,6 +204,21 @@ int grid_for(const Engine *e) {
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// fp32 rotary table covering positions [0, max_seq_len): grow-only, like the token staging buffer.
+int ensure_rope(Engine *e, int max_seq_len, cudaStream_t stream) {
+  if (e->rope_from_table || max_seq_len <= e->rope_cap) return QMK_OK;
+  if (e->rope) cudaFree(e->rope);
+  e->rope = nullptr;
+  e->rope_cap = 0;
+  int cap = 2048;
+  while (cap < max_seq_len) cap *= 2;
+  QMK_CUDA(e, cudaMalloc(&e->rope, sizeof(float) * qmk::D * cap));
+  qmk::rope_table_kernel<<<(cap * (qmk::D / 2) + 255) / 256, 256, 0, stream>>>(e->rope, cap);
+  QMK_CUDA(e, cudaGetLastError());
+  e->rope_cap = cap;
+  return QMK_OK;
+}
+
 // The producer code shared by both builds reads per-sequence entries: entry 0 mirrors the scalar fields.
 void mirror_sequence0(Params &P) {
   P.nseq = 1;
@@ -241,17 +257,8 @@ int launch(Engine *e, Params &P, cudaStream_t stream, bool synchronize, bool bat
     QMK_CUDA(e, cudaMemsetAsync(e->ll, 0, exchange_bytes(), stream));
     e->seq = 0;
   }
-  if (!e->rope_from_table && P.max_seq_len > e->rope_cap) {   // grow-only, like the token staging buffer
-    if (e->rope) cudaFree(e->rope);
-    e->rope = nullptr;
-    e->rope_cap = 0;
-    int cap = 2048;
-    while (cap < P.max_seq_len) cap *= 2;
-    QMK_CUDA(e, cudaMalloc(&e->rope, sizeof(float) * qmk::D * cap));
-    qmk::rope_table_kernel<<<(cap * (qmk::D / 2) + 255) / 256, 256, 0, stream>>>(e->rope, cap);
-    QMK_CUDA(e, cudaGetLastError());
-    e->rope_cap = cap;
-  }
+  rc = ensure_rope(e, P.max_seq_len, stream);
+  if (rc != QMK_OK) return rc;
   P.rope = e->rope;
   QMK_CUDA(e, cudaMemsetAsync(e->status, 0, 16, stream));
   P.ll = e->ll;
@@ -317,6 +324,28 @@ Params base_params(const void *embed, const LDGLayerWeight *layers, const void *
 }
 
 }  // namespace
+
+namespace qmk_internal {
+int prefill_env(int max_seq_len, cudaStream_t stream, PrefillEnv *out) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  Engine *e = current_engine_unlocked();
+  if (!e) return QMK_ERR_CUDA;
+  clear_error(e);
+  int rc = ensure_ready(e);
+  if (rc == QMK_OK) rc = ensure_rope(e, max_seq_len, stream);
+  if (rc != QMK_OK) return rc;
+  out->rope = e->rope;
+  out->vocab = e->vocab;
+  out->timeout_ms = e->timeout_ms;
+  out->wfmt = e->wfmt;
+  out->rope_from_table = e->rope_from_table;
+  return QMK_OK;
+}
+int report(int code, const std::string &msg) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  return fail(current_engine_unlocked(), code, msg);
+}
+}  // namespace qmk_internal
 
 extern "C" {
 

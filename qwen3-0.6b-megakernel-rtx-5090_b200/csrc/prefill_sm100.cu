@@ -11,6 +11,9 @@
 #include "../../include/qwen_megakernel.h"
 #include "gemm_tcgen05.cuh"
 #include "prefill_sm100.h"
+#include "prefill_kernels.cuh"
+#include "engine_internal.h"
+#include <vector>
 
 namespace qmk_tc {
 
@@ -81,6 +84,170 @@ int launch_gemm(const CUtensorMap &map_a, const CUtensorMap &map_b, float *C, in
 }
 
 }  // namespace qmk_tc
+
+// ----------------------------------------------------------------------------- chunked prefill
+namespace {
+
+constexpr int CHUNK = 512;          // prompt tokens per pass over the weights (a multiple of the GEMM's 128)
+constexpr int MAX_LAYERS = 48;
+
+struct Workspace {                  // per device, allocated on first use, never freed (like the engine's scratch)
+  bool ready = false;
+  int *tokens = nullptr;
+  float *x = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *qr = nullptr, *o = nullptr, *gate = nullptr,
+        *up = nullptr, *down = nullptr;
+  __half *xn = nullptr, *attn = nullptr, *act = nullptr;
+  unsigned int *status = nullptr;
+  CUtensorMap map_xn, map_attn, map_act;
+  // weight maps of the layer table seen last (rebuilt when the table's contents change)
+  unsigned long long table[MAX_LAYERS * 12] = {};
+  int table_layers = 0;
+  CUtensorMap wmap[MAX_LAYERS][7];  // q, k, v, o, gate, up, down
+};
+Workspace g_ws[16];
+std::mutex g_ws_mu;
+
+#define PF_CUDA(call)                                                                             \
+  do {                                                                                            \
+    cudaError_t err__ = (call);                                                                   \
+    if (err__ != cudaSuccess)                                                                     \
+      return qmk_internal::report(QMK_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(err__)); \
+  } while (0)
+
+int ensure_workspace(Workspace &w) {
+  if (w.ready) return QMK_OK;
+  using namespace qmk_pf;
+  const size_t C = CHUNK;
+  PF_CUDA(cudaMalloc(&w.tokens, sizeof(int) * C));
+  PF_CUDA(cudaMalloc(&w.x, sizeof(float) * C * H));
+  PF_CUDA(cudaMalloc(&w.q, sizeof(float) * C * QS));
+  PF_CUDA(cudaMalloc(&w.k, sizeof(float) * C * KVS));
+  PF_CUDA(cudaMalloc(&w.v, sizeof(float) * C * KVS));
+  PF_CUDA(cudaMalloc(&w.qr, sizeof(float) * C * QS));
+  PF_CUDA(cudaMalloc(&w.o, sizeof(float) * C * H));
+  PF_CUDA(cudaMalloc(&w.gate, sizeof(float) * C * I));
+  PF_CUDA(cudaMalloc(&w.up, sizeof(float) * C * I));
+  PF_CUDA(cudaMalloc(&w.down, sizeof(float) * C * H));
+  PF_CUDA(cudaMalloc(&w.xn, sizeof(__half) * C * H));
+  PF_CUDA(cudaMalloc(&w.attn, sizeof(__half) * C * QS));
+  PF_CUDA(cudaMalloc(&w.act, sizeof(__half) * C * I));
+  PF_CUDA(cudaMalloc(&w.status, 16));
+  // GEMM operand rows beyond a short chunk are read (and ignored): they must hold finite numbers
+  PF_CUDA(cudaMemset(w.xn, 0, sizeof(__half) * C * H));
+  PF_CUDA(cudaMemset(w.attn, 0, sizeof(__half) * C * QS));
+  PF_CUDA(cudaMemset(w.act, 0, sizeof(__half) * C * I));
+  std::string err;
+  int rc = qmk_tc::make_map_f16(&w.map_xn, w.xn, C, H, qmk_gemm::BM, &err);
+  if (rc == QMK_OK) rc = qmk_tc::make_map_f16(&w.map_attn, w.attn, C, QS, qmk_gemm::BM, &err);
+  if (rc == QMK_OK) rc = qmk_tc::make_map_f16(&w.map_act, w.act, C, I, qmk_gemm::BM, &err);
+  if (rc != QMK_OK) return qmk_internal::report(rc, err);
+  w.ready = true;
+  return QMK_OK;
+}
+
+// Tensor maps of the seven projection matrices of every layer.  The layer table lives in device memory
+// (the reference's packed pointer records): it is read back and the maps are rebuilt only when it changed.
+int ensure_weight_maps(Workspace &w, const LDGLayerWeight *layers_dev, int num_layers, cudaStream_t stream) {
+  using namespace qmk_pf;
+  std::vector<unsigned long long> host(static_cast<size_t>(num_layers) * 12);
+  PF_CUDA(cudaMemcpyAsync(host.data(), layers_dev, host.size() * 8, cudaMemcpyDeviceToHost, stream));
+  PF_CUDA(cudaStreamSynchronize(stream));
+  if (w.table_layers == num_layers && memcmp(host.data(), w.table, host.size() * 8) == 0) return QMK_OK;
+  // record order: in_ln, wq, wk, wv, q_norm, k_norm, wo, post_ln, gate, up, down, pad
+  static const int slot[7] = {1, 2, 3, 6, 8, 9, 10};
+  static const int rows[7] = {QS, KVS, KVS, H, I, I, H};
+  static const int cols[7] = {H, H, H, QS, H, H, I};
+  std::string err;
+  for (int l = 0; l < num_layers; ++l)
+    for (int j = 0; j < 7; ++j) {
+      const void *ptr = reinterpret_cast<const void *>(host[static_cast<size_t>(l) * 12 + slot[j]]);
+      if (!ptr) return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "prefill: null weight pointer in the layer table");
+      const int rc = qmk_tc::make_map_f16(&w.wmap[l][j], ptr, rows[j], cols[j], qmk_gemm::BN, &err);
+      if (rc != QMK_OK) return qmk_internal::report(rc, err);
+    }
+  memcpy(w.table, host.data(), host.size() * 8);
+  w.table_layers = num_layers;
+  return QMK_OK;
+}
+
+}  // namespace
+
+extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, const void *embed_weight,
+                                   const LDGLayerWeight *layer_weights, const void *cos_table, const void *sin_table,
+                                   void *k_cache, void *v_cache, int num_layers, int start_position, int max_seq_len,
+                                   float attn_scale, cudaStream_t stream) {
+  using namespace qmk_pf;
+  if (num_tokens <= 0) return QMK_OK;
+  qmk_internal::PrefillEnv env;
+  int rc = qmk_internal::prefill_env(max_seq_len, stream, &env);
+  if (rc != QMK_OK) return rc;
+  if (!token_ids_host || !embed_weight || !layer_weights || !k_cache || !v_cache)
+    return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "prefill: null pointer argument");
+  if (env.wfmt != 0)
+    return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "qmk_prefill_chunked handles fp16 weights only; use qmk_prefill");
+  if (num_layers < 1 || num_layers > MAX_LAYERS)
+    return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "num_layers must be in [1, 48]");
+  if (start_position < 0 || start_position + num_tokens > max_seq_len)
+    return qmk_internal::report(QMK_ERR_POSITION, "start_position + steps exceeds max_seq_len");
+  if (env.rope_from_table && (!cos_table || !sin_table))
+    return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "rope_from_table needs cos/sin tables");
+  for (int i = 0; i < num_tokens; ++i)
+    if (token_ids_host[i] < 0 || token_ids_host[i] >= env.vocab)
+      return qmk_internal::report(QMK_ERR_BAD_TOKEN, "prompt token outside [0, vocab)");
+  int dev = 0;
+  PF_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 16) return qmk_internal::report(QMK_ERR_CUDA, "device index out of range");
+  std::lock_guard<std::mutex> lock(g_ws_mu);
+  Workspace &w = g_ws[dev];
+  rc = ensure_workspace(w);
+  if (rc == QMK_OK) rc = ensure_weight_maps(w, layer_weights, num_layers, stream);
+  if (rc != QMK_OK) return rc;
+  std::vector<unsigned long long> rec(w.table, w.table + static_cast<size_t>(num_layers) * 12);
+  const float *rope = env.rope_from_table ? nullptr : env.rope;
+  const __half *cosv = static_cast<const __half *>(cos_table), *sinv = static_cast<const __half *>(sin_table);
+  const size_t layer_stride = static_cast<size_t>(NKV) * max_seq_len * D;
+  PF_CUDA(cudaMemsetAsync(w.status, 0, 16, stream));
+  std::string err;
+  auto gemm = [&](const CUtensorMap &a, const CUtensorMap &b, float *c, int M, int N, int K) {
+    return qmk_tc::launch_gemm(a, b, c, M, N, K, w.status, env.timeout_ms, stream, &err);
+  };
+  for (int c0 = 0; c0 < num_tokens; c0 += CHUNK) {
+    const int T = (num_tokens - c0 < CHUNK) ? num_tokens - c0 : CHUNK;
+    const int M = (T + qmk_gemm::BM - 1) / qmk_gemm::BM * qmk_gemm::BM;
+    const int pos0 = start_position + c0;
+    PF_CUDA(cudaMemcpyAsync(w.tokens, token_ids_host + c0, sizeof(int) * T, cudaMemcpyHostToDevice, stream));
+    embed_rows<<<T, 256, 0, stream>>>(w.tokens, static_cast<const __half *>(embed_weight), w.x);
+    for (int l = 0; l < num_layers; ++l) {
+      const unsigned long long *r = rec.data() + static_cast<size_t>(l) * 12;
+      __half *kc = static_cast<__half *>(k_cache) + l * layer_stride, *vc = static_cast<__half *>(v_cache) + l * layer_stride;
+      add_rmsnorm_rows<<<T, 256, 0, stream>>>(w.x, l > 0 ? w.down : nullptr, reinterpret_cast<const __half *>(r[0]), w.xn);
+      if ((rc = gemm(w.map_xn, w.wmap[l][0], w.q, M, QS, H)) != QMK_OK) break;
+      if ((rc = gemm(w.map_xn, w.wmap[l][1], w.k, M, KVS, H)) != QMK_OK) break;
+      if ((rc = gemm(w.map_xn, w.wmap[l][2], w.v, M, KVS, H)) != QMK_OK) break;
+      qk_norm_rope_cache<<<dim3(T, 4), 256, 0, stream>>>(w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]),
+                                                         reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv, w.qr, kc, vc,
+                                                         pos0, max_seq_len);
+      if (l == num_layers - 1) break;   // the cache is complete; nothing downstream of the last layer is kept
+      causal_attention<<<dim3((T + ATT_Q - 1) / ATT_Q, NKV), 128, 0, stream>>>(w.qr, kc, vc, w.attn, T, pos0, max_seq_len,
+                                                                              attn_scale);
+      if ((rc = gemm(w.map_attn, w.wmap[l][3], w.o, M, H, QS)) != QMK_OK) break;
+      add_rmsnorm_rows<<<T, 256, 0, stream>>>(w.x, w.o, reinterpret_cast<const __half *>(r[7]), w.xn);
+      if ((rc = gemm(w.map_xn, w.wmap[l][4], w.gate, M, I, H)) != QMK_OK) break;
+      if ((rc = gemm(w.map_xn, w.wmap[l][5], w.up, M, I, H)) != QMK_OK) break;
+      silu_mul_rows<<<592, 256, 0, stream>>>(w.gate, w.up, w.act, static_cast<size_t>(T) * I);
+      if ((rc = gemm(w.map_act, w.wmap[l][6], w.down, M, H, I)) != QMK_OK) break;
+    }
+    if (rc != QMK_OK) break;
+    PF_CUDA(cudaGetLastError());     // (the next chunk's token copy is stream-ordered behind this chunk's kernels)
+  }
+  if (rc != QMK_OK) return qmk_internal::report(rc, err);
+  unsigned int host_status[4] = {0, 0, 0, 0};
+  PF_CUDA(cudaMemcpyAsync(host_status, w.status, 16, cudaMemcpyDeviceToHost, stream));
+  PF_CUDA(cudaStreamSynchronize(stream));
+  if (host_status[0] != 0)
+    return qmk_internal::report(static_cast<int>(host_status[0]), "prefill: a bounded device wait ran out");
+  return QMK_OK;
+}
 
 extern "C" int qmk_gemm_f16_tn(const void *a, const void *b, float *c, int m, int n, int k, cudaStream_t stream) {
   std::string err;

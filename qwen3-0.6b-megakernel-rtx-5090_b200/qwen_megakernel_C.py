@@ -66,6 +66,8 @@ _lib.qmk_generate_static.argtypes = [_I, _I, *([_P] * 7), _P, _I, _I, _I, _F, _I
 _lib.qmk_generate_static.restype = _I
 _lib.qmk_generate_batch.argtypes = [_I, _P, _P, _I, *([_P] * 6), _P, _P, _P, _I, _I, _F, _I, _P]
 _lib.qmk_generate_batch.restype = _I
+_lib.qmk_prefill_chunked.argtypes = [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _P]
+_lib.qmk_prefill_chunked.restype = _I
 _lib.qmk_gemm_f16_tn.argtypes = [_P, _P, _P, _I, _I, _I, _P]
 _lib.qmk_gemm_f16_tn.restype = _I
 _lib.qmk_sync_status.restype = _I
@@ -78,7 +80,7 @@ _lib.qmk_selftest_wait_timeout.restype = _I
 EXPORTED_SYMBOLS = (
     "launch_ldg_decode_direct", "launch_ldg_decode_persistent", "launch_ldg_generate_nosync",
     "launch_ldg_prefill", "qmk_abi_version", "qmk_configure", "qmk_set_inv_freq", "qmk_set_logits_dump",
-    "qmk_set_weight_format", "qmk_set_tuning", "qmk_set_tuning2", "qmk_set_profile_buffer", "qmk_decode", "qmk_generate", "qmk_generate_static", "qmk_generate_batch", "qmk_gemm_f16_tn", "qmk_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
+    "qmk_set_weight_format", "qmk_set_tuning", "qmk_set_tuning2", "qmk_set_profile_buffer", "qmk_decode", "qmk_generate", "qmk_generate_static", "qmk_generate_batch", "qmk_gemm_f16_tn", "qmk_prefill_chunked", "qmk_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
     "qmk_scratch_bytes", "qmk_selftest_wait_timeout",
 )
 
@@ -286,6 +288,23 @@ def generate_batch(first_token_ids, start_positions, num_steps, embed_weight, la
     if rc != 0:
         raise RuntimeError(f"generate_batch: {_lib.qmk_last_error().decode()} (status {rc})")
     return output_logs
+
+
+def prefill_chunked(token_ids, embed_weight, layer_weights_packed, cos_table, sin_table, k_cache, v_cache,
+                    num_layers, start_position, max_seq_len, attn_scale):
+    """``prefill`` on the tensor cores (chunks of up to 512 tokens, tcgen05 GEMMs; fp16 weights only).
+    ``token_ids``: CPU int32 tensor.  Blocks; raises ``RuntimeError`` on any reported error."""
+    _require_cuda()
+    _check((not token_ids.is_cuda) and token_ids.dtype == torch.int32 and token_ids.is_contiguous(),
+           "prefill_chunked: token_ids must be a contiguous CPU int32 tensor")
+    _check_table(layer_weights_packed, "prefill_chunked")
+    rc = _lib.qmk_prefill_chunked(
+        token_ids.data_ptr(), int(token_ids.numel()), _ptr(embed_weight), _ptr(layer_weights_packed),
+        _ptr(cos_table), _ptr(sin_table), _ptr(k_cache), _ptr(v_cache), int(num_layers), int(start_position),
+        int(max_seq_len), float(attn_scale), _stream())
+    if rc != 0:
+        raise RuntimeError(f"prefill_chunked: {_lib.qmk_last_error().decode()} (status {rc})")
+    return None
 
 
 def gemm_f16_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
