@@ -124,6 +124,7 @@ __device__ __noinline__ float grp_poll_vec(const Params &P, int what, int layer,
 __device__ __noinline__ uint32_t grp_gemv_k1024(const Params &P, uint32_t chunk, int kind, int layer, int step, float ss) {
   Ctx c = make_ctx(P, chunk);
   const int wfmt = P.wfmt;
+  uint32_t seen = 0;   // issued-chunk counter cache (chunk_wait)
   const uint32_t tag = layer_tag(P, layer, step);
   const float *x = c.g(kind == K_GU ? G_X1 : G_X);
   unsigned long long *out = c.llw + (kind == K_GU ? LL_INTER : LL_QKV);
@@ -155,7 +156,7 @@ __device__ __noinline__ uint32_t grp_gemv_k1024(const Params &P, uint32_t chunk,
       const int r0 = ch << rsh;
       const int nr = min(RPC, nrows - r0);                      // warp-uniform
       float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
-      const bool ok = wait_full(P, c, idx);
+      const bool ok = wait_full(P, c, idx, seen);
       if (ok) {
         const unsigned char *p = c.slot(idx);
         if (kind == K_GU) {   // values 0,1 = gate rows, 2,3 = up rows
@@ -209,6 +210,7 @@ __device__ __noinline__ uint32_t grp_gemv_k1024(const Params &P, uint32_t chunk,
 // O (K = 2048, two rows per chunk) and down (K = 3072, one row per chunk) projections with residual.
 __device__ __noinline__ uint32_t grp_gemv_wide(const Params &P, uint32_t chunk, int kind, int layer, int step) {
   Ctx c = make_ctx(P, chunk);
+  uint32_t seen = 0;   // issued-chunk counter cache (chunk_wait)
   const uint32_t tag = layer_tag(P, layer, step);
   const float *act = c.g(G_VEC), *resid = c.g(kind == K_O ? G_X : G_X1);
   unsigned long long *out = c.llw + (kind == K_O ? LL_X1 : LL_X2);
@@ -229,7 +231,7 @@ __device__ __noinline__ uint32_t grp_gemv_wide(const Params &P, uint32_t chunk, 
       const int r0 = ch << rsh;
       const bool two = (nrows - r0) > 1 && RPC > 1;             // warp-uniform
       float p0 = 0.f, p1 = 0.f;
-      const bool ok = wait_full(P, c, idx);
+      const bool ok = wait_full(P, c, idx, seen);
       if (ok) {
         const unsigned char *w0 = c.slot(idx), *w1 = w0 + rb;
         float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -271,6 +273,7 @@ __device__ __noinline__ uint32_t grp_gemv_wide(const Params &P, uint32_t chunk, 
 // order, the cache rows of every sequence's item on this CTA: the chunks of the other sequences are skipped.
 __device__ __noinline__ uint32_t grp_attention(const Params &P, uint32_t chunk, int layer, int step) {
   Ctx c = make_ctx(P, chunk);
+  uint32_t seen = 0;   // issued-chunk counter cache (chunk_wait)
   const uint32_t tag = layer_tag(P, layer, step);
   const __half *nv = c.norms(layer_serial(P, layer, step) & 1u);
   AttnItem it;
@@ -367,7 +370,7 @@ __device__ __noinline__ uint32_t grp_attention(const Params &P, uint32_t chunk, 
   for (int j = c.gwarp; j < it.nchunks; j += c.gw) {
     const uint32_t idx = c.chunk + static_cast<uint32_t>(j);
     const int nrow = min(it.rpc, (p1 - p0) - j * it.rpc);
-    if (wait_full(P, c, idx)) {
+    if (wait_full(P, c, idx, seen)) {
       const unsigned char *kslot = c.slot(idx) + seg * 16;
 #pragma unroll 2
       for (int r = grp; r < nrow; r += 2) {

@@ -353,27 +353,39 @@ __device__ __forceinline__ bool mbar_wait(const Params &P, const Ctx &c, uint64_
 // says "complete".  So the wait first makes sure the producer has issued chunk `idx` (flags()[6] counts
 // issued chunks): from then on the slot's barrier is in use n and the parity is unambiguous.  Warps
 // that jump ahead in the ring (a group skipping another sequence's cache rows) depend on this.
-__device__ __forceinline__ bool chunk_wait(const Params &P, const Ctx &c, uint32_t idx) {
+#ifndef QMK_ISSUED_CHECK
+#define QMK_ISSUED_CHECK 1
+#endif
+#ifndef QMK_ISSUED_FENCE
+#define QMK_ISSUED_FENCE 1
+#endif
+// `seen` caches the last value read of the counter (it only grows): the producer usually runs a ring ahead,
+// so one read covers the next several chunks.  Callers keep it in a local and start it at 0.
+__device__ __forceinline__ bool chunk_wait(const Params &P, const Ctx &c, uint32_t idx, uint32_t &seen) {
   volatile int *fl = c.flags();
-  if (static_cast<uint32_t>(fl[6]) <= idx) {
-    unsigned long long t0 = 0;
-    uint32_t it = 0;
-    for (;;) {
-      if (static_cast<uint32_t>(fl[6]) > idx) break;
-      if ((++it & 31u) == 0u) {
-        if (fl[0]) return false;
-        if (ld_relaxed_u32(P.status) != 0u) { fl[0] = 1; return false; }
-        const unsigned long long t = now_ns();
-        if (t0 == 0) t0 = t;
-        if (t - t0 > P.timeout_ns) { raise_error(P, c, QMK_ERR_WAIT_TIMEOUT, WHERE_FULL); return false; }
+  if (QMK_ISSUED_CHECK && seen <= idx) {
+    seen = static_cast<uint32_t>(fl[6]);
+    if (seen <= idx) {
+      unsigned long long t0 = 0;
+      uint32_t it = 0;
+      for (;;) {
+        seen = static_cast<uint32_t>(fl[6]);
+        if (seen > idx) break;
+        if ((++it & 31u) == 0u) {
+          if (fl[0]) return false;
+          if (ld_relaxed_u32(P.status) != 0u) { fl[0] = 1; return false; }
+          const unsigned long long t = now_ns();
+          if (t0 == 0) t0 = t;
+          if (t - t0 > P.timeout_ns) { raise_error(P, c, QMK_ERR_WAIT_TIMEOUT, WHERE_FULL); return false; }
+        }
       }
     }
   }
   return mbar_wait(P, c, c.full(idx % NSLOTS), (idx / NSLOTS) & 1u, WHERE_FULL, false);
 }
 // The whole warp takes the same branch afterwards (shuffles follow).
-__device__ __forceinline__ bool wait_full(const Params &P, const Ctx &c, uint32_t idx) {
-  return __all_sync(0xffffffffu, chunk_wait(P, c, idx));
+__device__ __forceinline__ bool wait_full(const Params &P, const Ctx &c, uint32_t idx, uint32_t &seen) {
+  return __all_sync(0xffffffffu, chunk_wait(P, c, idx, seen));
 }
 
 // Rows [r0, r1) of an n-row matrix owned by CTA `cta` of `ncta` (launch-time only: 64-bit divisions).
@@ -474,8 +486,12 @@ __device__ __forceinline__ bool produce_chunk(const Params &P, const Ctx &c, uin
   bulk_g2s(dst, src, bytes, c.full(slot), pol);
   if (src2) bulk_g2s(dst + SLOT_BYTES / 2, src2, bytes, c.full(slot), pol);
   ++idx;
+#if QMK_ISSUED_CHECK
+#if QMK_ISSUED_FENCE
   __threadfence_block();          // the barrier's new use is visible before the count that announces it
+#endif
   c.flags()[6] = static_cast<int>(idx);
+#endif
   return true;
 }
 
@@ -500,7 +516,16 @@ __device__ __forceinline__ bool produce_phase(const Params &P, const Ctx &c, uin
   return true;
 }
 
-__device__ __forceinline__ void producer_main(const Params &P, const Ctx &c) {
+#ifndef QMK_PRODUCER_INLINE
+#define QMK_PRODUCER_INLINE 0
+#endif
+#if QMK_PRODUCER_INLINE
+__device__ __forceinline__
+#else
+// Not inlined: inside the kernel its loops raise the register pressure of the consumer path (kernel-level spills).
+__device__ __noinline__
+#endif
+void producer_main(const Params &P, const Ctx c) {
   const uint64_t pol = P.l2_evict_first ? l2_evict_first_policy() : l2_evict_normal_policy();
   uint32_t idx = 0;
   bool ok = true;
@@ -701,6 +726,7 @@ __device__ __forceinline__ void norm_to_regs(const Ctx &c, const float *x, float
 __device__ __noinline__ uint32_t gemv_k1024(const Params &P, Ctx c, int kind, const float *x, float ss,
                                             const __half *norm_w, unsigned long long *out, uint32_t tag, float *dump) {
   const int wfmt = P.wfmt;
+  uint32_t seen = 0;   // issued-chunk counter cache (chunk_wait)
   float a[32];
   norm_to_regs(c, x, ss, norm_w, a);
   if (kind == K_LM && c.cta == 0 && c.warp == 0 && (P.normalized_out || P.hidden_out)) {  // reference-signature outputs
@@ -721,6 +747,15 @@ __device__ __noinline__ uint32_t gemv_k1024(const Params &P, Ctx c, int kind, co
   float best = -INFINITY;
   int best_i = 0x7fffffff;
   const int n = t->nseg[kind];
+  // The issued-chunk check of chunk_wait can be skipped when the slot's previous use (NSLOTS chunks back) is
+  // known to have landed: (a) the phase has at most NSLOTS chunks on this CTA, so that use belongs to an
+  // earlier phase, which every warp finished before the barrier that opened this one; (b) LM head: one
+  // segment, NB * G = 9 chunks per pass and NSLOTS = 2 * 9 + G, so that use is a chunk this very warp
+  // consumed two passes ago.  Reduced grids (more chunks per phase) take the checked wait.
+  static_assert(NSLOTS == 21 && NB * (CONS_WARPS >> 2) == 9, "case (b) above is written for these values");
+  int phase_chunks = 0;
+  for (int s = 0; s < n; ++s) phase_chunks += (t->nrows[kind][s] + RPC - 1) >> rsh;
+  const bool plain_wait = (kind == K_LM) || phase_chunks <= NSLOTS;
   for (int s = 0; s < n; ++s) {
     const int nrows = t->nrows[kind][s];
     const int out0 = t->out0[kind][s];
@@ -737,7 +772,8 @@ __device__ __noinline__ uint32_t gemv_k1024(const Params &P, Ctx c, int kind, co
         valid[b] = ch < nchunks && ((ch << rsh) + sub) < nrows;          // warp-uniform
         if (valid[b]) {
           const uint32_t idx = c.chunk + static_cast<uint32_t>(ch);
-          ok &= chunk_wait(P, c, idx);
+          ok &= plain_wait ? mbar_wait(P, c, c.full(idx % NSLOTS), (idx / NSLOTS) & 1u, WHERE_FULL, false)
+                           : chunk_wait(P, c, idx, seen);
         }
       }
       ok = __all_sync(0xffffffffu, ok);   // the whole warp takes the same branch (shuffles follow)
@@ -801,6 +837,7 @@ __device__ __noinline__ uint32_t gemv_wide(const Params &P, Ctx c, int kind, con
                                            unsigned long long *out, uint32_t tag) {
   const int rsh = kind == K_O ? 1 : 0;
   const int wfmt = P.wfmt;
+  uint32_t seen = 0;   // issued-chunk counter cache (chunk_wait)
   const int RPC = 1 << rsh, G = CONS_WARPS >> rsh, K = kind == K_O ? QS : I, rb = kind_row_bytes(kind, wfmt);
   const int kiters = K / 256;    // 256 weights per warp pass: 8 or 12
   const SegTab *t = c.segs();
@@ -818,7 +855,7 @@ __device__ __noinline__ uint32_t gemv_wide(const Params &P, Ctx c, int kind, con
       bool have = false;
       if (ch < nchunks && row < nrows) {            // warp-uniform
         const uint32_t idx = c.chunk + static_cast<uint32_t>(ch);
-        if (wait_full(P, c, idx)) {
+        if (wait_full(P, c, idx, seen)) {
           const unsigned char *wrow = c.slot(idx) + sub * rb;
           float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
@@ -859,6 +896,7 @@ __device__ __noinline__ uint32_t gemv_wide(const Params &P, Ctx c, int kind, con
 __device__ __noinline__ uint32_t attention_phase(const Params &P, Ctx c, const __half *nv, int layer, int pos,
                                                  uint32_t tag) {
   const AttnItem it = attn_item(P, c, 0, 1, CONS_WARPS, pos);
+  uint32_t seen = 0;   // issued-chunk counter cache (chunk_wait)
   float *s_q = c.f(F_Q), *s_knew = c.f(F_KNEW), *s_vnew = c.f(F_VNEW), *s_wpart = c.f(F_WPART), *s_misc = c.f(F_MISC);
   const float *s_cs = c.f(F_CS);
   const unsigned long long *qkv = c.llr + LL_QKV;
@@ -939,7 +977,7 @@ __device__ __noinline__ uint32_t attention_phase(const Params &P, Ctx c, const _
   for (int j = c.warp; j < it.nchunks; j += CONS_WARPS) {
     const uint32_t idx = c.chunk + static_cast<uint32_t>(j);
     const int nrow = min(it.rpc, (p1 - p0) - j * it.rpc);
-    if (wait_full(P, c, idx)) {
+    if (wait_full(P, c, idx, seen)) {
       const unsigned char *kslot = c.slot(idx) + seg * 16;
 #pragma unroll 2
       for (int r = grp; r < nrow; r += 2) {
