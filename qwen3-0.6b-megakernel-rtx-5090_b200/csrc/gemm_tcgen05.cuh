@@ -1,9 +1,10 @@
 // C[M x N] (fp32) = A[M x K] (fp16, row-major) * B[N x K]^T (fp16, row-major) on the sm_100a tensor cores.
 //
-// One CTA per 128 x 128 output tile, warp-specialised:
-//   warp 0   : one thread streams 128 x 64 tiles of A and of B with tiled TMA loads (128-byte swizzle)
-//              into a 4-stage shared-memory ring (full/empty mbarriers);
-//   warp 1   : allocates 128 TMEM columns, then one thread issues tcgen05.mma (M 128, N 128, K 16; four per
+// One CTA per 128 x BN output tile (BN = 128, or 64 when 128-wide tiles would leave most SMs idle),
+// warp-specialised:
+//   warp 0   : one thread streams 128 x 64 tiles of A and BN x 64 tiles of B with tiled TMA loads (128-byte
+//              swizzle) into a 4-stage shared-memory ring (full/empty mbarriers);
+//   warp 1   : allocates BN TMEM columns, then one thread issues tcgen05.mma (M 128, N BN, K 16; four per
 //              64-wide K block) with shared-memory matrix descriptors, commits each stage back to the
 //              producer and finally commits the accumulator to the epilogue;
 //   warps 2-5: read the fp32 accumulator from TMEM (tcgen05.ld, each warp its own 32-lane quarter) and store
@@ -23,13 +24,12 @@
 
 namespace qmk_gemm {
 
-constexpr int BM = 128, BN = 128, BK = 64;       // BK * 2 bytes = one 128-byte swizzle row
+constexpr int BM = 128, BK = 64;                 // BK * 2 bytes = one 128-byte swizzle row; the N tile (128 or 64) is a template parameter
 constexpr int STAGES = 4;
 constexpr int THREADS = 192;
 constexpr uint32_t TILE_A_BYTES = BM * BK * 2;   // 16 KB
-constexpr uint32_t TILE_B_BYTES = BN * BK * 2;   // 16 KB
-constexpr uint32_t STAGE_BYTES = TILE_A_BYTES + TILE_B_BYTES;
-constexpr uint32_t TMEM_COLS = 128;              // fp32 accumulator: 128 lanes x 128 columns
+constexpr uint32_t TILE_B_MAX_BYTES = 128 * BK * 2;
+constexpr uint32_t STAGE_BYTES = TILE_A_BYTES + TILE_B_MAX_BYTES;   // the 64-wide variant uses half of the B part
 constexpr size_t SMEM_BYTES = 1024 /* alignment slack */ + static_cast<size_t>(STAGES) * STAGE_BYTES + 256;
 
 __device__ __forceinline__ uint32_t s32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -85,9 +85,12 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
   return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 // Instruction descriptor: fp32 accumulator, fp16 A and B, both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
-constexpr uint32_t IDESC = (1u << 4) | (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+constexpr uint32_t idesc_for(int bn) {
+  return (1u << 4) | (static_cast<uint32_t>(bn >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+}
 
-__device__ __forceinline__ void mma_f16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate) {
+__device__ __forceinline__ void mma_f16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate,
+                                           uint32_t IDESC) {
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
@@ -101,6 +104,7 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+template <int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, float *C, int M,
                    int N, int K, unsigned int *status, unsigned long long budget_ns) {
@@ -114,6 +118,8 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
   const int kblocks = K / BK;
+  constexpr uint32_t TILE_B_BYTES = BN * BK * 2;
+  constexpr uint32_t TMEM_COLS = BN;             // fp32 accumulator: 128 lanes x BN columns (a power of two >= 32)
   auto full = [&](int s) { return bars + 8u * s; };
   auto empty = [&](int s) { return bars + 8u * (STAGES + s); };
   const uint32_t acc_full = bars + 8u * (2 * STAGES);
@@ -141,7 +147,7 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         const int s = kb % STAGES;
         if (kb >= STAGES && !bar_wait(empty(s), ((kb / STAGES) - 1) & 1, abort_flag, status, budget_ns)) break;
         if (*abort_flag) break;
-        bar_expect_tx(full(s), STAGE_BYTES);
+        bar_expect_tx(full(s), TILE_A_BYTES + TILE_B_BYTES);
         tma_load_2d(base + s * STAGE_BYTES, &map_a, kb * BK, m0, full(s));
         tma_load_2d(base + s * STAGE_BYTES + TILE_A_BYTES, &map_b, kb * BK, n0, full(s));
         issued = kb + 1;
@@ -168,7 +174,7 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         const uint64_t db = smem_desc_sw128(base + s * STAGE_BYTES + TILE_A_BYTES);
 #pragma unroll
         for (int j = 0; j < BK / 16; ++j)   // 16 halves = 32 bytes = 2 descriptor address units per K step
-          mma_f16_ss(tmem_base, da + 2u * j, db + 2u * j, (kb > 0 || j > 0) ? 1u : 0u);
+          mma_f16_ss(tmem_base, da + 2u * j, db + 2u * j, (kb > 0 || j > 0) ? 1u : 0u, idesc_for(BN));
         mma_commit(empty(s));               // the stage is free once these MMAs have read it
       }
       if (ok) mma_commit(acc_full);         // accumulator complete

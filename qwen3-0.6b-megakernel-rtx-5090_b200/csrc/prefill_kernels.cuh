@@ -116,30 +116,31 @@ __global__ void qk_norm_rope_cache(const float *q, const float *k, const float *
 }
 
 // Causal attention of the chunk's queries over cache rows [0, pos0 + t] (the chunk's own rows are already
-// in the cache).  grid = (ceil(T / 16), 8 kv heads), block = 128 = 4 warps.  A CTA takes 16 query tokens x the
-// two query heads of its kv head; a warp takes 4 tokens and works on both heads of a token together (they
-// share every K and V row).  Keys go through shared memory in tiles of 32: lane j scores key j, and every
+// in the cache).  grid = (ceil(T / 16), 8 kv heads), block = 256 = 8 warps.  A CTA takes 16 query tokens x the
+// two query heads of its kv head; a warp takes 2 tokens and works on both heads of a token together (they
+// share every K and V row).  Query tiles are handed out last-first: the longest ones start first.  Keys go through shared memory in tiles of 32: lane j scores key j, and every
 // lane owns 4 of the 128 output dims.  Online softmax in fp32, base-2 exponent.
 constexpr int ATT_Q = 16, ATT_KEYS = 32;
 constexpr int ATT_KPITCH = D + 2;   // halves per K row in shared memory: an odd number of 32-bit words
-__global__ void __launch_bounds__(128) causal_attention(const float *qr, const __half *k_cache_layer,
+__global__ void __launch_bounds__(256) causal_attention(const float *qr, const __half *k_cache_layer,
                                                         const __half *v_cache_layer, __half *out, int T, int pos0,
                                                         int max_seq_len, float scale) {
   __shared__ __align__(16) __half sk[ATT_KEYS * ATT_KPITCH];
   __shared__ __align__(16) __half sv[ATT_KEYS * D];
   __shared__ __align__(16) float sq[ATT_Q * 2 * D];   // [token][head-in-pair][128]
-  __shared__ float sp[4][2][ATT_KEYS];                 // probabilities of the two heads, per warp
-  const int g = blockIdx.y, t0 = blockIdx.x * ATT_Q;
+  __shared__ float sp[8][2][ATT_KEYS];                 // probabilities of the two heads, per warp
+  const int g = blockIdx.y, t0 = (gridDim.x - 1 - blockIdx.x) * ATT_Q;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = min(ATT_Q, T - t0);
-  for (int i = threadIdx.x; i < ATT_Q * 2 * D; i += 128) {
+  for (int i = threadIdx.x; i < ATT_Q * 2 * D; i += 256) {
     const int tk = i / (2 * D), h = (i / D) & 1, d = i % D, tok = t0 + tk;
     sq[i] = (tok < T) ? qr[(static_cast<size_t>(tok) * NQ + 2 * g + h) * D + d] : 0.f;
   }
   const float sc = scale * 1.4426950408889634f;
-  float m[4][2], l[4][2], acc[4][2][4];
+  constexpr int TPW = 2;   // tokens per warp
+  float m[TPW][2], l[TPW][2], acc[TPW][2][4];
 #pragma unroll
-  for (int r = 0; r < 4; ++r)
+  for (int r = 0; r < TPW; ++r)
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       m[r][h] = -INFINITY; l[r][h] = 0.f;
@@ -151,7 +152,7 @@ __global__ void __launch_bounds__(128) causal_attention(const float *qr, const _
   const __half *vbase = v_cache_layer + static_cast<size_t>(g) * max_seq_len * D;
   for (int k0 = 0; k0 <= last_key; k0 += ATT_KEYS) {
     __syncthreads();   // previous tile fully used (also orders the sq fill before the first use)
-    for (int i = threadIdx.x; i < ATT_KEYS * (D / 8); i += 128) {
+    for (int i = threadIdx.x; i < ATT_KEYS * (D / 8); i += 256) {
       const int j = i / (D / 8), c = i % (D / 8);
       uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
       if (k0 + j <= last_key) {
@@ -164,8 +165,8 @@ __global__ void __launch_bounds__(128) causal_attention(const float *qr, const _
     }
     __syncthreads();
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int tk = warp * 4 + r, tok = t0 + tk;
+    for (int r = 0; r < TPW; ++r) {
+      const int tk = warp * TPW + r, tok = t0 + tk;
       if (tok >= T) continue;                       // warp-uniform
       const int limit = pos0 + tok;                 // last visible key of this query token
       if (k0 > limit) continue;                     // warp-uniform
@@ -209,8 +210,8 @@ __global__ void __launch_bounds__(128) causal_attention(const float *qr, const _
     }
   }
 #pragma unroll
-  for (int r = 0; r < 4; ++r) {
-    const int tok = t0 + warp * 4 + r;
+  for (int r = 0; r < TPW; ++r) {
+    const int tok = t0 + warp * TPW + r;
     if (tok >= T) continue;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {

@@ -26,6 +26,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
 std::mutex g_mu;
 EncodeTiledFn g_encode = nullptr;
 bool g_attr_set[16] = {};
+int g_sms[16] = {};
 
 // The driver's tensor-map encoder, looked up through the runtime (no link against libcuda).
 EncodeTiledFn encoder() {
@@ -57,10 +58,22 @@ int make_map_f16(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t cols
   return QMK_OK;
 }
 
-// C[M x N] fp32 = A[M x K] * B[N x K]^T.  M, N multiples of 128; K a multiple of 64.
-int launch_gemm(const CUtensorMap &map_a, const CUtensorMap &map_b, float *C, int M, int N, int K, unsigned int *status,
-                int timeout_ms, cudaStream_t stream, std::string *err) {
-  if (M <= 0 || N <= 0 || K <= 0 || M % qmk_gemm::BM || N % qmk_gemm::BN || K % qmk_gemm::BK) {
+// C[M x N] fp32 = A[M x K] * B[N x K]^T.  M, N multiples of 128; K a multiple of 64.  `map_b` must have been
+// made with gemm_box_n(M, N) rows per box: 64-wide N tiles when 128-wide ones would leave most SMs idle.
+int gemm_box_n(int M, int N) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int sms = (dev >= 0 && dev < 16) ? g_sms[dev] : 0;
+  if (sms == 0) {
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (dev >= 0 && dev < 16) g_sms[dev] = sms;
+  }
+  return ((M / qmk_gemm::BM) * (N / 128) * 3 < sms * 2) ? 64 : 128;
+}
+
+int launch_gemm(const CUtensorMap &map_a, const CUtensorMap &map_b, float *C, int M, int N, int K, int box_n,
+                unsigned int *status, int timeout_ms, cudaStream_t stream, std::string *err) {
+  if (M <= 0 || N <= 0 || K <= 0 || M % qmk_gemm::BM || N % 128 || K % qmk_gemm::BK || (box_n != 64 && box_n != 128)) {
     *err = "gemm: M and N must be multiples of 128 and K a multiple of 64";
     return QMK_ERR_BAD_ARGUMENT;
   }
@@ -69,15 +82,23 @@ int launch_gemm(const CUtensorMap &map_a, const CUtensorMap &map_b, float *C, in
   {
     std::lock_guard<std::mutex> lock(g_mu);
     if (dev >= 0 && dev < 16 && !g_attr_set[dev]) {
-      cudaError_t e = cudaFuncSetAttribute(qmk_gemm::gemm_f16_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      cudaError_t e = cudaFuncSetAttribute(qmk_gemm::gemm_f16_tn_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(qmk_gemm::SMEM_BYTES));
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(qmk_gemm::gemm_f16_tn_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(qmk_gemm::SMEM_BYTES));
       if (e != cudaSuccess) { *err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e); return QMK_ERR_CUDA; }
       g_attr_set[dev] = true;
     }
   }
-  dim3 grid(N / qmk_gemm::BN, M / qmk_gemm::BM);
-  qmk_gemm::gemm_f16_tn_kernel<<<grid, qmk_gemm::THREADS, qmk_gemm::SMEM_BYTES, stream>>>(
-      map_a, map_b, C, M, N, K, status, static_cast<unsigned long long>(timeout_ms) * 1000000ull);
+  dim3 grid(N / box_n, M / qmk_gemm::BM);
+  const unsigned long long budget = static_cast<unsigned long long>(timeout_ms) * 1000000ull;
+  if (box_n == 64)
+    qmk_gemm::gemm_f16_tn_kernel<64><<<grid, qmk_gemm::THREADS, qmk_gemm::SMEM_BYTES, stream>>>(map_a, map_b, C, M, N, K,
+                                                                                              status, budget);
+  else
+    qmk_gemm::gemm_f16_tn_kernel<128><<<grid, qmk_gemm::THREADS, qmk_gemm::SMEM_BYTES, stream>>>(map_a, map_b, C, M, N, K,
+                                                                                               status, budget);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { *err = std::string("gemm launch: ") + cudaGetErrorString(e); return QMK_ERR_CUDA; }
   return QMK_OK;
@@ -102,7 +123,7 @@ struct Workspace {                  // per device, allocated on first use, never
   // weight maps of the layer table seen last (rebuilt when the table's contents change)
   unsigned long long table[MAX_LAYERS * 12] = {};
   int table_layers = 0;
-  CUtensorMap wmap[MAX_LAYERS][7];  // q, k, v, o, gate, up, down
+  CUtensorMap wmap[MAX_LAYERS][7][2];  // q, k, v, o, gate, up, down; boxes of 64 and of 128 rows
 };
 Workspace g_ws[16];
 std::mutex g_ws_mu;
@@ -162,8 +183,10 @@ int ensure_weight_maps(Workspace &w, const LDGLayerWeight *layers_dev, int num_l
     for (int j = 0; j < 7; ++j) {
       const void *ptr = reinterpret_cast<const void *>(host[static_cast<size_t>(l) * 12 + slot[j]]);
       if (!ptr) return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "prefill: null weight pointer in the layer table");
-      const int rc = qmk_tc::make_map_f16(&w.wmap[l][j], ptr, rows[j], cols[j], qmk_gemm::BN, &err);
-      if (rc != QMK_OK) return qmk_internal::report(rc, err);
+      for (int b = 0; b < 2; ++b) {
+        const int rc = qmk_tc::make_map_f16(&w.wmap[l][j][b], ptr, rows[j], cols[j], b ? 128 : 64, &err);
+        if (rc != QMK_OK) return qmk_internal::report(rc, err);
+      }
     }
   memcpy(w.table, host.data(), host.size() * 8);
   w.table_layers = num_layers;
@@ -208,8 +231,9 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
   const size_t layer_stride = static_cast<size_t>(NKV) * max_seq_len * D;
   PF_CUDA(cudaMemsetAsync(w.status, 0, 16, stream));
   std::string err;
-  auto gemm = [&](const CUtensorMap &a, const CUtensorMap &b, float *c, int M, int N, int K) {
-    return qmk_tc::launch_gemm(a, b, c, M, N, K, w.status, env.timeout_ms, stream, &err);
+  auto gemm = [&](const CUtensorMap &a, const CUtensorMap (&b)[2], float *c, int M, int N, int K) {
+    const int box_n = qmk_tc::gemm_box_n(M, N);
+    return qmk_tc::launch_gemm(a, b[box_n == 128], c, M, N, K, box_n, w.status, env.timeout_ms, stream, &err);
   };
   for (int c0 = 0; c0 < num_tokens; c0 += CHUNK) {
     const int T = (num_tokens - c0 < CHUNK) ? num_tokens - c0 : CHUNK;
@@ -228,7 +252,7 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
                                                          reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv, w.qr, kc, vc,
                                                          pos0, max_seq_len);
       if (l == num_layers - 1) break;   // the cache is complete; nothing downstream of the last layer is kept
-      causal_attention<<<dim3((T + ATT_Q - 1) / ATT_Q, NKV), 128, 0, stream>>>(w.qr, kc, vc, w.attn, T, pos0, max_seq_len,
+      causal_attention<<<dim3((T + ATT_Q - 1) / ATT_Q, NKV), 256, 0, stream>>>(w.qr, kc, vc, w.attn, T, pos0, max_seq_len,
                                                                               attn_scale);
       if ((rc = gemm(w.map_attn, w.wmap[l][3], w.o, M, H, QS)) != QMK_OK) break;
       add_rmsnorm_rows<<<T, 256, 0, stream>>>(w.x, w.o, reinterpret_cast<const __half *>(r[7]), w.xn);
@@ -254,11 +278,12 @@ extern "C" int qmk_gemm_f16_tn(const void *a, const void *b, float *c, int m, in
   CUtensorMap ma, mb;
   unsigned int *status = nullptr;
   int rc = qmk_tc::make_map_f16(&ma, a, m, k, qmk_gemm::BM, &err);
-  if (rc == QMK_OK) rc = qmk_tc::make_map_f16(&mb, b, n, k, qmk_gemm::BN, &err);
+  const int box_n = (m > 0 && n > 0 && m % 128 == 0 && n % 128 == 0) ? qmk_tc::gemm_box_n(m, n) : 128;
+  if (rc == QMK_OK) rc = qmk_tc::make_map_f16(&mb, b, n, k, box_n, &err);
   if (rc == QMK_OK && cudaMalloc(&status, 16) != cudaSuccess) { rc = QMK_ERR_CUDA; err = "cudaMalloc failed"; }
   if (rc == QMK_OK) {
     cudaMemsetAsync(status, 0, 16, stream);
-    rc = qmk_tc::launch_gemm(ma, mb, c, m, n, k, status, 2000, stream, &err);
+    rc = qmk_tc::launch_gemm(ma, mb, c, m, n, k, box_n, status, 2000, stream, &err);
   }
   if (rc == QMK_OK) {
     unsigned int host[4] = {0, 0, 0, 0};
