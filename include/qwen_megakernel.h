@@ -229,6 +229,22 @@ int qmk_prefill_chunked(
     void *k_cache, void *v_cache, int num_layers, int start_position, int max_seq_len,
     float attn_scale, cudaStream_t stream);
 
+/* Greedy decode of up to 128 sequences on the tensor-core path (the batched configurations): each step runs
+ * the seven projections and the LM head as tcgen05 GEMMs over one 128-row tile of sequences, with row kernels
+ * for the norms, per-head QK-norm + RoPE + cache write (each sequence at its own position in its own cache),
+ * per-sequence attention over the cache, SwiGLU and the argmax.  Same arguments as qmk_generate_batch (host
+ * arrays of num_sequences entries; no EOS stop; logits dump [sequence][step][vocab]); fp16 weights only, vocab
+ * a multiple of 128; blocks until done.  One step costs about 400 kernel launches, so it pays from roughly
+ * eight sequences on; below that qmk_generate_batch (one persistent launch) is faster.  Numerics as
+ * qmk_prefill_chunked (GEMM operands rounded to fp16). */
+int qmk_decode_batched(
+    int num_sequences, const int *first_token_ids, const int *start_positions,
+    int num_steps, const void *embed_weight,
+    const struct LDGLayerWeight *layer_weights, const void *final_norm_weight,
+    const void *lm_head_weight, const void *cos_table, const void *sin_table,
+    void *const *k_caches, void *const *v_caches, int *const *output_logs,
+    int num_layers, int max_seq_len, float attn_scale, cudaStream_t stream);
+
 /* C[m x n] (fp32, row-major, DEVICE) = A[m x k] * B[n x k]^T with fp16 row-major DEVICE operands, on the
  * tcgen05 tensor cores (TMA-fed, accumulator in TMEM).  m and n multiples of 128, k a multiple of 64,
  * operands 16-byte aligned.  This is the GEMM the chunked prefill is built from; the reference has no

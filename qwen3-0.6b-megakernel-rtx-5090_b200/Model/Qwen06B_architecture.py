@@ -305,13 +305,24 @@ class BatchDecoder:
     the ``prefill`` op, then all sequences decode together.
     """
 
-    MAX_SEQUENCES = 4
+    MAX_SEQUENCES = 4            # per persistent launch
+    MAX_GEMM_SEQUENCES = 128     # per call of the tensor-core batched decode
 
     def __init__(self, weights=None, tokenizer=None, num_sequences: int = 4, max_seq_len: int = MAX_SEQ_LEN,
-                 verbose: bool = False, **decoder_kw):
-        if not 1 <= int(num_sequences) <= self.MAX_SEQUENCES:
-            raise ValueError("num_sequences must be 1..4")
-        self.num_sequences = int(num_sequences)
+                 verbose: bool = False, engine: str = "auto", **decoder_kw):
+        """``engine``: "persistent" (one megakernel launch, <= 4 sequences, fp32 activations), "gemm" (tcgen05
+        GEMMs per step, <= 128 sequences, fp16 GEMM operands, fp16 weights only) or "auto" (persistent up to 4
+        sequences, gemm above)."""
+        n = int(num_sequences)
+        if engine == "auto":
+            engine = "persistent" if n <= self.MAX_SEQUENCES else "gemm"
+        if engine not in ("persistent", "gemm"):
+            raise ValueError("engine must be 'auto', 'persistent' or 'gemm'")
+        limit = self.MAX_SEQUENCES if engine == "persistent" else self.MAX_GEMM_SEQUENCES
+        if not 1 <= n <= limit:
+            raise ValueError(f"num_sequences must be 1..{limit} for the {engine} engine")
+        self.engine = engine
+        self.num_sequences = n
         # slot 0 owns the weights, tables and the first cache; the other slots only add caches
         self._base = Decoder(weights=weights, tokenizer=tokenizer, max_seq_len=max_seq_len, verbose=verbose,
                              **decoder_kw)
@@ -326,7 +337,7 @@ class BatchDecoder:
                       for _ in range(self.num_sequences)]
         self._logs_cpu = torch.empty(self.num_sequences, self.max_seq_len, dtype=torch.int32).pin_memory()
         self.positions = [0] * self.num_sequences
-        self._gen_batch = _require_megakernel_op("generate_batch")
+        self._gen_batch = _require_megakernel_op("generate_batch" if engine == "persistent" else "decode_batched")
 
     def prefill_slot(self, b: int, ids: Sequence[int]) -> None:
         """Fill slot ``b``'s KV cache with ``ids`` from position 0 (the ``prefill`` op)."""

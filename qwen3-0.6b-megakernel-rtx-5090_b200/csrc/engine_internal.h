@@ -13,6 +13,7 @@ struct PrefillEnv {
   int timeout_ms;
   int wfmt;               // 0 fp16 weights, 1 fp8 rows
   int rope_from_table;
+  float *logits_out;      // debug dump set through qmk_set_logits_dump (may be null)
 };
 // Engine of the current device, created on first use; clears its last error.
 int prefill_env(int max_seq_len, cudaStream_t stream, PrefillEnv *out);

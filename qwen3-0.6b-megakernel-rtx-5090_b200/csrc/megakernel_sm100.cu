@@ -339,6 +339,7 @@ int prefill_env(int max_seq_len, cudaStream_t stream, PrefillEnv *out) {
   out->timeout_ms = e->timeout_ms;
   out->wfmt = e->wfmt;
   out->rope_from_table = e->rope_from_table;
+  out->logits_out = e->logits_out;
   return QMK_OK;
 }
 int report(int code, const std::string &msg) {

@@ -64,12 +64,20 @@ __global__ void add_rmsnorm_rows(float *x, const float *add, const __half *w, __
 // fp32 (qr[t][head][128]); K (normalised, rotated) and V go to the fp16 cache rows of this layer.
 // grid = (T, 4), block = 256 = 8 warps; warp w of block y handles head slot y * 8 + w of 32:
 // 0..15 query heads, 16..23 K heads, 24..31 V heads.
+// Two addressing modes: one sequence (row t at position pos0 + t of the one cache), or - `positions` non-null -
+// one row per sequence (row t at positions[t] of sequence t's own cache, k_ptrs[t] / v_ptrs[t] + layer_off).
 __global__ void qk_norm_rope_cache(const float *q, const float *k, const float *v, const __half *q_norm,
                                    const __half *k_norm, const float *rope, const __half *cos_table,
                                    const __half *sin_table, float *qr, __half *k_cache_layer, __half *v_cache_layer,
-                                   int pos0, int max_seq_len) {
+                                   int pos0, int max_seq_len, const int *positions, __half *const *k_ptrs,
+                                   __half *const *v_ptrs, size_t layer_off) {
   const int t = blockIdx.x, slot = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  const int pos = pos0 + t;
+  int pos = pos0 + t;
+  if (positions) {
+    pos = positions[t];
+    k_cache_layer = k_ptrs[t] + layer_off;
+    v_cache_layer = v_ptrs[t] + layer_off;
+  }
   if (slot >= 24) {   // V head: plain copy to the cache
     const int g = slot - 24;
     const float *src = v + static_cast<size_t>(t) * KVS + g * D;
@@ -219,6 +227,130 @@ __global__ void __launch_bounds__(256) causal_attention(const float *qr, const _
       __half *dst = out + static_cast<size_t>(tok) * QS + (2 * g + h) * D + lane * 4;
       *reinterpret_cast<__half2 *>(dst) = __floats2half2_rn(acc[r][h][0] * inv, acc[r][h][1] * inv);
       *reinterpret_cast<__half2 *>(dst + 2) = __floats2half2_rn(acc[r][h][2] * inv, acc[r][h][3] * inv);
+    }
+  }
+}
+
+// Decode-step attention for a batch of sequences: sequence b's single query token over its own cache rows
+// [0, positions[b]] (the new row is already in the cache).  grid = (B, 8 kv heads), block = 256 = 8 warps.
+// Warps take 32-key tiles round-robin straight from global memory: lane j scores key j for both query heads of
+// the group (q in shared memory, broadcast reads), probabilities travel by shuffle, every lane owns 4 output
+// dims; the eight warps' partial softmax states are merged through shared memory.
+__global__ void __launch_bounds__(256) decode_attention_seq(const float *qr, __half *const *k_ptrs, __half *const *v_ptrs,
+                                                            size_t layer_off, const int *positions, __half *out,
+                                                            int max_seq_len, float scale) {
+  __shared__ __align__(16) float sq[2 * D];
+  __shared__ float sm[8][2], sl[8][2];
+  __shared__ __align__(16) float sacc[8][2][D];
+  const int b = blockIdx.x, g = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nkeys = positions[b] + 1;
+  sq[threadIdx.x] = qr[(static_cast<size_t>(b) * NQ + 2 * g + (threadIdx.x >> 7)) * D + (threadIdx.x & (D - 1))];
+  __syncthreads();
+  const __half *kbase = k_ptrs[b] + layer_off + static_cast<size_t>(g) * max_seq_len * D;
+  const __half *vbase = v_ptrs[b] + layer_off + static_cast<size_t>(g) * max_seq_len * D;
+  const float sc = scale * 1.4426950408889634f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int k0 = warp * 32; k0 < nkeys; k0 += 8 * 32) {
+    const int key = k0 + lane;
+    float sa = 0.f, sb = 0.f;
+    if (key < nkeys) {
+      const uint4 *krow = reinterpret_cast<const uint4 *>(kbase + static_cast<size_t>(key) * D);
+#pragma unroll 4
+      for (int c = 0; c < D / 8; ++c) {
+        const uint4 kv = __ldg(krow + c);
+        const __half2 *h = reinterpret_cast<const __half2 *>(&kv);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 kf = __half22float2(h[i]);
+          const float2 qa = *reinterpret_cast<const float2 *>(sq + c * 8 + 2 * i);
+          const float2 qb = *reinterpret_cast<const float2 *>(sq + D + c * 8 + 2 * i);
+          sa = fmaf(qa.x, kf.x, sa); sa = fmaf(qa.y, kf.y, sa);
+          sb = fmaf(qb.x, kf.x, sb); sb = fmaf(qb.y, kf.y, sb);
+        }
+      }
+      sa *= sc; sb *= sc;
+    } else {
+      sa = -INFINITY; sb = -INFINITY;
+    }
+    const float na = fmaxf(m0, warp_max(sa)), nb = fmaxf(m1, warp_max(sb));   // lane 0's key is always valid
+    const float ca = exp2f(m0 - na), cb = exp2f(m1 - nb);
+    const float pa = exp2f(sa - na), pb = exp2f(sb - nb);
+    l0 = l0 * ca + warp_sum(pa);
+    l1 = l1 * cb + warp_sum(pb);
+    m0 = na; m1 = nb;
+#pragma unroll
+    for (int d = 0; d < 4; ++d) { a0[d] *= ca; a1[d] *= cb; }
+    const int nj = min(32, nkeys - k0);   // warp-uniform
+#pragma unroll 4
+    for (int j = 0; j < nj; ++j) {
+      const float pja = __shfl_sync(0xffffffffu, pa, j), pjb = __shfl_sync(0xffffffffu, pb, j);
+      const uint2 vv = __ldg(reinterpret_cast<const uint2 *>(vbase + static_cast<size_t>(k0 + j) * D + lane * 4));
+      const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&vv.x));
+      const float2 v23 = __half22float2(*reinterpret_cast<const __half2 *>(&vv.y));
+      a0[0] = fmaf(pja, v01.x, a0[0]); a0[1] = fmaf(pja, v01.y, a0[1]);
+      a0[2] = fmaf(pja, v23.x, a0[2]); a0[3] = fmaf(pja, v23.y, a0[3]);
+      a1[0] = fmaf(pjb, v01.x, a1[0]); a1[1] = fmaf(pjb, v01.y, a1[1]);
+      a1[2] = fmaf(pjb, v23.x, a1[2]); a1[3] = fmaf(pjb, v23.y, a1[3]);
+    }
+  }
+  if (lane == 0) { sm[warp][0] = m0; sm[warp][1] = m1; sl[warp][0] = l0; sl[warp][1] = l1; }
+#pragma unroll
+  for (int d = 0; d < 4; ++d) { sacc[warp][0][lane * 4 + d] = a0[d]; sacc[warp][1][lane * 4 + d] = a1[d]; }
+  __syncthreads();
+  {
+    const int h = threadIdx.x >> 7, d = threadIdx.x & (D - 1);
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) M = fmaxf(M, sm[w][h]);
+    float L = 0.f, A = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const float mw = sm[w][h];
+      const float s = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+      L = fmaf(sl[w][h], s, L);
+      A = fmaf(sacc[w][h][d], s, A);
+    }
+    out[static_cast<size_t>(b) * QS + (2 * g + h) * D + d] = __float2half_rn(A / L);
+  }
+}
+
+// Greedy pick per row: tokens[b] = argmax(logits[b][:]) (lowest index on ties), logged at log_ptrs[b][step];
+// the sequence's position advances by one.  grid = B, block = 1024.
+__global__ void __launch_bounds__(1024) argmax_rows(const float *logits, int vocab, int *tokens, int *const *log_ptrs,
+                                                    int step, int *positions) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const int b = blockIdx.x;
+  const float *row = logits + static_cast<size_t>(b) * vocab;
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int i = threadIdx.x; i < vocab; i += 1024) {
+    const float v = row[i];
+    if (v > best) { best = v; best_i = i; }      // increasing i per thread: strict > keeps the lowest index
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = best_i; }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    best = sv[threadIdx.x];
+    best_i = si[threadIdx.x];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    if (threadIdx.x == 0) {
+      tokens[b] = best_i;
+      if (log_ptrs[b]) log_ptrs[b][step] = best_i;
+      positions[b] += 1;
     }
   }
 }

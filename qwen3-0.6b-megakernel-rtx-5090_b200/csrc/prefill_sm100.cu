@@ -120,6 +120,14 @@ struct Workspace {                  // per device, allocated on first use, never
   __half *xn = nullptr, *attn = nullptr, *act = nullptr;
   unsigned int *status = nullptr;
   CUtensorMap map_xn, map_attn, map_act;
+  // batched decode: per-sequence state and the logits of one step
+  int *positions = nullptr;
+  __half **k_ptrs = nullptr, **v_ptrs = nullptr;
+  int **log_ptrs = nullptr;
+  float *logits = nullptr;
+  int logits_vocab = 0;
+  const void *lm_ptr = nullptr;
+  CUtensorMap map_lm;
   // weight maps of the layer table seen last (rebuilt when the table's contents change)
   unsigned long long table[MAX_LAYERS * 12] = {};
   int table_layers = 0;
@@ -250,7 +258,7 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
       if ((rc = gemm(w.map_xn, w.wmap[l][2], w.v, M, KVS, H)) != QMK_OK) break;
       qk_norm_rope_cache<<<dim3(T, 4), 256, 0, stream>>>(w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]),
                                                          reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv, w.qr, kc, vc,
-                                                         pos0, max_seq_len);
+                                                         pos0, max_seq_len, nullptr, nullptr, nullptr, 0);
       if (l == num_layers - 1) break;   // the cache is complete; nothing downstream of the last layer is kept
       causal_attention<<<dim3((T + ATT_Q - 1) / ATT_Q, NKV), 256, 0, stream>>>(w.qr, kc, vc, w.attn, T, pos0, max_seq_len,
                                                                               attn_scale);
@@ -270,6 +278,138 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
   PF_CUDA(cudaStreamSynchronize(stream));
   if (host_status[0] != 0)
     return qmk_internal::report(static_cast<int>(host_status[0]), "prefill: a bounded device wait ran out");
+  return QMK_OK;
+}
+
+// ----------------------------------------------------------------------------- batched decode on the GEMM path
+namespace {
+constexpr int MAX_BATCH = 128;      // one 128-row GEMM tile of sequences
+
+int ensure_decode_workspace(Workspace &w, const void *lm_head, int vocab) {
+  if (!w.positions) {
+    PF_CUDA(cudaMalloc(&w.positions, sizeof(int) * MAX_BATCH));
+    PF_CUDA(cudaMalloc(&w.k_ptrs, sizeof(void *) * MAX_BATCH));
+    PF_CUDA(cudaMalloc(&w.v_ptrs, sizeof(void *) * MAX_BATCH));
+    PF_CUDA(cudaMalloc(&w.log_ptrs, sizeof(void *) * MAX_BATCH));
+  }
+  if (w.logits_vocab < vocab) {
+    if (w.logits) cudaFree(w.logits);
+    w.logits = nullptr;
+    w.logits_vocab = 0;
+    PF_CUDA(cudaMalloc(&w.logits, sizeof(float) * static_cast<size_t>(MAX_BATCH) * vocab));
+    w.logits_vocab = vocab;
+    w.lm_ptr = nullptr;
+  }
+  if (w.lm_ptr != lm_head) {
+    std::string err;
+    const int rc = qmk_tc::make_map_f16(&w.map_lm, lm_head, vocab, qmk_pf::H, 128, &err);
+    if (rc != QMK_OK) return qmk_internal::report(rc, err);
+    w.lm_ptr = lm_head;
+  }
+  return QMK_OK;
+}
+}  // namespace
+
+extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids, const int *start_positions, int num_steps,
+                                  const void *embed_weight, const LDGLayerWeight *layer_weights,
+                                  const void *final_norm_weight, const void *lm_head_weight, const void *cos_table,
+                                  const void *sin_table, void *const *k_caches, void *const *v_caches,
+                                  int *const *output_logs, int num_layers, int max_seq_len, float attn_scale,
+                                  cudaStream_t stream) {
+  using namespace qmk_pf;
+  if (num_steps <= 0) return QMK_OK;
+  qmk_internal::PrefillEnv env;
+  int rc = qmk_internal::prefill_env(max_seq_len, stream, &env);
+  if (rc != QMK_OK) return rc;
+  if (num_sequences < 1 || num_sequences > MAX_BATCH)
+    return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "qmk_decode_batched: num_sequences must be in [1, 128]");
+  if (!first_token_ids || !start_positions || !k_caches || !v_caches || !output_logs || !embed_weight || !layer_weights ||
+      !final_norm_weight || !lm_head_weight)
+    return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "qmk_decode_batched: null pointer argument");
+  if (env.wfmt != 0)
+    return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "qmk_decode_batched handles fp16 weights only");
+  if (env.vocab % 128 != 0)
+    return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "qmk_decode_batched needs a vocabulary that is a multiple of 128");
+  if (num_layers < 1 || num_layers > MAX_LAYERS)
+    return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "num_layers must be in [1, 48]");
+  if (env.rope_from_table && (!cos_table || !sin_table))
+    return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "rope_from_table needs cos/sin tables");
+  const int B = num_sequences;
+  for (int b = 0; b < B; ++b) {
+    if (!k_caches[b] || !v_caches[b] || !output_logs[b])
+      return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "qmk_decode_batched: null cache or log pointer");
+    if (start_positions[b] < 0 || start_positions[b] + num_steps > max_seq_len)
+      return qmk_internal::report(QMK_ERR_POSITION, "start_position + steps exceeds max_seq_len");
+    if (first_token_ids[b] < 0 || first_token_ids[b] >= env.vocab)
+      return qmk_internal::report(QMK_ERR_BAD_TOKEN, "first token outside [0, vocab)");
+    for (int a = 0; a < b; ++a)
+      if (k_caches[a] == k_caches[b] || v_caches[a] == v_caches[b] || output_logs[a] == output_logs[b])
+        return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "qmk_decode_batched: two sequences share a cache or an output log");
+  }
+  int dev = 0;
+  PF_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 16) return qmk_internal::report(QMK_ERR_CUDA, "device index out of range");
+  std::lock_guard<std::mutex> lock(g_ws_mu);
+  Workspace &w = g_ws[dev];
+  rc = ensure_workspace(w);
+  if (rc == QMK_OK) rc = ensure_weight_maps(w, layer_weights, num_layers, stream);
+  if (rc == QMK_OK) rc = ensure_decode_workspace(w, lm_head_weight, env.vocab);
+  if (rc != QMK_OK) return rc;
+  std::vector<unsigned long long> rec(w.table, w.table + static_cast<size_t>(num_layers) * 12);
+  const float *rope = env.rope_from_table ? nullptr : env.rope;
+  const __half *cosv = static_cast<const __half *>(cos_table), *sinv = static_cast<const __half *>(sin_table);
+  const size_t layer_stride = static_cast<size_t>(NKV) * max_seq_len * D;
+  PF_CUDA(cudaMemsetAsync(w.status, 0, 16, stream));
+  PF_CUDA(cudaMemcpyAsync(w.tokens, first_token_ids, sizeof(int) * B, cudaMemcpyHostToDevice, stream));
+  PF_CUDA(cudaMemcpyAsync(w.positions, start_positions, sizeof(int) * B, cudaMemcpyHostToDevice, stream));
+  PF_CUDA(cudaMemcpyAsync(w.k_ptrs, k_caches, sizeof(void *) * B, cudaMemcpyHostToDevice, stream));
+  PF_CUDA(cudaMemcpyAsync(w.v_ptrs, v_caches, sizeof(void *) * B, cudaMemcpyHostToDevice, stream));
+  PF_CUDA(cudaMemcpyAsync(w.log_ptrs, output_logs, sizeof(void *) * B, cudaMemcpyHostToDevice, stream));
+  std::string err;
+  const int M = qmk_gemm::BM;   // one tile of rows; rows >= B are computed and ignored
+  auto gemm = [&](const CUtensorMap &a, const CUtensorMap (&bmap)[2], float *c, int N, int K) {
+    const int box_n = qmk_tc::gemm_box_n(M, N);
+    return qmk_tc::launch_gemm(a, bmap[box_n == 128], c, M, N, K, box_n, w.status, env.timeout_ms, stream, &err);
+  };
+  for (int step = 0; step < num_steps && rc == QMK_OK; ++step) {
+    embed_rows<<<B, 256, 0, stream>>>(w.tokens, static_cast<const __half *>(embed_weight), w.x);
+    for (int l = 0; l < num_layers; ++l) {
+      const unsigned long long *r = rec.data() + static_cast<size_t>(l) * 12;
+      const size_t layer_off = l * layer_stride;
+      add_rmsnorm_rows<<<B, 256, 0, stream>>>(w.x, l > 0 ? w.down : nullptr, reinterpret_cast<const __half *>(r[0]), w.xn);
+      if ((rc = gemm(w.map_xn, w.wmap[l][0], w.q, QS, H)) != QMK_OK) break;
+      if ((rc = gemm(w.map_xn, w.wmap[l][1], w.k, KVS, H)) != QMK_OK) break;
+      if ((rc = gemm(w.map_xn, w.wmap[l][2], w.v, KVS, H)) != QMK_OK) break;
+      qk_norm_rope_cache<<<dim3(B, 4), 256, 0, stream>>>(w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]),
+                                                         reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv, w.qr, nullptr,
+                                                         nullptr, 0, max_seq_len, w.positions, w.k_ptrs, w.v_ptrs, layer_off);
+      decode_attention_seq<<<dim3(B, NKV), 256, 0, stream>>>(w.qr, w.k_ptrs, w.v_ptrs, layer_off, w.positions, w.attn,
+                                                             max_seq_len, attn_scale);
+      if ((rc = gemm(w.map_attn, w.wmap[l][3], w.o, H, QS)) != QMK_OK) break;
+      add_rmsnorm_rows<<<B, 256, 0, stream>>>(w.x, w.o, reinterpret_cast<const __half *>(r[7]), w.xn);
+      if ((rc = gemm(w.map_xn, w.wmap[l][4], w.gate, I, H)) != QMK_OK) break;
+      if ((rc = gemm(w.map_xn, w.wmap[l][5], w.up, I, H)) != QMK_OK) break;
+      silu_mul_rows<<<(B * I + 255) / 256, 256, 0, stream>>>(w.gate, w.up, w.act, static_cast<size_t>(B) * I);
+      if ((rc = gemm(w.map_act, w.wmap[l][6], w.down, H, I)) != QMK_OK) break;
+    }
+    if (rc != QMK_OK) break;
+    add_rmsnorm_rows<<<B, 256, 0, stream>>>(w.x, w.down, static_cast<const __half *>(final_norm_weight), w.xn);
+    rc = qmk_tc::launch_gemm(w.map_xn, w.map_lm, w.logits, M, env.vocab, H, 128, w.status, env.timeout_ms, stream, &err);
+    if (rc != QMK_OK) break;
+    argmax_rows<<<B, 1024, 0, stream>>>(w.logits, env.vocab, w.tokens, w.log_ptrs, step, w.positions);
+    PF_CUDA(cudaGetLastError());
+    if (env.logits_out)   // debug dump [sequence][step][vocab]
+      for (int b = 0; b < B; ++b)
+        PF_CUDA(cudaMemcpyAsync(env.logits_out + (static_cast<size_t>(b) * num_steps + step) * env.vocab,
+                                w.logits + static_cast<size_t>(b) * env.vocab, sizeof(float) * env.vocab,
+                                cudaMemcpyDeviceToDevice, stream));
+  }
+  if (rc != QMK_OK) return qmk_internal::report(rc, err);
+  unsigned int host_status[4] = {0, 0, 0, 0};
+  PF_CUDA(cudaMemcpyAsync(host_status, w.status, 16, cudaMemcpyDeviceToHost, stream));
+  PF_CUDA(cudaStreamSynchronize(stream));
+  if (host_status[0] != 0)
+    return qmk_internal::report(static_cast<int>(host_status[0]), "decode_batched: a bounded device wait ran out");
   return QMK_OK;
 }
 

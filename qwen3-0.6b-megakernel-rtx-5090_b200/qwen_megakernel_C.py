@@ -66,6 +66,8 @@ _lib.qmk_generate_static.argtypes = [_I, _I, *([_P] * 7), _P, _I, _I, _I, _F, _I
 _lib.qmk_generate_static.restype = _I
 _lib.qmk_generate_batch.argtypes = [_I, _P, _P, _I, *([_P] * 6), _P, _P, _P, _I, _I, _F, _I, _P]
 _lib.qmk_generate_batch.restype = _I
+_lib.qmk_decode_batched.argtypes = [_I, _P, _P, _I, *([_P] * 6), _P, _P, _P, _I, _I, _F, _P]
+_lib.qmk_decode_batched.restype = _I
 _lib.qmk_prefill_chunked.argtypes = [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _P]
 _lib.qmk_prefill_chunked.restype = _I
 _lib.qmk_gemm_f16_tn.argtypes = [_P, _P, _P, _I, _I, _I, _P]
@@ -80,7 +82,7 @@ _lib.qmk_selftest_wait_timeout.restype = _I
 EXPORTED_SYMBOLS = (
     "launch_ldg_decode_direct", "launch_ldg_decode_persistent", "launch_ldg_generate_nosync",
     "launch_ldg_prefill", "qmk_abi_version", "qmk_configure", "qmk_set_inv_freq", "qmk_set_logits_dump",
-    "qmk_set_weight_format", "qmk_set_tuning", "qmk_set_tuning2", "qmk_set_profile_buffer", "qmk_decode", "qmk_generate", "qmk_generate_static", "qmk_generate_batch", "qmk_gemm_f16_tn", "qmk_prefill_chunked", "qmk_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
+    "qmk_set_weight_format", "qmk_set_tuning", "qmk_set_tuning2", "qmk_set_profile_buffer", "qmk_decode", "qmk_generate", "qmk_generate_static", "qmk_generate_batch", "qmk_gemm_f16_tn", "qmk_decode_batched", "qmk_prefill_chunked", "qmk_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
     "qmk_scratch_bytes", "qmk_selftest_wait_timeout",
 )
 
@@ -287,6 +289,35 @@ def generate_batch(first_token_ids, start_positions, num_steps, embed_weight, la
         1 if synchronize else 0, _stream())
     if rc != 0:
         raise RuntimeError(f"generate_batch: {_lib.qmk_last_error().decode()} (status {rc})")
+    return output_logs
+
+
+MAX_GEMM_BATCH_SEQUENCES = 128
+
+
+def decode_batched(first_token_ids, start_positions, num_steps, embed_weight, layer_weights_packed,
+                   final_norm_weight, lm_head_weight, cos_table, sin_table, k_caches, v_caches, output_logs,
+                   num_layers, max_seq_len, attn_scale):
+    """``generate_batch`` for up to 128 sequences on the tensor-core path (tcgen05 GEMMs per step instead of
+    one persistent kernel; fp16 weights only).  Same arguments and result."""
+    _require_cuda()
+    n = len(first_token_ids)
+    _check(1 <= n <= MAX_GEMM_BATCH_SEQUENCES, "decode_batched: 1 to 128 sequences per call")
+    _check(len(start_positions) == n and len(k_caches) == n and len(v_caches) == n and len(output_logs) == n,
+           "decode_batched: per-sequence lists differ in length")
+    for log in output_logs:
+        _check(log.dtype == torch.int32 and log.is_cuda and log.is_contiguous() and log.numel() >= num_steps,
+               "decode_batched: each output_log must be a contiguous int32 CUDA tensor of >= num_steps entries")
+    _check_table(layer_weights_packed, "decode_batched")
+    ints = ctypes.c_int * n
+    ptrs = ctypes.c_void_p * n
+    rc = _lib.qmk_decode_batched(
+        n, ints(*[int(t) for t in first_token_ids]), ints(*[int(p) for p in start_positions]), int(num_steps),
+        _ptr(embed_weight), _ptr(layer_weights_packed), _ptr(final_norm_weight), _ptr(lm_head_weight),
+        _ptr(cos_table), _ptr(sin_table), ptrs(*[_ptr(t) for t in k_caches]), ptrs(*[_ptr(t) for t in v_caches]),
+        ptrs(*[_ptr(t) for t in output_logs]), int(num_layers), int(max_seq_len), float(attn_scale), _stream())
+    if rc != 0:
+        raise RuntimeError(f"decode_batched: {_lib.qmk_last_error().decode()} (status {rc})")
     return output_logs
 
 
