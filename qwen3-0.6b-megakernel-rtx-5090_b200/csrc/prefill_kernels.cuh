@@ -316,10 +316,11 @@ __global__ void __launch_bounds__(256) decode_attention_seq(const float *qr, __h
   }
 }
 
-// Greedy pick per row: tokens[b] = argmax(logits[b][:]) (lowest index on ties), logged at log_ptrs[b][step];
-// the sequence's position advances by one.  grid = B, block = 1024.
+// Greedy pick per row: tokens[b] = argmax(logits[b][:]) (lowest index on ties), logged at
+// log_ptrs[b][positions[b] - start_positions[b]] (= the step index, kept out of the arguments so that one
+// captured graph serves every step); the sequence's position advances by one.  grid = B, block = 1024.
 __global__ void __launch_bounds__(1024) argmax_rows(const float *logits, int vocab, int *tokens, int *const *log_ptrs,
-                                                    int step, int *positions) {
+                                                    const int *start_positions, int *positions) {
   __shared__ float sv[32];
   __shared__ int si[32];
   const int b = blockIdx.x;
@@ -349,8 +350,9 @@ __global__ void __launch_bounds__(1024) argmax_rows(const float *logits, int voc
     }
     if (threadIdx.x == 0) {
       tokens[b] = best_i;
-      if (log_ptrs[b]) log_ptrs[b][step] = best_i;
-      positions[b] += 1;
+      const int pos = positions[b];
+      if (log_ptrs[b]) log_ptrs[b][pos - start_positions[b]] = best_i;
+      positions[b] = pos + 1;
     }
   }
 }

@@ -71,26 +71,31 @@ int gemm_box_n(int M, int N) {
   return ((M / qmk_gemm::BM) * (N / 128) * 3 < sms * 2) ? 64 : 128;
 }
 
+// Opt-in shared-memory size of both tile variants, once per device (outside any stream capture).
+int ensure_gemm_attrs(std::string *err) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (dev >= 0 && dev < 16 && !g_attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(qmk_gemm::gemm_f16_tn_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(qmk_gemm::SMEM_BYTES));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(qmk_gemm::gemm_f16_tn_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(qmk_gemm::SMEM_BYTES));
+    if (e != cudaSuccess) { *err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e); return QMK_ERR_CUDA; }
+    g_attr_set[dev] = true;
+  }
+  return QMK_OK;
+}
+
 int launch_gemm(const CUtensorMap &map_a, const CUtensorMap &map_b, float *C, int M, int N, int K, int box_n,
                 unsigned int *status, int timeout_ms, cudaStream_t stream, std::string *err) {
   if (M <= 0 || N <= 0 || K <= 0 || M % qmk_gemm::BM || N % 128 || K % qmk_gemm::BK || (box_n != 64 && box_n != 128)) {
     *err = "gemm: M and N must be multiples of 128 and K a multiple of 64";
     return QMK_ERR_BAD_ARGUMENT;
   }
-  int dev = 0;
-  cudaGetDevice(&dev);
-  {
-    std::lock_guard<std::mutex> lock(g_mu);
-    if (dev >= 0 && dev < 16 && !g_attr_set[dev]) {
-      cudaError_t e = cudaFuncSetAttribute(qmk_gemm::gemm_f16_tn_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(qmk_gemm::SMEM_BYTES));
-      if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(qmk_gemm::gemm_f16_tn_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(qmk_gemm::SMEM_BYTES));
-      if (e != cudaSuccess) { *err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e); return QMK_ERR_CUDA; }
-      g_attr_set[dev] = true;
-    }
-  }
+  const int arc = ensure_gemm_attrs(err);
+  if (arc != QMK_OK) return arc;
   dim3 grid(N / box_n, M / qmk_gemm::BM);
   const unsigned long long budget = static_cast<unsigned long long>(timeout_ms) * 1000000ull;
   if (box_n == 64)
@@ -121,7 +126,11 @@ struct Workspace {                  // per device, allocated on first use, never
   unsigned int *status = nullptr;
   CUtensorMap map_xn, map_attn, map_act;
   // batched decode: per-sequence state and the logits of one step
-  int *positions = nullptr;
+  int *positions = nullptr, *start_positions = nullptr;
+  cudaStream_t gstream = nullptr;        // capture needs a non-default stream
+  cudaEvent_t ev_in = nullptr, ev_out = nullptr;
+  cudaGraphExec_t step_graph = nullptr;  // one decode step; valid while step_key matches
+  unsigned long long step_key[12] = {};
   __half **k_ptrs = nullptr, **v_ptrs = nullptr;
   int **log_ptrs = nullptr;
   float *logits = nullptr;
@@ -198,6 +207,7 @@ int ensure_weight_maps(Workspace &w, const LDGLayerWeight *layers_dev, int num_l
     }
   memcpy(w.table, host.data(), host.size() * 8);
   w.table_layers = num_layers;
+  w.step_key[0] = 0;   // a captured decode step holds the old maps
   return QMK_OK;
 }
 
@@ -283,11 +293,21 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
 
 // ----------------------------------------------------------------------------- batched decode on the GEMM path
 namespace {
+unsigned int __float_as_uint_host(float f) {
+  unsigned int u;
+  memcpy(&u, &f, 4);
+  return u;
+}
+
 constexpr int MAX_BATCH = 128;      // one 128-row GEMM tile of sequences
 
 int ensure_decode_workspace(Workspace &w, const void *lm_head, int vocab) {
   if (!w.positions) {
     PF_CUDA(cudaMalloc(&w.positions, sizeof(int) * MAX_BATCH));
+    PF_CUDA(cudaMalloc(&w.start_positions, sizeof(int) * MAX_BATCH));
+    PF_CUDA(cudaStreamCreateWithFlags(&w.gstream, cudaStreamNonBlocking));
+    PF_CUDA(cudaEventCreateWithFlags(&w.ev_in, cudaEventDisableTiming));
+    PF_CUDA(cudaEventCreateWithFlags(&w.ev_out, cudaEventDisableTiming));
     PF_CUDA(cudaMalloc(&w.k_ptrs, sizeof(void *) * MAX_BATCH));
     PF_CUDA(cudaMalloc(&w.v_ptrs, sizeof(void *) * MAX_BATCH));
     PF_CUDA(cudaMalloc(&w.log_ptrs, sizeof(void *) * MAX_BATCH));
@@ -362,47 +382,93 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
   PF_CUDA(cudaMemsetAsync(w.status, 0, 16, stream));
   PF_CUDA(cudaMemcpyAsync(w.tokens, first_token_ids, sizeof(int) * B, cudaMemcpyHostToDevice, stream));
   PF_CUDA(cudaMemcpyAsync(w.positions, start_positions, sizeof(int) * B, cudaMemcpyHostToDevice, stream));
+  PF_CUDA(cudaMemcpyAsync(w.start_positions, start_positions, sizeof(int) * B, cudaMemcpyHostToDevice, stream));
   PF_CUDA(cudaMemcpyAsync(w.k_ptrs, k_caches, sizeof(void *) * B, cudaMemcpyHostToDevice, stream));
   PF_CUDA(cudaMemcpyAsync(w.v_ptrs, v_caches, sizeof(void *) * B, cudaMemcpyHostToDevice, stream));
   PF_CUDA(cudaMemcpyAsync(w.log_ptrs, output_logs, sizeof(void *) * B, cudaMemcpyHostToDevice, stream));
   std::string err;
+  if ((rc = qmk_tc::ensure_gemm_attrs(&err)) != QMK_OK) return qmk_internal::report(rc, err);
+  (void)qmk_tc::gemm_box_n(128, 128);   // caches the SM count before any capture
   const int M = qmk_gemm::BM;   // one tile of rows; rows >= B are computed and ignored
-  auto gemm = [&](const CUtensorMap &a, const CUtensorMap (&bmap)[2], float *c, int N, int K) {
-    const int box_n = qmk_tc::gemm_box_n(M, N);
-    return qmk_tc::launch_gemm(a, bmap[box_n == 128], c, M, N, K, box_n, w.status, env.timeout_ms, stream, &err);
-  };
-  for (int step = 0; step < num_steps && rc == QMK_OK; ++step) {
-    embed_rows<<<B, 256, 0, stream>>>(w.tokens, static_cast<const __half *>(embed_weight), w.x);
+  // One decode step for all sequences, enqueued on `s`.  Everything that changes from step to step (tokens,
+  // positions) or from call to call (cache and log pointers) lives in device arrays at fixed addresses, so the
+  // same sequence of launches - and a graph captured from it - serves every step.
+  auto enqueue_step = [&](cudaStream_t s) -> int {
+    auto gemm = [&](const CUtensorMap &a, const CUtensorMap (&bmap)[2], float *c, int N, int K) {
+      const int box_n = qmk_tc::gemm_box_n(M, N);
+      return qmk_tc::launch_gemm(a, bmap[box_n == 128], c, M, N, K, box_n, w.status, env.timeout_ms, s, &err);
+    };
+    int r2 = QMK_OK;
+    embed_rows<<<B, 256, 0, s>>>(w.tokens, static_cast<const __half *>(embed_weight), w.x);
     for (int l = 0; l < num_layers; ++l) {
       const unsigned long long *r = rec.data() + static_cast<size_t>(l) * 12;
       const size_t layer_off = l * layer_stride;
-      add_rmsnorm_rows<<<B, 256, 0, stream>>>(w.x, l > 0 ? w.down : nullptr, reinterpret_cast<const __half *>(r[0]), w.xn);
-      if ((rc = gemm(w.map_xn, w.wmap[l][0], w.q, QS, H)) != QMK_OK) break;
-      if ((rc = gemm(w.map_xn, w.wmap[l][1], w.k, KVS, H)) != QMK_OK) break;
-      if ((rc = gemm(w.map_xn, w.wmap[l][2], w.v, KVS, H)) != QMK_OK) break;
-      qk_norm_rope_cache<<<dim3(B, 4), 256, 0, stream>>>(w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]),
-                                                         reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv, w.qr, nullptr,
-                                                         nullptr, 0, max_seq_len, w.positions, w.k_ptrs, w.v_ptrs, layer_off);
-      decode_attention_seq<<<dim3(B, NKV), 256, 0, stream>>>(w.qr, w.k_ptrs, w.v_ptrs, layer_off, w.positions, w.attn,
-                                                             max_seq_len, attn_scale);
-      if ((rc = gemm(w.map_attn, w.wmap[l][3], w.o, H, QS)) != QMK_OK) break;
-      add_rmsnorm_rows<<<B, 256, 0, stream>>>(w.x, w.o, reinterpret_cast<const __half *>(r[7]), w.xn);
-      if ((rc = gemm(w.map_xn, w.wmap[l][4], w.gate, I, H)) != QMK_OK) break;
-      if ((rc = gemm(w.map_xn, w.wmap[l][5], w.up, I, H)) != QMK_OK) break;
-      silu_mul_rows<<<(B * I + 255) / 256, 256, 0, stream>>>(w.gate, w.up, w.act, static_cast<size_t>(B) * I);
-      if ((rc = gemm(w.map_act, w.wmap[l][6], w.down, H, I)) != QMK_OK) break;
+      add_rmsnorm_rows<<<B, 256, 0, s>>>(w.x, l > 0 ? w.down : nullptr, reinterpret_cast<const __half *>(r[0]), w.xn);
+      if ((r2 = gemm(w.map_xn, w.wmap[l][0], w.q, QS, H)) != QMK_OK) return r2;
+      if ((r2 = gemm(w.map_xn, w.wmap[l][1], w.k, KVS, H)) != QMK_OK) return r2;
+      if ((r2 = gemm(w.map_xn, w.wmap[l][2], w.v, KVS, H)) != QMK_OK) return r2;
+      qk_norm_rope_cache<<<dim3(B, 4), 256, 0, s>>>(w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]),
+                                                    reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv, w.qr, nullptr,
+                                                    nullptr, 0, max_seq_len, w.positions, w.k_ptrs, w.v_ptrs, layer_off);
+      decode_attention_seq<<<dim3(B, NKV), 256, 0, s>>>(w.qr, w.k_ptrs, w.v_ptrs, layer_off, w.positions, w.attn,
+                                                        max_seq_len, attn_scale);
+      if ((r2 = gemm(w.map_attn, w.wmap[l][3], w.o, H, QS)) != QMK_OK) return r2;
+      add_rmsnorm_rows<<<B, 256, 0, s>>>(w.x, w.o, reinterpret_cast<const __half *>(r[7]), w.xn);
+      if ((r2 = gemm(w.map_xn, w.wmap[l][4], w.gate, I, H)) != QMK_OK) return r2;
+      if ((r2 = gemm(w.map_xn, w.wmap[l][5], w.up, I, H)) != QMK_OK) return r2;
+      silu_mul_rows<<<(B * I + 255) / 256, 256, 0, s>>>(w.gate, w.up, w.act, static_cast<size_t>(B) * I);
+      if ((r2 = gemm(w.map_act, w.wmap[l][6], w.down, H, I)) != QMK_OK) return r2;
     }
-    if (rc != QMK_OK) break;
-    add_rmsnorm_rows<<<B, 256, 0, stream>>>(w.x, w.down, static_cast<const __half *>(final_norm_weight), w.xn);
-    rc = qmk_tc::launch_gemm(w.map_xn, w.map_lm, w.logits, M, env.vocab, H, 128, w.status, env.timeout_ms, stream, &err);
-    if (rc != QMK_OK) break;
-    argmax_rows<<<B, 1024, 0, stream>>>(w.logits, env.vocab, w.tokens, w.log_ptrs, step, w.positions);
-    PF_CUDA(cudaGetLastError());
-    if (env.logits_out)   // debug dump [sequence][step][vocab]
+    add_rmsnorm_rows<<<B, 256, 0, s>>>(w.x, w.down, static_cast<const __half *>(final_norm_weight), w.xn);
+    r2 = qmk_tc::launch_gemm(w.map_xn, w.map_lm, w.logits, M, env.vocab, H, 128, w.status, env.timeout_ms, s, &err);
+    if (r2 != QMK_OK) return r2;
+    argmax_rows<<<B, 1024, 0, s>>>(w.logits, env.vocab, w.tokens, w.log_ptrs, w.start_positions, w.positions);
+    return QMK_OK;
+  };
+
+  if (env.logits_out) {
+    // debug dump [sequence][step][vocab]: plain launches with a copy after every step
+    for (int step = 0; step < num_steps && rc == QMK_OK; ++step) {
+      rc = enqueue_step(stream);
+      if (rc != QMK_OK) break;
+      PF_CUDA(cudaGetLastError());
       for (int b = 0; b < B; ++b)
         PF_CUDA(cudaMemcpyAsync(env.logits_out + (static_cast<size_t>(b) * num_steps + step) * env.vocab,
                                 w.logits + static_cast<size_t>(b) * env.vocab, sizeof(float) * env.vocab,
                                 cudaMemcpyDeviceToDevice, stream));
+    }
+  } else {
+    // One step costs about 400 launches: capture it once as a CUDA graph (kept while nothing it bakes in
+    // changes) and replay it num_steps times.
+    const unsigned long long key[12] = {
+        1ull, static_cast<unsigned long long>(B), static_cast<unsigned long long>(num_layers),
+        static_cast<unsigned long long>(max_seq_len), static_cast<unsigned long long>(env.vocab),
+        static_cast<unsigned long long>(__float_as_uint_host(attn_scale)), reinterpret_cast<unsigned long long>(embed_weight),
+        reinterpret_cast<unsigned long long>(final_norm_weight), reinterpret_cast<unsigned long long>(lm_head_weight),
+        reinterpret_cast<unsigned long long>(rope), reinterpret_cast<unsigned long long>(cos_table),
+        reinterpret_cast<unsigned long long>(sin_table) ^ (static_cast<unsigned long long>(env.timeout_ms) << 48)};
+    if (memcmp(key, w.step_key, sizeof(key)) != 0) {
+      if (w.step_graph) { cudaGraphExecDestroy(w.step_graph); w.step_graph = nullptr; }
+      w.step_key[0] = 0;
+      cudaGraph_t graph = nullptr;
+      PF_CUDA(cudaStreamBeginCapture(w.gstream, cudaStreamCaptureModeThreadLocal));
+      rc = enqueue_step(w.gstream);
+      cudaError_t ce = cudaStreamEndCapture(w.gstream, &graph);   // always end the capture, also after an error
+      if (rc == QMK_OK && ce != cudaSuccess) { rc = QMK_ERR_CUDA; err = std::string("graph capture: ") + cudaGetErrorString(ce); }
+      if (rc == QMK_OK) {
+        ce = cudaGraphInstantiate(&w.step_graph, graph, 0);
+        if (ce != cudaSuccess) { rc = QMK_ERR_CUDA; err = std::string("cudaGraphInstantiate: ") + cudaGetErrorString(ce); }
+      }
+      if (graph) cudaGraphDestroy(graph);
+      if (rc == QMK_OK) memcpy(w.step_key, key, sizeof(key));
+    }
+    if (rc == QMK_OK) {
+      PF_CUDA(cudaEventRecord(w.ev_in, stream));          // the graph stream starts after the caller's stream
+      PF_CUDA(cudaStreamWaitEvent(w.gstream, w.ev_in, 0));
+      for (int step = 0; step < num_steps; ++step) PF_CUDA(cudaGraphLaunch(w.step_graph, w.gstream));
+      PF_CUDA(cudaEventRecord(w.ev_out, w.gstream));
+      PF_CUDA(cudaStreamWaitEvent(stream, w.ev_out, 0));  // ... and the caller's stream continues after it
+    }
   }
   if (rc != QMK_OK) return qmk_internal::report(rc, err);
   unsigned int host_status[4] = {0, 0, 0, 0};
