@@ -25,12 +25,16 @@
 namespace qmk_gemm {
 
 constexpr int BM = 128, BK = 64;                 // BK * 2 bytes = one 128-byte swizzle row; the N tile (128 or 64) is a template parameter
-constexpr int STAGES = 4;
+// Ring depth per N-tile variant: as many stages as fit in ~192 KB (a skinny M = 128 problem is bound by the
+// latency of its K loop, so the whole K extent of a 1024-wide matrix is in flight at once).
+constexpr int stages_for(int bn) { return bn == 64 ? 8 : 6; }
+constexpr int MAX_GROUPS = 3;   // matrices sharing one A operand that one launch can multiply (q/k/v, gate/up)
 constexpr int THREADS = 192;
 constexpr uint32_t TILE_A_BYTES = BM * BK * 2;   // 16 KB
-constexpr uint32_t TILE_B_MAX_BYTES = 128 * BK * 2;
-constexpr uint32_t STAGE_BYTES = TILE_A_BYTES + TILE_B_MAX_BYTES;   // the 64-wide variant uses half of the B part
-constexpr size_t SMEM_BYTES = 1024 /* alignment slack */ + static_cast<size_t>(STAGES) * STAGE_BYTES + 256;
+constexpr uint32_t stage_bytes_for(int bn) { return TILE_A_BYTES + static_cast<uint32_t>(bn) * BK * 2; }
+constexpr size_t smem_bytes_for(int bn) {
+  return 1024 /* alignment slack */ + static_cast<size_t>(stages_for(bn)) * stage_bytes_for(bn) + 256;
+}
 
 __device__ __forceinline__ uint32_t s32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ unsigned long long gtime() {
@@ -104,10 +108,27 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// Up to three B matrices (same K) against one A in one launch: blockIdx.x counts the N tiles of group 0, then of
+// group 1, then of group 2; C_g is [M x N_g].
+struct Groups {
+  float *C[MAX_GROUPS];
+  int N[MAX_GROUPS];
+};
+
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, float *C, int M,
-                   int N, int K, unsigned int *status, unsigned long long budget_ns) {
+gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
+                   const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_b2,
+                   const Groups groups, int M, int K, unsigned int *status, unsigned long long budget_ns) {
+  constexpr int STAGES = stages_for(BN);
+  constexpr uint32_t STAGE_BYTES = stage_bytes_for(BN);
+  // which matrix this CTA works on
+  int tile = blockIdx.x, grp = 0;
+  if (tile >= groups.N[0] / BN) { tile -= groups.N[0] / BN; grp = 1; }
+  if (grp == 1 && tile >= groups.N[1] / BN) { tile -= groups.N[1] / BN; grp = 2; }
+  const CUtensorMap *map_b = grp == 0 ? &map_b0 : grp == 1 ? &map_b1 : &map_b2;
+  float *C = grp == 0 ? groups.C[0] : grp == 1 ? groups.C[1] : groups.C[2];
+  const int N = grp == 0 ? groups.N[0] : grp == 1 ? groups.N[1] : groups.N[2];
   extern __shared__ unsigned char gemm_smem_raw[];
   const uint32_t raw = s32(gemm_smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;                 // swizzled tiles need 1024-byte alignment
@@ -116,7 +137,7 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(aligned + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 1));
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  const int n0 = tile * BN, m0 = blockIdx.y * BM;
   const int kblocks = K / BK;
   constexpr uint32_t TILE_B_BYTES = BN * BK * 2;
   constexpr uint32_t TMEM_COLS = BN;             // fp32 accumulator: 128 lanes x BN columns (a power of two >= 32)
@@ -149,7 +170,7 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         if (*abort_flag) break;
         bar_expect_tx(full(s), TILE_A_BYTES + TILE_B_BYTES);
         tma_load_2d(base + s * STAGE_BYTES, &map_a, kb * BK, m0, full(s));
-        tma_load_2d(base + s * STAGE_BYTES + TILE_A_BYTES, &map_b, kb * BK, n0, full(s));
+        tma_load_2d(base + s * STAGE_BYTES + TILE_A_BYTES, map_b, kb * BK, n0, full(s));
         issued = kb + 1;
       }
       // after an abort the copies already issued must land before the CTA can exit

@@ -257,9 +257,12 @@ __global__ void __launch_bounds__(256) decode_attention_seq(const float *qr, __h
     float sa = 0.f, sb = 0.f;
     if (key < nkeys) {
       const uint4 *krow = reinterpret_cast<const uint4 *>(kbase + static_cast<size_t>(key) * D);
-#pragma unroll 4
+      uint4 kreg[D / 8];
+#pragma unroll
+      for (int c = 0; c < D / 8; ++c) kreg[c] = __ldg(krow + c);   // the whole row in flight at once
+#pragma unroll
       for (int c = 0; c < D / 8; ++c) {
-        const uint4 kv = __ldg(krow + c);
+        const uint4 kv = kreg[c];
         const __half2 *h = reinterpret_cast<const __half2 *>(&kv);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -283,7 +286,7 @@ __global__ void __launch_bounds__(256) decode_attention_seq(const float *qr, __h
 #pragma unroll
     for (int d = 0; d < 4; ++d) { a0[d] *= ca; a1[d] *= cb; }
     const int nj = min(32, nkeys - k0);   // warp-uniform
-#pragma unroll 4
+#pragma unroll 8
     for (int j = 0; j < nj; ++j) {
       const float pja = __shfl_sync(0xffffffffu, pa, j), pjb = __shfl_sync(0xffffffffu, pb, j);
       const uint2 vv = __ldg(reinterpret_cast<const uint2 *>(vbase + static_cast<size_t>(k0 + j) * D + lane * 4));

@@ -78,35 +78,57 @@ int ensure_gemm_attrs(std::string *err) {
   std::lock_guard<std::mutex> lock(g_mu);
   if (dev >= 0 && dev < 16 && !g_attr_set[dev]) {
     cudaError_t e = cudaFuncSetAttribute(qmk_gemm::gemm_f16_tn_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(qmk_gemm::SMEM_BYTES));
+                                         static_cast<int>(qmk_gemm::smem_bytes_for(128)));
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(qmk_gemm::gemm_f16_tn_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(qmk_gemm::SMEM_BYTES));
+                               static_cast<int>(qmk_gemm::smem_bytes_for(64)));
     if (e != cudaSuccess) { *err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e); return QMK_ERR_CUDA; }
     g_attr_set[dev] = true;
   }
   return QMK_OK;
 }
 
-int launch_gemm(const CUtensorMap &map_a, const CUtensorMap &map_b, float *C, int M, int N, int K, int box_n,
-                unsigned int *status, int timeout_ms, cudaStream_t stream, std::string *err) {
-  if (M <= 0 || N <= 0 || K <= 0 || M % qmk_gemm::BM || N % 128 || K % qmk_gemm::BK || (box_n != 64 && box_n != 128)) {
+// C_g[M x N_g] fp32 = A[M x K] * B_g[N_g x K]^T for up to three matrices B_g in one launch.  M, N_g multiples of
+// 128; K a multiple of 64; every B map made with `box_n` rows per box (gemm_box_n(M, sum of N_g)).
+int launch_gemm_grouped(const CUtensorMap &map_a, int ngroups, const CUtensorMap *const *maps_b, float *const *Cs,
+                        const int *Ns, int M, int K, int box_n, unsigned int *status, int timeout_ms, cudaStream_t stream,
+                        std::string *err) {
+  bool bad = M <= 0 || K <= 0 || M % qmk_gemm::BM || K % qmk_gemm::BK || (box_n != 64 && box_n != 128) || ngroups < 1 ||
+             ngroups > qmk_gemm::MAX_GROUPS;
+  for (int g = 0; !bad && g < ngroups; ++g) bad = Ns[g] <= 0 || Ns[g] % 128;
+  if (bad) {
     *err = "gemm: M and N must be multiples of 128 and K a multiple of 64";
     return QMK_ERR_BAD_ARGUMENT;
   }
   const int arc = ensure_gemm_attrs(err);
   if (arc != QMK_OK) return arc;
-  dim3 grid(N / box_n, M / qmk_gemm::BM);
+  qmk_gemm::Groups gr;
+  int tiles = 0;
+  for (int g = 0; g < qmk_gemm::MAX_GROUPS; ++g) {
+    gr.C[g] = g < ngroups ? Cs[g] : nullptr;
+    gr.N[g] = g < ngroups ? Ns[g] : 0;
+    tiles += gr.N[g] / box_n;
+  }
+  const CUtensorMap &b0 = *maps_b[0], &b1 = *maps_b[ngroups > 1 ? 1 : 0], &b2 = *maps_b[ngroups > 2 ? 2 : 0];
+  dim3 grid(tiles, M / qmk_gemm::BM);
   const unsigned long long budget = static_cast<unsigned long long>(timeout_ms) * 1000000ull;
   if (box_n == 64)
-    qmk_gemm::gemm_f16_tn_kernel<64><<<grid, qmk_gemm::THREADS, qmk_gemm::SMEM_BYTES, stream>>>(map_a, map_b, C, M, N, K,
-                                                                                              status, budget);
+    qmk_gemm::gemm_f16_tn_kernel<64><<<grid, qmk_gemm::THREADS, qmk_gemm::smem_bytes_for(64), stream>>>(
+        map_a, b0, b1, b2, gr, M, K, status, budget);
   else
-    qmk_gemm::gemm_f16_tn_kernel<128><<<grid, qmk_gemm::THREADS, qmk_gemm::SMEM_BYTES, stream>>>(map_a, map_b, C, M, N, K,
-                                                                                               status, budget);
+    qmk_gemm::gemm_f16_tn_kernel<128><<<grid, qmk_gemm::THREADS, qmk_gemm::smem_bytes_for(128), stream>>>(
+        map_a, b0, b1, b2, gr, M, K, status, budget);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { *err = std::string("gemm launch: ") + cudaGetErrorString(e); return QMK_ERR_CUDA; }
   return QMK_OK;
+}
+
+int launch_gemm(const CUtensorMap &map_a, const CUtensorMap &map_b, float *C, int M, int N, int K, int box_n,
+                unsigned int *status, int timeout_ms, cudaStream_t stream, std::string *err) {
+  const CUtensorMap *maps[1] = {&map_b};
+  float *Cs[1] = {C};
+  const int Ns[1] = {N};
+  return launch_gemm_grouped(map_a, 1, maps, Cs, Ns, M, K, box_n, status, timeout_ms, stream, err);
 }
 
 }  // namespace qmk_tc
@@ -253,6 +275,16 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
     const int box_n = qmk_tc::gemm_box_n(M, N);
     return qmk_tc::launch_gemm(a, b[box_n == 128], c, M, N, K, box_n, w.status, env.timeout_ms, stream, &err);
   };
+  // several matrices against the same activations in one launch (q/k/v, gate/up)
+  auto gemm_group = [&](const CUtensorMap &a, int n, const CUtensorMap (*const *b)[2], float *const *cs, const int *ns,
+                        int M, int K) {
+    int total = 0;
+    for (int i = 0; i < n; ++i) total += ns[i];
+    const int box_n = qmk_tc::gemm_box_n(M, total);
+    const CUtensorMap *maps[3];
+    for (int i = 0; i < n; ++i) maps[i] = &(*b[i])[box_n == 128];
+    return qmk_tc::launch_gemm_grouped(a, n, maps, cs, ns, M, K, box_n, w.status, env.timeout_ms, stream, &err);
+  };
   for (int c0 = 0; c0 < num_tokens; c0 += CHUNK) {
     const int T = (num_tokens - c0 < CHUNK) ? num_tokens - c0 : CHUNK;
     const int M = (T + qmk_gemm::BM - 1) / qmk_gemm::BM * qmk_gemm::BM;
@@ -263,9 +295,12 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
       const unsigned long long *r = rec.data() + static_cast<size_t>(l) * 12;
       __half *kc = static_cast<__half *>(k_cache) + l * layer_stride, *vc = static_cast<__half *>(v_cache) + l * layer_stride;
       add_rmsnorm_rows<<<T, 256, 0, stream>>>(w.x, l > 0 ? w.down : nullptr, reinterpret_cast<const __half *>(r[0]), w.xn);
-      if ((rc = gemm(w.map_xn, w.wmap[l][0], w.q, M, QS, H)) != QMK_OK) break;
-      if ((rc = gemm(w.map_xn, w.wmap[l][1], w.k, M, KVS, H)) != QMK_OK) break;
-      if ((rc = gemm(w.map_xn, w.wmap[l][2], w.v, M, KVS, H)) != QMK_OK) break;
+      {
+        const CUtensorMap(*const b[3])[2] = {&w.wmap[l][0], &w.wmap[l][1], &w.wmap[l][2]};
+        float *const cs[3] = {w.q, w.k, w.v};
+        const int ns[3] = {QS, KVS, KVS};
+        if ((rc = gemm_group(w.map_xn, 3, b, cs, ns, M, H)) != QMK_OK) break;
+      }
       qk_norm_rope_cache<<<dim3(T, 4), 256, 0, stream>>>(w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]),
                                                          reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv, w.qr, kc, vc,
                                                          pos0, max_seq_len, nullptr, nullptr, nullptr, 0);
@@ -274,8 +309,12 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
                                                                               attn_scale);
       if ((rc = gemm(w.map_attn, w.wmap[l][3], w.o, M, H, QS)) != QMK_OK) break;
       add_rmsnorm_rows<<<T, 256, 0, stream>>>(w.x, w.o, reinterpret_cast<const __half *>(r[7]), w.xn);
-      if ((rc = gemm(w.map_xn, w.wmap[l][4], w.gate, M, I, H)) != QMK_OK) break;
-      if ((rc = gemm(w.map_xn, w.wmap[l][5], w.up, M, I, H)) != QMK_OK) break;
+      {
+        const CUtensorMap(*const b[2])[2] = {&w.wmap[l][4], &w.wmap[l][5]};
+        float *const cs[2] = {w.gate, w.up};
+        const int ns[2] = {I, I};
+        if ((rc = gemm_group(w.map_xn, 2, b, cs, ns, M, H)) != QMK_OK) break;
+      }
       silu_mul_rows<<<592, 256, 0, stream>>>(w.gate, w.up, w.act, static_cast<size_t>(T) * I);
       if ((rc = gemm(w.map_act, w.wmap[l][6], w.down, M, H, I)) != QMK_OK) break;
     }
@@ -398,15 +437,27 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
       const int box_n = qmk_tc::gemm_box_n(M, N);
       return qmk_tc::launch_gemm(a, bmap[box_n == 128], c, M, N, K, box_n, w.status, env.timeout_ms, s, &err);
     };
+    auto gemm_group = [&](const CUtensorMap &a, int n, const CUtensorMap (*const *b)[2], float *const *cs, const int *ns,
+                          int K) {
+      int total = 0;
+      for (int i = 0; i < n; ++i) total += ns[i];
+      const int box_n = qmk_tc::gemm_box_n(M, total);
+      const CUtensorMap *maps[3];
+      for (int i = 0; i < n; ++i) maps[i] = &(*b[i])[box_n == 128];
+      return qmk_tc::launch_gemm_grouped(a, n, maps, cs, ns, M, K, box_n, w.status, env.timeout_ms, s, &err);
+    };
     int r2 = QMK_OK;
     embed_rows<<<B, 256, 0, s>>>(w.tokens, static_cast<const __half *>(embed_weight), w.x);
     for (int l = 0; l < num_layers; ++l) {
       const unsigned long long *r = rec.data() + static_cast<size_t>(l) * 12;
       const size_t layer_off = l * layer_stride;
       add_rmsnorm_rows<<<B, 256, 0, s>>>(w.x, l > 0 ? w.down : nullptr, reinterpret_cast<const __half *>(r[0]), w.xn);
-      if ((r2 = gemm(w.map_xn, w.wmap[l][0], w.q, QS, H)) != QMK_OK) return r2;
-      if ((r2 = gemm(w.map_xn, w.wmap[l][1], w.k, KVS, H)) != QMK_OK) return r2;
-      if ((r2 = gemm(w.map_xn, w.wmap[l][2], w.v, KVS, H)) != QMK_OK) return r2;
+      {
+        const CUtensorMap(*const b[3])[2] = {&w.wmap[l][0], &w.wmap[l][1], &w.wmap[l][2]};
+        float *const cs[3] = {w.q, w.k, w.v};
+        const int ns[3] = {QS, KVS, KVS};
+        if ((r2 = gemm_group(w.map_xn, 3, b, cs, ns, H)) != QMK_OK) return r2;
+      }
       qk_norm_rope_cache<<<dim3(B, 4), 256, 0, s>>>(w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]),
                                                     reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv, w.qr, nullptr,
                                                     nullptr, 0, max_seq_len, w.positions, w.k_ptrs, w.v_ptrs, layer_off);
@@ -414,8 +465,12 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
                                                         max_seq_len, attn_scale);
       if ((r2 = gemm(w.map_attn, w.wmap[l][3], w.o, H, QS)) != QMK_OK) return r2;
       add_rmsnorm_rows<<<B, 256, 0, s>>>(w.x, w.o, reinterpret_cast<const __half *>(r[7]), w.xn);
-      if ((r2 = gemm(w.map_xn, w.wmap[l][4], w.gate, I, H)) != QMK_OK) return r2;
-      if ((r2 = gemm(w.map_xn, w.wmap[l][5], w.up, I, H)) != QMK_OK) return r2;
+      {
+        const CUtensorMap(*const b[2])[2] = {&w.wmap[l][4], &w.wmap[l][5]};
+        float *const cs[2] = {w.gate, w.up};
+        const int ns[2] = {I, I};
+        if ((r2 = gemm_group(w.map_xn, 2, b, cs, ns, H)) != QMK_OK) return r2;
+      }
       silu_mul_rows<<<(B * I + 255) / 256, 256, 0, s>>>(w.gate, w.up, w.act, static_cast<size_t>(B) * I);
       if ((r2 = gemm(w.map_act, w.wmap[l][6], w.down, H, I)) != QMK_OK) return r2;
     }
