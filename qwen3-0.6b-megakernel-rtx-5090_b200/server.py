@@ -72,8 +72,9 @@ def build_prompt(tokenizer, messages: List[Message]) -> str:
 
 
 def _load_decoder(model_name: str):
-    """``BATCH_SLOTS`` > 1 (up to 4) loads the multi-sequence engine: requests are then served
-    concurrently by the continuous-batching scheduler instead of one at a time."""
+    """``BATCH_SLOTS`` > 1 (up to 128; above 4 the tensor-core batched decode) loads the multi-sequence
+    engine: requests are then served concurrently by the continuous-batching scheduler, with tensor-core
+    prefill, instead of one at a time."""
     from Model.Qwen06B_architecture import BatchDecoder, Decoder, load_weights
     slots = int(os.getenv("BATCH_SLOTS", "1"))
     if os.getenv("SYNTHETIC", "0") == "1":
@@ -86,7 +87,7 @@ def _load_decoder(model_name: str):
     else:
         return Decoder(model_name=model_name, verbose=True)
     if slots > 1:
-        return BatchDecoder(weights=w, tokenizer=tok, num_sequences=slots, verbose=False)
+        return BatchDecoder(weights=w, tokenizer=tok, num_sequences=slots, verbose=False, prefill_mode="tensor")
     return Decoder(weights=w, tokenizer=tok, verbose=False)
 
 
