@@ -222,14 +222,22 @@ def run_ours(args):
     PROMPT_LEN, DECODE_TOKENS = args.prompt_len, args.decode_tokens   # defaults: the benchmark configuration
     MAX_SEQ_LEN = PROMPT_LEN + DECODE_TOKENS
     host_weights = S.make_weights(seed=0, max_seq_len=16)
-    if args.weights == "fp8":     # BASELINE.json configs[2] weight format at batch 1 (not the headline line)
+    expanded = False              # quantised weights stored as fp16 (engines without a packed path)
+    if args.weights != "fp16" and args.batch > 4:
+        import quantize
+        host_weights, _ = (quantize.expand_weights_fp8 if args.weights == "fp8" else quantize.expand_weights_nvfp4)(host_weights)
+        expanded = True
+    elif args.weights == "nvfp4":
+        raise SystemExit("bench.py: --weights nvfp4 needs --batch > 4 (expanded to fp16 on the tensor-core path)")
+    elif args.weights == "fp8":   # BASELINE.json configs[2] weight format, packed rows (batch <= 4)
         import quantize
         host_weights, _ = quantize.quantize_weights_fp8(host_weights)
+    engine_format = "fp16" if expanded else args.weights
     weights = S.weights_to(host_weights, str(device))
     B = args.batch
     if B == 1:
         eng = Decoder(weights=weights, tokenizer=S.StubTokenizer(-1), verbose=False, max_seq_len=MAX_SEQ_LEN,
-                      device=str(device), weight_format=args.weights)
+                      device=str(device), weight_format=engine_format)
         prompt = S.make_prompt(PROMPT_LEN, seed=rank)   # each replica serves its own stream
         eng.reset()
         eng.prefill_ids(prompt[:-1])                    # untimed; fills 4095 cache rows
@@ -257,8 +265,8 @@ def run_ours(args):
         # B sequences per launch (multi-sequence kernel), every one at the benchmark context length
         from Model.Qwen06B_architecture import BatchDecoder
         eng = BatchDecoder(weights=weights, tokenizer=S.StubTokenizer(-1), num_sequences=B, max_seq_len=MAX_SEQ_LEN,
-                           device=str(device), weight_format=args.weights,
-                           prefill_mode="tensor" if (B > 4 and args.weights == "fp16") else "serial")
+                           device=str(device), weight_format=engine_format,
+                           prefill_mode="tensor" if B > 4 else "serial")
         prompts = [S.make_prompt(PROMPT_LEN, seed=rank * 16 + b) for b in range(B)]
         for b in range(B):
             eng._prefill_slot(b, prompts[b][:-1])       # untimed
@@ -323,7 +331,7 @@ def run_ours(args):
     avg_launch_s = statistics.mean(launch_ms) / 1e3
     # algorithmic bytes of a launch: weights once per step, KV of every sequence
     kv_only = step_bytes(PROMPT_LEN, DECODE_TOKENS, "fp16") - DECODE_TOKENS * S.weight_bytes_fp16()
-    launch_bytes = step_bytes(PROMPT_LEN, DECODE_TOKENS, args.weights) + (B - 1) * kv_only
+    launch_bytes = step_bytes(PROMPT_LEN, DECODE_TOKENS, "fp16" if expanded else args.weights) + (B - 1) * kv_only
     achieved = launch_bytes / avg_launch_s / 1e9
     traffic = None   # DRAM bytes per launch from the committed ncu capture, scaled by tokens per launch
     try:
@@ -338,9 +346,9 @@ def run_ours(args):
         line = {
             "metric": METRIC if B == 1 else f"batch-{B} decode tok/s (all sequences)", "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": 1e3 * total_s / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "fp16" if args.weights == "fp16" else "fp8-e4m3 weights, fp32 math",
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp16" if (args.weights == "fp16" or expanded) else "fp8-e4m3 weights, fp32 math",
             "data": "synthetic",
-            "config": {"weights": args.weights, "workload": WORKLOAD if (PROMPT_LEN, DECODE_TOKENS) == (4096, 256) else
+            "config": {"weights": args.weights + (" (quantised values, stored expanded as fp16)" if expanded else ""), "workload": WORKLOAD if (PROMPT_LEN, DECODE_TOKENS) == (4096, 256) else
                        f"profiling case: {PROMPT_LEN} prompt tokens, {DECODE_TOKENS} decode tokens per step",
                        "tokens_per_step": DECODE_TOKENS * B, "sequences_per_launch": B,
                        "engine": "persistent megakernel" if B <= 4 else "tcgen05 GEMM path", "replicas": world,
@@ -440,7 +448,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle leg (profiling runs)")
-    ap.add_argument("--weights", choices=["fp16", "fp8"], default="fp16",
+    ap.add_argument("--weights", choices=["fp16", "fp8", "nvfp4"], default="fp16",
                     help="weight format (default fp16 = the benchmark configuration)")
     ap.add_argument("--batch", type=int, default=1,
                     help="sequences per GPU decoded together (default 1: the headline batch-1 configuration; 2-4: one "

@@ -68,3 +68,84 @@ def weight_bytes_fp8(num_layers: int = 28, vocab_size: int = 151936) -> int:
     rows_k = [(2048, 1024), (1024, 1024), (1024, 1024), (1024, 2048), (3072, 1024), (3072, 1024), (1024, 3072)]
     per_layer = sum(r * (k + TRAILER) for r, k in rows_k) + (1024 + 1024 + 128 + 128) * 2
     return num_layers * per_layer + vocab_size * (1024 + TRAILER) + 1024 * 2 + (1024 + TRAILER)
+
+
+# ----------------------------------------------------------------------------- NVFP4 (e2m1 values, block-16 scales)
+E2M1_GRID = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+E2M1_MAX = 6.0
+NVFP4_BLOCK = 16
+
+
+def round_to_e2m1(x: torch.Tensor) -> torch.Tensor:
+    """Nearest e2m1 value (sign-magnitude, magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6); ties go to the even code."""
+    grid = torch.tensor(E2M1_GRID, dtype=torch.float32, device=x.device)
+    mag = x.abs().clamp(max=E2M1_MAX)
+    dist = (mag[..., None] - grid).abs()
+    # among equally near grid points prefer the even index: subtract a tiny bonus from even codes' distance
+    bonus = torch.tensor([1e-7 if i % 2 == 0 else 0.0 for i in range(8)], dtype=torch.float32, device=x.device)
+    idx = (dist - bonus).argmin(dim=-1)
+    return torch.sign(x) * grid[idx]
+
+
+def quantize_blocks_nvfp4(w: torch.Tensor):
+    """fp16/fp32 matrix ``[out, in]`` (``in`` a multiple of 16) -> (e2m1 values as fp32 ``[out, in]``,
+    e4m3 block scales ``[out, in / 16]``, fp32 tensor scale).  ``w ~= tensor_scale * block_scale * value``:
+    the tensor scale maps the largest block maximum onto the e4m3 range, each block scale maps its block's
+    maximum onto 6 (the e2m1 maximum)."""
+    wf = w.detach().to(torch.float32)
+    rows, k = wf.shape
+    assert k % NVFP4_BLOCK == 0
+    blocks = wf.view(rows, k // NVFP4_BLOCK, NVFP4_BLOCK)
+    amax = blocks.abs().amax(dim=2)
+    tensor_scale = float(amax.max()) / (E2M1_MAX * E4M3_MAX)
+    if tensor_scale == 0.0:
+        tensor_scale = 1.0
+    sb = (amax / E2M1_MAX / tensor_scale).to(torch.float8_e4m3fn)
+    sbf = sb.to(torch.float32)
+    denom = torch.where(sbf > 0, sbf * tensor_scale, torch.ones_like(sbf))
+    vals = round_to_e2m1(blocks / denom[..., None])
+    vals = torch.where(sbf[..., None] > 0, vals, torch.zeros_like(vals))
+    return vals.view(rows, k), sb, tensor_scale
+
+
+def dequantize_nvfp4(vals: torch.Tensor, block_scales: torch.Tensor, tensor_scale: float) -> torch.Tensor:
+    rows, k = vals.shape
+    sbf = block_scales.to(torch.float32)
+    return (vals.view(rows, k // NVFP4_BLOCK, NVFP4_BLOCK) * (sbf * tensor_scale)[..., None]).view(rows, k)
+
+
+def _quantised_dicts(weights: dict, requant):
+    """(fp16 dict holding the dequantised matrices, fp32 oracle dict) with the embedding tie kept."""
+    deq_embed = requant(weights["embed_weight"])
+    e_layers, o_layers = [], []
+    for t in weights["layer_weights"]:
+        if t.dim() == 2:
+            d = requant(t)
+            e_layers.append(d.to(torch.float16))
+            o_layers.append(d)
+        else:
+            e_layers.append(t)
+            o_layers.append(t)
+    common = dict(final_norm_weight=weights["final_norm_weight"], cos_table=weights["cos_table"],
+                  sin_table=weights["sin_table"])
+    e16 = deq_embed.to(torch.float16)
+    return (dict(embed_weight=e16, lm_head_weight=e16, layer_weights=e_layers, **common),
+            dict(embed_weight=deq_embed, lm_head_weight=deq_embed, layer_weights=o_layers, **common))
+
+
+def expand_weights_fp8(weights: dict):
+    """FP8-E4M3 row-quantised weights EXPANDED to fp16 for engines without a packed-fp8 path (the tensor-core
+    batched decode): same quantisation as ``quantize_weights_fp8``, stored as fp16(q * scale).  Keeps the
+    numerics of the quantised model, not its memory footprint.  Returns (engine dict, oracle dict)."""
+    return _quantised_dicts(weights, lambda w: dequantize_rows_fp8(*quantize_rows_fp8(w)))
+
+
+def expand_weights_nvfp4(weights: dict):
+    """NVFP4 (e2m1 + e4m3 block-16 scales + fp32 tensor scale) quantised weights expanded to fp16, as above."""
+    return _quantised_dicts(weights, lambda w: dequantize_nvfp4(*quantize_blocks_nvfp4(w)))
+
+
+def weight_bytes_nvfp4(num_layers: int = 28, vocab_size: int = 151936) -> int:
+    """Bytes a packed NVFP4 model streams per decode step: 4-bit values + one e4m3 scale per 16 (norms fp16)."""
+    elems = num_layers * 15_728_640 + vocab_size * 1024
+    return elems // 2 + elems // 16 + num_layers * 2304 * 2 + 1024 * 2 + 4 * (7 * num_layers + 1)

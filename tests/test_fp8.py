@@ -127,3 +127,61 @@ def test_fp8_four_sequences_per_launch(built_library):
         print(f"fp8 batch 4, sequence {b}: max |logit - oracle(fp8 weights)| = {err:.3e}")
         assert got[b] == want
         assert err < 3e-2
+
+
+def test_nvfp4_quantiser_scheme():
+    g = torch.Generator("cpu").manual_seed(1)
+    w = (torch.randn(5, 64, generator=g) * 0.02).to(torch.float16)
+    w[2] = 0
+    vals, sb, st = Q.quantize_blocks_nvfp4(w)
+    assert sb.dtype == torch.float8_e4m3fn and sb.shape == (5, 4) and st > 0
+    assert set(vals.abs().unique().tolist()) <= set(Q.E2M1_GRID)
+    deq = Q.dequantize_nvfp4(vals, sb, st)
+    assert deq[2].abs().max() == 0
+    # e2m1 spacing is at most 2 on a scale of 6: error <= 1/6 of the block maximum (+ the e4m3 scale rounding)
+    blocks = w.float().view(5, 4, 16)
+    bound = blocks.abs().amax(dim=2, keepdim=True) * (1 / 6 + 1 / 8)
+    assert ((deq.view(5, 4, 16) - blocks).abs() <= bound + 1e-9).all()
+    # ties go to the even code: 0.25 -> 0, 0.75 -> 1, 2.5 -> 2, 5 -> 4
+    assert Q.round_to_e2m1(torch.tensor([0.25, 0.75, 2.5, 5.0, -1.25, 7.0])).tolist() == [0.0, 1.0, 2.0, 4.0, -1.0, 6.0]
+    assert 0.33e9 < Q.weight_bytes_nvfp4() < 0.34e9
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt,n", [("fp8", 16), ("nvfp4", 64)])
+def test_quantised_models_on_the_batched_tensor_core_path(built_library, fmt, n):
+    """The B = 16 FP8 and B = 64 NVFP4 configurations' shapes with the quantised weights expanded to fp16:
+    every sequence against the oracle on the same dequantised weights (logits within 3e-2; tokens equal
+    wherever the oracle's greedy margin exceeds twice the logit error)."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import qwen_megakernel_C as C
+    from Model.Qwen06B_architecture import BatchDecoder
+    vocab, steps, L = 2048, 4, 192
+    w = S.make_weights(seed=31, num_layers=2, vocab_size=vocab, norm_std=0.1, max_seq_len=16)
+    eng_w, ora_w = (Q.expand_weights_fp8 if fmt == "fp8" else Q.expand_weights_nvfp4)(w)
+    lens = [1 + (17 * i) % 150 for i in range(n)]
+    prompts = [S.make_prompt(Ln, seed=600 + i, vocab_size=vocab) for i, Ln in enumerate(lens)]
+    eng = BatchDecoder(weights=S.weights_to(eng_w, "cuda"), tokenizer=S.StubTokenizer(-1, vocab), num_sequences=n,
+                       max_seq_len=L, engine="gemm", prefill_mode="tensor")
+    dump = torch.zeros(n, steps, vocab, device="cuda")
+    C.set_logits_dump(dump)
+    try:
+        got = eng.generate_ids(prompts, steps)
+    finally:
+        C.set_logits_dump(None)
+    dump = dump.cpu()
+    worst, equal = 0.0, 0
+    for b in range(n):
+        want, logits = OracleDecoder(ora_w, max_seq_len=L).generate_ids(prompts[b], steps, keep_logits=True)
+        for s in range(steps):
+            err = float((dump[b, s] - logits[s]).abs().max())
+            worst = max(worst, err)
+            assert err < 3e-2
+            if got[b][s] != want[s]:
+                top2 = logits[s].topk(2).values
+                assert float(top2[0] - top2[1]) < 2 * err + 1e-6
+                break
+            equal += 1
+    print(f"{fmt} expanded, {n} sequences: worst max |logit - oracle| = {worst:.3e}; {equal}/{n * steps} steps token-equal")
+    assert equal >= n * steps - 4
