@@ -231,6 +231,162 @@ __global__ void __launch_bounds__(256) causal_attention(const float *qr, const _
   }
 }
 
+// Tensor-core version of causal_attention (mma.sync m16n8k16, fp16 operands, fp32 accumulate and softmax).
+// grid = (ceil(T / 32), 8 kv heads), block = 128 = 4 warps.  A CTA takes 32 query tokens x the two query heads
+// of its kv head; warp w works on head (w & 1) and tokens t0 + 16 * (w >> 1) + 0..15 (one 16-row MMA tile).
+// Keys go through shared memory in tiles of 64 rows of K and of V (row pitch 272 bytes: conflict-free for the
+// 32-bit B-fragment loads of K and for ldmatrix.trans on V).  Per key tile and warp: S = Q K^T (64 MMAs),
+// online softmax on the accumulator fragments, P (as fp16 A fragments, straight from the S registers) times V
+// (64 MMAs).  q is scaled by scale * log2(e) before it is rounded to fp16, so the softmax runs on exp2.
+constexpr int ATM_Q = 32, ATM_KEYS = 64, ATM_PITCH = D + 8;   // halves per K / V row in shared memory
+
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(128) causal_attention_mma(const float *qr, const __half *k_cache_layer,
+                                                            const __half *v_cache_layer, __half *out, int T, int pos0,
+                                                            int max_seq_len, float scale) {
+  __shared__ __align__(16) __half sk[ATM_KEYS * ATM_PITCH];
+  __shared__ __align__(16) __half sv[ATM_KEYS * ATM_PITCH];
+  const int g = blockIdx.y, t0 = (gridDim.x - 1 - blockIdx.x) * ATM_Q;   // longest tiles first
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = warp & 1, tw = t0 + 16 * (warp >> 1);     // this warp's head and first token
+  const int gr = lane >> 2, qd = lane & 3;                // fragment row within 8, quad lane
+  const int tok_lo = tw + gr, tok_hi = tw + gr + 8;       // the two query rows this lane holds
+  const float sc = scale * 1.4426950408889634f;
+
+  // Q fragments (A operand), 8 k-steps of 16 dims
+  uint32_t qa[8][4];
+  {
+    const float *q_lo = qr + (static_cast<size_t>(min(tok_lo, T - 1)) * NQ + 2 * g + h) * D;
+    const float *q_hi = qr + (static_cast<size_t>(min(tok_hi, T - 1)) * NQ + 2 * g + h) * D;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const int d = ks * 16 + qd * 2;
+      const float2 l0 = *reinterpret_cast<const float2 *>(q_lo + d), l1 = *reinterpret_cast<const float2 *>(q_lo + d + 8);
+      const float2 h0 = *reinterpret_cast<const float2 *>(q_hi + d), h1 = *reinterpret_cast<const float2 *>(q_hi + d + 8);
+      qa[ks][0] = pack_half2(l0.x * sc, l0.y * sc);
+      qa[ks][1] = pack_half2(h0.x * sc, h0.y * sc);
+      qa[ks][2] = pack_half2(l1.x * sc, l1.y * sc);
+      qa[ks][3] = pack_half2(h1.x * sc, h1.y * sc);
+    }
+  }
+  float o[16][4];
+#pragma unroll
+  for (int dt = 0; dt < 16; ++dt) { o[dt][0] = 0.f; o[dt][1] = 0.f; o[dt][2] = 0.f; o[dt][3] = 0.f; }
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+  // rows beyond the chunk see no key at all
+  const int lim_lo = tok_lo < T ? pos0 + tok_lo : -1, lim_hi = tok_hi < T ? pos0 + tok_hi : -1;
+  const int warp_last = pos0 + min(tw + 15, T - 1);                   // highest key this warp needs (tw < T or unused)
+  const int cta_last = pos0 + min(t0 + ATM_Q - 1, T - 1);
+  const __half *kbase = k_cache_layer + static_cast<size_t>(g) * max_seq_len * D;
+  const __half *vbase = v_cache_layer + static_cast<size_t>(g) * max_seq_len * D;
+
+  for (int k0 = 0; k0 <= cta_last; k0 += ATM_KEYS) {
+    __syncthreads();   // the previous tile is fully used
+    for (int i = threadIdx.x; i < ATM_KEYS * (D / 8); i += 128) {
+      const int j = i >> 4, c = i & 15;
+      uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+      if (k0 + j <= cta_last) {
+        kv = *reinterpret_cast<const uint4 *>(kbase + static_cast<size_t>(k0 + j) * D + c * 8);
+        vv = *reinterpret_cast<const uint4 *>(vbase + static_cast<size_t>(k0 + j) * D + c * 8);
+      }
+      *reinterpret_cast<uint4 *>(sk + j * ATM_PITCH + c * 8) = kv;
+      *reinterpret_cast<uint4 *>(sv + j * ATM_PITCH + c * 8) = vv;
+    }
+    __syncthreads();
+    if (tw >= T || k0 > warp_last) continue;   // warp-uniform: nothing (more) to do for this warp in this tile
+
+    // S = Q K^T for 64 keys: 8 n-tiles of 8 keys
+    float sacc[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      sacc[nt][0] = 0.f; sacc[nt][1] = 0.f; sacc[nt][2] = 0.f; sacc[nt][3] = 0.f;
+      const __half *krow = sk + (nt * 8 + gr) * ATM_PITCH + qd * 2;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t *>(krow + ks * 16);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t *>(krow + ks * 16 + 8);
+        mma_16816(sacc[nt], qa[ks], b0, b1);
+      }
+    }
+    // causal mask + row maxima (a row lives in the 4 lanes of a quad)
+    float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      const int key = k0 + nt * 8 + qd * 2;
+      if (key > lim_lo) sacc[nt][0] = -INFINITY;
+      if (key + 1 > lim_lo) sacc[nt][1] = -INFINITY;
+      if (key > lim_hi) sacc[nt][2] = -INFINITY;
+      if (key + 1 > lim_hi) sacc[nt][3] = -INFINITY;
+      mx_lo = fmaxf(mx_lo, fmaxf(sacc[nt][0], sacc[nt][1]));
+      mx_hi = fmaxf(mx_hi, fmaxf(sacc[nt][2], sacc[nt][3]));
+    }
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+    const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+    const float ref_lo = (mn_lo == -INFINITY) ? 0.f : mn_lo, ref_hi = (mn_hi == -INFINITY) ? 0.f : mn_hi;   // fully masked rows
+    const float c_lo = exp2f(m_lo - ref_lo), c_hi = exp2f(m_hi - ref_hi);
+    m_lo = mn_lo; m_hi = mn_hi;
+    float sum_lo = 0.f, sum_hi = 0.f;
+    uint32_t pa[4][4];   // P as A fragments: 4 key-steps of 16 keys
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      const float p0 = exp2f(sacc[nt][0] - ref_lo), p1 = exp2f(sacc[nt][1] - ref_lo);
+      const float p2 = exp2f(sacc[nt][2] - ref_hi), p3 = exp2f(sacc[nt][3] - ref_hi);
+      sum_lo += p0 + p1;
+      sum_hi += p2 + p3;
+      pa[nt >> 1][(nt & 1) * 2 + 0] = pack_half2(p0, p1);
+      pa[nt >> 1][(nt & 1) * 2 + 1] = pack_half2(p2, p3);
+    }
+    sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 1);
+    sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 2);
+    sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 1);
+    sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 2);
+    l_lo = l_lo * c_lo + sum_lo;
+    l_hi = l_hi * c_hi + sum_hi;
+#pragma unroll
+    for (int dt = 0; dt < 16; ++dt) { o[dt][0] *= c_lo; o[dt][1] *= c_lo; o[dt][2] *= c_hi; o[dt][3] *= c_hi; }
+    // O += P V: B fragments of V through ldmatrix.trans (4 8x8 matrices: keys 0-7 / 8-15 of the step x two dim tiles)
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      const int mi = lane >> 3;
+      const __half *vrow = sv + (kk * 16 + (mi & 1) * 8 + (lane & 7)) * ATM_PITCH + (mi >> 1) * 8;
+#pragma unroll
+      for (int dp = 0; dp < 8; ++dp) {
+        uint32_t b0, b1, b2, b3;
+        const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(vrow + dp * 16));
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                     : "r"(addr));
+        mma_16816(o[2 * dp], pa[kk], b0, b1);
+        mma_16816(o[2 * dp + 1], pa[kk], b2, b3);
+      }
+    }
+  }
+  if (tw < T) {
+    const float inv_lo = l_lo > 0.f ? 1.0f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.0f / l_hi : 0.f;
+#pragma unroll
+    for (int dt = 0; dt < 16; ++dt) {
+      const int d = (2 * g + h) * D + dt * 8 + qd * 2;
+      if (tok_lo < T)
+        *reinterpret_cast<__half2 *>(out + static_cast<size_t>(tok_lo) * QS + d) = __floats2half2_rn(o[dt][0] * inv_lo, o[dt][1] * inv_lo);
+      if (tok_hi < T)
+        *reinterpret_cast<__half2 *>(out + static_cast<size_t>(tok_hi) * QS + d) = __floats2half2_rn(o[dt][2] * inv_hi, o[dt][3] * inv_hi);
+    }
+  }
+}
+
 // Decode-step attention for a batch of sequences: sequence b's single query token over its own cache rows
 // [0, positions[b]] (the new row is already in the cache).  grid = (B, 8 kv heads), block = 256 = 8 warps.
 // Warps take 32-key tiles round-robin straight from global memory: lane j scores key j for both query heads of

@@ -305,8 +305,8 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
                                                          reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv, w.qr, kc, vc,
                                                          pos0, max_seq_len, nullptr, nullptr, nullptr, 0);
       if (l == num_layers - 1) break;   // the cache is complete; nothing downstream of the last layer is kept
-      causal_attention<<<dim3((T + ATT_Q - 1) / ATT_Q, NKV), 256, 0, stream>>>(w.qr, kc, vc, w.attn, T, pos0, max_seq_len,
-                                                                              attn_scale);
+      causal_attention_mma<<<dim3((T + ATM_Q - 1) / ATM_Q, NKV), 128, 0, stream>>>(w.qr, kc, vc, w.attn, T, pos0,
+                                                                                  max_seq_len, attn_scale);
       if ((rc = gemm(w.map_attn, w.wmap[l][3], w.o, M, H, QS)) != QMK_OK) break;
       add_rmsnorm_rows<<<T, 256, 0, stream>>>(w.x, w.o, reinterpret_cast<const __half *>(r[7]), w.xn);
       {
