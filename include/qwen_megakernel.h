@@ -264,6 +264,10 @@ long long qmk_scratch_bytes(void);
  * microseconds; returns QMK_ERR_WAIT_TIMEOUT when the wait gave up as designed. */
 int qmk_selftest_wait_timeout(int budget_us);
 
+/* The same for the tcgen05 GEMM: one tile whose loads are never issued; the MMA thread's wait runs out after
+ * budget_us, all roles leave, TMEM is freed; returns QMK_ERR_WAIT_TIMEOUT when that happened as designed. */
+int qmk_selftest_gemm_wait_timeout(int budget_us);
+
 #ifdef __cplusplus
 }
 #endif

@@ -115,17 +115,23 @@ struct Groups {
   int N[MAX_GROUPS];
 };
 
-template <int BN>
+// FUSE (BN = 64 only): B0 is the gate matrix and B1 the up matrix of a SwiGLU MLP; the CTA keeps two accumulators
+// (gate tile in TMEM columns [0, 64), up tile in [64, 128)) and its epilogue writes fp16 silu(gate) * up to
+// groups.C[0] (reinterpreted as __half [M x N]) instead of two fp32 matrices.
+template <int BN, bool FUSE = false>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
                    const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_b2,
-                   const Groups groups, int M, int K, unsigned int *status, unsigned long long budget_ns) {
-  constexpr int STAGES = stages_for(BN);
-  constexpr uint32_t STAGE_BYTES = stage_bytes_for(BN);
+                   const Groups groups, int M, int K, unsigned int *status, unsigned long long budget_ns,
+                   int selftest_no_loads) {
+  static_assert(!FUSE || BN == 64, "the fused SwiGLU epilogue is written for 64-wide tiles");
+  constexpr int SB = FUSE ? 2 * BN : BN;          // B rows held per stage / accumulator columns
+  constexpr int STAGES = stages_for(SB);
+  constexpr uint32_t STAGE_BYTES = stage_bytes_for(SB);
   // which matrix this CTA works on
   int tile = blockIdx.x, grp = 0;
-  if (tile >= groups.N[0] / BN) { tile -= groups.N[0] / BN; grp = 1; }
-  if (grp == 1 && tile >= groups.N[1] / BN) { tile -= groups.N[1] / BN; grp = 2; }
+  if (!FUSE && tile >= groups.N[0] / BN) { tile -= groups.N[0] / BN; grp = 1; }
+  if (!FUSE && grp == 1 && tile >= groups.N[1] / BN) { tile -= groups.N[1] / BN; grp = 2; }
   const CUtensorMap *map_b = grp == 0 ? &map_b0 : grp == 1 ? &map_b1 : &map_b2;
   float *C = grp == 0 ? groups.C[0] : grp == 1 ? groups.C[1] : groups.C[2];
   const int N = grp == 0 ? groups.N[0] : grp == 1 ? groups.N[1] : groups.N[2];
@@ -140,7 +146,7 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   const int n0 = tile * BN, m0 = blockIdx.y * BM;
   const int kblocks = K / BK;
   constexpr uint32_t TILE_B_BYTES = BN * BK * 2;
-  constexpr uint32_t TMEM_COLS = BN;             // fp32 accumulator: 128 lanes x BN columns (a power of two >= 32)
+  constexpr uint32_t TMEM_COLS = SB;             // fp32 accumulator(s): 128 lanes x SB columns (a power of two >= 32)
   auto full = [&](int s) { return bars + 8u * s; };
   auto empty = [&](int s) { return bars + 8u * (STAGES + s); };
   const uint32_t acc_full = bars + 8u * (2 * STAGES);
@@ -164,13 +170,15 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   if (warp == 0) {
     if (lane == 0) {                       // ---- producer
       int issued = 0;
-      for (int kb = 0; kb < kblocks; ++kb) {
+      // self test of the bounded waits: the loads are never issued, so the MMA thread's first wait runs out
+      for (int kb = 0; kb < (selftest_no_loads ? 0 : kblocks); ++kb) {
         const int s = kb % STAGES;
         if (kb >= STAGES && !bar_wait(empty(s), ((kb / STAGES) - 1) & 1, abort_flag, status, budget_ns)) break;
         if (*abort_flag) break;
-        bar_expect_tx(full(s), TILE_A_BYTES + TILE_B_BYTES);
+        bar_expect_tx(full(s), TILE_A_BYTES + (FUSE ? 2 : 1) * TILE_B_BYTES);
         tma_load_2d(base + s * STAGE_BYTES, &map_a, kb * BK, m0, full(s));
         tma_load_2d(base + s * STAGE_BYTES + TILE_A_BYTES, map_b, kb * BK, n0, full(s));
+        if (FUSE) tma_load_2d(base + s * STAGE_BYTES + TILE_A_BYTES + TILE_B_BYTES, &map_b1, kb * BK, n0, full(s));
         issued = kb + 1;
       }
       // after an abort the copies already issued must land before the CTA can exit
@@ -178,7 +186,7 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         for (int kb = (issued > STAGES ? issued - STAGES : 0); kb < issued; ++kb) {
           const unsigned long long t0 = gtime();
           while (!bar_try(full(kb % STAGES), (kb / STAGES) & 1)) {
-            if (gtime() - t0 > budget_ns) break;
+            if (gtime() - t0 > (budget_ns > 2000000ull ? budget_ns : 2000000ull)) break;   // landing takes microseconds
           }
         }
       }
@@ -194,8 +202,12 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         const uint64_t da = smem_desc_sw128(base + s * STAGE_BYTES);
         const uint64_t db = smem_desc_sw128(base + s * STAGE_BYTES + TILE_A_BYTES);
 #pragma unroll
-        for (int j = 0; j < BK / 16; ++j)   // 16 halves = 32 bytes = 2 descriptor address units per K step
+        for (int j = 0; j < BK / 16; ++j) {  // 16 halves = 32 bytes = 2 descriptor address units per K step
           mma_f16_ss(tmem_base, da + 2u * j, db + 2u * j, (kb > 0 || j > 0) ? 1u : 0u, idesc_for(BN));
+          if (FUSE)                          // the up tile sits TILE_B_BYTES (>> 4 in descriptor units) behind the gate tile
+            mma_f16_ss(tmem_base + BN, da + 2u * j, db + (TILE_B_BYTES >> 4) + 2u * j, (kb > 0 || j > 0) ? 1u : 0u,
+                       idesc_for(BN));
+        }
         mma_commit(empty(s));               // the stage is free once these MMAs have read it
       }
       if (ok) mma_commit(acc_full);         // accumulator complete
@@ -205,7 +217,42 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     // warp-uniform outcome: the TMEM loads below are warp-wide instructions
     const bool ok = __all_sync(0xffffffffu, bar_wait(acc_full, 0, abort_flag, status, budget_ns));
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
+    if (ok && FUSE) {
+      const int row = m0 + quarter * 32 + lane;
+      __half *arow = reinterpret_cast<__half *>(C) + static_cast<size_t>(row) * N + n0;
+#pragma unroll 1
+      for (int c = 0; c < BN / 16; ++c) {     // 16 columns of the gate tile and the same 16 of the up tile per pass
+        uint32_t g[16], u[16];
+        const uint32_t tg = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(c * 16);
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+            : "=r"(g[0]), "=r"(g[1]), "=r"(g[2]), "=r"(g[3]), "=r"(g[4]), "=r"(g[5]), "=r"(g[6]), "=r"(g[7]), "=r"(g[8]),
+              "=r"(g[9]), "=r"(g[10]), "=r"(g[11]), "=r"(g[12]), "=r"(g[13]), "=r"(g[14]), "=r"(g[15])
+            : "r"(tg)
+            : "memory");
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+            : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]),
+              "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
+            : "r"(tg + BN)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row < M) {
+          uint32_t packed[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float g0 = __uint_as_float(g[2 * i]), g1 = __uint_as_float(g[2 * i + 1]);
+            const __half2 h = __floats2half2_rn(g0 / (1.0f + expf(-g0)) * __uint_as_float(u[2 * i]),
+                                                g1 / (1.0f + expf(-g1)) * __uint_as_float(u[2 * i + 1]));
+            packed[i] = *reinterpret_cast<const uint32_t *>(&h);
+          }
+          *reinterpret_cast<uint4 *>(arow + c * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          *reinterpret_cast<uint4 *>(arow + c * 16 + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        }
+      }
+    } else if (ok) {
       const int row = m0 + quarter * 32 + lane;
       float *crow = C + static_cast<size_t>(row) * N + n0;
 #pragma unroll 1

@@ -516,14 +516,5 @@ __global__ void __launch_bounds__(1024) argmax_rows(const float *logits, int voc
   }
 }
 
-// act[t][m] = fp16(silu(gate[t][m]) * up[t][m]) in fp32 math.  grid-stride over T * I elements.
-__global__ void silu_mul_rows(const float *gate, const float *up, __half *act, size_t n) {
-  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
-       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const float g = gate[i];
-    act[i] = __float2half_rn(g / (1.0f + expf(-g)) * up[i]);
-  }
-}
-
 }  // namespace qmk_pf
 #endif  // QMK_PREFILL_KERNELS_CUH_

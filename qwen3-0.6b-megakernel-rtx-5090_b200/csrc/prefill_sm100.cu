@@ -82,6 +82,9 @@ int ensure_gemm_attrs(std::string *err) {
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(qmk_gemm::gemm_f16_tn_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(qmk_gemm::smem_bytes_for(64)));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(qmk_gemm::gemm_f16_tn_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(qmk_gemm::smem_bytes_for(128)));
     if (e != cudaSuccess) { *err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e); return QMK_ERR_CUDA; }
     g_attr_set[dev] = true;
   }
@@ -114,10 +117,31 @@ int launch_gemm_grouped(const CUtensorMap &map_a, int ngroups, const CUtensorMap
   const unsigned long long budget = static_cast<unsigned long long>(timeout_ms) * 1000000ull;
   if (box_n == 64)
     qmk_gemm::gemm_f16_tn_kernel<64><<<grid, qmk_gemm::THREADS, qmk_gemm::smem_bytes_for(64), stream>>>(
-        map_a, b0, b1, b2, gr, M, K, status, budget);
+        map_a, b0, b1, b2, gr, M, K, status, budget, 0);
   else
     qmk_gemm::gemm_f16_tn_kernel<128><<<grid, qmk_gemm::THREADS, qmk_gemm::smem_bytes_for(128), stream>>>(
-        map_a, b0, b1, b2, gr, M, K, status, budget);
+        map_a, b0, b1, b2, gr, M, K, status, budget, 0);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { *err = std::string("gemm launch: ") + cudaGetErrorString(e); return QMK_ERR_CUDA; }
+  return QMK_OK;
+}
+
+// act[M x N] fp16 = silu(A * Gate^T) * (A * Up^T): the gate/up pair of the MLP with the SwiGLU in the epilogue.
+// Both maps made with 64 rows per box.
+int launch_gemm_swiglu(const CUtensorMap &map_a, const CUtensorMap &map_gate, const CUtensorMap &map_up, __half *act, int M,
+                       int N, int K, unsigned int *status, int timeout_ms, cudaStream_t stream, std::string *err) {
+  if (M <= 0 || N <= 0 || K <= 0 || M % qmk_gemm::BM || N % 128 || K % qmk_gemm::BK) {
+    *err = "gemm: M and N must be multiples of 128 and K a multiple of 64";
+    return QMK_ERR_BAD_ARGUMENT;
+  }
+  const int arc = ensure_gemm_attrs(err);
+  if (arc != QMK_OK) return arc;
+  qmk_gemm::Groups gr;
+  gr.C[0] = reinterpret_cast<float *>(act); gr.C[1] = nullptr; gr.C[2] = nullptr;
+  gr.N[0] = N; gr.N[1] = 0; gr.N[2] = 0;
+  qmk_gemm::gemm_f16_tn_kernel<64, true><<<dim3(N / 64, M / qmk_gemm::BM), qmk_gemm::THREADS, qmk_gemm::smem_bytes_for(128),
+                                           stream>>>(map_a, map_gate, map_up, map_up, gr, M, K, status,
+                                                     static_cast<unsigned long long>(timeout_ms) * 1000000ull, 0);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { *err = std::string("gemm launch: ") + cudaGetErrorString(e); return QMK_ERR_CUDA; }
   return QMK_OK;
@@ -142,8 +166,7 @@ constexpr int MAX_LAYERS = 48;
 struct Workspace {                  // per device, allocated on first use, never freed (like the engine's scratch)
   bool ready = false;
   int *tokens = nullptr;
-  float *x = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *qr = nullptr, *o = nullptr, *gate = nullptr,
-        *up = nullptr, *down = nullptr;
+  float *x = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *qr = nullptr, *o = nullptr, *down = nullptr;
   __half *xn = nullptr, *attn = nullptr, *act = nullptr;
   unsigned int *status = nullptr;
   CUtensorMap map_xn, map_attn, map_act;
@@ -185,8 +208,6 @@ int ensure_workspace(Workspace &w) {
   PF_CUDA(cudaMalloc(&w.v, sizeof(float) * C * KVS));
   PF_CUDA(cudaMalloc(&w.qr, sizeof(float) * C * QS));
   PF_CUDA(cudaMalloc(&w.o, sizeof(float) * C * H));
-  PF_CUDA(cudaMalloc(&w.gate, sizeof(float) * C * I));
-  PF_CUDA(cudaMalloc(&w.up, sizeof(float) * C * I));
   PF_CUDA(cudaMalloc(&w.down, sizeof(float) * C * H));
   PF_CUDA(cudaMalloc(&w.xn, sizeof(__half) * C * H));
   PF_CUDA(cudaMalloc(&w.attn, sizeof(__half) * C * QS));
@@ -309,13 +330,9 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
                                                                                   max_seq_len, attn_scale);
       if ((rc = gemm(w.map_attn, w.wmap[l][3], w.o, M, H, QS)) != QMK_OK) break;
       add_rmsnorm_rows<<<T, 256, 0, stream>>>(w.x, w.o, reinterpret_cast<const __half *>(r[7]), w.xn);
-      {
-        const CUtensorMap(*const b[2])[2] = {&w.wmap[l][4], &w.wmap[l][5]};
-        float *const cs[2] = {w.gate, w.up};
-        const int ns[2] = {I, I};
-        if ((rc = gemm_group(w.map_xn, 2, b, cs, ns, M, H)) != QMK_OK) break;
-      }
-      silu_mul_rows<<<592, 256, 0, stream>>>(w.gate, w.up, w.act, static_cast<size_t>(T) * I);
+      if ((rc = qmk_tc::launch_gemm_swiglu(w.map_xn, w.wmap[l][4][0], w.wmap[l][5][0], w.act, M, I, H, w.status,
+                                           env.timeout_ms, stream, &err)) != QMK_OK)
+        break;
       if ((rc = gemm(w.map_act, w.wmap[l][6], w.down, M, H, I)) != QMK_OK) break;
     }
     if (rc != QMK_OK) break;
@@ -465,13 +482,9 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
                                                         max_seq_len, attn_scale);
       if ((r2 = gemm(w.map_attn, w.wmap[l][3], w.o, H, QS)) != QMK_OK) return r2;
       add_rmsnorm_rows<<<B, 256, 0, s>>>(w.x, w.o, reinterpret_cast<const __half *>(r[7]), w.xn);
-      {
-        const CUtensorMap(*const b[2])[2] = {&w.wmap[l][4], &w.wmap[l][5]};
-        float *const cs[2] = {w.gate, w.up};
-        const int ns[2] = {I, I};
-        if ((r2 = gemm_group(w.map_xn, 2, b, cs, ns, H)) != QMK_OK) return r2;
-      }
-      silu_mul_rows<<<(B * I + 255) / 256, 256, 0, s>>>(w.gate, w.up, w.act, static_cast<size_t>(B) * I);
+      if ((r2 = qmk_tc::launch_gemm_swiglu(w.map_xn, w.wmap[l][4][0], w.wmap[l][5][0], w.act, M, I, H, w.status,
+                                           env.timeout_ms, s, &err)) != QMK_OK)
+        return r2;
       if ((r2 = gemm(w.map_act, w.wmap[l][6], w.down, H, I)) != QMK_OK) return r2;
     }
     add_rmsnorm_rows<<<B, 256, 0, s>>>(w.x, w.down, static_cast<const __half *>(final_norm_weight), w.xn);
@@ -532,6 +545,42 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
   if (host_status[0] != 0)
     return qmk_internal::report(static_cast<int>(host_status[0]), "decode_batched: a bounded device wait ran out");
   return QMK_OK;
+}
+
+// Bounded-wait self test of the GEMM kernel: one 128 x 128 tile whose loads are never issued.  The MMA thread's
+// wait on the first stage runs out after budget_us, every role leaves its loop, TMEM is freed and the kernel
+// returns status 4 with the context intact.
+extern "C" int qmk_selftest_gemm_wait_timeout(int budget_us) {
+  std::string err;
+  if (budget_us < 1 || budget_us > 1000000) return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "budget_us must be in [1, 1e6]");
+  int rc = qmk_tc::ensure_gemm_attrs(&err);
+  if (rc != QMK_OK) return qmk_internal::report(rc, err);
+  __half *ab = nullptr;
+  float *c = nullptr;
+  unsigned int *status = nullptr;
+  PF_CUDA(cudaMalloc(&ab, sizeof(__half) * 128 * 64));
+  PF_CUDA(cudaMalloc(&c, sizeof(float) * 128 * 128));
+  PF_CUDA(cudaMalloc(&status, 16));
+  PF_CUDA(cudaMemset(ab, 0, sizeof(__half) * 128 * 64));
+  PF_CUDA(cudaMemset(status, 0, 16));
+  CUtensorMap m;
+  rc = qmk_tc::make_map_f16(&m, ab, 128, 64, 128, &err);
+  if (rc == QMK_OK) {
+    qmk_gemm::Groups gr;
+    gr.C[0] = c; gr.C[1] = nullptr; gr.C[2] = nullptr;
+    gr.N[0] = 128; gr.N[1] = 0; gr.N[2] = 0;
+    qmk_gemm::gemm_f16_tn_kernel<128><<<dim3(1, 1), qmk_gemm::THREADS, qmk_gemm::smem_bytes_for(128)>>>(
+        m, m, m, m, gr, 128, 64, status, static_cast<unsigned long long>(budget_us) * 1000ull, 1);
+    unsigned int host[4] = {0, 0, 0, 0};
+    cudaError_t e = cudaMemcpy(host, status, 16, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) { rc = QMK_ERR_CUDA; err = std::string("gemm self test: ") + cudaGetErrorString(e); }
+    else rc = static_cast<int>(host[0]);
+  }
+  cudaFree(ab);
+  cudaFree(c);
+  cudaFree(status);
+  if (rc != QMK_OK && rc != QMK_ERR_WAIT_TIMEOUT) return qmk_internal::report(rc, err);
+  return rc;
 }
 
 extern "C" int qmk_gemm_f16_tn(const void *a, const void *b, float *c, int m, int n, int k, cudaStream_t stream) {

@@ -78,12 +78,14 @@ _lib.qmk_num_ctas.restype = _I
 _lib.qmk_scratch_bytes.restype = ctypes.c_longlong
 _lib.qmk_selftest_wait_timeout.argtypes = [_I]
 _lib.qmk_selftest_wait_timeout.restype = _I
+_lib.qmk_selftest_gemm_wait_timeout.argtypes = [_I]
+_lib.qmk_selftest_gemm_wait_timeout.restype = _I
 
 EXPORTED_SYMBOLS = (
     "launch_ldg_decode_direct", "launch_ldg_decode_persistent", "launch_ldg_generate_nosync",
     "launch_ldg_prefill", "qmk_abi_version", "qmk_configure", "qmk_set_inv_freq", "qmk_set_logits_dump",
     "qmk_set_weight_format", "qmk_set_tuning", "qmk_set_tuning2", "qmk_set_profile_buffer", "qmk_decode", "qmk_generate", "qmk_generate_static", "qmk_generate_batch", "qmk_gemm_f16_tn", "qmk_decode_batched", "qmk_prefill_chunked", "qmk_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
-    "qmk_scratch_bytes", "qmk_selftest_wait_timeout",
+    "qmk_scratch_bytes", "qmk_selftest_wait_timeout", "qmk_selftest_gemm_wait_timeout",
 )
 
 
@@ -377,3 +379,9 @@ def scratch_bytes() -> int:
 def selftest_wait_timeout(budget_us: int = 200) -> int:
     _require_cuda()
     return int(_lib.qmk_selftest_wait_timeout(int(budget_us)))
+
+
+def selftest_gemm_wait_timeout(budget_us: int = 300) -> int:
+    """Runs the tcgen05 GEMM's bounded wait dry (its loads are never issued); 4 = gave up as designed."""
+    _require_cuda()
+    return int(_lib.qmk_selftest_gemm_wait_timeout(int(budget_us)))

@@ -46,3 +46,12 @@ def test_bad_shapes_are_refused(C):
     b = torch.zeros(128, 64, dtype=torch.float16, device="cuda")
     with pytest.raises(RuntimeError):
         C.gemm_f16_tn(a, b)
+
+
+def test_bounded_wait_reports_timeout_and_frees_tmem(C):
+    """Loads that never come: the kernel's waits give up after their budget, report status 4, release TMEM and
+    return; the context stays usable and the next GEMM (which needs TMEM on the same SM) is exact."""
+    for _ in range(3):
+        assert C.selftest_gemm_wait_timeout(300) == 4
+    a = torch.ones(128, 64, dtype=torch.float16, device="cuda")
+    assert torch.equal(C.gemm_f16_tn(a, a), torch.full((128, 128), 64.0, device="cuda"))
