@@ -145,3 +145,30 @@ def test_gpu_continuous_batching_equals_single_sequence_engine(built_library, ti
         assert r.tokens == cut
         assert r.finish_reason == ("stop" if eos in w_ else "length")
     assert sch.max_live == 4 and sch.launches < sum(n for _, n in reqs)
+
+
+def test_random_workloads_property():
+    """Property test over random request mixes, slot counts, quanta and EOS ids: every request's answer equals
+    its own sequential run, the slot limit holds, nobody overruns a budget, all futures resolve."""
+    hypothesis = pytest.importorskip("hypothesis")
+    from hypothesis import given, settings, strategies as st
+
+    req = st.tuples(st.lists(st.integers(0, 96), min_size=1, max_size=12), st.integers(0, 40))
+
+    @settings(max_examples=60, deadline=None)
+    @given(reqs=st.lists(req, min_size=1, max_size=25), slots=st.integers(1, 9), quantum=st.integers(1, 17),
+           eos=st.one_of(st.none(), st.integers(0, 96)))
+    def run(reqs, slots, quantum, eos):
+        eng = FakeEngine(num_sequences=slots, max_seq_len=64)
+        sch = ContinuousBatcher(eng, eos_token_id=eos, quantum=quantum)
+        futs = [sch.submit(ids, n) for ids, n in reqs]
+        sch.run_until_idle()
+        for (ids, n), f in zip(reqs, futs):
+            r = f.result(timeout=0)
+            want, why = FakeEngine.reference(ids, n, -1 if eos is None else eos) if n > 0 else ([], "length")
+            assert r.tokens == want and r.finish_reason == why
+        assert sch.max_live <= slots
+        assert all(len(s) <= slots and len(set(s)) == len(s) and 1 <= q <= quantum for s, q in eng.launch_log)
+        assert all(p <= 64 for p in eng.positions)
+
+    run()
