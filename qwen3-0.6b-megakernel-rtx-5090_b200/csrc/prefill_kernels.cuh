@@ -64,20 +64,12 @@ __global__ void add_rmsnorm_rows(float *x, const float *add, const __half *w, __
 // fp32 (qr[t][head][128]); K (normalised, rotated) and V go to the fp16 cache rows of this layer.
 // grid = (T, 4), block = 256 = 8 warps; warp w of block y handles head slot y * 8 + w of 32:
 // 0..15 query heads, 16..23 K heads, 24..31 V heads.
-// Two addressing modes: one sequence (row t at position pos0 + t of the one cache), or - `positions` non-null -
-// one row per sequence (row t at positions[t] of sequence t's own cache, k_ptrs[t] / v_ptrs[t] + layer_off).
 __global__ void qk_norm_rope_cache(const float *q, const float *k, const float *v, const __half *q_norm,
                                    const __half *k_norm, const float *rope, const __half *cos_table,
                                    const __half *sin_table, float *qr, __half *k_cache_layer, __half *v_cache_layer,
-                                   int pos0, int max_seq_len, const int *positions, __half *const *k_ptrs,
-                                   __half *const *v_ptrs, size_t layer_off) {
+                                   int pos0, int max_seq_len) {
   const int t = blockIdx.x, slot = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  int pos = pos0 + t;
-  if (positions) {
-    pos = positions[t];
-    k_cache_layer = k_ptrs[t] + layer_off;
-    v_cache_layer = v_ptrs[t] + layer_off;
-  }
+  const int pos = pos0 + t;
   if (slot >= 24) {   // V head: plain copy to the cache
     const int g = slot - 24;
     const float *src = v + static_cast<size_t>(t) * KVS + g * D;
@@ -387,39 +379,91 @@ __global__ void __launch_bounds__(128) causal_attention_mma(const float *qr, con
   }
 }
 
-// Decode-step attention for a batch of sequences: sequence b's single query token over its own cache rows
-// [0, positions[b]] (the new row is already in the cache).  grid = (B, 8 kv heads), block = 256 = 8 warps.
-// Warps take 32-key tiles round-robin straight from global memory: lane j scores key j for both query heads of
-// the group (q in shared memory, broadcast reads), probabilities travel by shuffle, every lane owns 4 output
-// dims; the eight warps' partial softmax states are merged through shared memory.
-__global__ void __launch_bounds__(256) decode_attention_seq(const float *qr, __half *const *k_ptrs, __half *const *v_ptrs,
-                                                            size_t layer_off, const int *positions, __half *out,
-                                                            int max_seq_len, float scale) {
+// Decode-step attention for a batch of sequences, with the per-head preparation fused in.  grid = (B, 8 kv
+// heads), block = 256 = 8 warps.  CTA (sequence b, kv head g) first normalises and rotates the two query heads
+// and the K head of row b of the q / k / v GEMM outputs (warps 0-2; warp 3 takes V), writes the new K and V rows
+// to sequence b's cache at positions[b], and then attends over the old rows [0, positions[b]) from the cache
+// plus the new row from shared memory (the fp16-rounded values, i.e. exactly what a later step reads back).
+// Warps take 32-key tiles round-robin straight from global memory: lane j scores key j for both query heads
+// (q in shared memory, broadcast reads), probabilities travel by shuffle, every lane owns 4 output dims; the
+// eight warps' partial softmax states and the new row are merged through shared memory.
+__global__ void __launch_bounds__(256) decode_attention_fused(const float *q, const float *k, const float *v,
+                                                              const __half *q_norm, const __half *k_norm, const float *rope,
+                                                              const __half *cos_table, const __half *sin_table,
+                                                              __half *const *k_ptrs, __half *const *v_ptrs, size_t layer_off,
+                                                              const int *positions, __half *out, int max_seq_len,
+                                                              float scale) {
   __shared__ __align__(16) float sq[2 * D];
+  __shared__ float sknew[D], svnew[D], snew_score[2];
   __shared__ float sm[8][2], sl[8][2];
   __shared__ __align__(16) float sacc[8][2][D];
   const int b = blockIdx.x, g = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nkeys = positions[b] + 1;
-  sq[threadIdx.x] = qr[(static_cast<size_t>(b) * NQ + 2 * g + (threadIdx.x >> 7)) * D + (threadIdx.x & (D - 1))];
+  const int pos = positions[b];
+  __half *kbase = k_ptrs[b] + layer_off + static_cast<size_t>(g) * max_seq_len * D;
+  __half *vbase = v_ptrs[b] + layer_off + static_cast<size_t>(g) * max_seq_len * D;
+  if (warp < 4) {
+    const float *src = warp < 2 ? q + static_cast<size_t>(b) * QS + (2 * g + warp) * D
+                                : (warp == 2 ? k : v) + static_cast<size_t>(b) * KVS + g * D;
+    float x[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) x[i] = src[lane + 32 * i];
+    if (warp < 3) {
+      const __half *nw = warp < 2 ? q_norm : k_norm;
+      float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+      ss = warp_sum(ss);
+      const float rstd = 1.0f / sqrtf(ss * (1.0f / D) + RMS_EPS);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) x[i] = x[i] * rstd * __half2float(nw[lane + 32 * i]);
+      float c0, s0, c1, s1;
+      if (rope) {
+        const float *r = rope + static_cast<size_t>(pos) * D;
+        c0 = r[lane]; c1 = r[lane + 32]; s0 = r[64 + lane]; s1 = r[64 + lane + 32];
+      } else {
+        const __half *ct = cos_table + static_cast<size_t>(pos) * D, *st = sin_table + static_cast<size_t>(pos) * D;
+        c0 = __half2float(ct[lane]); c1 = __half2float(ct[lane + 32]);
+        s0 = __half2float(st[lane]); s1 = __half2float(st[lane + 32]);
+      }
+      const float r0 = x[0] * c0 - x[2] * s0, r2 = x[0] * s0 + x[2] * c0;
+      const float r1 = x[1] * c1 - x[3] * s1, r3 = x[1] * s1 + x[3] * c1;
+      x[0] = r0; x[1] = r1; x[2] = r2; x[3] = r3;
+    }
+    if (warp < 2) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sq[warp * D + lane + 32 * i] = x[i];
+    } else {
+      float *snew = warp == 2 ? sknew : svnew;
+      __half *dst = (warp == 2 ? kbase : vbase) + static_cast<size_t>(pos) * D;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __half hv = __float2half_rn(x[i]);
+        dst[lane + 32 * i] = hv;
+        snew[lane + 32 * i] = __half2float(hv);
+      }
+    }
+  }
   __syncthreads();
-  const __half *kbase = k_ptrs[b] + layer_off + static_cast<size_t>(g) * max_seq_len * D;
-  const __half *vbase = v_ptrs[b] + layer_off + static_cast<size_t>(g) * max_seq_len * D;
   const float sc = scale * 1.4426950408889634f;
+  if (warp < 2) {   // score of the new row for query head `warp`
+    float d = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) d = fmaf(sq[warp * D + lane + 32 * i], sknew[lane + 32 * i], d);
+    d = warp_sum(d);
+    if (lane == 0) snew_score[warp] = d * sc;
+  }
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int k0 = warp * 32; k0 < nkeys; k0 += 8 * 32) {
+  for (int k0 = warp * 32; k0 < pos; k0 += 8 * 32) {   // old rows only
     const int key = k0 + lane;
     float sa = 0.f, sb = 0.f;
-    if (key < nkeys) {
+    if (key < pos) {
       const uint4 *krow = reinterpret_cast<const uint4 *>(kbase + static_cast<size_t>(key) * D);
       uint4 kreg[D / 8];
 #pragma unroll
-      for (int c = 0; c < D / 8; ++c) kreg[c] = __ldg(krow + c);   // the whole row in flight at once
+      for (int c = 0; c < D / 8; ++c) kreg[c] = __ldg(krow + c);
 #pragma unroll
       for (int c = 0; c < D / 8; ++c) {
-        const uint4 kv = kreg[c];
-        const __half2 *h = reinterpret_cast<const __half2 *>(&kv);
+        const __half2 *h = reinterpret_cast<const __half2 *>(&kreg[c]);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const float2 kf = __half22float2(h[i]);
@@ -441,7 +485,7 @@ __global__ void __launch_bounds__(256) decode_attention_seq(const float *qr, __h
     m0 = na; m1 = nb;
 #pragma unroll
     for (int d = 0; d < 4; ++d) { a0[d] *= ca; a1[d] *= cb; }
-    const int nj = min(32, nkeys - k0);   // warp-uniform
+    const int nj = min(32, pos - k0);   // warp-uniform
 #pragma unroll 8
     for (int j = 0; j < nj; ++j) {
       const float pja = __shfl_sync(0xffffffffu, pa, j), pjb = __shfl_sync(0xffffffffu, pb, j);
@@ -460,10 +504,10 @@ __global__ void __launch_bounds__(256) decode_attention_seq(const float *qr, __h
   __syncthreads();
   {
     const int h = threadIdx.x >> 7, d = threadIdx.x & (D - 1);
-    float M = -INFINITY;
+    float M = snew_score[h];          // the new row is always there
 #pragma unroll
     for (int w = 0; w < 8; ++w) M = fmaxf(M, sm[w][h]);
-    float L = 0.f, A = 0.f;
+    float L = exp2f(snew_score[h] - M), A = L * svnew[d];
 #pragma unroll
     for (int w = 0; w < 8; ++w) {
       const float mw = sm[w][h];

@@ -324,7 +324,7 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
       }
       qk_norm_rope_cache<<<dim3(T, 4), 256, 0, stream>>>(w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]),
                                                          reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv, w.qr, kc, vc,
-                                                         pos0, max_seq_len, nullptr, nullptr, nullptr, 0);
+                                                         pos0, max_seq_len);
       if (l == num_layers - 1) break;   // the cache is complete; nothing downstream of the last layer is kept
       causal_attention_mma<<<dim3((T + ATM_Q - 1) / ATM_Q, NKV), 128, 0, stream>>>(w.qr, kc, vc, w.attn, T, pos0,
                                                                                   max_seq_len, attn_scale);
@@ -475,11 +475,9 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
         const int ns[3] = {QS, KVS, KVS};
         if ((r2 = gemm_group(w.map_xn, 3, b, cs, ns, H)) != QMK_OK) return r2;
       }
-      qk_norm_rope_cache<<<dim3(B, 4), 256, 0, s>>>(w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]),
-                                                    reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv, w.qr, nullptr,
-                                                    nullptr, 0, max_seq_len, w.positions, w.k_ptrs, w.v_ptrs, layer_off);
-      decode_attention_seq<<<dim3(B, NKV), 256, 0, s>>>(w.qr, w.k_ptrs, w.v_ptrs, layer_off, w.positions, w.attn,
-                                                        max_seq_len, attn_scale);
+      decode_attention_fused<<<dim3(B, NKV), 256, 0, s>>>(w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]),
+                                                          reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv, w.k_ptrs,
+                                                          w.v_ptrs, layer_off, w.positions, w.attn, max_seq_len, attn_scale);
       if ((r2 = gemm(w.map_attn, w.wmap[l][3], w.o, H, QS)) != QMK_OK) return r2;
       add_rmsnorm_rows<<<B, 256, 0, s>>>(w.x, w.o, reinterpret_cast<const __half *>(r[7]), w.xn);
       if ((r2 = qmk_tc::launch_gemm_swiglu(w.map_xn, w.wmap[l][4][0], w.wmap[l][5][0], w.act, M, I, H, w.status,
