@@ -113,6 +113,11 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
 struct Groups {
   float *C[MAX_GROUPS];
   int N[MAX_GROUPS];
+  // Split-K (single group only): gridDim.z CTAs share an output tile, CTA z multiplies K blocks
+  // [z * kblocks_per_split, (z + 1) * kblocks_per_split) and writes its partial sums to C + z * split_stride
+  // (floats); the consumer adds the partial matrices in a fixed order.  0 = no split.
+  int kblocks_per_split;
+  size_t split_stride;
 };
 
 // FUSE (BN = 64 only): B0 is the gate matrix and B1 the up matrix of a SwiGLU MLP; the CTA keeps two accumulators
@@ -144,7 +149,8 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = tile * BN, m0 = blockIdx.y * BM;
-  const int kblocks = K / BK;
+  const int kblocks = groups.kblocks_per_split > 0 ? groups.kblocks_per_split : K / BK;
+  const int kb0 = groups.kblocks_per_split > 0 ? static_cast<int>(blockIdx.z) * groups.kblocks_per_split : 0;
   constexpr uint32_t TILE_B_BYTES = BN * BK * 2;
   constexpr uint32_t TMEM_COLS = SB;             // fp32 accumulator(s): 128 lanes x SB columns (a power of two >= 32)
   auto full = [&](int s) { return bars + 8u * s; };
@@ -176,9 +182,9 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         if (kb >= STAGES && !bar_wait(empty(s), ((kb / STAGES) - 1) & 1, abort_flag, status, budget_ns)) break;
         if (*abort_flag) break;
         bar_expect_tx(full(s), TILE_A_BYTES + (FUSE ? 2 : 1) * TILE_B_BYTES);
-        tma_load_2d(base + s * STAGE_BYTES, &map_a, kb * BK, m0, full(s));
-        tma_load_2d(base + s * STAGE_BYTES + TILE_A_BYTES, map_b, kb * BK, n0, full(s));
-        if (FUSE) tma_load_2d(base + s * STAGE_BYTES + TILE_A_BYTES + TILE_B_BYTES, &map_b1, kb * BK, n0, full(s));
+        tma_load_2d(base + s * STAGE_BYTES, &map_a, (kb0 + kb) * BK, m0, full(s));
+        tma_load_2d(base + s * STAGE_BYTES + TILE_A_BYTES, map_b, (kb0 + kb) * BK, n0, full(s));
+        if (FUSE) tma_load_2d(base + s * STAGE_BYTES + TILE_A_BYTES + TILE_B_BYTES, &map_b1, (kb0 + kb) * BK, n0, full(s));
         issued = kb + 1;
       }
       // after an abort the copies already issued must land before the CTA can exit
@@ -254,7 +260,7 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       }
     } else if (ok) {
       const int row = m0 + quarter * 32 + lane;
-      float *crow = C + static_cast<size_t>(row) * N + n0;
+      float *crow = C + static_cast<size_t>(blockIdx.z) * groups.split_stride + static_cast<size_t>(row) * N + n0;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];

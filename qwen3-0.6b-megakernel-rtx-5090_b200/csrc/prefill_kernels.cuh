@@ -33,7 +33,9 @@ __global__ void embed_rows(const int *tokens, const __half *embed, float *x) {
 }
 
 // Residual add + RMSNorm: x[t] += add[t] (if add), y[t] = fp16(x[t] * rstd * w).  grid = T, block = 256.
-__global__ void add_rmsnorm_rows(float *x, const float *add, const __half *w, __half *y) {
+// `add` may come as `nparts` partial matrices `part_stride` floats apart (split-K GEMM output): they are added
+// in index order.
+__global__ void add_rmsnorm_rows(float *x, const float *add, int nparts, size_t part_stride, const __half *w, __half *y) {
   __shared__ float red[8];
   const int t = blockIdx.x;
   float *xr = x + static_cast<size_t>(t) * H;
@@ -42,7 +44,10 @@ __global__ void add_rmsnorm_rows(float *x, const float *add, const __half *w, __
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int k = threadIdx.x + j * 256;
-    v[j] = xr[k] + (add ? add[static_cast<size_t>(t) * H + k] : 0.f);
+    float acc = xr[k];
+    if (add)
+      for (int p = 0; p < nparts; ++p) acc += add[p * part_stride + static_cast<size_t>(t) * H + k];
+    v[j] = acc;
     ss = fmaf(v[j], v[j], ss);
   }
   ss = warp_sum(ss);
@@ -380,14 +385,19 @@ __global__ void __launch_bounds__(128) causal_attention_mma(const float *qr, con
 }
 
 // Decode-step attention for a batch of sequences, with the per-head preparation fused in.  grid = (B, 8 kv
-// heads), block = 256 = 8 warps.  CTA (sequence b, kv head g) first normalises and rotates the two query heads
+// heads), block = 1024 = 32 warps.  CTA (sequence b, kv head g) first normalises and rotates the two query heads
 // and the K head of row b of the q / k / v GEMM outputs (warps 0-2; warp 3 takes V), writes the new K and V rows
 // to sequence b's cache at positions[b], and then attends over the old rows [0, positions[b]) from the cache
 // plus the new row from shared memory (the fp16-rounded values, i.e. exactly what a later step reads back).
 // Warps take 32-key tiles round-robin straight from global memory: lane j scores key j for both query heads
 // (q in shared memory, broadcast reads), probabilities travel by shuffle, every lane owns 4 output dims; the
-// eight warps' partial softmax states and the new row are merged through shared memory.
-__global__ void __launch_bounds__(256) decode_attention_fused(const float *q, const float *k, const float *v,
+// warps' partial softmax states and the new row are merged through shared memory.  32 warps because the loop is
+// latency-bound: with 8 warps a 16-sequence step spent 48 us per layer here.
+// DEC_ATT_WARPS warps per CTA, one 32-key tile per warp and round.  The loop is latency-bound: with few CTAs
+// (16 sequences: 128 CTAs, 48 us per layer with 8 warps) 32 warps keep 1024 keys in flight per SM; with many
+// CTAs (64 sequences) 8 warps per CTA and several CTAs per SM do better (12.4 k vs 16.3 k tok/s).
+template <int DEC_ATT_WARPS>
+__global__ void __launch_bounds__(DEC_ATT_WARPS * 32) decode_attention_fused(const float *q, const float *k, const float *v,
                                                               const __half *q_norm, const __half *k_norm, const float *rope,
                                                               const __half *cos_table, const __half *sin_table,
                                                               __half *const *k_ptrs, __half *const *v_ptrs, size_t layer_off,
@@ -395,8 +405,8 @@ __global__ void __launch_bounds__(256) decode_attention_fused(const float *q, co
                                                               float scale) {
   __shared__ __align__(16) float sq[2 * D];
   __shared__ float sknew[D], svnew[D], snew_score[2];
-  __shared__ float sm[8][2], sl[8][2];
-  __shared__ __align__(16) float sacc[8][2][D];
+  __shared__ float sm[DEC_ATT_WARPS][2], sl[DEC_ATT_WARPS][2];
+  __shared__ __align__(16) float sacc[DEC_ATT_WARPS][2][D];
   const int b = blockIdx.x, g = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = positions[b];
@@ -453,7 +463,7 @@ __global__ void __launch_bounds__(256) decode_attention_fused(const float *q, co
   }
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int k0 = warp * 32; k0 < pos; k0 += 8 * 32) {   // old rows only
+  for (int k0 = warp * 32; k0 < pos; k0 += DEC_ATT_WARPS * 32) {   // old rows only
     const int key = k0 + lane;
     float sa = 0.f, sb = 0.f;
     if (key < pos) {
@@ -502,14 +512,14 @@ __global__ void __launch_bounds__(256) decode_attention_fused(const float *q, co
 #pragma unroll
   for (int d = 0; d < 4; ++d) { sacc[warp][0][lane * 4 + d] = a0[d]; sacc[warp][1][lane * 4 + d] = a1[d]; }
   __syncthreads();
-  {
+  if (threadIdx.x < 2 * D) {
     const int h = threadIdx.x >> 7, d = threadIdx.x & (D - 1);
     float M = snew_score[h];          // the new row is always there
 #pragma unroll
-    for (int w = 0; w < 8; ++w) M = fmaxf(M, sm[w][h]);
+    for (int w = 0; w < DEC_ATT_WARPS; ++w) M = fmaxf(M, sm[w][h]);
     float L = exp2f(snew_score[h] - M), A = L * svnew[d];
 #pragma unroll
-    for (int w = 0; w < 8; ++w) {
+    for (int w = 0; w < DEC_ATT_WARPS; ++w) {
       const float mw = sm[w][h];
       const float s = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
       L = fmaf(sl[w][h], s, L);

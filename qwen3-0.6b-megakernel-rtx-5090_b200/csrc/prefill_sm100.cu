@@ -106,6 +106,8 @@ int launch_gemm_grouped(const CUtensorMap &map_a, int ngroups, const CUtensorMap
   const int arc = ensure_gemm_attrs(err);
   if (arc != QMK_OK) return arc;
   qmk_gemm::Groups gr;
+  gr.kblocks_per_split = 0;
+  gr.split_stride = 0;
   int tiles = 0;
   for (int g = 0; g < qmk_gemm::MAX_GROUPS; ++g) {
     gr.C[g] = g < ngroups ? Cs[g] : nullptr;
@@ -139,9 +141,35 @@ int launch_gemm_swiglu(const CUtensorMap &map_a, const CUtensorMap &map_gate, co
   qmk_gemm::Groups gr;
   gr.C[0] = reinterpret_cast<float *>(act); gr.C[1] = nullptr; gr.C[2] = nullptr;
   gr.N[0] = N; gr.N[1] = 0; gr.N[2] = 0;
+  gr.kblocks_per_split = 0;
+  gr.split_stride = 0;
   qmk_gemm::gemm_f16_tn_kernel<64, true><<<dim3(N / 64, M / qmk_gemm::BM), qmk_gemm::THREADS, qmk_gemm::smem_bytes_for(128),
                                            stream>>>(map_a, map_gate, map_up, map_up, gr, M, K, status,
                                                      static_cast<unsigned long long>(timeout_ms) * 1000000ull, 0);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { *err = std::string("gemm launch: ") + cudaGetErrorString(e); return QMK_ERR_CUDA; }
+  return QMK_OK;
+}
+
+// Split-K form for skinny problems (one 128-row tile, long K): `splits` CTAs per output tile, partial matrices
+// C + z * M * N.  K / 64 must be a multiple of `splits`.  `map_b` made with 64 rows per box.
+int launch_gemm_splitk(const CUtensorMap &map_a, const CUtensorMap &map_b, float *C, int M, int N, int K, int splits,
+                       unsigned int *status, int timeout_ms, cudaStream_t stream, std::string *err) {
+  if (M <= 0 || N <= 0 || K <= 0 || M % qmk_gemm::BM || N % 128 || K % qmk_gemm::BK || splits < 1 ||
+      (K / qmk_gemm::BK) % splits) {
+    *err = "gemm: bad split-K shape";
+    return QMK_ERR_BAD_ARGUMENT;
+  }
+  const int arc = ensure_gemm_attrs(err);
+  if (arc != QMK_OK) return arc;
+  qmk_gemm::Groups gr;
+  gr.C[0] = C; gr.C[1] = nullptr; gr.C[2] = nullptr;
+  gr.N[0] = N; gr.N[1] = 0; gr.N[2] = 0;
+  gr.kblocks_per_split = K / qmk_gemm::BK / splits;
+  gr.split_stride = static_cast<size_t>(M) * N;
+  qmk_gemm::gemm_f16_tn_kernel<64><<<dim3(N / 64, M / qmk_gemm::BM, splits), qmk_gemm::THREADS, qmk_gemm::smem_bytes_for(64),
+                                     stream>>>(map_a, map_b, map_b, map_b, gr, M, K, status,
+                                               static_cast<unsigned long long>(timeout_ms) * 1000000ull, 0);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { *err = std::string("gemm launch: ") + cudaGetErrorString(e); return QMK_ERR_CUDA; }
   return QMK_OK;
@@ -182,6 +210,10 @@ struct Workspace {                  // per device, allocated on first use, never
   int logits_vocab = 0;
   const void *lm_ptr = nullptr;
   CUtensorMap map_lm;
+  // A-operand maps that expose only the live rows: the rest of the 128-row box is zero-filled by the TMA unit
+  // without being read, which cuts the activation traffic of a small batch by 128 / rows
+  int a_rows = 0;
+  CUtensorMap map_xn_b, map_attn_b, map_act_b;
   // weight maps of the layer table seen last (rebuilt when the table's contents change)
   unsigned long long table[MAX_LAYERS * 12] = {};
   int table_layers = 0;
@@ -315,7 +347,7 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
     for (int l = 0; l < num_layers; ++l) {
       const unsigned long long *r = rec.data() + static_cast<size_t>(l) * 12;
       __half *kc = static_cast<__half *>(k_cache) + l * layer_stride, *vc = static_cast<__half *>(v_cache) + l * layer_stride;
-      add_rmsnorm_rows<<<T, 256, 0, stream>>>(w.x, l > 0 ? w.down : nullptr, reinterpret_cast<const __half *>(r[0]), w.xn);
+      add_rmsnorm_rows<<<T, 256, 0, stream>>>(w.x, l > 0 ? w.down : nullptr, 1, 0, reinterpret_cast<const __half *>(r[0]), w.xn);
       {
         const CUtensorMap(*const b[3])[2] = {&w.wmap[l][0], &w.wmap[l][1], &w.wmap[l][2]};
         float *const cs[3] = {w.q, w.k, w.v};
@@ -329,7 +361,7 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
       causal_attention_mma<<<dim3((T + ATM_Q - 1) / ATM_Q, NKV), 128, 0, stream>>>(w.qr, kc, vc, w.attn, T, pos0,
                                                                                   max_seq_len, attn_scale);
       if ((rc = gemm(w.map_attn, w.wmap[l][3], w.o, M, H, QS)) != QMK_OK) break;
-      add_rmsnorm_rows<<<T, 256, 0, stream>>>(w.x, w.o, reinterpret_cast<const __half *>(r[7]), w.xn);
+      add_rmsnorm_rows<<<T, 256, 0, stream>>>(w.x, w.o, 1, 0, reinterpret_cast<const __half *>(r[7]), w.xn);
       if ((rc = qmk_tc::launch_gemm_swiglu(w.map_xn, w.wmap[l][4][0], w.wmap[l][5][0], w.act, M, I, H, w.status,
                                            env.timeout_ms, stream, &err)) != QMK_OK)
         break;
@@ -445,15 +477,26 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
   std::string err;
   if ((rc = qmk_tc::ensure_gemm_attrs(&err)) != QMK_OK) return qmk_internal::report(rc, err);
   (void)qmk_tc::gemm_box_n(128, 128);   // caches the SM count before any capture
+  {
+    const int rows = (B + 7) / 8 * 8;
+    if (w.a_rows != rows) {
+      rc = qmk_tc::make_map_f16(&w.map_xn_b, w.xn, rows, H, qmk_gemm::BM, &err);
+      if (rc == QMK_OK) rc = qmk_tc::make_map_f16(&w.map_attn_b, w.attn, rows, QS, qmk_gemm::BM, &err);
+      if (rc == QMK_OK) rc = qmk_tc::make_map_f16(&w.map_act_b, w.act, rows, I, qmk_gemm::BM, &err);
+      if (rc != QMK_OK) return qmk_internal::report(rc, err);
+      w.a_rows = rows;
+      w.step_key[0] = 0;   // a captured step holds the old maps
+    }
+  }
   const int M = qmk_gemm::BM;   // one tile of rows; rows >= B are computed and ignored
   // One decode step for all sequences, enqueued on `s`.  Everything that changes from step to step (tokens,
   // positions) or from call to call (cache and log pointers) lives in device arrays at fixed addresses, so the
   // same sequence of launches - and a graph captured from it - serves every step.
+  // The O (K = 2048) and down (K = 3072) projections of a 128-row step would run on 16 CTAs for 32 / 48 K blocks
+  // each: split K so that every CTA has 16 K blocks (two ring fills); the following RMSNorm adds the partials.
+  constexpr int O_SPLITS = 2, DOWN_SPLITS = 3;
+  const size_t PART = static_cast<size_t>(M) * H;
   auto enqueue_step = [&](cudaStream_t s) -> int {
-    auto gemm = [&](const CUtensorMap &a, const CUtensorMap (&bmap)[2], float *c, int N, int K) {
-      const int box_n = qmk_tc::gemm_box_n(M, N);
-      return qmk_tc::launch_gemm(a, bmap[box_n == 128], c, M, N, K, box_n, w.status, env.timeout_ms, s, &err);
-    };
     auto gemm_group = [&](const CUtensorMap &a, int n, const CUtensorMap (*const *b)[2], float *const *cs, const int *ns,
                           int K) {
       int total = 0;
@@ -468,25 +511,36 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
     for (int l = 0; l < num_layers; ++l) {
       const unsigned long long *r = rec.data() + static_cast<size_t>(l) * 12;
       const size_t layer_off = l * layer_stride;
-      add_rmsnorm_rows<<<B, 256, 0, s>>>(w.x, l > 0 ? w.down : nullptr, reinterpret_cast<const __half *>(r[0]), w.xn);
+      add_rmsnorm_rows<<<B, 256, 0, s>>>(w.x, l > 0 ? w.down : nullptr, DOWN_SPLITS, PART, reinterpret_cast<const __half *>(r[0]), w.xn);
       {
         const CUtensorMap(*const b[3])[2] = {&w.wmap[l][0], &w.wmap[l][1], &w.wmap[l][2]};
         float *const cs[3] = {w.q, w.k, w.v};
         const int ns[3] = {QS, KVS, KVS};
-        if ((r2 = gemm_group(w.map_xn, 3, b, cs, ns, H)) != QMK_OK) return r2;
+        if ((r2 = gemm_group(w.map_xn_b, 3, b, cs, ns, H)) != QMK_OK) return r2;
       }
-      decode_attention_fused<<<dim3(B, NKV), 256, 0, s>>>(w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]),
-                                                          reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv, w.k_ptrs,
-                                                          w.v_ptrs, layer_off, w.positions, w.attn, max_seq_len, attn_scale);
-      if ((r2 = gemm(w.map_attn, w.wmap[l][3], w.o, H, QS)) != QMK_OK) return r2;
-      add_rmsnorm_rows<<<B, 256, 0, s>>>(w.x, w.o, reinterpret_cast<const __half *>(r[7]), w.xn);
-      if ((r2 = qmk_tc::launch_gemm_swiglu(w.map_xn, w.wmap[l][4][0], w.wmap[l][5][0], w.act, M, I, H, w.status,
+      if (B * NKV <= 2 * 148)
+        decode_attention_fused<32><<<dim3(B, NKV), 1024, 0, s>>>(w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]),
+                                                                 reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv,
+                                                                 w.k_ptrs, w.v_ptrs, layer_off, w.positions, w.attn,
+                                                                 max_seq_len, attn_scale);
+      else
+        decode_attention_fused<8><<<dim3(B, NKV), 256, 0, s>>>(w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]),
+                                                               reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv,
+                                                               w.k_ptrs, w.v_ptrs, layer_off, w.positions, w.attn,
+                                                               max_seq_len, attn_scale);
+      if ((r2 = qmk_tc::launch_gemm_splitk(w.map_attn_b, w.wmap[l][3][0], w.o, M, H, QS, O_SPLITS, w.status, env.timeout_ms, s,
+                                           &err)) != QMK_OK)
+        return r2;
+      add_rmsnorm_rows<<<B, 256, 0, s>>>(w.x, w.o, O_SPLITS, PART, reinterpret_cast<const __half *>(r[7]), w.xn);
+      if ((r2 = qmk_tc::launch_gemm_swiglu(w.map_xn_b, w.wmap[l][4][0], w.wmap[l][5][0], w.act, M, I, H, w.status,
                                            env.timeout_ms, s, &err)) != QMK_OK)
         return r2;
-      if ((r2 = gemm(w.map_act, w.wmap[l][6], w.down, H, I)) != QMK_OK) return r2;
+      if ((r2 = qmk_tc::launch_gemm_splitk(w.map_act_b, w.wmap[l][6][0], w.down, M, H, I, DOWN_SPLITS, w.status, env.timeout_ms,
+                                           s, &err)) != QMK_OK)
+        return r2;
     }
-    add_rmsnorm_rows<<<B, 256, 0, s>>>(w.x, w.down, static_cast<const __half *>(final_norm_weight), w.xn);
-    r2 = qmk_tc::launch_gemm(w.map_xn, w.map_lm, w.logits, M, env.vocab, H, 128, w.status, env.timeout_ms, s, &err);
+    add_rmsnorm_rows<<<B, 256, 0, s>>>(w.x, w.down, DOWN_SPLITS, PART, static_cast<const __half *>(final_norm_weight), w.xn);
+    r2 = qmk_tc::launch_gemm(w.map_xn_b, w.map_lm, w.logits, M, env.vocab, H, 128, w.status, env.timeout_ms, s, &err);
     if (r2 != QMK_OK) return r2;
     argmax_rows<<<B, 1024, 0, s>>>(w.logits, env.vocab, w.tokens, w.log_ptrs, w.start_positions, w.positions);
     return QMK_OK;
@@ -567,6 +621,8 @@ extern "C" int qmk_selftest_gemm_wait_timeout(int budget_us) {
     qmk_gemm::Groups gr;
     gr.C[0] = c; gr.C[1] = nullptr; gr.C[2] = nullptr;
     gr.N[0] = 128; gr.N[1] = 0; gr.N[2] = 0;
+    gr.kblocks_per_split = 0;
+    gr.split_stride = 0;
     qmk_gemm::gemm_f16_tn_kernel<128><<<dim3(1, 1), qmk_gemm::THREADS, qmk_gemm::smem_bytes_for(128)>>>(
         m, m, m, m, gr, 128, 64, status, static_cast<unsigned long long>(budget_us) * 1000ull, 1);
     unsigned int host[4] = {0, 0, 0, 0};

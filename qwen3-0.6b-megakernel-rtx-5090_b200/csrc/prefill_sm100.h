@@ -12,6 +12,8 @@ namespace qmk_tc {
 int make_map_f16(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t cols, uint32_t box_rows, std::string *err);
 int gemm_box_n(int M, int N);
 int ensure_gemm_attrs(std::string *err);
+int launch_gemm_splitk(const CUtensorMap &map_a, const CUtensorMap &map_b, float *C, int M, int N, int K, int splits,
+                       unsigned int *status, int timeout_ms, cudaStream_t stream, std::string *err);
 int launch_gemm_swiglu(const CUtensorMap &map_a, const CUtensorMap &map_gate, const CUtensorMap &map_up, __half *act, int M,
                        int N, int K, unsigned int *status, int timeout_ms, cudaStream_t stream, std::string *err);
 int launch_gemm_grouped(const CUtensorMap &map_a, int ngroups, const CUtensorMap *const *maps_b, float *const *Cs,
