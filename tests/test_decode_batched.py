@@ -31,10 +31,11 @@ def _engine(w, n, max_seq_len, **kw):
                         num_sequences=n, max_seq_len=max_seq_len, **kw)
 
 
-@pytest.mark.parametrize("n", [1, 5, 19])
+@pytest.mark.parametrize("n", [1, 5, 19, 40])
 def test_tiny_model_against_oracle(C, n):
-    """Sequence counts that are no multiple of anything; contexts from 1 token to several 256-key rounds of
-    the attention kernel, all different."""
+    """Sequence counts that are no multiple of anything; contexts from 1 token to several rounds of the attention
+    kernels, all different.  40 sequences take the bulk-copy-fed attention kernel (its 6-slot ring wraps from 193
+    cache rows on)."""
     vocab, steps, L = 2048, 5, 768
     w = S.make_weights(seed=21, num_layers=3, vocab_size=vocab, norm_std=0.1, max_seq_len=16)
     lens = [(1 + 37 * i * i) % 700 + 1 for i in range(n)]
