@@ -385,189 +385,17 @@ __global__ void __launch_bounds__(128) causal_attention_mma(const float *qr, con
 }
 
 // Decode-step attention for a batch of sequences, with the per-head preparation fused in.  grid = (B, 8 kv
-// heads), block = 1024 = 32 warps.  CTA (sequence b, kv head g) first normalises and rotates the two query heads
-// and the K head of row b of the q / k / v GEMM outputs (warps 0-2; warp 3 takes V), writes the new K and V rows
-// to sequence b's cache at positions[b], and then attends over the old rows [0, positions[b]) from the cache
-// plus the new row from shared memory (the fp16-rounded values, i.e. exactly what a later step reads back).
-// Warps take 32-key tiles round-robin straight from global memory: lane j scores key j for both query heads
-// (q in shared memory, broadcast reads), probabilities travel by shuffle, every lane owns 4 output dims; the
-// warps' partial softmax states and the new row are merged through shared memory.  32 warps because the loop is
-// latency-bound: with 8 warps a 16-sequence step spent 48 us per layer here.
-// DEC_ATT_WARPS warps per CTA, one 32-key tile per warp and round.  The loop is latency-bound: with few CTAs
-// (16 sequences: 128 CTAs, 48 us per layer with 8 warps) 32 warps keep 1024 keys in flight per SM; with many
-// CTAs (64 sequences) 8 warps per CTA and several CTAs per SM do better (12.4 k vs 16.3 k tok/s).
-// STAGE_K: K tiles go through a per-warp shared-memory buffer (DEC_ATT_WARPS * 8320 bytes of dynamic shared memory).
-template <int DEC_ATT_WARPS, bool STAGE_K>
-__global__ void __launch_bounds__(DEC_ATT_WARPS * 32) decode_attention_fused(const float *q, const float *k, const float *v,
-                                                              const __half *q_norm, const __half *k_norm, const float *rope,
-                                                              const __half *cos_table, const __half *sin_table,
-                                                              __half *const *k_ptrs, __half *const *v_ptrs, size_t layer_off,
-                                                              const int *positions, __half *out, int max_seq_len,
-                                                              float scale) {
-  __shared__ __align__(16) float sq[2 * D];
-  __shared__ float sknew[D], svnew[D], snew_score[2];
-  __shared__ float sm[DEC_ATT_WARPS][2], sl[DEC_ATT_WARPS][2];
-  __shared__ __align__(16) float sacc[DEC_ATT_WARPS][2][D];
-  const int b = blockIdx.x, g = blockIdx.y;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int pos = positions[b];
-  __half *kbase = k_ptrs[b] + layer_off + static_cast<size_t>(g) * max_seq_len * D;
-  __half *vbase = v_ptrs[b] + layer_off + static_cast<size_t>(g) * max_seq_len * D;
-  if (warp < 4) {
-    const float *src = warp < 2 ? q + static_cast<size_t>(b) * QS + (2 * g + warp) * D
-                                : (warp == 2 ? k : v) + static_cast<size_t>(b) * KVS + g * D;
-    float x[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) x[i] = src[lane + 32 * i];
-    if (warp < 3) {
-      const __half *nw = warp < 2 ? q_norm : k_norm;
-      float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
-      ss = warp_sum(ss);
-      const float rstd = 1.0f / sqrtf(ss * (1.0f / D) + RMS_EPS);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) x[i] = x[i] * rstd * __half2float(nw[lane + 32 * i]);
-      float c0, s0, c1, s1;
-      if (rope) {
-        const float *r = rope + static_cast<size_t>(pos) * D;
-        c0 = r[lane]; c1 = r[lane + 32]; s0 = r[64 + lane]; s1 = r[64 + lane + 32];
-      } else {
-        const __half *ct = cos_table + static_cast<size_t>(pos) * D, *st = sin_table + static_cast<size_t>(pos) * D;
-        c0 = __half2float(ct[lane]); c1 = __half2float(ct[lane + 32]);
-        s0 = __half2float(st[lane]); s1 = __half2float(st[lane + 32]);
-      }
-      const float r0 = x[0] * c0 - x[2] * s0, r2 = x[0] * s0 + x[2] * c0;
-      const float r1 = x[1] * c1 - x[3] * s1, r3 = x[1] * s1 + x[3] * c1;
-      x[0] = r0; x[1] = r1; x[2] = r2; x[3] = r3;
-    }
-    if (warp < 2) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) sq[warp * D + lane + 32 * i] = x[i];
-    } else {
-      float *snew = warp == 2 ? sknew : svnew;
-      __half *dst = (warp == 2 ? kbase : vbase) + static_cast<size_t>(pos) * D;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const __half hv = __float2half_rn(x[i]);
-        dst[lane + 32 * i] = hv;
-        snew[lane + 32 * i] = __half2float(hv);
-      }
-    }
-  }
-  __syncthreads();
-  const float sc = scale * 1.4426950408889634f;
-  if (warp < 2) {   // score of the new row for query head `warp`
-    float d = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) d = fmaf(sq[warp * D + lane + 32 * i], sknew[lane + 32 * i], d);
-    d = warp_sum(d);
-    if (lane == 0) snew_score[warp] = d * sc;
-  }
-  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-  float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int k0 = warp * 32; k0 < pos; k0 += DEC_ATT_WARPS * 32) {   // old rows only
-    const int key = k0 + lane;
-    float sa = 0.f, sb = 0.f;
-    if (STAGE_K) {
-      // K tile through this warp's shared-memory buffer: coalesced 16-byte global loads (two rows per warp
-      // instruction), then lane j reads row j with a 65-word pitch (no bank conflicts).  Direct per-lane row loads
-      // touch 32 different lines per instruction and bound this loop by load-unit wavefronts when many CTAs run.
-      extern __shared__ __align__(16) unsigned char dec_att_dyn[];
-      uint32_t *tile = reinterpret_cast<uint32_t *>(dec_att_dyn) + warp * (32 * 65);
-      const int nk = min(32, pos - k0);
-      __syncwarp();   // the previous tile has been read by every lane
-#pragma unroll
-      for (int it = 0; it < 16; ++it) {
-        const int row = it * 2 + (lane >> 4), c = lane & 15;
-        uint4 kv = make_uint4(0u, 0u, 0u, 0u);
-        if (row < nk) kv = __ldg(reinterpret_cast<const uint4 *>(kbase + static_cast<size_t>(k0 + row) * D) + c);
-        uint32_t *dst = tile + row * 65 + c * 4;
-        dst[0] = kv.x; dst[1] = kv.y; dst[2] = kv.z; dst[3] = kv.w;
-      }
-      __syncwarp();
-      if (key < pos) {
-        const uint32_t *krow = tile + lane * 65;
-#pragma unroll 16
-        for (int d2 = 0; d2 < D / 2; ++d2) {
-          const uint32_t kw = krow[d2];
-          const float2 kf = __half22float2(*reinterpret_cast<const __half2 *>(&kw));
-          const float2 qa = *reinterpret_cast<const float2 *>(sq + 2 * d2);
-          const float2 qb = *reinterpret_cast<const float2 *>(sq + D + 2 * d2);
-          sa = fmaf(qa.x, kf.x, sa); sa = fmaf(qa.y, kf.y, sa);
-          sb = fmaf(qb.x, kf.x, sb); sb = fmaf(qb.y, kf.y, sb);
-        }
-        sa *= sc; sb *= sc;
-      } else {
-        sa = -INFINITY; sb = -INFINITY;
-      }
-    } else if (key < pos) {
-      const uint4 *krow = reinterpret_cast<const uint4 *>(kbase + static_cast<size_t>(key) * D);
-      uint4 kreg[D / 8];
-#pragma unroll
-      for (int c = 0; c < D / 8; ++c) kreg[c] = __ldg(krow + c);
-#pragma unroll
-      for (int c = 0; c < D / 8; ++c) {
-        const __half2 *h = reinterpret_cast<const __half2 *>(&kreg[c]);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 kf = __half22float2(h[i]);
-          const float2 qa = *reinterpret_cast<const float2 *>(sq + c * 8 + 2 * i);
-          const float2 qb = *reinterpret_cast<const float2 *>(sq + D + c * 8 + 2 * i);
-          sa = fmaf(qa.x, kf.x, sa); sa = fmaf(qa.y, kf.y, sa);
-          sb = fmaf(qb.x, kf.x, sb); sb = fmaf(qb.y, kf.y, sb);
-        }
-      }
-      sa *= sc; sb *= sc;
-    } else {
-      sa = -INFINITY; sb = -INFINITY;
-    }
-    const float na = fmaxf(m0, warp_max(sa)), nb = fmaxf(m1, warp_max(sb));   // lane 0's key is always valid
-    const float ca = exp2f(m0 - na), cb = exp2f(m1 - nb);
-    const float pa = exp2f(sa - na), pb = exp2f(sb - nb);
-    l0 = l0 * ca + warp_sum(pa);
-    l1 = l1 * cb + warp_sum(pb);
-    m0 = na; m1 = nb;
-#pragma unroll
-    for (int d = 0; d < 4; ++d) { a0[d] *= ca; a1[d] *= cb; }
-    const int nj = min(32, pos - k0);   // warp-uniform
-#pragma unroll 8
-    for (int j = 0; j < nj; ++j) {
-      const float pja = __shfl_sync(0xffffffffu, pa, j), pjb = __shfl_sync(0xffffffffu, pb, j);
-      const uint2 vv = __ldg(reinterpret_cast<const uint2 *>(vbase + static_cast<size_t>(k0 + j) * D + lane * 4));
-      const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&vv.x));
-      const float2 v23 = __half22float2(*reinterpret_cast<const __half2 *>(&vv.y));
-      a0[0] = fmaf(pja, v01.x, a0[0]); a0[1] = fmaf(pja, v01.y, a0[1]);
-      a0[2] = fmaf(pja, v23.x, a0[2]); a0[3] = fmaf(pja, v23.y, a0[3]);
-      a1[0] = fmaf(pjb, v01.x, a1[0]); a1[1] = fmaf(pjb, v01.y, a1[1]);
-      a1[2] = fmaf(pjb, v23.x, a1[2]); a1[3] = fmaf(pjb, v23.y, a1[3]);
-    }
-  }
-  if (lane == 0) { sm[warp][0] = m0; sm[warp][1] = m1; sl[warp][0] = l0; sl[warp][1] = l1; }
-#pragma unroll
-  for (int d = 0; d < 4; ++d) { sacc[warp][0][lane * 4 + d] = a0[d]; sacc[warp][1][lane * 4 + d] = a1[d]; }
-  __syncthreads();
-  if (threadIdx.x < 2 * D) {
-    const int h = threadIdx.x >> 7, d = threadIdx.x & (D - 1);
-    float M = snew_score[h];          // the new row is always there
-#pragma unroll
-    for (int w = 0; w < DEC_ATT_WARPS; ++w) M = fmaxf(M, sm[w][h]);
-    float L = exp2f(snew_score[h] - M), A = L * svnew[d];
-#pragma unroll
-    for (int w = 0; w < DEC_ATT_WARPS; ++w) {
-      const float mw = sm[w][h];
-      const float s = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-      L = fmaf(sl[w][h], s, L);
-      A = fmaf(sacc[w][h][d], s, A);
-    }
-    out[static_cast<size_t>(b) * QS + (2 * g + h) * D + d] = __float2half_rn(A / L);
-  }
-}
-
-// decode_attention_fused for many sequences (several CTAs per SM): the old cache rows are streamed by one
-// producer thread with bulk copies (cp.async.bulk, 32 K rows + 32 V rows per 16 KB ring slot, full / empty
-// mbarriers) instead of by per-lane loads, so the bytes in flight no longer depend on how many loads the compiler
-// keeps in registers (the register version ran at 43 % of DRAM bandwidth with 64 sequences).  Eight consumer
-// warps take slots round-robin; lane j scores key j reading its K row in a lane-rotated order (word (d + j) mod
-// 64 at step d), which makes the 256-byte row pitch conflict-free; V rows are read by all lanes together.
+// heads), block = 288 = 8 consumer warps + 1 producer warp.  CTA (sequence b, kv head g) first normalises and
+// rotates the two query heads and the K head of row b of the q / k / v GEMM outputs (warps 0-2; warp 3 takes V),
+// writes the new K and V rows to sequence b's cache at positions[b], and then attends over the old rows
+// [0, positions[b]) plus the new row from shared memory (the fp16-rounded values, i.e. what later steps read).
+// The old rows are streamed by one producer thread with bulk copies (cp.async.bulk, 32 K rows + 32 V rows per
+// 16 KB ring slot, full / empty mbarriers): the bytes in flight then do not depend on how many loads the compiler
+// keeps in registers (a version with per-lane global loads ran at 43 % of DRAM bandwidth with 64 sequences and
+// was 7-30 % slower at every batch size).  The consumer warps take slots round-robin; lane j scores key j reading
+// its K row in a lane-rotated order (word (d + j) mod 64 at step d), which makes the 256-byte row pitch
+// conflict-free; V rows are read by all lanes together; probabilities travel by shuffle; every lane owns 4 output
+// dims; the warps' partial softmax states and the new row are merged through shared memory.
 // Waits are bounded: on a time-out the CTA sets *status = 4 and leaves after its copies have landed.
 constexpr int DAR_WARPS = 8, DAR_SLOTS = 6, DAR_ROWS = 32;
 constexpr int DAR_SLOT_BYTES = 2 * DAR_ROWS * D * 2;   // 16 KB: K rows then V rows
@@ -657,7 +485,7 @@ __global__ void __launch_bounds__((DAR_WARPS + 1) * 32) decode_attention_ring(
           }
         }
     }
-  } else if (warp < 4) {              // ---- head preparation (as in decode_attention_fused)
+  } else if (warp < 4) {              // ---- head preparation
     const float *src = warp < 2 ? q + static_cast<size_t>(b) * QS + (2 * g + warp) * D
                                 : (warp == 2 ? k : v) + static_cast<size_t>(b) * KVS + g * D;
     float x[4];

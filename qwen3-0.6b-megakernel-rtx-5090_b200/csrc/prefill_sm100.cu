@@ -521,16 +521,10 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
         const int ns[3] = {QS, KVS, KVS};
         if ((r2 = gemm_group(w.map_xn_b, 3, b, cs, ns, H)) != QMK_OK) return r2;
       }
-      if (B * NKV <= 2 * 148)
-        decode_attention_fused<32, false><<<dim3(B, NKV), 1024, 0, s>>>(w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]),
-                                                                 reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv,
-                                                                 w.k_ptrs, w.v_ptrs, layer_off, w.positions, w.attn,
-                                                                 max_seq_len, attn_scale);
-      else
-        decode_attention_ring<<<dim3(B, NKV), (DAR_WARPS + 1) * 32, DAR_SMEM_BYTES, s>>>(
-            w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]), reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv,
-            w.k_ptrs, w.v_ptrs, layer_off, w.positions, w.attn, max_seq_len, attn_scale, w.status,
-            static_cast<unsigned long long>(env.timeout_ms) * 1000000ull);
+      decode_attention_ring<<<dim3(B, NKV), (DAR_WARPS + 1) * 32, DAR_SMEM_BYTES, s>>>(
+          w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]), reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv,
+          w.k_ptrs, w.v_ptrs, layer_off, w.positions, w.attn, max_seq_len, attn_scale, w.status,
+          static_cast<unsigned long long>(env.timeout_ms) * 1000000ull);
       if ((r2 = qmk_tc::launch_gemm_splitk(w.map_attn_b, w.wmap[l][3][0], w.o, M, H, QS, O_SPLITS, w.status, env.timeout_ms, s,
                                            &err)) != QMK_OK)
         return r2;
