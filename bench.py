@@ -410,7 +410,8 @@ def run_continuous(args):
         inner(b, ids)
         prefill_s[0] += time.perf_counter() - t
     eng.prefill_slot = timed_prefill
-    sch = ContinuousBatcher(eng, eos_token_id=None, quantum=32)
+    sch = ContinuousBatcher(eng, eos_token_id=None, quantum=32,
+                            overlap_prefill=bool(args.overlap) and getattr(eng, "supports_overlap", False))
     sch.submit(prompts[0][:64], 8)                             # warm-up: both kernels, all buffers
     sch.run_until_idle()
     prefill_s[0] = 0.0
@@ -432,7 +433,7 @@ def run_continuous(args):
             "new_tokens_per_request": new_tokens, "prompt_tokens": sum(lens), "wall_s": wall,
             "prefill_s": prefill_s[0], "decode_s": wall - prefill_s[0],
             "decode_only_tok_s": n_out / max(wall - prefill_s[0], 1e-9), "launches": sch.launches - launches0,
-            "prefill": args.prefill, "prompt_tok_s": sum(lens) / max(prefill_s[0], 1e-9),
+            "prefill": args.prefill, "overlap_prefill": sch.overlap_prefill, "prompt_tok_s": sum(lens) / max(prefill_s[0], 1e-9),
             "scaling": "weak", "data": "synthetic", "dtype": "fp16", "clocks": clocks.summary(),
             "note": "rank 0's own prefill/decode split; value uses the slowest replica's wall time"}))
     if world > 1:
@@ -456,6 +457,8 @@ def main():
     ap.add_argument("--continuous", type=int, default=0, metavar="N",
                     help="instead of the headline workload: N requests per GPU through the continuous-batching "
                          "scheduler (prompt lengths 64..2048, 128 new tokens each, --batch live sequences)")
+    ap.add_argument("--overlap", type=int, default=1,
+                    help="--continuous only: 1 = prefill the next request while the live ones decode (tensor-core engines)")
     ap.add_argument("--prefill", choices=["serial", "tensor"], default="tensor",
                     help="--continuous only: token-serial prefill op or the tensor-core chunked prefill")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prefilled context (default: benchmark config)")

@@ -19,6 +19,7 @@ reference imports this file unchanged.  What differs underneath:
 
 from __future__ import annotations
 
+import contextlib
 import math
 import os
 from typing import List, Optional, Sequence, Tuple
@@ -338,6 +339,14 @@ class BatchDecoder:
         self._logs_cpu = torch.empty(self.num_sequences, self.max_seq_len, dtype=torch.int32).pin_memory()
         self.positions = [0] * self.num_sequences
         self._gen_batch = _require_megakernel_op("generate_batch" if engine == "persistent" else "decode_batched")
+        # The tensor-core prefill and the tensor-core batched decode use separate workspaces and locks in the
+        # library: a scheduler may prefill one slot (on its own stream) while other slots decode.  The persistent
+        # engine and the token-serial prefill share the megakernel's exchange area and must not overlap.
+        self.supports_overlap = engine == "gemm" and self._base.prefill_mode == "tensor"
+        self._prefill_stream = torch.cuda.Stream(device=dev) if self.supports_overlap else None
+        # Decode rounds of an overlapping scheduler must stay off the legacy default stream: work queued there
+        # (this op's event wait lasts a whole round) orders itself against every blocking stream of the process.
+        self._decode_stream = torch.cuda.Stream(device=dev) if self.supports_overlap else None
 
     def prefill_slot(self, b: int, ids: Sequence[int]) -> None:
         """Fill slot ``b``'s KV cache with ``ids`` from position 0 (the ``prefill`` op)."""
@@ -349,7 +358,11 @@ class BatchDecoder:
         base._k_cache, base._v_cache = self._k_caches[b], self._v_caches[b]
         try:
             base._position = 0
-            base.prefill_ids(ids)
+            if self._prefill_stream is not None:
+                with torch.cuda.stream(self._prefill_stream):   # the op blocks until its stream is idle
+                    base.prefill_ids(ids)
+            else:
+                base.prefill_ids(ids)
         finally:
             base._k_cache, base._v_cache = self._k_caches[0], self._v_caches[0]
         self.positions[b] = len(ids)
@@ -371,16 +384,20 @@ class BatchDecoder:
                 raise ValueError(f"slot {b}: position + steps exceeds max_seq_len")
         base = self._base
         logs = [self._logs[b][:steps] for b in slots]
-        self._gen_batch(list(first_tokens), [self.positions[b] for b in slots], steps, base._embed_weight,
-                        base._layer_weights_packed, base._final_norm_weight, base._lm_head_weight,
-                        base._cos_table, base._sin_table, [self._k_caches[b] for b in slots],
-                        [self._v_caches[b] for b in slots], logs, base.num_layers, self.max_seq_len,
-                        base._attn_scale)
+        ctx = torch.cuda.stream(self._decode_stream) if self._decode_stream is not None else contextlib.nullcontext()
         out = []
-        for i, b in enumerate(slots):
-            host = self._logs_cpu[b, :steps]
-            host.copy_(logs[i])
-            out.append(host.tolist())
+        with ctx:
+            self._gen_batch(list(first_tokens), [self.positions[b] for b in slots], steps, base._embed_weight,
+                            base._layer_weights_packed, base._final_norm_weight, base._lm_head_weight,
+                            base._cos_table, base._sin_table, [self._k_caches[b] for b in slots],
+                            [self._v_caches[b] for b in slots], logs, base.num_layers, self.max_seq_len,
+                            base._attn_scale)
+            for i, b in enumerate(slots):
+                host = self._logs_cpu[b, :steps]
+                host.copy_(logs[i], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        for b in slots:
+            out.append(self._logs_cpu[b, :steps].tolist())
             self.positions[b] += steps
         return out
 

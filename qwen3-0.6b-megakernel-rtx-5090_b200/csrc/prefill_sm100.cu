@@ -205,8 +205,11 @@ struct Workspace {                  // per device, allocated on first use, never
   int *positions = nullptr, *start_positions = nullptr;
   cudaStream_t gstream = nullptr;        // capture needs a non-default stream
   cudaEvent_t ev_in = nullptr, ev_out = nullptr;
-  cudaGraphExec_t step_graph = nullptr;  // one decode step; valid while step_key matches
-  unsigned long long step_key[12] = {};
+  // One captured decode step per batch size (a serving loop's live count changes from round to round and
+  // instantiating ~200 nodes costs tens of milliseconds); entry B is valid while its key matches.
+  cudaGraphExec_t step_graph[129] = {};
+  unsigned long long step_key[129][12] = {};
+  unsigned long long graph_epoch = 1;    // bumped whenever tensor maps baked into the graphs are rebuilt
   __half **k_ptrs = nullptr, **v_ptrs = nullptr;
   int **log_ptrs = nullptr;
   float *logits = nullptr;
@@ -222,8 +225,10 @@ struct Workspace {                  // per device, allocated on first use, never
   int table_layers = 0;
   CUtensorMap wmap[MAX_LAYERS][7][2];  // q, k, v, o, gate, up, down; boxes of 64 and of 128 rows
 };
-Workspace g_ws[16];
-std::mutex g_ws_mu;
+// Prefill and batched decode keep separate workspaces and locks: a serving loop prefills the next request on one
+// stream (and thread) while a decode step of the live sequences runs on another.
+Workspace g_ws[16], g_ws_decode[16];
+std::mutex g_ws_mu, g_ws_decode_mu;
 
 #define PF_CUDA(call)                                                                             \
   do {                                                                                            \
@@ -285,7 +290,7 @@ int ensure_weight_maps(Workspace &w, const LDGLayerWeight *layers_dev, int num_l
     }
   memcpy(w.table, host.data(), host.size() * 8);
   w.table_layers = num_layers;
-  w.step_key[0] = 0;   // a captured decode step holds the old maps
+  ++w.graph_epoch;   // captured decode steps hold the old maps
   return QMK_OK;
 }
 
@@ -460,8 +465,8 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
   int dev = 0;
   PF_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 16) return qmk_internal::report(QMK_ERR_CUDA, "device index out of range");
-  std::lock_guard<std::mutex> lock(g_ws_mu);
-  Workspace &w = g_ws[dev];
+  std::lock_guard<std::mutex> lock(g_ws_decode_mu);
+  Workspace &w = g_ws_decode[dev];
   rc = ensure_workspace(w);
   if (rc == QMK_OK) rc = ensure_weight_maps(w, layer_weights, num_layers, stream);
   if (rc == QMK_OK) rc = ensure_decode_workspace(w, lm_head_weight, env.vocab);
@@ -487,8 +492,7 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
       if (rc == QMK_OK) rc = qmk_tc::make_map_f16(&w.map_attn_b, w.attn, rows, QS, qmk_gemm::BM, &err);
       if (rc == QMK_OK) rc = qmk_tc::make_map_f16(&w.map_act_b, w.act, rows, I, qmk_gemm::BM, &err);
       if (rc != QMK_OK) return qmk_internal::report(rc, err);
-      w.a_rows = rows;
-      w.step_key[0] = 0;   // a captured step holds the old maps
+      w.a_rows = rows;   // (graphs captured earlier keep their own copies of the maps they were captured with)
     }
   }
   const int M = qmk_gemm::BM;   // one tile of rows; rows >= B are computed and ignored
@@ -558,31 +562,31 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
     // One step costs about 400 launches: capture it once as a CUDA graph (kept while nothing it bakes in
     // changes) and replay it num_steps times.
     const unsigned long long key[12] = {
-        1ull, static_cast<unsigned long long>(B), static_cast<unsigned long long>(num_layers),
+        w.graph_epoch, static_cast<unsigned long long>(B), static_cast<unsigned long long>(num_layers),
         static_cast<unsigned long long>(max_seq_len), static_cast<unsigned long long>(env.vocab),
         static_cast<unsigned long long>(__float_as_uint_host(attn_scale)), reinterpret_cast<unsigned long long>(embed_weight),
         reinterpret_cast<unsigned long long>(final_norm_weight), reinterpret_cast<unsigned long long>(lm_head_weight),
         reinterpret_cast<unsigned long long>(rope), reinterpret_cast<unsigned long long>(cos_table),
         reinterpret_cast<unsigned long long>(sin_table) ^ (static_cast<unsigned long long>(env.timeout_ms) << 48)};
-    if (memcmp(key, w.step_key, sizeof(key)) != 0) {
-      if (w.step_graph) { cudaGraphExecDestroy(w.step_graph); w.step_graph = nullptr; }
-      w.step_key[0] = 0;
+    if (memcmp(key, w.step_key[B], sizeof(key)) != 0) {
+      if (w.step_graph[B]) { cudaGraphExecDestroy(w.step_graph[B]); w.step_graph[B] = nullptr; }
+      w.step_key[B][0] = 0;
       cudaGraph_t graph = nullptr;
       PF_CUDA(cudaStreamBeginCapture(w.gstream, cudaStreamCaptureModeThreadLocal));
       rc = enqueue_step(w.gstream);
       cudaError_t ce = cudaStreamEndCapture(w.gstream, &graph);   // always end the capture, also after an error
       if (rc == QMK_OK && ce != cudaSuccess) { rc = QMK_ERR_CUDA; err = std::string("graph capture: ") + cudaGetErrorString(ce); }
       if (rc == QMK_OK) {
-        ce = cudaGraphInstantiate(&w.step_graph, graph, 0);
+        ce = cudaGraphInstantiate(&w.step_graph[B], graph, 0);
         if (ce != cudaSuccess) { rc = QMK_ERR_CUDA; err = std::string("cudaGraphInstantiate: ") + cudaGetErrorString(ce); }
       }
       if (graph) cudaGraphDestroy(graph);
-      if (rc == QMK_OK) memcpy(w.step_key, key, sizeof(key));
+      if (rc == QMK_OK) memcpy(w.step_key[B], key, sizeof(key));
     }
     if (rc == QMK_OK) {
       PF_CUDA(cudaEventRecord(w.ev_in, stream));          // the graph stream starts after the caller's stream
       PF_CUDA(cudaStreamWaitEvent(w.gstream, w.ev_in, 0));
-      for (int step = 0; step < num_steps; ++step) PF_CUDA(cudaGraphLaunch(w.step_graph, w.gstream));
+      for (int step = 0; step < num_steps; ++step) PF_CUDA(cudaGraphLaunch(w.step_graph[B], w.gstream));
       PF_CUDA(cudaEventRecord(w.ev_out, w.gstream));
       PF_CUDA(cudaStreamWaitEvent(stream, w.ev_out, 0));  // ... and the caller's stream continues after it
     }

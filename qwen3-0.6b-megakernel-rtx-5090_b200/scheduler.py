@@ -14,6 +14,11 @@ benchmark configurations also name a continuous-batching mode.  This scheduler k
 The engine is any object with ``num_sequences``, ``max_seq_len``, ``prefill_slot(slot, ids)`` and
 ``decode_slots(slots, first_tokens, steps) -> list of token lists`` (``BatchDecoder`` provides them);
 tests drive the scheduler with a fake engine on the CPU.
+
+``overlap_prefill=True`` moves step 1 to its own thread: while a decode launch of the live sequences runs, the
+next waiting request is prefilled into a free slot (the engine must allow ``prefill_slot`` of one slot to run
+concurrently with ``decode_slots`` of others; ``BatchDecoder`` with the tensor-core engines does, on separate
+CUDA streams and workspaces).  A slot joins the next decode round after its prefill has finished.
 """
 
 from __future__ import annotations
@@ -46,10 +51,13 @@ class Result:
 
 
 class ContinuousBatcher:
-    def __init__(self, engine, eos_token_id: Optional[int] = None, quantum: int = 16):
+    def __init__(self, engine, eos_token_id: Optional[int] = None, quantum: int = 16, overlap_prefill: bool = False):
         if quantum < 1:
             raise ValueError("quantum must be >= 1")
         self.engine = engine
+        self.overlap_prefill = bool(overlap_prefill)
+        self._prefilling = 0                          # requests taken from the queue whose prefill is running
+        self._admit_thread: Optional[threading.Thread] = None
         self.eos = -1 if eos_token_id is None else int(eos_token_id)
         self.quantum = int(quantum)
         self.num_slots = int(engine.num_sequences)
@@ -61,6 +69,7 @@ class ContinuousBatcher:
         self._next_id = 0
         self._thread: Optional[threading.Thread] = None
         self._stop = False
+        self._admit_stop = False
         # counters for tests and reports
         self.launches = 0
         self.decoded_tokens = 0        # tokens produced by launches, including ones cut after EOS
@@ -89,29 +98,41 @@ class ContinuousBatcher:
 
     # ------------------------------------------------------------------ one scheduling round
     def _admit(self) -> None:
+        """Prefills waiting requests into free slots until one of the two runs out."""
         while True:
-            with self._lock:
+            with self._wake:
                 if not self._waiting or not self._free:
                     return
                 req = self._waiting.popleft()
                 slot = self._free.pop(0)
+                self._prefilling += 1
             try:
                 self.engine.prefill_slot(slot, req.prompt_ids[:-1])
             except Exception as exc:           # a bad prompt fails its own request only
-                with self._lock:
+                with self._wake:
                     self._free.append(slot)
                     self._free.sort()
+                    self._prefilling -= 1
+                    self._wake.notify_all()
                 req.future.set_exception(exc)
                 continue
             req.slot = slot
             req.next_token = req.prompt_ids[-1]
-            with self._lock:
+            with self._wake:
                 self._live[slot] = req
+                self._prefilling -= 1
                 self.max_live = max(self.max_live, len(self._live))
+                self._wake.notify_all()
 
     def step(self) -> bool:
         """One round (admit, launch, retire).  Returns False when there was nothing to do."""
-        self._admit()
+        if self.overlap_prefill:
+            self._ensure_admit_thread()
+            with self._wake:                   # nothing live yet but a prefill is on its way: wait for it
+                while not self._live and (self._prefilling or (self._waiting and self._free)):
+                    self._wake.wait(timeout=0.05)
+        else:
+            self._admit()
         with self._lock:
             live = [self._live[s] for s in sorted(self._live)]
         if not live:
@@ -143,17 +164,38 @@ class ContinuousBatcher:
             if finish is None:
                 r.next_token = int(toks[-1])
                 continue
-            with self._lock:
+            with self._wake:
                 del self._live[r.slot]
                 self._free.append(r.slot)
                 self._free.sort()
+                self._wake.notify_all()        # the admission thread may be waiting for a slot
             r.future.set_result(Result(r.rid, r.out, len(r.prompt_ids), finish))
         return True
 
+    # ------------------------------------------------------------------ overlapped admission
+    def _ensure_admit_thread(self) -> None:
+        if self._admit_thread is None or not self._admit_thread.is_alive():
+            self._admit_stop = False
+            self._admit_thread = threading.Thread(target=self._admit_loop, name="batcher-prefill", daemon=True)
+            self._admit_thread.start()
+
+    def _admit_loop(self) -> None:
+        while True:
+            self._admit()
+            with self._wake:
+                if self._admit_stop:
+                    return
+                if not (self._waiting and self._free):
+                    self._wake.wait(timeout=0.05)
+
     def run_until_idle(self) -> None:
-        """Synchronous driver: rounds until no request is waiting or live."""
-        while self.step():
-            pass
+        """Synchronous driver: rounds until no request is waiting, being prefilled or live."""
+        while True:
+            if self.step():
+                continue
+            with self._lock:
+                if not self._waiting and not self._live and not self._prefilling:
+                    return
 
     # ------------------------------------------------------------------ background driver
     def start(self) -> None:
@@ -170,6 +212,12 @@ class ContinuousBatcher:
         if self._thread is not None:
             self._thread.join()
             self._thread = None
+        if self._admit_thread is not None:
+            with self._wake:
+                self._admit_stop = True
+                self._wake.notify_all()
+            self._admit_thread.join()
+            self._admit_thread = None
 
     def _loop(self) -> None:
         while True:
@@ -177,8 +225,8 @@ class ContinuousBatcher:
                 with self._wake:
                     if self._stop:
                         return
-                    if not self._waiting and not self._live:
+                    if not self._waiting and not self._live and not self._prefilling:
                         self._wake.wait(timeout=0.5)
             with self._lock:
-                if self._stop and not self._waiting and not self._live:
+                if self._stop and not self._waiting and not self._live and not self._prefilling:
                     return

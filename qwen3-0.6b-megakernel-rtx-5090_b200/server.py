@@ -103,7 +103,8 @@ def create_app(decoder=None, model_name: Optional[str] = None, default_max_token
         if state["batcher"] is None and hasattr(dec, "decode_slots"):   # multi-sequence engine
             from scheduler import ContinuousBatcher
             eos = getattr(dec.tokenizer, "eos_token_id", None)
-            state["batcher"] = ContinuousBatcher(dec, eos_token_id=eos, quantum=int(os.getenv("BATCH_QUANTUM", "16")))
+            state["batcher"] = ContinuousBatcher(dec, eos_token_id=eos, quantum=int(os.getenv("BATCH_QUANTUM", "16")),
+                                                 overlap_prefill=getattr(dec, "supports_overlap", False))
             state["batcher"].start()
 
     @asynccontextmanager

@@ -172,3 +172,58 @@ def test_random_workloads_property():
         assert all(p <= 64 for p in eng.positions)
 
     run()
+
+
+def test_overlapped_admission_gives_the_same_answers():
+    """Prefill on its own thread: same tokens per request, slot limit respected, everything resolves; the fake
+    engine's prefill sleeps so that decode rounds really run while a prefill is in flight."""
+    import time
+
+    class SlowPrefill(FakeEngine):
+        def __init__(self, *a, **k):
+            super().__init__(*a, **k)
+            self.concurrent = 0
+
+        def prefill_slot(self, b, ids):
+            time.sleep(0.004)
+            super().prefill_slot(b, ids)
+
+        def decode_slots(self, slots, firsts, steps):
+            time.sleep(0.001)
+            return super().decode_slots(slots, firsts, steps)
+
+    eng = SlowPrefill(num_sequences=3)
+    sch = ContinuousBatcher(eng, eos_token_id=None, quantum=4, overlap_prefill=True)
+    reqs = [(S.make_prompt(1 + (i * 5) % 11, seed=i, vocab_size=97), 2 + (i * 7) % 19) for i in range(14)]
+    futs = [sch.submit(ids, n) for ids, n in reqs]
+    sch.run_until_idle()
+    sch.stop()
+    for (ids, n), f in zip(reqs, futs):
+        assert f.result(timeout=0).tokens == FakeEngine.reference(ids, n)[0]
+    assert sch.max_live <= 3 and all(len(s) <= 3 for s, _ in eng.launch_log)
+    # decode rounds with fewer than all slots live happened while later prefills were still running
+    assert any(len(s) < 3 for s, _ in eng.launch_log[:5])
+
+
+@pytest.mark.gpu
+def test_gpu_overlapped_prefill_matches_serial_scheduling(built_library, tiny_cfg):
+    """Tensor-core engines, 8 slots: prefill of the next request on its own stream and thread while the live
+    ones decode.  A sequence's tokens do not depend on who shares its launches, so both schedules must agree."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from Model.Qwen06B_architecture import BatchDecoder
+    vocab = 2048
+    w = S.weights_to(S.make_weights(seed=5, num_layers=2, vocab_size=vocab, norm_std=0.1, max_seq_len=16), "cuda")
+    tok = S.StubTokenizer(-1, vocab)
+    reqs = [(S.make_prompt(3 + (i * 37) % 300, seed=200 + i, vocab_size=vocab), 4 + (i * 5) % 23) for i in range(20)]
+    outs = []
+    for overlap in (False, True):
+        eng = BatchDecoder(weights=w, tokenizer=tok, num_sequences=8, max_seq_len=384, engine="gemm", prefill_mode="tensor")
+        assert eng.supports_overlap
+        sch = ContinuousBatcher(eng, eos_token_id=None, quantum=8, overlap_prefill=overlap)
+        futs = [sch.submit(ids, n) for ids, n in reqs]
+        sch.run_until_idle()
+        sch.stop()
+        outs.append([f.result(timeout=0).tokens for f in futs])
+        assert all(len(t) == n for t, (_, n) in zip(outs[-1], reqs))
+    assert outs[0] == outs[1]
