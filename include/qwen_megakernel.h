@@ -215,14 +215,14 @@ int qmk_generate_static(
     int *output_log, int num_layers, int start_position, int max_seq_len,
     float attn_scale, int eos_token_id, cudaStream_t stream);
 
-/* qmk_prefill on the tensor cores: the prompt is processed in chunks of up to 512 tokens; per layer the
+/* qmk_prefill on the tensor cores: the prompt is processed in chunks of up to 2048 tokens; per layer the
  * seven projections run as tcgen05 GEMMs over the whole chunk (weights are read once per chunk instead
  * of once per token, megakernel_5090.cu:1324-1350), with row-wise kernels for RMSNorm, per-head QK-norm +
  * RoPE + cache write, causal attention over the cache, and SwiGLU between them.  Same arguments, cache
  * layout, position rule and blocking behaviour as qmk_prefill; fp16 weights only (with FP8 weights
  * selected it returns QMK_ERR_BAD_ARGUMENT: use qmk_prefill).  GEMM operands are rounded to fp16 (the
  * decode kernel keeps fp32 activations), so cache rows agree with qmk_prefill's to fp16 rounding, not
- * bit for bit.  Scratch (about 40 MB) is allocated on the first call per device. */
+ * bit for bit.  Scratch (about 160 MB) is allocated on the first call per device. */
 int qmk_prefill_chunked(
     const int *token_ids_host, int num_tokens, const void *embed_weight,
     const struct LDGLayerWeight *layer_weights, const void *cos_table, const void *sin_table,

@@ -191,7 +191,7 @@ int launch_gemm(const CUtensorMap &map_a, const CUtensorMap &map_b, float *C, in
 // ----------------------------------------------------------------------------- chunked prefill
 namespace {
 
-constexpr int CHUNK = 512;          // prompt tokens per pass over the weights (a multiple of the GEMM's 128)
+constexpr int CHUNK = 2048;         // prompt tokens per pass over the weights (a multiple of the GEMM's 128)
 constexpr int MAX_LAYERS = 48;
 
 struct Workspace {                  // per device, allocated on first use, never freed (like the engine's scratch)
@@ -237,10 +237,11 @@ std::mutex g_ws_mu, g_ws_decode_mu;
       return qmk_internal::report(QMK_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(err__)); \
   } while (0)
 
-int ensure_workspace(Workspace &w) {
+// `rows`: activation rows the buffers hold (CHUNK for prefill, one 128-row tile for the batched decode)
+int ensure_workspace(Workspace &w, int rows) {
   if (w.ready) return QMK_OK;
   using namespace qmk_pf;
-  const size_t C = CHUNK;
+  const size_t C = static_cast<size_t>(rows);
   PF_CUDA(cudaMalloc(&w.tokens, sizeof(int) * C));
   PF_CUDA(cudaMalloc(&w.x, sizeof(float) * C * H));
   PF_CUDA(cudaMalloc(&w.q, sizeof(float) * C * QS));
@@ -323,7 +324,7 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
   if (dev < 0 || dev >= 16) return qmk_internal::report(QMK_ERR_CUDA, "device index out of range");
   std::lock_guard<std::mutex> lock(g_ws_mu);
   Workspace &w = g_ws[dev];
-  rc = ensure_workspace(w);
+  rc = ensure_workspace(w, CHUNK);
   if (rc == QMK_OK) rc = ensure_weight_maps(w, layer_weights, num_layers, stream);
   if (rc != QMK_OK) return rc;
   std::vector<unsigned long long> rec(w.table, w.table + static_cast<size_t>(num_layers) * 12);
@@ -467,7 +468,7 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
   if (dev < 0 || dev >= 16) return qmk_internal::report(QMK_ERR_CUDA, "device index out of range");
   std::lock_guard<std::mutex> lock(g_ws_decode_mu);
   Workspace &w = g_ws_decode[dev];
-  rc = ensure_workspace(w);
+  rc = ensure_workspace(w, 512);   // room for the split-K partial matrices (up to 3 x 128 rows)
   if (rc == QMK_OK) rc = ensure_weight_maps(w, layer_weights, num_layers, stream);
   if (rc == QMK_OK) rc = ensure_decode_workspace(w, lm_head_weight, env.vocab);
   if (rc != QMK_OK) return rc;

@@ -30,10 +30,11 @@ def _engine(w, max_seq_len, mode, **kw):
                    verbose=False, max_seq_len=max_seq_len, prefill_mode=mode, **kw)
 
 
-@pytest.mark.parametrize("n_prompt", [1, 37, 128, 700])
+@pytest.mark.parametrize("n_prompt", [1, 37, 128, 700, 2300])
 def test_cache_and_next_tokens_match_oracle(C, n_prompt):
-    """Prompt lengths below a tile, one tile exactly, and two chunks (512 + 187) with a ragged tail."""
-    vocab, steps, L = 2048, 4, 768
+    """Prompt lengths below a tile, one tile exactly, several tiles with a ragged tail, and two chunks
+    (2048 + 252)."""
+    vocab, steps, L = 2048, 4, 2560
     w = S.make_weights(seed=12, num_layers=3, vocab_size=vocab, norm_std=0.1, max_seq_len=16)
     ids = S.make_prompt(n_prompt + 1, seed=n_prompt, vocab_size=vocab)
     o = OracleDecoder(w, max_seq_len=L)
