@@ -120,115 +120,8 @@ __global__ void qk_norm_rope_cache(const float *q, const float *k, const float *
   }
 }
 
-// Causal attention of the chunk's queries over cache rows [0, pos0 + t] (the chunk's own rows are already
-// in the cache).  grid = (ceil(T / 16), 8 kv heads), block = 256 = 8 warps.  A CTA takes 16 query tokens x the
-// two query heads of its kv head; a warp takes 2 tokens and works on both heads of a token together (they
-// share every K and V row).  Query tiles are handed out last-first: the longest ones start first.  Keys go through shared memory in tiles of 32: lane j scores key j, and every
-// lane owns 4 of the 128 output dims.  Online softmax in fp32, base-2 exponent.
-constexpr int ATT_Q = 16, ATT_KEYS = 32;
-constexpr int ATT_KPITCH = D + 2;   // halves per K row in shared memory: an odd number of 32-bit words
-__global__ void __launch_bounds__(256) causal_attention(const float *qr, const __half *k_cache_layer,
-                                                        const __half *v_cache_layer, __half *out, int T, int pos0,
-                                                        int max_seq_len, float scale) {
-  __shared__ __align__(16) __half sk[ATT_KEYS * ATT_KPITCH];
-  __shared__ __align__(16) __half sv[ATT_KEYS * D];
-  __shared__ __align__(16) float sq[ATT_Q * 2 * D];   // [token][head-in-pair][128]
-  __shared__ float sp[8][2][ATT_KEYS];                 // probabilities of the two heads, per warp
-  const int g = blockIdx.y, t0 = (gridDim.x - 1 - blockIdx.x) * ATT_Q;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nq = min(ATT_Q, T - t0);
-  for (int i = threadIdx.x; i < ATT_Q * 2 * D; i += 256) {
-    const int tk = i / (2 * D), h = (i / D) & 1, d = i % D, tok = t0 + tk;
-    sq[i] = (tok < T) ? qr[(static_cast<size_t>(tok) * NQ + 2 * g + h) * D + d] : 0.f;
-  }
-  const float sc = scale * 1.4426950408889634f;
-  constexpr int TPW = 2;   // tokens per warp
-  float m[TPW][2], l[TPW][2], acc[TPW][2][4];
-#pragma unroll
-  for (int r = 0; r < TPW; ++r)
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      m[r][h] = -INFINITY; l[r][h] = 0.f;
-#pragma unroll
-      for (int d = 0; d < 4; ++d) acc[r][h][d] = 0.f;
-    }
-  const int last_key = pos0 + t0 + nq - 1;   // highest key any query of this CTA may see
-  const __half *kbase = k_cache_layer + static_cast<size_t>(g) * max_seq_len * D;
-  const __half *vbase = v_cache_layer + static_cast<size_t>(g) * max_seq_len * D;
-  for (int k0 = 0; k0 <= last_key; k0 += ATT_KEYS) {
-    __syncthreads();   // previous tile fully used (also orders the sq fill before the first use)
-    for (int i = threadIdx.x; i < ATT_KEYS * (D / 8); i += 256) {
-      const int j = i / (D / 8), c = i % (D / 8);
-      uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
-      if (k0 + j <= last_key) {
-        kv = *reinterpret_cast<const uint4 *>(kbase + static_cast<size_t>(k0 + j) * D + c * 8);
-        vv = *reinterpret_cast<const uint4 *>(vbase + static_cast<size_t>(k0 + j) * D + c * 8);
-      }
-      uint32_t *kd = reinterpret_cast<uint32_t *>(sk + j * ATT_KPITCH + c * 8);
-      kd[0] = kv.x; kd[1] = kv.y; kd[2] = kv.z; kd[3] = kv.w;
-      *reinterpret_cast<uint4 *>(sv + j * D + c * 8) = vv;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int r = 0; r < TPW; ++r) {
-      const int tk = warp * TPW + r, tok = t0 + tk;
-      if (tok >= T) continue;                       // warp-uniform
-      const int limit = pos0 + tok;                 // last visible key of this query token
-      if (k0 > limit) continue;                     // warp-uniform
-      const float2 *qa = reinterpret_cast<const float2 *>(sq + (tk * 2 + 0) * D);
-      const float2 *qb = reinterpret_cast<const float2 *>(sq + (tk * 2 + 1) * D);
-      const __half2 *krow = reinterpret_cast<const __half2 *>(sk + lane * ATT_KPITCH);
-      float sa = 0.f, sb = 0.f;
-#pragma unroll 16
-      for (int d = 0; d < D / 2; ++d) {
-        const float2 kf = __half22float2(krow[d]);
-        const float2 a = qa[d], b = qb[d];
-        sa = fmaf(a.x, kf.x, sa); sa = fmaf(a.y, kf.y, sa);
-        sb = fmaf(b.x, kf.x, sb); sb = fmaf(b.y, kf.y, sb);
-      }
-      const bool vis = (k0 + lane <= limit);
-      sa = vis ? sa * sc : -INFINITY;
-      sb = vis ? sb * sc : -INFINITY;
-      const float ma = fmaxf(m[r][0], warp_max(sa)), mb = fmaxf(m[r][1], warp_max(sb));
-      const float ca = exp2f(m[r][0] - ma), cb = exp2f(m[r][1] - mb);   // first tile: exp2f(-inf) = 0
-      const float pa = exp2f(sa - ma), pb = exp2f(sb - mb);
-      l[r][0] = l[r][0] * ca + warp_sum(pa);
-      l[r][1] = l[r][1] * cb + warp_sum(pb);
-      m[r][0] = ma; m[r][1] = mb;
-      __syncwarp();
-      sp[warp][0][lane] = pa;
-      sp[warp][1][lane] = pb;
-      __syncwarp();
-#pragma unroll
-      for (int d = 0; d < 4; ++d) { acc[r][0][d] *= ca; acc[r][1][d] *= cb; }
-#pragma unroll 8
-      for (int j = 0; j < ATT_KEYS; ++j) {
-        const float pja = sp[warp][0][j], pjb = sp[warp][1][j];
-        const uint2 vv = *reinterpret_cast<const uint2 *>(sv + j * D + lane * 4);
-        const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&vv.x));
-        const float2 v23 = __half22float2(*reinterpret_cast<const __half2 *>(&vv.y));
-        acc[r][0][0] = fmaf(pja, v01.x, acc[r][0][0]); acc[r][0][1] = fmaf(pja, v01.y, acc[r][0][1]);
-        acc[r][0][2] = fmaf(pja, v23.x, acc[r][0][2]); acc[r][0][3] = fmaf(pja, v23.y, acc[r][0][3]);
-        acc[r][1][0] = fmaf(pjb, v01.x, acc[r][1][0]); acc[r][1][1] = fmaf(pjb, v01.y, acc[r][1][1]);
-        acc[r][1][2] = fmaf(pjb, v23.x, acc[r][1][2]); acc[r][1][3] = fmaf(pjb, v23.y, acc[r][1][3]);
-      }
-    }
-  }
-#pragma unroll
-  for (int r = 0; r < TPW; ++r) {
-    const int tok = t0 + warp * TPW + r;
-    if (tok >= T) continue;
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const float inv = 1.0f / l[r][h];
-      __half *dst = out + static_cast<size_t>(tok) * QS + (2 * g + h) * D + lane * 4;
-      *reinterpret_cast<__half2 *>(dst) = __floats2half2_rn(acc[r][h][0] * inv, acc[r][h][1] * inv);
-      *reinterpret_cast<__half2 *>(dst + 2) = __floats2half2_rn(acc[r][h][2] * inv, acc[r][h][3] * inv);
-    }
-  }
-}
-
-// Tensor-core version of causal_attention (mma.sync m16n8k16, fp16 operands, fp32 accumulate and softmax).
+// Causal attention of the chunk's queries over cache rows [0, pos0 + t] (the chunk's own rows are already in the
+// cache), on the tensor cores: mma.sync m16n8k16, fp16 operands, fp32 accumulate and softmax.
 // grid = (ceil(T / 32), 8 kv heads), block = 128 = 4 warps.  A CTA takes 32 query tokens x the two query heads
 // of its kv head; warp w works on head (w & 1) and tokens t0 + 16 * (w >> 1) + 0..15 (one 16-row MMA tile).
 // Keys go through shared memory in tiles of 64 rows of K and of V (row pitch 272 bytes: conflict-free for the
