@@ -223,6 +223,7 @@ struct SegTab {
   int nrows[NKIND][3];
   int out0[NKIND][3];    // index of the first output element
   int e0, e1;            // attention outputs this CTA merges when KV is split
+  int long_phase;        // some projection phase (QKV .. down) has more chunks here than the ring has slots
 };
 constexpr size_t SMEM_BYTES = OFF_SEGS + ((sizeof(SegTab) + 63) / 64) * 64;
 static_assert((I + CONS_THREADS - 1) / CONS_THREADS <= 8, "poll_vec handles at most 8 words per thread");
@@ -353,8 +354,11 @@ __device__ __forceinline__ bool mbar_wait(const Params &P, const Ctx &c, uint64_
 // says "complete".  So the wait first makes sure the producer has issued chunk `idx` (flags()[6] counts
 // issued chunks): from then on the slot's barrier is in use n and the parity is unambiguous.  Warps
 // that jump ahead in the ring (a group skipping another sequence's cache rows) depend on this.
+// Only the multi-sequence build needs the counter.  The single-sequence kernel's warps never skip chunks: a
+// phase with more chunks than ring slots is walked in passes with a CTA barrier between them (see pass_gate),
+// which orders the previous use of every slot before the wait, and its hot loops stay free of the check.
 #ifndef QMK_ISSUED_CHECK
-#define QMK_ISSUED_CHECK 1
+#define QMK_ISSUED_CHECK (QMK_MAX_SEQ > 1)
 #endif
 #ifndef QMK_ISSUED_FENCE
 #define QMK_ISSUED_FENCE 1
@@ -389,7 +393,7 @@ __device__ __forceinline__ bool wait_full(const Params &P, const Ctx &c, uint32_
 }
 
 // Rows [r0, r1) of an n-row matrix owned by CTA `cta` of `ncta` (launch-time only: 64-bit divisions).
-__device__ __forceinline__ void split_rows(int n, int ncta, int cta, int &r0, int &r1) {
+__host__ __device__ __forceinline__ void split_rows(int n, int ncta, int cta, int &r0, int &r1) {
   r0 = static_cast<int>((static_cast<long long>(n) * cta) / ncta);
   r1 = static_cast<int>((static_cast<long long>(n) * (cta + 1)) / ncta);
 }
@@ -401,10 +405,10 @@ constexpr int FP8_TRAILER = 16;
 __device__ __forceinline__ constexpr int kind_row_bytes(int kind, int wfmt) {
   return wfmt ? kind_k(kind) + FP8_TRAILER : kind_k(kind) * 2;
 }
-__device__ __forceinline__ constexpr int kind_rpc(int kind) { return (kind == K_QKV || kind == K_LM) ? 4 : kind == K_DOWN ? 1 : 2; }
+__host__ __device__ __forceinline__ constexpr int kind_rpc(int kind) { return (kind == K_QKV || kind == K_LM) ? 4 : kind == K_DOWN ? 1 : 2; }
 
 // Thread 0, once per launch.
-__device__ void build_segtab(SegTab *t, int cta, int ncta, int vocab) {
+__host__ __device__ inline void build_segtab(SegTab *t, int cta, int ncta, int vocab) {
   int r0, r1;
   for (int k = 0; k < NKIND; ++k) t->nseg[k] = 0;
   split_rows(QKV_ROWS, ncta, cta, r0, r1);
@@ -423,6 +427,13 @@ __device__ void build_segtab(SegTab *t, int cta, int ncta, int vocab) {
     if (r0 < r1) { t->nseg[k] = 1; t->tsel[k][0] = rec[k]; t->row0[k][0] = r0; t->nrows[k][0] = r1 - r0; t->out0[k][0] = r0; }
   }
   split_rows(QS, ncta, cta, t->e0, t->e1);
+  t->long_phase = 0;
+  for (int k = K_QKV; k <= K_DOWN; ++k) {
+    const int rpc = kind_rpc(k);
+    int chunks = 0;
+    for (int s = 0; s < t->nseg[k]; ++s) chunks += (t->nrows[k][s] + rpc - 1) / rpc;
+    if (chunks > NSLOTS) t->long_phase = 1;
+  }
 }
 
 // Weight rows of segment s of phase `kind` (layer record `rec` in shared memory, or the LM head).
@@ -723,10 +734,12 @@ __device__ __forceinline__ void norm_to_regs(const Ctx &c, const float *x, float
 // K = 1024 phases (fused QKV, gate/up, LM head): RMSNorm of x into registers, then this CTA's rows.
 // One shared non-inlined copy (runtime `kind`); returns the advanced chunk counter.  For K_LM each warp
 // leaves its running (max, argmax) in s_misc[32 + warp] / s_misc[48 + warp].
+// GATED: see the comment at the waits below; the barrier inside the pass loop costs ~2.5 % of a decode step
+// even when it is never taken, hence a separate copy (and kernel entry point) for grids that need it.
+template <bool GATED>
 __device__ __noinline__ uint32_t gemv_k1024(const Params &P, Ctx c, int kind, const float *x, float ss,
                                             const __half *norm_w, unsigned long long *out, uint32_t tag, float *dump) {
   const int wfmt = P.wfmt;
-  uint32_t seen = 0;   // issued-chunk counter cache (chunk_wait)
   float a[32];
   norm_to_regs(c, x, ss, norm_w, a);
   if (kind == K_LM && c.cta == 0 && c.warp == 0 && (P.normalized_out || P.hidden_out)) {  // reference-signature outputs
@@ -747,15 +760,15 @@ __device__ __noinline__ uint32_t gemv_k1024(const Params &P, Ctx c, int kind, co
   float best = -INFINITY;
   int best_i = 0x7fffffff;
   const int n = t->nseg[kind];
-  // The issued-chunk check of chunk_wait can be skipped when the slot's previous use (NSLOTS chunks back) is
-  // known to have landed: (a) the phase has at most NSLOTS chunks on this CTA, so that use belongs to an
-  // earlier phase, which every warp finished before the barrier that opened this one; (b) LM head: one
-  // segment, NB * G = 9 chunks per pass and NSLOTS = 2 * 9 + G, so that use is a chunk this very warp
-  // consumed two passes ago.  Reduced grids (more chunks per phase) take the checked wait.
+  // A parity wait is exact only when the slot's previous use (NSLOTS chunks back) has landed: (a) the phase
+  // has at most NSLOTS chunks on this CTA, so that use belongs to an earlier phase, which every warp finished
+  // before the barrier that opened this one; (b) LM head: one segment, NB * G = 9 chunks per pass and
+  // NSLOTS = 2 * 9 + G, so that use is a chunk this very warp consumed two passes ago; (c) otherwise
+  // (GATED: reduced grids, where some phase is longer than the ring) a barrier after every pass: a pass
+  // has fewer chunks than the ring, so that use lies in an earlier pass.
   static_assert(NSLOTS == 21 && NB * (CONS_WARPS >> 2) == 9, "case (b) above is written for these values");
-  int phase_chunks = 0;
-  for (int s = 0; s < n; ++s) phase_chunks += (t->nrows[kind][s] + RPC - 1) >> rsh;
-  const bool plain_wait = (kind == K_LM) || phase_chunks <= NSLOTS;
+  static_assert(NB * (CONS_WARPS >> 1) <= NSLOTS, "case (c): a pass must fit the ring");
+  const bool pass_gate = GATED && kind != K_LM;
   for (int s = 0; s < n; ++s) {
     const int nrows = t->nrows[kind][s];
     const int out0 = t->out0[kind][s];
@@ -772,8 +785,7 @@ __device__ __noinline__ uint32_t gemv_k1024(const Params &P, Ctx c, int kind, co
         valid[b] = ch < nchunks && ((ch << rsh) + sub) < nrows;          // warp-uniform
         if (valid[b]) {
           const uint32_t idx = c.chunk + static_cast<uint32_t>(ch);
-          ok &= plain_wait ? mbar_wait(P, c, c.full(idx % NSLOTS), (idx / NSLOTS) & 1u, WHERE_FULL, false)
-                           : chunk_wait(P, c, idx, seen);
+          ok &= mbar_wait(P, c, c.full(idx % NSLOTS), (idx / NSLOTS) & 1u, WHERE_FULL, false);
         }
       }
       ok = __all_sync(0xffffffffu, ok);   // the whole warp takes the same branch (shuffles follow)
@@ -816,6 +828,7 @@ __device__ __noinline__ uint32_t gemv_k1024(const Params &P, Ctx c, int kind, co
           ll_publish(out + o, r, tag, c.repl);                      // one store instruction covers the NB rows
         }
       }
+      if (pass_gate) cons_sync();
     }
     c.chunk += static_cast<uint32_t>(nchunks);
   }
@@ -833,16 +846,19 @@ __device__ __noinline__ uint32_t gemv_k1024(const Params &P, Ctx c, int kind, co
 
 // O (K = 2048) and down (K = 3072) projections: out[row] = W.act + resid[row], activations and residual
 // in shared memory.  One shared non-inlined copy; returns the advanced chunk counter.
+template <bool GATED>
 __device__ __noinline__ uint32_t gemv_wide(const Params &P, Ctx c, int kind, const float *act, const float *resid,
                                            unsigned long long *out, uint32_t tag) {
   const int rsh = kind == K_O ? 1 : 0;
   const int wfmt = P.wfmt;
-  uint32_t seen = 0;   // issued-chunk counter cache (chunk_wait)
   const int RPC = 1 << rsh, G = CONS_WARPS >> rsh, K = kind == K_O ? QS : I, rb = kind_row_bytes(kind, wfmt);
   const int kiters = K / 256;    // 256 weights per warp pass: 8 or 12
   const SegTab *t = c.segs();
   const int sub = c.warp & (RPC - 1), wch = c.warp >> rsh;
   const int n = t->nseg[kind];
+  // plain parity waits; GATED (some phase longer than the ring) puts a barrier after every pass of G chunks,
+  // see gemv_k1024
+  constexpr bool pass_gate = GATED;
   for (int s = 0; s < n; ++s) {
     const int nrows = t->nrows[kind][s];
     const int out0 = t->out0[kind][s];
@@ -855,7 +871,7 @@ __device__ __noinline__ uint32_t gemv_wide(const Params &P, Ctx c, int kind, con
       bool have = false;
       if (ch < nchunks && row < nrows) {            // warp-uniform
         const uint32_t idx = c.chunk + static_cast<uint32_t>(ch);
-        if (wait_full(P, c, idx, seen)) {
+        if (__all_sync(0xffffffffu, mbar_wait(P, c, c.full(idx % NSLOTS), (idx / NSLOTS) & 1u, WHERE_FULL, false))) {
           const unsigned char *wrow = c.slot(idx) + sub * rb;
           float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
@@ -883,6 +899,7 @@ __device__ __noinline__ uint32_t gemv_wide(const Params &P, Ctx c, int kind, con
         const float r = warp_sum(part) + resid[o];
         if (c.lane == 0) ll_publish(out + o, r, tag, c.repl);
       }
+      if (pass_gate) cons_sync();
     }
     c.chunk += static_cast<uint32_t>(nchunks);
   }
@@ -896,7 +913,6 @@ __device__ __noinline__ uint32_t gemv_wide(const Params &P, Ctx c, int kind, con
 __device__ __noinline__ uint32_t attention_phase(const Params &P, Ctx c, const __half *nv, int layer, int pos,
                                                  uint32_t tag) {
   const AttnItem it = attn_item(P, c, 0, 1, CONS_WARPS, pos);
-  uint32_t seen = 0;   // issued-chunk counter cache (chunk_wait)
   float *s_q = c.f(F_Q), *s_knew = c.f(F_KNEW), *s_vnew = c.f(F_VNEW), *s_wpart = c.f(F_WPART), *s_misc = c.f(F_MISC);
   const float *s_cs = c.f(F_CS);
   const unsigned long long *qkv = c.llr + LL_QKV;
@@ -972,12 +988,20 @@ __device__ __noinline__ uint32_t attention_phase(const Params &P, Ctx c, const _
   // only the 16 lanes of the group.
   const uint32_t grp_mask = 0xffffu << (grp * 16);
   // Old rows arrive through the ring in chunks of 16 K rows + 16 V rows; warp w takes chunks
-  // w, w + CONS_WARPS, ... and hands each slot back when done.
+  // w, w + CONS_WARPS, ... and hands each slot back when done.  Plain parity waits: an item with more chunks
+  // than ring slots (more than 336 rows: contexts past 6000 tokens, or reduced grids) puts a barrier after
+  // every pass of CONS_WARPS chunks, see gemv_k1024.
+  const bool pass_gate = it.nchunks > NSLOTS;
 #pragma unroll 1
-  for (int j = c.warp; j < it.nchunks; j += CONS_WARPS) {
+  for (int j0 = 0; j0 < it.nchunks; j0 += CONS_WARPS) {
+    const int j = j0 + c.warp;
+    if (j >= it.nchunks) {
+      if (pass_gate) cons_sync();
+      continue;
+    }
     const uint32_t idx = c.chunk + static_cast<uint32_t>(j);
     const int nrow = min(it.rpc, (p1 - p0) - j * it.rpc);
-    if (wait_full(P, c, idx, seen)) {
+    if (__all_sync(0xffffffffu, mbar_wait(P, c, c.full(idx % NSLOTS), (idx / NSLOTS) & 1u, WHERE_FULL, false))) {
       const unsigned char *kslot = c.slot(idx) + seg * 16;
 #pragma unroll 2
       for (int r = grp; r < nrow; r += 2) {
@@ -1010,6 +1034,7 @@ __device__ __noinline__ uint32_t attention_phase(const Params &P, Ctx c, const _
     }
     __syncwarp();
     if (c.lane == 0) mbar_arrive_n(c.empty(idx % NSLOTS), EMPTY_UNITS);
+    if (pass_gate) cons_sync();
   }
   c.chunk += static_cast<uint32_t>(it.nchunks);
   // (3) merge the 2 row groups of the warp (rows differ, dims match for equal `seg`)
@@ -1107,7 +1132,10 @@ __device__ __noinline__ void attention_merge(const Params &P, const Ctx c, int S
       P.prof[static_cast<size_t>(c.cta) * PROF_STRIDE + (slot)] = now_ns();                       \
   } while (0)
 
-__global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __grid_constant__ Params P) {
+// GATED: the grid is so small (below ~74 CTAs) that a projection phase has more chunks on a CTA than the ring
+// has slots; the host picks the entry point with grid_has_long_phase().
+template <bool GATED>
+__device__ __forceinline__ void decode_body(const Params &P) {
   extern __shared__ __align__(128) unsigned char smem[];
   Ctx c;
   c.smem = smem;
@@ -1192,7 +1220,7 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
         mbar_wait(P, c, c.nfull(Lg & 1u), (Lg >> 1) & 1u, WHERE_FULL, false);
         // P1: input RMSNorm + fused QKV rows
         QMK_STAMP(layer * 12 + 0);
-        c.chunk = gemv_k1024(P, c, K_QKV, s_x, ss, nv + NB_IN_LN, P.ll + LL_QKV, tag, nullptr);
+        c.chunk = gemv_k1024<GATED>(P, c, K_QKV, s_x, ss, nv + NB_IN_LN, P.ll + LL_QKV, tag, nullptr);
         // P2/P3: attention work items, then merge of split partials
         QMK_STAMP(layer * 12 + 1);
         c.chunk = attention_phase(P, c, nv, layer, pos, tag);
@@ -1203,18 +1231,18 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
         poll_vec(P, c, c.llr + LL_ATTN, QS, tag, s_vec);
         QMK_STAMP(layer * 12 + 4);
         cons_sync();
-        c.chunk = gemv_wide(P, c, K_O, s_vec, s_x, P.ll + LL_X1, tag);
+        c.chunk = gemv_wide<GATED>(P, c, K_O, s_vec, s_x, P.ll + LL_X1, tag);
         // P5: post-attention RMSNorm + gate/up + SwiGLU
         QMK_STAMP(layer * 12 + 5);
         ss = poll_vec(P, c, c.llr + LL_X1, H, tag, s_x1);
         QMK_STAMP(layer * 12 + 6);
-        c.chunk = gemv_k1024(P, c, K_GU, s_x1, ss, nv + NB_POST_LN, P.ll + LL_INTER, tag, nullptr);
+        c.chunk = gemv_k1024<GATED>(P, c, K_GU, s_x1, ss, nv + NB_POST_LN, P.ll + LL_INTER, tag, nullptr);
         // P6: down-proj + residual
         QMK_STAMP(layer * 12 + 7);
         poll_vec(P, c, c.llr + LL_INTER, I, tag, s_vec);
         QMK_STAMP(layer * 12 + 8);
         cons_sync();
-        c.chunk = gemv_wide(P, c, K_DOWN, s_vec, s_x1, P.ll + LL_X2, tag);
+        c.chunk = gemv_wide<GATED>(P, c, K_DOWN, s_vec, s_x1, P.ll + LL_X2, tag);
         // next layer's input (in prefill mode the last layer's output is not needed)
         QMK_STAMP(layer * 12 + 9);
         if (!(P.prefill && layer == P.num_layers - 1)) ss = poll_vec(P, c, c.llr + LL_X2, H, tag, s_x);
@@ -1228,8 +1256,8 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
       }
       // final RMSNorm + tied LM head + argmax (megakernel_5090.cu:921-947, 1024-1167)
       QMK_STAMP(P.num_layers * 12 + 0);
-      c.chunk = gemv_k1024(P, c, K_LM, s_x, ss, P.final_norm, nullptr, 0u,
-                           P.logits_out ? P.logits_out + static_cast<size_t>(step) * P.vocab : nullptr);
+      c.chunk = gemv_k1024<false>(P, c, K_LM, s_x, ss, P.final_norm, nullptr, 0u,
+                                  P.logits_out ? P.logits_out + static_cast<size_t>(step) * P.vocab : nullptr);
       QMK_STAMP(P.num_layers * 12 + 1);
       cons_sync();
       const uint32_t atag = tag_base + 63u;
@@ -1304,6 +1332,22 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __gr
       }
     }
   }
+}
+
+__global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel(const __grid_constant__ Params P) {
+  decode_body<false>(P);
+}
+__global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel_small_grid(const __grid_constant__ Params P) {
+  decode_body<true>(P);
+}
+// Host side: which of the two a grid of `ncta` CTAs needs (the same row split the kernel computes).
+inline bool grid_has_long_phase(int ncta) {
+  SegTab t;
+  for (int cta = 0; cta < ncta; ++cta) {
+    build_segtab(&t, cta, ncta, 0);
+    if (t.long_phase) return true;
+  }
+  return false;
 }
 
 #endif  // QMK_MAX_SEQ == 1

@@ -170,6 +170,8 @@ int ensure_ready(Engine *e) {
   e->num_sms = prop.multiProcessorCount;
   QMK_CUDA(e, cudaFuncSetAttribute(qmk::qwen3_decode_megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(qmk::SMEM_BYTES)));
+  QMK_CUDA(e, cudaFuncSetAttribute(qmk::qwen3_decode_megakernel_small_grid, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(qmk::SMEM_BYTES)));
   QMK_CUDA(e, cudaFuncSetAttribute(qmk::wait_timeout_probe, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(qmk::SMEM_BYTES)));
   int per_sm = 0;
@@ -200,6 +202,16 @@ int grid_for(const Engine *e) {
   int g = e->grid;
   if (e->max_ctas > 0 && e->max_ctas < g) g = e->max_ctas;
   return g;
+}
+
+// Entry point of the single-sequence kernel for a grid of `grid` CTAs: small grids, where a projection phase
+// has more ring chunks on a CTA than the ring has slots, take the copy with a barrier between passes.
+const void *single_sequence_kernel(int grid) {
+  static signed char cache[qmk::MAX_CTAS + 1];   // 0 unknown, 1 plain, 2 small grid (a race stores the same value)
+  if (grid < 1 || grid > qmk::MAX_CTAS) grid = qmk::MAX_CTAS;
+  if (cache[grid] == 0) cache[grid] = qmk::grid_has_long_phase(grid) ? 2 : 1;
+  return cache[grid] == 2 ? reinterpret_cast<const void *>(qmk::qwen3_decode_megakernel_small_grid)
+                          : reinterpret_cast<const void *>(qmk::qwen3_decode_megakernel);
 }
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -282,8 +294,8 @@ int launch(Engine *e, Params &P, cudaStream_t stream, bool synchronize, bool bat
   cudaError_t err =
       batch ? cudaLaunchCooperativeKernel(qmk_batch::kernel(), dim3(grid), dim3(qmk_batch::threads()), args,
                                           qmk_batch::smem_bytes(), stream)
-            : cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(qmk::qwen3_decode_megakernel), dim3(grid),
-                                          dim3(qmk::THREADS), args, qmk::SMEM_BYTES, stream);
+            : cudaLaunchCooperativeKernel(single_sequence_kernel(grid), dim3(grid), dim3(qmk::THREADS), args,
+                                          qmk::SMEM_BYTES, stream);
   if (err == cudaErrorCooperativeLaunchTooLarge)
     return fail(e, QMK_ERR_NOT_RESIDENT, "persistent grid cannot be co-resident on this device");
   if (err != cudaSuccess) return fail(e, QMK_ERR_CUDA, std::string("cudaLaunchCooperativeKernel: ") + cudaGetErrorString(err));
@@ -643,6 +655,8 @@ int qmk_generate_static(int first_token_id, int num_steps, const void *embed_wei
     if (prop.major < 10) return fail(e, QMK_ERR_CUDA, "this library is built for sm_100a only");
     QMK_CUDA(e, cudaFuncSetAttribute(qmk::qwen3_decode_megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(qmk::SMEM_BYTES)));
+    QMK_CUDA(e, cudaFuncSetAttribute(qmk::qwen3_decode_megakernel_small_grid, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(qmk::SMEM_BYTES)));
     void *dev_ptr = nullptr;
     QMK_CUDA(e, cudaGetSymbolAddress(&dev_ptr, qmk::g_static_scratch));
     st.base = static_cast<unsigned char *>(dev_ptr);
@@ -695,8 +709,8 @@ int qmk_generate_static(int first_token_id, int num_steps, const void *embed_wei
   int grid = st.grid;
   if (e->max_ctas > 0 && e->max_ctas < grid) grid = e->max_ctas;
   void *args[] = {&P};
-  cudaError_t err = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(qmk::qwen3_decode_megakernel), dim3(grid),
-                                                dim3(qmk::THREADS), args, qmk::SMEM_BYTES, stream);
+  cudaError_t err = cudaLaunchCooperativeKernel(single_sequence_kernel(grid), dim3(grid), dim3(qmk::THREADS), args,
+                                                qmk::SMEM_BYTES, stream);
   if (err == cudaErrorCooperativeLaunchTooLarge)
     return fail(e, QMK_ERR_NOT_RESIDENT, "persistent grid cannot be co-resident on this device");
   if (err != cudaSuccess) return fail(e, QMK_ERR_CUDA, std::string("cudaLaunchCooperativeKernel: ") + cudaGetErrorString(err));

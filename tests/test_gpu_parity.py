@@ -161,6 +161,14 @@ def test_context_beyond_2048_all_splits(C):
     err = float((dump.cpu() - logits).abs().max())
     print(f"ctx 3000: max |logit - oracle| = {err:.3e}")
     assert got == want and err < LOGIT_TOL
+    # 16 CTAs: two KV splits of ~1500 rows each, i.e. attention items of ~94 ring chunks on a 21-slot ring
+    # (several laps inside one phase), and projection phases longer than the ring as well
+    try:
+        C.configure(max_ctas=16)
+        eng2 = _engine(w, 3072)
+        assert eng2.generate_ids(ids, 5) == want
+    finally:
+        C.configure(max_ctas=0)
 
 
 def test_reduced_grid_gives_same_tokens(C, tiny_cfg):
