@@ -27,7 +27,7 @@ namespace qmk_gemm {
 constexpr int BM = 128, BK = 64;                 // BK * 2 bytes = one 128-byte swizzle row; the N tile (128 or 64) is a template parameter
 // Ring depth per N-tile variant: as many stages as fit in ~192 KB (a skinny M = 128 problem is bound by the
 // latency of its K loop, so the whole K extent of a 1024-wide matrix is in flight at once).
-constexpr int stages_for(int bn) { return bn == 64 ? 8 : 6; }
+constexpr int stages_for(int bn) { return bn == 32 ? 10 : bn == 64 ? 8 : 6; }
 constexpr int MAX_GROUPS = 3;   // matrices sharing one A operand that one launch can multiply (q/k/v, gate/up)
 constexpr int THREADS = 192;
 constexpr uint32_t TILE_A_BYTES = BM * BK * 2;   // 16 KB
@@ -120,8 +120,8 @@ struct Groups {
   size_t split_stride;
 };
 
-// FUSE (BN = 64 only): B0 is the gate matrix and B1 the up matrix of a SwiGLU MLP; the CTA keeps two accumulators
-// (gate tile in TMEM columns [0, 64), up tile in [64, 128)) and its epilogue writes fp16 silu(gate) * up to
+// FUSE (BN = 32 or 64): B0 is the gate matrix and B1 the up matrix of a SwiGLU MLP; the CTA keeps two accumulators
+// (gate tile in TMEM columns [0, BN), up tile in [BN, 2 BN)) and its epilogue writes fp16 silu(gate) * up to
 // groups.C[0] (reinterpreted as __half [M x N]) instead of two fp32 matrices.
 template <int BN, bool FUSE = false>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -129,7 +129,8 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                    const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_b2,
                    const Groups groups, int M, int K, unsigned int *status, unsigned long long budget_ns,
                    int selftest_no_loads) {
-  static_assert(!FUSE || BN == 64, "the fused SwiGLU epilogue is written for 64-wide tiles");
+  static_assert(BN == 32 || BN == 64 || BN == 128, "N tiles of 32, 64 or 128 columns");
+  static_assert(!FUSE || BN <= 64, "the fused SwiGLU epilogue keeps two accumulators of at most 64 columns");
   constexpr int SB = FUSE ? 2 * BN : BN;          // B rows held per stage / accumulator columns
   constexpr int STAGES = stages_for(SB);
   constexpr uint32_t STAGE_BYTES = stage_bytes_for(SB);
