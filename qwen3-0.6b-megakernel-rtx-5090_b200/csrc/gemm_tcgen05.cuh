@@ -118,6 +118,10 @@ struct Groups {
   // (floats); the consumer adds the partial matrices in a fixed order.  0 = no split.
   int kblocks_per_split;
   size_t split_stride;
+  // Bytes one A box brings in (0 = the whole 128 x 64 tile).  A map whose box has fewer than 128 rows fills only
+  // the first rows of the tile; the MMA still reads all 128, so output rows past the box are garbage and the
+  // caller must not store them (kernel argument M <= box rows).
+  uint32_t a_box_bytes;
 };
 
 // FUSE (BN = 32 or 64): B0 is the gate matrix and B1 the up matrix of a SwiGLU MLP; the CTA keeps two accumulators
@@ -182,7 +186,7 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         const int s = kb % STAGES;
         if (kb >= STAGES && !bar_wait(empty(s), ((kb / STAGES) - 1) & 1, abort_flag, status, budget_ns)) break;
         if (*abort_flag) break;
-        bar_expect_tx(full(s), TILE_A_BYTES + (FUSE ? 2 : 1) * TILE_B_BYTES);
+        bar_expect_tx(full(s), (groups.a_box_bytes ? groups.a_box_bytes : TILE_A_BYTES) + (FUSE ? 2 : 1) * TILE_B_BYTES);
         tma_load_2d(base + s * STAGE_BYTES, &map_a, (kb0 + kb) * BK, m0, full(s));
         tma_load_2d(base + s * STAGE_BYTES + TILE_A_BYTES, map_b, (kb0 + kb) * BK, n0, full(s));
         if (FUSE) tma_load_2d(base + s * STAGE_BYTES + TILE_A_BYTES + TILE_B_BYTES, &map_b1, (kb0 + kb) * BK, n0, full(s));

@@ -102,11 +102,22 @@ int ensure_gemm_attrs(std::string *err) {
   return QMK_OK;
 }
 
+// A maps with short boxes (`a_box_rows` < 128 rows per box, a multiple of 8; decode steps with few live rows): one
+// row tile only, and the epilogue must stay inside the box.
+static bool a_box_ok(int a_box_rows, int M, int *rows, uint32_t *a_box_bytes, std::string *err) {
+  *a_box_bytes = 0;
+  if (a_box_rows <= 0 || a_box_rows == qmk_gemm::BM) return true;
+  if (a_box_rows % 8 || a_box_rows > qmk_gemm::BM || M != qmk_gemm::BM) { *err = "gemm: bad A box"; return false; }
+  if (*rows > a_box_rows) *rows = a_box_rows;
+  *a_box_bytes = static_cast<uint32_t>(a_box_rows) * qmk_gemm::BK * 2;
+  return true;
+}
+
 // C_g[M x N_g] fp32 = A[M x K] * B_g[N_g x K]^T for up to three matrices B_g in one launch.  M, N_g multiples of
 // 128; K a multiple of 64; every B map made with `box_n` rows per box (gemm_box_n(M, sum of N_g)).
 int launch_gemm_grouped(const CUtensorMap &map_a, int ngroups, const CUtensorMap *const *maps_b, float *const *Cs,
                         const int *Ns, int M, int K, int box_n, unsigned int *status, int timeout_ms, cudaStream_t stream,
-                        std::string *err, int live_rows) {
+                        std::string *err, int live_rows, int a_box_rows) {
   bool bad = M <= 0 || K <= 0 || M % qmk_gemm::BM || K % qmk_gemm::BK || (box_n != 32 && box_n != 64 && box_n != 128) ||
              ngroups < 1 || ngroups > qmk_gemm::MAX_GROUPS;
   for (int g = 0; !bad && g < ngroups; ++g) bad = Ns[g] <= 0 || Ns[g] % 128;
@@ -128,7 +139,8 @@ int launch_gemm_grouped(const CUtensorMap &map_a, int ngroups, const CUtensorMap
   const CUtensorMap &b0 = *maps_b[0], &b1 = *maps_b[ngroups > 1 ? 1 : 0], &b2 = *maps_b[ngroups > 2 ? 2 : 0];
   dim3 grid(tiles, M / qmk_gemm::BM);
   const unsigned long long budget = static_cast<unsigned long long>(timeout_ms) * 1000000ull;
-  const int rows = live_rows > 0 ? live_rows : M;   // rows the epilogue stores (the rest of the tile is padding)
+  int rows = live_rows > 0 ? live_rows : M;   // rows the epilogue stores (the rest of the tile is padding)
+  if (!a_box_ok(a_box_rows, M, &rows, &gr.a_box_bytes, err)) return QMK_ERR_BAD_ARGUMENT;
   if (box_n == 32)
     qmk_gemm::gemm_f16_tn_kernel<32><<<grid, qmk_gemm::THREADS, qmk_gemm::smem_bytes_for(32), stream>>>(
         map_a, b0, b1, b2, gr, rows, K, status, budget, 0);
@@ -147,7 +159,7 @@ int launch_gemm_grouped(const CUtensorMap &map_a, int ngroups, const CUtensorMap
 // Both maps made with `box_n` (64 or 32) rows per box.
 int launch_gemm_swiglu(const CUtensorMap &map_a, const CUtensorMap &map_gate, const CUtensorMap &map_up, __half *act, int M,
                        int N, int K, unsigned int *status, int timeout_ms, cudaStream_t stream, std::string *err,
-                       int box_n, int live_rows) {
+                       int box_n, int live_rows, int a_box_rows) {
   if (M <= 0 || N <= 0 || K <= 0 || M % qmk_gemm::BM || N % 128 || K % qmk_gemm::BK || (box_n != 32 && box_n != 64)) {
     *err = "gemm: M and N must be multiples of 128 and K a multiple of 64";
     return QMK_ERR_BAD_ARGUMENT;
@@ -159,7 +171,8 @@ int launch_gemm_swiglu(const CUtensorMap &map_a, const CUtensorMap &map_gate, co
   gr.N[0] = N; gr.N[1] = 0; gr.N[2] = 0;
   gr.kblocks_per_split = 0;
   gr.split_stride = 0;
-  const int rows = live_rows > 0 ? live_rows : M;
+  int rows = live_rows > 0 ? live_rows : M;
+  if (!a_box_ok(a_box_rows, M, &rows, &gr.a_box_bytes, err)) return QMK_ERR_BAD_ARGUMENT;
   const unsigned long long budget = static_cast<unsigned long long>(timeout_ms) * 1000000ull;
   if (box_n == 32)
     qmk_gemm::gemm_f16_tn_kernel<32, true><<<dim3(N / 32, M / qmk_gemm::BM), qmk_gemm::THREADS, qmk_gemm::smem_bytes_for(64),
@@ -176,7 +189,7 @@ int launch_gemm_swiglu(const CUtensorMap &map_a, const CUtensorMap &map_gate, co
 // C + z * M * N.  K / 64 must be a multiple of `splits`.  `map_b` made with `box_n` (64 or 32) rows per box.
 int launch_gemm_splitk(const CUtensorMap &map_a, const CUtensorMap &map_b, float *C, int M, int N, int K, int splits,
                        unsigned int *status, int timeout_ms, cudaStream_t stream, std::string *err, int box_n,
-                       int live_rows) {
+                       int live_rows, int a_box_rows) {
   if (M <= 0 || N <= 0 || K <= 0 || M % qmk_gemm::BM || N % 128 || K % qmk_gemm::BK || splits < 1 ||
       (K / qmk_gemm::BK) % splits || (box_n != 32 && box_n != 64)) {
     *err = "gemm: bad split-K shape";
@@ -189,7 +202,8 @@ int launch_gemm_splitk(const CUtensorMap &map_a, const CUtensorMap &map_b, float
   gr.N[0] = N; gr.N[1] = 0; gr.N[2] = 0;
   gr.kblocks_per_split = K / qmk_gemm::BK / splits;
   gr.split_stride = static_cast<size_t>(M) * N;
-  const int rows = live_rows > 0 ? live_rows : M;
+  int rows = live_rows > 0 ? live_rows : M;
+  if (!a_box_ok(a_box_rows, M, &rows, &gr.a_box_bytes, err)) return QMK_ERR_BAD_ARGUMENT;
   const unsigned long long budget = static_cast<unsigned long long>(timeout_ms) * 1000000ull;
   if (box_n == 32)
     qmk_gemm::gemm_f16_tn_kernel<32><<<dim3(N / 32, M / qmk_gemm::BM, splits), qmk_gemm::THREADS, qmk_gemm::smem_bytes_for(32),
@@ -203,11 +217,11 @@ int launch_gemm_splitk(const CUtensorMap &map_a, const CUtensorMap &map_b, float
 }
 
 int launch_gemm(const CUtensorMap &map_a, const CUtensorMap &map_b, float *C, int M, int N, int K, int box_n,
-                unsigned int *status, int timeout_ms, cudaStream_t stream, std::string *err, int live_rows) {
+                unsigned int *status, int timeout_ms, cudaStream_t stream, std::string *err, int live_rows, int a_box_rows) {
   const CUtensorMap *maps[1] = {&map_b};
   float *Cs[1] = {C};
   const int Ns[1] = {N};
-  return launch_gemm_grouped(map_a, 1, maps, Cs, Ns, M, K, box_n, status, timeout_ms, stream, err, live_rows);
+  return launch_gemm_grouped(map_a, 1, maps, Cs, Ns, M, K, box_n, status, timeout_ms, stream, err, live_rows, a_box_rows);
 }
 
 }  // namespace qmk_tc
@@ -525,9 +539,10 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
   {
     const int rows = (B + 7) / 8 * 8;
     if (w.a_rows != rows) {
-      rc = qmk_tc::make_map_f16(&w.map_xn_b, w.xn, rows, H, qmk_gemm::BM, &err);
-      if (rc == QMK_OK) rc = qmk_tc::make_map_f16(&w.map_attn_b, w.attn, rows, QS, qmk_gemm::BM, &err);
-      if (rc == QMK_OK) rc = qmk_tc::make_map_f16(&w.map_act_b, w.act, rows, I, qmk_gemm::BM, &err);
+      // boxes of just the live rows: the rest of the 128-row tile in shared memory is never written (nor needed)
+      rc = qmk_tc::make_map_f16(&w.map_xn_b, w.xn, rows, H, rows, &err);
+      if (rc == QMK_OK) rc = qmk_tc::make_map_f16(&w.map_attn_b, w.attn, rows, QS, rows, &err);
+      if (rc == QMK_OK) rc = qmk_tc::make_map_f16(&w.map_act_b, w.act, rows, I, rows, &err);
       if (rc != QMK_OK) return qmk_internal::report(rc, err);
       w.a_rows = rows;   // (graphs captured earlier keep their own copies of the maps they were captured with)
     }
@@ -543,7 +558,7 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
   // The epilogues store only the B live rows of the 128-row tile (the LM head alone would otherwise write
   // 78 MB of padding logits per step).  Measured: 6.5 k -> 7.5 k tok/s at B = 16, 18.3 k -> 21.0 k at B = 64.
   constexpr int TILE_N = 32, O_SPLITS = 4, DOWN_SPLITS = 4;
-  const int live = B;
+  const int live = B, a_box = w.a_rows;
   const size_t PART = static_cast<size_t>(M) * H;
   auto enqueue_step = [&](cudaStream_t s) -> int {
     int r2 = QMK_OK;
@@ -558,7 +573,7 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
         float *const cs[3] = {w.q, w.k, w.v};
         const int ns[3] = {QS, KVS, KVS};
         if ((r2 = qmk_tc::launch_gemm_grouped(w.map_xn_b, 3, maps, cs, ns, M, H, TILE_N, w.status, env.timeout_ms, s, &err,
-                                              live)) != QMK_OK)
+                                              live, a_box)) != QMK_OK)
           return r2;
       }
       decode_attention_ring<<<dim3(B, NKV), (DAR_WARPS + 1) * 32, DAR_SMEM_BYTES, s>>>(
@@ -566,18 +581,18 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
           w.k_ptrs, w.v_ptrs, layer_off, w.positions, w.attn, max_seq_len, attn_scale, w.status,
           static_cast<unsigned long long>(env.timeout_ms) * 1000000ull);
       if ((r2 = qmk_tc::launch_gemm_splitk(w.map_attn_b, wm(3), w.o, M, H, QS, O_SPLITS, w.status, env.timeout_ms, s, &err,
-                                           TILE_N, live)) != QMK_OK)
+                                           TILE_N, live, a_box)) != QMK_OK)
         return r2;
       add_rmsnorm_rows<<<B, 256, 0, s>>>(w.x, w.o, O_SPLITS, PART, reinterpret_cast<const __half *>(r[7]), w.xn);
       if ((r2 = qmk_tc::launch_gemm_swiglu(w.map_xn_b, wm(4), wm(5), w.act, M, I, H, w.status, env.timeout_ms, s, &err, TILE_N,
-                                           live)) != QMK_OK)
+                                           live, a_box)) != QMK_OK)
         return r2;
       if ((r2 = qmk_tc::launch_gemm_splitk(w.map_act_b, wm(6), w.down, M, H, I, DOWN_SPLITS, w.status, env.timeout_ms, s, &err,
-                                           TILE_N, live)) != QMK_OK)
+                                           TILE_N, live, a_box)) != QMK_OK)
         return r2;
     }
     add_rmsnorm_rows<<<B, 256, 0, s>>>(w.x, w.down, DOWN_SPLITS, PART, static_cast<const __half *>(final_norm_weight), w.xn);
-    r2 = qmk_tc::launch_gemm(w.map_xn_b, w.map_lm, w.logits, M, env.vocab, H, 128, w.status, env.timeout_ms, s, &err, live);
+    r2 = qmk_tc::launch_gemm(w.map_xn_b, w.map_lm, w.logits, M, env.vocab, H, 128, w.status, env.timeout_ms, s, &err, live, a_box);
     if (r2 != QMK_OK) return r2;
     argmax_rows<<<B, 1024, 0, s>>>(w.logits, env.vocab, w.tokens, w.log_ptrs, w.start_positions, w.positions);
     return QMK_OK;
@@ -660,6 +675,7 @@ extern "C" int qmk_selftest_gemm_wait_timeout(int budget_us) {
     gr.N[0] = 128; gr.N[1] = 0; gr.N[2] = 0;
     gr.kblocks_per_split = 0;
     gr.split_stride = 0;
+    gr.a_box_bytes = 0;
     qmk_gemm::gemm_f16_tn_kernel<128><<<dim3(1, 1), qmk_gemm::THREADS, qmk_gemm::smem_bytes_for(128)>>>(
         m, m, m, m, gr, 128, 64, status, static_cast<unsigned long long>(budget_us) * 1000ull, 1);
     unsigned int host[4] = {0, 0, 0, 0};
