@@ -296,7 +296,8 @@ constexpr int DAR_SMEM_BYTES = DAR_SLOTS * DAR_SLOT_BYTES + 2 * DAR_SLOTS * 8 + 
 __global__ void __launch_bounds__((DAR_WARPS + 1) * 32) decode_attention_ring(
     const float *q, const float *k, const float *v, const __half *q_norm, const __half *k_norm, const float *rope,
     const __half *cos_table, const __half *sin_table, __half *const *k_ptrs, __half *const *v_ptrs, size_t layer_off,
-    const int *positions, __half *out, int max_seq_len, float scale, unsigned int *status, unsigned long long budget_ns) {
+    const int *positions, __half *out, int max_seq_len, float scale, unsigned int *status, unsigned long long budget_ns,
+    float *split_part, unsigned int *split_count) {
   extern __shared__ __align__(128) unsigned char dar_smem[];
   __shared__ __align__(16) float sq[2 * D];
   __shared__ float sknew[D], svnew[D], snew_score[2];
@@ -311,7 +312,13 @@ __global__ void __launch_bounds__((DAR_WARPS + 1) * 32) decode_attention_ring(
   const int b = blockIdx.x, g = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = positions[b];
-  const int nchunks = (pos + DAR_ROWS - 1) / DAR_ROWS;
+  const int nchunks_all = (pos + DAR_ROWS - 1) / DAR_ROWS;
+  // gridDim.z CTAs share a (sequence, kv head): CTA z streams chunks [c_begin, c_end) of the old rows, the last one
+  // also folds in the new row; see the merge at the end.
+  const int nsplit = gridDim.z, split = blockIdx.z;
+  const int c_begin = nchunks_all * split / nsplit, c_end = nchunks_all * (split + 1) / nsplit;
+  const int nchunks = c_end - c_begin;        // ring indices below are local: chunk c_begin + i is ring chunk i
+  const bool owner = split == nsplit - 1;
   __half *kbase = k_ptrs[b] + layer_off + static_cast<size_t>(g) * max_seq_len * D;
   __half *vbase = v_ptrs[b] + layer_off + static_cast<size_t>(g) * max_seq_len * D;
   auto s32 = [](const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); };
@@ -356,13 +363,14 @@ __global__ void __launch_bounds__((DAR_WARPS + 1) * 32) decode_attention_ring(
       for (int c = 0; c < nchunks; ++c) {
         const int slot = c % DAR_SLOTS;
         if (c >= DAR_SLOTS && !wait(empty + slot, ((c / DAR_SLOTS) - 1) & 1)) break;
-        const uint32_t bytes = static_cast<uint32_t>(min(DAR_ROWS, pos - c * DAR_ROWS)) * D * 2;
+        const int cg = c_begin + c;          // chunk index within the sequence
+        const uint32_t bytes = static_cast<uint32_t>(min(DAR_ROWS, pos - cg * DAR_ROWS)) * D * 2;
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(full + slot)), "r"(2 * bytes) : "memory");
         unsigned char *dst = dar_smem + slot * DAR_SLOT_BYTES;
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                     ::"r"(s32(dst)), "l"(kbase + static_cast<size_t>(c) * DAR_ROWS * D), "r"(bytes), "r"(s32(full + slot)) : "memory");
+                     ::"r"(s32(dst)), "l"(kbase + static_cast<size_t>(cg) * DAR_ROWS * D), "r"(bytes), "r"(s32(full + slot)) : "memory");
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                     ::"r"(s32(dst + DAR_SLOT_BYTES / 2)), "l"(vbase + static_cast<size_t>(c) * DAR_ROWS * D), "r"(bytes),
+                     ::"r"(s32(dst + DAR_SLOT_BYTES / 2)), "l"(vbase + static_cast<size_t>(cg) * DAR_ROWS * D), "r"(bytes),
                      "r"(s32(full + slot)) : "memory");
         issued = c + 1;
         __threadfence_block();
@@ -413,7 +421,7 @@ __global__ void __launch_bounds__((DAR_WARPS + 1) * 32) decode_attention_ring(
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const __half hv = __float2half_rn(x[i]);
-        dst[lane + 32 * i] = hv;
+        if (owner) dst[lane + 32 * i] = hv;
         snew[lane + 32 * i] = __half2float(hv);
       }
     }
@@ -446,7 +454,7 @@ __global__ void __launch_bounds__((DAR_WARPS + 1) * 32) decode_attention_ring(
         }
       }
       const bool ok = __all_sync(0xffffffffu, mine && wait(full + slot, (c / DAR_SLOTS) & 1));
-      const int nrow = min(DAR_ROWS, pos - c * DAR_ROWS);
+      const int nrow = min(DAR_ROWS, pos - (c_begin + c) * DAR_ROWS);
       float sa = -INFINITY, sb = -INFINITY;
       const unsigned char *sk = dar_smem + slot * DAR_SLOT_BYTES, *sv = sk + DAR_SLOT_BYTES / 2;
       if (ok && lane < nrow) {
@@ -494,12 +502,14 @@ __global__ void __launch_bounds__((DAR_WARPS + 1) * 32) decode_attention_ring(
     for (int d = 0; d < 4; ++d) { sacc[warp][0][lane * 4 + d] = a0[d]; sacc[warp][1][lane * 4 + d] = a1[d]; }
   }
   __syncthreads();
+  // This CTA's state per (head, dim): running maximum M, sum L, unnormalised output A.
+  float M = -INFINITY, L = 0.f, A = 0.f;
+  const int h = (threadIdx.x >> 7) & 1, d = threadIdx.x & (D - 1);
   if (threadIdx.x < 2 * D) {
-    const int h = threadIdx.x >> 7, d = threadIdx.x & (D - 1);
-    float M = snew_score[h];          // the new row is always there
+    if (owner) M = snew_score[h];     // the new row is always there
 #pragma unroll
     for (int w = 0; w < DAR_WARPS; ++w) M = fmaxf(M, sm[w][h]);
-    float L = exp2f(snew_score[h] - M), A = L * svnew[d];
+    if (owner) { L = exp2f(snew_score[h] - M); A = L * svnew[d]; }
 #pragma unroll
     for (int w = 0; w < DAR_WARPS; ++w) {
       const float mw = sm[w][h];
@@ -507,8 +517,40 @@ __global__ void __launch_bounds__((DAR_WARPS + 1) * 32) decode_attention_ring(
       L = fmaf(sl[w][h], s, L);
       A = fmaf(sacc[w][h][d], s, A);
     }
-    out[static_cast<size_t>(b) * QS + (2 * g + h) * D + d] = __float2half_rn(A / L);
   }
+  if (nsplit == 1) {
+    if (threadIdx.x < 2 * D) out[static_cast<size_t>(b) * QS + (2 * g + h) * D + d] = __float2half_rn(A / L);
+    return;
+  }
+  // Split sequence: every CTA leaves (A, M, L) in global memory; the CTA that arrives last (a counter per
+  // (sequence, kv head), no waiting) adds the partial states in split order and resets the counter.
+  constexpr int PART = 2 * (D + 2);                       // floats per partial state: two heads of A[128], M, L
+  float *mine = split_part + (static_cast<size_t>(b * NKV + g) * nsplit + split) * PART;
+  if (threadIdx.x < 2 * D) {
+    mine[h * (D + 2) + d] = A;
+    if (d == 0) { mine[h * (D + 2) + D] = M; mine[h * (D + 2) + D + 1] = L; }
+  }
+  __threadfence();
+  __syncthreads();
+  __shared__ unsigned int s_last;
+  if (threadIdx.x == 0) s_last = atomicAdd(split_count + b * NKV + g, 1u) == static_cast<unsigned int>(nsplit - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (threadIdx.x < 2 * D) {
+    const float *base = split_part + static_cast<size_t>(b * NKV + g) * nsplit * PART + h * (D + 2);
+    float Mt = -INFINITY;
+    for (int sp = 0; sp < nsplit; ++sp) Mt = fmaxf(Mt, __ldcg(base + sp * PART + D));
+    float Lt = 0.f, At = 0.f;
+    for (int sp = 0; sp < nsplit; ++sp) {
+      const float ms = __ldcg(base + sp * PART + D);
+      const float sc2 = (ms == -INFINITY) ? 0.f : exp2f(ms - Mt);
+      Lt = fmaf(__ldcg(base + sp * PART + D + 1), sc2, Lt);
+      At = fmaf(__ldcg(base + sp * PART + d), sc2, At);
+    }
+    out[static_cast<size_t>(b) * QS + (2 * g + h) * D + d] = __float2half_rn(At / Lt);
+  }
+  if (threadIdx.x == 0) split_count[b * NKV + g] = 0u;   // ready for the next launch (stream order)
 }
 
 // Greedy pick per row: tokens[b] = argmax(logits[b][:]) (lowest index on ties), logged at

@@ -250,6 +250,8 @@ struct Workspace {                  // per device, allocated on first use, never
   unsigned long long graph_epoch = 1;    // bumped whenever tensor maps baked into the graphs are rebuilt
   __half **k_ptrs = nullptr, **v_ptrs = nullptr;
   int **log_ptrs = nullptr;
+  float *split_part = nullptr;            // partial attention states of split sequences (decode_attention_ring)
+  unsigned int *split_count = nullptr;    // arrival counters, one per (sequence, kv head); zero between launches
   float *logits = nullptr;
   int logits_vocab = 0;
   const void *lm_ptr = nullptr;
@@ -448,6 +450,7 @@ unsigned int __float_as_uint_host(float f) {
 
 constexpr int MAX_BATCH = 128;      // one 128-row GEMM tile of sequences
 
+constexpr int MAX_ATTN_SPLITS = 8;
 int ensure_decode_workspace(Workspace &w, const void *lm_head, int vocab) {
   if (!w.positions) {
     PF_CUDA(cudaMalloc(&w.positions, sizeof(int) * MAX_BATCH));
@@ -458,6 +461,9 @@ int ensure_decode_workspace(Workspace &w, const void *lm_head, int vocab) {
     PF_CUDA(cudaMalloc(&w.k_ptrs, sizeof(void *) * MAX_BATCH));
     PF_CUDA(cudaMalloc(&w.v_ptrs, sizeof(void *) * MAX_BATCH));
     PF_CUDA(cudaMalloc(&w.log_ptrs, sizeof(void *) * MAX_BATCH));
+    PF_CUDA(cudaMalloc(&w.split_part, sizeof(float) * MAX_BATCH * qmk_pf::NKV * MAX_ATTN_SPLITS * 2 * (qmk_pf::D + 2)));
+    PF_CUDA(cudaMalloc(&w.split_count, sizeof(unsigned int) * MAX_BATCH * qmk_pf::NKV));
+    PF_CUDA(cudaMemset(w.split_count, 0, sizeof(unsigned int) * MAX_BATCH * qmk_pf::NKV));
   }
   if (w.logits_vocab < vocab) {
     if (w.logits) cudaFree(w.logits);
@@ -559,6 +565,10 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
   // 78 MB of padding logits per step).  Measured: 6.5 k -> 7.5 k tok/s at B = 16, 18.3 k -> 21.0 k at B = 64.
   constexpr int TILE_N = 32, O_SPLITS = 4, DOWN_SPLITS = 4;
   const int live = B, a_box = w.a_rows;
+  // Few sequences: split every sequence's cache rows over several CTAs so that the attention fills the device
+  // (two CTAs fit on an SM): 8 B CTAs otherwise, each streaming a whole sequence through one ring.
+  int attn_splits = (2 * qmk_tc::g_sms[dev]) / (B * NKV);   // (gemm_box_n above cached the SM count of this device)
+  attn_splits = attn_splits < 1 ? 1 : attn_splits > MAX_ATTN_SPLITS ? MAX_ATTN_SPLITS : attn_splits;
   const size_t PART = static_cast<size_t>(M) * H;
   auto enqueue_step = [&](cudaStream_t s) -> int {
     int r2 = QMK_OK;
@@ -576,10 +586,10 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
                                               live, a_box)) != QMK_OK)
           return r2;
       }
-      decode_attention_ring<<<dim3(B, NKV), (DAR_WARPS + 1) * 32, DAR_SMEM_BYTES, s>>>(
+      decode_attention_ring<<<dim3(B, NKV, attn_splits), (DAR_WARPS + 1) * 32, DAR_SMEM_BYTES, s>>>(
           w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]), reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv,
           w.k_ptrs, w.v_ptrs, layer_off, w.positions, w.attn, max_seq_len, attn_scale, w.status,
-          static_cast<unsigned long long>(env.timeout_ms) * 1000000ull);
+          static_cast<unsigned long long>(env.timeout_ms) * 1000000ull, w.split_part, w.split_count);
       if ((r2 = qmk_tc::launch_gemm_splitk(w.map_attn_b, wm(3), w.o, M, H, QS, O_SPLITS, w.status, env.timeout_ms, s, &err,
                                            TILE_N, live, a_box)) != QMK_OK)
         return r2;
