@@ -278,7 +278,9 @@ __global__ void __launch_bounds__(128) causal_attention_mma(const float *qr, con
 }
 
 // Decode-step attention for a batch of sequences, with the per-head preparation fused in.  grid = (B, 8 kv
-// heads), block = 288 = 8 consumer warps + 1 producer warp.  CTA (sequence b, kv head g) first normalises and
+// heads, splits), block = 288 = 8 consumer warps + 1 producer warp.  With splits > 1 the old rows of a sequence are
+// divided among `splits` CTAs, which leave their softmax states in `split_part`; the CTA that arrives last at the
+// counter in `split_count` adds them up in split order (no CTA waits for another).  CTA (sequence b, kv head g) first normalises and
 // rotates the two query heads and the K head of row b of the q / k / v GEMM outputs (warps 0-2; warp 3 takes V),
 // writes the new K and V rows to sequence b's cache at positions[b], and then attends over the old rows
 // [0, positions[b]) plus the new row from shared memory (the fp16-rounded values, i.e. what later steps read).
