@@ -266,7 +266,8 @@ def run_ours(args):
         from Model.Qwen06B_architecture import BatchDecoder
         eng = BatchDecoder(weights=weights, tokenizer=S.StubTokenizer(-1), num_sequences=B, max_seq_len=MAX_SEQ_LEN,
                            device=str(device), weight_format=engine_format,
-                           prefill_mode="tensor" if B > 4 else "serial")
+                           prefill_mode="tensor" if engine_format == "fp16" else "serial")
+        persistent = eng.engine == "persistent"
         prompts = [S.make_prompt(PROMPT_LEN, seed=rank * 16 + b) for b in range(B)]
         for b in range(B):
             eng._prefill_slot(b, prompts[b][:-1])       # untimed
@@ -351,7 +352,7 @@ def run_ours(args):
             "config": {"weights": args.weights + (" (quantised values, stored expanded as fp16)" if expanded else ""), "workload": WORKLOAD if (PROMPT_LEN, DECODE_TOKENS) == (4096, 256) else
                        f"profiling case: {PROMPT_LEN} prompt tokens, {DECODE_TOKENS} decode tokens per step",
                        "tokens_per_step": DECODE_TOKENS * B, "sequences_per_launch": B,
-                       "engine": "persistent megakernel" if B <= 4 else "tcgen05 GEMM path", "replicas": world,
+                       "engine": "persistent megakernel" if (B == 1 or persistent) else "tcgen05 GEMM path", "replicas": world,
                        "l2": "no flush needed: each token streams 1.19 GB of weights + 0.47 GB of KV, > 126 MB L2",
                        "grid_ctas": C.num_ctas()},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -360,7 +361,7 @@ def run_ours(args):
                          "frac_of_nominal_8TBs": achieved / 8000.0},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * B,
                     "d2h_bytes_per_step": 4 * DECODE_TOKENS * B},
-            "gpu_launches": args.steps if B <= 4 else args.steps * DECODE_TOKENS * (13 * 28 + 4),
+            "gpu_launches": args.steps if (B == 1 or persistent) else args.steps * DECODE_TOKENS * (7 * 28 + 4),
             "clocks": clocks.summary(),
         }
         if world == 1 and not args.no_cpu_baseline:
@@ -452,8 +453,8 @@ def main():
     ap.add_argument("--weights", choices=["fp16", "fp8", "nvfp4"], default="fp16",
                     help="weight format (default fp16 = the benchmark configuration)")
     ap.add_argument("--batch", type=int, default=1,
-                    help="sequences per GPU decoded together (default 1: the headline batch-1 configuration; 2-4: one "
-                         "persistent launch; 5-128: tensor-core batched decode)")
+                    help="sequences per GPU decoded together (default 1: the headline batch-1 configuration; 2-3 (4 with fp8): one "
+                         "persistent launch; above: tensor-core batched decode)")
     ap.add_argument("--continuous", type=int, default=0, metavar="N",
                     help="instead of the headline workload: N requests per GPU through the continuous-batching "
                          "scheduler (prompt lengths 64..2048, 128 new tokens each, --batch live sequences)")

@@ -28,6 +28,7 @@ def C(built_library):
 
 def _batch_engine(w, n, max_seq_len, **kw):
     from Model.Qwen06B_architecture import BatchDecoder
+    kw.setdefault("engine", "persistent")   # this file covers the multi-sequence persistent kernel
     return BatchDecoder(weights=S.weights_to(w, "cuda"), tokenizer=S.StubTokenizer(-1, w["embed_weight"].shape[0]),
                         num_sequences=n, max_seq_len=max_seq_len, **kw)
 

@@ -131,7 +131,7 @@ def test_gpu_continuous_batching_equals_single_sequence_engine(built_library, ti
     w = S.weights_to(S.make_weights(seed=tiny_cfg["seed"], num_layers=tiny_cfg["num_layers"], vocab_size=vocab,
                                     norm_std=tiny_cfg["norm_std"], max_seq_len=16), "cuda")
     tok = S.StubTokenizer(-1, vocab)
-    eng = BatchDecoder(weights=w, tokenizer=tok, num_sequences=4, max_seq_len=256)
+    eng = BatchDecoder(weights=w, tokenizer=tok, num_sequences=4, max_seq_len=256, engine="persistent")
     reqs = [(S.make_prompt(3 + (i * 13) % 60, seed=100 + i, vocab_size=vocab), 4 + (i * 5) % 29) for i in range(11)]
     single = Decoder(weights=w, tokenizer=tok, verbose=False, max_seq_len=256)
     want = [single.generate_ids(ids, n) for ids, n in reqs]
