@@ -58,10 +58,12 @@ int make_map_f16(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t cols
   return QMK_OK;
 }
 
-// C[M x N] fp32 = A[M x K] * B[N x K]^T.  M, N multiples of 128; K a multiple of 64.  `map_b` must have been
-// made with gemm_box_n(M, N) rows per box: the widest N tile (128, 64, 32) that still gives about two thirds as
-// many CTAs as the device has SMs; skinny problems are bound by how many SMs pull operands at once.
-int gemm_box_n(int M, int N) {
+// Width of the N tiles for C[M x N] = A[M x K] * B[N x K]^T (M, N multiples of 128).  `map_b` must have been made
+// with that many rows per box.  Skinny problems are bound by how many SMs pull operands at once and by the fixed
+// cost of a CTA (launch, barrier and TMEM set-up, pipeline fill, epilogue - worth about 320 columns of streaming in
+// the launch lists of decode steps), so: as few waves as possible, then the narrower tile.  `b_tiles` = B tiles a
+// CTA multiplies per K block (2 for the fused gate/up kernel, whose widest tile is 64).
+static int sm_count() {
   int dev = 0;
   cudaGetDevice(&dev);
   int sms = (dev >= 0 && dev < 16) ? g_sms[dev] : 0;
@@ -69,9 +71,21 @@ int gemm_box_n(int M, int N) {
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (dev >= 0 && dev < 16) g_sms[dev] = sms;
   }
-  const int tiles128 = (M / qmk_gemm::BM) * (N / 128);
-  return tiles128 * 3 >= sms * 2 ? 128 : tiles128 * 2 * 3 >= sms * 2 ? 64 : 32;
+  return sms > 0 ? sms : 148;
 }
+static int pick_box_n(int M, int N, int b_tiles) {
+  const int sms = sm_count();
+  int best = 0;
+  long best_cost = 0;
+  for (int bn = b_tiles == 2 ? 64 : 128; bn >= 32; bn /= 2) {
+    const long ctas = static_cast<long>(M / qmk_gemm::BM) * (N / bn);
+    const long cost = ((ctas + sms - 1) / sms) * (b_tiles * bn + 320);
+    if (best == 0 || cost < best_cost) { best = bn; best_cost = cost; }
+  }
+  return best;
+}
+int gemm_box_n(int M, int N) { return pick_box_n(M, N, 1); }
+int gemm_box_n_fused(int M, int N) { return pick_box_n(M, N, 2); }
 
 // Opt-in shared-memory size of every tile variant, once per device (outside any stream capture).
 int ensure_gemm_attrs(std::string *err) {
@@ -421,7 +435,7 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
       if ((rc = gemm(w.map_attn, l, 3, w.o, M, H, QS, T)) != QMK_OK) break;
       add_rmsnorm_rows<<<T, 256, 0, stream>>>(w.x, w.o, 1, 0, reinterpret_cast<const __half *>(r[7]), w.xn);
       {
-        const int box_gu = qmk_tc::gemm_box_n(M, I) == 32 ? 32 : 64;   // the fused kernel has 32- and 64-wide tiles
+        const int box_gu = qmk_tc::gemm_box_n_fused(M, I);
         if ((rc = qmk_tc::launch_gemm_swiglu(w.map_xn, wmap_for(l, 4, box_gu), wmap_for(l, 5, box_gu), w.act, M, I, H,
                                              w.status, env.timeout_ms, stream, &err, box_gu, T)) != QMK_OK)
           break;

@@ -14,6 +14,7 @@ namespace qmk_tc {
 // the first B.  `a_box_rows` (0 = 128): rows per box of the A map when it is shorter than the tile.
 int make_map_f16(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t cols, uint32_t box_rows, std::string *err);
 int gemm_box_n(int M, int N);
+int gemm_box_n_fused(int M, int N);   // for launch_gemm_swiglu (N = columns of the gate matrix)
 int ensure_gemm_attrs(std::string *err);
 int launch_gemm_splitk(const CUtensorMap &map_a, const CUtensorMap &map_b, float *C, int M, int N, int K, int splits,
                        unsigned int *status, int timeout_ms, cudaStream_t stream, std::string *err, int box_n = 64,

@@ -17,7 +17,7 @@ def C(built_library):
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 128, 64), (128, 128, 256), (256, 1024, 1024), (512, 3072, 1024), (128, 1024, 3072),
-                                   (1024, 2048, 512)])   # N tiles of 32, 32, 32, 64, 32 and 128 columns on 148 SMs
+                                   (1024, 2048, 512), (512, 2048, 256)])   # N tiles of 32, 32, 32, 128, 32, 128 and 64 columns on 148 SMs
 def test_matches_torch(C, m, n, k):
     g = torch.Generator("cpu").manual_seed(m + n + k)
     a = torch.randn(m, k, generator=g).to(torch.float16).cuda()
