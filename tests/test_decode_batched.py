@@ -58,6 +58,29 @@ def test_tiny_model_against_oracle(C, n):
     assert eng.positions[:n] == [Ln - 1 + steps for Ln in lens]
 
 
+def test_long_contexts_split_over_several_ctas(C):
+    """Two sequences: the attention kernel divides each sequence's cache rows among eight CTAs (nine ring chunks
+    per CTA at 2300 tokens, more than the ring has slots) and the last CTA to arrive adds the partial states."""
+    vocab, steps, L = 2048, 4, 2432
+    w = S.make_weights(seed=23, num_layers=2, vocab_size=vocab, norm_std=0.1, max_seq_len=16)
+    lens = [2300, 901]
+    prompts = [S.make_prompt(Ln, seed=450 + i, vocab_size=vocab) for i, Ln in enumerate(lens)]
+    eng = _engine(w, 2, L, engine="gemm", prefill_mode="serial")
+    dump = torch.zeros(2, steps, vocab, device="cuda")
+    C.set_logits_dump(dump)
+    try:
+        got = eng.generate_ids(prompts, steps)
+    finally:
+        C.set_logits_dump(None)
+    for b in range(2):
+        want, logits = OracleDecoder(w, max_seq_len=L).generate_ids(prompts[b], steps, keep_logits=True)
+        err = float((dump[b].cpu() - logits).abs().max())
+        print(f"split attention, {lens[b]}-token context: max |logit - oracle| = {err:.3e}")
+        assert got[b] == want and err < LOGIT_TOL
+    # a second call reuses the arrival counters the first one left at zero
+    assert eng.generate_ids(prompts, steps) == got
+
+
 def test_both_engines_and_tensor_prefill_agree(C):
     """Four sequences through the persistent launch and through the GEMM path (with tensor-core prefill):
     same tokens."""
