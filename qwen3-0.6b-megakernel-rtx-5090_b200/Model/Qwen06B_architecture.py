@@ -96,9 +96,11 @@ def build_rope_tables(max_seq_len: int, device="cuda", theta: float = ROPE_THETA
     return cos, sin
 
 
-def load_weights(model_name: str = "Qwen/Qwen3-0.6B", verbose: bool = True, max_seq_len: int = MAX_SEQ_LEN):
+def load_weights(model_name: str = "Qwen/Qwen3-0.6B", verbose: bool = True, max_seq_len: int = MAX_SEQ_LEN,
+                 device: str = "cuda"):
     """HF checkpoint -> (weights dict, tokenizer) in the reference layout
-    (Model/Qwen06B_architecture.py:96-163).  Needs the checkpoint on disk or a network."""
+    (Model/Qwen06B_architecture.py:96-163).  Needs the checkpoint on disk or a network.  ``device`` is where the
+    tensors end up (the reference always loads to "cuda"; "cpu" serves tests of the layout)."""
     if not verbose:
         os.environ.setdefault("HF_HUB_DISABLE_PROGRESS_BARS", "1")
         os.environ.setdefault("TRANSFORMERS_NO_ADVISORY_WARNINGS", "1")
@@ -106,7 +108,8 @@ def load_weights(model_name: str = "Qwen/Qwen3-0.6B", verbose: bool = True, max_
 
     if verbose:
         print(f"Loading {model_name}...")
-    model = AutoModelForCausalLM.from_pretrained(model_name, dtype=torch.float16, device_map="cuda")
+    # (no device_map: it needs the accelerate package; load on the host, then move)
+    model = AutoModelForCausalLM.from_pretrained(model_name, dtype=torch.float16).to(device)
     tokenizer = AutoTokenizer.from_pretrained(model_name)
     sd = model.state_dict()
     hf_names = ("input_layernorm", "self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj",
@@ -115,12 +118,13 @@ def load_weights(model_name: str = "Qwen/Qwen3-0.6B", verbose: bool = True, max_
     n_layers = model.config.num_hidden_layers
     layer_weights = [sd[f"model.layers.{li}.{n}.weight"].contiguous() for li in range(n_layers) for n in hf_names]
     embed = sd["model.embed_tokens.weight"].contiguous()
-    cos, sin = build_rope_tables(max_seq_len)
+    cos, sin = build_rope_tables(max_seq_len, device=device)
     weights = dict(embed_weight=embed, layer_weights=layer_weights,
                    final_norm_weight=sd["model.norm.weight"].contiguous(), lm_head_weight=embed,
                    cos_table=cos, sin_table=sin)
     del model
-    torch.cuda.empty_cache()
+    if torch.cuda.is_available():
+        torch.cuda.empty_cache()
     return weights, tokenizer
 
 
@@ -151,7 +155,7 @@ class Decoder:
         if not torch.cuda.is_available():
             raise RuntimeError("Decoder needs a CUDA device (sm_100a); there is no CPU path")
         if weights is None:
-            weights, tokenizer = load_weights(model_name, verbose=verbose, max_seq_len=max_seq_len)
+            weights, tokenizer = load_weights(model_name, verbose=verbose, max_seq_len=max_seq_len, device=device)
         self.tokenizer = tokenizer
         self.max_seq_len = int(max_seq_len)
         self._position = 0
