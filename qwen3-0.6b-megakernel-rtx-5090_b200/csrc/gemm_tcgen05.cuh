@@ -162,11 +162,23 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   auto empty = [&](int s) { return bars + 8u * (STAGES + s); };
   const uint32_t acc_full = bars + 8u * (2 * STAGES);
 
+  // the first fill of the ring needs no free-slot wait: thread 0 issues it before the CTA-wide barrier below, so
+  // that the first TMA round trip overlaps the TMEM allocation
+  const int prologue = selftest_no_loads ? 0 : (kblocks < STAGES ? kblocks : STAGES);
   if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map_b)) : "memory");
+    if (FUSE) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b1)) : "memory");
     for (int s = 0; s < STAGES; ++s) { bar_init(full(s), 1); bar_init(empty(s), 1); }
     bar_init(acc_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (int kb = 0; kb < prologue; ++kb) {
+      bar_expect_tx(full(kb), (groups.a_box_bytes ? groups.a_box_bytes : TILE_A_BYTES) + (FUSE ? 2 : 1) * TILE_B_BYTES);
+      tma_load_2d(base + kb * STAGE_BYTES, &map_a, (kb0 + kb) * BK, m0, full(kb));
+      tma_load_2d(base + kb * STAGE_BYTES + TILE_A_BYTES, map_b, (kb0 + kb) * BK, n0, full(kb));
+      if (FUSE) tma_load_2d(base + kb * STAGE_BYTES + TILE_A_BYTES + TILE_B_BYTES, &map_b1, (kb0 + kb) * BK, n0, full(kb));
+    }
   }
   if (warp == 1) {   // the whole warp allocates; the address lands in shared memory
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(TMEM_COLS)
@@ -180,9 +192,9 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
   if (warp == 0) {
     if (lane == 0) {                       // ---- producer
-      int issued = 0;
+      int issued = prologue;
       // self test of the bounded waits: the loads are never issued, so the MMA thread's first wait runs out
-      for (int kb = 0; kb < (selftest_no_loads ? 0 : kblocks); ++kb) {
+      for (int kb = prologue; kb < (selftest_no_loads ? 0 : kblocks); ++kb) {
         const int s = kb % STAGES;
         if (kb >= STAGES && !bar_wait(empty(s), ((kb / STAGES) - 1) & 1, abort_flag, status, budget_ns)) break;
         if (*abort_flag) break;
