@@ -39,7 +39,7 @@ def test_quantised_weight_dicts_and_byte_count():
     assert shapes[1] == (2048, 1040) and shapes[6] == (1024, 2064) and shapes[10] == (1024, 3088)
     assert eng["layer_weights"][0].dtype == torch.float16          # norm vectors untouched
     assert ora["layer_weights"][1].dtype == torch.float32
-    # ~598 MB per decode step for the full model (BASELINE.md gives 598.1 M with bare fp32 scales)
+    # ~598 MB per decode step for the full model (598.1 M with bare fp32 row scales and no 16-byte trailers)
     assert 0.595e9 < Q.weight_bytes_fp8() < 0.610e9
 
 
