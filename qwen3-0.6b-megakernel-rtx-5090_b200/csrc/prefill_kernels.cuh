@@ -33,21 +33,29 @@ __global__ void embed_rows(const int *tokens, const __half *embed, float *x) {
 }
 
 // Residual add + RMSNorm: x[t] += add[t] (if add), y[t] = fp16(x[t] * rstd * w).  grid = T, block = 256.
-// `add` may come as `nparts` partial matrices `part_stride` floats apart (split-K GEMM output): they are added
-// in index order.
+// `add` may come as `nparts` (<= 4) partial matrices `part_stride` floats apart (split-K GEMM output): they are
+// added in index order.
 __global__ void add_rmsnorm_rows(float *x, const float *add, int nparts, size_t part_stride, const __half *w, __half *y) {
   __shared__ float red[8];
   const int t = blockIdx.x;
   float *xr = x + static_cast<size_t>(t) * H;
   float v[4];
   float ss = 0.f;
+  constexpr int MAX_PARTS = 4;   // all loads of a thread are issued before the first add (one L2 round trip)
+  float part[4][MAX_PARTS];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int k = threadIdx.x + j * 256;
-    float acc = xr[k];
-    if (add)
-      for (int p = 0; p < nparts; ++p) acc += add[p * part_stride + static_cast<size_t>(t) * H + k];
-    v[j] = acc;
+    v[j] = xr[k];
+#pragma unroll
+    for (int p = 0; p < MAX_PARTS; ++p)
+      part[j][p] = (add && p < nparts) ? add[p * part_stride + static_cast<size_t>(t) * H + k] : 0.f;
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+#pragma unroll
+    for (int p = 0; p < MAX_PARTS; ++p)
+      if (add && p < nparts) v[j] += part[j][p];   // index order, as the split-K contract says
     ss = fmaf(v[j], v[j], ss);
   }
   ss = warp_sum(ss);
