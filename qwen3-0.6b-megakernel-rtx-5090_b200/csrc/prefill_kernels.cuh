@@ -549,14 +549,24 @@ __global__ void __launch_bounds__((DAR_WARPS + 1) * 32) decode_attention_ring(
   __threadfence();
   if (threadIdx.x < 2 * D) {
     const float *base = split_part + static_cast<size_t>(b * NKV + g) * nsplit * PART + h * (D + 2);
+    constexpr int MAX_SPLITS = 8;      // (the host never launches more) all loads first: one L2 round trip
+    float ms[MAX_SPLITS], ls[MAX_SPLITS], as[MAX_SPLITS];
+#pragma unroll
+    for (int sp = 0; sp < MAX_SPLITS; ++sp) {
+      const bool have = sp < nsplit;
+      ms[sp] = have ? __ldcg(base + sp * PART + D) : -INFINITY;
+      ls[sp] = have ? __ldcg(base + sp * PART + D + 1) : 0.f;
+      as[sp] = have ? __ldcg(base + sp * PART + d) : 0.f;
+    }
     float Mt = -INFINITY;
-    for (int sp = 0; sp < nsplit; ++sp) Mt = fmaxf(Mt, __ldcg(base + sp * PART + D));
+#pragma unroll
+    for (int sp = 0; sp < MAX_SPLITS; ++sp) Mt = fmaxf(Mt, ms[sp]);
     float Lt = 0.f, At = 0.f;
-    for (int sp = 0; sp < nsplit; ++sp) {
-      const float ms = __ldcg(base + sp * PART + D);
-      const float sc2 = (ms == -INFINITY) ? 0.f : exp2f(ms - Mt);
-      Lt = fmaf(__ldcg(base + sp * PART + D + 1), sc2, Lt);
-      At = fmaf(__ldcg(base + sp * PART + d), sc2, At);
+#pragma unroll
+    for (int sp = 0; sp < MAX_SPLITS; ++sp) {      // split order
+      const float sc2 = (ms[sp] == -INFINITY) ? 0.f : exp2f(ms[sp] - Mt);
+      Lt = fmaf(ls[sp], sc2, Lt);
+      At = fmaf(as[sp], sc2, At);
     }
     out[static_cast<size_t>(b) * QS + (2 * g + h) * D + d] = __float2half_rn(At / Lt);
   }
