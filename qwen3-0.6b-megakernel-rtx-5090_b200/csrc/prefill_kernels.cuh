@@ -137,6 +137,8 @@ __global__ void qk_norm_rope_cache(const float *q, const float *k, const float *
 // online softmax on the accumulator fragments, P (as fp16 A fragments, straight from the S registers) times V
 // (64 MMAs).  q is scaled by scale * log2(e) before it is rounded to fp16, so the softmax runs on exp2.
 constexpr int ATM_Q = 32, ATM_KEYS = 64, ATM_PITCH = D + 8;   // halves per K / V row in shared memory
+constexpr int ATM_STAGE_HALVES = 2 * ATM_KEYS * ATM_PITCH;      // one stage: a K tile and a V tile
+constexpr int ATM_SMEM_BYTES = 2 * ATM_STAGE_HALVES * 2;        // two stages, 69,632 bytes
 
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
   const __half2 h = __floats2half2_rn(a, b);
@@ -152,8 +154,9 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
 __global__ void __launch_bounds__(128) causal_attention_mma(const float *qr, const __half *k_cache_layer,
                                                             const __half *v_cache_layer, __half *out, int T, int pos0,
                                                             int max_seq_len, float scale) {
-  __shared__ __align__(16) __half sk[ATM_KEYS * ATM_PITCH];
-  __shared__ __align__(16) __half sv[ATM_KEYS * ATM_PITCH];
+  // two stages of (K tile, V tile): the next 64 keys are fetched with cp.async while this tile is multiplied
+  extern __shared__ __align__(16) unsigned char atm_smem[];
+  __half *const tiles = reinterpret_cast<__half *>(atm_smem);
   const int g = blockIdx.y, t0 = (gridDim.x - 1 - blockIdx.x) * ATM_Q;   // longest tiles first
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = warp & 1, tw = t0 + 16 * (warp >> 1);     // this warp's head and first token
@@ -188,20 +191,37 @@ __global__ void __launch_bounds__(128) causal_attention_mma(const float *qr, con
   const __half *kbase = k_cache_layer + static_cast<size_t>(g) * max_seq_len * D;
   const __half *vbase = v_cache_layer + static_cast<size_t>(g) * max_seq_len * D;
 
-  for (int k0 = 0; k0 <= cta_last; k0 += ATM_KEYS) {
-    __syncthreads();   // the previous tile is fully used
+  auto fetch_tile = [&](int k0, int stage) {   // rows past the last key this CTA needs are zero-filled
+    __half *dk = tiles + stage * ATM_STAGE_HALVES, *dv = dk + ATM_KEYS * ATM_PITCH;
     for (int i = threadIdx.x; i < ATM_KEYS * (D / 8); i += 128) {
       const int j = i >> 4, c = i & 15;
-      uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
-      if (k0 + j <= cta_last) {
-        kv = *reinterpret_cast<const uint4 *>(kbase + static_cast<size_t>(k0 + j) * D + c * 8);
-        vv = *reinterpret_cast<const uint4 *>(vbase + static_cast<size_t>(k0 + j) * D + c * 8);
-      }
-      *reinterpret_cast<uint4 *>(sk + j * ATM_PITCH + c * 8) = kv;
-      *reinterpret_cast<uint4 *>(sv + j * ATM_PITCH + c * 8) = vv;
+      const bool in = k0 + j <= cta_last;
+      const size_t off = static_cast<size_t>(in ? k0 + j : 0) * D + c * 8;
+      const uint32_t bytes = in ? 16u : 0u;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dk + j * ATM_PITCH + c * 8))),
+                   "l"(kbase + off), "r"(bytes) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dv + j * ATM_PITCH + c * 8))),
+                   "l"(vbase + off), "r"(bytes) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  fetch_tile(0, 0);
+  int stage = 0;
+  for (int k0 = 0; k0 <= cta_last; k0 += ATM_KEYS, stage ^= 1) {
+    // the other stage was last read in the previous iteration, which ended with a barrier
+    const bool more = k0 + ATM_KEYS <= cta_last;
+    if (more) {
+      fetch_tile(k0 + ATM_KEYS, stage ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
-    if (tw >= T || k0 > warp_last) continue;   // warp-uniform: nothing (more) to do for this warp in this tile
+    const __half *sk = tiles + stage * ATM_STAGE_HALVES, *sv = sk + ATM_KEYS * ATM_PITCH;
+    if (tw >= T || k0 > warp_last) {   // warp-uniform: nothing (more) to do for this warp in this tile
+      __syncthreads();
+      continue;
+    }
 
     // S = Q K^T for 64 keys: 8 n-tiles of 8 keys
     float sacc[8][4];
@@ -271,6 +291,7 @@ __global__ void __launch_bounds__(128) causal_attention_mma(const float *qr, con
         mma_16816(o[2 * dp + 1], pa[kk], b2, b3);
       }
     }
+    __syncthreads();   // this stage is free for the fetch of the iteration after next
   }
   if (tw < T) {
     const float inv_lo = l_lo > 0.f ? 1.0f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.0f / l_hi : 0.f;

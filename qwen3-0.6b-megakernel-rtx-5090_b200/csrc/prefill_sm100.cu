@@ -108,6 +108,9 @@ int ensure_gemm_attrs(std::string *err) {
       e = cudaFuncSetAttribute(qmk_gemm::gemm_f16_tn_kernel<32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(qmk_gemm::smem_bytes_for(64)));
     if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(qmk_pf::causal_attention_mma, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               qmk_pf::ATM_SMEM_BYTES);
+    if (e == cudaSuccess)
       e = cudaFuncSetAttribute(qmk_pf::decode_attention_ring, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                qmk_pf::DAR_SMEM_BYTES);
     if (e != cudaSuccess) { *err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e); return QMK_ERR_CUDA; }
@@ -430,7 +433,7 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
                                                          reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv, w.qr, kc, vc,
                                                          pos0, max_seq_len);
       if (l == num_layers - 1) break;   // the cache is complete; nothing downstream of the last layer is kept
-      causal_attention_mma<<<dim3((T + ATM_Q - 1) / ATM_Q, NKV), 128, 0, stream>>>(w.qr, kc, vc, w.attn, T, pos0,
+      causal_attention_mma<<<dim3((T + ATM_Q - 1) / ATM_Q, NKV), 128, ATM_SMEM_BYTES, stream>>>(w.qr, kc, vc, w.attn, T, pos0,
                                                                                   max_seq_len, attn_scale);
       if ((rc = gemm(w.map_attn, l, 3, w.o, M, H, QS, T)) != QMK_OK) break;
       add_rmsnorm_rows<<<T, 256, 0, stream>>>(w.x, w.o, 1, 0, reinterpret_cast<const __half *>(r[7]), w.xn);
