@@ -133,7 +133,8 @@ __global__ void qk_norm_rope_cache(const float *q, const float *k, const float *
 // grid = (ceil(T / 32), 8 kv heads), block = 128 = 4 warps.  A CTA takes 32 query tokens x the two query heads
 // of its kv head; warp w works on head (w & 1) and tokens t0 + 16 * (w >> 1) + 0..15 (one 16-row MMA tile).
 // Keys go through shared memory in tiles of 64 rows of K and of V (row pitch 272 bytes: conflict-free for the
-// 32-bit B-fragment loads of K and for ldmatrix.trans on V).  Per key tile and warp: S = Q K^T (64 MMAs),
+// 32-bit B-fragment loads of K and for ldmatrix.trans on V), two stages filled with cp.async so that the next tile
+// arrives while this one is multiplied (dynamic shared memory: ATM_SMEM_BYTES).  Per key tile and warp: S = Q K^T (64 MMAs),
 // online softmax on the accumulator fragments, P (as fp16 A fragments, straight from the S registers) times V
 // (64 MMAs).  q is scaled by scale * log2(e) before it is rounded to fp16, so the softmax runs on exp2.
 constexpr int ATM_Q = 32, ATM_KEYS = 64, ATM_PITCH = D + 8;   // halves per K / V row in shared memory
