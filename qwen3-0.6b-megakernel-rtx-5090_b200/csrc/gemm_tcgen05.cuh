@@ -226,10 +226,9 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         const uint64_t db = smem_desc_sw128(base + s * STAGE_BYTES + TILE_A_BYTES);
 #pragma unroll
         for (int j = 0; j < BK / 16; ++j) {  // 16 halves = 32 bytes = 2 descriptor address units per K step
-          mma_f16_ss(tmem_base, da + 2u * j, db + 2u * j, (kb > 0 || j > 0) ? 1u : 0u, idesc_for(BN));
-          if (FUSE)                          // the up tile sits TILE_B_BYTES (>> 4 in descriptor units) behind the gate tile
-            mma_f16_ss(tmem_base + BN, da + 2u * j, db + (TILE_B_BYTES >> 4) + 2u * j, (kb > 0 || j > 0) ? 1u : 0u,
-                       idesc_for(BN));
+          // FUSE: the up tile follows the gate tile in shared memory (BN more rows of the same 8-row-group layout),
+          // so one MMA of N = 2 BN covers both and leaves gate in columns [0, BN), up in [BN, 2 BN)
+          mma_f16_ss(tmem_base, da + 2u * j, db + 2u * j, (kb > 0 || j > 0) ? 1u : 0u, idesc_for(SB));
         }
         mma_commit(empty(s));               // the stage is free once these MMAs have read it
       }
