@@ -433,7 +433,7 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
                                                          reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv, w.qr, kc, vc,
                                                          pos0, max_seq_len);
       if (l == num_layers - 1) break;   // the cache is complete; nothing downstream of the last layer is kept
-      causal_attention_mma<<<dim3((T + ATM_Q - 1) / ATM_Q, NKV), 128, ATM_SMEM_BYTES, stream>>>(w.qr, kc, vc, w.attn, T, pos0,
+      causal_attention_mma<<<dim3((T + ATM_Q - 1) / ATM_Q, NKV), ATM_THREADS, ATM_SMEM_BYTES, stream>>>(w.qr, kc, vc, w.attn, T, pos0,
                                                                                   max_seq_len, attn_scale);
       if ((rc = gemm(w.map_attn, l, 3, w.o, M, H, QS, T)) != QMK_OK) break;
       add_rmsnorm_rows<<<T, 256, 0, stream>>>(w.x, w.o, 1, 0, reinterpret_cast<const __half *>(r[7]), w.xn);
