@@ -550,6 +550,8 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
   const __half *cosv = static_cast<const __half *>(cos_table), *sinv = static_cast<const __half *>(sin_table);
   const size_t layer_stride = static_cast<size_t>(NKV) * max_seq_len * D;
   PF_CUDA(cudaMemsetAsync(w.status, 0, 16, stream));
+  // (the attention kernels leave their arrival counters at zero; a call that failed half-way may not have)
+  PF_CUDA(cudaMemsetAsync(w.split_count, 0, sizeof(unsigned int) * MAX_BATCH * NKV, stream));
   PF_CUDA(cudaMemcpyAsync(w.tokens, first_token_ids, sizeof(int) * B, cudaMemcpyHostToDevice, stream));
   PF_CUDA(cudaMemcpyAsync(w.positions, start_positions, sizeof(int) * B, cudaMemcpyHostToDevice, stream));
   PF_CUDA(cudaMemcpyAsync(w.start_positions, start_positions, sizeof(int) * B, cudaMemcpyHostToDevice, stream));
