@@ -493,7 +493,8 @@ __global__ void __launch_bounds__((DAR_WARPS + 1) * 32) decode_attention_ring(
       const unsigned char *sk = dar_smem + slot * DAR_SLOT_BYTES, *sv = sk + DAR_SLOT_BYTES / 2;
       if (ok && lane < nrow) {
         const uint32_t *krow = reinterpret_cast<const uint32_t *>(sk + lane * (D * 2));
-        sa = 0.f; sb = 0.f;
+        // packed fp32 FMAs (two lanes per instruction): even and odd dims accumulate separately
+        float2 sa2 = make_float2(0.f, 0.f), sb2 = make_float2(0.f, 0.f);
 #pragma unroll 16
         for (int d = 0; d < D / 2; ++d) {
           const int w = (d + lane) & (D / 2 - 1);      // lane-rotated word index: conflict-free at a 256-byte pitch
@@ -501,10 +502,10 @@ __global__ void __launch_bounds__((DAR_WARPS + 1) * 32) decode_attention_ring(
           const float2 kf = __half22float2(*reinterpret_cast<const __half2 *>(&kw));
           const float2 qa = *reinterpret_cast<const float2 *>(sq + 2 * w);
           const float2 qb = *reinterpret_cast<const float2 *>(sq + D + 2 * w);
-          sa = fmaf(qa.x, kf.x, sa); sa = fmaf(qa.y, kf.y, sa);
-          sb = fmaf(qb.x, kf.x, sb); sb = fmaf(qb.y, kf.y, sb);
+          sa2 = __ffma2_rn(qa, kf, sa2);
+          sb2 = __ffma2_rn(qb, kf, sb2);
         }
-        sa *= sc; sb *= sc;
+        sa = (sa2.x + sa2.y) * sc; sb = (sb2.x + sb2.y) * sc;
       }
       if (ok) {   // warp-uniform
         const float na = fmaxf(m0, warp_max(sa)), nb = fmaxf(m1, warp_max(sb));   // row 0 of a chunk always exists
@@ -513,19 +514,20 @@ __global__ void __launch_bounds__((DAR_WARPS + 1) * 32) decode_attention_ring(
         l0 = l0 * ca + warp_sum(pa);
         l1 = l1 * cb + warp_sum(pb);
         m0 = na; m1 = nb;
-#pragma unroll
-        for (int d = 0; d < 4; ++d) { a0[d] *= ca; a1[d] *= cb; }
+        float2 a0l = make_float2(a0[0] * ca, a0[1] * ca), a0h = make_float2(a0[2] * ca, a0[3] * ca);
+        float2 a1l = make_float2(a1[0] * cb, a1[1] * cb), a1h = make_float2(a1[2] * cb, a1[3] * cb);
 #pragma unroll 8
         for (int j = 0; j < nrow; ++j) {
           const float pja = __shfl_sync(0xffffffffu, pa, j), pjb = __shfl_sync(0xffffffffu, pb, j);
           const uint2 vv = *reinterpret_cast<const uint2 *>(sv + j * (D * 2) + lane * 8);
           const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&vv.x));
           const float2 v23 = __half22float2(*reinterpret_cast<const __half2 *>(&vv.y));
-          a0[0] = fmaf(pja, v01.x, a0[0]); a0[1] = fmaf(pja, v01.y, a0[1]);
-          a0[2] = fmaf(pja, v23.x, a0[2]); a0[3] = fmaf(pja, v23.y, a0[3]);
-          a1[0] = fmaf(pjb, v01.x, a1[0]); a1[1] = fmaf(pjb, v01.y, a1[1]);
-          a1[2] = fmaf(pjb, v23.x, a1[2]); a1[3] = fmaf(pjb, v23.y, a1[3]);
+          const float2 pa2 = make_float2(pja, pja), pb2 = make_float2(pjb, pjb);
+          a0l = __ffma2_rn(pa2, v01, a0l); a0h = __ffma2_rn(pa2, v23, a0h);
+          a1l = __ffma2_rn(pb2, v01, a1l); a1h = __ffma2_rn(pb2, v23, a1h);
         }
+        a0[0] = a0l.x; a0[1] = a0l.y; a0[2] = a0h.x; a0[3] = a0h.y;
+        a1[0] = a1l.x; a1[1] = a1l.y; a1[2] = a1h.x; a1[3] = a1h.y;
       }
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s32(empty + slot)) : "memory");
