@@ -603,10 +603,24 @@ __device__ __forceinline__ void load_w8(const unsigned char *row, int idx8, int 
     }
   }
 }
+// Packed FMAs pay in the multi-sequence build, where the row products are the limit (3 sequences 1879 -> 1924 tok/s,
+// 4 sequences with FP8 rows 2143 -> 2234); the single-sequence kernel measured the same within its run-to-run spread.
+#ifndef QMK_PACKED_FMA
+#define QMK_PACKED_FMA (QMK_MAX_SEQ > 1)
+#endif
+// acc + sum w[i] a[i].  Packed form: four fma.rn.f32x2 (even and odd terms accumulate in the two halves of a
+// register pair) and one add instead of eight scalar FMAs; the order of the sum is fixed either way.
 __device__ __forceinline__ float dot8f(const float (&w)[8], const float *a, float acc) {
+#if QMK_PACKED_FMA
+  float2 s2 = make_float2(acc, 0.f);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) s2 = __ffma2_rn(make_float2(w[2 * i], w[2 * i + 1]), make_float2(a[2 * i], a[2 * i + 1]), s2);
+  return s2.x + s2.y;
+#else
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc = fmaf(w[i], a[i], acc);
   return acc;
+#endif
 }
 // fp32 scale of an fp8 row (1 for fp16 rows): first word of the trailer behind the K weights
 __device__ __forceinline__ float row_scale(const unsigned char *row, int k, int wfmt) {
