@@ -128,7 +128,7 @@ int qmk_set_logits_dump(float *logits_out);
 int qmk_set_weight_format(int format);
 
 /* Performance knobs; negative keeps a value.  spin_sleep_ns: nanosleep between
- * polls of an exchange word (default 600).  l2_evict_first: 1 (default) streams
+ * polls of an exchange word (default: 600 for the unfused kernel, 0 for the fused one; setting it sets both).  l2_evict_first: 1 (default) streams
  * weights with an evict-first L2 policy, 0 uses the default policy. */
 int qmk_set_tuning(int spin_sleep_ns, int l2_evict_first);
 /* More knobs; negative keeps a value.  repl (1, 2 or 4): copies of the exchange
@@ -136,6 +136,22 @@ int qmk_set_tuning(int spin_sleep_ns, int l2_evict_first);
  * which divides the number of pollers per cache line (default 4).  stream_inflight: cap on
  * weight/KV chunks in flight per SM during the layer phases (0 = ring depth). */
 int qmk_set_tuning2(int repl, int stream_inflight);
+
+/* Kernel choice for one sequence (qmk_decode / qmk_generate / qmk_prefill); negative keeps a value.
+ *  fused  1 (default): the fused kernel - the O and down projections run as split-K slices on the CTAs that
+ *         produced their inputs, and the two residual sums of a layer are all-reduced in 64-bit integer
+ *         accumulators (four cross-CTA hand-overs per layer).  It reads K-major copies of W_o and W_down that
+ *         the library makes from the caller's matrices (294 MB for 28 fp16 layers) on the first call with a
+ *         layer table and re-checks by sampled hashes on every call.  Grids below 74 CTAs and
+ *         qmk_generate_static use the unfused kernel (six hand-overs, no copies).  0: always unfused.
+ *  red_copies  1 or 2 accumulator copies per sum (2 halves the same-address add queue, doubles the words read).
+ * The reference has neither (its layer is eight grid barriers, megakernel_5090.cu:879-915). */
+int qmk_set_fused(int fused, int red_copies);
+/* Marks every K-major copy on the current device stale: the next call rebuilds it.  Needed only after editing
+ * W_o / W_down in place in a way the sampled hashes may miss. */
+int qmk_invalidate_weights(void);
+/* Frees the K-major copies made for this layer table (null: all tables) on the current device. */
+int qmk_release_weights(const struct LDGLayerWeight *layer_weights);
 
 /* Debug: when non-null, every CTA writes globaltimer stamps (ns) of the phase
  * boundaries of the LAST step of each launch to timestamps[cta * 768 + slot]

@@ -223,9 +223,11 @@ struct SegTab {
   int nrows[NKIND][3];
   int out0[NKIND][3];    // index of the first output element
   int e0, e1;            // attention outputs this CTA merges when KV is split
+  int n0, n1;            // fused kernel: outputs of the hidden vector whose residual this CTA adds into the sums
   int long_phase;        // some projection phase (QKV .. down) has more chunks here than the ring has slots
 };
-constexpr size_t SMEM_BYTES = OFF_SEGS + ((sizeof(SegTab) + 63) / 64) * 64;
+constexpr size_t OFF_LAYERS_T = OFF_SEGS + ((sizeof(SegTab) + 63) / 64) * 64;   // fused kernel: K-major pointers, 2 x u64 per layer
+constexpr size_t SMEM_BYTES = OFF_LAYERS_T + MAX_LAYERS * sizeof(qmkp::LayerT);
 static_assert((I + CONS_THREADS - 1) / CONS_THREADS <= 8, "poll_vec handles at most 8 words per thread");
 static_assert(SMEM_BYTES <= 232448, "over the 227 KB shared-memory limit of one CTA");
 static_assert(OFF_FULL % 8 == 0 && OFF_LAYERS % 16 == 0 && OFF_NORMS % 16 == 0, "shared-memory alignment");
@@ -253,6 +255,9 @@ struct Ctx {
   __device__ __forceinline__ volatile int *flags() const { return reinterpret_cast<volatile int *>(smem + OFF_FLAGS); }
   __device__ __forceinline__ const unsigned long long *layer_rec(int l) const {
     return reinterpret_cast<const unsigned long long *>(smem + OFF_LAYERS) + l * 12;
+  }
+  __device__ __forceinline__ const unsigned long long *layer_rec_t(int l) const {
+    return reinterpret_cast<const unsigned long long *>(smem + OFF_LAYERS_T) + l * 2;
   }
   __device__ __forceinline__ const SegTab *segs() const { return reinterpret_cast<const SegTab *>(smem + OFF_SEGS); }
   __device__ __forceinline__ unsigned char *slot(uint32_t idx) const { return smem + static_cast<size_t>(idx % NSLOTS) * SLOT_BYTES; }
@@ -427,6 +432,7 @@ __host__ __device__ inline void build_segtab(SegTab *t, int cta, int ncta, int v
     if (r0 < r1) { t->nseg[k] = 1; t->tsel[k][0] = rec[k]; t->row0[k][0] = r0; t->nrows[k][0] = r1 - r0; t->out0[k][0] = r0; }
   }
   split_rows(QS, ncta, cta, t->e0, t->e1);
+  split_rows(H, ncta, cta, t->n0, t->n1);
   t->long_phase = 0;
   for (int k = K_QKV; k <= K_DOWN; ++k) {
     const int rpc = kind_rpc(k);
@@ -480,6 +486,18 @@ __device__ __forceinline__ AttnItem attn_item(const Params &P, const Ctx &c, int
   it.nchunks = (rows + it.rpc - 1) / it.rpc;
   return it;
 }
+
+// Debug build only (-DQMK_FINE_PROF): cycle stamps inside the phases of ONE layer (flags()[8] != 0 marks it),
+// written by thread 0 to slots 400 + i of its CTA's profile row.
+#ifdef QMK_FINE_PROF
+#define QMK_FINE(i)                                                                               \
+  do {                                                                                            \
+    if (P.prof && c.tid == 0 && c.flags()[8])                                                     \
+      P.prof[static_cast<size_t>(c.cta) * PROF_STRIDE + 400 + (i)] = static_cast<unsigned long long>(clock64()); \
+  } while (0)
+#else
+#define QMK_FINE(i) do { } while (0)
+#endif
 
 // ----------------------------------------------------------------------------- producer (one thread)
 __device__ __forceinline__ bool produce_chunk(const Params &P, const Ctx &c, uint32_t &idx, uint64_t pol,
@@ -752,10 +770,14 @@ __device__ __forceinline__ void norm_to_regs(const Ctx &c, const float *x, float
 // even when it is never taken, hence a separate copy (and kernel entry point) for grids that need it.
 template <bool GATED>
 __device__ __noinline__ uint32_t gemv_k1024(const Params &P, Ctx c, int kind, const float *x, float ss,
-                                            const __half *norm_w, unsigned long long *out, uint32_t tag, float *dump) {
+                                            const __half *norm_w, unsigned long long *out, uint32_t tag, float *dump,
+                                            float *local_out = nullptr) {
   const int wfmt = P.wfmt;
   float a[32];
+  const int fb = kind == K_QKV ? 0 : 10;
+  QMK_FINE(fb + 0);
   norm_to_regs(c, x, ss, norm_w, a);
+  QMK_FINE(fb + 1);
   if (kind == K_LM && c.cta == 0 && c.warp == 0 && (P.normalized_out || P.hidden_out)) {  // reference-signature outputs
 #pragma unroll
     for (int j = 0; j < 4; ++j)
@@ -803,6 +825,7 @@ __device__ __noinline__ uint32_t gemv_k1024(const Params &P, Ctx c, int kind, co
         }
       }
       ok = __all_sync(0xffffffffu, ok);   // the whole warp takes the same branch (shuffles follow)
+      if (kind != K_LM) QMK_FINE(fb + 2);
 #pragma unroll
       for (int b = 0; b < NB; ++b) {
         v[b] = 0.f;
@@ -817,6 +840,7 @@ __device__ __noinline__ uint32_t gemv_k1024(const Params &P, Ctx c, int kind, co
       // The rows are in registers now: hand the slots back BEFORE publishing (mbarrier.arrive has
       // release semantics and would otherwise wait for the global stores).  The RPC warps mapped to a
       // chunk each return EMPTY_UNITS/RPC units, whether or not their row exists (a short last chunk).
+      if (kind != K_LM) QMK_FINE(fb + 3);
       __syncwarp();
       if (c.lane == 0) {
 #pragma unroll
@@ -838,11 +862,14 @@ __device__ __noinline__ uint32_t gemv_k1024(const Params &P, Ctx c, int kind, co
         if (kind == K_LM) {
           if (r > best || (r == best && o < best_i)) { best = r; best_i = o; }
           if (dump) dump[o] = r;
+        } else if (local_out) {
+          local_out[o - out0] = r;                                  // fused kernel: the row's result stays in this CTA
         } else {
           ll_publish(out + o, r, tag, c.repl);                      // one store instruction covers the NB rows
         }
       }
       if (pass_gate) cons_sync();
+      if (kind != K_LM) QMK_FINE(fb + 4);
     }
     c.chunk += static_cast<uint32_t>(nchunks);
   }
@@ -924,6 +951,8 @@ __device__ __noinline__ uint32_t gemv_wide(const Params &P, Ctx c, int kind, con
 // Work item (kv head g, split s) on CTA g + 8*s: old cache rows [p0, p1); the last split also
 // normalises/rotates/stores the new K,V row and folds it in.  Writes either the final head
 // outputs (one split) or unnormalised partials.
+// FUSED: unnormalised partials also when there is one split (the merge follows in every case).
+template <bool FUSED>
 __device__ __noinline__ uint32_t attention_phase(const Params &P, Ctx c, const __half *nv, int layer, int pos,
                                                  uint32_t tag) {
   const AttnItem it = attn_item(P, c, 0, 1, CONS_WARPS, pos);
@@ -936,6 +965,7 @@ __device__ __noinline__ uint32_t attention_phase(const Params &P, Ctx c, const _
   const int p0 = it.p0, p1 = it.p1;
   const size_t head_base = (static_cast<size_t>(layer) * NKV + g) * static_cast<size_t>(P.max_seq_len) * D;
 
+  QMK_FINE(60);
   // (1) head preparation: warps 0,1 = the two query heads; owner: warp 2 = K, warp 3 = V
   if (c.warp < 2 || (owner && c.warp < 4)) {
     const int w = c.warp, lane = c.lane;
@@ -974,7 +1004,9 @@ __device__ __noinline__ uint32_t attention_phase(const Params &P, Ctx c, const _
       for (int i = 0; i < 4; ++i) snew[lane + 32 * i] = __half2float(__float2half_rn(v[i]));
     }
   }
+  QMK_FINE(61);
   cons_sync();
+  QMK_FINE(62);
 
   const float sc_log2 = P.attn_scale * 1.4426950408889634f;
   // score of the new row (owner only), by warps 0 and 1
@@ -1054,6 +1086,7 @@ __device__ __noinline__ uint32_t attention_phase(const Params &P, Ctx c, const _
     if (pass_gate) cons_sync();
   }
   c.chunk += static_cast<uint32_t>(it.nchunks);
+  QMK_FINE(63);
   // (3) merge the 2 row groups of the warp (rows differ, dims match for equal `seg`)
   __syncwarp();
   {
@@ -1079,7 +1112,9 @@ __device__ __noinline__ uint32_t attention_phase(const Params &P, Ctx c, const _
     for (int i = 0; i < 8; ++i) { w0[seg * 8 + i] = a0[i]; w1[seg * 8 + i] = a1[i]; }
     if (seg == 0) { w0[D] = m0; w0[D + 1] = l0; w1[D] = m1; w1[D + 1] = l1; }
   }
+  QMK_FINE(64);
   cons_sync();
+  QMK_FINE(65);
   // (4) merge the 16 warps (+ the new row) per (head, dim)
   if (c.tid < 2 * D) {
     const int h = c.tid >> 7, d = c.tid & (D - 1);
@@ -1101,7 +1136,7 @@ __device__ __noinline__ uint32_t attention_phase(const Params &P, Ctx c, const _
       }
     }
     const int hq = 2 * g + h;
-    if (S == 1) {
+    if (!FUSED && S == 1) {
       ll_publish(P.ll + LL_ATTN + hq * D + d, A / L, tag, c.repl);
     } else {
       unsigned long long *part = P.ll + LL_PART + static_cast<size_t>(hq * MAX_SPLITS + s) * PART_STRIDE;
@@ -1109,6 +1144,7 @@ __device__ __noinline__ uint32_t attention_phase(const Params &P, Ctx c, const _
       if (d == 0) { ll_publish(part + D, M, tag, c.repl); ll_publish(part + D + 1, L, tag, c.repl); }
     }
   }
+  QMK_FINE(66);
   // New K,V row -> cache (megakernel_5090.cu:392-397), off the critical path.  The fence orders
   // the row before the exchange words this CTA publishes later; readers fence once per step.
   if (owner && (c.warp == 2 || c.warp == 3)) {
@@ -1240,7 +1276,7 @@ __device__ __forceinline__ void decode_body(const Params &P) {
         c.chunk = gemv_k1024<GATED>(P, c, K_QKV, s_x, ss, nv + NB_IN_LN, P.ll + LL_QKV, tag, nullptr);
         // P2/P3: attention work items, then merge of split partials
         QMK_STAMP(layer * 12 + 1);
-        c.chunk = attention_phase(P, c, nv, layer, pos, tag);
+        c.chunk = attention_phase<false>(P, c, nv, layer, pos, tag);
         QMK_STAMP(layer * 12 + 2);
         if (S_step > 1) attention_merge(P, c, S_step, tag);
         QMK_STAMP(layer * 12 + 3);

@@ -14,6 +14,15 @@ struct __align__(16) LayerW {
   const void *pad;
 };
 
+// K-major copies of the two projections whose input is produced slice by slice (O: the attention output, down:
+// the MLP activations).  The library makes them from the caller's [out,in] matrices: row e of wo_t holds
+// W_o[:, e], row m of wd_t holds W_down[:, m] (1024 outputs each), so that the rows a CTA needs for ITS slice of
+// the input form one contiguous range.  fp8 format: 1024 e4m3 bytes per row, the per-output fp32 scales of the
+// matrix follow the last row.
+struct __align__(16) LayerT {
+  const void *wo_t, *wd_t;
+};
+
 constexpr int MAX_SEQ = 4;       // sequences one launch of the multi-sequence build can carry
 
 struct Params {
@@ -52,6 +61,11 @@ struct Params {
   int start_positions[MAX_SEQ];
   __half *k_caches[MAX_SEQ], *v_caches[MAX_SEQ];
   int *output_logs[MAX_SEQ];     // decode: token per step of each sequence
+  // Fused single-sequence kernel only (null / 0 elsewhere).
+  const LayerT *layers_t;        // K-major copies, one record per layer
+  unsigned long long *red;       // all-reduce words of the two residual sums, zeroed by the host before the launch
+  int red_copies;                // accumulator copies per sum (1 or 2): CTA i adds into copy i % red_copies
+  int ll_sleep_ns;               // back-off between polls of the small (few-reader) exchanges
 };
 
 }  // namespace qmkp

@@ -34,6 +34,7 @@
 #include <math.h>
 #include <mutex>
 #include <string>
+#include <vector>
 
 #include "../../include/qwen_megakernel.h"
 
@@ -42,6 +43,7 @@
 #define QMK_NS qmk
 #define QMK_MAX_SEQ 1
 #include "megakernel_device.cuh"
+#include "megakernel_fused.cuh"
 #include "megakernel_batch.h"
 #include "engine_internal.h"
 
@@ -72,6 +74,78 @@ __global__ void wait_timeout_probe(const __grid_constant__ Params P, unsigned lo
     c.llr = word;
     c.flags()[0] = 0;
     ll_wait(P, c, word, 0xfffffff0u);
+  }
+}
+
+// ---- K-major copies of W_o and W_down for the fused kernel ------------------------------------------------
+// One launch both checks and (re)builds them, so that nothing on the host has to wait for the answer: CTA group
+// (layer, matrix) hashes 256 sampled 16-byte pieces of the caller's matrix (and its address), compares the hash
+// with the one stored when the copy was made, and transposes again when they differ.  The hashes live in two
+// arrays used in turn (read `parity`, write `parity ^ 1`), so that the CTA that stores the new hash cannot change
+// what the other CTAs of its group compare against.  A change confined to unsampled elements goes unnoticed:
+// callers that edit weights in place call qmk_invalidate_weights().
+constexpr int PREP_SUB = 16;      // CTAs per matrix
+struct PrepArgs {
+  const LayerW *layers;           // the caller's table (device)
+  const qmkp::LayerT *out;        // destinations (device)
+  unsigned long long *fp;         // [2][2 * num_layers] hashes
+  int num_layers, wfmt, parity, force;
+};
+__global__ void __launch_bounds__(256) kmajor_prepare_kernel(const PrepArgs a) {
+  __shared__ unsigned long long s_hash;
+  __shared__ int s_redo;
+  __shared__ unsigned short tile16[32][33];
+  __shared__ unsigned char tile8[32][33];
+  const int m = blockIdx.y, l = m >> 1, which = m & 1, t = threadIdx.x;
+  const int K = which ? I : QS;                       // inputs of the projection = rows of the K-major copy
+  const unsigned char *src = reinterpret_cast<const unsigned char *>(which ? a.layers[l].w_down : a.layers[l].wo);
+  unsigned char *dst = reinterpret_cast<unsigned char *>(const_cast<void *>(which ? a.out[l].wd_t : a.out[l].wo_t));
+  const size_t in_row = a.wfmt ? static_cast<size_t>(K) + FP8_TRAILER : static_cast<size_t>(K) * 2;
+  const size_t n16 = in_row * H / 16;
+  if (t == 0) s_hash = reinterpret_cast<unsigned long long>(src) * 0x9E3779B97F4A7C15ull;
+  __syncthreads();
+  {
+    const size_t per = n16 / 256;
+    const size_t i16 = static_cast<size_t>(t) * per + (static_cast<size_t>(t) * 37u) % per;
+    const uint4 v = __ldg(reinterpret_cast<const uint4 *>(src) + i16);
+    unsigned long long h = (static_cast<unsigned long long>(v.x) << 32 | v.y) * 0xD6E8FEB86659FD93ull;
+    h ^= (static_cast<unsigned long long>(v.z) << 32 | v.w) * 0xA0761D6478BD642Full;
+    h = (h ^ (h >> 29)) * (2ull * static_cast<unsigned long long>(t) + 1ull);
+    atomicAdd(&s_hash, h);
+  }
+  __syncthreads();
+  const unsigned long long hash = s_hash;
+  const int M = 2 * a.num_layers;
+  if (t == 0) {
+    s_redo = (a.force || a.fp[static_cast<size_t>(a.parity) * M + m] != hash) ? 1 : 0;
+    if (blockIdx.x == 0) a.fp[static_cast<size_t>(a.parity ^ 1) * M + m] = hash;
+  }
+  __syncthreads();
+  if (!s_redo) return;
+  const int tx = t & 31, ty = t >> 5;                 // 32 x 8 threads, four rows each per tile
+  const int ntiles = (H / 32) * (K / 32);
+  for (int tile = blockIdx.x; tile < ntiles; tile += PREP_SUB) {
+    const int tn = tile % (H / 32), tk = tile / (H / 32);
+    if (a.wfmt == 0) {
+      const unsigned short *in = reinterpret_cast<const unsigned short *>(src);
+      unsigned short *out = reinterpret_cast<unsigned short *>(dst);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) tile16[ty + 8 * i][tx] = in[static_cast<size_t>(tn * 32 + ty + 8 * i) * K + tk * 32 + tx];
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) out[static_cast<size_t>(tk * 32 + ty + 8 * i) * H + tn * 32 + tx] = tile16[tx][ty + 8 * i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) tile8[ty + 8 * i][tx] = src[static_cast<size_t>(tn * 32 + ty + 8 * i) * in_row + tk * 32 + tx];
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) dst[static_cast<size_t>(tk * 32 + ty + 8 * i) * H + tn * 32 + tx] = tile8[tx][ty + 8 * i];
+    }
+    __syncthreads();
+  }
+  if (a.wfmt && blockIdx.x == 0) {                    // per-output scales follow the K rows
+    float *sc = reinterpret_cast<float *>(dst + static_cast<size_t>(K) * H);
+    for (int n = t; n < H; n += 256) sc[n] = *reinterpret_cast<const float *>(src + static_cast<size_t>(n) * in_row + K);
   }
 }
 
@@ -123,6 +197,21 @@ struct Engine {
   int repl = 4;              // measured: 835 -> 752 us/token at short context, 1152 -> 1061 at 4096
   int stream_inflight = 0;   // measured: pacing the stream changes nothing
   bool inv_freq_set = false;
+  // fused single-sequence kernel (megakernel_fused.cuh)
+  int fused = 1;             // 0: always the unfused kernel
+  int red_copies = 1;
+  int fused_sleep_ns = 0;    // measured at 4096-token context: 600 ns 1224 tok/s, 200 ns 1259, 0 ns 1305 (few pollers per word)
+  unsigned long long *red = nullptr;   // the two residual sums
+  struct Prepared {          // K-major copies of W_o / W_down of one caller table
+    const void *table = nullptr;
+    int num_layers = 0, wfmt = 0, parity = 0, force = 1;
+    unsigned char *buf = nullptr;
+    qmkp::LayerT *tbl = nullptr;
+    unsigned long long *fp = nullptr;
+    unsigned long long last_use = 0;
+  };
+  std::vector<Prepared> prepared;
+  unsigned long long use_clock = 0;
 };
 
 constexpr int MAX_DEVICES = 16;
@@ -174,6 +263,8 @@ int ensure_ready(Engine *e) {
                                    static_cast<int>(qmk::SMEM_BYTES)));
   QMK_CUDA(e, cudaFuncSetAttribute(qmk::wait_timeout_probe, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(qmk::SMEM_BYTES)));
+  QMK_CUDA(e, cudaFuncSetAttribute(qmk::qwen3_decode_megakernel_fused, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(qmk::SMEM_BYTES)));
   int per_sm = 0;
   QMK_CUDA(e, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, qmk::qwen3_decode_megakernel, qmk::THREADS,
                                                             qmk::SMEM_BYTES));
@@ -186,6 +277,7 @@ int ensure_ready(Engine *e) {
   QMK_CUDA(e, cudaMemset(e->ll, 0, exchange_bytes()));
   QMK_CUDA(e, cudaMalloc(&e->status, 16));
   QMK_CUDA(e, cudaMemset(e->status, 0, 16));
+  QMK_CUDA(e, cudaMalloc(&e->red, sizeof(unsigned long long) * qmk::RED_WORDS));
   QMK_CUDA(e, cudaHostAlloc(&e->status_host, 16, cudaHostAllocDefault));
   memset(e->status_host, 0, 16);
   if (!e->inv_freq_set) {
@@ -228,6 +320,73 @@ int ensure_rope(Engine *e, int max_seq_len, cudaStream_t stream) {
   qmk::rope_table_kernel<<<(cap * (qmk::D / 2) + 255) / 256, 256, 0, stream>>>(e->rope, cap);
   QMK_CUDA(e, cudaGetLastError());
   e->rope_cap = cap;
+  return QMK_OK;
+}
+
+// Bytes of the K-major copies of one layer: O rows then down rows (fp8: each followed by 1024 fp32 scales).
+size_t kmajor_o_bytes(int wfmt) {
+  const size_t b = wfmt ? static_cast<size_t>(qmk::QS) * qmk::H + qmk::H * 4 : static_cast<size_t>(qmk::QS) * qmk::H * 2;
+  return (b + 255) / 256 * 256;
+}
+size_t kmajor_d_bytes(int wfmt) {
+  const size_t b = wfmt ? static_cast<size_t>(qmk::I) * qmk::H + qmk::H * 4 : static_cast<size_t>(qmk::I) * qmk::H * 2;
+  return (b + 255) / 256 * 256;
+}
+void free_prepared(Engine::Prepared &p) {
+  if (p.buf) cudaFree(p.buf);
+  if (p.tbl) cudaFree(p.tbl);
+  if (p.fp) cudaFree(p.fp);
+  p = Engine::Prepared();
+}
+constexpr size_t MAX_PREPARED = 4;   // weight sets kept per device (a 28-layer fp16 set is 294 MB)
+
+// Finds or creates the K-major copies for the caller's layer table and enqueues the check-and-rebuild kernel.
+int ensure_prepared(Engine *e, const Params &P, int wfmt, cudaStream_t stream, Engine::Prepared **out) {
+  Engine::Prepared *hit = nullptr;
+  for (auto &p : e->prepared)
+    if (p.table == P.layers && p.num_layers == P.num_layers && p.wfmt == wfmt) hit = &p;
+  if (!hit) {
+    if (e->prepared.size() >= MAX_PREPARED) {   // drop the set used longest ago
+      size_t victim = 0;
+      for (size_t i = 1; i < e->prepared.size(); ++i)
+        if (e->prepared[i].last_use < e->prepared[victim].last_use) victim = i;
+      QMK_CUDA(e, cudaDeviceSynchronize());
+      free_prepared(e->prepared[victim]);
+      e->prepared.erase(e->prepared.begin() + static_cast<long>(victim));
+    }
+    Engine::Prepared p;
+    p.table = P.layers;
+    p.num_layers = P.num_layers;
+    p.wfmt = wfmt;
+    const size_t ob = kmajor_o_bytes(wfmt), db = kmajor_d_bytes(wfmt);
+    QMK_CUDA(e, cudaMalloc(&p.buf, (ob + db) * P.num_layers));
+    QMK_CUDA(e, cudaMalloc(&p.tbl, sizeof(qmkp::LayerT) * P.num_layers));
+    QMK_CUDA(e, cudaMalloc(&p.fp, sizeof(unsigned long long) * 4 * P.num_layers));
+    QMK_CUDA(e, cudaMemsetAsync(p.fp, 0, sizeof(unsigned long long) * 4 * P.num_layers, stream));
+    std::vector<qmkp::LayerT> host(P.num_layers);
+    for (int l = 0; l < P.num_layers; ++l) {
+      host[l].wo_t = p.buf + (ob + db) * l;
+      host[l].wd_t = p.buf + (ob + db) * l + ob;
+    }
+    QMK_CUDA(e, cudaMemcpyAsync(p.tbl, host.data(), sizeof(qmkp::LayerT) * P.num_layers, cudaMemcpyHostToDevice, stream));
+    QMK_CUDA(e, cudaStreamSynchronize(stream));   // `host` goes out of scope
+    e->prepared.push_back(p);
+    hit = &e->prepared.back();
+  }
+  hit->last_use = ++e->use_clock;
+  qmk::PrepArgs a;
+  a.layers = P.layers;
+  a.out = hit->tbl;
+  a.fp = hit->fp;
+  a.num_layers = P.num_layers;
+  a.wfmt = wfmt;
+  a.parity = hit->parity;
+  a.force = hit->force;
+  qmk::kmajor_prepare_kernel<<<dim3(qmk::PREP_SUB, 2 * P.num_layers), 256, 0, stream>>>(a);
+  QMK_CUDA(e, cudaGetLastError());
+  hit->parity ^= 1;
+  hit->force = 0;
+  *out = hit;
   return QMK_OK;
 }
 
@@ -291,11 +450,24 @@ int launch(Engine *e, Params &P, cudaStream_t stream, bool synchronize, bool bat
 
   void *args[] = {&P};
   const int grid = grid_for(e);
+  const void *kernel = batch ? qmk_batch::kernel() : single_sequence_kernel(grid);
+  if (!batch && e->fused && grid >= qmk::FUSED_MIN_CTAS &&
+      kernel == reinterpret_cast<const void *>(qmk::qwen3_decode_megakernel)) {
+    // fused kernel: O and down projections as split-K slices of K-major copies, two all-reduced residual sums
+    Engine::Prepared *prep = nullptr;
+    rc = ensure_prepared(e, P, e->wfmt, stream, &prep);
+    if (rc != QMK_OK) return rc;
+    QMK_CUDA(e, cudaMemsetAsync(e->red, 0, sizeof(unsigned long long) * qmk::RED_WORDS, stream));
+    P.layers_t = prep->tbl;
+    P.red = e->red;
+    P.red_copies = e->red_copies;
+    P.spin_sleep_ns = e->fused_sleep_ns;
+    kernel = reinterpret_cast<const void *>(qmk::qwen3_decode_megakernel_fused);
+  }
   cudaError_t err =
-      batch ? cudaLaunchCooperativeKernel(qmk_batch::kernel(), dim3(grid), dim3(qmk_batch::threads()), args,
+      batch ? cudaLaunchCooperativeKernel(kernel, dim3(grid), dim3(qmk_batch::threads()), args,
                                           qmk_batch::smem_bytes(), stream)
-            : cudaLaunchCooperativeKernel(single_sequence_kernel(grid), dim3(grid), dim3(qmk::THREADS), args,
-                                          qmk::SMEM_BYTES, stream);
+            : cudaLaunchCooperativeKernel(kernel, dim3(grid), dim3(qmk::THREADS), args, qmk::SMEM_BYTES, stream);
   if (err == cudaErrorCooperativeLaunchTooLarge)
     return fail(e, QMK_ERR_NOT_RESIDENT, "persistent grid cannot be co-resident on this device");
   if (err != cudaSuccess) return fail(e, QMK_ERR_CUDA, std::string("cudaLaunchCooperativeKernel: ") + cudaGetErrorString(err));
@@ -420,8 +592,42 @@ int qmk_set_tuning(int spin_sleep_ns, int l2_evict_first) {
   std::lock_guard<std::mutex> lock(g_mutex);
   Engine *e = current_engine_unlocked();
   if (!e) return QMK_ERR_CUDA;
-  if (spin_sleep_ns >= 0) e->spin_sleep_ns = spin_sleep_ns > 10000 ? 10000 : spin_sleep_ns;
+  if (spin_sleep_ns >= 0) e->spin_sleep_ns = e->fused_sleep_ns = spin_sleep_ns > 10000 ? 10000 : spin_sleep_ns;
   if (l2_evict_first >= 0) e->l2_evict_first = l2_evict_first ? 1 : 0;
+  return QMK_OK;
+}
+
+int qmk_set_fused(int fused, int red_copies) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  Engine *e = current_engine_unlocked();
+  if (!e) return QMK_ERR_CUDA;
+  if (fused >= 0) e->fused = fused ? 1 : 0;
+  if (red_copies == 1 || red_copies == 2) e->red_copies = red_copies;
+  else if (red_copies >= 0) return fail(e, QMK_ERR_BAD_ARGUMENT, "red_copies must be 1 or 2");
+  return QMK_OK;
+}
+
+int qmk_invalidate_weights(void) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  Engine *e = current_engine_unlocked();
+  if (!e) return QMK_ERR_CUDA;
+  for (auto &p : e->prepared) p.force = 1;
+  return QMK_OK;
+}
+
+int qmk_release_weights(const LDGLayerWeight *layer_weights) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  Engine *e = current_engine_unlocked();
+  if (!e) return QMK_ERR_CUDA;
+  for (size_t i = 0; i < e->prepared.size();) {
+    if (layer_weights == nullptr || e->prepared[i].table == layer_weights) {
+      QMK_CUDA(e, cudaDeviceSynchronize());
+      free_prepared(e->prepared[i]);
+      e->prepared.erase(e->prepared.begin() + static_cast<long>(i));
+    } else {
+      ++i;
+    }
+  }
   return QMK_OK;
 }
 

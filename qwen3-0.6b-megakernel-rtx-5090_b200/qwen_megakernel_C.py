@@ -56,6 +56,11 @@ _lib.qmk_set_tuning2.argtypes = [_I, _I]
 _lib.qmk_set_tuning2.restype = _I
 _lib.qmk_set_profile_buffer.argtypes = [_P]
 _lib.qmk_set_profile_buffer.restype = _I
+_lib.qmk_set_fused.argtypes = [_I, _I]
+_lib.qmk_set_fused.restype = _I
+_lib.qmk_invalidate_weights.restype = _I
+_lib.qmk_release_weights.argtypes = [_P]
+_lib.qmk_release_weights.restype = _I
 _lib.qmk_decode.argtypes = [_I, _P, *([_P] * 12), _I, _I, _I, _F, _P]
 _lib.qmk_decode.restype = _I
 _lib.qmk_generate.argtypes = [_I, _I, *([_P] * 12), _P, _I, _I, _I, _F, _I, _I, _P]
@@ -84,7 +89,7 @@ _lib.qmk_selftest_gemm_wait_timeout.restype = _I
 EXPORTED_SYMBOLS = (
     "launch_ldg_decode_direct", "launch_ldg_decode_persistent", "launch_ldg_generate_nosync",
     "launch_ldg_prefill", "qmk_abi_version", "qmk_configure", "qmk_set_inv_freq", "qmk_set_logits_dump",
-    "qmk_set_weight_format", "qmk_set_tuning", "qmk_set_tuning2", "qmk_set_profile_buffer", "qmk_decode", "qmk_generate", "qmk_generate_static", "qmk_generate_batch", "qmk_gemm_f16_tn", "qmk_decode_batched", "qmk_prefill_chunked", "qmk_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
+    "qmk_set_weight_format", "qmk_set_tuning", "qmk_set_tuning2", "qmk_set_profile_buffer", "qmk_set_fused", "qmk_invalidate_weights", "qmk_release_weights", "qmk_decode", "qmk_generate", "qmk_generate_static", "qmk_generate_batch", "qmk_gemm_f16_tn", "qmk_decode_batched", "qmk_prefill_chunked", "qmk_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
     "qmk_scratch_bytes", "qmk_selftest_wait_timeout", "qmk_selftest_gemm_wait_timeout",
 )
 
@@ -228,6 +233,27 @@ def set_weight_format(fmt) -> None:
 
 
 PROFILE_STRIDE = 768
+
+
+def set_fused(fused=-1, red_copies=-1) -> None:
+    """Single-sequence kernel choice: fused (default) or unfused; accumulator copies of the fused kernel's sums."""
+    _require_cuda()
+    if _lib.qmk_set_fused(int(fused), int(red_copies)) != 0:
+        _raise_if_failed("set_fused")
+
+
+def invalidate_weights() -> None:
+    """After editing W_o / W_down in place: the fused kernel's K-major copies are rebuilt at the next call."""
+    _require_cuda()
+    if _lib.qmk_invalidate_weights() != 0:
+        _raise_if_failed("invalidate_weights")
+
+
+def release_weights(layer_weights_packed=None) -> None:
+    """Frees the K-major copies made for this layer table (None: for all tables) on the current device."""
+    _require_cuda()
+    if _lib.qmk_release_weights(_ptr(layer_weights_packed)) != 0:
+        _raise_if_failed("release_weights")
 
 
 def set_profile_buffer(buf) -> None:

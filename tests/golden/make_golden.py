@@ -14,6 +14,9 @@ Files written:
                              per-step top-8 logits, greedy margins (fp16 KV cache,
                              the oracle default), and the tokens / max logit shift
                              of the same run with an fp32 cache.
+  full_seed0_prompt4096.json the benchmarked configuration: same model, prompt = make_prompt(4096,
+                             seed 0) (4095 tokens prefilled in chunks, decode from the last one);
+                             8 greedy tokens, per-step top-8 logits and greedy margins.
   tiny_l2_v4096.npz          2 layers, vocab 4096, norm_std 0.1, seed 3:
                              prompt 12 tokens, 8 greedy tokens, logits per step,
                              and the per-phase trace of the first decode step.
@@ -39,6 +42,10 @@ TINY = dict(seed=3, num_layers=2, vocab_size=4096, norm_std=0.1, prompt_len=12, 
             max_seq_len=64)
 FULL = dict(seed=0, num_layers=28, vocab_size=151936, norm_std=0.0, prompt_len=32, prompt_seed=0, steps=32,
             max_seq_len=128)
+
+
+FULL4096 = dict(seed=0, num_layers=28, vocab_size=151936, norm_std=0.0, prompt_len=4096, prompt_seed=0, steps=8,
+                max_seq_len=4352)
 
 
 def run(cfg, kv_dtype=torch.float16, trace_first=False):
@@ -86,11 +93,26 @@ def make_full():
           "max logit diff", doc["fp32_kv_max_abs_logit_diff"])
 
 
+def make_full_ctx4096():
+    ids, toks, logits, _ = run(FULL4096)
+    top = torch.topk(logits, 8, dim=-1)
+    margins = (top.values[:, 0] - top.values[:, 1]).tolist()
+    doc = dict(config=FULL4096, prompt_seed=FULL4096["prompt_seed"], prompt_len=len(ids), prompt_head=ids[:8],
+               prompt_tail=ids[-8:], tokens=toks,
+               top8_values=[[float(x) for x in r] for r in top.values.tolist()],
+               top8_indices=top.indices.tolist(), margins=margins, min_margin=min(margins))
+    with open(os.path.join(HERE, "full_seed0_prompt4096.json"), "w") as f:
+        json.dump(doc, f, indent=1)
+    print("ctx4096 tokens", toks, "margins", margins)
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", choices=["tiny", "full"])
+    ap.add_argument("--only", choices=["tiny", "full", "ctx4096"])
     a = ap.parse_args()
     if a.only in (None, "tiny"):
         make_tiny()
     if a.only in (None, "full"):
         make_full()
+    if a.only in (None, "ctx4096"):
+        make_full_ctx4096()

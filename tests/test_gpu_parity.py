@@ -239,3 +239,91 @@ def test_full_model_32_greedy_steps_match_oracle(C, full_cfg):
     finally:
         C.set_logits_dump(None)
     assert torch.equal(dump, dump2)
+
+
+def _golden_ctx4096():
+    return json.load(open(os.path.join(GOLDEN, "full_seed0_prompt4096.json")))
+
+
+@pytest.mark.parametrize("prefill_mode", ["serial", "tensor"])
+def test_benchmark_configuration_matches_golden(C, prefill_mode):
+    """The configuration bench.py times (full model, seed 0, make_prompt(4096, seed 0), max_seq_len 4352):
+    first 8 greedy tokens identical to the oracle's golden file, their top-8 logits within 3e-2.  Both prefill
+    paths: the token-serial op (fp32 activations) and the chunked tensor-core prefill (fp16 GEMM operands)."""
+    g = _golden_ctx4096()
+    cfg = g["config"]
+    ids = S.make_prompt(cfg["prompt_len"], seed=cfg["prompt_seed"])
+    assert ids[:8] == g["prompt_head"] and ids[-8:] == g["prompt_tail"]
+    w = S.make_weights(seed=cfg["seed"], num_layers=cfg["num_layers"], vocab_size=cfg["vocab_size"], max_seq_len=16)
+    eng = _engine(w, cfg["max_seq_len"], prefill_mode=prefill_mode)
+    steps = cfg["steps"]
+    dump = torch.zeros(steps, cfg["vocab_size"], device="cuda")
+    C.set_logits_dump(dump)
+    try:
+        got = eng.generate_ids(ids, steps)
+    finally:
+        C.set_logits_dump(None)
+    idx = torch.tensor(g["top8_indices"], device="cuda")
+    vals = torch.gather(dump, 1, idx).cpu()
+    err = float((vals - torch.tensor(g["top8_values"])).abs().max())
+    print(f"ctx 4096 ({prefill_mode} prefill): max |top-8 logit - golden| = {err:.3e}; min margin {g['min_margin']:.3e}")
+    assert got == g["tokens"]
+    assert err < LOGIT_TOL
+
+
+def test_fused_and_unfused_kernels_agree(C, tiny_cfg):
+    """The fused kernel (split-K O/down slices, integer all-reduced residual sums) and the unfused kernel sum in
+    different orders: same tokens, logits equal to round-off, and each bit-identical to itself run to run."""
+    g = np.load(os.path.join(GOLDEN, "tiny_l2_v4096.npz"))
+    w = _tiny_weights(tiny_cfg)
+    ids = g["prompt"].tolist()
+    eng = _engine(w, tiny_cfg["max_seq_len"])
+    dumps = {}
+    try:
+        for mode in (1, 0, 1):
+            C.set_fused(fused=mode)
+            dump = torch.zeros(tiny_cfg["steps"], tiny_cfg["vocab_size"], device="cuda")
+            C.set_logits_dump(dump)
+            try:
+                assert eng.generate_ids(ids, tiny_cfg["steps"]) == g["tokens"].tolist(), mode
+            finally:
+                C.set_logits_dump(None)
+            assert (dump.cpu() - torch.from_numpy(g["logits"])).abs().max() < LOGIT_TOL
+            if mode in dumps:
+                assert torch.equal(dumps[mode], dump), "fused kernel is not reproducible run to run"
+            dumps[mode] = dump
+        diff = float((dumps[0] - dumps[1]).abs().max())
+        print(f"fused vs unfused: max |logit diff| = {diff:.3e}")
+        assert diff < 1e-3
+        # two accumulator copies per sum: same integers, added in two groups
+        C.set_fused(fused=1, red_copies=2)
+        dump = torch.zeros(tiny_cfg["steps"], tiny_cfg["vocab_size"], device="cuda")
+        C.set_logits_dump(dump)
+        try:
+            assert eng.generate_ids(ids, tiny_cfg["steps"]) == g["tokens"].tolist()
+        finally:
+            C.set_logits_dump(None)
+        assert torch.equal(dump, dumps[1]), "integer sums must not depend on how contributions are grouped"
+    finally:
+        C.set_fused(fused=1, red_copies=1)
+
+
+def test_kmajor_copies_follow_the_weights(C, tiny_cfg):
+    """The fused kernel reads library-made K-major copies of W_o / W_down.  New weights behind the SAME layer
+    table (same addresses, new contents) must be picked up by the per-call hash check."""
+    w1 = _tiny_weights(tiny_cfg)
+    cfg2 = dict(tiny_cfg, seed=tiny_cfg["seed"] + 1)
+    w2 = _tiny_weights(cfg2)
+    ids = S.make_prompt(10, seed=4, vocab_size=tiny_cfg["vocab_size"])
+    want1 = OracleDecoder(w1, max_seq_len=tiny_cfg["max_seq_len"]).generate_ids(ids, 5)[0]
+    want2 = OracleDecoder(w2, max_seq_len=tiny_cfg["max_seq_len"]).generate_ids(ids, 5)[0]
+    assert want1 != want2
+    dev = S.weights_to(w1, "cuda")
+    from Model.Qwen06B_architecture import Decoder
+    eng = Decoder(weights=dev, verbose=False, max_seq_len=tiny_cfg["max_seq_len"])
+    assert eng.generate_ids(ids, 5) == want1
+    for dst, src in zip(dev["layer_weights"], w2["layer_weights"]):     # overwrite in place: the table is unchanged
+        dst.copy_(src)
+    dev["embed_weight"].copy_(w2["embed_weight"])
+    dev["final_norm_weight"].copy_(w2["final_norm_weight"])
+    assert eng.generate_ids(ids, 5) == want2
