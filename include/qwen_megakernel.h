@@ -138,12 +138,15 @@ int qmk_set_tuning(int spin_sleep_ns, int l2_evict_first);
 int qmk_set_tuning2(int repl, int stream_inflight);
 
 /* Kernel choice for one sequence (qmk_decode / qmk_generate / qmk_prefill); negative keeps a value.
- *  fused  1 (default): the fused kernel - the O and down projections run as split-K slices on the CTAs that
+ *  fused  2 (default) or 1: the fused kernel - the O and down projections run as split-K slices on the CTAs that
  *         produced their inputs, and the two residual sums of a layer are all-reduced in 64-bit integer
  *         accumulators (four cross-CTA hand-overs per layer).  It reads K-major copies of W_o and W_down that
  *         the library makes from the caller's matrices (294 MB for 28 fp16 layers) on the first call with a
  *         layer table and re-checks by sampled hashes on every call.  Grids below 74 CTAs and
  *         qmk_generate_static use the unfused kernel (six hand-overs, no copies).  0: always unfused.
+ *         2 multiplies weight rows on the tensor cores (mma.sync tiles of 16 rows, the fp32 activation vector
+ *         split into two fp16 columns); it needs fp16 weights and a vocabulary that is a multiple of 4, and falls
+ *         back to 1 (CUDA-core row products, any format) otherwise.
  *  red_copies  1 or 2 accumulator copies per sum (2 halves the same-address add queue, doubles the words read).
  * The reference has neither (its layer is eight grid barriers, megakernel_5090.cu:879-915). */
 int qmk_set_fused(int fused, int red_copies);

@@ -15,10 +15,12 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 SOURCES = [os.path.join(HERE, "csrc", "megakernel_sm100.cu"), os.path.join(HERE, "csrc", "megakernel_batch_sm100.cu"),
+           os.path.join(HERE, "csrc", "megakernel_tc_sm100.cu"),
            os.path.join(HERE, "csrc", "prefill_sm100.cu")]
 HEADERS = [os.path.join(os.path.dirname(HERE), "include", "qwen_megakernel.h"),
            os.path.join(HERE, "csrc", "megakernel_device.cuh"), os.path.join(HERE, "csrc", "megakernel_params.h"),
-           os.path.join(HERE, "csrc", "megakernel_batch.cuh"), os.path.join(HERE, "csrc", "megakernel_fused.cuh"), os.path.join(HERE, "csrc", "megakernel_batch.h"),
+           os.path.join(HERE, "csrc", "megakernel_batch.cuh"), os.path.join(HERE, "csrc", "megakernel_fused.cuh"),
+           os.path.join(HERE, "csrc", "megakernel_tc.cuh"), os.path.join(HERE, "csrc", "megakernel_tc.h"), os.path.join(HERE, "csrc", "megakernel_batch.h"),
            os.path.join(HERE, "csrc", "gemm_tcgen05.cuh"), os.path.join(HERE, "csrc", "prefill_sm100.h"),
            os.path.join(HERE, "csrc", "prefill_kernels.cuh"), os.path.join(HERE, "csrc", "engine_internal.h")]
 LIB_PATH = os.path.join(HERE, "libqwen_megakernel.so")

@@ -32,14 +32,27 @@ constexpr float RMS_EPS = 1e-6f;
 constexpr int CONS_WARPS = QMK_CONS_WARPS;
 constexpr int CONS_THREADS = CONS_WARPS * 32;   // 512 math threads
 constexpr int THREADS = CONS_THREADS + 32;      // + 1 producer warp
+// Ring geometry.  The tensor-core build (QMK_TC_BUILD) overrides it: slots hold four weight rows padded to
+// 2064 bytes, and a slot is freed by 12 arrival units (1, 2, 3, 4, 6 or 12 warps share a chunk there).
+#ifdef QMK_SLOT_BYTES
+constexpr int SLOT_BYTES = QMK_SLOT_BYTES;
+#else
 constexpr int SLOT_BYTES = 8192;
-#if QMK_MAX_SEQ == 1
+#endif
+#ifdef QMK_NSLOTS
+constexpr int NSLOTS = QMK_NSLOTS;
+#elif QMK_MAX_SEQ == 1
 constexpr int NSLOTS = 21;
 #else
 constexpr int NSLOTS = 13;       // every sequence keeps its own activations in shared memory: a shorter ring
 #endif
 static_assert(NSLOTS >= CONS_WARPS, "a group of chunks (up to one per warp) must fit in the ring");
+#ifdef QMK_EMPTY_UNITS
+constexpr int EMPTY_UNITS = QMK_EMPTY_UNITS;
+#else
 constexpr int EMPTY_UNITS = 4;   // single-sequence build: arrival units that free a ring slot (rows-per-chunk is 4, 2 or 1)
+#endif
+constexpr int SLOT_HALF = (SLOT_BYTES / 2) & ~15;   // second source of a two-source chunk (V rows, up rows)
 constexpr int MAX_SPLITS = 24;   // attention work items per kv head (<= grid / 8)
 constexpr int MAX_CTAS = 256;
 constexpr int MAX_LAYERS = 48;
@@ -483,6 +496,9 @@ __device__ __forceinline__ AttnItem attn_item(const Params &P, const Ctx &c, int
   const int rows = it.p1 - it.p0;
   const int rounds = max(1, (rows + gw * KV_ROWS_PER_CHUNK - 1) / (gw * KV_ROWS_PER_CHUNK));
   it.rpc = min(KV_ROWS_PER_CHUNK, max(1, (rows + gw * rounds - 1) / (gw * rounds)));
+#ifdef QMK_TC_BUILD
+  it.rpc = KV_ROWS_PER_CHUNK;   // tensor-core build: a chunk is one 16-row MMA tile
+#endif
   it.nchunks = (rows + it.rpc - 1) / it.rpc;
   return it;
 }
@@ -513,7 +529,7 @@ __device__ __forceinline__ bool produce_chunk(const Params &P, const Ctx &c, uin
   unsigned char *dst = c.slot(idx);
   mbar_arrive_expect_tx(c.full(slot), src2 ? 2 * bytes : bytes);
   bulk_g2s(dst, src, bytes, c.full(slot), pol);
-  if (src2) bulk_g2s(dst + SLOT_BYTES / 2, src2, bytes, c.full(slot), pol);
+  if (src2) bulk_g2s(dst + SLOT_HALF, src2, bytes, c.full(slot), pol);
   ++idx;
 #if QMK_ISSUED_CHECK
 #if QMK_ISSUED_FENCE
@@ -731,6 +747,7 @@ __device__ __forceinline__ float block_sum(const Ctx &c, float v) {
   return t;
 }
 
+#ifndef QMK_TC_BUILD
 // Polls N exchange words into shared memory as fp32; returns this thread's sum of squares.
 // All loads are issued before the first one is looked at.
 // One shared (non-inlined) copy: the kernel's per-layer code has to stay small enough for the
@@ -834,7 +851,7 @@ __device__ __noinline__ uint32_t gemv_k1024(const Params &P, Ctx c, int kind, co
           const uint32_t idx = c.chunk + static_cast<uint32_t>(c0 + b * G + wch);
           const unsigned char *p = c.slot(idx) + sub * kind_row_bytes(K_QKV, wfmt);
           v[b] = row_partial_regs(p, a, c.lane, wfmt);
-          if (kind == K_GU) u[b] = row_partial_regs(p + SLOT_BYTES / 2, a, c.lane, wfmt);
+          if (kind == K_GU) u[b] = row_partial_regs(p + SLOT_HALF, a, c.lane, wfmt);
         }
       }
       // The rows are in registers now: hand the slots back BEFORE publishing (mbarrier.arrive has
@@ -947,6 +964,7 @@ __device__ __noinline__ uint32_t gemv_wide(const Params &P, Ctx c, int kind, con
   return c.chunk;
 }
 
+#endif  // QMK_TC_BUILD
 // ----------------------------------------------------------------------------- attention
 // Work item (kv head g, split s) on CTA g + 8*s: old cache rows [p0, p1); the last split also
 // normalises/rotates/stores the new K,V row and folds it in.  Writes either the final head
@@ -1052,7 +1070,7 @@ __device__ __noinline__ uint32_t attention_phase(const Params &P, Ctx c, const _
 #pragma unroll 2
       for (int r = grp; r < nrow; r += 2) {
         const uint4 k0 = *reinterpret_cast<const uint4 *>(kslot + r * (D * 2));
-        const uint4 v0 = *reinterpret_cast<const uint4 *>(kslot + SLOT_BYTES / 2 + r * (D * 2));
+        const uint4 v0 = *reinterpret_cast<const uint4 *>(kslot + SLOT_HALF + r * (D * 2));
         float d0 = dot8(k0, q0, 0.f), d1 = dot8(k0, q1, 0.f);
 #pragma unroll
         for (int o = 1; o < 16; o <<= 1) {
@@ -1157,6 +1175,13 @@ __device__ __noinline__ uint32_t attention_phase(const Params &P, Ctx c, const _
   return c.chunk;
 }
 
+#define QMK_STAMP(slot)                                                                           \
+  do {                                                                                            \
+    if (P.prof && c.tid == 0 && step == P.num_steps - 1)                                          \
+      P.prof[static_cast<size_t>(c.cta) * PROF_STRIDE + (slot)] = now_ns();                       \
+  } while (0)
+
+#ifndef QMK_TC_BUILD
 // Combines the S partials of each attention output element this CTA owns (S > 1 only).
 __device__ __noinline__ void attention_merge(const Params &P, const Ctx c, int S, uint32_t tag) {
   const int e0 = c.segs()->e0, e1 = c.segs()->e1;
@@ -1179,12 +1204,6 @@ __device__ __noinline__ void attention_merge(const Params &P, const Ctx c, int S
 }
 
 // ----------------------------------------------------------------------------- the kernel
-#define QMK_STAMP(slot)                                                                           \
-  do {                                                                                            \
-    if (P.prof && c.tid == 0 && step == P.num_steps - 1)                                          \
-      P.prof[static_cast<size_t>(c.cta) * PROF_STRIDE + (slot)] = now_ns();                       \
-  } while (0)
-
 // GATED: the grid is so small (below ~74 CTAs) that a projection phase has more chunks on a CTA than the ring
 // has slots; the host picks the entry point with grid_has_long_phase().
 template <bool GATED>
@@ -1402,6 +1421,7 @@ inline bool grid_has_long_phase(int ncta) {
   }
   return false;
 }
+#endif  // QMK_TC_BUILD
 
 #endif  // QMK_MAX_SEQ == 1
 

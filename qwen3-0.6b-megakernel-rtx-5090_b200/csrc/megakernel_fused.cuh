@@ -60,6 +60,7 @@ __device__ __forceinline__ void red_add_u64(unsigned long long *p, unsigned long
 // Contributors to copy r of a sum: CTAs r, r + R, ...
 __device__ __forceinline__ uint32_t red_contributors(int ncta, int R, int r) { return static_cast<uint32_t>((ncta - r + R - 1) / R); }
 
+#ifndef QMK_TC_BUILD
 // Waits until use number `use` (1-based) of a sum is complete, writes its 1024 fp32 values to shared memory
 // and returns this thread's share of the sum of squares.  Every thread polls its own three words; all loads
 // of a round are issued before any is looked at.  With two accumulator copies the copies are taken one after
@@ -203,6 +204,8 @@ __device__ __noinline__ uint32_t slice_colgemv(const Params &P, Ctx c, int which
   return c.chunk + static_cast<uint32_t>(nch);
 }
 
+#endif  // QMK_TC_BUILD
+
 // Combines the S partials of every attention output element this CTA owns into s_attn[e - e0] (shared memory).
 // The slice [e0, e1) lies in at most two query heads.  The last two warps fetch the (max, sum) pairs of those
 // heads' splits and turn them into one weight per split, exp2(max_s - max) / sum; meanwhile every warp fetches
@@ -254,6 +257,7 @@ __device__ __noinline__ void merge_slice(const Params &P, const Ctx c, int S, ui
   }
 }
 
+#ifndef QMK_TC_BUILD
 __device__ __forceinline__ bool produce_rows(const Params &P, const Ctx &c, uint32_t &idx, uint64_t pol, const unsigned char *src,
                                              int nrows, int row_bytes) {
 #pragma unroll 1
@@ -339,6 +343,8 @@ __device__ __noinline__ float embed_row(const Params &P, const Ctx c, int token)
   return ss;
 }
 
+#endif  // QMK_TC_BUILD
+
 // Argmax across the grid (megakernel_5090.cu:1137-1167): every CTA publishes the best (value, row) of its LM-head
 // rows (left per warp in s_misc[32..], s_misc[48..]), reads all CTAs' pairs and leaves the winning row, lowest
 // index on ties, in s_misc[16].  Entered after a consumer barrier.
@@ -380,6 +386,7 @@ __device__ __noinline__ void argmax_exchange(const Params &P, const Ctx c, uint3
   }
 }
 
+#ifndef QMK_TC_BUILD
 __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel_fused(const __grid_constant__ Params P) {
   extern __shared__ __align__(128) unsigned char smem[];
   Ctx c;
@@ -521,6 +528,8 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel_fused(cons
     }
   }
 }
+
+#endif  // QMK_TC_BUILD
 
 #endif  // QMK_MAX_SEQ == 1
 }  // namespace QMK_NS

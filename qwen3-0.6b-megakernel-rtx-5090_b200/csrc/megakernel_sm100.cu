@@ -45,6 +45,8 @@
 #include "megakernel_device.cuh"
 #include "megakernel_fused.cuh"
 #include "megakernel_batch.h"
+#include "megakernel_tc.h"
+#include "prefill_sm100.h"
 #include "engine_internal.h"
 
 namespace qmk {
@@ -198,7 +200,7 @@ struct Engine {
   int stream_inflight = 0;   // measured: pacing the stream changes nothing
   bool inv_freq_set = false;
   // fused single-sequence kernel (megakernel_fused.cuh)
-  int fused = 1;             // 0: always the unfused kernel
+  int fused = 2;             // 0: always the unfused kernel; 1: fused, CUDA-core row products; 2: fused, tensor-core row products (fp16 weights)
   int red_copies = 1;
   int fused_sleep_ns = 0;    // measured at 4096-token context: 600 ns 1224 tok/s, 200 ns 1259, 0 ns 1305 (few pollers per word)
   unsigned long long *red = nullptr;   // the two residual sums
@@ -273,6 +275,8 @@ int ensure_ready(Engine *e) {
   if (e->grid > qmk::MAX_CTAS) e->grid = qmk::MAX_CTAS;
   QMK_CUDA(e, cudaFuncSetAttribute(qmk_batch::kernel(), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(qmk_batch::smem_bytes())));
+  QMK_CUDA(e, cudaFuncSetAttribute(qmk_fused_tc::kernel(), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(qmk_fused_tc::smem_bytes())));
   QMK_CUDA(e, cudaMalloc(&e->ll, exchange_bytes()));
   QMK_CUDA(e, cudaMemset(e->ll, 0, exchange_bytes()));
   QMK_CUDA(e, cudaMalloc(&e->status, 16));
@@ -451,6 +455,7 @@ int launch(Engine *e, Params &P, cudaStream_t stream, bool synchronize, bool bat
   void *args[] = {&P};
   const int grid = grid_for(e);
   const void *kernel = batch ? qmk_batch::kernel() : single_sequence_kernel(grid);
+  size_t smem = qmk::SMEM_BYTES;
   if (!batch && e->fused && grid >= qmk::FUSED_MIN_CTAS &&
       kernel == reinterpret_cast<const void *>(qmk::qwen3_decode_megakernel)) {
     // fused kernel: O and down projections as split-K slices of K-major copies, two all-reduced residual sums
@@ -463,11 +468,22 @@ int launch(Engine *e, Params &P, cudaStream_t stream, bool synchronize, bool bat
     P.red_copies = e->red_copies;
     P.spin_sleep_ns = e->fused_sleep_ns;
     kernel = reinterpret_cast<const void *>(qmk::qwen3_decode_megakernel_fused);
+    // row products on the tensor cores: fp16 weights, rows owned in units of four
+    if (e->fused >= 2 && e->wfmt == 0 && P.vocab % 4 == 0 && grid >= qmk_fused_tc::min_ctas()) {
+      // tiled-copy descriptors of the caller's caches (host-side encode, a few microseconds)
+      std::string merr;
+      const uint64_t kv_rows = static_cast<uint64_t>(P.num_layers) * qmk::NKV * static_cast<uint64_t>(P.max_seq_len);
+      rc = qmk_tc::make_map_f16(reinterpret_cast<CUtensorMap *>(P.kmap), P.k_cache, kv_rows, qmk::D, 16, &merr);
+      if (rc == QMK_OK) rc = qmk_tc::make_map_f16(reinterpret_cast<CUtensorMap *>(P.vmap), P.v_cache, kv_rows, qmk::D, 16, &merr);
+      if (rc != QMK_OK) return fail(e, rc, "KV cache tensor map: " + merr);
+      kernel = qmk_fused_tc::kernel();
+      smem = qmk_fused_tc::smem_bytes();
+    }
   }
   cudaError_t err =
       batch ? cudaLaunchCooperativeKernel(kernel, dim3(grid), dim3(qmk_batch::threads()), args,
                                           qmk_batch::smem_bytes(), stream)
-            : cudaLaunchCooperativeKernel(kernel, dim3(grid), dim3(qmk::THREADS), args, qmk::SMEM_BYTES, stream);
+            : cudaLaunchCooperativeKernel(kernel, dim3(grid), dim3(qmk::THREADS), args, smem, stream);
   if (err == cudaErrorCooperativeLaunchTooLarge)
     return fail(e, QMK_ERR_NOT_RESIDENT, "persistent grid cannot be co-resident on this device");
   if (err != cudaSuccess) return fail(e, QMK_ERR_CUDA, std::string("cudaLaunchCooperativeKernel: ") + cudaGetErrorString(err));
@@ -601,7 +617,8 @@ int qmk_set_fused(int fused, int red_copies) {
   std::lock_guard<std::mutex> lock(g_mutex);
   Engine *e = current_engine_unlocked();
   if (!e) return QMK_ERR_CUDA;
-  if (fused >= 0) e->fused = fused ? 1 : 0;
+  if (fused > 2) return fail(e, QMK_ERR_BAD_ARGUMENT, "fused must be 0, 1 or 2");
+  if (fused >= 0) e->fused = fused;
   if (red_copies == 1 || red_copies == 2) e->red_copies = red_copies;
   else if (red_copies >= 0) return fail(e, QMK_ERR_BAD_ARGUMENT, "red_copies must be 1 or 2");
   return QMK_OK;

@@ -272,7 +272,8 @@ def test_benchmark_configuration_matches_golden(C, prefill_mode):
 
 
 def test_fused_and_unfused_kernels_agree(C, tiny_cfg):
-    """The fused kernel (split-K O/down slices, integer all-reduced residual sums) and the unfused kernel sum in
+    """The fused kernels (split-K O/down slices, integer all-reduced residual sums; 2 = row products on the tensor
+    cores with the activations split into two fp16 columns, 1 = on the CUDA cores) and the unfused kernel (0) sum in
     different orders: same tokens, logits equal to round-off, and each bit-identical to itself run to run."""
     g = np.load(os.path.join(GOLDEN, "tiny_l2_v4096.npz"))
     w = _tiny_weights(tiny_cfg)
@@ -280,7 +281,7 @@ def test_fused_and_unfused_kernels_agree(C, tiny_cfg):
     eng = _engine(w, tiny_cfg["max_seq_len"])
     dumps = {}
     try:
-        for mode in (1, 0, 1):
+        for mode in (2, 1, 0, 2, 1):
             C.set_fused(fused=mode)
             dump = torch.zeros(tiny_cfg["steps"], tiny_cfg["vocab_size"], device="cuda")
             C.set_logits_dump(dump)
@@ -292,20 +293,22 @@ def test_fused_and_unfused_kernels_agree(C, tiny_cfg):
             if mode in dumps:
                 assert torch.equal(dumps[mode], dump), "fused kernel is not reproducible run to run"
             dumps[mode] = dump
-        diff = float((dumps[0] - dumps[1]).abs().max())
-        print(f"fused vs unfused: max |logit diff| = {diff:.3e}")
-        assert diff < 1e-3
+        for a, b in ((0, 1), (0, 2)):
+            diff = float((dumps[a] - dumps[b]).abs().max())
+            print(f"kernel {a} vs kernel {b}: max |logit diff| = {diff:.3e}")
+            assert diff < 1e-3
         # two accumulator copies per sum: same integers, added in two groups
-        C.set_fused(fused=1, red_copies=2)
-        dump = torch.zeros(tiny_cfg["steps"], tiny_cfg["vocab_size"], device="cuda")
-        C.set_logits_dump(dump)
-        try:
-            assert eng.generate_ids(ids, tiny_cfg["steps"]) == g["tokens"].tolist()
-        finally:
-            C.set_logits_dump(None)
-        assert torch.equal(dump, dumps[1]), "integer sums must not depend on how contributions are grouped"
+        for mode in (1, 2):
+            C.set_fused(fused=mode, red_copies=2)
+            dump = torch.zeros(tiny_cfg["steps"], tiny_cfg["vocab_size"], device="cuda")
+            C.set_logits_dump(dump)
+            try:
+                assert eng.generate_ids(ids, tiny_cfg["steps"]) == g["tokens"].tolist()
+            finally:
+                C.set_logits_dump(None)
+            assert torch.equal(dump, dumps[mode]), "integer sums must not depend on how contributions are grouped"
     finally:
-        C.set_fused(fused=1, red_copies=1)
+        C.set_fused(fused=2, red_copies=1)
 
 
 def test_kmajor_copies_follow_the_weights(C, tiny_cfg):
