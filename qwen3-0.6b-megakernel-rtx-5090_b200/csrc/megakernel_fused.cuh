@@ -211,7 +211,10 @@ __device__ __noinline__ uint32_t slice_colgemv(const Params &P, Ctx c, int which
 // heads' splits and turn them into one weight per split, exp2(max_s - max) / sum; meanwhile every warp fetches
 // the unnormalised outputs of its elements (lanes = splits, up to three elements per warp, all words polled
 // together).  After a barrier an element is the weighted sum over its splits.
-__device__ __noinline__ void merge_slice(const Params &P, const Ctx c, int S, uint32_t tag) {
+// act16 (tensor-core build): also leave the outputs as fp16 hi / scaled-lo halves at act16[i] / act16[ACT16_PITCH + i],
+// zero from the slice's end up to 32.
+constexpr int ACT16_PITCH = 72;                // halves between the hi and the lo row (64 + 8: other banks)
+__device__ __noinline__ void merge_slice(const Params &P, const Ctx c, int S, uint32_t tag, __half *act16 = nullptr) {
   float *s_attn = c.f(FF_ATTN), *s_wt = c.f(FF_SPLITW);
   const int e0 = c.segs()->e0, e1 = c.segs()->e1;
   const int h0 = e0 >> 7;
@@ -228,33 +231,52 @@ __device__ __noinline__ void merge_slice(const Params &P, const Ctx c, int S, ui
   }
   float a[NE];
   QMK_FINE(50);
-  ll_wait_many<NE>(P, c, wp, valid, tag, a);
-  QMK_FINE(51);
-  if (c.warp >= CONS_WARPS - 2) {
-    const int h = h0 + (c.warp - (CONS_WARPS - 2));
-    if (h <= ((e1 - 1) >> 7)) {                                   // warp-uniform
-      const unsigned long long *part = c.llr + LL_PART + static_cast<size_t>(h * MAX_SPLITS + s) * PART_STRIDE;
-      const unsigned long long *mp[2] = {part + D, part + D + 1};
-      float ml[2];
-      ll_wait_many<2>(P, c, mp, c.lane < S ? 3u : 0u, tag, ml);
-      const float m = c.lane < S ? ml[0] : -INFINITY, l = c.lane < S ? ml[1] : 0.f;
-      const float M = warp_max(m);
-      const float sc = (m == -INFINITY) ? 0.f : exp2f(m - M);
-      const float L = warp_sum(l * sc);
-      s_wt[(h - h0) * 32 + c.lane] = sc / L;
-    }
+  const int hw = h0 + (c.warp - (CONS_WARPS - 2));                // head whose split weights this warp makes (last two warps)
+  if (c.warp >= CONS_WARPS - 2 && hw <= ((e1 - 1) >> 7)) {        // warp-uniform
+    // outputs and the head's (max, sum) pairs in ONE round of polls (one after the other costs a second L2 round trip)
+    const unsigned long long *part = c.llr + LL_PART + static_cast<size_t>(hw * MAX_SPLITS + s) * PART_STRIDE;
+    const unsigned long long *wp5[NE + 2] = {wp[0], wp[1], wp[2], part + D, part + D + 1};
+    float v5[NE + 2];
+    ll_wait_many<NE + 2>(P, c, wp5, valid | (c.lane < S ? (3u << NE) : 0u), tag, v5);
+    QMK_FINE(51);
+#pragma unroll
+    for (int q = 0; q < NE; ++q) a[q] = v5[q];
+    const float m = c.lane < S ? v5[NE] : -INFINITY, l = c.lane < S ? v5[NE + 1] : 0.f;
+    const float M = warp_max(m);
+    const float sc = (m == -INFINITY) ? 0.f : exp2f(m - M);
+    const float L = warp_sum(l * sc);
+    s_wt[(hw - h0) * 32 + c.lane] = sc / L;
+  } else {
+    ll_wait_many<NE>(P, c, wp, valid, tag, a);
+    QMK_FINE(51);
   }
   cons_sync();
   QMK_FINE(52);
+  // the (up to three) weighted sums of this warp side by side: their shuffle chains overlap
+  float A[NE];
+#pragma unroll
+  for (int q = 0; q < NE; ++q) {
+    const int e = min(e0 + c.warp + q * CONS_WARPS, e1 - 1);
+    const float wgt = s_wt[((e >> 7) - h0) * 32 + c.lane];        // 0 for lanes >= S
+    A[q] = (valid & (1u << q)) ? a[q] * wgt : 0.f;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+    for (int q = 0; q < NE; ++q) A[q] += __shfl_xor_sync(0xffffffffu, A[q], o);
 #pragma unroll
   for (int q = 0; q < NE; ++q) {
     const int e = e0 + c.warp + q * CONS_WARPS;
-    if (e < e1) {                                                 // warp-uniform
-      const float wgt = s_wt[((e >> 7) - h0) * 32 + c.lane];      // 0 for lanes >= S
-      const float A = warp_sum((valid & (1u << q)) ? a[q] * wgt : 0.f);
-      if (c.lane == 0) s_attn[e - e0] = A;
+    if (e < e1 && c.lane == 0) {
+      s_attn[e - e0] = A[q];
+      if (act16) {
+        const __half h = __float2half_rn(A[q]);
+        act16[e - e0] = h;
+        act16[ACT16_PITCH + e - e0] = __float2half_rn((A[q] - __half2float(h)) * 2048.0f);
+      }
     }
   }
+  if (act16 && c.tid < 32 && c.tid >= e1 - e0) { act16[c.tid] = __float2half_rn(0.f); act16[ACT16_PITCH + c.tid] = __float2half_rn(0.f); }
 }
 
 #ifndef QMK_TC_BUILD

@@ -41,15 +41,30 @@ constexpr int QKV_CHUNKS = QKV_ROWS / CH_ROWS, GU_CHUNKS = I / CH_ROWS;
 constexpr int KPAIRS = H / 32;                 // pairs of 16-input k-steps in a row
 
 // Extra shared memory of this kernel, behind the single-sequence layout.
-constexpr size_t OFF_XH = SMEM_BYTES;                          // fp16 hi halves of the normalised activations [1024]
-constexpr size_t OFF_XL = OFF_XH + 2 * H + 16;                 // fp16 scaled lo halves [1024] (+16: other banks than hi)
-constexpr size_t OFF_PART = OFF_XL + 2 * H;                    // fp32 tile partials [2][12 tasks][16 rows]
+// Normalised activations as the B operand of the row products, in MMA fragment order: 128 bytes per pair of
+// k-steps (32 inputs) = [hi: 4 lanes x 16 bytes][lo: 4 lanes x 16 bytes]; the 16 bytes of lane kq are the halves
+// {b0, b1} of the first k-step (inputs 2kq, 2kq+1, 2kq+8, 2kq+9) and of the second (the same + 16).  Lanes 0..7 of a
+// warp fetch a pair's operand with ONE 128-byte wavefront (ldmatrix.x4 over plain hi / lo rows takes four; the row
+// products are bound by shared-memory bandwidth, where that is a third of the traffic).
+constexpr size_t OFF_XF = (SMEM_BYTES + 127) / 128 * 128;
+constexpr size_t OFF_PART = OFF_XF + 4 * H;                    // fp32 tile partials [2][12 tasks][16 rows]
 constexpr size_t OFF_QF = OFF_PART + 2 * 12 * 16 * 4;           // fp16 query operand [4: q0 hi, q0 lo, q1 hi, q1 lo][128], rows at KV_PITCH
-constexpr size_t OFF_TCTAB = OFF_QF + 4 * KV_PITCH;
-struct TcTab { int q0, nq, g0, ng, lm0, nlm, pad0, pad1; };    // first chunk / chunks of this CTA: q|k|v rows, gate (= up) rows, LM-head rows
+constexpr size_t OFF_ACT16 = OFF_QF + 4 * KV_PITCH;            // fp16 hi row, scaled-lo row of a slice's activations (merge / gate-up outputs)
+constexpr size_t OFF_TCTAB = OFF_ACT16 + ((2 * ACT16_PITCH * 2 + 15) / 16) * 16;
+struct alignas(16) TileTask { int active, first, valid, p0, p1, units, pad0, pad1; };   // see build_tile_tasks
+struct alignas(16) TcTab {
+  int q0, nq, g0, ng, lm0, nlm;    // first chunk / chunks of this CTA: q|k|v rows, gate (= up) rows, LM-head rows
+  int nkb_qkv, nkb_gu;             // warps per tile in the two row-product phases
+  TileTask qkv[12], gu[12];        // each warp's tile task in those phases
+};
 constexpr size_t TC_SMEM_BYTES = OFF_TCTAB + sizeof(TcTab);
 static_assert(TC_SMEM_BYTES <= 232448, "over the 227 KB shared-memory limit of one CTA");
-static_assert(OFF_XH % 16 == 0 && OFF_XL % 16 == 0 && OFF_QF % 16 == 0, "ldmatrix rows are 16-byte aligned");
+static_assert(OFF_XF % 128 == 0 && OFF_QF % 16 == 0, "operand rows are 16-byte aligned, a pair's 128 bytes one wavefront");
+// Byte offset in the fragment-order array of input i's hi (lo = 0) or lo (1) half.
+__device__ __forceinline__ int xf_offset(int i, int lo) {
+  const int kk = i & 31, rem = kk & 15, r8 = rem & 7;
+  return (i >> 5) * 128 + lo * 64 + (r8 >> 1) * 16 + ((kk >> 4) * 4 + (rem >> 3) * 2 + (r8 & 1)) * 2;
+}
 
 __device__ __forceinline__ const TcTab *tctab(const Ctx &c) { return reinterpret_cast<const TcTab *>(c.smem + OFF_TCTAB); }
 __device__ __forceinline__ float *tc_part(const Ctx &c) { return reinterpret_cast<float *>(c.smem + OFF_PART); }
@@ -77,11 +92,10 @@ __device__ __forceinline__ uint32_t pack_half2(__half a, __half b) {
   return static_cast<uint32_t>(__half_as_ushort(a)) | (static_cast<uint32_t>(__half_as_ushort(b)) << 16);
 }
 
-// Address (shared window) this lane gives ldmatrix for the activation operand: matrix j = lane / 8 covers inputs
-// [8j, 8j + 8) of a 32-input pair; row n = lane % 8 of the B^T tile is the hi vector for even n, the lo vector for
-// odd n (columns 2..7 of the product repeat columns 0 and 1 and are ignored).
-__device__ __forceinline__ uint32_t b_lane_addr(const Ctx &c) {
-  return smem_u32(c.smem + ((c.lane & 1) ? OFF_XL : OFF_XH)) + (c.lane >> 3) * 16;
+// Activation operand of k-step pair p for this lane: column n = lane / 4 of B is the hi vector (n = 0), the lo vector
+// (n = 1) or zero; {x, y} = fragments of the first k-step, {z, w} of the second.
+__device__ __forceinline__ uint4 b_pair(const Ctx &c, int p) {
+  return c.lane < 8 ? *reinterpret_cast<const uint4 *>(c.smem + OFF_XF + p * 128 + c.lane * 16) : make_uint4(0u, 0u, 0u, 0u);
 }
 
 // Shared-window address of row 0 of the weight chunk with ring index idx.
@@ -95,76 +109,83 @@ __device__ __forceinline__ void tma_box_2d(uint32_t dst, const void *map, int c0
 
 // One warp: rows of the 16-row tile that starts at ring chunk `first` (valid rows <= 16), k-step pairs [p0, p1).
 // Leaves the 16 row sums of that k range in part[0..15] and hands the tile's chunks back with `units` each.
+// Lanes 0..3 each wait for one of the tile's chunks (the vote that follows orders the copied bytes before every
+// lane's loads); two accumulators halve the chain of dependent MMAs.
 __device__ __forceinline__ void tile_task(const Params &P, const Ctx &c, uint32_t first, int valid_rows, int p0, int p1,
-                                          float *part, int units, int fslot = 70, bool dry = false) {
+                                          float *part, int units, int fslot = 70) {
   const int nch = (valid_rows + CH_ROWS - 1) / CH_ROWS;
   bool ok = true;
-#pragma unroll 1
-  for (int i = 0; i < nch; ++i) {
-    const uint32_t idx = first + static_cast<uint32_t>(i);
-    ok &= mbar_wait(P, c, c.full(idx % NSLOTS), (idx / NSLOTS) & 1u, WHERE_FULL, false);
+  if (c.lane < nch) {
+    const uint32_t idx = first + static_cast<uint32_t>(c.lane);
+    ok = mbar_wait(P, c, c.full(idx % NSLOTS), (idx / NSLOTS) & 1u, WHERE_FULL, false);
   }
   ok = __all_sync(0xffffffffu, ok);
   QMK_FINE(fslot + 1);
   int lr = (c.lane & 7) + ((c.lane >> 3) & 1) * 8;      // tile row whose address this lane supplies
   if (lr >= valid_rows) lr = 0;                         // rows past the end repeat row 0 (their sums are not used)
   const uint32_t a_addr = weight_rows(c, first + static_cast<uint32_t>(lr >> 2)) + (lr & 3) * ROW_PITCH + (c.lane >> 4) * 16;
-  const uint32_t b_addr = b_lane_addr(c);
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
   if (ok) {
 #pragma unroll 2
     for (int p = p0; p < p1; ++p) {
-      uint32_t b[4], a0[4], a1[4];
-      ldsm_x4(b_addr + p * 64, b);
+      uint32_t a0[4], a1[4];
+      const uint4 b = b_pair(c, p);
       ldsm_x4(a_addr + p * 64, a0);
       ldsm_x4(a_addr + p * 64 + 32, a1);
-      mma_16816(acc, a0, b[0], b[1]);
-      mma_16816(acc, a1, b[2], b[3]);
+      mma_16816(acc0, a0, b.x, b.y);
+      mma_16816(acc1, a1, b.z, b.w);
     }
   }
   QMK_FINE(fslot + 5);
   __syncwarp();
-  if (c.lane < nch && !dry) mbar_arrive_n(c.empty((first + static_cast<uint32_t>(c.lane)) % NSLOTS), static_cast<uint32_t>(units));
+  if (c.lane < nch) mbar_arrive_n(c.empty((first + static_cast<uint32_t>(c.lane)) % NSLOTS), static_cast<uint32_t>(units));
   if ((c.lane & 3) == 0) {
-    part[c.lane >> 2] = fmaf(acc[1], LO_INV, acc[0]);
-    part[(c.lane >> 2) + 8] = fmaf(acc[3], LO_INV, acc[2]);
+    part[c.lane >> 2] = fmaf(acc0[1] + acc1[1], LO_INV, acc0[0] + acc1[0]);
+    part[(c.lane >> 2) + 8] = fmaf(acc0[3] + acc1[3], LO_INV, acc0[2] + acc1[2]);
   }
 }
 
-// Row products of a layer phase: `groups` runs of `nch` consecutive chunks starting at ring chunk c.chunk
-// (q|k|v: one run; gate/up: the gate rows' chunks, then the up rows').  Tiles of 16 rows; the 12 warps share a
-// tile's inputs (k range) when there are fewer tiles than warps.  Partials land in tc_part()[task * 16 + row];
-// returns warps per tile (NKB).  A consumer barrier must follow before the partials are read.
-__device__ __forceinline__ int gemv_tiles(const Params &P, const Ctx &c, int groups, int nch, int fslot = 70, bool dry = false) {
-  const int tpg = (nch + 3) >> 2;                       // tiles per group
-  const int T = groups * tpg;
-  const int nkb = T >= CONS_WARPS ? 1 : CONS_WARPS / T;  // 12, 6, 4, 3, 2, 2, 1, ...: divides EMPTY_UNITS
-  float *part = tc_part(c);
-#pragma unroll 1
-  for (int task = c.warp; task < T * nkb; task += CONS_WARPS) {
-    const int tile = task / nkb, kb = task - tile * nkb;
-    const int grp = tile / tpg, t = tile - grp * tpg;
-    const uint32_t first = c.chunk + static_cast<uint32_t>(grp * nch + t * 4);
-    const int valid = min(16, (nch - t * 4) * CH_ROWS);
-    tile_task(P, c, first, valid, (KPAIRS * kb) / nkb, (KPAIRS * (kb + 1)) / nkb, part + task * 16, EMPTY_UNITS / nkb, fslot, dry);
+// Per-warp work of a layer phase, fixed for the launch (computed once: the integer divisions behind it cost more
+// than the MMAs).  Phase rows = `groups` runs of `nch` consecutive chunks (q|k|v: one run; gate/up: the gate rows'
+// chunks, then the up rows'); tiles of 16 rows; when there are fewer tiles than warps, nkb warps share a tile's
+// 1024 inputs.  Grids of at least FUSED_MIN_CTAS CTAs have at most 6 tiles per phase: one task per warp.
+__device__ inline void build_tile_tasks(TileTask *tasks, int *nkb_out, int groups, int nch) {
+  const int tpg = (nch + 3) >> 2, T = groups * tpg;
+  const int nkb = T >= CONS_WARPS ? 1 : CONS_WARPS / T;   // 12, 6, 4, 3, 2, 2, 1: divides EMPTY_UNITS
+  *nkb_out = nkb;
+  for (int w = 0; w < CONS_WARPS; ++w) {
+    TileTask &t = tasks[w];
+    t.active = w < T * nkb ? 1 : 0;
+    const int tile = w / nkb, kb = w - tile * nkb, grp = tile / tpg, tt = tile - grp * tpg;
+    t.first = grp * nch + tt * 4;
+    t.valid = min(16, (nch - tt * 4) * CH_ROWS);
+    t.p0 = (KPAIRS * kb) / nkb;
+    t.p1 = (KPAIRS * (kb + 1)) / nkb;
+    t.units = EMPTY_UNITS / nkb;
+    t.pad0 = t.pad1 = 0;
   }
-  return nkb;
+}
+__device__ __forceinline__ void run_tile_task(const Params &P, const Ctx &c, const TileTask *tasks, int fslot) {
+  const int4 a = reinterpret_cast<const int4 *>(tasks + c.warp)[0], b = reinterpret_cast<const int4 *>(tasks + c.warp)[1];
+  // a = {active, first, valid, p0}, b = {p1, units, -, -}
+  if (a.x) tile_task(P, c, c.chunk + static_cast<uint32_t>(a.y), a.z, a.w, b.x, tc_part(c) + c.warp * 16, b.y, fslot);
 }
 
 // q|k|v rows of this CTA -> exchange words (megakernel_5090.cu:251-302).
 __device__ __noinline__ uint32_t qkv_phase(const Params &P, Ctx c, uint32_t tag) {
   const TcTab *t = tctab(c);
-  const int nch = t->nq;
+  const int nch = t->nq, nkb = t->nkb_qkv;
   QMK_FINE(0);
-  const int nkb = gemv_tiles(P, c, 1, nch, 0);
+  run_tile_task(P, c, t->qkv, 0);
   QMK_FINE(2);
   cons_sync();
-  const float *part = tc_part(c);
-  for (int r = c.tid; r < nch * CH_ROWS; r += CONS_THREADS) {
-    const float *p = part + (r >> 4) * nkb * 16 + (r & 15);
+  if (c.tid < nch * CH_ROWS) {
+    const int r = c.tid;
+    const float *p = tc_part(c) + (r >> 4) * nkb * 16 + (r & 15);
     float v = 0.f;
-#pragma unroll 1
-    for (int kb = 0; kb < nkb; ++kb) v += p[kb * 16];
+#pragma unroll
+    for (int kb = 0; kb < CONS_WARPS; ++kb)
+      if (kb < nkb) v += p[kb * 16];
     ll_store(P.ll + LL_QKV + t->q0 * CH_ROWS + r, v, tag);
   }
   QMK_FINE(4);
@@ -174,21 +195,28 @@ __device__ __noinline__ uint32_t qkv_phase(const Params &P, Ctx c, uint32_t tag)
 // gate/up rows of this CTA -> silu(gate) * up in shared memory (megakernel_5090.cu:653-685, SiLU in fp32).
 __device__ __noinline__ uint32_t gateup_phase(const Params &P, Ctx c) {
   const TcTab *t = tctab(c);
-  const int nch = t->ng;
+  const int nch = t->ng, nkb = t->nkb_gu;
   QMK_FINE(10);
-  const int nkb = gemv_tiles(P, c, 2, nch, 10);
+  run_tile_task(P, c, t->gu, 10);
   QMK_FINE(12);
   cons_sync();
-  const float *part = tc_part(c);
-  float *s_inter = c.f(FF_INTER);
-  const int tpg = (nch + 3) >> 2;
-  for (int r = c.tid; r < nch * CH_ROWS; r += CONS_THREADS) {
-    const float *pg = part + (r >> 4) * nkb * 16 + (r & 15);
+  if (c.tid < nch * CH_ROWS) {
+    const int r = c.tid, tpg = (nch + 3) >> 2;
+    const float *pg = tc_part(c) + (r >> 4) * nkb * 16 + (r & 15);
     const float *pu = pg + tpg * nkb * 16;
     float g = 0.f, u = 0.f;
-#pragma unroll 1
-    for (int kb = 0; kb < nkb; ++kb) { g += pg[kb * 16]; u += pu[kb * 16]; }
-    s_inter[r] = g / (1.0f + expf(-g)) * u;
+#pragma unroll
+    for (int kb = 0; kb < CONS_WARPS / 2; ++kb)
+      if (kb < nkb) { g += pg[kb * 16]; u += pu[kb * 16]; }
+    const float a = g / (1.0f + expf(-g)) * u;
+    c.f(FF_INTER)[r] = a;
+    __half *act16 = reinterpret_cast<__half *>(c.smem + OFF_ACT16);
+    act16[r] = split_half(a, false);
+    act16[ACT16_PITCH + r] = split_half(a, true);
+  } else if (c.tid < 64) {   // rows past the slice multiply stale bytes: zero activations
+    __half *act16 = reinterpret_cast<__half *>(c.smem + OFF_ACT16);
+    act16[c.tid] = __float2half_rn(0.f);
+    act16[ACT16_PITCH + c.tid] = __float2half_rn(0.f);
   }
   QMK_FINE(14);
   return c.chunk + static_cast<uint32_t>(2 * nch);
@@ -304,7 +332,7 @@ __device__ __noinline__ uint32_t attention_tc(const Params &P, Ctx c, const __ha
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // these stores precede the slot's next tiled copy
         __syncwarp();
       }
-      float sc[4] = {0.f, 0.f, 0.f, 0.f};
+      float sc[4] = {0.f, 0.f, 0.f, 0.f}, sc2[4] = {0.f, 0.f, 0.f, 0.f};   // two chains of four dependent MMAs instead of one of eight
       const uint32_t k_row = base + lr * 128;                        // this lane's K row in box 0
       const uint32_t k_xor = ((k_row >> 7) & 7u) << 4;               // swizzle of that row (the same in box 1: boxes are 2048 bytes)
       const uint32_t k_off = (c.lane >> 4) * 16;
@@ -314,9 +342,9 @@ __device__ __noinline__ uint32_t attention_tc(const Params &P, Ctx c, const __ha
         ldsm_x4(k_row + (p >> 1) * KV_BOX + ((((p & 1) * 64) + k_off) ^ k_xor), a0);
         ldsm_x4(k_row + (p >> 1) * KV_BOX + ((((p & 1) * 64) + 32 + k_off) ^ k_xor), a1);
         mma_16816(sc, a0, qf[p][0], qf[p][1]);
-        mma_16816(sc, a1, qf[p][2], qf[p][3]);
+        mma_16816(sc2, a1, qf[p][2], qf[p][3]);
       }
-      float s_top = fmaf(sc[1], LO_INV, sc[0]) * sc_log2, s_bot = fmaf(sc[3], LO_INV, sc[2]) * sc_log2;
+      float s_top = fmaf(sc[1] + sc2[1], LO_INV, sc[0] + sc2[0]) * sc_log2, s_bot = fmaf(sc[3] + sc2[3], LO_INV, sc[2] + sc2[2]) * sc_log2;
       if (rowq >= nrow) s_top = -INFINITY;
       if (rowq + 8 >= nrow) s_bot = -INFINITY;
       float cm = fmaxf(s_top, s_bot);
@@ -411,12 +439,25 @@ __device__ __noinline__ uint32_t attention_tc(const Params &P, Ctx c, const __ha
   return c.chunk;
 }
 
+// 1 / sqrt(mean of squares + eps) over the 1024 values whose squares the consumer threads hold in `ss`; one barrier.
+// (rsqrt.approx: 2 ulp; the sum's order is fixed.)
+__device__ __forceinline__ float block_rstd(const Ctx &c, float ss) {
+  ss = warp_sum(ss);
+  float *red = c.f(F_RED);
+  if (c.lane == 0) red[c.warp] = ss;
+  cons_sync();
+  const float4 r0 = reinterpret_cast<const float4 *>(red)[0], r1 = reinterpret_cast<const float4 *>(red)[1],
+               r2 = reinterpret_cast<const float4 *>(red)[2];
+  const float tot = (((r0.x + r0.y) + (r0.z + r0.w)) + ((r1.x + r1.y) + (r1.z + r1.w))) + ((r2.x + r2.y) + (r2.z + r2.w));
+  return rsqrtf(tot * (1.0f / H) + RMS_EPS);
+}
+
 // fp32 vector value -> residual stream (fp32) and the hi/lo fp16 halves of its RMS-normalised form.
 __device__ __forceinline__ void store_normalised(const Ctx &c, int n, float v, float rstd, float w, float *dst) {
   dst[n] = v;
   const float xn = v * rstd * w;
-  reinterpret_cast<__half *>(c.smem + OFF_XH)[n] = split_half(xn, false);
-  reinterpret_cast<__half *>(c.smem + OFF_XL)[n] = split_half(xn, true);
+  *reinterpret_cast<__half *>(c.smem + OFF_XF + xf_offset(n, 0)) = split_half(xn, false);
+  *reinterpret_cast<__half *>(c.smem + OFF_XF + xf_offset(n, 1)) = split_half(xn, true);
 }
 
 // Waits until use number `use` (1-based) of a sum is complete (see megakernel_fused.cuh), writes the 1024 values
@@ -475,8 +516,7 @@ __device__ __noinline__ void red_wait_norm(const Params &P, const Ctx c, int whi
     v[j] = (valid & (1u << j)) ? static_cast<float>(vi[j]) * RED_INV_SCALE : 0.f;
     ss = fmaf(v[j], v[j], ss);
   }
-  const float tot = block_sum(c, ss);
-  const float rstd = 1.0f / sqrtf(tot * (1.0f / H) + RMS_EPS);
+  const float rstd = block_rstd(c, ss);
 #pragma unroll
   for (int j = 0; j < PT; ++j)
     if (valid & (1u << j)) {
@@ -503,8 +543,7 @@ __device__ __noinline__ void embed_norm(const Params &P, const Ctx c, int token,
     v[j] = n < H ? __half2float(__ldg(erow + n)) : 0.f;
     ss = fmaf(v[j], v[j], ss);
   }
-  const float tot = block_sum(c, ss);
-  const float rstd = 1.0f / sqrtf(tot * (1.0f / H) + RMS_EPS);
+  const float rstd = block_rstd(c, ss);
 #pragma unroll
   for (int j = 0; j < PT; ++j) {
     const int n = c.tid + j * CONS_THREADS;
@@ -513,61 +552,74 @@ __device__ __noinline__ void embed_norm(const Params &P, const Ctx c, int token,
   cons_sync();
 }
 
-// Split-K slice of the O (which = 0) or down (1) projection, as slice_colgemv of megakernel_fused.cuh, on chunks
-// of four K-major rows at the padded pitch.
+// Split-K slice of the O (which = 0) or down (1) projection (see slice_colgemv of megakernel_fused.cuh) on the
+// tensor cores: partial[n] = sum_i act[i] * Wt[first + i][n] with the K-major rows as the A operand read through
+// ldmatrix.trans (tile = 16 outputs x 16 rows), the slice's activations as B (hi / lo columns, from act16).  Warp w
+// takes output tiles w, w + 12, ... over ALL rows of the slice, so a partial is complete when it leaves the warp.
 __device__ __noinline__ uint32_t slice_cols(const Params &P, Ctx c, int which) {
   const SegTab *t = c.segs();
   const int nrows = which ? tctab(c)->ng * CH_ROWS : t->e1 - t->e0;
-  const float *act = c.f(which ? FF_INTER : FF_ATTN);
   const float *resid = c.f(which ? F_X1 : F_X);
   unsigned long long *buf = P.red + (which ? RED_X2 : RED_X1);
   float *prev = c.f(FF_PREV) + (which ? H : 0);
-  const int g = c.warp >> 2, cb = c.warp & 3;
   const int nch = (nrows + CH_ROWS - 1) / CH_ROWS;
-  const int col8 = cb * 32 + c.lane;                // group of eight outputs this lane owns
-  float acc[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  const int ksteps = (nrows + 15) >> 4;               // <= 4 (slices of at most 64 rows)
   const int fb = which ? 30 : 20;
   QMK_FINE(fb + 0);
-#pragma unroll 1
-  for (int ch = g; ch < nch; ch += CONS_WARPS / 4) {
-    const uint32_t idx = c.chunk + static_cast<uint32_t>(ch);
-    if (__all_sync(0xffffffffu, mbar_wait(P, c, c.full(idx % NSLOTS), (idx / NSLOTS) & 1u, WHERE_FULL, false))) {
-      const unsigned char *rows = c.slot(idx) + (idx & 1u) * ODD_SLOT_SKEW;
-#pragma unroll 1
-      for (int r = 0; r < CH_ROWS; ++r) {
-        const int i = ch * CH_ROWS + r;
-        if (i < nrows) {                              // warp-uniform
-          const float a = act[i];
-          float w[8];
-          load_w8(rows + r * ROW_PITCH, col8, 0, w);
+  bool ok = true;
+  if (c.lane < nch) {
+    const uint32_t idx = c.chunk + static_cast<uint32_t>(c.lane);
+    ok = mbar_wait(P, c, c.full(idx % NSLOTS), (idx / NSLOTS) & 1u, WHERE_FULL, false);
+  }
+  ok = __all_sync(0xffffffffu, ok);
+  float *colpart = c.f(FF_COLPART);
+  if (ok) {
+    // B: activations, k-steps 0,1 in bq[0..3] (and 2,3 in bq2); row n of B^T = hi (even n) / lo (odd n) vector
+    const uint32_t act_addr = smem_u32(c.smem + OFF_ACT16) + (c.lane & 1) * (ACT16_PITCH * 2) + (c.lane >> 3) * 16;
+    uint32_t bq[4], bq2[4] = {0u, 0u, 0u, 0u};
+    ldsm_x4(act_addr, bq);
+    if (ksteps > 2) ldsm_x4(act_addr + 64, bq2);
+    // A: this lane's row of each k-step (rows past the slice repeat row 0: their activations are zero)
+    uint32_t arow[4];
 #pragma unroll
-          for (int q = 0; q < 8; ++q) acc[q] = fmaf(w[q], a, acc[q]);
-        }
+    for (int ks = 0; ks < 4; ++ks) {
+      int row = ks * 16 + (c.lane & 7) + 8 * (c.lane >> 4);
+      if (row >= nrows) row = 0;
+      arow[ks] = weight_rows(c, c.chunk + static_cast<uint32_t>(row >> 2)) + (row & 3) * ROW_PITCH + ((c.lane >> 3) & 1) * 16;
+    }
+    // (storing a tile's sums one iteration later, behind the next tile's loads and MMAs, measured slower: 1.65 -> 2.1 us)
+#pragma unroll 1
+    for (int tile = c.warp; tile < H / 16; tile += CONS_WARPS) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t a[4];
+      ldsm_x4_trans(arow[0] + tile * 32, a);
+      mma_16816(acc, a, bq[0], bq[1]);
+      if (ksteps > 1) { ldsm_x4_trans(arow[1] + tile * 32, a); mma_16816(acc, a, bq[2], bq[3]); }
+      if (ksteps > 2) { ldsm_x4_trans(arow[2] + tile * 32, a); mma_16816(acc, a, bq2[0], bq2[1]); }
+      if (ksteps > 3) { ldsm_x4_trans(arow[3] + tile * 32, a); mma_16816(acc, a, bq2[2], bq2[3]); }
+      if ((c.lane & 3) == 0) {
+        colpart[tile * 16 + (c.lane >> 2)] = fmaf(acc[1], LO_INV, acc[0]);
+        colpart[tile * 16 + (c.lane >> 2) + 8] = fmaf(acc[3], LO_INV, acc[2]);
       }
     }
-    __syncwarp();
-    if (c.lane == 0) mbar_arrive_n(c.empty(idx % NSLOTS), EMPTY_UNITS / 4);   // four column-block warps per chunk
   }
+  __syncwarp();
+  if (c.lane < nch) mbar_arrive_n(c.empty((c.chunk + static_cast<uint32_t>(c.lane)) % NSLOTS), EMPTY_UNITS / CONS_WARPS);
   QMK_FINE(fb + 1);
-  float *colpart = c.f(FF_COLPART);
-  {
-    float4 *dst = reinterpret_cast<float4 *>(colpart + g * H + col8 * 8);
-    dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
-  }
   cons_sync();
   QMK_FINE(fb + 2);
   const int n0 = t->n0, n1 = t->n1;
   unsigned long long *mine = buf + (c.cta % P.red_copies) * H;
-#pragma unroll 1
-  for (int n = c.tid; n < H; n += CONS_THREADS) {
-    float v = (colpart[n] + colpart[H + n]) + colpart[2 * H + n];
-    if (n >= n0 && n < n1) v += resid[n];
-    const long long fx = __float2ll_rn(v * RED_SCALE), fx_prev = __float2ll_rn(prev[n] * RED_SCALE);
-    prev[n] = v;
-    red_add_u64(mine + n, (static_cast<unsigned long long>(fx - fx_prev) << RED_CNT_BITS) + 1ull);
+#pragma unroll
+  for (int j = 0; j < (H + CONS_THREADS - 1) / CONS_THREADS; ++j) {
+    const int n = c.tid + j * CONS_THREADS;
+    if (n < H) {
+      float v = colpart[n];
+      if (n >= n0 && n < n1) v += resid[n];
+      const long long fx = __float2ll_rn(v * RED_SCALE), fx_prev = __float2ll_rn(prev[n] * RED_SCALE);
+      prev[n] = v;
+      red_add_u64(mine + n, (static_cast<unsigned long long>(fx - fx_prev) << RED_CNT_BITS) + 1ull);
+    }
   }
   QMK_FINE(fb + 3);
   return c.chunk + static_cast<uint32_t>(nch);
@@ -754,6 +806,8 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel_tc(const _
     split_rows(QKV_CHUNKS, c.ncta, c.cta, a, b); tt->q0 = a; tt->nq = b - a;
     split_rows(GU_CHUNKS, c.ncta, c.cta, a, b); tt->g0 = a; tt->ng = b - a;
     split_rows(P.vocab / CH_ROWS, c.ncta, c.cta, a, b); tt->lm0 = a; tt->nlm = b - a;
+    build_tile_tasks(tt->qkv, &tt->nkb_qkv, 1, tt->nq);
+    build_tile_tasks(tt->gu, &tt->nkb_gu, 2, tt->ng);
   }
   {
     const unsigned long long *src = reinterpret_cast<const unsigned long long *>(P.layers);
@@ -811,7 +865,7 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel_tc(const _
         QMK_STAMP(layer * 12 + 1);
         c.chunk = attention_tc(P, c, nv, layer, pos, tag);
         QMK_STAMP(layer * 12 + 2);
-        merge_slice(P, c, S_step, tag);
+        merge_slice(P, c, S_step, tag, reinterpret_cast<__half *>(c.smem + OFF_ACT16));
         QMK_STAMP(layer * 12 + 3);
         cons_sync();
         c.chunk = slice_cols(P, c, 0);
