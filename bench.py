@@ -204,50 +204,64 @@ def run_reference(args):
 
 
 # --------------------------------------------------------------------------- the engine arm
-def run_ours(args):
-    rank, world, local = dist_env()
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py: no CUDA device; the engine has no CPU path (use --impl reference for the oracle)")
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=device)
+GOLDEN_CTX4096 = os.path.join(ROOT, "tests", "golden", "full_seed0_prompt4096.json")
 
-    import build
-    build.build()
+
+def kv_bytes(context_lens, decode_tokens: int) -> int:
+    """Algorithmic KV bytes of `decode_tokens` steps of sequences that start with these many cached positions:
+    per step and sequence 114,688 B per position attended (the new one included) + one new row written."""
+    per_pos = S.decode_step_bytes(1) - S.decode_step_bytes(0)
+    total = 0
+    for L in context_lens:
+        total += sum(per_pos * (L + i + 1) + per_pos for i in range(decode_tokens))
+    return total
+
+
+def weight_bytes(kind: str) -> int:
+    if kind == "fp8":
+        import quantize
+        return quantize.weight_bytes_fp8()
+    if kind == "nvfp4":
+        import quantize
+        return quantize.weight_bytes_nvfp4()
+    return S.weight_bytes_fp16()
+
+
+def decode_case(device, rank, world, fp16_weights, weights_kind, B, prompt_lens, decode_tokens, steps, warmup,
+                check_golden=False):
+    """One decode configuration on this rank's GPU: prompts prefilled (untimed), then `steps` timed launches of
+    `decode_tokens` greedy tokens for all B sequences, then the same through the host API.  Returns a dict with the
+    device-timed and end-to-end rates (max over ranks), per-launch times and the HBM roofline of the launch."""
     import qwen_megakernel_C as C
-    from Model.Qwen06B_architecture import Decoder
-
-    PROMPT_LEN, DECODE_TOKENS = args.prompt_len, args.decode_tokens   # defaults: the benchmark configuration
-    MAX_SEQ_LEN = PROMPT_LEN + DECODE_TOKENS
-    host_weights = S.make_weights(seed=0, max_seq_len=16)
-    expanded = False              # quantised weights stored as fp16 (engines without a packed path)
-    if args.weights != "fp16" and args.batch > 4:
+    from Model.Qwen06B_architecture import BatchDecoder, Decoder
+    max_seq = max(prompt_lens) + decode_tokens
+    expanded = False
+    weights = fp16_weights
+    if weights_kind != "fp16":
         import quantize
-        host_weights, _ = (quantize.expand_weights_fp8 if args.weights == "fp8" else quantize.expand_weights_nvfp4)(host_weights)
-        expanded = True
-    elif args.weights == "nvfp4":
-        raise SystemExit("bench.py: --weights nvfp4 needs --batch > 4 (expanded to fp16 on the tensor-core path)")
-    elif args.weights == "fp8":   # BASELINE.json configs[2] weight format, packed rows (batch <= 4)
-        import quantize
-        host_weights, _ = quantize.quantize_weights_fp8(host_weights)
-    engine_format = "fp16" if expanded else args.weights
-    weights = S.weights_to(host_weights, str(device))
-    B = args.batch
+        if B > 4:      # tensor-core batched path: the quantised VALUES, stored expanded as fp16 (no packed GEMM operand)
+            weights, _ = (quantize.expand_weights_fp8 if weights_kind == "fp8" else quantize.expand_weights_nvfp4)(fp16_weights)
+            expanded = True
+        elif weights_kind == "fp8":
+            weights, _ = quantize.quantize_weights_fp8(fp16_weights)
+        else:
+            raise SystemExit("bench.py: nvfp4 needs --batch > 4 (values expanded to fp16 on the tensor-core path)")
+    engine_format = "fp16" if (expanded or weights_kind == "fp16") else weights_kind
+    parity = None
     if B == 1:
-        eng = Decoder(weights=weights, tokenizer=S.StubTokenizer(-1), verbose=False, max_seq_len=MAX_SEQ_LEN,
+        eng = Decoder(weights=weights, tokenizer=S.StubTokenizer(-1), verbose=False, max_seq_len=max_seq,
                       device=str(device), weight_format=engine_format)
-        prompt = S.make_prompt(PROMPT_LEN, seed=rank)   # each replica serves its own stream
+        prompt = S.make_prompt(prompt_lens[0], seed=rank)   # each replica serves its own stream
         eng.reset()
-        eng.prefill_ids(prompt[:-1])                    # untimed; fills 4095 cache rows
+        eng.prefill_ids(prompt[:-1])                        # untimed
         start_pos = eng.position
         first = prompt[-1]
-        log = eng._output_log[:DECODE_TOKENS]
-        host_log = eng._output_log_cpu[:DECODE_TOKENS]
+        log = eng._output_log[:decode_tokens]
+        host_log = eng._output_log_cpu[:decode_tokens]
+        engine_name = "persistent megakernel"
 
         def op_call():
-            eng._gen(first, DECODE_TOKENS, *eng._common(), log, eng.num_layers, start_pos, eng.max_seq_len,
+            eng._gen(first, decode_tokens, *eng._common(), log, eng.num_layers, start_pos, eng.max_seq_len,
                      eng._attn_scale, -1)
 
         def api_call():
@@ -262,23 +276,21 @@ def run_ours(args):
                 out.append(t)
             return out
     else:
-        # B sequences per launch (multi-sequence kernel), every one at the benchmark context length
-        from Model.Qwen06B_architecture import BatchDecoder
-        eng = BatchDecoder(weights=weights, tokenizer=S.StubTokenizer(-1), num_sequences=B, max_seq_len=MAX_SEQ_LEN,
+        eng = BatchDecoder(weights=weights, tokenizer=S.StubTokenizer(-1), num_sequences=B, max_seq_len=max_seq,
                            device=str(device), weight_format=engine_format,
                            prefill_mode="tensor" if engine_format == "fp16" else "serial")
-        persistent = eng.engine == "persistent"
-        prompts = [S.make_prompt(PROMPT_LEN, seed=rank * 16 + b) for b in range(B)]
+        engine_name = "persistent megakernel" if eng.engine == "persistent" else "tcgen05 GEMM path"
+        prompts = [S.make_prompt(prompt_lens[b], seed=rank * 128 + b) for b in range(B)]
         for b in range(B):
-            eng._prefill_slot(b, prompts[b][:-1])       # untimed
+            eng._prefill_slot(b, prompts[b][:-1])           # untimed
         firsts = [p[-1] for p in prompts]
         starts = list(eng.positions)
-        logs = [eng._logs[b][:DECODE_TOKENS] for b in range(B)]
-        host_logs = eng._logs_cpu[:, :DECODE_TOKENS]
+        logs = [eng._logs[b][:decode_tokens] for b in range(B)]
+        host_logs = eng._logs_cpu[:, :decode_tokens]
         base = eng._base
 
         def op_call():
-            eng._gen_batch(firsts, starts, DECODE_TOKENS, base._embed_weight, base._layer_weights_packed,
+            eng._gen_batch(firsts, starts, decode_tokens, base._embed_weight, base._layer_weights_packed,
                            base._final_norm_weight, base._lm_head_weight, base._cos_table, base._sin_table,
                            eng._k_caches, eng._v_caches, logs, base.num_layers, eng.max_seq_len, base._attn_scale)
 
@@ -295,15 +307,23 @@ def run_ours(args):
                     out.append(t)
             return out
 
-    for _ in range(max(args.warmup, 0)):
+    for _ in range(max(warmup, 0)):
         op_call()
     ref_tokens = api_call()
-    assert len(ref_tokens) == DECODE_TOKENS * B
+    assert len(ref_tokens) == decode_tokens * B
+    if check_golden and rank == 0:
+        # parity of the benchmarked configuration itself (outside the timed region): rank 0's prompt is the golden
+        # file's, its first tokens must be the CPU oracle's
+        with open(GOLDEN_CTX4096) as f:
+            g = json.load(f)
+        n = len(g["tokens"])
+        parity = (prompt_lens[0] == g["prompt_len"] and ref_tokens[:n] == g["tokens"])
+        if not parity:
+            raise SystemExit(f"bench.py: decode does not reproduce the golden tokens: {ref_tokens[:n]} vs {g['tokens']}")
 
-    # ---- device-timed region: K steps, one launch each
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     barrier(world)
-    with ClockSampler(local) as clocks:
+    with ClockSampler(device.index) as clocks:
         t_begin = torch.cuda.Event(enable_timing=True)
         t_end = torch.cuda.Event(enable_timing=True)
         t_begin.record()
@@ -313,95 +333,52 @@ def run_ours(args):
             b.record()
         t_end.record()
         barrier(world)
-    total_s = t_begin.elapsed_time(t_end) / 1e3
+    own_s = t_begin.elapsed_time(t_end) / 1e3
     launch_ms = [a.elapsed_time(b) for a, b in ev]
-    total_s = max_over_ranks(total_s, world, device)
-    value = aggregate(args.steps * DECODE_TOKENS * B, total_s, world)
+    total_s = max_over_ranks(own_s, world, device)
 
-    # ---- end-to-end region through the host API
     barrier(world)
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(steps):
         out = api_call()
     torch.cuda.synchronize()
     e2e_s = max_over_ranks(time.perf_counter() - t0, world, device)
     assert out == ref_tokens, "decode is not reproducible run to run"
-    e2e_value = aggregate(args.steps * DECODE_TOKENS * B, e2e_s, world)
 
+    per_rank = [statistics.mean(launch_ms)]
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor(per_rank, dtype=torch.float64, device=device)
+        gathered = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(gathered, t)
+        per_rank = [float(x.item()) for x in gathered]
+    tokens = steps * decode_tokens * B
+    launch_bytes = decode_tokens * weight_bytes("fp16" if expanded else weights_kind) + kv_bytes(
+        [L - 1 for L in prompt_lens], decode_tokens)
     peak, peak_kind = measured_peak_gbs()
-    avg_launch_s = statistics.mean(launch_ms) / 1e3
-    # algorithmic bytes of a launch: weights once per step, KV of every sequence
-    kv_only = step_bytes(PROMPT_LEN, DECODE_TOKENS, "fp16") - DECODE_TOKENS * S.weight_bytes_fp16()
-    launch_bytes = step_bytes(PROMPT_LEN, DECODE_TOKENS, "fp16" if expanded else args.weights) + (B - 1) * kv_only
-    achieved = launch_bytes / avg_launch_s / 1e9
-    traffic = None   # DRAM bytes per launch from the committed ncu capture, scaled by tokens per launch
-    try:
-        with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
-            per_token = json.load(f).get("qwen3_decode_megakernel_dram_bytes_per_token")
-        if per_token and args.weights == "fp16" and B == 1:
-            traffic = per_token * DECODE_TOKENS
-    except Exception:
-        pass
-
-    if rank == 0:
-        line = {
-            "metric": METRIC if B == 1 else f"batch-{B} decode tok/s (all sequences)", "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": 1e3 * total_s / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "fp16" if (args.weights == "fp16" or expanded) else "fp8-e4m3 weights, fp32 math",
-            "data": "synthetic",
-            "config": {"weights": args.weights + (" (quantised values, stored expanded as fp16)" if expanded else ""), "workload": WORKLOAD if (PROMPT_LEN, DECODE_TOKENS) == (4096, 256) else
-                       f"profiling case: {PROMPT_LEN} prompt tokens, {DECODE_TOKENS} decode tokens per step",
-                       "tokens_per_step": DECODE_TOKENS * B, "sequences_per_launch": B,
-                       "engine": "persistent megakernel" if (B == 1 or persistent) else "tcgen05 GEMM path", "replicas": world,
-                       "l2": "no flush needed: each token streams 1.19 GB of weights + 0.47 GB of KV, > 126 MB L2",
-                       "grid_ctas": C.num_ctas()},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": traffic, "peak_kind": f"of {peak_kind}",
-                         "bytes_per_launch": launch_bytes, "launch_ms": statistics.mean(launch_ms),
-                         "frac_of_nominal_8TBs": achieved / 8000.0},
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * B,
-                    "d2h_bytes_per_step": 4 * DECODE_TOKENS * B},
-            "gpu_launches": args.steps if (B == 1 or persistent) else args.steps * DECODE_TOKENS * (7 * 28 + 4),
-            "clocks": clocks.summary(),
-        }
-        if world == 1 and not args.no_cpu_baseline:
-            threads = os.cpu_count() or 1
-            n = 16
-            rate, dt, _ = cpu_decode_rate(n, threads)
-            line["cpu_baseline"] = {
-                "value": rate, "unit": UNIT, "cores": threads, "kind": "port",
-                "sample": f"{n} greedy tokens at context {PROMPT_LEN} (KV pre-filled with random values), "
-                          f"oracle torch fp32, {dt:.1f} s"}
-        print(json.dumps(line))
-    if world > 1:
-        import torch.distributed as dist
-        dist.barrier()
-        dist.destroy_process_group()
+    achieved = launch_bytes / (statistics.mean(launch_ms) / 1e3) / 1e9
+    res = dict(value=aggregate(tokens, total_s, world), e2e=aggregate(tokens, e2e_s, world),
+               ms_per_step=1e3 * total_s / steps, launch_ms=statistics.mean(launch_ms),
+               per_rank_launch_ms={"min": min(per_rank), "median": statistics.median(per_rank), "max": max(per_rank)},
+               bytes_per_launch=launch_bytes, achieved_gbs=achieved, frac=achieved / peak, peak=peak, peak_kind=peak_kind,
+               engine=engine_name, expanded=expanded, clocks=clocks.summary(), grid=C.num_ctas(), parity=parity,
+               launches=steps if engine_name == "persistent megakernel" else steps * decode_tokens * (7 * 28 + 4))
+    del eng
+    torch.cuda.empty_cache()
+    return res
 
 
-def run_continuous(args):
-    """Continuous-batching job (the multi-replica serving configuration, scaled by --continuous): N requests
-    per GPU, prompt lengths uniform in [64, 2048], 128 greedy tokens each, up to --batch live sequences.
-    Wall-clock of the whole job, prefill included; one JSON line with its own metric name."""
-    rank, world, local = dist_env()
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py: no CUDA device; the engine has no CPU path")
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=device)
-    import build
-    build.build()
+def continuous_case(device, rank, world, fp16_weights, requests, slots, prefill="tensor", overlap=1):
+    """BASELINE.json's serving configuration on this rank's GPU: `requests` requests, prompt lengths uniform in
+    [64, 2048], 128 greedy tokens each, continuous batching with up to `slots` live sequences; wall clock of the
+    whole job (prefill included), slowest replica."""
     from Model.Qwen06B_architecture import BatchDecoder
     from scheduler import ContinuousBatcher
-    slots = max(args.batch, 2)
     new_tokens = 128
-    weights = S.weights_to(S.make_weights(seed=0, max_seq_len=16), str(device))
-    eng = BatchDecoder(weights=weights, tokenizer=S.StubTokenizer(-1), num_sequences=slots, max_seq_len=2048 + new_tokens,
-                       device=str(device), prefill_mode=args.prefill)
+    eng = BatchDecoder(weights=fp16_weights, tokenizer=S.StubTokenizer(-1), num_sequences=slots, max_seq_len=2048 + new_tokens,
+                       device=str(device), prefill_mode=prefill)
     gen = torch.Generator("cpu").manual_seed(rank)             # a different request stream per replica
-    lens = torch.randint(64, 2049, (args.continuous,), generator=gen).tolist()
+    lens = torch.randint(64, 2049, (requests,), generator=gen).tolist()
     prompts = [S.make_prompt(L, seed=1000 * rank + i) for i, L in enumerate(lens)]
     prefill_s = [0.0]
     inner = eng.prefill_slot
@@ -412,35 +389,135 @@ def run_continuous(args):
         prefill_s[0] += time.perf_counter() - t
     eng.prefill_slot = timed_prefill
     sch = ContinuousBatcher(eng, eos_token_id=None, quantum=32,
-                            overlap_prefill=bool(args.overlap) and getattr(eng, "supports_overlap", False))
+                            overlap_prefill=bool(overlap) and getattr(eng, "supports_overlap", False))
     sch.submit(prompts[0][:64], 8)                             # warm-up: both kernels, all buffers
     sch.run_until_idle()
     prefill_s[0] = 0.0
     launches0 = sch.launches
     barrier(world)
-    with ClockSampler(local) as clocks:
+    with ClockSampler(device.index) as clocks:
         t0 = time.perf_counter()
         futs = [sch.submit(p, new_tokens) for p in prompts]
         sch.run_until_idle()
         torch.cuda.synchronize()
-        wall = time.perf_counter() - t0
+        own_wall = time.perf_counter() - t0
     n_out = sum(len(f.result().tokens) for f in futs)
-    assert n_out == args.continuous * new_tokens
-    wall = max_over_ranks(wall, world, device)
-    if rank == 0:
-        print(json.dumps({
-            "metric": "continuous-batching generated tok/s (prefill included)", "value": world * n_out / wall,
-            "unit": UNIT, "n_gpus": world, "requests_per_gpu": args.continuous, "live_sequences": slots,
-            "new_tokens_per_request": new_tokens, "prompt_tokens": sum(lens), "wall_s": wall,
-            "prefill_s": prefill_s[0], "decode_s": wall - prefill_s[0],
-            "decode_only_tok_s": n_out / max(wall - prefill_s[0], 1e-9), "launches": sch.launches - launches0,
-            "prefill": args.prefill, "overlap_prefill": sch.overlap_prefill, "prompt_tok_s": sum(lens) / max(prefill_s[0], 1e-9),
-            "scaling": "weak", "data": "synthetic", "dtype": "fp16", "clocks": clocks.summary(),
-            "note": "rank 0's own prefill/decode split; value uses the slowest replica's wall time"}))
+    assert n_out == requests * new_tokens
+    wall = max_over_ranks(own_wall, world, device)
+    res = dict(value=world * n_out / wall, wall_s=wall, own_wall_s=own_wall, requests_per_gpu=requests, live_sequences=slots,
+               new_tokens_per_request=new_tokens, prompt_tokens=sum(lens), prefill_s=prefill_s[0],
+               decode_s=own_wall - prefill_s[0], decode_only_tok_s=n_out / max(own_wall - prefill_s[0], 1e-9),
+               prompt_tok_s=sum(lens) / max(prefill_s[0], 1e-9), launches=sch.launches - launches0, prefill=prefill,
+               overlap_prefill=sch.overlap_prefill, clocks=clocks.summary())
+    del sch, eng
+    torch.cuda.empty_cache()
+    return res
+
+
+def init_engine_arm():
+    rank, world, local = dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the engine has no CPU path (use --impl reference for the oracle)")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    import build
+    build.build()
+    return rank, world, device
+
+
+def finish_engine_arm(world):
     if world > 1:
         import torch.distributed as dist
         dist.barrier()
         dist.destroy_process_group()
+
+
+def run_ours(args):
+    rank, world, device = init_engine_arm()
+    weights = S.weights_to(S.make_weights(seed=0, max_seq_len=16), str(device))
+    B = args.batch
+    headline = (args.prompt_len, args.decode_tokens, args.weights, B) == (PROMPT_LEN, DECODE_TOKENS, "fp16", 1)
+    r = decode_case(device, rank, world, weights, args.weights, B, [args.prompt_len] * B, args.decode_tokens, args.steps,
+                    args.warmup, check_golden=headline)
+    traffic = None   # DRAM bytes per launch from the committed ncu capture, scaled by tokens per launch
+    try:
+        with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
+            per_token = json.load(f).get("qwen3_decode_megakernel_dram_bytes_per_token")
+        if per_token and headline:
+            traffic = per_token * args.decode_tokens
+    except Exception:
+        pass
+    line = {
+        "metric": METRIC if B == 1 else f"batch-{B} decode tok/s (all sequences)", "value": r["value"], "unit": UNIT,
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp16" if (args.weights == "fp16" or r["expanded"]) else "fp8-e4m3 weights, fp32 math", "data": "synthetic",
+        "config": {"weights": args.weights + (" (quantised values, stored expanded as fp16)" if r["expanded"] else ""),
+                   "workload": WORKLOAD if (args.prompt_len, args.decode_tokens) == (PROMPT_LEN, DECODE_TOKENS) else
+                   f"profiling case: {args.prompt_len} prompt tokens, {args.decode_tokens} decode tokens per step",
+                   "tokens_per_step": args.decode_tokens * B, "sequences_per_launch": B, "engine": r["engine"], "replicas": world,
+                   "l2": "no flush needed: each token streams 1.19 GB of weights + 0.47 GB of KV, > 126 MB L2",
+                   "grid_ctas": r["grid"]},
+        "roofline": {"bound": "hbm", "achieved": r["achieved_gbs"], "peak": r["peak"], "unit": "GB/s", "frac": r["frac"],
+                     "traffic": traffic, "peak_kind": f"of {r['peak_kind']}", "bytes_per_launch": r["bytes_per_launch"],
+                     "launch_ms": r["launch_ms"], "frac_of_nominal_8TBs": r["achieved_gbs"] / 8000.0},
+        "e2e": {"value": r["e2e"], "unit": UNIT, "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * args.decode_tokens * B},
+        "gpu_launches": r["launches"], "clocks": r["clocks"], "per_rank_launch_ms": r["per_rank_launch_ms"],
+    }
+    if r["parity"] is not None:
+        line["parity_checked"] = bool(r["parity"])
+    if headline and not args.no_extra:
+        # the other BASELINE.json configurations, each with its own algorithmic-bytes roofline; every rank runs them
+        def brief(c):
+            return {"value": c["value"], "unit": UNIT, "e2e": c["e2e"], "ms_per_step": c["ms_per_step"], "engine": c["engine"],
+                    "roofline_frac": c["frac"], "achieved_gbs": c["achieved_gbs"], "bytes_per_launch": c["bytes_per_launch"],
+                    "weights_stored_as": "fp16 (quantised values expanded)" if c["expanded"] else None,
+                    "per_rank_launch_ms": c["per_rank_launch_ms"]}
+        extra = {}
+        c3 = {}
+        for b3 in (1, 4, 16):
+            c3[f"batch{b3}"] = brief(decode_case(device, rank, world, weights, "fp8", b3, [1024] * b3, 128, 2, 1))
+        extra["config3"] = {"workload": "configs[2]: FP8-E4M3 weights (per-row fp32 scale), 1024-token prompts, 128 decode steps",
+                            **c3}
+        gen = torch.Generator("cpu").manual_seed(0)
+        lens4 = torch.randint(128, 2049, (64,), generator=gen).tolist()
+        extra["config4"] = {"workload": "configs[3]: NVFP4 weight values, batch 64, prompt lengths uniform in [128, 2048], 128 decode steps",
+                            **brief(decode_case(device, rank, world, weights, "nvfp4", 64, lens4, 128, 2, 1))}
+        c5 = continuous_case(device, rank, world, weights, 256, 32)
+        extra["config5"] = {"workload": "configs[4]: 256 requests per GPU, prompts uniform in [64, 2048], 128 greedy tokens each, "
+                                        "continuous batching, <= 32 live sequences", "unit": UNIT,
+                            **{k: c5[k] for k in ("value", "wall_s", "prefill_s", "decode_s", "decode_only_tok_s", "prompt_tok_s",
+                                                  "launches", "overlap_prefill")}}
+        line["extra"] = extra
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            n = 16
+            rate, dt, _ = cpu_decode_rate(n, threads)
+            line["cpu_baseline"] = {
+                "value": rate, "unit": UNIT, "cores": threads, "kind": "port",
+                "sample": f"{n} greedy tokens at context {PROMPT_LEN} (KV pre-filled with random values), "
+                          f"oracle torch fp32, {dt:.1f} s"}
+        print(json.dumps(line))
+    finish_engine_arm(world)
+
+
+def run_continuous(args):
+    """Continuous-batching job (the multi-replica serving configuration, scaled by --continuous): N requests
+    per GPU, prompt lengths uniform in [64, 2048], 128 greedy tokens each, up to --batch live sequences.
+    Wall-clock of the whole job, prefill included; one JSON line with its own metric name."""
+    rank, world, device = init_engine_arm()
+    weights = S.weights_to(S.make_weights(seed=0, max_seq_len=16), str(device))
+    c = continuous_case(device, rank, world, weights, args.continuous, max(args.batch, 2), args.prefill, args.overlap)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "continuous-batching generated tok/s (prefill included)", "unit": UNIT, "n_gpus": world,
+            "scaling": "weak", "data": "synthetic", "dtype": "fp16",
+            "note": "rank 0's own prefill/decode split; value uses the slowest replica's wall time", **c}))
+    finish_engine_arm(world)
 
 
 def main():
@@ -450,6 +527,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle leg (profiling runs)")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="headline workload only: skip the FP8 / NVFP4 / continuous-batching configurations of `extra`")
     ap.add_argument("--weights", choices=["fp16", "fp8", "nvfp4"], default="fp16",
                     help="weight format (default fp16 = the benchmark configuration)")
     ap.add_argument("--batch", type=int, default=1,

@@ -206,10 +206,22 @@ class Decoder:
 
         self._gen = _require_megakernel_op("generate_nosync")
         self._prefill_op = _require_megakernel_op("prefill")
+        self._rope_from_table = int(bool(rope_from_table))
+        self._inv_freq = rope_inv_freq()
+        row_bytes = (HIDDEN_SIZE + 16) if weight_format == "fp8" else 2 * HIDDEN_SIZE
+        if self._embed_weight.numel() * self._embed_weight.element_size() != self.vocab_size * row_bytes:
+            raise RuntimeError(f"embedding tensor does not have {self.vocab_size} rows of {row_bytes} bytes: "
+                               f"weight_format={weight_format!r} does not match the weights")
+        self.apply_options()
+
+    def apply_options(self) -> None:
+        """The library keeps vocabulary size, weight format, RoPE mode and frequencies per DEVICE, not per decoder.
+        Every op of this decoder re-applies its own values first (host-side and cheap: unchanged values are
+        recognised), so decoders with different vocabularies or weight formats can live on one GPU."""
         if qwen_megakernel_C is not None and hasattr(qwen_megakernel_C, "configure"):
-            qwen_megakernel_C.configure(vocab_size=self.vocab_size, rope_from_table=int(bool(rope_from_table)))
-            qwen_megakernel_C.set_weight_format(weight_format)
-            qwen_megakernel_C.set_inv_freq(rope_inv_freq())
+            qwen_megakernel_C.configure(vocab_size=self.vocab_size, rope_from_table=self._rope_from_table)
+            qwen_megakernel_C.set_weight_format(self.weight_format)
+            qwen_megakernel_C.set_inv_freq(self._inv_freq)
 
     # ------------------------------------------------------------------ argument packing
     def _common(self):
@@ -243,6 +255,7 @@ class Decoder:
 
     def step(self, input_token_id: int) -> int:
         """One decode step through the ``decode`` op (Model/Qwen06B_architecture.py:351-380)."""
+        self.apply_options()
         out = _decode(int(input_token_id), *self._common(), self.num_layers, self._position,
                       self.max_seq_len, self._attn_scale)
         tok = int(out.item())
@@ -254,6 +267,7 @@ class Decoder:
         """KV cache for ``ids`` at the current position through the ``prefill`` op."""
         if len(ids) == 0:
             return
+        self.apply_options()
         t = torch.tensor(list(ids), dtype=torch.int32)
         if self.prefill_mode == "tensor":
             _require_megakernel_op("prefill_chunked")(
@@ -280,6 +294,7 @@ class Decoder:
         log = self._output_log[:max_tokens]
         log.fill_(-1)
         eos = self._eos()
+        self.apply_options()
         self._gen(ids[-1], max_tokens, *self._common(), log, self.num_layers, self._position,
                   self.max_seq_len, self._attn_scale, eos)
         host = self._output_log_cpu[:max_tokens]
@@ -393,6 +408,7 @@ class BatchDecoder:
         logs = [self._logs[b][:steps] for b in slots]
         ctx = torch.cuda.stream(self._decode_stream) if self._decode_stream is not None else contextlib.nullcontext()
         out = []
+        base.apply_options()
         with ctx:
             self._gen_batch(list(first_tokens), [self.positions[b] for b in slots], steps, base._embed_weight,
                             base._layer_weights_packed, base._final_norm_weight, base._lm_head_weight,
@@ -430,6 +446,7 @@ class BatchDecoder:
         logs = [self._logs[b][:max_tokens] for b in range(n)]
         for log in logs:
             log.fill_(-1)
+        base.apply_options()
         self._gen_batch(firsts, self.positions[:n], max_tokens, base._embed_weight, base._layer_weights_packed,
                         base._final_norm_weight, base._lm_head_weight, base._cos_table, base._sin_table,
                         self._k_caches[:n], self._v_caches[:n], logs, base.num_layers, self.max_seq_len,

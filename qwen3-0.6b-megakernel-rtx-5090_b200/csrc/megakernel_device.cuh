@@ -30,7 +30,7 @@ constexpr float RMS_EPS = 1e-6f;
 // most 4 warps on each SM sub-partition, which allows 128 registers per thread and a spill-free
 // kernel; 16 + 1 caps registers at 96 and spills.
 constexpr int CONS_WARPS = QMK_CONS_WARPS;
-constexpr int CONS_THREADS = CONS_WARPS * 32;   // 512 math threads
+constexpr int CONS_THREADS = CONS_WARPS * 32;   // 384 math threads
 constexpr int THREADS = CONS_THREADS + 32;      // + 1 producer warp
 // Ring geometry.  The tensor-core build (QMK_TC_BUILD) overrides it: slots hold four weight rows padded to
 // 2064 bytes, and a slot is freed by 12 arrival units (1, 2, 3, 4, 6 or 12 warps share a chunk there).
@@ -126,7 +126,7 @@ __device__ __forceinline__ unsigned long long now_ns() {
 }
 __device__ __forceinline__ void cons_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONS_THREADS) : "memory"); }
 
-// Consumer barrier that also ORs a predicate over all 512 threads (same result everywhere).
+// Consumer barrier that also ORs a predicate over all math threads (same result everywhere).
 __device__ __forceinline__ bool cons_any(bool pred) {
   uint32_t r;
   asm volatile(
@@ -176,10 +176,11 @@ __device__ __forceinline__ float warp_max(float v) {
 
 // ----------------------------------------------------------------------------- per-CTA state
 // Everything below is force-inlined into the one kernel and keeps its state in registers or in
-// shared memory at fixed offsets.  The kernel must compile to a ZERO-byte stack frame: with 222 KB
-// of shared memory carved out, L1 is ~30 KB for 544 threads, so any per-thread local memory
+// shared memory at fixed offsets.  The kernel must compile to (next to) no stack frame: with 222 KB
+// of shared memory carved out, L1 is ~30 KB for 416 threads, so any per-thread local memory
 // (escaping structs, dynamically indexed local arrays, spills) turns every touch into an L2
-// round trip on the critical path.  build.py fails the build if ptxas reports a stack frame.
+// round trip on the critical path.  build.py reads ptxas' report and fails the build when a decode
+// megakernel's frame exceeds 16 bytes (they have 0 to 8).
 
 constexpr size_t SMEM_RING = static_cast<size_t>(NSLOTS) * SLOT_BYTES;
 // fp32 regions (offsets in floats from the end of the ring)
@@ -191,7 +192,7 @@ constexpr int F_RED = F_VEC + I;             // block reduction scratch         
 constexpr int F_Q = F_RED + 32;              // rotated query heads                [2][128]
 constexpr int F_KNEW = F_Q + 2 * D;          // new K row (fp16-rounded)           [128]
 constexpr int F_VNEW = F_KNEW + D;           // new V row (fp16-rounded)           [128]
-constexpr int F_WPART = F_VNEW + D;          // per-warp attention partials        [16][2][130]
+constexpr int F_WPART = F_VNEW + D;          // per-warp attention partials        [12][2][130]
 constexpr int F_CS = F_WPART + CONS_WARPS * 2 * PART_STRIDE;  // cos[64], sin[64] of this position
 constexpr int F_AMAX = F_CS + 2 * (D / 2);   // argmax partials of all CTAs        [2*256]
 constexpr int F_MISC = F_AMAX + 2 * MAX_CTAS;  // [0,1] new-row scores, [16] token, [32..47]/[48..63] warp argmax
@@ -735,7 +736,7 @@ __device__ __forceinline__ float row_partial_regs(const unsigned char *row, cons
 }
 #if QMK_MAX_SEQ == 1
 // ----------------------------------------------------------------------------- single-sequence math
-// sum over the 512 consumer threads; contains one consumer barrier
+// sum over the consumer threads; contains one consumer barrier
 __device__ __forceinline__ float block_sum(const Ctx &c, float v) {
   v = warp_sum(v);
   float *red = c.f(F_RED);

@@ -199,6 +199,7 @@ struct Engine {
   int repl = 4;              // measured: 835 -> 752 us/token at short context, 1152 -> 1061 at 4096
   int stream_inflight = 0;   // measured: pacing the stream changes nothing
   bool inv_freq_set = false;
+  float inv_freq[qmk::D / 2] = {};   // host copy of what c_inv_freq holds (when inv_freq_set)
   // fused single-sequence kernel (megakernel_fused.cuh)
   int fused = 2;             // 0: always the unfused kernel; 1: fused, CUDA-core row products; 2: fused, tensor-core row products (fp16 weights)
   int red_copies = 1;
@@ -323,6 +324,8 @@ int ensure_rope(Engine *e, int max_seq_len, cudaStream_t stream) {
   QMK_CUDA(e, cudaMalloc(&e->rope, sizeof(float) * qmk::D * cap));
   qmk::rope_table_kernel<<<(cap * (qmk::D / 2) + 255) / 256, 256, 0, stream>>>(e->rope, cap);
   QMK_CUDA(e, cudaGetLastError());
+  // the table is shared by launches on other streams (overlapped prefill): it is complete before it is published
+  QMK_CUDA(e, cudaStreamSynchronize(stream));
   e->rope_cap = cap;
   return QMK_OK;
 }
@@ -570,8 +573,11 @@ int qmk_set_inv_freq(const float *inv_freq64) {
   std::lock_guard<std::mutex> lock(g_mutex);
   Engine *e = current_engine_unlocked();
   if (!e || !inv_freq64) return QMK_ERR_BAD_ARGUMENT;
+  // callers re-apply their options before every op: the same frequencies again cost nothing
+  if (e->inv_freq_set && memcmp(e->inv_freq, inv_freq64, sizeof(e->inv_freq)) == 0) return QMK_OK;
   QMK_CUDA(e, cudaDeviceSynchronize());   // no launch may still be reading the old table
   QMK_CUDA(e, cudaMemcpyToSymbol(qmk::c_inv_freq, inv_freq64, sizeof(float) * (qmk::D / 2)));
+  memcpy(e->inv_freq, inv_freq64, sizeof(e->inv_freq));
   e->inv_freq_set = true;
   e->rope_cap = 0;   // rebuilt with the new frequencies at the next launch
   return QMK_OK;
@@ -788,9 +794,12 @@ int qmk_sync_status(void) {
 }
 
 const char *qmk_last_error(void) {
+  // a copy per calling thread, taken under the lock: another thread's next call may rewrite the engine's string
+  static thread_local std::string mine;
   std::lock_guard<std::mutex> lock(g_mutex);
   Engine *e = current_engine_unlocked();
-  return e ? e->last_error.c_str() : "no CUDA device";
+  mine = e ? e->last_error : std::string("no CUDA device");
+  return mine.c_str();
 }
 
 int qmk_num_ctas(void) {

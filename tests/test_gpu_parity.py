@@ -330,3 +330,39 @@ def test_kmajor_copies_follow_the_weights(C, tiny_cfg):
     dev["embed_weight"].copy_(w2["embed_weight"])
     dev["final_norm_weight"].copy_(w2["final_norm_weight"])
     assert eng.generate_ids(ids, 5) == want2
+
+
+def test_decoders_with_different_options_share_a_gpu(C, tiny_cfg):
+    """Vocabulary size, weight format and RoPE mode are per-device state of the library; every decoder re-applies
+    its own before each op, so two live decoders that differ in them can be used in turn."""
+    import quantize
+    w_a = _tiny_weights(tiny_cfg)
+    cfg_b = dict(tiny_cfg, seed=tiny_cfg["seed"] + 7, vocab_size=2048)
+    w_b = _tiny_weights(cfg_b)
+    ids_a = S.make_prompt(9, seed=21, vocab_size=tiny_cfg["vocab_size"])
+    ids_b = S.make_prompt(7, seed=22, vocab_size=cfg_b["vocab_size"])
+    eng_b_w, oracle_b_w = quantize.quantize_weights_fp8(w_b)
+    want_a = OracleDecoder(w_a, max_seq_len=tiny_cfg["max_seq_len"]).generate_ids(ids_a, 5)[0]
+    want_b = OracleDecoder(oracle_b_w, max_seq_len=tiny_cfg["max_seq_len"]).generate_ids(ids_b, 5)[0]
+    from Model.Qwen06B_architecture import Decoder
+    a = Decoder(weights=S.weights_to(w_a, "cuda"), verbose=False, max_seq_len=tiny_cfg["max_seq_len"])
+    b = Decoder(weights=S.weights_to(eng_b_w, "cuda"), verbose=False, max_seq_len=tiny_cfg["max_seq_len"],
+                weight_format="fp8")
+    try:
+        for _ in range(2):
+            assert a.generate_ids(ids_a, 5) == want_a
+            assert b.generate_ids(ids_b, 5) == want_b
+        # step mode too
+        a.reset()
+        b.reset()
+        ta = tb = None
+        for t in ids_a:
+            ta = a.step(t)
+        for t in ids_b:
+            tb = b.step(t)
+        assert ta == want_a[0] and tb == want_b[0]
+        with pytest.raises(RuntimeError, match="weight_format"):
+            Decoder(weights=S.weights_to(eng_b_w, "cuda"), verbose=False, max_seq_len=tiny_cfg["max_seq_len"])
+    finally:
+        C.set_weight_format("fp16")
+        C.configure(vocab_size=tiny_cfg["vocab_size"])

@@ -81,3 +81,16 @@ def test_stub_tokenizer_roundtrip():
     assert tok.encode("5 17 230") == [5, 17, 30]
     assert tok.decode([5, 17]) == "5 17"
     assert tok.apply_chat_template([{"role": "user", "content": "1 2"}]) == "1 2"
+
+
+def test_build_rejects_a_stack_frame_in_a_decode_megakernel():
+    """build.py reads ptxas' report: a decode megakernel with a per-thread stack frame must fail the build."""
+    import build
+    ok = ("ptxas info    : Function properties for _ZN3qmk23qwen3_decode_megakernelEN4qmkp6ParamsE\n"
+          "    8 bytes stack frame, 4 bytes spill stores, 4 bytes spill loads\n"
+          "ptxas info    : Function properties for _ZN3qmk17rope_table_kernelEPfi\n"
+          "    400 bytes stack frame, 0 bytes spill stores, 0 bytes spill loads\n")
+    build.check_stack_frames(ok)          # small frame; other kernels are not held to the limit
+    bad = ok.replace("    8 bytes stack frame", "    408 bytes stack frame")
+    with pytest.raises(RuntimeError, match="stack frame"):
+        build.check_stack_frames(bad)
