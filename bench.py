@@ -520,6 +520,39 @@ def run_continuous(args):
     finish_engine_arm(world)
 
 
+def run_prefill_only(args):
+    """Chunked tensor-core prefill alone (the step before the decode path): N prompt tokens through
+    ``Decoder(prefill_mode="tensor").prefill_ids``, timed with CUDA events; prompt tok/s and dense fp16 TFLOP/s
+    (2 x 440 M matrix weights per token, the LM head is not part of a prefill, + causal attention)."""
+    rank, world, device = init_engine_arm()
+    from Model.Qwen06B_architecture import Decoder
+    n = args.prefill_only
+    weights = S.weights_to(S.make_weights(seed=0, max_seq_len=16), str(device))
+    eng = Decoder(weights=weights, tokenizer=S.StubTokenizer(-1), verbose=False, max_seq_len=n + 8, device=str(device),
+                  prefill_mode="tensor")
+    prompt = S.make_prompt(n, seed=rank)
+    for _ in range(max(args.warmup, 1)):
+        eng.reset()
+        eng.prefill_ids(prompt)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier(world)
+    for a, b in ev:
+        eng.reset()
+        a.record()
+        eng.prefill_ids(prompt)
+        b.record()
+    barrier(world)
+    ms = statistics.mean(a.elapsed_time(b) for a, b in ev)
+    ms = max_over_ranks(ms, world, device)
+    per_layer_w = sum(S.math.prod(shape) for _, shape in S.LAYER_FIELDS if len(shape) == 2)
+    flops = n * 2.0 * S.NUM_LAYERS * per_layer_w + S.NUM_LAYERS * 4.0 * 16 * 128 * n * (n + 1) / 2
+    if rank == 0:
+        print(json.dumps({"metric": "chunked tensor-core prefill, prompt tok/s", "value": world * n / (ms / 1e3), "unit": UNIT,
+                          "n_gpus": world, "prompt_tokens": n, "ms_per_prefill": ms, "tflops": flops / (ms / 1e3) / 1e12,
+                          "steps": args.steps, "warmup": args.warmup, "dtype": "fp16", "data": "synthetic"}))
+    finish_engine_arm(world)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -541,12 +574,16 @@ def main():
                     help="--continuous only: 1 = prefill the next request while the live ones decode (tensor-core engines)")
     ap.add_argument("--prefill", choices=["serial", "tensor"], default="tensor",
                     help="--continuous only: token-serial prefill op or the tensor-core chunked prefill")
+    ap.add_argument("--prefill-only", type=int, default=0, metavar="N",
+                    help="instead of the headline workload: time the chunked tensor-core prefill of N prompt tokens")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prefilled context (default: benchmark config)")
     ap.add_argument("--decode-tokens", type=int, default=DECODE_TOKENS,
                     help="greedy tokens per step (default: benchmark config; smaller for ncu captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.prefill_only > 0:
+        run_prefill_only(args)
     elif args.continuous > 0:
         run_continuous(args)
     else:

@@ -222,6 +222,10 @@ int qmk_generate_batch(
  * refused with QMK_ERR_BAD_ARGUMENT and a message), num_layers <= 48.
  * The first call on a device looks up the array's device address and sets the
  * kernel's shared-memory attribute: make that call before any stream capture.
+ * Every call blocks until the stream is idle (it reads the kernel's status word
+ * back into host memory).  The array is part of the library's CUDA module, which
+ * the runtime loads on first use: a process that is about to hand all free HBM
+ * to its own pool should touch the library first (qmk_num_ctas() is enough).
  * All calls on a device share the array, which keeps the previous call's
  * contents (status and rotary table are rewritten per call, exchange words
  * are distinguished by tags): calls that overlap on the GPU race.  Blocks

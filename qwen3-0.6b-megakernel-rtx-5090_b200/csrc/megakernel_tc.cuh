@@ -402,29 +402,37 @@ __device__ __noinline__ uint32_t attention_tc(const Params &P, Ctx c, const __ha
   QMK_FINE(64);
   cons_sync();
   QMK_FINE(65);
-  // (4) merge the warps (+ the new row) per (head, dim)
+  // (4) merge the warps (+ the new row).  First the 2 x 13 weights exp2(max_w - max) and the head's (max, sum), by
+  // warps 0 and 1 (one head each, lane = contributing warp, lane 12 = the new row); then every (head, dim) is a
+  // weighted sum of 13 independent loads (a running max + rescale per thread took 1180 cycles here).
+  float *s_scale = c.f(FF_SPLITW);                       // [2][16], free between the merges
+  if (c.warp < 2) {
+    const int h = c.warp;
+    float mw = -INFINITY, lw = 0.f;
+    if (c.lane < CONS_WARPS) {
+      mw = s_wpart[(c.lane * 2 + h) * PART_STRIDE + D];
+      lw = s_wpart[(c.lane * 2 + h) * PART_STRIDE + D + 1];
+    } else if (c.lane == CONS_WARPS && owner) {
+      mw = s_misc[h];
+      lw = 1.f;
+    }
+    const float M = warp_max(mw);
+    const float scw = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+    const float L = warp_sum(lw * scw);
+    if (c.lane < 16) s_scale[h * 16 + c.lane] = scw;
+    if (c.lane == 0) {
+      unsigned long long *part = P.ll + LL_PART + static_cast<size_t>((2 * g + h) * MAX_SPLITS + s) * PART_STRIDE;
+      ll_store(part + D, M, tag);
+      ll_store(part + D + 1, L, tag);
+    }
+  }
+  cons_sync();
   if (c.tid < 2 * D) {
     const int h = c.tid >> 7, d = c.tid & (D - 1);
-    float M = owner ? s_misc[h] : -INFINITY;
-    for (int w = 0; w < CONS_WARPS; ++w) M = fmaxf(M, s_wpart[(w * 2 + h) * PART_STRIDE + D]);
-    float L = 0.f, A = 0.f;
-    if (M != -INFINITY) {
-      for (int w = 0; w < CONS_WARPS; ++w) {
-        const float *wp = s_wpart + (w * 2 + h) * PART_STRIDE;
-        const float mw = wp[D];
-        const float scw = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-        L = fmaf(wp[D + 1], scw, L);
-        A = fmaf(wp[d], scw, A);
-      }
-      if (owner) {
-        const float scn = exp2f(s_misc[h] - M);
-        L += scn;
-        A = fmaf(s_vnew[d], scn, A);
-      }
-    }
-    unsigned long long *part = P.ll + LL_PART + static_cast<size_t>((2 * g + h) * MAX_SPLITS + s) * PART_STRIDE;
-    ll_store(part + d, A, tag);
-    if (d == 0) { ll_store(part + D, M, tag); ll_store(part + D + 1, L, tag); }
+    float A = s_vnew[d] * s_scale[h * 16 + CONS_WARPS];   // 0 weight unless this CTA owns the new row
+#pragma unroll
+    for (int w = 0; w < CONS_WARPS; ++w) A = fmaf(s_wpart[(w * 2 + h) * PART_STRIDE + d], s_scale[h * 16 + w], A);
+    ll_store(P.ll + LL_PART + static_cast<size_t>((2 * g + h) * MAX_SPLITS + s) * PART_STRIDE + d, A, tag);
   }
   QMK_FINE(66);
   // New K,V row -> cache (megakernel_5090.cu:392-397), off the critical path.  The fence orders the row before the
@@ -574,32 +582,62 @@ __device__ __noinline__ uint32_t slice_cols(const Params &P, Ctx c, int which) {
   ok = __all_sync(0xffffffffu, ok);
   float *colpart = c.f(FF_COLPART);
   if (ok) {
-    // B: activations, k-steps 0,1 in bq[0..3] (and 2,3 in bq2); row n of B^T = hi (even n) / lo (odd n) vector
+    // B: the slice's activations; row n of B^T = hi (even n) / lo (odd n) vector; one ldmatrix.x4 = two k-steps
     const uint32_t act_addr = smem_u32(c.smem + OFF_ACT16) + (c.lane & 1) * (ACT16_PITCH * 2) + (c.lane >> 3) * 16;
-    uint32_t bq[4], bq2[4] = {0u, 0u, 0u, 0u};
-    ldsm_x4(act_addr, bq);
-    if (ksteps > 2) ldsm_x4(act_addr + 64, bq2);
-    // A: this lane's row of each k-step (rows past the slice repeat row 0: their activations are zero)
-    uint32_t arow[4];
-#pragma unroll
-    for (int ks = 0; ks < 4; ++ks) {
+    // A: this lane's row of a k-step (rows past the slice repeat row 0: their activations are zero)
+    auto a_row = [&](int ks) -> uint32_t {
       int row = ks * 16 + (c.lane & 7) + 8 * (c.lane >> 4);
       if (row >= nrows) row = 0;
-      arow[ks] = weight_rows(c, c.chunk + static_cast<uint32_t>(row >> 2)) + (row & 3) * ROW_PITCH + ((c.lane >> 3) & 1) * 16;
-    }
-    // (storing a tile's sums one iteration later, behind the next tile's loads and MMAs, measured slower: 1.65 -> 2.1 us)
+      return weight_rows(c, c.chunk + static_cast<uint32_t>(row >> 2)) + (row & 3) * ROW_PITCH + ((c.lane >> 3) & 1) * 16;
+    };
+    if (ksteps <= 2) {
+      uint32_t bq[4];
+      ldsm_x4(act_addr, bq);
+      const uint32_t arow0 = a_row(0), arow1 = a_row(1);
+      // two tiles at a time (w, w + 12; then w + 24, w + 36; ...): their loads first, then their MMAs, then their
+      // stores, so that the dependent chains overlap (one tile after the other: ~150 cycles per tile; three at a
+      // time need registers that the kernel then spills around the call)
 #pragma unroll 1
-    for (int tile = c.warp; tile < H / 16; tile += CONS_WARPS) {
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t a[4];
-      ldsm_x4_trans(arow[0] + tile * 32, a);
-      mma_16816(acc, a, bq[0], bq[1]);
-      if (ksteps > 1) { ldsm_x4_trans(arow[1] + tile * 32, a); mma_16816(acc, a, bq[2], bq[3]); }
-      if (ksteps > 2) { ldsm_x4_trans(arow[2] + tile * 32, a); mma_16816(acc, a, bq2[0], bq2[1]); }
-      if (ksteps > 3) { ldsm_x4_trans(arow[3] + tile * 32, a); mma_16816(acc, a, bq2[2], bq2[3]); }
-      if ((c.lane & 3) == 0) {
-        colpart[tile * 16 + (c.lane >> 2)] = fmaf(acc[1], LO_INV, acc[0]);
-        colpart[tile * 16 + (c.lane >> 2) + 8] = fmaf(acc[3], LO_INV, acc[2]);
+      for (int t0 = c.warp; t0 < H / 16; t0 += 2 * CONS_WARPS) {
+        float acc[2][4];
+        uint32_t a[2][4], a2[2][4];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int tile = min(t0 + u * CONS_WARPS, H / 16 - 1);   // past the end: repeat a valid tile, not stored
+          acc[u][0] = 0.f; acc[u][1] = 0.f; acc[u][2] = 0.f; acc[u][3] = 0.f;
+          ldsm_x4_trans(arow0 + tile * 32, a[u]);
+          if (ksteps > 1) ldsm_x4_trans(arow1 + tile * 32, a2[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          mma_16816(acc[u], a[u], bq[0], bq[1]);
+          if (ksteps > 1) mma_16816(acc[u], a2[u], bq[2], bq[3]);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int tile = t0 + u * CONS_WARPS;
+          if (tile < H / 16 && (c.lane & 3) == 0) {
+            colpart[tile * 16 + (c.lane >> 2)] = fmaf(acc[u][1], LO_INV, acc[u][0]);
+            colpart[tile * 16 + (c.lane >> 2) + 8] = fmaf(acc[u][3], LO_INV, acc[u][2]);
+          }
+        }
+      }
+    } else {   // slices of 33..64 rows (grids near the smallest this kernel takes): tile by tile
+#pragma unroll 1
+      for (int tile = c.warp; tile < H / 16; tile += CONS_WARPS) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+        for (int ks = 0; ks < ksteps; ks += 2) {
+          uint32_t bq[4], a[4];
+          ldsm_x4(act_addr + ks * 32, bq);
+          ldsm_x4_trans(a_row(ks) + tile * 32, a);
+          mma_16816(acc, a, bq[0], bq[1]);
+          if (ks + 1 < ksteps) { ldsm_x4_trans(a_row(ks + 1) + tile * 32, a); mma_16816(acc, a, bq[2], bq[3]); }
+        }
+        if ((c.lane & 3) == 0) {
+          colpart[tile * 16 + (c.lane >> 2)] = fmaf(acc[1], LO_INV, acc[0]);
+          colpart[tile * 16 + (c.lane >> 2) + 8] = fmaf(acc[3], LO_INV, acc[2]);
+        }
       }
     }
   }
