@@ -314,6 +314,20 @@ __device__ __forceinline__ float ll_wait(const Params &P, const Ctx &c, const un
   return __uint_as_float(static_cast<uint32_t>(w));
 }
 
+// One lane of the warp watches ONE word until it carries `tag`; the warp then goes on to its full wait.  Polls of
+// every lane on every word slow the very stores (and adds) they wait for; while most of the wait is spent here,
+// the lines see 1/32 of the polls.  Bounded: gives up silently, the full wait that follows reports time-outs.
+__device__ __forceinline__ void ll_sentinel(const Params &P, const Ctx &c, const unsigned long long *p, uint32_t tag) {
+  if (c.lane == 0) {
+    uint32_t n = 0;
+    while (static_cast<uint32_t>(ll_load(p) >> 32) != tag) {
+      if ((++n & 1023u) == 0u && (c.flags()[0] || ld_relaxed_u32(P.status) != 0u)) break;
+      if (n > (1u << 22)) break;
+    }
+  }
+  __syncwarp();
+}
+
 // Waits for NW exchange words at once: every pass re-loads ALL words still missing before looking at
 // any of them, so the whole set completes one L2 round trip after its last word lands (polling them
 // one after the other costs a round trip per word that was stale in the first pass).

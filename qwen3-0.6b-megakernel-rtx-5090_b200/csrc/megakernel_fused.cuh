@@ -231,6 +231,11 @@ __device__ __noinline__ void merge_slice(const Params &P, const Ctx c, int S, ui
   }
   float a[NE];
   QMK_FINE(50);
+#ifdef QMK_TC_BUILD
+  // the owner split (the last one) also handles the new row: its words arrive last
+  ll_sentinel(P, c, c.llr + LL_PART + static_cast<size_t>((min(e0 + c.warp, e1 - 1) >> 7) * MAX_SPLITS + S - 1) * PART_STRIDE +
+                        (min(e0 + c.warp, e1 - 1) & (D - 1)), tag);
+#endif
   const int hw = h0 + (c.warp - (CONS_WARPS - 2));                // head whose split weights this warp makes (last two warps)
   if (c.warp >= CONS_WARPS - 2 && hw <= ((e1 - 1) >> 7)) {        // warp-uniform
     // outputs and the head's (max, sum) pairs in ONE round of polls (one after the other costs a second L2 round trip)

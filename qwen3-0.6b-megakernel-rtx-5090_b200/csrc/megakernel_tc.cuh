@@ -24,6 +24,9 @@
 namespace QMK_NS {
 #if QMK_MAX_SEQ == 1 && defined(QMK_TC_BUILD)
 
+constexpr int TC_MIN_CTAS = 96;                // smallest grid: <= 2 attention outputs per warp to merge, O / down slices of <= 32 rows
+static_assert((QS + TC_MIN_CTAS - 1) / TC_MIN_CTAS <= 2 * CONS_WARPS && TC_MIN_CTAS >= FUSED_MIN_CTAS, "merge_slice2 takes two elements per warp");
+static_assert(4 * ((I / 4 + TC_MIN_CTAS - 1) / TC_MIN_CTAS) <= 32, "slice_cols takes two k-steps");
 constexpr int ROW_PITCH = 2 * H + 16;          // bytes between the rows of a chunk in shared memory
 constexpr int CH_ROWS = 4;
 constexpr int ODD_SLOT_SKEW = 64;              // weight rows of chunks in odd slots start four 16-byte bank groups later
@@ -255,6 +258,7 @@ __device__ __noinline__ uint32_t attention_tc(const Params &P, Ctx c, const __ha
     float v[4];
     {
       const unsigned long long *wp[4] = {src + lane, src + lane + 32, src + lane + 64, src + lane + 96};
+      // (a sentinel poll first, as in the residual-sum wait, costs its extra round trip here: 4.05 -> 4.34 us)
       ll_wait_many<4>(P, c, wp, 0xfu, tag, v);
     }
     if (w < 3) {
@@ -489,6 +493,19 @@ __device__ __noinline__ void red_wait_norm(const Params &P, const Ctx c, int whi
   for (int r = 0; r < R; ++r) {
     const unsigned long long base = static_cast<unsigned long long>(use) * red_contributors(c.ncta, R, r);
     const unsigned long long *src = buf + r * H + c.tid;
+    {
+      // one lane per warp watches one word until it is complete, then the warp fetches its words: 32x fewer polls
+      // hitting the lines the adds are draining into, at the price of one more L2 round trip at the end (measured at
+      // 4096-token context: 1714 -> 1784 tok/s; one lane per CTA + a barrier: the same; a pause between polls: slower)
+      if (c.lane == 0) {
+        uint32_t n = 0;
+        while (((ll_load(src) - base) & RED_CNT_MASK) != 0ull) {
+          if ((++n & 1023u) == 0u && (c.flags()[0] || ld_relaxed_u32(P.status) != 0u)) break;   // the full wait below reports time-outs
+          if (n > (1u << 22)) break;
+        }
+      }
+      __syncwarp();
+    }
     unsigned long long w[PT];
 #pragma unroll
     for (int j = 0; j < PT; ++j)
@@ -560,18 +577,103 @@ __device__ __noinline__ void embed_norm(const Params &P, const Ctx c, int token,
   cons_sync();
 }
 
+// merge_slice (megakernel_fused.cuh) for slices of at most two elements per warp (grids from TC_MIN_CTAS on), without
+// its barrier: every warp fetches the outputs AND the (max, sum) pairs of its elements' heads in one round of polls
+// and makes the split weights itself (15 shuffles per element, the two elements' chains side by side), instead of
+// waiting for the two warps that make them for everybody.
+__device__ __noinline__ void merge_slice2(const Params &P, const Ctx c, int S, uint32_t tag) {
+  float *s_attn = c.f(FF_ATTN);
+  __half *act16 = reinterpret_cast<__half *>(c.smem + OFF_ACT16);
+  const int e0 = c.segs()->e0, e1 = c.segs()->e1;
+  const int s = min(c.lane, S - 1);
+  // words of element q: its unnormalised output, and the (max, sum) pair of its head: part_q + {d_q, 128, 129}
+  const int ea = min(e0 + c.warp, e1 - 1), eb = min(e0 + c.warp + CONS_WARPS, e1 - 1);
+  const unsigned long long *pa = c.llr + LL_PART + static_cast<size_t>((ea >> 7) * MAX_SPLITS + s) * PART_STRIDE;
+  const unsigned long long *pb = c.llr + LL_PART + static_cast<size_t>((eb >> 7) * MAX_SPLITS + s) * PART_STRIDE;
+  const int da = ea & (D - 1), db = eb & (D - 1);
+  uint32_t valid = 0;
+  if (c.lane < S && e0 + c.warp < e1) valid |= 7u;
+  if (c.lane < S && e0 + c.warp + CONS_WARPS < e1) valid |= 56u;
+  unsigned long long w[6];
+  QMK_FINE(50);
+  {
+    uint32_t pending = valid, it = 0;
+    unsigned long long t0 = 0;
+    for (;;) {
+      if (pending & 1u) w[0] = ll_load(pa + da);
+      if (pending & 2u) w[1] = ll_load(pa + D);
+      if (pending & 4u) w[2] = ll_load(pa + D + 1);
+      if (pending & 8u) w[3] = ll_load(pb + db);
+      if (pending & 16u) w[4] = ll_load(pb + D);
+      if (pending & 32u) w[5] = ll_load(pb + D + 1);
+#pragma unroll
+      for (int j = 0; j < 6; ++j)
+        if ((pending & (1u << j)) && static_cast<uint32_t>(w[j] >> 32) == tag) pending &= ~(1u << j);
+      if (pending == 0u) break;
+      if (P.spin_sleep_ns) __nanosleep(P.spin_sleep_ns);
+      if ((++it & 255u) == 0u) {
+        if (c.flags()[0]) break;
+        if (ld_relaxed_u32(P.status) != 0u) { c.flags()[0] = 1; break; }
+        const unsigned long long t = now_ns();
+        if (t0 == 0) t0 = t;
+        if (t - t0 > P.timeout_ns) { raise_error(P, c, QMK_ERR_WAIT_TIMEOUT, WHERE_LL); break; }
+      }
+    }
+  }
+  float v[6];
+#pragma unroll
+  for (int j = 0; j < 6; ++j) v[j] = __uint_as_float(static_cast<uint32_t>(w[j]));
+  QMK_FINE(51);
+  float m[2], M[2], L[2], A[2];
+#pragma unroll
+  for (int q = 0; q < 2; ++q) { m[q] = (valid >> (3 * q)) & 1u ? v[3 * q + 1] : -INFINITY; M[q] = m[q]; }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+    for (int q = 0; q < 2; ++q) M[q] = fmaxf(M[q], __shfl_xor_sync(0xffffffffu, M[q], o));
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    const float sc = (m[q] == -INFINITY) ? 0.f : exp2f(m[q] - M[q]);
+    const bool on = (valid >> (3 * q)) & 1u;
+    L[q] = on ? v[3 * q + 2] * sc : 0.f;
+    A[q] = on ? v[3 * q] * sc : 0.f;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      L[q] += __shfl_xor_sync(0xffffffffu, L[q], o);
+      A[q] += __shfl_xor_sync(0xffffffffu, A[q], o);
+    }
+  QMK_FINE(52);
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    const int e = e0 + c.warp + q * CONS_WARPS;
+    if (e < e1 && c.lane == 0) {
+      const float out = A[q] / L[q];
+      s_attn[e - e0] = out;
+      act16[e - e0] = split_half(out, false);
+      act16[ACT16_PITCH + e - e0] = split_half(out, true);
+    }
+  }
+  if (c.tid < 32 && c.tid >= e1 - e0) { act16[c.tid] = __float2half_rn(0.f); act16[ACT16_PITCH + c.tid] = __float2half_rn(0.f); }
+}
+
 // Split-K slice of the O (which = 0) or down (1) projection (see slice_colgemv of megakernel_fused.cuh) on the
 // tensor cores: partial[n] = sum_i act[i] * Wt[first + i][n] with the K-major rows as the A operand read through
-// ldmatrix.trans (tile = 16 outputs x 16 rows), the slice's activations as B (hi / lo columns, from act16).  Warp w
-// takes output tiles w, w + 12, ... over ALL rows of the slice, so a partial is complete when it leaves the warp.
+// ldmatrix.trans (tile = 16 outputs x 16 rows, at most two k-steps: slices of at most 32 rows), the slice's
+// activations as B (hi / lo columns, from act16).  Warp w takes output tiles w, w + 12, ... over ALL rows of the
+// slice, so a partial is complete when it leaves the warp: after each pair of tiles the 32 sums are spread over
+// the 32 lanes (four shuffles) and every lane adds its one output into the residual sum - no staging in shared
+// memory, no barrier, and the adds of early tiles drain while later tiles are computed.
 __device__ __noinline__ uint32_t slice_cols(const Params &P, Ctx c, int which) {
   const SegTab *t = c.segs();
   const int nrows = which ? tctab(c)->ng * CH_ROWS : t->e1 - t->e0;
   const float *resid = c.f(which ? F_X1 : F_X);
-  unsigned long long *buf = P.red + (which ? RED_X2 : RED_X1);
   float *prev = c.f(FF_PREV) + (which ? H : 0);
+  unsigned long long *mine = P.red + (which ? RED_X2 : RED_X1) + (c.cta % P.red_copies) * H;
   const int nch = (nrows + CH_ROWS - 1) / CH_ROWS;
-  const int ksteps = (nrows + 15) >> 4;               // <= 4 (slices of at most 64 rows)
+  const bool two = nrows > 16;
   const int fb = which ? 30 : 20;
   QMK_FINE(fb + 0);
   bool ok = true;
@@ -580,85 +682,55 @@ __device__ __noinline__ uint32_t slice_cols(const Params &P, Ctx c, int which) {
     ok = mbar_wait(P, c, c.full(idx % NSLOTS), (idx / NSLOTS) & 1u, WHERE_FULL, false);
   }
   ok = __all_sync(0xffffffffu, ok);
-  float *colpart = c.f(FF_COLPART);
   if (ok) {
     // B: the slice's activations; row n of B^T = hi (even n) / lo (odd n) vector; one ldmatrix.x4 = two k-steps
-    const uint32_t act_addr = smem_u32(c.smem + OFF_ACT16) + (c.lane & 1) * (ACT16_PITCH * 2) + (c.lane >> 3) * 16;
-    // A: this lane's row of a k-step (rows past the slice repeat row 0: their activations are zero)
-    auto a_row = [&](int ks) -> uint32_t {
+    uint32_t bq[4];
+    ldsm_x4(smem_u32(c.smem + OFF_ACT16) + (c.lane & 1) * (ACT16_PITCH * 2) + (c.lane >> 3) * 16, bq);
+    // A: this lane's row of each k-step (rows past the slice repeat row 0: their activations are zero)
+    uint32_t arow[2];
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
       int row = ks * 16 + (c.lane & 7) + 8 * (c.lane >> 4);
       if (row >= nrows) row = 0;
-      return weight_rows(c, c.chunk + static_cast<uint32_t>(row >> 2)) + (row & 3) * ROW_PITCH + ((c.lane >> 3) & 1) * 16;
-    };
-    if (ksteps <= 2) {
-      uint32_t bq[4];
-      ldsm_x4(act_addr, bq);
-      const uint32_t arow0 = a_row(0), arow1 = a_row(1);
-      // two tiles at a time (w, w + 12; then w + 24, w + 36; ...): their loads first, then their MMAs, then their
-      // stores, so that the dependent chains overlap (one tile after the other: ~150 cycles per tile; three at a
-      // time need registers that the kernel then spills around the call)
+      arow[ks] = weight_rows(c, c.chunk + static_cast<uint32_t>(row >> 2)) + (row & 3) * ROW_PITCH + ((c.lane >> 3) & 1) * 16;
+    }
+    const int n0 = t->n0, n1 = t->n1;
+    const int src = (c.lane & 7) * 4;                 // lane that holds this lane's output row (fragment row = lane / 4)
 #pragma unroll 1
-      for (int t0 = c.warp; t0 < H / 16; t0 += 2 * CONS_WARPS) {
-        float acc[2][4];
-        uint32_t a[2][4], a2[2][4];
+    for (int t0 = c.warp; t0 < H / 16; t0 += 2 * CONS_WARPS) {
+      float acc[2][4];
+      uint32_t a[2][4], a2[2][4];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int tile = min(t0 + u * CONS_WARPS, H / 16 - 1);   // past the end: repeat a valid tile, not stored
-          acc[u][0] = 0.f; acc[u][1] = 0.f; acc[u][2] = 0.f; acc[u][3] = 0.f;
-          ldsm_x4_trans(arow0 + tile * 32, a[u]);
-          if (ksteps > 1) ldsm_x4_trans(arow1 + tile * 32, a2[u]);
-        }
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          mma_16816(acc[u], a[u], bq[0], bq[1]);
-          if (ksteps > 1) mma_16816(acc[u], a2[u], bq[2], bq[3]);
-        }
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int tile = t0 + u * CONS_WARPS;
-          if (tile < H / 16 && (c.lane & 3) == 0) {
-            colpart[tile * 16 + (c.lane >> 2)] = fmaf(acc[u][1], LO_INV, acc[u][0]);
-            colpart[tile * 16 + (c.lane >> 2) + 8] = fmaf(acc[u][3], LO_INV, acc[u][2]);
-          }
-        }
+      for (int u = 0; u < 2; ++u) {
+        const int tile = min(t0 + u * CONS_WARPS, H / 16 - 1);   // past the end: repeat a valid tile, not added
+        acc[u][0] = 0.f; acc[u][1] = 0.f; acc[u][2] = 0.f; acc[u][3] = 0.f;
+        ldsm_x4_trans(arow[0] + tile * 32, a[u]);
+        if (two) ldsm_x4_trans(arow[1] + tile * 32, a2[u]);
       }
-    } else {   // slices of 33..64 rows (grids near the smallest this kernel takes): tile by tile
-#pragma unroll 1
-      for (int tile = c.warp; tile < H / 16; tile += CONS_WARPS) {
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 1
-        for (int ks = 0; ks < ksteps; ks += 2) {
-          uint32_t bq[4], a[4];
-          ldsm_x4(act_addr + ks * 32, bq);
-          ldsm_x4_trans(a_row(ks) + tile * 32, a);
-          mma_16816(acc, a, bq[0], bq[1]);
-          if (ks + 1 < ksteps) { ldsm_x4_trans(a_row(ks + 1) + tile * 32, a); mma_16816(acc, a, bq[2], bq[3]); }
-        }
-        if ((c.lane & 3) == 0) {
-          colpart[tile * 16 + (c.lane >> 2)] = fmaf(acc[1], LO_INV, acc[0]);
-          colpart[tile * 16 + (c.lane >> 2) + 8] = fmaf(acc[3], LO_INV, acc[2]);
-        }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        mma_16816(acc[u], a[u], bq[0], bq[1]);
+        if (two) mma_16816(acc[u], a2[u], bq[2], bq[3]);
+      }
+      // lanes of quad 0 hold (hi, lo) sums of rows lane / 4 and lane / 4 + 8 of both tiles; lane L takes output
+      // L % 16 of tile L / 16
+      const float s0 = __shfl_sync(0xffffffffu, fmaf(acc[0][1], LO_INV, acc[0][0]), src);
+      const float s1 = __shfl_sync(0xffffffffu, fmaf(acc[0][3], LO_INV, acc[0][2]), src);
+      const float s2 = __shfl_sync(0xffffffffu, fmaf(acc[1][1], LO_INV, acc[1][0]), src);
+      const float s3 = __shfl_sync(0xffffffffu, fmaf(acc[1][3], LO_INV, acc[1][2]), src);
+      const int tile = t0 + (c.lane >> 4) * CONS_WARPS;
+      if (tile < H / 16) {
+        const int n = tile * 16 + (c.lane & 15);
+        float v = (c.lane & 16) ? ((c.lane & 8) ? s3 : s2) : ((c.lane & 8) ? s1 : s0);
+        if (n >= n0 && n < n1) v += resid[n];
+        const long long fx = __float2ll_rn(v * RED_SCALE), fx_prev = __float2ll_rn(prev[n] * RED_SCALE);
+        prev[n] = v;
+        red_add_u64(mine + n, (static_cast<unsigned long long>(fx - fx_prev) << RED_CNT_BITS) + 1ull);
       }
     }
   }
   __syncwarp();
   if (c.lane < nch) mbar_arrive_n(c.empty((c.chunk + static_cast<uint32_t>(c.lane)) % NSLOTS), EMPTY_UNITS / CONS_WARPS);
-  QMK_FINE(fb + 1);
-  cons_sync();
-  QMK_FINE(fb + 2);
-  const int n0 = t->n0, n1 = t->n1;
-  unsigned long long *mine = buf + (c.cta % P.red_copies) * H;
-#pragma unroll
-  for (int j = 0; j < (H + CONS_THREADS - 1) / CONS_THREADS; ++j) {
-    const int n = c.tid + j * CONS_THREADS;
-    if (n < H) {
-      float v = colpart[n];
-      if (n >= n0 && n < n1) v += resid[n];
-      const long long fx = __float2ll_rn(v * RED_SCALE), fx_prev = __float2ll_rn(prev[n] * RED_SCALE);
-      prev[n] = v;
-      red_add_u64(mine + n, (static_cast<unsigned long long>(fx - fx_prev) << RED_CNT_BITS) + 1ull);
-    }
-  }
   QMK_FINE(fb + 3);
   return c.chunk + static_cast<uint32_t>(nch);
 }
@@ -903,7 +975,11 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel_tc(const _
         QMK_STAMP(layer * 12 + 1);
         c.chunk = attention_tc(P, c, nv, layer, pos, tag);
         QMK_STAMP(layer * 12 + 2);
+#ifdef QMK_MERGE2
+        merge_slice2(P, c, S_step, tag);
+#else
         merge_slice(P, c, S_step, tag, reinterpret_cast<__half *>(c.smem + OFF_ACT16));
+#endif
         QMK_STAMP(layer * 12 + 3);
         cons_sync();
         c.chunk = slice_cols(P, c, 0);

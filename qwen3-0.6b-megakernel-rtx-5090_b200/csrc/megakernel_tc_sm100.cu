@@ -26,5 +26,5 @@ namespace qmk_fused_tc {
 const void *kernel() { return reinterpret_cast<const void *>(qmkt::qwen3_decode_megakernel_tc); }
 size_t smem_bytes() { return qmkt::TC_SMEM_BYTES; }
 int threads() { return qmkt::THREADS; }
-int min_ctas() { return qmkt::FUSED_MIN_CTAS; }
+int min_ctas() { return qmkt::TC_MIN_CTAS; }
 }  // namespace qmk_fused_tc
