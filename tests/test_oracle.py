@@ -102,6 +102,47 @@ def test_against_transformers_qwen3(tiny_cfg):
     assert (hf[-1] - d.last_logits).abs().max() < 2e-5
 
 
+def test_against_transformers_qwen3_full_depth():
+    """The same cross-check on the benchmarked shape: 28 layers, vocabulary 151936, seed-0 weights, the first 12
+    tokens of the 32-token golden prompt.  Also ties the golden file to the independent implementation: at the
+    12th position both predict from the same logits."""
+    tr = pytest.importorskip("transformers")
+    w = S.make_weights(seed=0, max_seq_len=16)
+    ids = S.make_prompt(32, seed=0)[:12]
+    d = Decoder(w, max_seq_len=16, kv_dtype=torch.float32)
+    cfg = tr.Qwen3Config(hidden_size=1024, num_hidden_layers=S.NUM_LAYERS, num_attention_heads=16, num_key_value_heads=8,
+                         head_dim=128, intermediate_size=3072, vocab_size=S.VOCAB_SIZE, rms_norm_eps=1e-6,
+                         tie_word_embeddings=True, rope_parameters={"rope_theta": 1e6, "rope_type": "default"},
+                         max_position_embeddings=64)
+    m = tr.Qwen3ForCausalLM(cfg).float().eval()
+    names = ["input_layernorm", "self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.q_norm",
+             "self_attn.k_norm", "self_attn.o_proj", "post_attention_layernorm", "mlp.gate_proj", "mlp.up_proj",
+             "mlp.down_proj"]
+    sd = {f"model.layers.{li}.{n}.weight": w["layer_weights"][li * 11 + j].float()
+          for li in range(S.NUM_LAYERS) for j, n in enumerate(names)}
+    sd["model.embed_tokens.weight"] = w["embed_weight"].float()
+    sd["model.norm.weight"] = w["final_norm_weight"].float()
+    sd["lm_head.weight"] = w["embed_weight"].float()
+    missing = m.load_state_dict(sd, strict=False)
+    assert not missing.missing_keys and not missing.unexpected_keys
+    with torch.no_grad():
+        hf = m(torch.tensor([ids])).logits[0]
+    d.prefill(ids[:-1])
+    tok = d.step(ids[-1])
+    err = float((hf[-1] - d.last_logits).abs().max())
+    print(f"28 layers: max |oracle - transformers| = {err:.3e}")
+    assert err < 5e-5
+    assert tok == int(torch.argmax(hf[-1]))
+
+
+def test_benchmark_golden_file_is_consistent():
+    g = json.load(open(os.path.join(GOLDEN, "full_seed0_prompt4096.json")))
+    ids = S.make_prompt(g["config"]["prompt_len"], seed=g["config"]["prompt_seed"])
+    assert ids[:8] == g["prompt_head"] and ids[-8:] == g["prompt_tail"] and len(ids) == g["prompt_len"] == 4096
+    assert len(g["tokens"]) == 8 and [r[0] for r in g["top8_indices"]] == g["tokens"]
+    assert g["min_margin"] == min(g["margins"]) > 0.1
+
+
 def test_full_golden_file_is_consistent():
     """Cheap checks of the full-size golden file (the full-size oracle run itself is exercised by the
     GPU parity test and by make_golden.py)."""
