@@ -116,6 +116,57 @@ int qmk_configure(int vocab_size, int rope_from_table, int split_len, int max_ct
  * (HOST pointer).  Default: theta = 1e6. */
 int qmk_set_inv_freq(const float *inv_freq64);
 
+/* ---- engine handles ---------------------------------------------------------
+ * The options above (qmk_configure, qmk_set_inv_freq, qmk_set_weight_format,
+ * qmk_set_fused) are state of the library per device: two clients of one GPU
+ * that differ in them would have to re-apply theirs before every op.  A handle
+ * keeps one client's options and applies them together with the op under one
+ * hold of the library's lock, so clients with different vocabularies, weight
+ * formats or RoPE settings can share a GPU, also from several threads.  The
+ * reference has no such object (its ops are free functions over one implicit
+ * GPU state, qwen_ops.cpp:262-270); qmk_engine_decode / _generate / _prefill
+ * take the handle first and then exactly the arguments of qmk_decode /
+ * qmk_generate / qmk_prefill.  A handle call makes the handle's device the
+ * calling thread's current device; the stream must belong to it. */
+typedef struct qmk_engine qmk_engine;
+typedef struct qmk_engine_config {
+  int device;              /* CUDA device ordinal */
+  int vocab_size;          /* LM-head rows; <= 0: 151936 */
+  int weight_format;       /* 0 fp16, 1 FP8-E4M3 rows (see qmk_set_weight_format) */
+  int rope_from_table;     /* see qmk_configure */
+  int split_len;           /* <= 0: qmk_configure's value */
+  int max_ctas;            /* <= 0: qmk_configure's value */
+  int timeout_ms;          /* <= 0: qmk_configure's value */
+  int fused;               /* 2, 1, 0 as qmk_set_fused; negative: whatever qmk_set_fused last chose */
+  const float *inv_freq64; /* HOST, 64 floats, copied by qmk_engine_create; NULL: theta = 1e6 */
+} qmk_engine_config;
+int qmk_engine_create(const qmk_engine_config *config, qmk_engine **out);
+/* Frees the handle and the K-major weight copies made for the layer tables it decoded with. */
+int qmk_engine_destroy(qmk_engine *engine);
+/* Makes the handle's options the device's current ones (for the entry points that take no handle). */
+int qmk_engine_apply(qmk_engine *engine);
+int qmk_engine_decode(
+    qmk_engine *engine, int input_token_id, int *output_token_id, const void *embed_weight,
+    const struct LDGLayerWeight *layer_weights, const void *final_norm_weight,
+    const void *lm_head_weight, const void *cos_table, const void *sin_table,
+    void *k_cache, void *v_cache, void *hidden_buffer, void *g_normalized,
+    void *block_max_vals, void *block_max_idxs, int num_layers, int position,
+    int max_seq_len, float attn_scale, cudaStream_t stream);
+int qmk_engine_generate(
+    qmk_engine *engine, int first_token_id, int num_steps, const void *embed_weight,
+    const struct LDGLayerWeight *layer_weights, const void *final_norm_weight,
+    const void *lm_head_weight, const void *cos_table, const void *sin_table,
+    void *k_cache, void *v_cache, void *hidden_buffer, void *g_normalized,
+    void *block_max_vals, void *block_max_idxs, int *output_log, int num_layers,
+    int start_position, int max_seq_len, float attn_scale, int eos_token_id,
+    int synchronize, cudaStream_t stream);
+int qmk_engine_prefill(
+    qmk_engine *engine, const int *token_ids_host, int num_tokens, const void *embed_weight,
+    const struct LDGLayerWeight *layer_weights, const void *final_norm_weight,
+    const void *cos_table, const void *sin_table, void *k_cache, void *v_cache,
+    int num_layers, int start_position, int max_seq_len, float attn_scale,
+    cudaStream_t stream);
+
 /* Debug: when non-null, decode steps also write every logit to
  * logits_out[step * vocab_size + row] (DEVICE fp32).  Null switches it off. */
 int qmk_set_logits_dump(float *logits_out);

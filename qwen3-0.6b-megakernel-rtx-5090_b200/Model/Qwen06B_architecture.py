@@ -204,10 +204,22 @@ class Decoder:
         self._output_log = torch.full((self.max_seq_len,), -1, dtype=torch.int32, device=dev)
         self._output_log_cpu = torch.empty(self.max_seq_len, dtype=torch.int32).pin_memory()
 
-        self._gen = _require_megakernel_op("generate_nosync")
-        self._prefill_op = _require_megakernel_op("prefill")
         self._rope_from_table = int(bool(rope_from_table))
         self._inv_freq = rope_inv_freq()
+        # An engine handle of the library carries this decoder's options and applies them with every op; the
+        # reference's pybind module (free functions only) has none, and the module-level ops are used instead.
+        self._engine = None
+        if qwen_megakernel_C is not None and hasattr(qwen_megakernel_C, "Engine"):
+            self._engine = qwen_megakernel_C.Engine(
+                device=dev, vocab_size=self.vocab_size, weight_format=weight_format,
+                rope_from_table=self._rope_from_table, inv_freq=self._inv_freq)
+            self._decode_op = self._engine.decode
+            self._gen = self._engine.generate_nosync
+            self._prefill_op = self._engine.prefill
+        else:
+            self._decode_op = _decode
+            self._gen = _require_megakernel_op("generate_nosync")
+            self._prefill_op = _require_megakernel_op("prefill")
         row_bytes = (HIDDEN_SIZE + 16) if weight_format == "fp8" else 2 * HIDDEN_SIZE
         if self._embed_weight.numel() * self._embed_weight.element_size() != self.vocab_size * row_bytes:
             raise RuntimeError(f"embedding tensor does not have {self.vocab_size} rows of {row_bytes} bytes: "
@@ -218,7 +230,9 @@ class Decoder:
         """The library keeps vocabulary size, weight format, RoPE mode and frequencies per DEVICE, not per decoder.
         Every op of this decoder re-applies its own values first (host-side and cheap: unchanged values are
         recognised), so decoders with different vocabularies or weight formats can live on one GPU."""
-        if qwen_megakernel_C is not None and hasattr(qwen_megakernel_C, "configure"):
+        if self._engine is not None:
+            self._engine.apply()
+        elif qwen_megakernel_C is not None and hasattr(qwen_megakernel_C, "configure"):
             qwen_megakernel_C.configure(vocab_size=self.vocab_size, rope_from_table=self._rope_from_table)
             qwen_megakernel_C.set_weight_format(self.weight_format)
             qwen_megakernel_C.set_inv_freq(self._inv_freq)
@@ -256,7 +270,7 @@ class Decoder:
     def step(self, input_token_id: int) -> int:
         """One decode step through the ``decode`` op (Model/Qwen06B_architecture.py:351-380)."""
         self.apply_options()
-        out = _decode(int(input_token_id), *self._common(), self.num_layers, self._position,
+        out = self._decode_op(int(input_token_id), *self._common(), self.num_layers, self._position,
                       self.max_seq_len, self._attn_scale)
         tok = int(out.item())
         self._position += 1

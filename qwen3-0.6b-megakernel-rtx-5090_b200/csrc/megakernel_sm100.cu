@@ -663,12 +663,14 @@ int qmk_set_profile_buffer(unsigned long long *timestamps) {
   return QMK_OK;
 }
 
-int qmk_decode(int input_token_id, int *output_token_id, const void *embed_weight, const LDGLayerWeight *layer_weights,
-               const void *final_norm_weight, const void *lm_head_weight, const void *cos_table, const void *sin_table,
-               void *k_cache, void *v_cache, void *hidden_buffer, void *g_normalized, void *block_max_vals,
-               void *block_max_idxs, int num_layers, int position, int max_seq_len, float attn_scale,
-               cudaStream_t stream) {
-  std::lock_guard<std::mutex> lock(g_mutex);
+}  // extern "C"
+
+namespace {
+int decode_unlocked(int input_token_id, int *output_token_id, const void *embed_weight, const LDGLayerWeight *layer_weights,
+                    const void *final_norm_weight, const void *lm_head_weight, const void *cos_table, const void *sin_table,
+                    void *k_cache, void *v_cache, void *hidden_buffer, void *g_normalized, void *block_max_vals,
+                    void *block_max_idxs, int num_layers, int position, int max_seq_len, float attn_scale,
+                    cudaStream_t stream) {
   Engine *e = current_engine_unlocked();
   if (!e) return QMK_ERR_CUDA;
   clear_error(e);
@@ -684,12 +686,11 @@ int qmk_decode(int input_token_id, int *output_token_id, const void *embed_weigh
   return launch(e, P, stream, false);
 }
 
-int qmk_generate(int first_token_id, int num_steps, const void *embed_weight, const LDGLayerWeight *layer_weights,
-                 const void *final_norm_weight, const void *lm_head_weight, const void *cos_table,
-                 const void *sin_table, void *k_cache, void *v_cache, void *hidden_buffer, void *g_normalized,
-                 void *block_max_vals, void *block_max_idxs, int *output_log, int num_layers, int start_position,
-                 int max_seq_len, float attn_scale, int eos_token_id, int synchronize, cudaStream_t stream) {
-  std::lock_guard<std::mutex> lock(g_mutex);
+int generate_unlocked(int first_token_id, int num_steps, const void *embed_weight, const LDGLayerWeight *layer_weights,
+                      const void *final_norm_weight, const void *lm_head_weight, const void *cos_table,
+                      const void *sin_table, void *k_cache, void *v_cache, void *hidden_buffer, void *g_normalized,
+                      void *block_max_vals, void *block_max_idxs, int *output_log, int num_layers, int start_position,
+                      int max_seq_len, float attn_scale, int eos_token_id, int synchronize, cudaStream_t stream) {
   Engine *e = current_engine_unlocked();
   if (!e) return QMK_ERR_CUDA;
   clear_error(e);
@@ -705,6 +706,32 @@ int qmk_generate(int first_token_id, int num_steps, const void *embed_weight, co
   P.bmax_vals = static_cast<float *>(block_max_vals);
   P.bmax_idxs = static_cast<int *>(block_max_idxs);
   return launch(e, P, stream, synchronize != 0);
+}
+}  // namespace
+
+extern "C" {
+
+int qmk_decode(int input_token_id, int *output_token_id, const void *embed_weight, const LDGLayerWeight *layer_weights,
+               const void *final_norm_weight, const void *lm_head_weight, const void *cos_table, const void *sin_table,
+               void *k_cache, void *v_cache, void *hidden_buffer, void *g_normalized, void *block_max_vals,
+               void *block_max_idxs, int num_layers, int position, int max_seq_len, float attn_scale,
+               cudaStream_t stream) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  return decode_unlocked(input_token_id, output_token_id, embed_weight, layer_weights, final_norm_weight, lm_head_weight,
+                         cos_table, sin_table, k_cache, v_cache, hidden_buffer, g_normalized, block_max_vals, block_max_idxs,
+                         num_layers, position, max_seq_len, attn_scale, stream);
+}
+
+int qmk_generate(int first_token_id, int num_steps, const void *embed_weight, const LDGLayerWeight *layer_weights,
+                 const void *final_norm_weight, const void *lm_head_weight, const void *cos_table,
+                 const void *sin_table, void *k_cache, void *v_cache, void *hidden_buffer, void *g_normalized,
+                 void *block_max_vals, void *block_max_idxs, int *output_log, int num_layers, int start_position,
+                 int max_seq_len, float attn_scale, int eos_token_id, int synchronize, cudaStream_t stream) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  return generate_unlocked(first_token_id, num_steps, embed_weight, layer_weights, final_norm_weight, lm_head_weight,
+                           cos_table, sin_table, k_cache, v_cache, hidden_buffer, g_normalized, block_max_vals,
+                           block_max_idxs, output_log, num_layers, start_position, max_seq_len, attn_scale, eos_token_id,
+                           synchronize, stream);
 }
 
 int qmk_generate_batch(int num_sequences, const int *first_token_ids, const int *start_positions, int num_steps,
@@ -747,11 +774,13 @@ int qmk_generate_batch(int num_sequences, const int *first_token_ids, const int 
   return launch(e, P, stream, synchronize != 0, true);
 }
 
-int qmk_prefill(const int *token_ids_host, int num_tokens, const void *embed_weight,
-                const LDGLayerWeight *layer_weights, const void *final_norm_weight, const void *cos_table,
-                const void *sin_table, void *k_cache, void *v_cache, int num_layers, int start_position,
-                int max_seq_len, float attn_scale, cudaStream_t stream) {
-  std::lock_guard<std::mutex> lock(g_mutex);
+}  // extern "C"
+
+namespace {
+int prefill_unlocked(const int *token_ids_host, int num_tokens, const void *embed_weight,
+                     const LDGLayerWeight *layer_weights, const void *final_norm_weight, const void *cos_table,
+                     const void *sin_table, void *k_cache, void *v_cache, int num_layers, int start_position,
+                     int max_seq_len, float attn_scale, cudaStream_t stream) {
   Engine *e = current_engine_unlocked();
   if (!e) return QMK_ERR_CUDA;
   clear_error(e);
@@ -776,6 +805,155 @@ int qmk_prefill(const int *token_ids_host, int num_tokens, const void *embed_wei
   P.num_steps = num_tokens;
   P.token_ids = e->tok_dev;
   return launch(e, P, stream, true);
+}
+
+// ---- engine handles ------------------------------------------------------------------------------------------
+// The per-device state above (scratch, options) is shared by everything that decodes on a GPU.  A handle is one
+// client's view of it: its own options (vocabulary, weight format, RoPE mode and frequencies, grid cap, split length,
+// time-out, kernel choice) and its own K-major weight copies.  Every handle call makes the handle's options current
+// and runs the op under ONE hold of the lock, so clients with different options can share a GPU from several threads.
+}  // namespace
+
+struct qmk_engine {
+  int device = 0;
+  qmk_engine_config cfg;
+  float inv_freq[qmk::D / 2];
+  std::vector<const void *> tables;   // layer tables this handle decoded with (their K-major copies die with it)
+};
+
+namespace {
+int apply_handle_unlocked(qmk_engine *h, const void *table) {
+  if (!h) return QMK_ERR_BAD_ARGUMENT;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return QMK_ERR_CUDA;
+  if (dev != h->device && cudaSetDevice(h->device) != cudaSuccess) return QMK_ERR_CUDA;
+  Engine *e = current_engine_unlocked();
+  if (!e) return QMK_ERR_CUDA;
+  const qmk_engine_config &c = h->cfg;
+  e->vocab = c.vocab_size > 0 ? c.vocab_size : 151936;   // a handle never inherits another client's values
+  e->rope_from_table = c.rope_from_table ? 1 : 0;
+  if (c.split_len > 0) e->split_len = c.split_len;      // speed / debugging knobs: non-positive leaves qmk_configure's value
+  if (c.max_ctas > 0) e->max_ctas = c.max_ctas;
+  if (c.timeout_ms > 0) e->timeout_ms = c.timeout_ms;
+  e->wfmt = c.weight_format ? 1 : 0;
+  if (c.fused >= 0) e->fused = c.fused;   // a speed knob, not a property of the weights: negative leaves qmk_set_fused's value
+  if ((!e->inv_freq_set || memcmp(e->inv_freq, h->inv_freq, sizeof(h->inv_freq)) != 0)) {
+    QMK_CUDA(e, cudaDeviceSynchronize());   // no launch may still be reading the old table
+    QMK_CUDA(e, cudaMemcpyToSymbol(qmk::c_inv_freq, h->inv_freq, sizeof(h->inv_freq)));
+    memcpy(e->inv_freq, h->inv_freq, sizeof(h->inv_freq));
+    e->inv_freq_set = true;
+    e->rope_cap = 0;
+  }
+  if (table) {
+    bool seen = false;
+    for (const void *t : h->tables) seen |= (t == table);
+    if (!seen) h->tables.push_back(table);
+  }
+  return QMK_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int qmk_prefill(const int *token_ids_host, int num_tokens, const void *embed_weight,
+                const LDGLayerWeight *layer_weights, const void *final_norm_weight, const void *cos_table,
+                const void *sin_table, void *k_cache, void *v_cache, int num_layers, int start_position,
+                int max_seq_len, float attn_scale, cudaStream_t stream) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  return prefill_unlocked(token_ids_host, num_tokens, embed_weight, layer_weights, final_norm_weight, cos_table, sin_table,
+                          k_cache, v_cache, num_layers, start_position, max_seq_len, attn_scale, stream);
+}
+
+int qmk_engine_create(const qmk_engine_config *config, qmk_engine **out) {
+  if (!config || !out) return QMK_ERR_BAD_ARGUMENT;
+  if (config->weight_format != 0 && config->weight_format != 1) return QMK_ERR_BAD_ARGUMENT;
+  if (config->fused > 2 || (config->max_ctas > 0 && config->max_ctas < qmk::NKV)) return QMK_ERR_BAD_ARGUMENT;
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || config->device < 0 || config->device >= ndev || config->device >= MAX_DEVICES)
+    return QMK_ERR_CUDA;
+  qmk_engine *h = new qmk_engine();
+  h->device = config->device;
+  h->cfg = *config;
+  if (config->inv_freq64) {
+    memcpy(h->inv_freq, config->inv_freq64, sizeof(h->inv_freq));
+  } else {   // the library's default: theta = 1e6
+    for (int i = 0; i < qmk::D / 2; ++i) h->inv_freq[i] = static_cast<float>(1.0 / pow(1.0e6, (2.0 * i) / qmk::D));
+  }
+  h->cfg.inv_freq64 = nullptr;   // copied: the caller's array need not outlive the call
+  *out = h;
+  return QMK_OK;
+}
+
+int qmk_engine_destroy(qmk_engine *h) {
+  if (!h) return QMK_OK;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int prev = 0;
+    cudaGetDevice(&prev);
+    if (cudaSetDevice(h->device) == cudaSuccess) {
+      Engine *e = current_engine_unlocked();
+      if (e) {
+        for (size_t i = 0; i < e->prepared.size();) {
+          bool mine = false;
+          for (const void *t : h->tables) mine |= (t == e->prepared[i].table);
+          if (mine) {
+            cudaDeviceSynchronize();
+            free_prepared(e->prepared[i]);
+            e->prepared.erase(e->prepared.begin() + static_cast<long>(i));
+          } else {
+            ++i;
+          }
+        }
+      }
+      cudaSetDevice(prev);
+    }
+  }
+  delete h;
+  return QMK_OK;
+}
+
+int qmk_engine_apply(qmk_engine *h) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  return apply_handle_unlocked(h, nullptr);
+}
+
+int qmk_engine_decode(qmk_engine *h, int input_token_id, int *output_token_id, const void *embed_weight,
+                      const LDGLayerWeight *layer_weights, const void *final_norm_weight, const void *lm_head_weight,
+                      const void *cos_table, const void *sin_table, void *k_cache, void *v_cache, void *hidden_buffer,
+                      void *g_normalized, void *block_max_vals, void *block_max_idxs, int num_layers, int position,
+                      int max_seq_len, float attn_scale, cudaStream_t stream) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  const int rc = apply_handle_unlocked(h, layer_weights);
+  if (rc != QMK_OK) return rc;
+  return decode_unlocked(input_token_id, output_token_id, embed_weight, layer_weights, final_norm_weight, lm_head_weight,
+                         cos_table, sin_table, k_cache, v_cache, hidden_buffer, g_normalized, block_max_vals, block_max_idxs,
+                         num_layers, position, max_seq_len, attn_scale, stream);
+}
+
+int qmk_engine_generate(qmk_engine *h, int first_token_id, int num_steps, const void *embed_weight,
+                        const LDGLayerWeight *layer_weights, const void *final_norm_weight, const void *lm_head_weight,
+                        const void *cos_table, const void *sin_table, void *k_cache, void *v_cache, void *hidden_buffer,
+                        void *g_normalized, void *block_max_vals, void *block_max_idxs, int *output_log, int num_layers,
+                        int start_position, int max_seq_len, float attn_scale, int eos_token_id, int synchronize,
+                        cudaStream_t stream) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  const int rc = apply_handle_unlocked(h, layer_weights);
+  if (rc != QMK_OK) return rc;
+  return generate_unlocked(first_token_id, num_steps, embed_weight, layer_weights, final_norm_weight, lm_head_weight,
+                           cos_table, sin_table, k_cache, v_cache, hidden_buffer, g_normalized, block_max_vals,
+                           block_max_idxs, output_log, num_layers, start_position, max_seq_len, attn_scale, eos_token_id,
+                           synchronize, stream);
+}
+
+int qmk_engine_prefill(qmk_engine *h, const int *token_ids_host, int num_tokens, const void *embed_weight,
+                       const LDGLayerWeight *layer_weights, const void *final_norm_weight, const void *cos_table,
+                       const void *sin_table, void *k_cache, void *v_cache, int num_layers, int start_position,
+                       int max_seq_len, float attn_scale, cudaStream_t stream) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  const int rc = apply_handle_unlocked(h, layer_weights);
+  if (rc != QMK_OK) return rc;
+  return prefill_unlocked(token_ids_host, num_tokens, embed_weight, layer_weights, final_norm_weight, cos_table, sin_table,
+                          k_cache, v_cache, num_layers, start_position, max_seq_len, attn_scale, stream);
 }
 
 int qmk_sync_status(void) {

@@ -77,6 +77,25 @@ _lib.qmk_prefill_chunked.argtypes = [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I,
 _lib.qmk_prefill_chunked.restype = _I
 _lib.qmk_gemm_f16_tn.argtypes = [_P, _P, _P, _I, _I, _I, _P]
 _lib.qmk_gemm_f16_tn.restype = _I
+
+
+class _EngineConfig(ctypes.Structure):
+    _fields_ = [("device", _I), ("vocab_size", _I), ("weight_format", _I), ("rope_from_table", _I),
+                ("split_len", _I), ("max_ctas", _I), ("timeout_ms", _I), ("fused", _I), ("inv_freq64", _P)]
+
+
+_lib.qmk_engine_create.argtypes = [ctypes.POINTER(_EngineConfig), ctypes.POINTER(_P)]
+_lib.qmk_engine_create.restype = _I
+_lib.qmk_engine_destroy.argtypes = [_P]
+_lib.qmk_engine_destroy.restype = _I
+_lib.qmk_engine_apply.argtypes = [_P]
+_lib.qmk_engine_apply.restype = _I
+_lib.qmk_engine_decode.argtypes = [_P] + _lib.qmk_decode.argtypes
+_lib.qmk_engine_decode.restype = _I
+_lib.qmk_engine_generate.argtypes = [_P] + _lib.qmk_generate.argtypes
+_lib.qmk_engine_generate.restype = _I
+_lib.qmk_engine_prefill.argtypes = [_P] + _lib.qmk_prefill.argtypes
+_lib.qmk_engine_prefill.restype = _I
 _lib.qmk_sync_status.restype = _I
 _lib.qmk_last_error.restype = ctypes.c_char_p
 _lib.qmk_num_ctas.restype = _I
@@ -89,7 +108,7 @@ _lib.qmk_selftest_gemm_wait_timeout.restype = _I
 EXPORTED_SYMBOLS = (
     "launch_ldg_decode_direct", "launch_ldg_decode_persistent", "launch_ldg_generate_nosync",
     "launch_ldg_prefill", "qmk_abi_version", "qmk_configure", "qmk_set_inv_freq", "qmk_set_logits_dump",
-    "qmk_set_weight_format", "qmk_set_tuning", "qmk_set_tuning2", "qmk_set_profile_buffer", "qmk_set_fused", "qmk_invalidate_weights", "qmk_release_weights", "qmk_decode", "qmk_generate", "qmk_generate_static", "qmk_generate_batch", "qmk_gemm_f16_tn", "qmk_decode_batched", "qmk_prefill_chunked", "qmk_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
+    "qmk_set_weight_format", "qmk_set_tuning", "qmk_set_tuning2", "qmk_set_profile_buffer", "qmk_set_fused", "qmk_invalidate_weights", "qmk_release_weights", "qmk_decode", "qmk_generate", "qmk_generate_static", "qmk_generate_batch", "qmk_gemm_f16_tn", "qmk_decode_batched", "qmk_prefill_chunked", "qmk_prefill", "qmk_engine_create", "qmk_engine_destroy", "qmk_engine_apply", "qmk_engine_decode", "qmk_engine_generate", "qmk_engine_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
     "qmk_scratch_bytes", "qmk_selftest_wait_timeout", "qmk_selftest_gemm_wait_timeout",
 )
 
@@ -194,6 +213,101 @@ def prefill(token_ids, embed_weight, layer_weights_packed, final_norm_weight, lm
 
 
 # ---------------------------------------------------------------- additions
+class Engine:
+    """One client's view of a GPU: an engine handle of the library (``qmk_engine_create``) that carries the
+    client's options - vocabulary size, weight format, RoPE mode and frequencies, grid cap, time-out - and offers
+    ``decode`` / ``generate_nosync`` / ``prefill`` with the arguments of the module-level ops.  Each call applies the
+    options and runs the op under one hold of the library's lock, so engines with different options can share a GPU."""
+
+    def __init__(self, device=None, vocab_size=151936, weight_format="fp16", rope_from_table=False, inv_freq=None,
+                 split_len=-1, max_ctas=-1, timeout_ms=-1, fused=-1):
+        _require_cuda()
+        if device is None:
+            device = torch.cuda.current_device()
+        index = torch.device(device).index if not isinstance(device, int) else device
+        fmt = {"fp16": 0, "fp8": 1, 0: 0, 1: 1}.get(weight_format)
+        _check(fmt is not None, f"Engine: unknown weight_format {weight_format!r}")
+        freq = None
+        if inv_freq is not None:
+            freq = inv_freq.detach().to(dtype=torch.float32, device="cpu").contiguous()
+            _check(freq.numel() == 64, "Engine: inv_freq must hold 64 values")
+        cfg = _EngineConfig(int(index if index is not None else torch.cuda.current_device()), int(vocab_size), fmt,
+                            int(bool(rope_from_table)), int(split_len), int(max_ctas), int(timeout_ms), int(fused),
+                            freq.data_ptr() if freq is not None else None)
+        handle = _P()
+        rc = _lib.qmk_engine_create(ctypes.byref(cfg), ctypes.byref(handle))
+        if rc != 0:
+            raise RuntimeError(f"Engine: qmk_engine_create failed (status {rc})")
+        self._handle = handle
+        self.device = cfg.device
+
+    def close(self) -> None:
+        handle, self._handle = getattr(self, "_handle", None), None
+        if handle:
+            _lib.qmk_engine_destroy(handle)
+
+    __del__ = close
+
+    def _live(self):
+        _check(bool(self._handle), "Engine: used after close()")
+        return self._handle
+
+    def _done(self, who: str, rc: int) -> None:
+        if rc != 0:
+            raise RuntimeError(f"{who}: {_lib.qmk_last_error().decode()} (status {rc})")
+
+    def apply(self) -> None:
+        """Makes this engine's options the device's current ones, for the entry points that take no handle
+        (``generate_batch``, ``decode_batched``, ``prefill_chunked``, ``generate_static``)."""
+        self._done("Engine.apply", _lib.qmk_engine_apply(self._live()))
+
+    def decode(self, input_token_id, embed_weight, layer_weights_packed, final_norm_weight, lm_head_weight,
+               cos_table, sin_table, k_cache, v_cache, hidden, act, res, q, k, v, attn_out, mlp_inter,
+               norm_out, bmax_vals, bmax_idxs, num_layers, position, max_seq_len, attn_scale):
+        """``decode`` of the module (same arguments and result) with this engine's options."""
+        _check_table(layer_weights_packed, "decode")
+        out = torch.zeros(1, dtype=torch.int32, device=embed_weight.device)
+        self._done("decode", _lib.qmk_engine_decode(
+            self._live(), int(input_token_id), out.data_ptr(), _ptr(embed_weight), _ptr(layer_weights_packed),
+            _ptr(final_norm_weight), _ptr(lm_head_weight), _ptr(cos_table), _ptr(sin_table), _ptr(k_cache),
+            _ptr(v_cache), _ptr(hidden), _ptr(norm_out), _ptr(bmax_vals), _ptr(bmax_idxs), int(num_layers),
+            int(position), int(max_seq_len), float(attn_scale), _stream()))
+        return out
+
+    def generate_nosync(self, first_token_id, num_steps, embed_weight, layer_weights_packed, final_norm_weight,
+                        lm_head_weight, cos_table, sin_table, k_cache, v_cache, hidden, act, res, q, k, v,
+                        attn_out, mlp_inter, norm_out, bmax_vals, bmax_idxs, output_log, num_layers,
+                        start_position, max_seq_len, attn_scale, eos_token_id=151645):
+        """``generate_nosync`` of the module (same arguments and result) with this engine's options."""
+        _check(output_log.dtype == torch.int32 and output_log.is_cuda and output_log.is_contiguous(),
+               "generate_nosync: output_log must be a contiguous int32 CUDA tensor")
+        _check(output_log.numel() >= num_steps,
+               f"generate_nosync: output_log.numel() ({output_log.numel()}) < num_steps ({num_steps})")
+        _check_table(layer_weights_packed, "generate_nosync")
+        self._done("generate_nosync", _lib.qmk_engine_generate(
+            self._live(), int(first_token_id), int(num_steps), _ptr(embed_weight), _ptr(layer_weights_packed),
+            _ptr(final_norm_weight), _ptr(lm_head_weight), _ptr(cos_table), _ptr(sin_table), _ptr(k_cache),
+            _ptr(v_cache), _ptr(hidden), _ptr(norm_out), _ptr(bmax_vals), _ptr(bmax_idxs), output_log.data_ptr(),
+            int(num_layers), int(start_position), int(max_seq_len), float(attn_scale),
+            -1 if eos_token_id is None else int(eos_token_id), 1, _stream()))
+        return output_log
+
+    def prefill(self, token_ids, embed_weight, layer_weights_packed, final_norm_weight, lm_head_weight, cos_table,
+                sin_table, k_cache, v_cache, hidden, act, res, q, k, v, attn_out, mlp_inter, norm_out,
+                bmax_vals, bmax_idxs, num_layers, start_position, max_seq_len, attn_scale):
+        """``prefill`` of the module (same arguments) with this engine's options."""
+        _check(token_ids.dtype == torch.int32, "token_ids must be int32")
+        _check(not token_ids.is_cuda, "prefill: token_ids must be a CPU tensor")
+        _check(token_ids.is_contiguous(), "prefill: token_ids must be contiguous")
+        if token_ids.numel() == 0:
+            return None
+        _check_table(layer_weights_packed, "prefill")
+        self._done("prefill", _lib.qmk_engine_prefill(
+            self._live(), token_ids.data_ptr(), int(token_ids.numel()), _ptr(embed_weight), _ptr(layer_weights_packed),
+            _ptr(final_norm_weight), _ptr(cos_table), _ptr(sin_table), _ptr(k_cache), _ptr(v_cache),
+            int(num_layers), int(start_position), int(max_seq_len), float(attn_scale), _stream()))
+
+
 def configure(vocab_size=-1, rope_from_table=-1, split_len=-1, max_ctas=-1, timeout_ms=-1) -> None:
     """Engine options of the current device; negative keeps the present value."""
     rc = _lib.qmk_configure(int(vocab_size), int(rope_from_table), int(split_len), int(max_ctas), int(timeout_ms))

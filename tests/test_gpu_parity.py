@@ -366,3 +366,55 @@ def test_decoders_with_different_options_share_a_gpu(C, tiny_cfg):
     finally:
         C.set_weight_format("fp16")
         C.configure(vocab_size=tiny_cfg["vocab_size"])
+
+
+def test_engine_handles_from_two_threads(C, tiny_cfg):
+    """Engine handles (``qmk_engine_create``): each carries one client's options and applies them with the op under
+    one hold of the library's lock, so two threads that decode with different vocabularies and weight formats on one
+    GPU - with no re-application by the caller - both get the oracle's tokens.  Destroying a handle frees the K-major
+    weight copies made for its table; the decoder that owned it can no longer be used."""
+    import threading
+    import quantize
+    from Model.Qwen06B_architecture import Decoder
+    w_a = _tiny_weights(tiny_cfg)
+    cfg_b = dict(tiny_cfg, seed=tiny_cfg["seed"] + 11, vocab_size=2048)
+    eng_b_w, oracle_b_w = quantize.quantize_weights_fp8(_tiny_weights(cfg_b))
+    ids_a = S.make_prompt(9, seed=31, vocab_size=tiny_cfg["vocab_size"])
+    ids_b = S.make_prompt(7, seed=32, vocab_size=cfg_b["vocab_size"])
+    want_a = OracleDecoder(w_a, max_seq_len=tiny_cfg["max_seq_len"]).generate_ids(ids_a, 5)[0]
+    want_b = OracleDecoder(oracle_b_w, max_seq_len=tiny_cfg["max_seq_len"]).generate_ids(ids_b, 5)[0]
+    a = Decoder(weights=S.weights_to(w_a, "cuda"), verbose=False, max_seq_len=tiny_cfg["max_seq_len"])
+    b = Decoder(weights=S.weights_to(eng_b_w, "cuda"), verbose=False, max_seq_len=tiny_cfg["max_seq_len"],
+                weight_format="fp8")
+    assert a._engine is not None and b._engine is not None
+    results, errors = {"a": [], "b": []}, []
+
+    def work(name, dec, ids):
+        try:
+            torch.cuda.set_device(0)
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                for _ in range(6):
+                    results[name].append(dec.generate_ids(ids, 5))
+        except Exception as exc:   # surfaced below: an exception in a thread would otherwise pass silently
+            errors.append(repr(exc))
+
+    try:
+        torch.cuda.synchronize()
+        threads = [threading.Thread(target=work, args=("a", a, ids_a)), threading.Thread(target=work, args=("b", b, ids_b))]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join(timeout=300)
+        assert not errors, errors
+        assert results["a"] == [want_a] * 6 and results["b"] == [want_b] * 6
+        # bad configurations are refused without a handle
+        with pytest.raises(RuntimeError, match="qmk_engine_create"):
+            C.Engine(vocab_size=2048, weight_format="fp16", fused=7)
+        a._engine.close()
+        with pytest.raises(RuntimeError, match="after close"):
+            a.generate_ids(ids_a, 2)
+        assert b.generate_ids(ids_b, 5) == want_b
+    finally:
+        C.set_weight_format("fp16")
+        C.configure(vocab_size=tiny_cfg["vocab_size"])

@@ -23,6 +23,19 @@ def test_library_exports_every_declared_symbol(built_library):
     assert declared == set(C.EXPORTED_SYMBOLS)
 
 
+def test_engine_handle_argument_checks(built_library):
+    """qmk_engine_create refuses null pointers and unknown weight formats before touching a GPU; destroying a null
+    handle is a no-op."""
+    import qwen_megakernel_C as C
+    lib = C._lib
+    handle = ctypes.c_void_p()
+    assert lib.qmk_engine_create(None, ctypes.byref(handle)) != 0
+    cfg = C._EngineConfig(0, 151936, 5, 0, -1, -1, -1, -1, None)
+    assert lib.qmk_engine_create(ctypes.byref(cfg), ctypes.byref(handle)) != 0 and not handle
+    assert lib.qmk_engine_destroy(None) == 0
+    assert lib.qmk_engine_apply(None) != 0
+
+
 def test_abi_version_handshake(built_library):
     import qwen_megakernel_C as C
     from Model import Qwen06B_architecture as A
