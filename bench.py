@@ -239,13 +239,14 @@ def decode_case(device, rank, world, fp16_weights, weights_kind, B, prompt_lens,
     weights = fp16_weights
     if weights_kind != "fp16":
         import quantize
-        if B > 4:      # tensor-core batched path: the quantised VALUES, stored expanded as fp16 (no packed GEMM operand)
-            weights, _ = (quantize.expand_weights_fp8 if weights_kind == "fp8" else quantize.expand_weights_nvfp4)(fp16_weights)
-            expanded = True
-        elif weights_kind == "fp8":
+        # packed rows in HBM on every path: the persistent kernels read FP8 rows directly, the tensor-core path
+        # expands FP8 / NVFP4 K blocks to fp16 tiles inside its GEMMs
+        if weights_kind == "fp8":
             weights, _ = quantize.quantize_weights_fp8(fp16_weights)
+        elif B > 3:
+            weights, _ = quantize.quantize_weights_nvfp4(fp16_weights)
         else:
-            raise SystemExit("bench.py: nvfp4 needs --batch > 4 (values expanded to fp16 on the tensor-core path)")
+            raise SystemExit("bench.py: nvfp4 needs --batch > 3 (only the tensor-core path reads NVFP4 rows)")
     engine_format = "fp16" if (expanded or weights_kind == "fp16") else weights_kind
     parity = None
     if B == 1:
@@ -278,7 +279,7 @@ def decode_case(device, rank, world, fp16_weights, weights_kind, B, prompt_lens,
     else:
         eng = BatchDecoder(weights=weights, tokenizer=S.StubTokenizer(-1), num_sequences=B, max_seq_len=max_seq,
                            device=str(device), weight_format=engine_format,
-                           prefill_mode="tensor" if engine_format == "fp16" else "serial")
+                           prefill_mode="serial" if (engine_format == "fp8" and B <= 3) else "tensor")
         engine_name = "persistent megakernel" if eng.engine == "persistent" else "tcgen05 GEMM path"
         prompts = [S.make_prompt(prompt_lens[b], seed=rank * 128 + b) for b in range(B)]
         for b in range(B):
@@ -361,7 +362,9 @@ def decode_case(device, rank, world, fp16_weights, weights_kind, B, prompt_lens,
                ms_per_step=1e3 * total_s / steps, launch_ms=statistics.mean(launch_ms),
                per_rank_launch_ms={"min": min(per_rank), "median": statistics.median(per_rank), "max": max(per_rank)},
                bytes_per_launch=launch_bytes, achieved_gbs=achieved, frac=achieved / peak, peak=peak, peak_kind=peak_kind,
-               engine=engine_name, expanded=expanded, clocks=clocks.summary(), grid=C.num_ctas(), parity=parity,
+               engine=engine_name, expanded=expanded,
+               stored={"fp16": "fp16", "fp8": "packed FP8-E4M3 rows (fp32 row scales)",
+                       "nvfp4": "packed NVFP4 rows (e2m1 pairs, e4m3 block-16 scales, fp32 tensor scale)"}[weights_kind], clocks=clocks.summary(), grid=C.num_ctas(), parity=parity,
                launches=steps if engine_name == "persistent megakernel" else steps * decode_tokens * (7 * 28 + 4))
     del eng
     torch.cuda.empty_cache()
@@ -454,7 +457,7 @@ def run_ours(args):
         "metric": METRIC if B == 1 else f"batch-{B} decode tok/s (all sequences)", "value": r["value"], "unit": UNIT,
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "fp16" if (args.weights == "fp16" or r["expanded"]) else "fp8-e4m3 weights, fp32 math", "data": "synthetic",
+        "dtype": "fp16" if (args.weights == "fp16" or r["expanded"]) else f"{args.weights} weights, fp32 accumulation", "data": "synthetic",
         "config": {"weights": args.weights + (" (quantised values, stored expanded as fp16)" if r["expanded"] else ""),
                    "workload": WORKLOAD if (args.prompt_len, args.decode_tokens) == (PROMPT_LEN, DECODE_TOKENS) else
                    f"profiling case: {args.prompt_len} prompt tokens, {args.decode_tokens} decode tokens per step",
@@ -474,7 +477,7 @@ def run_ours(args):
         def brief(c):
             return {"value": c["value"], "unit": UNIT, "e2e": c["e2e"], "ms_per_step": c["ms_per_step"], "engine": c["engine"],
                     "roofline_frac": c["frac"], "achieved_gbs": c["achieved_gbs"], "bytes_per_launch": c["bytes_per_launch"],
-                    "weights_stored_as": "fp16 (quantised values expanded)" if c["expanded"] else None,
+                    "weights_stored_as": c["stored"],
                     "per_rank_launch_ms": c["per_rank_launch_ms"]}
         extra = {}
         c3 = {}

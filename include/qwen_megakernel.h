@@ -175,7 +175,11 @@ int qmk_set_logits_dump(float *logits_out);
  * and the LM head (norm vectors stay fp16).  0 (default): fp16 row-major [out,in].
  * 1: FP8-E4M3 rows - each row is `in` e4m3 bytes followed by a 16-byte trailer
  * whose first 4 bytes are the row's fp32 scale (w = scale * e4m3); row stride
- * in + 16 bytes.  Activations, accumulation and the KV cache are unchanged. */
+ * in + 16 bytes.  Activations, accumulation and the KV cache are unchanged.
+ * 2: NVFP4 rows - `in`/2 bytes of e2m1 pairs (element 2i in the low nibble of byte i), `in`/16 e4m3 scales (one per
+ * 16 values), then a 16-byte trailer whose first 4 bytes are the matrix's fp32 tensor scale
+ * (w = tensor_scale * block_scale * e2m1); row stride in/2 + in/16 + 16 bytes.  Format 2 is read by the tensor-core
+ * entry points only (qmk_prefill_chunked, qmk_decode_batched, qmk_gemm_packed_tn); the persistent kernels refuse it. */
 int qmk_set_weight_format(int format);
 
 /* Performance knobs; negative keeps a value.  spin_sleep_ns: nanosleep between
@@ -187,6 +191,12 @@ int qmk_set_tuning(int spin_sleep_ns, int l2_evict_first);
  * which divides the number of pollers per cache line (default 4).  stream_inflight: cap on
  * weight/KV chunks in flight per SM during the layer phases (0 = ring depth). */
 int qmk_set_tuning2(int repl, int stream_inflight);
+
+/* Batched decode (qmk_decode_batched): 1 (default) launches the ~200 kernels of a decode step as programmatic
+ * dependents of one another - each kernel is scheduled while its predecessor still runs, sets itself up, streams the
+ * operands no kernel of the step writes (weight tiles, cache rows of earlier steps) and only then waits for the
+ * predecessor to complete; 0 launches them strictly one after the other.  Same results either way; negative keeps. */
+int qmk_set_step_overlap(int enabled);
 
 /* Kernel choice for one sequence (qmk_decode / qmk_generate / qmk_prefill); negative keeps a value.
  *  fused  2 (default) or 1: the fused kernel - the O and down projections run as split-K slices on the CTAs that
@@ -293,8 +303,8 @@ int qmk_generate_static(
  * seven projections run as tcgen05 GEMMs over the whole chunk (weights are read once per chunk instead
  * of once per token, megakernel_5090.cu:1324-1350), with row-wise kernels for RMSNorm, per-head QK-norm +
  * RoPE + cache write, causal attention over the cache, and SwiGLU between them.  Same arguments, cache
- * layout, position rule and blocking behaviour as qmk_prefill; fp16 weights only (with FP8 weights
- * selected it returns QMK_ERR_BAD_ARGUMENT: use qmk_prefill).  GEMM operands are rounded to fp16 (the
+ * layout, position rule and blocking behaviour as qmk_prefill; all three weight formats (packed FP8 / NVFP4 matrices
+ * stay packed in HBM and are expanded to fp16 tiles inside the GEMM, see qmk_gemm_packed_tn).  GEMM operands are rounded to fp16 (the
  * decode kernel keeps fp32 activations), so cache rows agree with qmk_prefill's to fp16 rounding, not
  * bit for bit.  Scratch (about 160 MB) is allocated on the first call per device. */
 int qmk_prefill_chunked(
@@ -307,7 +317,8 @@ int qmk_prefill_chunked(
  * the seven projections and the LM head as tcgen05 GEMMs over one 128-row tile of sequences, with row kernels
  * for the norms, per-head QK-norm + RoPE + cache write (each sequence at its own position in its own cache),
  * per-sequence attention over the cache, SwiGLU and the argmax.  Same arguments as qmk_generate_batch (host
- * arrays of num_sequences entries; no EOS stop; logits dump [sequence][step][vocab]); fp16 weights only, vocab
+ * arrays of num_sequences entries; no EOS stop; logits dump [sequence][step][vocab]); all three weight formats
+ * (packed matrices are expanded inside the GEMMs, which halves / quarters the weight bytes of a step), vocab
  * a multiple of 128; blocks until done.  One step costs about 400 kernel launches, so it pays from roughly
  * eight sequences on; below that qmk_generate_batch (one persistent launch) is faster.  Numerics as
  * qmk_prefill_chunked (GEMM operands rounded to fp16). */
@@ -325,6 +336,19 @@ int qmk_decode_batched(
  * counterpart (its prefill repeats the decode kernels once per prompt token, megakernel_5090.cu:1324-1350).
  * Blocks until done. */
 int qmk_gemm_f16_tn(const void *a, const void *b, float *c, int m, int n, int k, cudaStream_t stream);
+
+/* The same GEMM with B kept PACKED in device memory: weight_format 1 = FP8-E4M3 rows (k bytes + 16-byte trailer with
+ * the fp32 row scale), 2 = NVFP4 rows (k/2 bytes of e2m1 pairs, low nibble first; k/16 e4m3 block-16 scales; 16-byte
+ * trailer with the fp32 tensor scale).  The packed K blocks cross HBM as they are and are expanded to fp16 tiles in
+ * shared memory inside the kernel (e4m3 and e2m1 x block scale are exact in fp16), the fp32 scale multiplies the
+ * accumulator: products are those of the dequantised matrix with fp16 activations, fp32 accumulation.  k <= 3072,
+ * a multiple of 64 (NVFP4: of 256, so that rows stay 16-byte aligned).
+ * mode 0: c fp32 [m x n].  mode 1: split-K by four, c fp32 [4][m x n] partial matrices.  mode 2: b = gate, b2 = up,
+ * c fp16 [m x n] = silu(a gate^T) * (a up^T).  box_n: rows of B per CTA (32, 64, 128; modes 1 and 2: 32 or 64), 0 picks.
+ * These are the three forms qmk_decode_batched and qmk_prefill_chunked use when a packed weight format is selected.
+ * No counterpart in the reference (fp16 only).  Blocks until done. */
+int qmk_gemm_packed_tn(const void *a, const void *b, const void *b2, void *c, int m, int n, int k, int weight_format,
+                       int mode, int box_n, cudaStream_t stream);
 
 /* Synchronises the device and returns the status word of the last launch
  * (QMK_OK, or the first error a CTA recorded). */

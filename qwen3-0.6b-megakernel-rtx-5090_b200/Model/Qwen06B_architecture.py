@@ -166,13 +166,18 @@ class Decoder:
         dev = self._embed_weight.device
         self.num_layers = len(weights["layer_weights"]) // FIELDS_PER_LAYER
         self.vocab_size = int(self._embed_weight.shape[0])
-        self.weight_format = weight_format   # "fp16", or "fp8" (matrices packed by quantize.quantize_weights_fp8)
+        # "fp16"; "fp8" (matrices packed by quantize.quantize_weights_fp8); "nvfp4" (quantize.quantize_weights_nvfp4:
+        # read by the tensor-core ops only - tensor prefill, BatchDecoder(engine="gemm"))
+        if weight_format not in ("fp16", "fp8", "nvfp4"):
+            raise ValueError("weight_format must be 'fp16', 'fp8' or 'nvfp4'")
+        self.weight_format = weight_format
         # "serial": the reference's token-by-token prefill (fp32 activations, bit-identical to decoding the
-        # prompt); "tensor": chunked prefill on the tensor cores (fp16 GEMM operands, fp16 weights only)
+        # prompt); "tensor": chunked prefill on the tensor cores (fp16 GEMM operands; packed matrices are expanded
+        # inside the GEMMs)
         if prefill_mode not in ("serial", "tensor"):
             raise ValueError("prefill_mode must be 'serial' or 'tensor'")
-        if prefill_mode == "tensor" and weight_format != "fp16":
-            raise ValueError("tensor-core prefill needs fp16 weights")
+        if prefill_mode == "serial" and weight_format == "nvfp4":
+            raise ValueError("NVFP4 weights need prefill_mode='tensor' (the persistent kernels do not read them)")
         self.prefill_mode = prefill_mode
         cos, sin = weights.get("cos_table"), weights.get("sin_table")
         if cos is None or cos.shape[0] < self.max_seq_len or cos.device != dev:
@@ -220,7 +225,8 @@ class Decoder:
             self._decode_op = _decode
             self._gen = _require_megakernel_op("generate_nosync")
             self._prefill_op = _require_megakernel_op("prefill")
-        row_bytes = (HIDDEN_SIZE + 16) if weight_format == "fp8" else 2 * HIDDEN_SIZE
+        row_bytes = {"fp16": 2 * HIDDEN_SIZE, "fp8": HIDDEN_SIZE + 16,
+                     "nvfp4": HIDDEN_SIZE // 2 + HIDDEN_SIZE // 16 + 16}[weight_format]
         if self._embed_weight.numel() * self._embed_weight.element_size() != self.vocab_size * row_bytes:
             raise RuntimeError(f"embedding tensor does not have {self.vocab_size} rows of {row_bytes} bytes: "
                                f"weight_format={weight_format!r} does not match the weights")
@@ -345,14 +351,13 @@ class BatchDecoder:
     def __init__(self, weights=None, tokenizer=None, num_sequences: int = 4, max_seq_len: int = MAX_SEQ_LEN,
                  verbose: bool = False, engine: str = "auto", **decoder_kw):
         """``engine``: "persistent" (one megakernel launch, <= 4 sequences, fp32 activations), "gemm" (tcgen05
-        GEMMs per step, <= 128 sequences, fp16 GEMM operands, fp16 weights only) or "auto": persistent up to 3
-        sequences (and up to 4 with packed FP8 rows, which only the persistent kernels read), gemm above -
+        GEMMs per step, <= 128 sequences, fp16 GEMM operands; packed FP8 / NVFP4 matrices are expanded inside the
+        GEMMs) or "auto": persistent up to 3 sequences, gemm above (NVFP4: always gemm) -
         measured at 1024-token contexts, 4 sequences: 2060 tok/s persistent, 2566 tok/s gemm; 2 sequences: 1519
         against 1321."""
         n = int(num_sequences)
         if engine == "auto":
-            packed = decoder_kw.get("weight_format", "fp16") != "fp16"
-            engine = "persistent" if n <= (self.MAX_SEQUENCES if packed else 3) else "gemm"
+            engine = "persistent" if n <= 3 and decoder_kw.get("weight_format", "fp16") != "nvfp4" else "gemm"
         if engine not in ("persistent", "gemm"):
             raise ValueError("engine must be 'auto', 'persistent' or 'gemm'")
         limit = self.MAX_SEQUENCES if engine == "persistent" else self.MAX_GEMM_SEQUENCES

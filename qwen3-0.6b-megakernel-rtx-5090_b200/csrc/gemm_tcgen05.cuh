@@ -14,11 +14,22 @@
 // context survives.  No cluster multicast anywhere.
 //
 // Shapes: M, N multiples of 128, K a multiple of 64 (the callers pad the token dimension).
+//
+// Packed weights (template parameter WQ): B may stay in its packed form in global memory - WQ 1: FP8-E4M3 rows
+// with an fp32 row scale in a 16-byte trailer; WQ 2: NVFP4 rows (two e2m1 values per byte, one e4m3 scale per 16
+// values behind them, the fp32 tensor scale in the trailer).  The producer then brings the PACKED K block into a raw
+// area of the stage (half or a quarter of the fp16 bytes cross HBM and L2), warps 2-5 - idle until the epilogue
+// otherwise - expand it to the fp16, 128-byte-swizzled tile the MMA descriptors expect (e4m3 and e2m1 x block scale
+// are exact in fp16), fence the writes towards the async proxy and arrive on the stage's `full` barrier; the fp32
+// row / tensor scale multiplies the accumulator in the epilogue.  The activations stay fp16 and the accumulation fp32,
+// so the products are those of the dequantised matrix: tcgen05's own narrow kinds (f8f6f4, mxf4nvf4) would need the
+// ACTIVATIONS in 8 or 4 bits as well, which a greedy decoder checked token by token cannot afford.
 #ifndef QMK_GEMM_TCGEN05_CUH_
 #define QMK_GEMM_TCGEN05_CUH_
 
 #include <cuda.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -27,13 +38,26 @@ namespace qmk_gemm {
 constexpr int BM = 128, BK = 64;                 // BK * 2 bytes = one 128-byte swizzle row; the N tile (128 or 64) is a template parameter
 // Ring depth per N-tile variant: as many stages as fit in ~192 KB (a skinny M = 128 problem is bound by the
 // latency of its K loop, so the whole K extent of a 1024-wide matrix is in flight at once).
-constexpr int stages_for(int bn) { return bn == 32 ? 10 : bn == 64 ? 8 : 6; }
+constexpr int stages_for(int bn, int wq = 0) { return wq ? (bn == 32 ? 8 : bn == 64 ? 6 : 4) : (bn == 32 ? 10 : bn == 64 ? 8 : 6); }
 constexpr int MAX_GROUPS = 3;   // matrices sharing one A operand that one launch can multiply (q/k/v, gate/up)
 constexpr int THREADS = 192;
 constexpr uint32_t TILE_A_BYTES = BM * BK * 2;   // 16 KB
-constexpr uint32_t stage_bytes_for(int bn) { return TILE_A_BYTES + static_cast<uint32_t>(bn) * BK * 2; }
-constexpr size_t smem_bytes_for(int bn) {
-  return 1024 /* alignment slack */ + static_cast<size_t>(stages_for(bn)) * stage_bytes_for(bn) + 256;
+// Packed K block of one B row: 64 e4m3 bytes, or 32 bytes of e2m1 pairs
+constexpr uint32_t raw_row_bytes(int wq) { return wq == 1 ? 64u : wq == 2 ? 32u : 0u; }
+constexpr uint32_t stage_bytes_for(int bn, int wq = 0) {
+  return TILE_A_BYTES + static_cast<uint32_t>(bn) * BK * 2 + static_cast<uint32_t>(bn) * raw_row_bytes(wq);
+}
+// Per-row scales kept in shared memory for the whole tile: the fp32 row / tensor scale, and for NVFP4 the block
+// scales of the CTA's K range (one byte per 16 values; K <= 3072 -> 192 bytes, rows 196 bytes apart against bank
+// conflicts).
+constexpr int MAX_K_PACKED = 3072;
+constexpr uint32_t BS_PITCH = MAX_K_PACKED / 16 + 4;
+constexpr uint32_t scale_bytes_for(int bn, int wq) {
+  return wq == 0 ? 0u : static_cast<uint32_t>(bn) * 4u + (wq == 2 ? static_cast<uint32_t>(bn) * BS_PITCH : 0u);
+}
+constexpr size_t smem_bytes_for(int bn, int wq = 0) {
+  return 1024 /* alignment slack */ + static_cast<size_t>(stages_for(bn, wq)) * stage_bytes_for(bn, wq) + 256 +
+         scale_bytes_for(bn, wq);
 }
 
 __device__ __forceinline__ uint32_t s32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -104,6 +128,10 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t tmem_d, uint64_t desc_a, uin
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(IDESC), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
       : "memory");
 }
+// Programmatic dependent launch (see prefill_kernels.cuh): no-ops unless the launch carries the attribute.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -122,22 +150,40 @@ struct Groups {
   // the first rows of the tile; the MMA still reads all 128, so output rows past the box are garbage and the
   // caller must not store them (kernel argument M <= box rows).
   uint32_t a_box_bytes;
+  // Packed weights (WQ != 0): base of every group's packed matrix, bytes between rows, offset of the block scales
+  // (NVFP4) and of the fp32 scale (the trailer) inside a row.
+  const unsigned char *braw[MAX_GROUPS];
+  uint32_t raw_pitch, raw_bs_off, raw_scale_off;
 };
+
+// e2m1 pairs of one byte -> two fp16 values.  (code & 7) << 9 read as fp16 is the e2m1 magnitude times 2^-14 - the
+// two-bit exponent lands in the low exponent bits, subnormal code 1 (0.5) included - so one multiplication by 2^14
+// finishes the conversion exactly; bit 3 is the sign.
+__device__ __forceinline__ __half2 e2m1x2_to_half2(uint32_t byte) {
+  const uint32_t bits = ((byte & 0x07u) << 9) | ((byte & 0x08u) << 12) | ((byte & 0x70u) << 21) | ((byte & 0x80u) << 24);
+  return __hmul2(*reinterpret_cast<const __half2 *>(&bits), __float2half2_rn(16384.0f));
+}
+__device__ __forceinline__ uint32_t e4m3x2_to_half2_bits(uint32_t two_bytes) {
+  const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(two_bytes & 0xFFFFu), __NV_E4M3);
+  return static_cast<uint32_t>(h.x) | (static_cast<uint32_t>(h.y) << 16);
+}
 
 // FUSE (BN = 32 or 64): B0 is the gate matrix and B1 the up matrix of a SwiGLU MLP; the CTA keeps two accumulators
 // (gate tile in TMEM columns [0, BN), up tile in [BN, 2 BN)) and its epilogue writes fp16 silu(gate) * up to
 // groups.C[0] (reinterpreted as __half [M x N]) instead of two fp32 matrices.
-template <int BN, bool FUSE = false>
+template <int BN, bool FUSE = false, int WQ = 0>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
                    const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_b2,
                    const Groups groups, int M, int K, unsigned int *status, unsigned long long budget_ns,
                    int selftest_no_loads) {
   static_assert(BN == 32 || BN == 64 || BN == 128, "N tiles of 32, 64 or 128 columns");
+  pdl_trigger();   // the next kernel of a decode step may set itself up (and stream ITS weights) behind this one
   static_assert(!FUSE || BN <= 64, "the fused SwiGLU epilogue keeps two accumulators of at most 64 columns");
   constexpr int SB = FUSE ? 2 * BN : BN;          // B rows held per stage / accumulator columns
-  constexpr int STAGES = stages_for(SB);
-  constexpr uint32_t STAGE_BYTES = stage_bytes_for(SB);
+  constexpr int STAGES = stages_for(SB, WQ);
+  constexpr uint32_t STAGE_BYTES = stage_bytes_for(SB, WQ);
+  constexpr uint32_t RAW_ROW = raw_row_bytes(WQ);
   // which matrix this CTA works on
   int tile = blockIdx.x, grp = 0;
   if (!FUSE && tile >= groups.N[0] / BN) { tile -= groups.N[0] / BN; grp = 1; }
@@ -149,8 +195,11 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   const uint32_t raw = s32(gemm_smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;                 // swizzled tiles need 1024-byte alignment
   unsigned char *aligned = gemm_smem_raw + (base - raw);
-  const uint32_t bars = base + STAGES * STAGE_BYTES;            // full[STAGES], empty[STAGES], acc_full, then scratch
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(aligned + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 1));
+  const uint32_t bars = base + STAGES * STAGE_BYTES;            // full[STAGES], empty[STAGES], acc_full, raw_full[STAGES], then scratch
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(aligned + STAGES * STAGE_BYTES + 8 * (3 * STAGES + 1));
+  float *s_rowscale = reinterpret_cast<float *>(aligned + STAGES * STAGE_BYTES + 256);   // [SB] (WQ != 0)
+  unsigned char *s_bs = reinterpret_cast<unsigned char *>(s_rowscale + SB);                // [SB][BS_PITCH] (WQ == 2)
+  static_assert(8 * (3 * stages_for(32, 0) + 1) + 8 <= 256, "barriers and scratch fit the 256 bytes behind the ring");
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = tile * BN, m0 = blockIdx.y * BM;
@@ -161,7 +210,15 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   auto full = [&](int s) { return bars + 8u * s; };
   auto empty = [&](int s) { return bars + 8u * (STAGES + s); };
   const uint32_t acc_full = bars + 8u * (2 * STAGES);
-
+  auto raw_full = [&](int s) { return bars + 8u * (2 * STAGES + 1 + s); };   // packed K block (and A) landed
+  // what the producer's copies of one stage signal: with packed weights the expanding warps wait for them and
+  // arrive on `full` themselves (one warp per stage)
+  auto landed = [&](int s) { return WQ ? raw_full(s) : full(s); };
+  constexpr uint32_t TILE_RAW_BYTES = BN * RAW_ROW;
+  const uint32_t stage_tx = (groups.a_box_bytes ? groups.a_box_bytes : TILE_A_BYTES) + (FUSE ? 2u : 1u) * (WQ ? TILE_RAW_BYTES : TILE_B_BYTES);
+  const int kcol = WQ ? static_cast<int>(RAW_ROW) : BK;          // B-map columns (bytes for packed rows) per K block
+  const uint32_t b_dst = WQ ? TILE_A_BYTES + (FUSE ? 2u : 1u) * TILE_B_BYTES : TILE_A_BYTES;   // where the B copies land in a stage
+  const uint32_t b_dst_step = WQ ? TILE_RAW_BYTES : TILE_B_BYTES;
   // the first fill of the ring needs no free-slot wait: thread 0 issues it before the CTA-wide barrier below, so
   // that the first TMA round trip overlaps the TMEM allocation
   const int prologue = selftest_no_loads ? 0 : (kblocks < STAGES ? kblocks : STAGES);
@@ -169,15 +226,42 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map_b)) : "memory");
     if (FUSE) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b1)) : "memory");
-    for (int s = 0; s < STAGES; ++s) { bar_init(full(s), 1); bar_init(empty(s), 1); }
+    for (int s = 0; s < STAGES; ++s) {
+      bar_init(full(s), 1);
+      bar_init(empty(s), 1);
+      if (WQ) bar_init(raw_full(s), 1);
+    }
     bar_init(acc_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // B is a weight matrix: its first tiles are requested before the wait for the preceding kernel (whose output is
+    // A, requested behind the wait below), so the weight stream of this GEMM overlaps that kernel's tail
     for (int kb = 0; kb < prologue; ++kb) {
-      bar_expect_tx(full(kb), (groups.a_box_bytes ? groups.a_box_bytes : TILE_A_BYTES) + (FUSE ? 2 : 1) * TILE_B_BYTES);
-      tma_load_2d(base + kb * STAGE_BYTES, &map_a, (kb0 + kb) * BK, m0, full(kb));
-      tma_load_2d(base + kb * STAGE_BYTES + TILE_A_BYTES, map_b, (kb0 + kb) * BK, n0, full(kb));
-      if (FUSE) tma_load_2d(base + kb * STAGE_BYTES + TILE_A_BYTES + TILE_B_BYTES, &map_b1, (kb0 + kb) * BK, n0, full(kb));
+      bar_expect_tx(landed(kb), stage_tx);
+      tma_load_2d(base + kb * STAGE_BYTES + b_dst, map_b, (kb0 + kb) * kcol, n0, landed(kb));
+      if (FUSE) tma_load_2d(base + kb * STAGE_BYTES + b_dst + b_dst_step, &map_b1, (kb0 + kb) * kcol, n0, landed(kb));
+    }
+  }
+  if (WQ != 0 && warp >= 2) {
+    // scales of this CTA's B rows into shared memory while the first copies are in flight (the CTA-wide barrier below
+    // publishes them): the fp32 row / tensor scale of every row and, for NVFP4, the block scales of the K range
+    const int ct = static_cast<int>(threadIdx.x) - 64;          // 0..127
+    // (selected with conditionals: a run-time index into the kernel parameter would copy the struct to local memory)
+    const unsigned char *braw_lo = FUSE ? groups.braw[0] : grp == 0 ? groups.braw[0] : grp == 1 ? groups.braw[1] : groups.braw[2];
+    const unsigned char *braw_hi = FUSE ? groups.braw[1] : braw_lo;
+    for (int r = ct; r < SB; r += 128) {
+      const unsigned char *row = (FUSE && r >= BN ? braw_hi : braw_lo) +
+                                 static_cast<size_t>(n0 + (FUSE && r >= BN ? r - BN : r)) * groups.raw_pitch;
+      s_rowscale[r] = *reinterpret_cast<const float *>(row + groups.raw_scale_off);
+    }
+    if (WQ == 2) {                                              // one word (four block scales) per row and K block
+      for (int i = ct; i < SB * kblocks; i += 128) {
+        const int r = i / kblocks, w = i - r * kblocks;
+        const unsigned char *row = (FUSE && r >= BN ? braw_hi : braw_lo) +
+                                   static_cast<size_t>(n0 + (FUSE && r >= BN ? r - BN : r)) * groups.raw_pitch;
+        *reinterpret_cast<uint32_t *>(s_bs + r * BS_PITCH + 4 * w) =
+            *reinterpret_cast<const uint32_t *>(row + groups.raw_bs_off + 4 * (kb0 + w));
+      }
     }
   }
   if (warp == 1) {   // the whole warp allocates; the address lands in shared memory
@@ -192,23 +276,25 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
   if (warp == 0) {
     if (lane == 0) {                       // ---- producer
+      pdl_wait();                          // A is the preceding kernel's output
+      for (int kb = 0; kb < prologue; ++kb) tma_load_2d(base + kb * STAGE_BYTES, &map_a, (kb0 + kb) * BK, m0, landed(kb));
       int issued = prologue;
       // self test of the bounded waits: the loads are never issued, so the MMA thread's first wait runs out
       for (int kb = prologue; kb < (selftest_no_loads ? 0 : kblocks); ++kb) {
         const int s = kb % STAGES;
         if (kb >= STAGES && !bar_wait(empty(s), ((kb / STAGES) - 1) & 1, abort_flag, status, budget_ns)) break;
         if (*abort_flag) break;
-        bar_expect_tx(full(s), (groups.a_box_bytes ? groups.a_box_bytes : TILE_A_BYTES) + (FUSE ? 2 : 1) * TILE_B_BYTES);
-        tma_load_2d(base + s * STAGE_BYTES, &map_a, (kb0 + kb) * BK, m0, full(s));
-        tma_load_2d(base + s * STAGE_BYTES + TILE_A_BYTES, map_b, (kb0 + kb) * BK, n0, full(s));
-        if (FUSE) tma_load_2d(base + s * STAGE_BYTES + TILE_A_BYTES + TILE_B_BYTES, &map_b1, (kb0 + kb) * BK, n0, full(s));
+        bar_expect_tx(landed(s), stage_tx);
+        tma_load_2d(base + s * STAGE_BYTES, &map_a, (kb0 + kb) * BK, m0, landed(s));
+        tma_load_2d(base + s * STAGE_BYTES + b_dst, map_b, (kb0 + kb) * kcol, n0, landed(s));
+        if (FUSE) tma_load_2d(base + s * STAGE_BYTES + b_dst + b_dst_step, &map_b1, (kb0 + kb) * kcol, n0, landed(s));
         issued = kb + 1;
       }
       // after an abort the copies already issued must land before the CTA can exit
       if (*abort_flag) {
         for (int kb = (issued > STAGES ? issued - STAGES : 0); kb < issued; ++kb) {
           const unsigned long long t0 = gtime();
-          while (!bar_try(full(kb % STAGES), (kb / STAGES) & 1)) {
+          while (!bar_try(landed(kb % STAGES), (kb / STAGES) & 1)) {
             if (gtime() - t0 > (budget_ns > 2000000ull ? budget_ns : 2000000ull)) break;   // landing takes microseconds
           }
         }
@@ -236,6 +322,55 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     }
   } else {                                 // ---- epilogue: warps 2..5 own TMEM lanes 32 * (warp % 4) ..
     const int quarter = warp & 3;
+    if (WQ) {
+      // ---- expansion of the packed K blocks (these warps have nothing else to do until the accumulator is done)
+      // Each of the four warps expands every fourth K block on its own: the chain wait -> load -> convert -> store ->
+      // fence -> arrive is latency, not throughput, so four chains in flight finish a K loop four times sooner than
+      // four warps sharing every block.
+      bool live = !selftest_no_loads;
+      for (int kb = quarter; kb < kblocks && live; kb += 4) {
+        const int s = kb % STAGES;
+        live = __all_sync(0xffffffffu, bar_wait(raw_full(s), (kb / STAGES) & 1, abort_flag, status, budget_ns));
+        if (!live) break;
+        const uint32_t btile = base + s * STAGE_BYTES + TILE_A_BYTES;
+        const uint32_t rawt = base + s * STAGE_BYTES + b_dst;
+        // one 16-value chunk per lane and pass: chunk i = row * 4 + quarter of the 64-wide K block; the packed
+        // rows are dense, so consecutive lanes read consecutive bytes
+#pragma unroll 4
+        for (int i = lane; i < SB * 4; i += 32) {
+          const int r = i >> 2, c = i & 3;
+          uint32_t h[8];
+          if (WQ == 1) {
+            uint32_t v0, v1, v2, v3;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(rawt + i * 16));
+            h[0] = e4m3x2_to_half2_bits(v0); h[1] = e4m3x2_to_half2_bits(v0 >> 16);
+            h[2] = e4m3x2_to_half2_bits(v1); h[3] = e4m3x2_to_half2_bits(v1 >> 16);
+            h[4] = e4m3x2_to_half2_bits(v2); h[5] = e4m3x2_to_half2_bits(v2 >> 16);
+            h[6] = e4m3x2_to_half2_bits(v3); h[7] = e4m3x2_to_half2_bits(v3 >> 16);
+          } else {
+            uint32_t v0, v1;
+            asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(v0), "=r"(v1) : "r"(rawt + i * 8));
+            const uint32_t sb2 = e4m3x2_to_half2_bits(s_bs[r * BS_PITCH + 4 * kb + c]);   // low half = the block's scale
+            const __half2 sc = __half2half2(__ushort_as_half(static_cast<unsigned short>(sb2 & 0xFFFFu)));
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const __half2 a = __hmul2(e2m1x2_to_half2((v0 >> (8 * j)) & 0xFFu), sc);
+              const __half2 b = __hmul2(e2m1x2_to_half2((v1 >> (8 * j)) & 0xFFu), sc);
+              h[j] = *reinterpret_cast<const uint32_t *>(&a);
+              h[4 + j] = *reinterpret_cast<const uint32_t *>(&b);
+            }
+          }
+          // 128-byte swizzle of the MMA tile: 16-byte segment index XOR (row mod 8)
+          const uint32_t rowaddr = btile + static_cast<uint32_t>(r) * 128u;
+          const uint32_t x = static_cast<uint32_t>(r & 7);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + (((2u * c) ^ x) << 4)), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + (((2u * c + 1u) ^ x) << 4)), "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes before the MMA's async-proxy reads
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(full(s)) : "memory");
+      }
+    }
     // warp-uniform outcome: the TMEM loads below are warp-wide instructions
     const bool ok = __all_sync(0xffffffffu, bar_wait(acc_full, 0, abort_flag, status, budget_ns));
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -265,9 +400,13 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           uint32_t packed[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const float g0 = __uint_as_float(g[2 * i]), g1 = __uint_as_float(g[2 * i + 1]);
-            const __half2 h = __floats2half2_rn(g0 / (1.0f + expf(-g0)) * __uint_as_float(u[2 * i]),
-                                                g1 / (1.0f + expf(-g1)) * __uint_as_float(u[2 * i + 1]));
+            float g0 = __uint_as_float(g[2 * i]), g1 = __uint_as_float(g[2 * i + 1]);
+            float u0 = __uint_as_float(u[2 * i]), u1 = __uint_as_float(u[2 * i + 1]);
+            if (WQ) {
+              g0 *= s_rowscale[c * 16 + 2 * i]; g1 *= s_rowscale[c * 16 + 2 * i + 1];
+              u0 *= s_rowscale[BN + c * 16 + 2 * i]; u1 *= s_rowscale[BN + c * 16 + 2 * i + 1];
+            }
+            const __half2 h = __floats2half2_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
             packed[i] = *reinterpret_cast<const uint32_t *>(&h);
           }
           *reinterpret_cast<uint4 *>(arow + c * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
@@ -294,10 +433,15 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (row < M) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            *reinterpret_cast<float4 *>(crow + c * 32 + i) =
-                make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
-                            __uint_as_float(r[i + 3]));
+          for (int i = 0; i < 32; i += 4) {
+            float4 o = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
+                                   __uint_as_float(r[i + 3]));
+            if (WQ) {
+              const float *sc = s_rowscale + c * 32 + i;
+              o.x *= sc[0]; o.y *= sc[1]; o.z *= sc[2]; o.w *= sc[3];
+            }
+            *reinterpret_cast<float4 *>(crow + c * 32 + i) = o;
+          }
         }
       }
     }

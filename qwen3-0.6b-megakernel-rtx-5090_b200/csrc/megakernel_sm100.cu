@@ -204,6 +204,7 @@ struct Engine {
   // fused single-sequence kernel (megakernel_fused.cuh)
   int fused = 2;             // 0: always the unfused kernel; 1: fused, CUDA-core row products; 2: fused, tensor-core row products (fp16 weights)
   int red_copies = 1;
+  int step_overlap = 1;      // batched decode: kernels of a step launched as programmatic dependents of one another
   int fused_sleep_ns = 0;    // measured at 4096-token context: 600 ns 1224 tok/s, 200 ns 1259, 0 ns 1305 (few pollers per word)
   unsigned long long *red = nullptr;   // the two residual sums
   struct Prepared {          // K-major copies of W_o / W_down of one caller table
@@ -428,6 +429,9 @@ int launch(Engine *e, Params &P, cudaStream_t stream, bool synchronize, bool bat
   }
   if (e->rope_from_table && (!P.cos_table || !P.sin_table))
     return fail(e, QMK_ERR_BAD_ARGUMENT, "rope_from_table needs cos/sin tables");
+  if (e->wfmt == 2)
+    return fail(e, QMK_ERR_BAD_ARGUMENT,
+                "NVFP4 rows are read by the tensor-core entry points only (qmk_prefill_chunked, qmk_decode_batched)");
   int rc = ensure_ready(e);
   if (rc != QMK_OK) return rc;
 
@@ -544,6 +548,7 @@ int prefill_env(int max_seq_len, cudaStream_t stream, PrefillEnv *out) {
   out->wfmt = e->wfmt;
   out->rope_from_table = e->rope_from_table;
   out->logits_out = e->logits_out;
+  out->pdl = e->step_overlap;
   return QMK_OK;
 }
 int report(int code, const std::string &msg) {
@@ -596,8 +601,17 @@ int qmk_set_weight_format(int format) {
   std::lock_guard<std::mutex> lock(g_mutex);
   Engine *e = current_engine_unlocked();
   if (!e) return QMK_ERR_CUDA;
-  if (format != 0 && format != 1) return fail(e, QMK_ERR_BAD_ARGUMENT, "weight format must be 0 (fp16) or 1 (fp8-e4m3 rows)");
+  if (format < 0 || format > 2)
+    return fail(e, QMK_ERR_BAD_ARGUMENT, "weight format must be 0 (fp16), 1 (fp8-e4m3 rows) or 2 (nvfp4 rows)");
   e->wfmt = format;
+  return QMK_OK;
+}
+
+int qmk_set_step_overlap(int enabled) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  Engine *e = current_engine_unlocked();
+  if (!e) return QMK_ERR_CUDA;
+  if (enabled >= 0) e->step_overlap = enabled ? 1 : 0;
   return QMK_OK;
 }
 
@@ -835,7 +849,7 @@ int apply_handle_unlocked(qmk_engine *h, const void *table) {
   if (c.split_len > 0) e->split_len = c.split_len;      // speed / debugging knobs: non-positive leaves qmk_configure's value
   if (c.max_ctas > 0) e->max_ctas = c.max_ctas;
   if (c.timeout_ms > 0) e->timeout_ms = c.timeout_ms;
-  e->wfmt = c.weight_format ? 1 : 0;
+  e->wfmt = c.weight_format;
   if (c.fused >= 0) e->fused = c.fused;   // a speed knob, not a property of the weights: negative leaves qmk_set_fused's value
   if ((!e->inv_freq_set || memcmp(e->inv_freq, h->inv_freq, sizeof(h->inv_freq)) != 0)) {
     QMK_CUDA(e, cudaDeviceSynchronize());   // no launch may still be reading the old table
@@ -866,7 +880,7 @@ int qmk_prefill(const int *token_ids_host, int num_tokens, const void *embed_wei
 
 int qmk_engine_create(const qmk_engine_config *config, qmk_engine **out) {
   if (!config || !out) return QMK_ERR_BAD_ARGUMENT;
-  if (config->weight_format != 0 && config->weight_format != 1) return QMK_ERR_BAD_ARGUMENT;
+  if (config->weight_format < 0 || config->weight_format > 2) return QMK_ERR_BAD_ARGUMENT;
   if (config->fused > 2 || (config->max_ctas > 0 && config->max_ctas < qmk::NKV)) return QMK_ERR_BAD_ARGUMENT;
   int ndev = 0;
   if (cudaGetDeviceCount(&ndev) != cudaSuccess || config->device < 0 || config->device >= ndev || config->device >= MAX_DEVICES)
@@ -1045,6 +1059,7 @@ int qmk_generate_static(int first_token_id, int num_steps, const void *embed_wei
   if (num_steps <= 0) return QMK_OK;
   if (!output_log || !embed_weight || !layer_weights || !final_norm_weight || !lm_head_weight || !k_cache || !v_cache)
     return fail(e, QMK_ERR_BAD_ARGUMENT, "qmk_generate_static: null pointer argument");
+  if (e->wfmt == 2) return fail(e, QMK_ERR_BAD_ARGUMENT, "qmk_generate_static reads fp16 or FP8-E4M3 rows, not NVFP4");
   if (!aligned16(embed_weight) || !aligned16(layer_weights) || !aligned16(lm_head_weight) || !aligned16(k_cache) ||
       !aligned16(v_cache))
     return fail(e, QMK_ERR_BAD_ARGUMENT, "weight, cache and layer-table pointers must be 16-byte aligned");

@@ -6,10 +6,20 @@
 #define QMK_PREFILL_KERNELS_CUH_
 
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 namespace qmk_pf {
+
+// Programmatic dependent launch: the kernels of a decode step are launched with the stream-serialisation attribute,
+// so kernel n + 1 may be scheduled as soon as every CTA of kernel n has executed pdl_trigger(); pdl_wait() then blocks
+// until kernel n has COMPLETED and its writes are visible.  Whatever a kernel does before pdl_wait() - barrier and
+// TMEM set-up, tensor-map prefetch, streaming weights or cache rows no kernel of the step writes - overlaps the tail
+// of its predecessor.  Every kernel of the chain waits before its first dependent read and before any global write,
+// so completion of kernel n implies completion of all earlier ones.  Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 constexpr int H = 1024, I = 3072, NQ = 16, NKV = 8, D = 128, QS = NQ * D, KVS = NKV * D;
 constexpr float RMS_EPS = 1e-6f;
@@ -25,11 +35,34 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
-// x[t][:] = embedding row of token t (fp16 -> fp32).  grid = T, block = 256.
-__global__ void embed_rows(const int *tokens, const __half *embed, float *x) {
+// x[t][:] = embedding row of token t as fp32.  grid = T, block = 256.  `wq`: 0 fp16 rows; 1 FP8-E4M3 rows (H bytes,
+// then a 16-byte trailer with the fp32 row scale); 2 NVFP4 rows (H / 2 bytes of e2m1 pairs, low nibble first, H / 16
+// e4m3 block scales, then the trailer with the fp32 tensor scale).
+__global__ void embed_rows(const int *tokens, const void *embed, int wq, float *x) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
-  const __half *row = embed + static_cast<size_t>(tokens[t]) * H;
-  for (int k = threadIdx.x; k < H; k += blockDim.x) x[static_cast<size_t>(t) * H + k] = __half2float(row[k]);
+  float *out = x + static_cast<size_t>(t) * H;
+  if (wq == 0) {
+    const __half *row = static_cast<const __half *>(embed) + static_cast<size_t>(tokens[t]) * H;
+    for (int k = threadIdx.x; k < H; k += blockDim.x) out[k] = __half2float(row[k]);
+  } else if (wq == 1) {
+    const unsigned char *row = static_cast<const unsigned char *>(embed) + static_cast<size_t>(tokens[t]) * (H + 16);
+    const float scale = *reinterpret_cast<const float *>(row + H);
+    for (int k = threadIdx.x; k < H; k += blockDim.x)
+      out[k] = scale * __half2float(__half(__nv_cvt_fp8_to_halfraw(row[k], __NV_E4M3)));
+  } else {
+    constexpr int PITCH = H / 2 + H / 16 + 16;
+    const unsigned char *row = static_cast<const unsigned char *>(embed) + static_cast<size_t>(tokens[t]) * PITCH;
+    const float scale = *reinterpret_cast<const float *>(row + H / 2 + H / 16);
+    for (int k = threadIdx.x; k < H; k += blockDim.x) {
+      const unsigned int code = (row[k >> 1] >> ((k & 1) * 4)) & 0xFu;
+      const unsigned int m = code & 7u;
+      const float mag = m < 2u ? 0.5f * static_cast<float>(m) : static_cast<float>(2u + (m & 1u)) * static_cast<float>(1u << ((m >> 1) - 1u)) * 0.5f;
+      const float bs = __half2float(__half(__nv_cvt_fp8_to_halfraw(row[H / 2 + (k >> 4)], __NV_E4M3)));
+      out[k] = scale * bs * ((code & 8u) ? -mag : mag);
+    }
+  }
 }
 
 // Residual add + RMSNorm: x[t] += add[t] (if add), y[t] = fp16(x[t] * rstd * w).  grid = T, block = 256.
@@ -37,6 +70,8 @@ __global__ void embed_rows(const int *tokens, const __half *embed, float *x) {
 // added in index order.
 __global__ void add_rmsnorm_rows(float *x, const float *add, int nparts, size_t part_stride, const __half *w, __half *y) {
   __shared__ float red[8];
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   float *xr = x + static_cast<size_t>(t) * H;
   float v[4];
@@ -335,6 +370,7 @@ __global__ void __launch_bounds__((DAR_WARPS + 1) * 32) decode_attention_ring(
   extern __shared__ __align__(128) unsigned char dar_smem[];
   __shared__ __align__(16) float sq[2 * D];
   __shared__ float sknew[D], svnew[D], snew_score[2];
+  pdl_trigger();
   __shared__ float sm[DAR_WARPS][2], sl[DAR_WARPS][2];
   __shared__ __align__(16) float sacc[DAR_WARPS][2][D];
   uint64_t *full = reinterpret_cast<uint64_t *>(dar_smem + DAR_SLOTS * DAR_SLOT_BYTES);
@@ -391,6 +427,9 @@ __global__ void __launch_bounds__((DAR_WARPS + 1) * 32) decode_attention_ring(
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  // The producer streams cache rows written by EARLIER steps, so it starts at once; everyone else reads what the
+  // q/k/v GEMM launched just before wrote, and writes (cache row, output, split partials) only after it completed.
+  if (warp != DAR_WARPS) pdl_wait();
   if (warp == DAR_WARPS) {            // ---- producer: old rows [0, pos) in chunks of 32
     if (lane == 0) {
       int issued = 0;
@@ -606,6 +645,8 @@ __global__ void __launch_bounds__(1024) argmax_rows(const float *logits, int voc
                                                     const int *start_positions, int *positions) {
   __shared__ float sv[32];
   __shared__ int si[32];
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.x;
   const float *row = logits + static_cast<size_t>(b) * vocab;
   float best = -INFINITY;

@@ -58,6 +58,41 @@ int make_map_f16(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t cols
   return QMK_OK;
 }
 
+// Packed weight rows (weight formats 1 and 2): bytes of values, where the NVFP4 block scales and the 16-byte trailer
+// with the fp32 scale sit inside a row, and the bytes between rows.
+PackedRow packed_row(int wq, int K) {
+  PackedRow r;
+  r.data_bytes = wq == 1 ? static_cast<uint32_t>(K) : static_cast<uint32_t>(K) / 2;
+  r.bs_off = r.data_bytes;
+  r.scale_off = wq == 1 ? r.data_bytes : r.data_bytes + static_cast<uint32_t>(K) / 16;
+  r.pitch = r.scale_off + 16;
+  return r;
+}
+
+// Tensor map of the VALUES of a packed matrix (bytes; scales and trailers stay outside the mapped extent): boxes of
+// box_rows rows x one 64-value K block, no swizzle - the expanding warps read it linearly.
+int make_map_packed(CUtensorMap *map, const void *ptr, uint64_t rows, int K, uint32_t box_rows, int wq, std::string *err) {
+  EncodeTiledFn enc = encoder();
+  if (!enc) { *err = "cuTensorMapEncodeTiled is not available from this driver"; return QMK_ERR_CUDA; }
+  const PackedRow pr = packed_row(wq, K);
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15u) || K % 64 || K > qmk_gemm::MAX_K_PACKED || pr.pitch % 16) {
+    *err = "packed matrix: base not 16-byte aligned, or K not a multiple of 64 (NVFP4: of 256, rows must stay 16-byte aligned) up to 3072";
+    return QMK_ERR_BAD_ARGUMENT;
+  }
+  const cuuint64_t dims[2] = {pr.data_bytes, rows};
+  const cuuint64_t strides[1] = {pr.pitch};
+  const cuuint32_t box[2] = {qmk_gemm::raw_row_bytes(wq), box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { *err = "cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)); return QMK_ERR_CUDA; }
+  return QMK_OK;
+}
+int make_map_b(CUtensorMap *map, const void *ptr, uint64_t rows, int K, uint32_t box_rows, int wq, std::string *err) {
+  return wq ? make_map_packed(map, ptr, rows, K, box_rows, wq, err) : make_map_f16(map, ptr, rows, static_cast<uint64_t>(K), box_rows, err);
+}
+
 // Width of the N tiles for C[M x N] = A[M x K] * B[N x K]^T (M, N multiples of 128).  `map_b` must have been made
 // with that many rows per box.  Skinny problems are bound by how many SMs pull operands at once and by the fixed
 // cost of a CTA (launch, barrier and TMEM set-up, pipeline fill, epilogue - worth about 320 columns of streaming in
@@ -87,26 +122,39 @@ static int pick_box_n(int M, int N, int b_tiles) {
 int gemm_box_n(int M, int N) { return pick_box_n(M, N, 1); }
 int gemm_box_n_fused(int M, int N) { return pick_box_n(M, N, 2); }
 
+// Launches of a decode step carry the programmatic-stream-serialisation attribute (see pdl_wait in
+// prefill_kernels.cuh); the step builder switches it on for the calling thread, everything else launches plainly.
+thread_local bool t_pdl = false;
+PdlScope::PdlScope(bool on) : prev_(t_pdl) { t_pdl = on; }
+PdlScope::~PdlScope() { t_pdl = prev_; }
+bool pdl_active() { return t_pdl; }
+
+// The kernel for an N tile, epilogue and weight format, and its dynamic shared memory.
+using GemmKernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const qmk_gemm::Groups,
+                            int, int, unsigned int *, unsigned long long, int);
+template <int WQ>
+static GemmKernel gemm_kernel_wq(int bn, bool fuse) {
+  if (fuse) return bn == 32 ? qmk_gemm::gemm_f16_tn_kernel<32, true, WQ> : qmk_gemm::gemm_f16_tn_kernel<64, true, WQ>;
+  return bn == 32 ? qmk_gemm::gemm_f16_tn_kernel<32, false, WQ>
+                  : bn == 64 ? qmk_gemm::gemm_f16_tn_kernel<64, false, WQ> : qmk_gemm::gemm_f16_tn_kernel<128, false, WQ>;
+}
+static GemmKernel gemm_kernel(int bn, bool fuse, int wq) {
+  return wq == 0 ? gemm_kernel_wq<0>(bn, fuse) : wq == 1 ? gemm_kernel_wq<1>(bn, fuse) : gemm_kernel_wq<2>(bn, fuse);
+}
+static size_t gemm_smem(int bn, bool fuse, int wq) { return qmk_gemm::smem_bytes_for(fuse ? 2 * bn : bn, wq); }
+
 // Opt-in shared-memory size of every tile variant, once per device (outside any stream capture).
 int ensure_gemm_attrs(std::string *err) {
   int dev = 0;
   cudaGetDevice(&dev);
   std::lock_guard<std::mutex> lock(g_mu);
   if (dev >= 0 && dev < 16 && !g_attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(qmk_gemm::gemm_f16_tn_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(qmk_gemm::smem_bytes_for(128)));
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(qmk_gemm::gemm_f16_tn_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(qmk_gemm::smem_bytes_for(64)));
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(qmk_gemm::gemm_f16_tn_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(qmk_gemm::smem_bytes_for(128)));
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(qmk_gemm::gemm_f16_tn_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(qmk_gemm::smem_bytes_for(32)));
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(qmk_gemm::gemm_f16_tn_kernel<32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(qmk_gemm::smem_bytes_for(64)));
+    cudaError_t e = cudaSuccess;
+    for (int wq = 0; wq < 3 && e == cudaSuccess; ++wq)
+      for (int fuse = 0; fuse < 2 && e == cudaSuccess; ++fuse)
+        for (int bn = 32; bn <= (fuse ? 64 : 128) && e == cudaSuccess; bn *= 2)
+          e = cudaFuncSetAttribute(reinterpret_cast<const void *>(gemm_kernel(bn, fuse != 0, wq)),
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(gemm_smem(bn, fuse != 0, wq)));
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(qmk_pf::causal_attention_mma, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                qmk_pf::ATM_SMEM_BYTES);
@@ -117,6 +165,23 @@ int ensure_gemm_attrs(std::string *err) {
     g_attr_set[dev] = true;
   }
   return QMK_OK;
+}
+
+// Packed-weight fields of a launch: row geometry for K and the groups' base pointers.
+static bool set_packed(qmk_gemm::Groups *gr, int wq, int K, int ngroups, const void *const *raws, std::string *err) {
+  for (int g = 0; g < qmk_gemm::MAX_GROUPS; ++g) gr->braw[g] = nullptr;
+  gr->raw_pitch = gr->raw_bs_off = gr->raw_scale_off = 0;
+  if (wq == 0) return true;
+  if (wq < 0 || wq > 2 || !raws || K > qmk_gemm::MAX_K_PACKED) { *err = "gemm: bad packed-weight arguments"; return false; }
+  const PackedRow pr = packed_row(wq, K);
+  gr->raw_pitch = pr.pitch;
+  gr->raw_bs_off = pr.bs_off;
+  gr->raw_scale_off = pr.scale_off;
+  for (int g = 0; g < ngroups; ++g) {
+    if (!raws[g]) { *err = "gemm: null packed matrix"; return false; }
+    gr->braw[g] = static_cast<const unsigned char *>(raws[g]);
+  }
+  return true;
 }
 
 // A maps with short boxes (`a_box_rows` < 128 rows per box, a multiple of 8; decode steps with few live rows): one
@@ -134,7 +199,7 @@ static bool a_box_ok(int a_box_rows, int M, int *rows, uint32_t *a_box_bytes, st
 // 128; K a multiple of 64; every B map made with `box_n` rows per box (gemm_box_n(M, sum of N_g)).
 int launch_gemm_grouped(const CUtensorMap &map_a, int ngroups, const CUtensorMap *const *maps_b, float *const *Cs,
                         const int *Ns, int M, int K, int box_n, unsigned int *status, int timeout_ms, cudaStream_t stream,
-                        std::string *err, int live_rows, int a_box_rows) {
+                        std::string *err, int live_rows, int a_box_rows, int wq, const void *const *raws) {
   bool bad = M <= 0 || K <= 0 || M % qmk_gemm::BM || K % qmk_gemm::BK || (box_n != 32 && box_n != 64 && box_n != 128) ||
              ngroups < 1 || ngroups > qmk_gemm::MAX_GROUPS;
   for (int g = 0; !bad && g < ngroups; ++g) bad = Ns[g] <= 0 || Ns[g] % 128;
@@ -147,6 +212,7 @@ int launch_gemm_grouped(const CUtensorMap &map_a, int ngroups, const CUtensorMap
   qmk_gemm::Groups gr;
   gr.kblocks_per_split = 0;
   gr.split_stride = 0;
+  if (!set_packed(&gr, wq, K, ngroups, raws, err)) return QMK_ERR_BAD_ARGUMENT;
   int tiles = 0;
   for (int g = 0; g < qmk_gemm::MAX_GROUPS; ++g) {
     gr.C[g] = g < ngroups ? Cs[g] : nullptr;
@@ -158,16 +224,8 @@ int launch_gemm_grouped(const CUtensorMap &map_a, int ngroups, const CUtensorMap
   const unsigned long long budget = static_cast<unsigned long long>(timeout_ms) * 1000000ull;
   int rows = live_rows > 0 ? live_rows : M;   // rows the epilogue stores (the rest of the tile is padding)
   if (!a_box_ok(a_box_rows, M, &rows, &gr.a_box_bytes, err)) return QMK_ERR_BAD_ARGUMENT;
-  if (box_n == 32)
-    qmk_gemm::gemm_f16_tn_kernel<32><<<grid, qmk_gemm::THREADS, qmk_gemm::smem_bytes_for(32), stream>>>(
-        map_a, b0, b1, b2, gr, rows, K, status, budget, 0);
-  else if (box_n == 64)
-    qmk_gemm::gemm_f16_tn_kernel<64><<<grid, qmk_gemm::THREADS, qmk_gemm::smem_bytes_for(64), stream>>>(
-        map_a, b0, b1, b2, gr, rows, K, status, budget, 0);
-  else
-    qmk_gemm::gemm_f16_tn_kernel<128><<<grid, qmk_gemm::THREADS, qmk_gemm::smem_bytes_for(128), stream>>>(
-        map_a, b0, b1, b2, gr, rows, K, status, budget, 0);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_kernel(gemm_kernel(box_n, false, wq), grid, dim3(qmk_gemm::THREADS), gemm_smem(box_n, false, wq), stream,
+                                map_a, b0, b1, b2, gr, rows, K, status, budget, 0);
   if (e != cudaSuccess) { *err = std::string("gemm launch: ") + cudaGetErrorString(e); return QMK_ERR_CUDA; }
   return QMK_OK;
 }
@@ -176,7 +234,7 @@ int launch_gemm_grouped(const CUtensorMap &map_a, int ngroups, const CUtensorMap
 // Both maps made with `box_n` (64 or 32) rows per box.
 int launch_gemm_swiglu(const CUtensorMap &map_a, const CUtensorMap &map_gate, const CUtensorMap &map_up, __half *act, int M,
                        int N, int K, unsigned int *status, int timeout_ms, cudaStream_t stream, std::string *err,
-                       int box_n, int live_rows, int a_box_rows) {
+                       int box_n, int live_rows, int a_box_rows, int wq, const void *raw_gate, const void *raw_up) {
   if (M <= 0 || N <= 0 || K <= 0 || M % qmk_gemm::BM || N % 128 || K % qmk_gemm::BK || (box_n != 32 && box_n != 64)) {
     *err = "gemm: M and N must be multiples of 128 and K a multiple of 64";
     return QMK_ERR_BAD_ARGUMENT;
@@ -188,16 +246,13 @@ int launch_gemm_swiglu(const CUtensorMap &map_a, const CUtensorMap &map_gate, co
   gr.N[0] = N; gr.N[1] = 0; gr.N[2] = 0;
   gr.kblocks_per_split = 0;
   gr.split_stride = 0;
+  const void *raws[2] = {raw_gate, raw_up};
+  if (!set_packed(&gr, wq, K, 2, raws, err)) return QMK_ERR_BAD_ARGUMENT;
   int rows = live_rows > 0 ? live_rows : M;
   if (!a_box_ok(a_box_rows, M, &rows, &gr.a_box_bytes, err)) return QMK_ERR_BAD_ARGUMENT;
   const unsigned long long budget = static_cast<unsigned long long>(timeout_ms) * 1000000ull;
-  if (box_n == 32)
-    qmk_gemm::gemm_f16_tn_kernel<32, true><<<dim3(N / 32, M / qmk_gemm::BM), qmk_gemm::THREADS, qmk_gemm::smem_bytes_for(64),
-                                             stream>>>(map_a, map_gate, map_up, map_up, gr, rows, K, status, budget, 0);
-  else
-    qmk_gemm::gemm_f16_tn_kernel<64, true><<<dim3(N / 64, M / qmk_gemm::BM), qmk_gemm::THREADS, qmk_gemm::smem_bytes_for(128),
-                                             stream>>>(map_a, map_gate, map_up, map_up, gr, rows, K, status, budget, 0);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_kernel(gemm_kernel(box_n, true, wq), dim3(N / box_n, M / qmk_gemm::BM), dim3(qmk_gemm::THREADS),
+                                gemm_smem(box_n, true, wq), stream, map_a, map_gate, map_up, map_up, gr, rows, K, status, budget, 0);
   if (e != cudaSuccess) { *err = std::string("gemm launch: ") + cudaGetErrorString(e); return QMK_ERR_CUDA; }
   return QMK_OK;
 }
@@ -206,7 +261,7 @@ int launch_gemm_swiglu(const CUtensorMap &map_a, const CUtensorMap &map_gate, co
 // C + z * M * N.  K / 64 must be a multiple of `splits`.  `map_b` made with `box_n` (64 or 32) rows per box.
 int launch_gemm_splitk(const CUtensorMap &map_a, const CUtensorMap &map_b, float *C, int M, int N, int K, int splits,
                        unsigned int *status, int timeout_ms, cudaStream_t stream, std::string *err, int box_n,
-                       int live_rows, int a_box_rows) {
+                       int live_rows, int a_box_rows, int wq, const void *raw) {
   if (M <= 0 || N <= 0 || K <= 0 || M % qmk_gemm::BM || N % 128 || K % qmk_gemm::BK || splits < 1 ||
       (K / qmk_gemm::BK) % splits || (box_n != 32 && box_n != 64)) {
     *err = "gemm: bad split-K shape";
@@ -219,26 +274,24 @@ int launch_gemm_splitk(const CUtensorMap &map_a, const CUtensorMap &map_b, float
   gr.N[0] = N; gr.N[1] = 0; gr.N[2] = 0;
   gr.kblocks_per_split = K / qmk_gemm::BK / splits;
   gr.split_stride = static_cast<size_t>(M) * N;
+  if (!set_packed(&gr, wq, K, 1, &raw, err)) return QMK_ERR_BAD_ARGUMENT;
   int rows = live_rows > 0 ? live_rows : M;
   if (!a_box_ok(a_box_rows, M, &rows, &gr.a_box_bytes, err)) return QMK_ERR_BAD_ARGUMENT;
   const unsigned long long budget = static_cast<unsigned long long>(timeout_ms) * 1000000ull;
-  if (box_n == 32)
-    qmk_gemm::gemm_f16_tn_kernel<32><<<dim3(N / 32, M / qmk_gemm::BM, splits), qmk_gemm::THREADS, qmk_gemm::smem_bytes_for(32),
-                                       stream>>>(map_a, map_b, map_b, map_b, gr, rows, K, status, budget, 0);
-  else
-    qmk_gemm::gemm_f16_tn_kernel<64><<<dim3(N / 64, M / qmk_gemm::BM, splits), qmk_gemm::THREADS, qmk_gemm::smem_bytes_for(64),
-                                       stream>>>(map_a, map_b, map_b, map_b, gr, rows, K, status, budget, 0);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_kernel(gemm_kernel(box_n, false, wq), dim3(N / box_n, M / qmk_gemm::BM, splits), dim3(qmk_gemm::THREADS),
+                                gemm_smem(box_n, false, wq), stream, map_a, map_b, map_b, map_b, gr, rows, K, status, budget, 0);
   if (e != cudaSuccess) { *err = std::string("gemm launch: ") + cudaGetErrorString(e); return QMK_ERR_CUDA; }
   return QMK_OK;
 }
 
 int launch_gemm(const CUtensorMap &map_a, const CUtensorMap &map_b, float *C, int M, int N, int K, int box_n,
-                unsigned int *status, int timeout_ms, cudaStream_t stream, std::string *err, int live_rows, int a_box_rows) {
+                unsigned int *status, int timeout_ms, cudaStream_t stream, std::string *err, int live_rows, int a_box_rows,
+                int wq, const void *raw) {
   const CUtensorMap *maps[1] = {&map_b};
   float *Cs[1] = {C};
   const int Ns[1] = {N};
-  return launch_gemm_grouped(map_a, 1, maps, Cs, Ns, M, K, box_n, status, timeout_ms, stream, err, live_rows, a_box_rows);
+  return launch_gemm_grouped(map_a, 1, maps, Cs, Ns, M, K, box_n, status, timeout_ms, stream, err, live_rows, a_box_rows, wq,
+                             &raw);
 }
 
 }  // namespace qmk_tc
@@ -272,6 +325,7 @@ struct Workspace {                  // per device, allocated on first use, never
   float *logits = nullptr;
   int logits_vocab = 0;
   const void *lm_ptr = nullptr;
+  int lm_wq = 0;
   CUtensorMap map_lm;
   // A-operand maps that expose only the live rows: the rest of the 128-row box is zero-filled by the TMA unit
   // without being read, which cuts the activation traffic of a small batch by 128 / rows
@@ -280,6 +334,7 @@ struct Workspace {                  // per device, allocated on first use, never
   // weight maps of the layer table seen last (rebuilt when the table's contents change)
   unsigned long long table[MAX_LAYERS * 12] = {};
   int table_layers = 0;
+  int table_wq = 0;                    // weight format the maps below were made for
   CUtensorMap wmap[MAX_LAYERS][7][2];  // q, k, v, o, gate, up, down; boxes of 64 and of 128 rows
   CUtensorMap wmap32[MAX_LAYERS][7];   // the same matrices in boxes of 32 rows (decode steps: more, smaller tiles)
 };
@@ -327,12 +382,12 @@ int ensure_workspace(Workspace &w, int rows) {
 
 // Tensor maps of the seven projection matrices of every layer.  The layer table lives in device memory
 // (the reference's packed pointer records): it is read back and the maps are rebuilt only when it changed.
-int ensure_weight_maps(Workspace &w, const LDGLayerWeight *layers_dev, int num_layers, cudaStream_t stream) {
+int ensure_weight_maps(Workspace &w, const LDGLayerWeight *layers_dev, int num_layers, int wq, cudaStream_t stream) {
   using namespace qmk_pf;
   std::vector<unsigned long long> host(static_cast<size_t>(num_layers) * 12);
   PF_CUDA(cudaMemcpyAsync(host.data(), layers_dev, host.size() * 8, cudaMemcpyDeviceToHost, stream));
   PF_CUDA(cudaStreamSynchronize(stream));
-  if (w.table_layers == num_layers && memcmp(host.data(), w.table, host.size() * 8) == 0) return QMK_OK;
+  if (w.table_layers == num_layers && w.table_wq == wq && memcmp(host.data(), w.table, host.size() * 8) == 0) return QMK_OK;
   // record order: in_ln, wq, wk, wv, q_norm, k_norm, wo, post_ln, gate, up, down, pad
   static const int slot[7] = {1, 2, 3, 6, 8, 9, 10};
   static const int rows[7] = {QS, KVS, KVS, H, I, I, H};
@@ -343,16 +398,17 @@ int ensure_weight_maps(Workspace &w, const LDGLayerWeight *layers_dev, int num_l
       const void *ptr = reinterpret_cast<const void *>(host[static_cast<size_t>(l) * 12 + slot[j]]);
       if (!ptr) return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "prefill: null weight pointer in the layer table");
       {
-        const int rc = qmk_tc::make_map_f16(&w.wmap32[l][j], ptr, rows[j], cols[j], 32, &err);
+        const int rc = qmk_tc::make_map_b(&w.wmap32[l][j], ptr, rows[j], cols[j], 32, wq, &err);
         if (rc != QMK_OK) return qmk_internal::report(rc, err);
       }
       for (int b = 0; b < 2; ++b) {
-        const int rc = qmk_tc::make_map_f16(&w.wmap[l][j][b], ptr, rows[j], cols[j], b ? 128 : 64, &err);
+        const int rc = qmk_tc::make_map_b(&w.wmap[l][j][b], ptr, rows[j], cols[j], b ? 128 : 64, wq, &err);
         if (rc != QMK_OK) return qmk_internal::report(rc, err);
       }
     }
   memcpy(w.table, host.data(), host.size() * 8);
   w.table_layers = num_layers;
+  w.table_wq = wq;
   ++w.graph_epoch;   // captured decode steps hold the old maps
   return QMK_OK;
 }
@@ -370,8 +426,7 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
   if (rc != QMK_OK) return rc;
   if (!token_ids_host || !embed_weight || !layer_weights || !k_cache || !v_cache)
     return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "prefill: null pointer argument");
-  if (env.wfmt != 0)
-    return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "qmk_prefill_chunked handles fp16 weights only; use qmk_prefill");
+  const int wq = env.wfmt;   // 0 fp16, 1 FP8-E4M3 rows, 2 NVFP4 rows: packed matrices are expanded inside the GEMM
   if (num_layers < 1 || num_layers > MAX_LAYERS)
     return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "num_layers must be in [1, 48]");
   if (start_position < 0 || start_position + num_tokens > max_seq_len)
@@ -387,7 +442,7 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
   std::lock_guard<std::mutex> lock(g_ws_mu);
   Workspace &w = g_ws[dev];
   rc = ensure_workspace(w, CHUNK);
-  if (rc == QMK_OK) rc = ensure_weight_maps(w, layer_weights, num_layers, stream);
+  if (rc == QMK_OK) rc = ensure_weight_maps(w, layer_weights, num_layers, wq, stream);
   if (rc != QMK_OK) return rc;
   std::vector<unsigned long long> rec(w.table, w.table + static_cast<size_t>(num_layers) * 12);
   const float *rope = env.rope_from_table ? nullptr : env.rope;
@@ -399,9 +454,12 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
   auto wmap_for = [&](int l, int j, int box_n) -> const CUtensorMap & {
     return box_n == 32 ? w.wmap32[l][j] : w.wmap[l][j][box_n == 128];
   };
+  static const int rec_slot[7] = {1, 2, 3, 6, 8, 9, 10};   // q, k, v, o, gate, up, down inside a layer record
+  auto wptr = [&](int l, int j) { return reinterpret_cast<const void *>(rec[static_cast<size_t>(l) * 12 + rec_slot[j]]); };
   auto gemm = [&](const CUtensorMap &a, int l, int j, float *c, int M, int N, int K, int live) {
     const int box_n = qmk_tc::gemm_box_n(M, N);
-    return qmk_tc::launch_gemm(a, wmap_for(l, j, box_n), c, M, N, K, box_n, w.status, env.timeout_ms, stream, &err, live);
+    return qmk_tc::launch_gemm(a, wmap_for(l, j, box_n), c, M, N, K, box_n, w.status, env.timeout_ms, stream, &err, live, 0,
+                               wq, wptr(l, j));
   };
   // several matrices against the same activations in one launch (q/k/v)
   auto gemm_group = [&](const CUtensorMap &a, int l, int n, const int *js, float *const *cs, const int *ns, int M, int K,
@@ -410,15 +468,17 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
     for (int i = 0; i < n; ++i) total += ns[i];
     const int box_n = qmk_tc::gemm_box_n(M, total);
     const CUtensorMap *maps[3];
-    for (int i = 0; i < n; ++i) maps[i] = &wmap_for(l, js[i], box_n);
-    return qmk_tc::launch_gemm_grouped(a, n, maps, cs, ns, M, K, box_n, w.status, env.timeout_ms, stream, &err, live);
+    const void *raws[3] = {nullptr, nullptr, nullptr};
+    for (int i = 0; i < n; ++i) { maps[i] = &wmap_for(l, js[i], box_n); raws[i] = wptr(l, js[i]); }
+    return qmk_tc::launch_gemm_grouped(a, n, maps, cs, ns, M, K, box_n, w.status, env.timeout_ms, stream, &err, live, 0, wq,
+                                       raws);
   };
   for (int c0 = 0; c0 < num_tokens; c0 += CHUNK) {
     const int T = (num_tokens - c0 < CHUNK) ? num_tokens - c0 : CHUNK;
     const int M = (T + qmk_gemm::BM - 1) / qmk_gemm::BM * qmk_gemm::BM;
     const int pos0 = start_position + c0;
     PF_CUDA(cudaMemcpyAsync(w.tokens, token_ids_host + c0, sizeof(int) * T, cudaMemcpyHostToDevice, stream));
-    embed_rows<<<T, 256, 0, stream>>>(w.tokens, static_cast<const __half *>(embed_weight), w.x);
+    embed_rows<<<T, 256, 0, stream>>>(w.tokens, embed_weight, wq, w.x);
     for (int l = 0; l < num_layers; ++l) {
       const unsigned long long *r = rec.data() + static_cast<size_t>(l) * 12;
       __half *kc = static_cast<__half *>(k_cache) + l * layer_stride, *vc = static_cast<__half *>(v_cache) + l * layer_stride;
@@ -440,7 +500,8 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
       {
         const int box_gu = qmk_tc::gemm_box_n_fused(M, I);
         if ((rc = qmk_tc::launch_gemm_swiglu(w.map_xn, wmap_for(l, 4, box_gu), wmap_for(l, 5, box_gu), w.act, M, I, H,
-                                             w.status, env.timeout_ms, stream, &err, box_gu, T)) != QMK_OK)
+                                             w.status, env.timeout_ms, stream, &err, box_gu, T, 0, wq, wptr(l, 4),
+                                             wptr(l, 5))) != QMK_OK)
           break;
       }
       if ((rc = gemm(w.map_act, l, 6, w.down, M, H, I, T)) != QMK_OK) break;
@@ -468,7 +529,7 @@ unsigned int __float_as_uint_host(float f) {
 constexpr int MAX_BATCH = 128;      // one 128-row GEMM tile of sequences
 
 constexpr int MAX_ATTN_SPLITS = 8;
-int ensure_decode_workspace(Workspace &w, const void *lm_head, int vocab) {
+int ensure_decode_workspace(Workspace &w, const void *lm_head, int vocab, int wq) {
   if (!w.positions) {
     PF_CUDA(cudaMalloc(&w.positions, sizeof(int) * MAX_BATCH));
     PF_CUDA(cudaMalloc(&w.start_positions, sizeof(int) * MAX_BATCH));
@@ -490,11 +551,13 @@ int ensure_decode_workspace(Workspace &w, const void *lm_head, int vocab) {
     w.logits_vocab = vocab;
     w.lm_ptr = nullptr;
   }
-  if (w.lm_ptr != lm_head) {
+  if (w.lm_ptr != lm_head || w.lm_wq != wq) {
     std::string err;
-    const int rc = qmk_tc::make_map_f16(&w.map_lm, lm_head, vocab, qmk_pf::H, 128, &err);
+    const int rc = qmk_tc::make_map_b(&w.map_lm, lm_head, vocab, qmk_pf::H, 128, wq, &err);
     if (rc != QMK_OK) return qmk_internal::report(rc, err);
     w.lm_ptr = lm_head;
+    w.lm_wq = wq;
+    ++w.graph_epoch;
   }
   return QMK_OK;
 }
@@ -516,8 +579,7 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
   if (!first_token_ids || !start_positions || !k_caches || !v_caches || !output_logs || !embed_weight || !layer_weights ||
       !final_norm_weight || !lm_head_weight)
     return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "qmk_decode_batched: null pointer argument");
-  if (env.wfmt != 0)
-    return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "qmk_decode_batched handles fp16 weights only");
+  const int wq = env.wfmt;   // packed FP8 / NVFP4 matrices stay packed in HBM and are expanded inside the GEMMs
   if (env.vocab % 128 != 0)
     return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "qmk_decode_batched needs a vocabulary that is a multiple of 128");
   if (num_layers < 1 || num_layers > MAX_LAYERS)
@@ -542,8 +604,8 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
   std::lock_guard<std::mutex> lock(g_ws_decode_mu);
   Workspace &w = g_ws_decode[dev];
   rc = ensure_workspace(w, 512);   // room for the split-K partial matrices (4 x 128 rows)
-  if (rc == QMK_OK) rc = ensure_weight_maps(w, layer_weights, num_layers, stream);
-  if (rc == QMK_OK) rc = ensure_decode_workspace(w, lm_head_weight, env.vocab);
+  if (rc == QMK_OK) rc = ensure_weight_maps(w, layer_weights, num_layers, wq, stream);
+  if (rc == QMK_OK) rc = ensure_decode_workspace(w, lm_head_weight, env.vocab, wq);
   if (rc != QMK_OK) return rc;
   std::vector<unsigned long long> rec(w.table, w.table + static_cast<size_t>(num_layers) * 12);
   const float *rope = env.rope_from_table ? nullptr : env.rope;
@@ -591,39 +653,51 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
   const size_t PART = static_cast<size_t>(M) * H;
   auto enqueue_step = [&](cudaStream_t s) -> int {
     int r2 = QMK_OK;
-    embed_rows<<<B, 256, 0, s>>>(w.tokens, static_cast<const __half *>(embed_weight), w.x);
+    qmk_tc::PdlScope pdl_scope(env.pdl != 0);   // every launch below may start behind its predecessor's tail
+    {
+      qmk_tc::PdlScope first(false);            // (the first kernel of a step has no predecessor inside the step)
+      PF_CUDA(qmk_tc::launch_kernel(embed_rows, dim3(B), dim3(256), 0, s, w.tokens, embed_weight, wq, w.x));
+    }
     for (int l = 0; l < num_layers; ++l) {
       const unsigned long long *r = rec.data() + static_cast<size_t>(l) * 12;
       const size_t layer_off = l * layer_stride;
       auto wm = [&](int j) -> const CUtensorMap & { return w.wmap32[l][j]; };
-      add_rmsnorm_rows<<<B, 256, 0, s>>>(w.x, l > 0 ? w.down : nullptr, DOWN_SPLITS, PART, reinterpret_cast<const __half *>(r[0]), w.xn);
+      static const int rec_slot[7] = {1, 2, 3, 6, 8, 9, 10};   // q, k, v, o, gate, up, down inside a layer record
+      auto wp = [&](int j) { return reinterpret_cast<const void *>(r[rec_slot[j]]); };
+      PF_CUDA(qmk_tc::launch_kernel(add_rmsnorm_rows, dim3(B), dim3(256), 0, s, w.x, l > 0 ? w.down : nullptr, DOWN_SPLITS, PART,
+                                    reinterpret_cast<const __half *>(r[0]), w.xn));
       {
         const CUtensorMap *maps[3] = {&wm(0), &wm(1), &wm(2)};
         float *const cs[3] = {w.q, w.k, w.v};
         const int ns[3] = {QS, KVS, KVS};
+        const void *raws[3] = {wp(0), wp(1), wp(2)};
         if ((r2 = qmk_tc::launch_gemm_grouped(w.map_xn_b, 3, maps, cs, ns, M, H, TILE_N, w.status, env.timeout_ms, s, &err,
-                                              live, a_box)) != QMK_OK)
+                                              live, a_box, wq, raws)) != QMK_OK)
           return r2;
       }
-      decode_attention_ring<<<dim3(B, NKV, attn_splits), (DAR_WARPS + 1) * 32, DAR_SMEM_BYTES, s>>>(
-          w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]), reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv,
-          w.k_ptrs, w.v_ptrs, layer_off, w.positions, w.attn, max_seq_len, attn_scale, w.status,
-          static_cast<unsigned long long>(env.timeout_ms) * 1000000ull, w.split_part, w.split_count);
+      PF_CUDA(qmk_tc::launch_kernel(decode_attention_ring, dim3(B, NKV, attn_splits), dim3((DAR_WARPS + 1) * 32), DAR_SMEM_BYTES, s,
+                                    w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]), reinterpret_cast<const __half *>(r[5]), rope,
+                                    cosv, sinv, w.k_ptrs, w.v_ptrs, layer_off, w.positions, w.attn, max_seq_len, attn_scale, w.status,
+                                    static_cast<unsigned long long>(env.timeout_ms) * 1000000ull, w.split_part, w.split_count));
       if ((r2 = qmk_tc::launch_gemm_splitk(w.map_attn_b, wm(3), w.o, M, H, QS, O_SPLITS, w.status, env.timeout_ms, s, &err,
-                                           TILE_N, live, a_box)) != QMK_OK)
+                                           TILE_N, live, a_box, wq, wp(3))) != QMK_OK)
         return r2;
-      add_rmsnorm_rows<<<B, 256, 0, s>>>(w.x, w.o, O_SPLITS, PART, reinterpret_cast<const __half *>(r[7]), w.xn);
+      PF_CUDA(qmk_tc::launch_kernel(add_rmsnorm_rows, dim3(B), dim3(256), 0, s, w.x, w.o, O_SPLITS, PART,
+                                    reinterpret_cast<const __half *>(r[7]), w.xn));
       if ((r2 = qmk_tc::launch_gemm_swiglu(w.map_xn_b, wm(4), wm(5), w.act, M, I, H, w.status, env.timeout_ms, s, &err, TILE_N,
-                                           live, a_box)) != QMK_OK)
+                                           live, a_box, wq, wp(4), wp(5))) != QMK_OK)
         return r2;
       if ((r2 = qmk_tc::launch_gemm_splitk(w.map_act_b, wm(6), w.down, M, H, I, DOWN_SPLITS, w.status, env.timeout_ms, s, &err,
-                                           TILE_N, live, a_box)) != QMK_OK)
+                                           TILE_N, live, a_box, wq, wp(6))) != QMK_OK)
         return r2;
     }
-    add_rmsnorm_rows<<<B, 256, 0, s>>>(w.x, w.down, DOWN_SPLITS, PART, static_cast<const __half *>(final_norm_weight), w.xn);
-    r2 = qmk_tc::launch_gemm(w.map_xn_b, w.map_lm, w.logits, M, env.vocab, H, 128, w.status, env.timeout_ms, s, &err, live, a_box);
+    PF_CUDA(qmk_tc::launch_kernel(add_rmsnorm_rows, dim3(B), dim3(256), 0, s, w.x, w.down, DOWN_SPLITS, PART,
+                                  static_cast<const __half *>(final_norm_weight), w.xn));
+    r2 = qmk_tc::launch_gemm(w.map_xn_b, w.map_lm, w.logits, M, env.vocab, H, 128, w.status, env.timeout_ms, s, &err, live, a_box,
+                             wq, lm_head_weight);
     if (r2 != QMK_OK) return r2;
-    argmax_rows<<<B, 1024, 0, s>>>(w.logits, env.vocab, w.tokens, w.log_ptrs, w.start_positions, w.positions);
+    PF_CUDA(qmk_tc::launch_kernel(argmax_rows, dim3(B), dim3(1024), 0, s, w.logits, env.vocab, w.tokens, w.log_ptrs,
+                                  w.start_positions, w.positions));
     return QMK_OK;
   };
 
@@ -642,12 +716,13 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
     // One step costs about 400 launches: capture it once as a CUDA graph (kept while nothing it bakes in
     // changes) and replay it num_steps times.
     const unsigned long long key[12] = {
-        w.graph_epoch, static_cast<unsigned long long>(B), static_cast<unsigned long long>(num_layers),
+        w.graph_epoch, static_cast<unsigned long long>(B) | (static_cast<unsigned long long>(wq) << 32), static_cast<unsigned long long>(num_layers),
         static_cast<unsigned long long>(max_seq_len), static_cast<unsigned long long>(env.vocab),
         static_cast<unsigned long long>(__float_as_uint_host(attn_scale)), reinterpret_cast<unsigned long long>(embed_weight),
         reinterpret_cast<unsigned long long>(final_norm_weight), reinterpret_cast<unsigned long long>(lm_head_weight),
         reinterpret_cast<unsigned long long>(rope), reinterpret_cast<unsigned long long>(cos_table),
-        reinterpret_cast<unsigned long long>(sin_table) ^ (static_cast<unsigned long long>(env.timeout_ms) << 48)};
+        reinterpret_cast<unsigned long long>(sin_table) ^ (static_cast<unsigned long long>(env.timeout_ms) << 48) ^
+            (static_cast<unsigned long long>(env.pdl != 0) << 63)};
     if (memcmp(key, w.step_key[B], sizeof(key)) != 0) {
       if (w.step_graph[B]) { cudaGraphExecDestroy(w.step_graph[B]); w.step_graph[B] = nullptr; }
       w.step_key[B][0] = 0;
@@ -730,6 +805,47 @@ extern "C" int qmk_gemm_f16_tn(const void *a, const void *b, float *c, int m, in
   if (rc == QMK_OK) {
     cudaMemsetAsync(status, 0, 16, stream);
     rc = qmk_tc::launch_gemm(ma, mb, c, m, n, k, box_n, status, 2000, stream, &err);
+  }
+  if (rc == QMK_OK) {
+    unsigned int host[4] = {0, 0, 0, 0};
+    cudaError_t e = cudaMemcpyAsync(host, status, 16, cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) { rc = QMK_ERR_CUDA; err = std::string("gemm: ") + cudaGetErrorString(e); }
+    else if (host[0] != 0) { rc = static_cast<int>(host[0]); err = "gemm: a bounded device wait ran out"; }
+  }
+  if (status) cudaFree(status);
+  if (rc != QMK_OK) fprintf(stderr, "[qwen_megakernel] error %d: %s\n", rc, err.c_str());
+  return rc;
+}
+
+// The same GEMM with B in a packed weight format (1: FP8-E4M3 rows, 2: NVFP4 rows).  `mode` 0: C fp32 [m x n];
+// mode 1: split-K in four parts, C holds the four partial matrices; mode 2: `b` is a gate matrix and `b2` an up
+// matrix, C receives fp16 silu(A gate^T) * (A up^T) - the three forms the decode step uses.
+extern "C" int qmk_gemm_packed_tn(const void *a, const void *b, const void *b2, void *c, int m, int n, int k, int weight_format,
+                                  int mode, int box_n, cudaStream_t stream) {
+  std::string err;
+  CUtensorMap ma, mb, mb2;
+  unsigned int *status = nullptr;
+  if (weight_format < 1 || weight_format > 2 || mode < 0 || mode > 2 || m <= 0 || n <= 0 || m % 128 || n % 128 ||
+      (mode == 2 && !b2) || !a || !b || !c) {
+    fprintf(stderr, "[qwen_megakernel] error %d: qmk_gemm_packed_tn: bad argument\n", QMK_ERR_BAD_ARGUMENT);
+    return QMK_ERR_BAD_ARGUMENT;
+  }
+  if (box_n <= 0) box_n = mode == 2 ? qmk_tc::gemm_box_n_fused(m, n) : mode == 1 ? 32 : qmk_tc::gemm_box_n(m, n);
+  int rc = qmk_tc::make_map_f16(&ma, a, m, k, qmk_gemm::BM, &err);
+  if (rc == QMK_OK) rc = qmk_tc::make_map_packed(&mb, b, n, k, box_n, weight_format, &err);
+  if (rc == QMK_OK && mode == 2) rc = qmk_tc::make_map_packed(&mb2, b2, n, k, box_n, weight_format, &err);
+  if (rc == QMK_OK && cudaMalloc(&status, 16) != cudaSuccess) { rc = QMK_ERR_CUDA; err = "cudaMalloc failed"; }
+  if (rc == QMK_OK) {
+    cudaMemsetAsync(status, 0, 16, stream);
+    if (mode == 0)
+      rc = qmk_tc::launch_gemm(ma, mb, static_cast<float *>(c), m, n, k, box_n, status, 2000, stream, &err, 0, 0, weight_format, b);
+    else if (mode == 1)
+      rc = qmk_tc::launch_gemm_splitk(ma, mb, static_cast<float *>(c), m, n, k, 4, status, 2000, stream, &err, box_n, 0, 0,
+                                      weight_format, b);
+    else
+      rc = qmk_tc::launch_gemm_swiglu(ma, mb, mb2, static_cast<__half *>(c), m, n, k, status, 2000, stream, &err, box_n, 0, 0,
+                                      weight_format, b, b2);
   }
   if (rc == QMK_OK) {
     unsigned int host[4] = {0, 0, 0, 0};

@@ -114,6 +114,49 @@ def dequantize_nvfp4(vals: torch.Tensor, block_scales: torch.Tensor, tensor_scal
     return (vals.view(rows, k // NVFP4_BLOCK, NVFP4_BLOCK) * (sbf * tensor_scale)[..., None]).view(rows, k)
 
 
+def nvfp4_row_bytes(k: int) -> int:
+    return k // 2 + k // NVFP4_BLOCK + TRAILER
+
+
+def pack_rows_nvfp4(vals: torch.Tensor, block_scales: torch.Tensor, tensor_scale: float) -> torch.Tensor:
+    """uint8 ``[out, in/2 + in/16 + 16]`` in the engine's NVFP4 row format: e2m1 codes two per byte (element 2i in
+    the low nibble), the row's e4m3 block scales, a 16-byte trailer whose first four bytes are the fp32 tensor
+    scale (``include/qwen_megakernel.h``, ``qmk_set_weight_format``)."""
+    rows, k = vals.shape
+    grid = torch.tensor(E2M1_GRID, dtype=torch.float32, device=vals.device)
+    code = torch.searchsorted(grid, vals.abs().contiguous()).to(torch.uint8)       # exact grid values -> their index
+    code = code | ((vals < 0) | ((vals == 0) & (torch.signbit(vals)))).to(torch.uint8) * 8
+    out = torch.zeros(rows, nvfp4_row_bytes(k), dtype=torch.uint8, device=vals.device)
+    out[:, :k // 2] = code[:, 0::2] | (code[:, 1::2] << 4)
+    out[:, k // 2:k // 2 + k // NVFP4_BLOCK] = block_scales.contiguous().view(torch.uint8)
+    ts = torch.tensor([tensor_scale], dtype=torch.float32, device=vals.device).view(torch.uint8)
+    out[:, k // 2 + k // NVFP4_BLOCK:k // 2 + k // NVFP4_BLOCK + 4] = ts
+    return out.contiguous()
+
+
+def quantize_weights_nvfp4(weights: dict):
+    """Reference-layout fp16 weight dict -> (engine dict with PACKED NVFP4 matrices, oracle dict with the
+    dequantised fp32 matrices), embedding / LM-head tie kept - the packed counterpart of ``expand_weights_nvfp4``."""
+    def both(w):
+        vals, sb, ts = quantize_blocks_nvfp4(w)
+        return pack_rows_nvfp4(vals, sb, ts), dequantize_nvfp4(vals, sb, ts)
+
+    e_embed, o_embed = both(weights["embed_weight"])
+    e_layers, o_layers = [], []
+    for t in weights["layer_weights"]:
+        if t.dim() == 2:
+            p, d = both(t)
+            e_layers.append(p)
+            o_layers.append(d)
+        else:
+            e_layers.append(t)
+            o_layers.append(t)
+    common = dict(final_norm_weight=weights["final_norm_weight"], cos_table=weights["cos_table"],
+                  sin_table=weights["sin_table"])
+    return (dict(embed_weight=e_embed, lm_head_weight=e_embed, layer_weights=e_layers, **common),
+            dict(embed_weight=o_embed, lm_head_weight=o_embed, layer_weights=o_layers, **common))
+
+
 def _quantised_dicts(weights: dict, requant):
     """(fp16 dict holding the dequantised matrices, fp32 oracle dict) with the embedding tie kept."""
     deq_embed = requant(weights["embed_weight"])

@@ -56,6 +56,8 @@ _lib.qmk_set_tuning2.argtypes = [_I, _I]
 _lib.qmk_set_tuning2.restype = _I
 _lib.qmk_set_profile_buffer.argtypes = [_P]
 _lib.qmk_set_profile_buffer.restype = _I
+_lib.qmk_set_step_overlap.argtypes = [_I]
+_lib.qmk_set_step_overlap.restype = _I
 _lib.qmk_set_fused.argtypes = [_I, _I]
 _lib.qmk_set_fused.restype = _I
 _lib.qmk_invalidate_weights.restype = _I
@@ -77,6 +79,8 @@ _lib.qmk_prefill_chunked.argtypes = [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I,
 _lib.qmk_prefill_chunked.restype = _I
 _lib.qmk_gemm_f16_tn.argtypes = [_P, _P, _P, _I, _I, _I, _P]
 _lib.qmk_gemm_f16_tn.restype = _I
+_lib.qmk_gemm_packed_tn.argtypes = [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]
+_lib.qmk_gemm_packed_tn.restype = _I
 
 
 class _EngineConfig(ctypes.Structure):
@@ -108,7 +112,7 @@ _lib.qmk_selftest_gemm_wait_timeout.restype = _I
 EXPORTED_SYMBOLS = (
     "launch_ldg_decode_direct", "launch_ldg_decode_persistent", "launch_ldg_generate_nosync",
     "launch_ldg_prefill", "qmk_abi_version", "qmk_configure", "qmk_set_inv_freq", "qmk_set_logits_dump",
-    "qmk_set_weight_format", "qmk_set_tuning", "qmk_set_tuning2", "qmk_set_profile_buffer", "qmk_set_fused", "qmk_invalidate_weights", "qmk_release_weights", "qmk_decode", "qmk_generate", "qmk_generate_static", "qmk_generate_batch", "qmk_gemm_f16_tn", "qmk_decode_batched", "qmk_prefill_chunked", "qmk_prefill", "qmk_engine_create", "qmk_engine_destroy", "qmk_engine_apply", "qmk_engine_decode", "qmk_engine_generate", "qmk_engine_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
+    "qmk_set_weight_format", "qmk_set_tuning", "qmk_set_tuning2", "qmk_set_profile_buffer", "qmk_set_fused", "qmk_set_step_overlap", "qmk_invalidate_weights", "qmk_release_weights", "qmk_decode", "qmk_generate", "qmk_generate_static", "qmk_generate_batch", "qmk_gemm_f16_tn", "qmk_gemm_packed_tn", "qmk_decode_batched", "qmk_prefill_chunked", "qmk_prefill", "qmk_engine_create", "qmk_engine_destroy", "qmk_engine_apply", "qmk_engine_decode", "qmk_engine_generate", "qmk_engine_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
     "qmk_scratch_bytes", "qmk_selftest_wait_timeout", "qmk_selftest_gemm_wait_timeout",
 )
 
@@ -225,7 +229,7 @@ class Engine:
         if device is None:
             device = torch.cuda.current_device()
         index = torch.device(device).index if not isinstance(device, int) else device
-        fmt = {"fp16": 0, "fp8": 1, 0: 0, 1: 1}.get(weight_format)
+        fmt = {"fp16": 0, "fp8": 1, "nvfp4": 2, 0: 0, 1: 1, 2: 2}.get(weight_format)
         _check(fmt is not None, f"Engine: unknown weight_format {weight_format!r}")
         freq = None
         if inv_freq is not None:
@@ -337,11 +341,12 @@ def set_tuning(spin_sleep_ns=-1, l2_evict_first=-1, repl=-1, stream_inflight=-1)
     _check(_lib.qmk_set_tuning2(int(repl), int(stream_inflight)) == 0, "set_tuning failed")
 
 
-WEIGHT_FORMATS = {"fp16": 0, "fp8": 1}
+WEIGHT_FORMATS = {"fp16": 0, "fp8": 1, "nvfp4": 2}
 
 
 def set_weight_format(fmt) -> None:
-    """"fp16" (default) or "fp8" (e4m3 rows with a 16-byte scale trailer, see include/qwen_megakernel.h)."""
+    """"fp16" (default), "fp8" (e4m3 rows with a 16-byte scale trailer) or "nvfp4" (e2m1 pairs + e4m3 block scales +
+    trailer; tensor-core entry points only); see include/qwen_megakernel.h."""
     code = WEIGHT_FORMATS[fmt] if isinstance(fmt, str) else int(fmt)
     _check(_lib.qmk_set_weight_format(code) == 0, f"set_weight_format({fmt!r}) failed")
 
@@ -354,6 +359,11 @@ def set_fused(fused=-1, red_copies=-1) -> None:
     _require_cuda()
     if _lib.qmk_set_fused(int(fused), int(red_copies)) != 0:
         _raise_if_failed("set_fused")
+
+
+def set_step_overlap(enabled: bool) -> None:
+    """Batched decode: launch the kernels of a step as programmatic dependents of one another (default on)."""
+    _check(_lib.qmk_set_step_overlap(int(bool(enabled))) == 0, "set_step_overlap failed")
 
 
 def invalidate_weights() -> None:
@@ -496,6 +506,33 @@ def gemm_f16_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None) -> t
     rc = _lib.qmk_gemm_f16_tn(_ptr(a), _ptr(b), _ptr(out), int(m), int(n), int(k), _stream())
     if rc != 0:
         raise RuntimeError(f"gemm_f16_tn failed with status {rc}")
+    return out
+
+
+def gemm_packed_tn(a: torch.Tensor, b: torch.Tensor, weight_format, b2: torch.Tensor = None, mode: str = "plain",
+                   box_n: int = 0) -> torch.Tensor:
+    """``a @ dequantised(b).T`` with ``b`` kept packed on the device (uint8 ``[n, row_bytes]``: ``"fp8"`` or ``"nvfp4"``
+    rows, see ``quantize.pack_rows_fp8`` / ``pack_rows_nvfp4``).  ``mode``: ``"plain"`` -> fp32 ``[m, n]``; ``"splitk"`` ->
+    fp32 ``[4, m, n]`` partial matrices; ``"swiglu"`` (``b`` gate, ``b2`` up) -> fp16 ``[m, n]``."""
+    _require_cuda()
+    fmt = WEIGHT_FORMATS[weight_format] if isinstance(weight_format, str) else int(weight_format)
+    code = {"plain": 0, "splitk": 1, "swiglu": 2}[mode]
+    _check(a.is_cuda and a.dtype == torch.float16 and a.is_contiguous() and a.dim() == 2,
+           "gemm_packed_tn: a must be a contiguous fp16 CUDA matrix [m, k]")
+    m, k = a.shape
+    row_bytes = {1: k + 16, 2: k // 2 + k // 16 + 16}[fmt]
+    for t in (b,) if b2 is None else (b, b2):
+        _check(t.is_cuda and t.dtype == torch.uint8 and t.is_contiguous() and t.dim() == 2 and t.shape[1] == row_bytes,
+               f"gemm_packed_tn: packed matrices must be contiguous uint8 CUDA tensors [n, {row_bytes}]")
+    n = b.shape[0]
+    if code == 2:
+        out = torch.empty(m, n, dtype=torch.float16, device=a.device)
+    else:
+        out = torch.empty((4, m, n) if code == 1 else (m, n), dtype=torch.float32, device=a.device)
+    rc = _lib.qmk_gemm_packed_tn(_ptr(a), _ptr(b), _ptr(b2), _ptr(out), int(m), int(n), int(k), fmt, code, int(box_n),
+                                 _stream())
+    if rc != 0:
+        raise RuntimeError(f"gemm_packed_tn failed with status {rc}")
     return out
 
 

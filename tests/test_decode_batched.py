@@ -132,6 +132,38 @@ def test_full_model_sixteen_sequences(C, full_cfg):
     assert checked >= 16 * steps - 8
 
 
+def test_step_overlap_changes_nothing_but_time(C):
+    """The kernels of a decode step are launched as programmatic dependents of one another (each sets itself up and
+    streams its weights behind its predecessor's tail, then waits for it to complete).  Switched off, the same kernels
+    run strictly one after the other: tokens and every logit must be bit-identical, through the captured graph and
+    through the plain launches of the logits-dump path."""
+    vocab, steps, L, n = 2048, 6, 256, 9
+    w = S.make_weights(seed=23, num_layers=3, vocab_size=vocab, norm_std=0.1, max_seq_len=16)
+    prompts = [S.make_prompt(5 + 23 * i, seed=900 + i, vocab_size=vocab) for i in range(n)]
+    eng = _engine(w, n, L, engine="gemm")
+    results = {}
+    try:
+        for overlap in (True, False, True):
+            C.set_step_overlap(overlap)
+            graph_tokens = eng.generate_ids(prompts, steps)
+            dump = torch.zeros(n, steps, vocab, device="cuda")
+            C.set_logits_dump(dump)
+            try:
+                plain_tokens = eng.generate_ids(prompts, steps)
+            finally:
+                C.set_logits_dump(None)
+            assert graph_tokens == plain_tokens
+            results.setdefault(overlap, []).append((graph_tokens, dump.cpu()))
+    finally:
+        C.set_step_overlap(True)
+    (tok_on, logit_on), (tok_on2, logit_on2) = results[True]
+    (tok_off, logit_off), = results[False]
+    assert tok_on == tok_off == tok_on2
+    assert torch.equal(logit_on, logit_off) and torch.equal(logit_on, logit_on2)
+    want = [OracleDecoder(w, max_seq_len=L).generate_ids(p, steps)[0] for p in prompts]
+    assert tok_on == want
+
+
 def test_refusals(C):
     vocab = 2048
     w = S.make_weights(seed=1, num_layers=2, vocab_size=vocab, max_seq_len=16)

@@ -150,26 +150,28 @@ def test_nvfp4_quantiser_scheme():
 @pytest.mark.gpu
 @pytest.mark.parametrize("fmt,n", [("fp8", 16), ("nvfp4", 64)])
 def test_quantised_models_on_the_batched_tensor_core_path(built_library, fmt, n):
-    """The B = 16 FP8 and B = 64 NVFP4 configurations' shapes with the quantised weights expanded to fp16:
-    every sequence against the oracle on the same dequantised weights (logits within 3e-2; tokens equal
-    wherever the oracle's greedy margin exceeds twice the logit error)."""
+    """The B = 16 FP8 and B = 64 NVFP4 configurations' shapes with the weights PACKED in device memory (expanded to
+    fp16 tiles inside the GEMMs) and the tensor-core prefill on the same packed matrices: every sequence against
+    the oracle on the dequantised weights (logits within 3e-2; tokens equal wherever the oracle's greedy margin
+    exceeds twice the logit error)."""
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     import qwen_megakernel_C as C
     from Model.Qwen06B_architecture import BatchDecoder
     vocab, steps, L = 2048, 4, 192
     w = S.make_weights(seed=31, num_layers=2, vocab_size=vocab, norm_std=0.1, max_seq_len=16)
-    eng_w, ora_w = (Q.expand_weights_fp8 if fmt == "fp8" else Q.expand_weights_nvfp4)(w)
+    eng_w, ora_w = (Q.quantize_weights_fp8 if fmt == "fp8" else Q.quantize_weights_nvfp4)(w)
     lens = [1 + (17 * i) % 150 for i in range(n)]
     prompts = [S.make_prompt(Ln, seed=600 + i, vocab_size=vocab) for i, Ln in enumerate(lens)]
     eng = BatchDecoder(weights=S.weights_to(eng_w, "cuda"), tokenizer=S.StubTokenizer(-1, vocab), num_sequences=n,
-                       max_seq_len=L, engine="gemm", prefill_mode="tensor")
+                       max_seq_len=L, engine="gemm", prefill_mode="tensor", weight_format=fmt)
     dump = torch.zeros(n, steps, vocab, device="cuda")
     C.set_logits_dump(dump)
     try:
         got = eng.generate_ids(prompts, steps)
     finally:
         C.set_logits_dump(None)
+        C.set_weight_format("fp16")
     dump = dump.cpu()
     worst, equal = 0.0, 0
     for b in range(n):
@@ -183,5 +185,5 @@ def test_quantised_models_on_the_batched_tensor_core_path(built_library, fmt, n)
                 assert float(top2[0] - top2[1]) < 2 * err + 1e-6
                 break
             equal += 1
-    print(f"{fmt} expanded, {n} sequences: worst max |logit - oracle| = {worst:.3e}; {equal}/{n * steps} steps token-equal")
+    print(f"{fmt} packed, {n} sequences: worst max |logit - oracle| = {worst:.3e}; {equal}/{n * steps} steps token-equal")
     assert equal >= 0.9 * n * steps    # near-ties (margin below twice the logit error) may break a sequence off early

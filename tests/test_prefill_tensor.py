@@ -56,6 +56,28 @@ def test_cache_and_next_tokens_match_oracle(C, n_prompt):
     assert got == want
 
 
+def test_packed_fp8_weights_prefill_on_the_tensor_cores(C):
+    """FP8-E4M3 rows stay packed in device memory; the prefill GEMMs expand them tile by tile.  Cache rows against the
+    oracle on the dequantised weights, then greedy tokens through the persistent kernel (which reads the same rows)."""
+    import quantize as Q
+    vocab, steps, L, n = 2048, 4, 640, 333
+    w = S.make_weights(seed=14, num_layers=3, vocab_size=vocab, norm_std=0.1, max_seq_len=16)
+    eng_w, ora_w = Q.quantize_weights_fp8(w)
+    ids = S.make_prompt(n + 1, seed=77, vocab_size=vocab)
+    o = OracleDecoder(ora_w, max_seq_len=L)
+    want, _ = o.generate_ids(ids, steps)
+    try:
+        eng = _engine(eng_w, L, "tensor", weight_format="fp8")
+        got = eng.generate_ids(ids, steps)
+        kerr = float((eng._k_cache[:, :, :n].float().cpu() - o.k_cache[:, :, :n].float()).abs().max())
+        verr = float((eng._v_cache[:, :, :n].float().cpu() - o.v_cache[:, :, :n].float()).abs().max())
+    finally:
+        C.set_weight_format("fp16")
+    print(f"packed fp8 tensor prefill, prompt {n}: cache max err K {kerr:.2e} V {verr:.2e}")
+    assert kerr < CACHE_TOL and verr < CACHE_TOL
+    assert got == want
+
+
 def test_appends_at_a_start_position_and_agrees_with_serial_prefill(C):
     """Prefill in two calls (the second starts at position 300) and compare with the token-serial op."""
     vocab, L = 2048, 1024
@@ -91,8 +113,8 @@ def test_table_rope_mode(C):
 def test_refusals(C):
     import quantize as Q
     w = S.make_weights(seed=1, num_layers=2, vocab_size=512, max_seq_len=16)
-    with pytest.raises(ValueError):
-        _engine(Q.quantize_weights_fp8(w)[0], 64, "tensor", weight_format="fp8")
+    with pytest.raises(ValueError):        # NVFP4 rows are read by the tensor-core ops only
+        _engine(Q.quantize_weights_nvfp4(w)[0], 64, "serial", weight_format="nvfp4")
     eng = _engine(w, 64, "tensor")
     with pytest.raises(RuntimeError, match="max_seq_len"):
         eng.prefill_ids(list(range(65)))
