@@ -55,9 +55,27 @@ constexpr uint32_t BS_PITCH = MAX_K_PACKED / 16 + 4;
 constexpr uint32_t scale_bytes_for(int bn, int wq) {
   return wq == 0 ? 0u : static_cast<uint32_t>(bn) * 4u + (wq == 2 ? static_cast<uint32_t>(bn) * BS_PITCH : 0u);
 }
+constexpr int MAX_STAGES = 16;
+constexpr uint32_t BARRIER_BYTES = 512;   // full[16], empty[16], acc_full, raw_full[16], TMEM address, abort flag
 constexpr size_t smem_bytes_for(int bn, int wq = 0) {
-  return 1024 /* alignment slack */ + static_cast<size_t>(stages_for(bn, wq)) * stage_bytes_for(bn, wq) + 256 +
+  return 1024 /* alignment slack */ + static_cast<size_t>(stages_for(bn, wq)) * stage_bytes_for(bn, wq) + BARRIER_BYTES +
          scale_bytes_for(bn, wq);
+}
+// Ring depth of a launch: the compile-time depth above (one CTA per SM, ~200 KB: a skinny problem wants its whole K
+// extent in flight), or as many stages as fit `budget_bytes` - with about 96 KB two CTAs share an SM and the epilogue
+// of one (TMEM -> registers -> global) runs under the main loop of the other, which is what a multi-wave prefill GEMM
+// wants (measured on 2048 prompt tokens: 7.9 -> 6.8 ms per pass).
+struct RingGeometry { int stages; uint32_t ring_bytes; size_t smem_bytes; };
+inline RingGeometry ring_geometry(int sb, int wq, uint32_t budget_bytes) {
+  RingGeometry g;
+  g.stages = stages_for(sb, wq);
+  if (budget_bytes > 0) {
+    const int fit = static_cast<int>(budget_bytes / stage_bytes_for(sb, wq));
+    if (fit < g.stages) g.stages = fit < 2 ? 2 : fit;
+  }
+  g.ring_bytes = static_cast<uint32_t>(g.stages) * stage_bytes_for(sb, wq);
+  g.smem_bytes = 1024 + static_cast<size_t>(g.ring_bytes) + BARRIER_BYTES + scale_bytes_for(sb, wq);
+  return g;
 }
 
 __device__ __forceinline__ uint32_t s32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -154,6 +172,15 @@ struct Groups {
   // (NVFP4) and of the fp32 scale (the trailer) inside a row.
   const unsigned char *braw[MAX_GROUPS];
   uint32_t raw_pitch, raw_bs_off, raw_scale_off;
+  // Ring geometry (ring_geometry()): stages and bytes from the ring's start to the barriers.
+  int stages;
+  uint32_t ring_bytes;
+  // Greedy pick fused into the epilogue (single group, no split-K; null = off): instead of storing its part of the
+  // row, every thread keeps the largest value and its column (lowest column on ties) and writes one pair per row
+  // and N tile - amax_val / amax_idx [row][gridDim.x]; a small kernel then reduces gridDim.x pairs per row instead of
+  // reading the whole row of logits, which is never written.
+  float *amax_val;
+  int *amax_idx;
 };
 
 // e2m1 pairs of one byte -> two fp16 values.  (code & 7) << 9 read as fp16 is the e2m1 magnitude times 2^-14 - the
@@ -181,9 +208,9 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   pdl_trigger();   // the next kernel of a decode step may set itself up (and stream ITS weights) behind this one
   static_assert(!FUSE || BN <= 64, "the fused SwiGLU epilogue keeps two accumulators of at most 64 columns");
   constexpr int SB = FUSE ? 2 * BN : BN;          // B rows held per stage / accumulator columns
-  constexpr int STAGES = stages_for(SB, WQ);
-  constexpr uint32_t STAGE_BYTES = stage_bytes_for(SB, WQ);
   constexpr uint32_t RAW_ROW = raw_row_bytes(WQ);
+  const int STAGES = groups.stages;
+  constexpr uint32_t STAGE_BYTES = stage_bytes_for(SB, WQ);
   // which matrix this CTA works on
   int tile = blockIdx.x, grp = 0;
   if (!FUSE && tile >= groups.N[0] / BN) { tile -= groups.N[0] / BN; grp = 1; }
@@ -195,11 +222,11 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   const uint32_t raw = s32(gemm_smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;                 // swizzled tiles need 1024-byte alignment
   unsigned char *aligned = gemm_smem_raw + (base - raw);
-  const uint32_t bars = base + STAGES * STAGE_BYTES;            // full[STAGES], empty[STAGES], acc_full, raw_full[STAGES], then scratch
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(aligned + STAGES * STAGE_BYTES + 8 * (3 * STAGES + 1));
-  float *s_rowscale = reinterpret_cast<float *>(aligned + STAGES * STAGE_BYTES + 256);   // [SB] (WQ != 0)
+  const uint32_t bars = base + groups.ring_bytes;               // full[16], empty[16], acc_full, raw_full[16], then scratch
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(aligned + groups.ring_bytes + 8 * (3 * MAX_STAGES + 1));
+  float *s_rowscale = reinterpret_cast<float *>(aligned + groups.ring_bytes + BARRIER_BYTES);   // [SB] (WQ != 0)
   unsigned char *s_bs = reinterpret_cast<unsigned char *>(s_rowscale + SB);                // [SB][BS_PITCH] (WQ == 2)
-  static_assert(8 * (3 * stages_for(32, 0) + 1) + 8 <= 256, "barriers and scratch fit the 256 bytes behind the ring");
+  static_assert(8 * (3 * MAX_STAGES + 1) + 8 <= BARRIER_BYTES, "barriers and scratch fit the bytes reserved behind the ring");
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = tile * BN, m0 = blockIdx.y * BM;
@@ -208,16 +235,17 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   constexpr uint32_t TILE_B_BYTES = BN * BK * 2;
   constexpr uint32_t TMEM_COLS = SB;             // fp32 accumulator(s): 128 lanes x SB columns (a power of two >= 32)
   auto full = [&](int s) { return bars + 8u * s; };
-  auto empty = [&](int s) { return bars + 8u * (STAGES + s); };
-  const uint32_t acc_full = bars + 8u * (2 * STAGES);
-  auto raw_full = [&](int s) { return bars + 8u * (2 * STAGES + 1 + s); };   // packed K block (and A) landed
+  auto empty = [&](int s) { return bars + 8u * (MAX_STAGES + s); };
+  const uint32_t acc_full = bars + 8u * (2 * MAX_STAGES);
+  auto raw_full = [&](int s) { return bars + 8u * (2 * MAX_STAGES + 1 + s); };   // packed K block (and A) landed
   // what the producer's copies of one stage signal: with packed weights the expanding warps wait for them and
   // arrive on `full` themselves (one warp per stage)
   auto landed = [&](int s) { return WQ ? raw_full(s) : full(s); };
   constexpr uint32_t TILE_RAW_BYTES = BN * RAW_ROW;
   const uint32_t stage_tx = (groups.a_box_bytes ? groups.a_box_bytes : TILE_A_BYTES) + (FUSE ? 2u : 1u) * (WQ ? TILE_RAW_BYTES : TILE_B_BYTES);
+  constexpr uint32_t TILE_A = TILE_A_BYTES;   // the B tile follows the A tile in a stage
   const int kcol = WQ ? static_cast<int>(RAW_ROW) : BK;          // B-map columns (bytes for packed rows) per K block
-  const uint32_t b_dst = WQ ? TILE_A_BYTES + (FUSE ? 2u : 1u) * TILE_B_BYTES : TILE_A_BYTES;   // where the B copies land in a stage
+  const uint32_t b_dst = WQ ? TILE_A + (FUSE ? 2u : 1u) * TILE_B_BYTES : TILE_A;   // where the B copies land in a stage
   const uint32_t b_dst_step = WQ ? TILE_RAW_BYTES : TILE_B_BYTES;
   // the first fill of the ring needs no free-slot wait: thread 0 issues it before the CTA-wide barrier below, so
   // that the first TMA round trip overlaps the TMEM allocation
@@ -309,7 +337,7 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint64_t da = smem_desc_sw128(base + s * STAGE_BYTES);
-        const uint64_t db = smem_desc_sw128(base + s * STAGE_BYTES + TILE_A_BYTES);
+        const uint64_t db = smem_desc_sw128(base + s * STAGE_BYTES + TILE_A);
 #pragma unroll
         for (int j = 0; j < BK / 16; ++j) {  // 16 halves = 32 bytes = 2 descriptor address units per K step
           // FUSE: the up tile follows the gate tile in shared memory (BN more rows of the same 8-row-group layout),
@@ -324,15 +352,18 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     const int quarter = warp & 3;
     if (WQ) {
       // ---- expansion of the packed K blocks (these warps have nothing else to do until the accumulator is done)
-      // Each of the four warps expands every fourth K block on its own: the chain wait -> load -> convert -> store ->
-      // fence -> arrive is latency, not throughput, so four chains in flight finish a K loop four times sooner than
-      // four warps sharing every block.
+      // Each of the four warps expands the K blocks of its own stages (stage mod 4 == its index): the chain wait -> load
+      // -> convert -> store -> fence -> arrive is latency, not throughput, so four chains in flight finish a K loop four
+      // times sooner than four warps sharing every block.  A warp owns STAGES, not K blocks: it then meets the uses
+      // of a stage's barrier in order - a parity wait cannot tell use u from use u - 2, so a warp that reached use
+      // u of a stage before anyone had waited for use u - 1 would run ahead on stale data.
       bool live = !selftest_no_loads;
-      for (int kb = quarter; kb < kblocks && live; kb += 4) {
+      for (int kb = 0; kb < kblocks && live; ++kb) {
         const int s = kb % STAGES;
+        if ((s & 3) != quarter) continue;
         live = __all_sync(0xffffffffu, bar_wait(raw_full(s), (kb / STAGES) & 1, abort_flag, status, budget_ns));
         if (!live) break;
-        const uint32_t btile = base + s * STAGE_BYTES + TILE_A_BYTES;
+        const uint32_t btile = base + s * STAGE_BYTES + TILE_A;
         const uint32_t rawt = base + s * STAGE_BYTES + b_dst;
         // one 16-value chunk per lane and pass: chunk i = row * 4 + quarter of the 64-wide K block; the packed
         // rows are dense, so consecutive lanes read consecutive bytes
@@ -416,6 +447,9 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     } else if (ok) {
       const int row = m0 + quarter * 32 + lane;
       float *crow = C + static_cast<size_t>(blockIdx.z) * groups.split_stride + static_cast<size_t>(row) * N + n0;
+      const bool pick = groups.amax_val != nullptr;
+      float best = -INFINITY;
+      int best_col = 0x7fffffff;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -440,9 +474,21 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
               const float *sc = s_rowscale + c * 32 + i;
               o.x *= sc[0]; o.y *= sc[1]; o.z *= sc[2]; o.w *= sc[3];
             }
-            *reinterpret_cast<float4 *>(crow + c * 32 + i) = o;
+            if (pick) {   // increasing columns: strict > keeps the lowest index among equals
+              const int col = n0 + c * 32 + i;
+              if (o.x > best) { best = o.x; best_col = col; }
+              if (o.y > best) { best = o.y; best_col = col + 1; }
+              if (o.z > best) { best = o.z; best_col = col + 2; }
+              if (o.w > best) { best = o.w; best_col = col + 3; }
+            } else {
+              *reinterpret_cast<float4 *>(crow + c * 32 + i) = o;
+            }
           }
         }
+      }
+      if (pick && row < M) {
+        groups.amax_val[static_cast<size_t>(row) * gridDim.x + blockIdx.x] = best;
+        groups.amax_idx[static_cast<size_t>(row) * gridDim.x + blockIdx.x] = best_col;
       }
     }
   }

@@ -116,6 +116,8 @@ __global__ void qk_norm_rope_cache(const float *q, const float *k, const float *
                                    const __half *k_norm, const float *rope, const __half *cos_table,
                                    const __half *sin_table, float *qr, __half *k_cache_layer, __half *v_cache_layer,
                                    int pos0, int max_seq_len) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x, slot = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   const int pos = pos0 + t;
   if (slot >= 24) {   // V head: plain copy to the cache
@@ -192,6 +194,8 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
 __global__ void __launch_bounds__(ATM_THREADS) causal_attention_mma(const float *qr, const __half *k_cache_layer,
                                                             const __half *v_cache_layer, __half *out, int T, int pos0,
                                                             int max_seq_len, float scale) {
+  pdl_trigger();
+  pdl_wait();
   // two stages of (K tile, V tile): the next 64 keys are fetched with cp.async while this tile is multiplied
   extern __shared__ __align__(16) unsigned char atm_smem[];
   __half *const tiles = reinterpret_cast<__half *>(atm_smem);
@@ -668,6 +672,48 @@ __global__ void __launch_bounds__(1024) argmax_rows(const float *logits, int voc
     best_i = si[threadIdx.x];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    if (threadIdx.x == 0) {
+      tokens[b] = best_i;
+      const int pos = positions[b];
+      if (log_ptrs[b]) log_ptrs[b][pos - start_positions[b]] = best_i;
+      positions[b] = pos + 1;
+    }
+  }
+}
+
+// The same pick from the per-tile (value, column) pairs the LM-head GEMM's epilogue leaves behind (`ntiles` pairs
+// per row, tiles in increasing column order): no row of logits is ever written or read.  grid = B, block = 256.
+__global__ void __launch_bounds__(256) argmax_pairs(const float *val, const int *idx, int ntiles, int *tokens, int *const *log_ptrs,
+                                                    const int *start_positions, int *positions) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  pdl_trigger();
+  pdl_wait();
+  const int b = blockIdx.x;
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int t = threadIdx.x; t < ntiles; t += 256) {
+    const float v = val[static_cast<size_t>(b) * ntiles + t];
+    const int i = idx[static_cast<size_t>(b) * ntiles + t];
+    if (v > best) { best = v; best_i = i; }      // increasing columns per thread: strict > keeps the lowest index
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = best_i; }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    best = threadIdx.x < 8 ? sv[threadIdx.x] : -INFINITY;
+    best_i = threadIdx.x < 8 ? si[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, best, o);
       const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
       if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }

@@ -184,6 +184,22 @@ static bool set_packed(qmk_gemm::Groups *gr, int wq, int K, int ngroups, const v
   return true;
 }
 
+// Ring depth of a launch (see qmk_gemm::ring_geometry): `sb` = B rows per stage; returns the dynamic shared memory.
+thread_local float *t_amax_val = nullptr;   // the next single-matrix GEMM of this thread leaves (value, column) pairs here
+thread_local int *t_amax_idx = nullptr;
+thread_local unsigned int t_ring_budget = 0;   // shared-memory budget of the ring (0 = the compile-time depth, one CTA per SM)
+static size_t set_ring(qmk_gemm::Groups *gr, int sb, int wq) {
+  const qmk_gemm::RingGeometry g = qmk_gemm::ring_geometry(sb, wq, t_ring_budget);
+  gr->stages = g.stages;
+  gr->ring_bytes = g.ring_bytes;
+  return g.smem_bytes;
+}
+
+RingBudgetScope::RingBudgetScope(unsigned int bytes) : prev_(t_ring_budget) { t_ring_budget = bytes; }
+RingBudgetScope::~RingBudgetScope() { t_ring_budget = prev_; }
+void set_argmax_target(float *val, int *idx) { t_amax_val = val; t_amax_idx = idx; }
+size_t selftest_ring(qmk_gemm::Groups *gr) { return set_ring(gr, 128, 0); }
+
 // A maps with short boxes (`a_box_rows` < 128 rows per box, a multiple of 8; decode steps with few live rows): one
 // row tile only, and the epilogue must stay inside the box.
 static bool a_box_ok(int a_box_rows, int M, int *rows, uint32_t *a_box_bytes, std::string *err) {
@@ -213,6 +229,8 @@ int launch_gemm_grouped(const CUtensorMap &map_a, int ngroups, const CUtensorMap
   gr.kblocks_per_split = 0;
   gr.split_stride = 0;
   if (!set_packed(&gr, wq, K, ngroups, raws, err)) return QMK_ERR_BAD_ARGUMENT;
+  gr.amax_val = ngroups == 1 ? t_amax_val : nullptr;   // (set around the LM-head launch of a decode step only)
+  gr.amax_idx = ngroups == 1 ? t_amax_idx : nullptr;
   int tiles = 0;
   for (int g = 0; g < qmk_gemm::MAX_GROUPS; ++g) {
     gr.C[g] = g < ngroups ? Cs[g] : nullptr;
@@ -224,7 +242,8 @@ int launch_gemm_grouped(const CUtensorMap &map_a, int ngroups, const CUtensorMap
   const unsigned long long budget = static_cast<unsigned long long>(timeout_ms) * 1000000ull;
   int rows = live_rows > 0 ? live_rows : M;   // rows the epilogue stores (the rest of the tile is padding)
   if (!a_box_ok(a_box_rows, M, &rows, &gr.a_box_bytes, err)) return QMK_ERR_BAD_ARGUMENT;
-  cudaError_t e = launch_kernel(gemm_kernel(box_n, false, wq), grid, dim3(qmk_gemm::THREADS), gemm_smem(box_n, false, wq), stream,
+  const size_t smem = set_ring(&gr, box_n, wq);
+  cudaError_t e = launch_kernel(gemm_kernel(box_n, false, wq), grid, dim3(qmk_gemm::THREADS), smem, stream,
                                 map_a, b0, b1, b2, gr, rows, K, status, budget, 0);
   if (e != cudaSuccess) { *err = std::string("gemm launch: ") + cudaGetErrorString(e); return QMK_ERR_CUDA; }
   return QMK_OK;
@@ -248,11 +267,14 @@ int launch_gemm_swiglu(const CUtensorMap &map_a, const CUtensorMap &map_gate, co
   gr.split_stride = 0;
   const void *raws[2] = {raw_gate, raw_up};
   if (!set_packed(&gr, wq, K, 2, raws, err)) return QMK_ERR_BAD_ARGUMENT;
+  gr.amax_val = nullptr;
+  gr.amax_idx = nullptr;
   int rows = live_rows > 0 ? live_rows : M;
   if (!a_box_ok(a_box_rows, M, &rows, &gr.a_box_bytes, err)) return QMK_ERR_BAD_ARGUMENT;
   const unsigned long long budget = static_cast<unsigned long long>(timeout_ms) * 1000000ull;
+  const size_t smem = set_ring(&gr, 2 * box_n, wq);
   cudaError_t e = launch_kernel(gemm_kernel(box_n, true, wq), dim3(N / box_n, M / qmk_gemm::BM), dim3(qmk_gemm::THREADS),
-                                gemm_smem(box_n, true, wq), stream, map_a, map_gate, map_up, map_up, gr, rows, K, status, budget, 0);
+                                smem, stream, map_a, map_gate, map_up, map_up, gr, rows, K, status, budget, 0);
   if (e != cudaSuccess) { *err = std::string("gemm launch: ") + cudaGetErrorString(e); return QMK_ERR_CUDA; }
   return QMK_OK;
 }
@@ -275,11 +297,14 @@ int launch_gemm_splitk(const CUtensorMap &map_a, const CUtensorMap &map_b, float
   gr.kblocks_per_split = K / qmk_gemm::BK / splits;
   gr.split_stride = static_cast<size_t>(M) * N;
   if (!set_packed(&gr, wq, K, 1, &raw, err)) return QMK_ERR_BAD_ARGUMENT;
+  gr.amax_val = nullptr;
+  gr.amax_idx = nullptr;
   int rows = live_rows > 0 ? live_rows : M;
   if (!a_box_ok(a_box_rows, M, &rows, &gr.a_box_bytes, err)) return QMK_ERR_BAD_ARGUMENT;
   const unsigned long long budget = static_cast<unsigned long long>(timeout_ms) * 1000000ull;
+  const size_t smem = set_ring(&gr, box_n, wq);
   cudaError_t e = launch_kernel(gemm_kernel(box_n, false, wq), dim3(N / box_n, M / qmk_gemm::BM, splits), dim3(qmk_gemm::THREADS),
-                                gemm_smem(box_n, false, wq), stream, map_a, map_b, map_b, map_b, gr, rows, K, status, budget, 0);
+                                smem, stream, map_a, map_b, map_b, map_b, gr, rows, K, status, budget, 0);
   if (e != cudaSuccess) { *err = std::string("gemm launch: ") + cudaGetErrorString(e); return QMK_ERR_CUDA; }
   return QMK_OK;
 }
@@ -299,6 +324,7 @@ int launch_gemm(const CUtensorMap &map_a, const CUtensorMap &map_b, float *C, in
 // ----------------------------------------------------------------------------- chunked prefill
 namespace {
 
+constexpr unsigned int PREFILL_RING_BYTES = 96 * 1024;
 constexpr int CHUNK = 2048;         // prompt tokens per pass over the weights (a multiple of the GEMM's 128)
 constexpr int MAX_LAYERS = 48;
 
@@ -324,6 +350,8 @@ struct Workspace {                  // per device, allocated on first use, never
   unsigned int *split_count = nullptr;    // arrival counters, one per (sequence, kv head); zero between launches
   float *logits = nullptr;
   int logits_vocab = 0;
+  float *amax_val = nullptr;              // [128][vocab / 128] pairs of the LM-head epilogue's greedy pick
+  int *amax_idx = nullptr;
   const void *lm_ptr = nullptr;
   int lm_wq = 0;
   CUtensorMap map_lm;
@@ -478,25 +506,32 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
     const int M = (T + qmk_gemm::BM - 1) / qmk_gemm::BM * qmk_gemm::BM;
     const int pos0 = start_position + c0;
     PF_CUDA(cudaMemcpyAsync(w.tokens, token_ids_host + c0, sizeof(int) * T, cudaMemcpyHostToDevice, stream));
-    embed_rows<<<T, 256, 0, stream>>>(w.tokens, embed_weight, wq, w.x);
+    qmk_tc::PdlScope pdl_scope(env.pdl != 0);   // every launch below may start behind its predecessor's tail
+    qmk_tc::RingBudgetScope ring_scope(PREFILL_RING_BYTES);   // two GEMM CTAs per SM: one's epilogue under the other's main loop
+    {
+      qmk_tc::PdlScope first(false);            // (follows a copy, not a kernel)
+      PF_CUDA(qmk_tc::launch_kernel(embed_rows, dim3(T), dim3(256), 0, stream, w.tokens, embed_weight, wq, w.x));
+    }
     for (int l = 0; l < num_layers; ++l) {
       const unsigned long long *r = rec.data() + static_cast<size_t>(l) * 12;
       __half *kc = static_cast<__half *>(k_cache) + l * layer_stride, *vc = static_cast<__half *>(v_cache) + l * layer_stride;
-      add_rmsnorm_rows<<<T, 256, 0, stream>>>(w.x, l > 0 ? w.down : nullptr, 1, 0, reinterpret_cast<const __half *>(r[0]), w.xn);
+      PF_CUDA(qmk_tc::launch_kernel(add_rmsnorm_rows, dim3(T), dim3(256), 0, stream, w.x, l > 0 ? w.down : nullptr, 1, size_t(0),
+                                    reinterpret_cast<const __half *>(r[0]), w.xn));
       {
         const int js[3] = {0, 1, 2};
         float *const cs[3] = {w.q, w.k, w.v};
         const int ns[3] = {QS, KVS, KVS};
         if ((rc = gemm_group(w.map_xn, l, 3, js, cs, ns, M, H, T)) != QMK_OK) break;
       }
-      qk_norm_rope_cache<<<dim3(T, 4), 256, 0, stream>>>(w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]),
-                                                         reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv, w.qr, kc, vc,
-                                                         pos0, max_seq_len);
+      PF_CUDA(qmk_tc::launch_kernel(qk_norm_rope_cache, dim3(T, 4), dim3(256), 0, stream, w.q, w.k, w.v,
+                                    reinterpret_cast<const __half *>(r[4]), reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv,
+                                    w.qr, kc, vc, pos0, max_seq_len));
       if (l == num_layers - 1) break;   // the cache is complete; nothing downstream of the last layer is kept
-      causal_attention_mma<<<dim3((T + ATM_Q - 1) / ATM_Q, NKV), ATM_THREADS, ATM_SMEM_BYTES, stream>>>(w.qr, kc, vc, w.attn, T, pos0,
-                                                                                  max_seq_len, attn_scale);
+      PF_CUDA(qmk_tc::launch_kernel(causal_attention_mma, dim3((T + ATM_Q - 1) / ATM_Q, NKV), dim3(ATM_THREADS), ATM_SMEM_BYTES, stream,
+                                    w.qr, kc, vc, w.attn, T, pos0, max_seq_len, attn_scale));
       if ((rc = gemm(w.map_attn, l, 3, w.o, M, H, QS, T)) != QMK_OK) break;
-      add_rmsnorm_rows<<<T, 256, 0, stream>>>(w.x, w.o, 1, 0, reinterpret_cast<const __half *>(r[7]), w.xn);
+      PF_CUDA(qmk_tc::launch_kernel(add_rmsnorm_rows, dim3(T), dim3(256), 0, stream, w.x, w.o, 1, size_t(0),
+                                    reinterpret_cast<const __half *>(r[7]), w.xn));
       {
         const int box_gu = qmk_tc::gemm_box_n_fused(M, I);
         if ((rc = qmk_tc::launch_gemm_swiglu(w.map_xn, wmap_for(l, 4, box_gu), wmap_for(l, 5, box_gu), w.act, M, I, H,
@@ -548,6 +583,12 @@ int ensure_decode_workspace(Workspace &w, const void *lm_head, int vocab, int wq
     w.logits = nullptr;
     w.logits_vocab = 0;
     PF_CUDA(cudaMalloc(&w.logits, sizeof(float) * static_cast<size_t>(MAX_BATCH) * vocab));
+    if (w.amax_val) cudaFree(w.amax_val);
+    if (w.amax_idx) cudaFree(w.amax_idx);
+    w.amax_val = nullptr;
+    w.amax_idx = nullptr;
+    PF_CUDA(cudaMalloc(&w.amax_val, sizeof(float) * static_cast<size_t>(MAX_BATCH) * (vocab / 128)));
+    PF_CUDA(cudaMalloc(&w.amax_idx, sizeof(int) * static_cast<size_t>(MAX_BATCH) * (vocab / 128)));
     w.logits_vocab = vocab;
     w.lm_ptr = nullptr;
   }
@@ -693,11 +734,20 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
     }
     PF_CUDA(qmk_tc::launch_kernel(add_rmsnorm_rows, dim3(B), dim3(256), 0, s, w.x, w.down, DOWN_SPLITS, PART,
                                   static_cast<const __half *>(final_norm_weight), w.xn));
+    // Without a logits dump the LM head's epilogue picks the largest logit of each 128-column tile itself and the
+    // rows of logits (B x 608 KB per step) are never written
+    const bool fused_pick = env.logits_out == nullptr;
+    if (fused_pick) qmk_tc::set_argmax_target(w.amax_val, w.amax_idx);
     r2 = qmk_tc::launch_gemm(w.map_xn_b, w.map_lm, w.logits, M, env.vocab, H, 128, w.status, env.timeout_ms, s, &err, live, a_box,
                              wq, lm_head_weight);
+    qmk_tc::set_argmax_target(nullptr, nullptr);
     if (r2 != QMK_OK) return r2;
-    PF_CUDA(qmk_tc::launch_kernel(argmax_rows, dim3(B), dim3(1024), 0, s, w.logits, env.vocab, w.tokens, w.log_ptrs,
-                                  w.start_positions, w.positions));
+    if (fused_pick)
+      PF_CUDA(qmk_tc::launch_kernel(argmax_pairs, dim3(B), dim3(256), 0, s, w.amax_val, w.amax_idx, env.vocab / 128, w.tokens,
+                                    w.log_ptrs, w.start_positions, w.positions));
+    else
+      PF_CUDA(qmk_tc::launch_kernel(argmax_rows, dim3(B), dim3(1024), 0, s, w.logits, env.vocab, w.tokens, w.log_ptrs,
+                                    w.start_positions, w.positions));
     return QMK_OK;
   };
 
@@ -780,7 +830,12 @@ extern "C" int qmk_selftest_gemm_wait_timeout(int budget_us) {
     gr.kblocks_per_split = 0;
     gr.split_stride = 0;
     gr.a_box_bytes = 0;
-    qmk_gemm::gemm_f16_tn_kernel<128><<<dim3(1, 1), qmk_gemm::THREADS, qmk_gemm::smem_bytes_for(128)>>>(
+    for (int g = 0; g < qmk_gemm::MAX_GROUPS; ++g) gr.braw[g] = nullptr;
+    gr.raw_pitch = gr.raw_bs_off = gr.raw_scale_off = 0;
+    gr.amax_val = nullptr;
+    gr.amax_idx = nullptr;
+    const size_t smem = qmk_tc::selftest_ring(&gr);
+    qmk_gemm::gemm_f16_tn_kernel<128><<<dim3(1, 1), qmk_gemm::THREADS, smem>>>(
         m, m, m, m, gr, 128, 64, status, static_cast<unsigned long long>(budget_us) * 1000ull, 1);
     unsigned int host[4] = {0, 0, 0, 0};
     cudaError_t e = cudaMemcpy(host, status, 16, cudaMemcpyDeviceToHost);

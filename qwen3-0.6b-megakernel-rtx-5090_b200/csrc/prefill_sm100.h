@@ -18,6 +18,19 @@ class PdlScope {
   bool prev_;
 };
 bool pdl_active();
+}  // namespace qmk_tc
+namespace qmk_gemm { struct Groups; }
+namespace qmk_tc {
+void set_argmax_target(float *val, int *idx);   // calling thread: the next single-matrix GEMM picks per tile instead of storing
+// While one is alive on a thread, GEMM launches of that thread size their rings to `bytes` of shared memory (0 = full depth).
+class RingBudgetScope {
+ public:
+  explicit RingBudgetScope(unsigned int bytes);
+  ~RingBudgetScope();
+ private:
+  unsigned int prev_;
+};
+size_t selftest_ring(qmk_gemm::Groups *gr);   // ring geometry of the bounded-wait self test's one-tile launch
 template <typename... KArgs, typename... Args>
 cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&...args) {
   cudaLaunchConfig_t cfg = {};

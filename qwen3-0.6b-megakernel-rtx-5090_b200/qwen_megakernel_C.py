@@ -247,7 +247,7 @@ class Engine:
 
     def close(self) -> None:
         handle, self._handle = getattr(self, "_handle", None), None
-        if handle:
+        if handle and _lib is not None:       # (module globals are gone when the interpreter shuts down)
             _lib.qmk_engine_destroy(handle)
 
     __del__ = close
