@@ -192,6 +192,11 @@ int qmk_set_tuning(int spin_sleep_ns, int l2_evict_first);
  * weight/KV chunks in flight per SM during the layer phases (0 = ring depth). */
 int qmk_set_tuning2(int repl, int stream_inflight);
 
+/* Chunked prefill (qmk_prefill_chunked): 1 (default) runs the causal attention on the tcgen05 tensor cores (S and O
+ * accumulators in TMEM, K / V tiles by TMA from the cache), 0 on the mma.sync kernel.  Same tolerance against the
+ * oracle either way; negative keeps. */
+int qmk_set_prefill_attention(int tensor_core);
+
 /* Batched decode (qmk_decode_batched): 1 (default) launches the ~200 kernels of a decode step as programmatic
  * dependents of one another - each kernel is scheduled while its predecessor still runs, sets itself up, streams the
  * operands no kernel of the step writes (weight tiles, cache rows of earlier steps) and only then waits for the

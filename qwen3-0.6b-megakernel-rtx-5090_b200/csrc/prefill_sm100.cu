@@ -12,6 +12,7 @@
 #include "gemm_tcgen05.cuh"
 #include "prefill_sm100.h"
 #include "prefill_kernels.cuh"
+#include "attention_tcgen05.cuh"
 #include "engine_internal.h"
 #include <vector>
 
@@ -93,6 +94,23 @@ int make_map_b(CUtensorMap *map, const void *ptr, uint64_t rows, int K, uint32_t
   return wq ? make_map_packed(map, ptr, rows, K, box_rows, wq, err) : make_map_f16(map, ptr, rows, static_cast<uint64_t>(K), box_rows, err);
 }
 
+// 3-D tensor map of an fp16 KV cache [heads][max_seq_len][128] of which the first `rows` positions of every head are
+// valid: boxes of 64 dims x 64 positions of one head, 128-byte swizzle; positions >= rows read as zeros.
+int make_map_kv(CUtensorMap *map, const void *cache, uint64_t rows, uint64_t max_seq_len, uint64_t heads, std::string *err) {
+  EncodeTiledFn enc = encoder();
+  if (!enc) { *err = "cuTensorMapEncodeTiled is not available from this driver"; return QMK_ERR_CUDA; }
+  if (reinterpret_cast<uintptr_t>(cache) & 15u) { *err = "cache not 16-byte aligned"; return QMK_ERR_BAD_ARGUMENT; }
+  const cuuint64_t dims[3] = {128, rows, heads};
+  const cuuint64_t strides[2] = {256, max_seq_len * 256};
+  const cuuint32_t box[3] = {64, 64, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(cache), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { *err = "cuTensorMapEncodeTiled (cache) failed with code " + std::to_string(static_cast<int>(r)); return QMK_ERR_CUDA; }
+  return QMK_OK;
+}
+
 // Width of the N tiles for C[M x N] = A[M x K] * B[N x K]^T (M, N multiples of 128).  `map_b` must have been made
 // with that many rows per box.  Skinny problems are bound by how many SMs pull operands at once and by the fixed
 // cost of a CTA (launch, barrier and TMEM set-up, pipeline fill, epilogue - worth about 320 columns of streaming in
@@ -158,6 +176,9 @@ int ensure_gemm_attrs(std::string *err) {
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(qmk_pf::causal_attention_mma, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                qmk_pf::ATM_SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(qmk_attn::causal_attention_tc, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(qmk_attn::SMEM_BYTES));
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(qmk_pf::decode_attention_ring, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                qmk_pf::DAR_SMEM_BYTES);
@@ -501,10 +522,20 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
     return qmk_tc::launch_gemm_grouped(a, n, maps, cs, ns, M, K, box_n, w.status, env.timeout_ms, stream, &err, live, 0, wq,
                                        raws);
   };
+  if ((rc = qmk_tc::ensure_gemm_attrs(&err)) != QMK_OK) return qmk_internal::report(rc, err);
   for (int c0 = 0; c0 < num_tokens; c0 += CHUNK) {
     const int T = (num_tokens - c0 < CHUNK) ? num_tokens - c0 : CHUNK;
     const int M = (T + qmk_gemm::BM - 1) / qmk_gemm::BM * qmk_gemm::BM;
     const int pos0 = start_position + c0;
+    CUtensorMap map_kc, map_vc;   // the caches up to this chunk's last position, all layers
+    if (env.attn_tc) {
+      rc = qmk_tc::make_map_kv(&map_kc, k_cache, static_cast<uint64_t>(pos0 + T), static_cast<uint64_t>(max_seq_len),
+                               static_cast<uint64_t>(num_layers) * NKV, &err);
+      if (rc == QMK_OK)
+        rc = qmk_tc::make_map_kv(&map_vc, v_cache, static_cast<uint64_t>(pos0 + T), static_cast<uint64_t>(max_seq_len),
+                                 static_cast<uint64_t>(num_layers) * NKV, &err);
+      if (rc != QMK_OK) break;
+    }
     PF_CUDA(cudaMemcpyAsync(w.tokens, token_ids_host + c0, sizeof(int) * T, cudaMemcpyHostToDevice, stream));
     qmk_tc::PdlScope pdl_scope(env.pdl != 0);   // every launch below may start behind its predecessor's tail
     qmk_tc::RingBudgetScope ring_scope(PREFILL_RING_BYTES);   // two GEMM CTAs per SM: one's epilogue under the other's main loop
@@ -527,8 +558,13 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
                                     reinterpret_cast<const __half *>(r[4]), reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv,
                                     w.qr, kc, vc, pos0, max_seq_len));
       if (l == num_layers - 1) break;   // the cache is complete; nothing downstream of the last layer is kept
-      PF_CUDA(qmk_tc::launch_kernel(causal_attention_mma, dim3((T + ATM_Q - 1) / ATM_Q, NKV), dim3(ATM_THREADS), ATM_SMEM_BYTES, stream,
-                                    w.qr, kc, vc, w.attn, T, pos0, max_seq_len, attn_scale));
+      if (env.attn_tc)
+        PF_CUDA(qmk_tc::launch_kernel(qmk_attn::causal_attention_tc, dim3((T + qmk_attn::TQ - 1) / qmk_attn::TQ, NQ),
+                                      dim3(qmk_attn::THREADS), qmk_attn::SMEM_BYTES, stream, w.qr, map_kc, map_vc, l * NKV, w.attn, T,
+                                      pos0, attn_scale, w.status, static_cast<unsigned long long>(env.timeout_ms) * 1000000ull));
+      else
+        PF_CUDA(qmk_tc::launch_kernel(causal_attention_mma, dim3((T + ATM_Q - 1) / ATM_Q, NKV), dim3(ATM_THREADS), ATM_SMEM_BYTES, stream,
+                                      w.qr, kc, vc, w.attn, T, pos0, max_seq_len, attn_scale));
       if ((rc = gemm(w.map_attn, l, 3, w.o, M, H, QS, T)) != QMK_OK) break;
       PF_CUDA(qmk_tc::launch_kernel(add_rmsnorm_rows, dim3(T), dim3(256), 0, stream, w.x, w.o, 1, size_t(0),
                                     reinterpret_cast<const __half *>(r[7]), w.xn));
@@ -549,7 +585,9 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
   PF_CUDA(cudaMemcpyAsync(host_status, w.status, 16, cudaMemcpyDeviceToHost, stream));
   PF_CUDA(cudaStreamSynchronize(stream));
   if (host_status[0] != 0)
-    return qmk_internal::report(static_cast<int>(host_status[0]), "prefill: a bounded device wait ran out");
+    return qmk_internal::report(static_cast<int>(host_status[0]) == 5 ? QMK_ERR_CUDA : static_cast<int>(host_status[0]),
+                                host_status[0] == 5 ? "prefill: dynamic shared memory of the attention kernel is not 1024-byte aligned"
+                                                    : "prefill: a bounded device wait ran out");
   return QMK_OK;
 }
 
