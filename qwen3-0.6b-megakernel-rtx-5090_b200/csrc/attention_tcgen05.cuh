@@ -9,10 +9,12 @@
 //   O[128 x 128] += P[128 x 64] . V_tile[64 x 128]   tcgen05.mma, B read MN-major straight from the [key][dim] rows
 // The running row maximum is only raised when it grew by more than 2^8 (P stays below 256, far inside fp16), so the
 // accumulator in TMEM is rescaled a handful of times per row instead of once per tile; the row sums follow the same
-// stale maximum and the final division makes the result exact again.  One thread feeds the ring, one thread issues
-// every MMA; an MMA pipe executes in order, so "S of tile j + 1 is complete" (a commit) also says "O has taken tile j",
-// which is all the softmax warps need to know before they touch P or O again.  Two CTAs share an SM (112 KB of shared
-// memory, 256 TMEM columns each): one's softmax runs under the other's MMAs.  Every wait is bounded (status 4).
+// stale maximum and the final division makes the result exact again.  One thread feeds the K and V rings (two
+// stages each; a K slot is free again as soon as its S product is done, a V slot after its P . V), one thread issues
+// every MMA.  S is double-buffered in TMEM: the product for tile j + 1 is issued before the thread waits for P of tile
+// j, so the softmax warps find their next tile ready and only wait (for "O has taken tile j", one commit) before they
+// overwrite P or rescale O.  Two CTAs share an SM (112 KB of shared memory, 256 TMEM columns each): one's softmax
+// runs under the other's MMAs.  Every wait is bounded (status 4).
 #ifndef QMK_ATTENTION_TCGEN05_CUH_
 #define QMK_ATTENTION_TCGEN05_CUH_
 
@@ -34,7 +36,7 @@ constexpr uint32_t P_BYTES = TQ * TK * 2;
 constexpr int STAGES = 2;
 constexpr uint32_t OFF_KV = Q_BYTES, OFF_P = OFF_KV + STAGES * KV_STAGE_BYTES, OFF_BARS = OFF_P + P_BYTES;
 constexpr size_t SMEM_BYTES = OFF_BARS + 128;
-constexpr uint32_t TMEM_COLS = 256;              // S in columns [0, 64), O in [64, 192)
+constexpr uint32_t TMEM_COLS = 256;              // S buffers in columns [0, 64) and [64, 128), O in [128, 256)
 constexpr float RESCALE_THRESHOLD = 8.0f;        // log2 units
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t bar) {
@@ -77,25 +79,37 @@ constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 16) /* B MN-major */ | (static_
 
 // qr: fp32 [T][16 heads][128] (normalised, rotated queries of the chunk; query t sits at position pos0 + t and sees
 // cache rows 0 .. pos0 + t).  map_k / map_v: 3-D maps {128 dims, pos0 + T rows, layers x 8 kv heads} of the fp16
-// caches, boxes of {64, 64, 1}, 128-byte swizzle.  out: fp16 [T][2048].  grid = (ceil(T / 128), 16).
+// caches, boxes of {64, 64, 1}, 128-byte swizzle.  out: fp16 [T][2048].  grid = ceil(T / 128) * 16 CTAs in one
+// dimension; `first_wave` = CTAs that start at once with one CTA per SM (the SM count).
+//
+// Work per CTA grows with the position of its query tile (causal: tile i sees 2 (i + 1) key tiles of 64).  CTAs are
+// therefore numbered so that the block scheduler, which hands them out in order, gives every SM one heavy and one
+// light tile: ids below `first_wave` take the (tile, head) pairs from the heaviest down, the ids after that take the
+// remaining pairs from the LIGHTEST up - SM k's second CTA (id first_wave + k) is the lighter the heavier its first.
 __global__ void __launch_bounds__(THREADS, 2)
 causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                     int layer_head0, __half *out, int T, int pos0, float scale, unsigned int *status,
-                    unsigned long long budget_ns) {
+                    unsigned long long budget_ns, int first_wave) {
   using namespace qmk_gemm;
   pdl_trigger();
   extern __shared__ __align__(1024) unsigned char attn_smem[];
   const uint32_t base = s32(attn_smem);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int head = blockIdx.y, g = head >> 1;
-  const int q0 = (static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)) * TQ;   // longest tiles first
+  const int total = static_cast<int>(gridDim.x), id = static_cast<int>(blockIdx.x);
+  const int rank = id < first_wave ? id : total - 1 - (id - first_wave);     // position in the heaviest-first order
+  const int head = rank % NQ, g = head >> 1;
+  const int q0 = (total / NQ - 1 - rank / NQ) * TQ;
   const int last_q = (q0 + TQ < T ? q0 + TQ : T) - 1;                                        // last live query of the tile
   const int ntiles = (pos0 + last_q) / TK + 1;                                              // key tiles it can see
   const uint32_t bars = base + OFF_BARS;
-  auto kv_full = [&](int s) { return bars + 8u * s; };
-  auto kv_empty = [&](int s) { return bars + 8u * (STAGES + s); };
-  const uint32_t s_full = bars + 8u * (2 * STAGES), p_ready = s_full + 8u, o_final = s_full + 16u;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(attn_smem + OFF_BARS + 8 * (2 * STAGES + 3));
+  auto k_full = [&](int s) { return bars + 8u * s; };
+  auto k_empty = [&](int s) { return bars + 8u * (2 + s); };
+  auto v_full = [&](int s) { return bars + 8u * (4 + s); };
+  auto v_empty = [&](int s) { return bars + 8u * (6 + s); };
+  auto s_full = [&](int b) { return bars + 8u * (8 + b); };
+  const uint32_t p_ready = bars + 8u * 10, pv_done = bars + 8u * 11;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(attn_smem + OFF_BARS + 8 * 12);
+  static_assert(STAGES == 2, "barrier layout above");
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   if ((base & 1023u) != 0u) {   // the swizzled tiles need a 1024-byte aligned window: report instead of computing garbage
@@ -105,10 +119,11 @@ causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, 
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
-    for (int s = 0; s < STAGES; ++s) { bar_init(kv_full(s), 1); bar_init(kv_empty(s), 1); }
-    bar_init(s_full, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      bar_init(k_full(s), 1); bar_init(k_empty(s), 1); bar_init(v_full(s), 1); bar_init(v_empty(s), 1); bar_init(s_full(s), 1);
+    }
     bar_init(p_ready, 4);      // one arrival per softmax warp
-    bar_init(o_final, 1);
+    bar_init(pv_done, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -139,27 +154,32 @@ causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, 
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 64u;
+  const uint32_t tmem_o = tmem_base + 128u;   // S buffer b at tmem_base + 64 b
 
   if (warp == 0) {
-    if (lane == 0) {                       // ---- producer: K and V tiles of 64 rows
+    if (lane == 0) {                       // ---- producer: K and V tiles of 64 rows, each ring on its own barriers
       int issued = 0;
       for (int j = 0; j < ntiles; ++j) {
         const int s = j % STAGES;
-        if (j >= STAGES && !bar_wait(kv_empty(s), ((j / STAGES) - 1) & 1, abort_flag, status, budget_ns)) break;
-        if (*abort_flag) break;
-        bar_expect_tx(kv_full(s), KV_STAGE_BYTES);
         const uint32_t dst = base + OFF_KV + s * KV_STAGE_BYTES;
-        tma_load_3d(dst, &map_k, 0, j * TK, layer_head0 + g, kv_full(s));
-        tma_load_3d(dst + TK * 128, &map_k, 64, j * TK, layer_head0 + g, kv_full(s));
-        tma_load_3d(dst + 2 * TK * 128, &map_v, 0, j * TK, layer_head0 + g, kv_full(s));
-        tma_load_3d(dst + 3 * TK * 128, &map_v, 64, j * TK, layer_head0 + g, kv_full(s));
-        issued = j + 1;
+        if (j >= STAGES && !bar_wait(k_empty(s), ((j / STAGES) - 1) & 1, abort_flag, status, budget_ns)) break;
+        if (*abort_flag) break;
+        bar_expect_tx(k_full(s), KV_STAGE_BYTES / 2);
+        tma_load_3d(dst, &map_k, 0, j * TK, layer_head0 + g, k_full(s));
+        tma_load_3d(dst + TK * 128, &map_k, 64, j * TK, layer_head0 + g, k_full(s));
+        if (j >= STAGES && !bar_wait(v_empty(s), ((j / STAGES) - 1) & 1, abort_flag, status, budget_ns)) { issued = 2 * j + 1; break; }
+        bar_expect_tx(v_full(s), KV_STAGE_BYTES / 2);
+        tma_load_3d(dst + 2 * TK * 128, &map_v, 0, j * TK, layer_head0 + g, v_full(s));
+        tma_load_3d(dst + 3 * TK * 128, &map_v, 64, j * TK, layer_head0 + g, v_full(s));
+        issued = 2 * j + 2;
       }
       if (*abort_flag) {                   // copies already issued must land before the CTA may exit
-        for (int j = (issued > STAGES ? issued - STAGES : 0); j < issued; ++j) {
+        // `issued` counts half-tiles in issue order (K of tile 0, V of tile 0, K of tile 1, ...): wait for the last four
+        for (int h = (issued > 2 * STAGES ? issued - 2 * STAGES : 0); h < issued; ++h) {
+          const int jj = h >> 1;
+          const uint32_t bar = (h & 1) ? v_full(jj % STAGES) : k_full(jj % STAGES);
           const unsigned long long t0 = gtime();
-          while (!bar_try(kv_full(j % STAGES), (j / STAGES) & 1)) {
+          while (!bar_try(bar, (jj / STAGES) & 1)) {
             if (gtime() - t0 > (budget_ns > 2000000ull ? budget_ns : 2000000ull)) break;
           }
         }
@@ -168,24 +188,36 @@ causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, 
   } else if (warp == 1) {
     if (lane == 0) {                       // ---- MMA issuer
       bool ok = true;
-      auto issue_s = [&](int j) {          // S = Q . K_j^T: two 64-wide halves of the head dimension, four K = 16 steps each
+      // S_j = Q . K_j^T into S buffer j mod 2: two 64-wide halves of the head dimension, four K = 16 steps each
+      auto issue_s = [&](int j) {
         const uint32_t kt = base + OFF_KV + (j % STAGES) * KV_STAGE_BYTES;
+        const uint32_t ts = tmem_base + 64u * static_cast<uint32_t>(j & 1);
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb) {
           const uint64_t da = smem_desc_sw128(base + kb * (TQ * 128));
           const uint64_t db = smem_desc_sw128(kt + kb * (TK * 128));
 #pragma unroll
-          for (int i = 0; i < 4; ++i) mma_f16_ss(tmem_s, da + 2u * i, db + 2u * i, (kb > 0 || i > 0) ? 1u : 0u, IDESC_S);
+          for (int i = 0; i < 4; ++i) mma_f16_ss(ts, da + 2u * i, db + 2u * i, (kb > 0 || i > 0) ? 1u : 0u, IDESC_S);
         }
-        mma_commit(s_full);
+        mma_commit(s_full(j & 1));
+        mma_commit(k_empty(j % STAGES));   // the K slot can be refilled as soon as this product is done
       };
-      ok = bar_wait(kv_full(0), 0, abort_flag, status, budget_ns);
+      ok = bar_wait(k_full(0), 0, abort_flag, status, budget_ns);
       if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         issue_s(0);
       }
       for (int j = 0; j < ntiles && ok; ++j) {
-        ok = bar_wait(p_ready, j & 1, abort_flag, status, budget_ns);
+        if (j + 1 < ntiles) {
+          // next tile's scores first: its S buffer was last read for tile j - 1, whose P this thread has already
+          // waited for, and the softmax warps find it ready when they are done with tile j
+          ok = bar_wait(k_full((j + 1) % STAGES), ((j + 1) / STAGES) & 1, abort_flag, status, budget_ns);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          issue_s(j + 1);
+        }
+        ok = bar_wait(p_ready, j & 1, abort_flag, status, budget_ns) &&
+             bar_wait(v_full(j % STAGES), (j / STAGES) & 1, abort_flag, status, budget_ns);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         // O += P . V_j: four steps of 16 keys; V rows are [key][dim], i.e. MN-major for the B operand
@@ -194,15 +226,8 @@ causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, 
 #pragma unroll
         for (int i = 0; i < 4; ++i)
           mma_f16_ss(tmem_o, dp + 2u * i, smem_desc_mn_sw128(vt + i * 16 * 128, TK * 128), (j > 0 || i > 0) ? 1u : 0u, IDESC_PV);
-        mma_commit(kv_empty(j % STAGES));  // the stage is free once these MMAs (and the S MMAs before them) have read it
-        if (j + 1 < ntiles) {
-          ok = bar_wait(kv_full((j + 1) % STAGES), ((j + 1) / STAGES) & 1, abort_flag, status, budget_ns);
-          if (!ok) break;
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          issue_s(j + 1);                  // completes after the P . V above: the pipe runs in order
-        } else {
-          mma_commit(o_final);
-        }
+        mma_commit(pv_done);               // O has taken tile j: P may be overwritten, O rescaled (or, at the end, read)
+        mma_commit(v_empty(j % STAGES));
       }
     }
   } else {                                 // ---- softmax: thread = query row = TMEM lane
@@ -212,9 +237,10 @@ causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, 
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < ntiles && ok; ++j) {
-      ok = __all_sync(0xffffffffu, bar_wait(s_full, j & 1, abort_flag, status, budget_ns));
+      ok = __all_sync(0xffffffffu, bar_wait(s_full(j & 1), (j >> 1) & 1, abort_flag, status, budget_ns));
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t tmem_s = tmem_base + 64u * static_cast<uint32_t>(j & 1);
       uint32_t s0[32], s1[32];
       QMK_TMEM_LD32(s0, tmem_s + lane_base);
       QMK_TMEM_LD32(s1, tmem_s + lane_base + 32u);
@@ -237,8 +263,12 @@ causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, 
       const bool raise = mx > m_used + RESCALE_THRESHOLD;
       const float m_new = raise ? mx : m_used;
       const float alpha = raise ? exp2f(m_used - m_new) : 1.0f;     // first tile: exp2(-inf) = 0, l and O are empty
+      if (j > 0) {   // P of tile j - 1 must have been consumed, and O must be at rest, before either is touched
+        ok = __all_sync(0xffffffffu, bar_wait(pv_done, (j - 1) & 1, abort_flag, status, budget_ns));
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      }
       if (j > 0 && __any_sync(0xffffffffu, raise)) {
-        // O has taken tile j - 1 (s_full of tile j was committed behind it) and nobody else touches it now
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
           uint32_t o[32];
@@ -277,7 +307,7 @@ causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, 
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(p_ready) : "memory");
     }
-    ok = ok && __all_sync(0xffffffffu, bar_wait(o_final, 0, abort_flag, status, budget_ns));
+    ok = ok && __all_sync(0xffffffffu, bar_wait(pv_done, (ntiles - 1) & 1, abort_flag, status, budget_ns));
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float inv = 1.0f / l;

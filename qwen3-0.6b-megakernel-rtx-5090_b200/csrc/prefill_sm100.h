@@ -57,6 +57,7 @@ int make_map_packed(CUtensorMap *map, const void *ptr, uint64_t rows, int K, uin
 int make_map_b(CUtensorMap *map, const void *ptr, uint64_t rows, int K, uint32_t box_rows, int wq, std::string *err);
 int make_map_kv(CUtensorMap *map, const void *cache, uint64_t rows, uint64_t max_seq_len, uint64_t heads, std::string *err);
 int make_map_f16(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t cols, uint32_t box_rows, std::string *err);
+int gemm_sm_count();
 int gemm_box_n(int M, int N);
 int gemm_box_n_fused(int M, int N);   // for launch_gemm_swiglu (N = columns of the gate matrix)
 int ensure_gemm_attrs(std::string *err);
