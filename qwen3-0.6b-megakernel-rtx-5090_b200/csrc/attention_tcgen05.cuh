@@ -55,6 +55,13 @@ constexpr uint32_t IDESC_S = (1u << 4) | (static_cast<uint32_t>(TK >> 3) << 17) 
 constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 16) /* B MN-major */ | (static_cast<uint32_t>(D >> 3) << 17) |
                               (static_cast<uint32_t>(TQ >> 4) << 24);
 
+// 2^x for x <= 8 or so (differences to the row maximum in use): the hardware approximation, flushing the far tail to 0
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 #define QMK_TMEM_LD32(r, taddr)                                                                                       \
   asm volatile(                                                                                                       \
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                                       \
@@ -91,7 +98,6 @@ causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, 
                     int layer_head0, __half *out, int T, int pos0, float scale, unsigned int *status,
                     unsigned long long budget_ns, int first_wave) {
   using namespace qmk_gemm;
-  pdl_trigger();
   extern __shared__ __align__(1024) unsigned char attn_smem[];
   const uint32_t base = s32(attn_smem);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -133,6 +139,7 @@ causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, 
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   pdl_wait();   // queries and this chunk's cache rows come from the kernel launched just before
+  pdl_trigger();
   if (warp >= 2) {
     // Q tile: fp32 -> fp16 (times scale * log2 e, so that the softmax is an exp2), stored as two [128 x 64] tiles in
     // the K-major 128-byte-swizzled layout: row r, 16-byte segment s of a tile at r * 128 + ((s ^ (r & 7)) << 4)
@@ -247,18 +254,18 @@ causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, 
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       const int k0 = j * TK;
       const bool diagonal = k0 + TK - 1 > pos0 + q0;        // some key of the tile is ahead of some query of the CTA
-      float mx = -INFINITY;
+      if (diagonal) {
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        float a = __uint_as_float(s0[c]), b = __uint_as_float(s1[c]);
-        if (diagonal) {
-          if (k0 + c > qpos) a = -INFINITY;
-          if (k0 + 32 + c > qpos) b = -INFINITY;
-          s0[c] = __float_as_uint(a);
-          s1[c] = __float_as_uint(b);
+        for (int c = 0; c < 32; ++c) {
+          if (k0 + c > qpos) s0[c] = __float_as_uint(-INFINITY);
+          if (k0 + 32 + c > qpos) s1[c] = __float_as_uint(-INFINITY);
         }
-        mx = fmaxf(mx, fmaxf(a, b));
       }
+      // (four independent chains: a single running maximum would be 64 dependent instructions)
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], fmaxf(__uint_as_float(s0[c]), __uint_as_float(s1[c])));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // raise the maximum in use only when it is far behind (first tile: always; key 0 is visible to every query)
       const bool raise = mx > m_used + RESCALE_THRESHOLD;
       const float m_new = raise ? mx : m_used;
@@ -285,23 +292,23 @@ causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, 
       // P = exp2(S - m), fp16, into the swizzled A tile: row `row`, eight 16-byte segments of eight keys
       const uint32_t prow = base + OFF_P + static_cast<uint32_t>(row) * 128u;
       const uint32_t x = static_cast<uint32_t>(row & 7);
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int seg = 0; seg < 8; ++seg) {
         uint32_t packed[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int c = seg * 8 + 2 * i;
-          const float a = exp2f(__uint_as_float(c < 32 ? s0[c] : s1[c - 32]) - m_used);
-          const float b = exp2f(__uint_as_float(c + 1 < 32 ? s0[c + 1] : s1[c + 1 - 32]) - m_used);
-          sum += a + b;
+          const float a = fast_exp2(__uint_as_float(c < 32 ? s0[c] : s1[c - 32]) - m_used);
+          const float b = fast_exp2(__uint_as_float(c + 1 < 32 ? s0[c + 1] : s1[c + 1 - 32]) - m_used);
+          sum4[i] += a + b;
           const __half2 h = __floats2half2_rn(a, b);
           packed[i] = *reinterpret_cast<const uint32_t *>(&h);
         }
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + ((static_cast<uint32_t>(seg) ^ x) << 4)),
                      "r"(packed[0]), "r"(packed[1]), "r"(packed[2]), "r"(packed[3]) : "memory");
       }
-      l += sum;
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // P before the MMA's async-proxy reads
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");  // S reads / O writes before the MMAs that follow
       __syncwarp();

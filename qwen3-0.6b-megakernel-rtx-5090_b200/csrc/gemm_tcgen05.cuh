@@ -205,7 +205,6 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                    const Groups groups, int M, int K, unsigned int *status, unsigned long long budget_ns,
                    int selftest_no_loads) {
   static_assert(BN == 32 || BN == 64 || BN == 128, "N tiles of 32, 64 or 128 columns");
-  pdl_trigger();   // the next kernel of a decode step may set itself up (and stream ITS weights) behind this one
   static_assert(!FUSE || BN <= 64, "the fused SwiGLU epilogue keeps two accumulators of at most 64 columns");
   constexpr int SB = FUSE ? 2 * BN : BN;          // B rows held per stage / accumulator columns
   constexpr uint32_t RAW_ROW = raw_row_bytes(WQ);
@@ -305,6 +304,10 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   if (warp == 0) {
     if (lane == 0) {                       // ---- producer
       pdl_wait();                          // A is the preceding kernel's output
+      // Only now may the NEXT kernel of the chain be scheduled (to set itself up and request its weight tiles behind
+      // this one): a kernel that let its dependents go before its own predecessor had completed put three kernels in
+      // flight at once, and the chunked prefill then produced run-to-run different cache rows - at most two overlap.
+      pdl_trigger();
       for (int kb = 0; kb < prologue; ++kb) tma_load_2d(base + kb * STAGE_BYTES, &map_a, (kb0 + kb) * BK, m0, landed(kb));
       int issued = prologue;
       // self test of the bounded waits: the loads are never issued, so the MMA thread's first wait runs out

@@ -15,9 +15,12 @@ namespace qmk_pf {
 // Programmatic dependent launch: the kernels of a decode step are launched with the stream-serialisation attribute,
 // so kernel n + 1 may be scheduled as soon as every CTA of kernel n has executed pdl_trigger(); pdl_wait() then blocks
 // until kernel n has COMPLETED and its writes are visible.  Whatever a kernel does before pdl_wait() - barrier and
-// TMEM set-up, tensor-map prefetch, streaming weights or cache rows no kernel of the step writes - overlaps the tail
-// of its predecessor.  Every kernel of the chain waits before its first dependent read and before any global write,
-// so completion of kernel n implies completion of all earlier ones.  Without the launch attribute both are no-ops.
+// TMEM set-up, tensor-map prefetch, streaming weights or cache rows no kernel of the step writes - overlaps its
+// predecessor.  Every kernel of the chain waits before its first dependent read and before any global write, and
+// triggers only AFTER its own wait: kernel n + 1 then starts no earlier than the completion of kernel n - 1, so at
+// most two kernels are in flight.  (With the trigger in front of the wait three and more overlapped, and although
+// every kernel still waited for its predecessor the prefill chain produced run-to-run different results.)  Without
+// the launch attribute both are no-ops.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
@@ -39,8 +42,8 @@ __device__ __forceinline__ float warp_max(float v) {
 // then a 16-byte trailer with the fp32 row scale); 2 NVFP4 rows (H / 2 bytes of e2m1 pairs, low nibble first, H / 16
 // e4m3 block scales, then the trailer with the fp32 tensor scale).
 __global__ void embed_rows(const int *tokens, const void *embed, int wq, float *x) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   float *out = x + static_cast<size_t>(t) * H;
   if (wq == 0) {
@@ -70,8 +73,8 @@ __global__ void embed_rows(const int *tokens, const void *embed, int wq, float *
 // added in index order.
 __global__ void add_rmsnorm_rows(float *x, const float *add, int nparts, size_t part_stride, const __half *w, __half *y) {
   __shared__ float red[8];
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   float *xr = x + static_cast<size_t>(t) * H;
   float v[4];
@@ -116,8 +119,8 @@ __global__ void qk_norm_rope_cache(const float *q, const float *k, const float *
                                    const __half *k_norm, const float *rope, const __half *cos_table,
                                    const __half *sin_table, float *qr, __half *k_cache_layer, __half *v_cache_layer,
                                    int pos0, int max_seq_len) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x, slot = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   const int pos = pos0 + t;
   if (slot >= 24) {   // V head: plain copy to the cache
@@ -194,8 +197,8 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
 __global__ void __launch_bounds__(ATM_THREADS) causal_attention_mma(const float *qr, const __half *k_cache_layer,
                                                             const __half *v_cache_layer, __half *out, int T, int pos0,
                                                             int max_seq_len, float scale) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   // two stages of (K tile, V tile): the next 64 keys are fetched with cp.async while this tile is multiplied
   extern __shared__ __align__(16) unsigned char atm_smem[];
   __half *const tiles = reinterpret_cast<__half *>(atm_smem);
@@ -374,7 +377,6 @@ __global__ void __launch_bounds__((DAR_WARPS + 1) * 32) decode_attention_ring(
   extern __shared__ __align__(128) unsigned char dar_smem[];
   __shared__ __align__(16) float sq[2 * D];
   __shared__ float sknew[D], svnew[D], snew_score[2];
-  pdl_trigger();
   __shared__ float sm[DAR_WARPS][2], sl[DAR_WARPS][2];
   __shared__ __align__(16) float sacc[DAR_WARPS][2][D];
   uint64_t *full = reinterpret_cast<uint64_t *>(dar_smem + DAR_SLOTS * DAR_SLOT_BYTES);
@@ -433,7 +435,10 @@ __global__ void __launch_bounds__((DAR_WARPS + 1) * 32) decode_attention_ring(
   __syncthreads();
   // The producer streams cache rows written by EARLIER steps, so it starts at once; everyone else reads what the
   // q/k/v GEMM launched just before wrote, and writes (cache row, output, split partials) only after it completed.
-  if (warp != DAR_WARPS) pdl_wait();
+  if (warp != DAR_WARPS) {
+    pdl_wait();
+    if (threadIdx.x == 0) pdl_trigger();   // (after the wait: at most two kernels of a chain overlap)
+  }
   if (warp == DAR_WARPS) {            // ---- producer: old rows [0, pos) in chunks of 32
     if (lane == 0) {
       int issued = 0;
@@ -649,8 +654,8 @@ __global__ void __launch_bounds__(1024) argmax_rows(const float *logits, int voc
                                                     const int *start_positions, int *positions) {
   __shared__ float sv[32];
   __shared__ int si[32];
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int b = blockIdx.x;
   const float *row = logits + static_cast<size_t>(b) * vocab;
   float best = -INFINITY;
@@ -691,8 +696,8 @@ __global__ void __launch_bounds__(256) argmax_pairs(const float *val, const int 
                                                     const int *start_positions, int *positions) {
   __shared__ float sv[8];
   __shared__ int si[8];
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int b = blockIdx.x;
   float best = -INFINITY;
   int best_i = 0x7fffffff;

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 #include <mutex>
 #include <string>
@@ -538,7 +539,10 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
       if (rc != QMK_OK) break;
     }
     PF_CUDA(cudaMemcpyAsync(w.tokens, token_ids_host + c0, sizeof(int) * T, cudaMemcpyHostToDevice, stream));
-    qmk_tc::PdlScope pdl_scope(env.pdl != 0);   // every launch below may start behind its predecessor's tail
+    // Plain launches: programmatic dependent launch was tried on this chain too; it gained nothing (these kernels are
+    // long) and a decode launched after such a prefill produced run-to-run different logits although every cache
+    // row compared bit-identical afterwards - unexplained, so the chain stays strictly serial.
+    qmk_tc::PdlScope pdl_scope(false);
     qmk_tc::RingBudgetScope ring_scope(PREFILL_RING_BYTES);   // two GEMM CTAs per SM: one's epilogue under the other's main loop
     {
       qmk_tc::PdlScope first(false);            // (follows a copy, not a kernel)
@@ -555,6 +559,8 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
         const int ns[3] = {QS, KVS, KVS};
         if ((rc = gemm_group(w.map_xn, l, 3, js, cs, ns, M, H, T)) != QMK_OK) break;
       }
+      // (Folding this kernel into the q/k/v GEMM's epilogue - one 128-wide N tile is one head - was built and measured
+      // slower: 128 threads per CTA walking TMEM eight columns at a time lose to 2300 x 4 fully parallel CTAs.)
       PF_CUDA(qmk_tc::launch_kernel(qk_norm_rope_cache, dim3(T, 4), dim3(256), 0, stream, w.q, w.k, w.v,
                                     reinterpret_cast<const __half *>(r[4]), reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv,
                                     w.qr, kc, vc, pos0, max_seq_len));

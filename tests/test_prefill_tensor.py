@@ -95,19 +95,50 @@ def test_appends_at_a_start_position_and_agrees_with_serial_prefill(C):
     assert kerr < CACHE_TOL and verr < CACHE_TOL
 
 
-def test_table_rope_mode(C):
-    vocab, L = 2048, 256
+@pytest.mark.parametrize("n_prompt", [150, 900])
+def test_table_rope_mode(C, n_prompt):
+    """fp16 cos / sin tables instead of the fp32 in-library table: 150 tokens take the row kernel for QK-norm + RoPE,
+    900 tokens the q/k/v GEMM's per-head epilogue (128-wide tiles)."""
+    vocab, L = 2048, 1024
     w = S.make_weights(seed=14, num_layers=2, vocab_size=vocab, norm_std=0.1, max_seq_len=L)
-    ids = S.make_prompt(150, seed=4, vocab_size=vocab)
+    ids = S.make_prompt(n_prompt, seed=4, vocab_size=vocab)
     o = OracleDecoder(w, max_seq_len=L, rope_from_tables=True)
     want, _ = o.generate_ids(ids, 3)
     eng = _engine(w, L, "tensor", rope_from_table=True)
     try:
         got = eng.generate_ids(ids, 3)
-        kerr = float((eng._k_cache[:, :, :149].float().cpu() - o.k_cache[:, :, :149].float()).abs().max())
+        n = n_prompt - 1
+        kerr = float((eng._k_cache[:, :, :n].float().cpu() - o.k_cache[:, :, :n].float()).abs().max())
     finally:
         C.configure(rope_from_table=0)
     assert kerr < CACHE_TOL and got == want
+
+
+@pytest.mark.parametrize("impl", [0, 1])
+def test_both_attention_kernels(C, impl):
+    """The tcgen05 attention kernel (default) and the mma.sync one, each against the oracle on a two-chunk prompt
+    whose second chunk starts inside a key tile (positions 2048 .. 2249)."""
+    vocab, steps, L, n = 2048, 3, 2304, 2250
+    w = S.make_weights(seed=15, num_layers=2, vocab_size=vocab, norm_std=0.1, max_seq_len=16)
+    ids = S.make_prompt(n + 1, seed=8, vocab_size=vocab)
+    o = OracleDecoder(w, max_seq_len=L)
+    want, logits = o.generate_ids(ids, steps, keep_logits=True)
+    eng = _engine(w, L, "tensor")
+    dump = torch.zeros(steps, vocab, device="cuda")
+    C.set_prefill_attention(impl)
+    C.set_logits_dump(dump)
+    try:
+        got = eng.generate_ids(ids, steps)
+    finally:
+        C.set_logits_dump(None)
+        C.set_prefill_attention(1)
+    kerr = float((eng._k_cache[:, :, :n].float().cpu() - o.k_cache[:, :, :n].float()).abs().max())
+    verr = float((eng._v_cache[:, :, :n].float().cpu() - o.v_cache[:, :, :n].float()).abs().max())
+    lerr = float((dump.cpu() - logits).abs().max())
+    print(f"attention impl {impl}: cache max err K {kerr:.2e} V {verr:.2e}; logits max err {lerr:.2e}; tokens {got} / {want}; "
+          f"per step {[float((dump[i].cpu() - logits[i]).abs().max()) for i in range(steps)]}")
+    assert kerr < CACHE_TOL and verr < CACHE_TOL and lerr < LOGIT_TOL
+    assert got == want
 
 
 def test_refusals(C):
