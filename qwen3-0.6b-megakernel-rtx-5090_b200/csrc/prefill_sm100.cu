@@ -127,8 +127,9 @@ static int sm_count() {
   }
   return sms > 0 ? sms : 148;
 }
+thread_local unsigned int t_ring_budget = 0;   // shared-memory budget of the ring (0 = the compile-time depth, one CTA per SM)
 static int pick_box_n(int M, int N, int b_tiles) {
-  const int sms = sm_count();
+  const int sms = sm_count() * (t_ring_budget ? 2 : 1);   // CTA slots of one wave: rings sized to a budget share an SM in pairs
   int best = 0;
   long best_cost = 0;
   for (int bn = b_tiles == 2 ? 64 : 128; bn >= 32; bn /= 2) {
@@ -210,7 +211,6 @@ static bool set_packed(qmk_gemm::Groups *gr, int wq, int K, int ngroups, const v
 // Ring depth of a launch (see qmk_gemm::ring_geometry): `sb` = B rows per stage; returns the dynamic shared memory.
 thread_local float *t_amax_val = nullptr;   // the next single-matrix GEMM of this thread leaves (value, column) pairs here
 thread_local int *t_amax_idx = nullptr;
-thread_local unsigned int t_ring_budget = 0;   // shared-memory budget of the ring (0 = the compile-time depth, one CTA per SM)
 static size_t set_ring(qmk_gemm::Groups *gr, int sb, int wq) {
   const qmk_gemm::RingGeometry g = qmk_gemm::ring_geometry(sb, wq, t_ring_budget);
   gr->stages = g.stages;
