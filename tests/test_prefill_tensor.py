@@ -141,6 +141,28 @@ def test_both_attention_kernels(C, impl):
     assert got == want
 
 
+def test_decode_after_tensor_prefill_is_reproducible(C):
+    """Prefill on the tensor cores, then greedy decode on the persistent kernel, eight times over: tokens and every
+    logit must come out bit-identical (a prefill chain launched as programmatic dependents once left the decode that
+    followed it different from run to run, with identical cache rows)."""
+    vocab, steps, L, n = 2048, 3, 2560, 2300
+    w = S.make_weights(seed=15, num_layers=3, vocab_size=vocab, norm_std=0.1, max_seq_len=16)
+    ids = S.make_prompt(n + 1, seed=8, vocab_size=vocab)
+    eng = _engine(w, L, "tensor")
+    runs = []
+    for _ in range(8):
+        dump = torch.zeros(steps, vocab, device="cuda")
+        C.set_logits_dump(dump)
+        try:
+            got = eng.generate_ids(ids, steps)
+        finally:
+            C.set_logits_dump(None)
+        runs.append((got, dump.cpu()))
+    assert all(r[0] == runs[0][0] for r in runs)
+    assert all(torch.equal(r[1], runs[0][1]) for r in runs)
+    assert runs[0][0] == OracleDecoder(w, max_seq_len=L).generate_ids(ids, steps)[0]
+
+
 def test_refusals(C):
     import quantize as Q
     w = S.make_weights(seed=1, num_layers=2, vocab_size=512, max_seq_len=16)
