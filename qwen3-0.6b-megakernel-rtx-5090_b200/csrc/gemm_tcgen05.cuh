@@ -38,7 +38,9 @@ namespace qmk_gemm {
 constexpr int BM = 128, BK = 64;                 // BK * 2 bytes = one 128-byte swizzle row; the N tile (128 or 64) is a template parameter
 // Ring depth per N-tile variant: as many stages as fit in ~192 KB (a skinny M = 128 problem is bound by the
 // latency of its K loop, so the whole K extent of a 1024-wide matrix is in flight at once).
-constexpr int stages_for(int bn, int wq = 0) { return wq ? (bn == 32 ? 8 : bn == 64 ? 6 : 4) : (bn == 32 ? 10 : bn == 64 ? 8 : 6); }
+constexpr int stages_for(int bn, int wq = 0) {
+  return wq ? (bn == 32 ? 8 : bn == 64 ? 6 : bn == 128 ? 4 : 2) : (bn == 32 ? 10 : bn == 64 ? 8 : bn == 128 ? 6 : 4);
+}
 constexpr int MAX_GROUPS = 3;   // matrices sharing one A operand that one launch can multiply (q/k/v, gate/up)
 constexpr int THREADS = 192;
 constexpr uint32_t TILE_A_BYTES = BM * BK * 2;   // 16 KB
@@ -204,8 +206,9 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                    const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_b2,
                    const Groups groups, int M, int K, unsigned int *status, unsigned long long budget_ns,
                    int selftest_no_loads) {
-  static_assert(BN == 32 || BN == 64 || BN == 128, "N tiles of 32, 64 or 128 columns");
-  static_assert(!FUSE || BN <= 64, "the fused SwiGLU epilogue keeps two accumulators of at most 64 columns");
+  static_assert(BN == 32 || BN == 64 || BN == 128 || BN == 256, "N tiles of 32, 64, 128 or 256 columns");
+  static_assert(!FUSE || BN <= 128, "the fused SwiGLU epilogue keeps two accumulators of at most 128 columns (one MMA of N = 256)");
+  static_assert(WQ == 0 || (FUSE ? 2 * BN : BN) <= 128, "packed weights: at most 128 B rows per stage (scales live in shared memory)");
   constexpr int SB = FUSE ? 2 * BN : BN;          // B rows held per stage / accumulator columns
   constexpr uint32_t RAW_ROW = raw_row_bytes(WQ);
   const int STAGES = groups.stages;

@@ -159,7 +159,10 @@ static GemmKernel gemm_kernel_wq(int bn, bool fuse) {
   return bn == 32 ? qmk_gemm::gemm_f16_tn_kernel<32, false, WQ>
                   : bn == 64 ? qmk_gemm::gemm_f16_tn_kernel<64, false, WQ> : qmk_gemm::gemm_f16_tn_kernel<128, false, WQ>;
 }
+// (the widest tiles - 256 B rows per stage - exist for fp16 weights only)
 static GemmKernel gemm_kernel(int bn, bool fuse, int wq) {
+  if (wq == 0 && fuse && bn == 128) return qmk_gemm::gemm_f16_tn_kernel<128, true, 0>;
+  if (wq == 0 && !fuse && bn == 256) return qmk_gemm::gemm_f16_tn_kernel<256, false, 0>;
   return wq == 0 ? gemm_kernel_wq<0>(bn, fuse) : wq == 1 ? gemm_kernel_wq<1>(bn, fuse) : gemm_kernel_wq<2>(bn, fuse);
 }
 static size_t gemm_smem(int bn, bool fuse, int wq) { return qmk_gemm::smem_bytes_for(fuse ? 2 * bn : bn, wq); }
@@ -173,7 +176,7 @@ int ensure_gemm_attrs(std::string *err) {
     cudaError_t e = cudaSuccess;
     for (int wq = 0; wq < 3 && e == cudaSuccess; ++wq)
       for (int fuse = 0; fuse < 2 && e == cudaSuccess; ++fuse)
-        for (int bn = 32; bn <= (fuse ? 64 : 128) && e == cudaSuccess; bn *= 2)
+        for (int bn = 32; bn <= (fuse ? 64 : 128) * (wq == 0 ? 2 : 1) && e == cudaSuccess; bn *= 2)
           e = cudaFuncSetAttribute(reinterpret_cast<const void *>(gemm_kernel(bn, fuse != 0, wq)),
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(gemm_smem(bn, fuse != 0, wq)));
     if (e == cudaSuccess)
@@ -239,9 +242,10 @@ static bool a_box_ok(int a_box_rows, int M, int *rows, uint32_t *a_box_bytes, st
 int launch_gemm_grouped(const CUtensorMap &map_a, int ngroups, const CUtensorMap *const *maps_b, float *const *Cs,
                         const int *Ns, int M, int K, int box_n, unsigned int *status, int timeout_ms, cudaStream_t stream,
                         std::string *err, int live_rows, int a_box_rows, int wq, const void *const *raws) {
-  bool bad = M <= 0 || K <= 0 || M % qmk_gemm::BM || K % qmk_gemm::BK || (box_n != 32 && box_n != 64 && box_n != 128) ||
+  bool bad = M <= 0 || K <= 0 || M % qmk_gemm::BM || K % qmk_gemm::BK ||
+             (box_n != 32 && box_n != 64 && box_n != 128 && !(box_n == 256 && wq == 0)) ||
              ngroups < 1 || ngroups > qmk_gemm::MAX_GROUPS;
-  for (int g = 0; !bad && g < ngroups; ++g) bad = Ns[g] <= 0 || Ns[g] % 128;
+  for (int g = 0; !bad && g < ngroups; ++g) bad = Ns[g] <= 0 || Ns[g] % (box_n > 128 ? box_n : 128);
   if (bad) {
     *err = "gemm: M and N must be multiples of 128 and K a multiple of 64";
     return QMK_ERR_BAD_ARGUMENT;
@@ -277,7 +281,8 @@ int launch_gemm_grouped(const CUtensorMap &map_a, int ngroups, const CUtensorMap
 int launch_gemm_swiglu(const CUtensorMap &map_a, const CUtensorMap &map_gate, const CUtensorMap &map_up, __half *act, int M,
                        int N, int K, unsigned int *status, int timeout_ms, cudaStream_t stream, std::string *err,
                        int box_n, int live_rows, int a_box_rows, int wq, const void *raw_gate, const void *raw_up) {
-  if (M <= 0 || N <= 0 || K <= 0 || M % qmk_gemm::BM || N % 128 || K % qmk_gemm::BK || (box_n != 32 && box_n != 64)) {
+  if (M <= 0 || N <= 0 || K <= 0 || M % qmk_gemm::BM || N % 128 || K % qmk_gemm::BK ||
+      (box_n != 32 && box_n != 64 && !(box_n == 128 && wq == 0))) {
     *err = "gemm: M and N must be multiples of 128 and K a multiple of 64";
     return QMK_ERR_BAD_ARGUMENT;
   }
@@ -347,7 +352,7 @@ int launch_gemm(const CUtensorMap &map_a, const CUtensorMap &map_b, float *C, in
 // ----------------------------------------------------------------------------- chunked prefill
 namespace {
 
-constexpr unsigned int PREFILL_RING_BYTES = 96 * 1024;
+constexpr unsigned int PREFILL_RING_BYTES = 96 * 1024, GATE_UP_RING_BYTES = 64 * 1024;
 constexpr int CHUNK = 2048;         // prompt tokens per pass over the weights (a multiple of the GEMM's 128)
 constexpr int MAX_LAYERS = 48;
 
@@ -386,7 +391,7 @@ struct Workspace {                  // per device, allocated on first use, never
   unsigned long long table[MAX_LAYERS * 12] = {};
   int table_layers = 0;
   int table_wq = 0;                    // weight format the maps below were made for
-  CUtensorMap wmap[MAX_LAYERS][7][2];  // q, k, v, o, gate, up, down; boxes of 64 and of 128 rows
+  CUtensorMap wmap[MAX_LAYERS][7][3];  // q, k, v, o, gate, up, down; boxes of 64, 128 and (fp16 weights) 256 rows
   CUtensorMap wmap32[MAX_LAYERS][7];   // the same matrices in boxes of 32 rows (decode steps: more, smaller tiles)
 };
 // Prefill and batched decode keep separate workspaces and locks: a serving loop prefills the next request on one
@@ -452,8 +457,8 @@ int ensure_weight_maps(Workspace &w, const LDGLayerWeight *layers_dev, int num_l
         const int rc = qmk_tc::make_map_b(&w.wmap32[l][j], ptr, rows[j], cols[j], 32, wq, &err);
         if (rc != QMK_OK) return qmk_internal::report(rc, err);
       }
-      for (int b = 0; b < 2; ++b) {
-        const int rc = qmk_tc::make_map_b(&w.wmap[l][j][b], ptr, rows[j], cols[j], b ? 128 : 64, wq, &err);
+      for (int b = 0; b < (wq == 0 ? 3 : 2); ++b) {
+        const int rc = qmk_tc::make_map_b(&w.wmap[l][j][b], ptr, rows[j], cols[j], 64 << b, wq, &err);
         if (rc != QMK_OK) return qmk_internal::report(rc, err);
       }
     }
@@ -503,7 +508,7 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
   std::string err;
   // weight matrix j of layer l in boxes of `box_n` rows
   auto wmap_for = [&](int l, int j, int box_n) -> const CUtensorMap & {
-    return box_n == 32 ? w.wmap32[l][j] : w.wmap[l][j][box_n == 128];
+    return box_n == 32 ? w.wmap32[l][j] : w.wmap[l][j][box_n == 64 ? 0 : box_n == 128 ? 1 : 2];
   };
   static const int rec_slot[7] = {1, 2, 3, 6, 8, 9, 10};   // q, k, v, o, gate, up, down inside a layer record
   auto wptr = [&](int l, int j) { return reinterpret_cast<const void *>(rec[static_cast<size_t>(l) * 12 + rec_slot[j]]); };
@@ -517,7 +522,11 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
                         int live) {
     int total = 0;
     for (int i = 0; i < n; ++i) total += ns[i];
-    const int box_n = qmk_tc::gemm_box_n(M, total);
+    // Long chunks of fp16 weights: 256-wide tiles (one MMA of N = 256 per K step; a third fewer operand bytes per
+    // flop than 128-wide ones - these GEMMs are bound by the L2 -> shared-memory feed).  Measured on the q/k/v shape at
+    // 2048 rows: 28.8 -> 26.5 us.
+    const int box_n = (wq == 0 && M >= 1024 && total / 256 * (M / qmk_gemm::BM) >= qmk_tc::gemm_sm_count()) ? 256
+                                                                                                           : qmk_tc::gemm_box_n(M, total);
     const CUtensorMap *maps[3];
     const void *raws[3] = {nullptr, nullptr, nullptr};
     for (int i = 0; i < n; ++i) { maps[i] = &wmap_for(l, js[i], box_n); raws[i] = wptr(l, js[i]); }
@@ -578,6 +587,8 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
                                     reinterpret_cast<const __half *>(r[7]), w.xn));
       {
         const int box_gu = qmk_tc::gemm_box_n_fused(M, I);
+        // three of these CTAs per SM instead of two: their epilogue (two TMEM reads, SiLU, fp16 pack) is the long part
+        qmk_tc::RingBudgetScope gu_scope(M >= 1024 ? GATE_UP_RING_BYTES : PREFILL_RING_BYTES);
         if ((rc = qmk_tc::launch_gemm_swiglu(w.map_xn, wmap_for(l, 4, box_gu), wmap_for(l, 5, box_gu), w.act, M, I, H,
                                              w.status, env.timeout_ms, stream, &err, box_gu, T, 0, wq, wptr(l, 4),
                                              wptr(l, 5))) != QMK_OK)
