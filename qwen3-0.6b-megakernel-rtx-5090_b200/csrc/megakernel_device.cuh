@@ -806,7 +806,7 @@ __device__ __noinline__ uint32_t gemv_k1024(const Params &P, Ctx c, int kind, co
                                             float *local_out = nullptr) {
   const int wfmt = P.wfmt;
   float a[32];
-  const int fb = kind == K_QKV ? 0 : 10;
+  [[maybe_unused]] const int fb = kind == K_QKV ? 0 : 10;   // (stamp base of the fine-grained profile build)
   QMK_FINE(fb + 0);
   norm_to_regs(c, x, ss, norm_w, a);
   QMK_FINE(fb + 1);

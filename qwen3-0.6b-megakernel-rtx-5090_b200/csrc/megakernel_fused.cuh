@@ -148,7 +148,7 @@ __device__ __noinline__ uint32_t slice_colgemv(const Params &P, Ctx c, int which
   float acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-  const int fb = which ? 30 : 20;
+  [[maybe_unused]] const int fb = which ? 30 : 20;   // (stamp base of the fine-grained profile build)
   QMK_FINE(fb + 0);
 #pragma unroll 1
   for (int ch = g; ch < nch; ch += CONS_WARPS / 4) {

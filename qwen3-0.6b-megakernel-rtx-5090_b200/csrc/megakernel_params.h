@@ -65,7 +65,6 @@ struct Params {
   const LayerT *layers_t;        // K-major copies, one record per layer
   unsigned long long *red;       // all-reduce words of the two residual sums, zeroed by the host before the launch
   int red_copies;                // accumulator copies per sum (1 or 2): CTA i adds into copy i % red_copies
-  int ll_sleep_ns;               // back-off between polls of the small (few-reader) exchanges
   // Tensor-core build: tiled-copy descriptors (CUtensorMap, 128 bytes each) of the K and V caches seen as
   // [layers * 8 * max_seq_len rows][128] fp16, boxes of 16 rows x 64 columns with the 128-byte swizzle.
   alignas(64) unsigned char kmap[128];

@@ -25,7 +25,7 @@ namespace QMK_NS {
 #if QMK_MAX_SEQ == 1 && defined(QMK_TC_BUILD)
 
 constexpr int TC_MIN_CTAS = 96;                // smallest grid: <= 2 attention outputs per warp to merge, O / down slices of <= 32 rows
-static_assert((QS + TC_MIN_CTAS - 1) / TC_MIN_CTAS <= 2 * CONS_WARPS && TC_MIN_CTAS >= FUSED_MIN_CTAS, "merge_slice2 takes two elements per warp");
+static_assert(TC_MIN_CTAS >= FUSED_MIN_CTAS, "the tensor-core kernel shares the fused kernel's slice layout");
 static_assert(4 * ((I / 4 + TC_MIN_CTAS - 1) / TC_MIN_CTAS) <= 32, "slice_cols takes two k-steps");
 constexpr int ROW_PITCH = 2 * H + 16;          // bytes between the rows of a chunk in shared memory
 constexpr int CH_ROWS = 4;
@@ -577,88 +577,6 @@ __device__ __noinline__ void embed_norm(const Params &P, const Ctx c, int token,
   cons_sync();
 }
 
-// merge_slice (megakernel_fused.cuh) for slices of at most two elements per warp (grids from TC_MIN_CTAS on), without
-// its barrier: every warp fetches the outputs AND the (max, sum) pairs of its elements' heads in one round of polls
-// and makes the split weights itself (15 shuffles per element, the two elements' chains side by side), instead of
-// waiting for the two warps that make them for everybody.
-__device__ __noinline__ void merge_slice2(const Params &P, const Ctx c, int S, uint32_t tag) {
-  float *s_attn = c.f(FF_ATTN);
-  __half *act16 = reinterpret_cast<__half *>(c.smem + OFF_ACT16);
-  const int e0 = c.segs()->e0, e1 = c.segs()->e1;
-  const int s = min(c.lane, S - 1);
-  // words of element q: its unnormalised output, and the (max, sum) pair of its head: part_q + {d_q, 128, 129}
-  const int ea = min(e0 + c.warp, e1 - 1), eb = min(e0 + c.warp + CONS_WARPS, e1 - 1);
-  const unsigned long long *pa = c.llr + LL_PART + static_cast<size_t>((ea >> 7) * MAX_SPLITS + s) * PART_STRIDE;
-  const unsigned long long *pb = c.llr + LL_PART + static_cast<size_t>((eb >> 7) * MAX_SPLITS + s) * PART_STRIDE;
-  const int da = ea & (D - 1), db = eb & (D - 1);
-  uint32_t valid = 0;
-  if (c.lane < S && e0 + c.warp < e1) valid |= 7u;
-  if (c.lane < S && e0 + c.warp + CONS_WARPS < e1) valid |= 56u;
-  unsigned long long w[6];
-  QMK_FINE(50);
-  {
-    uint32_t pending = valid, it = 0;
-    unsigned long long t0 = 0;
-    for (;;) {
-      if (pending & 1u) w[0] = ll_load(pa + da);
-      if (pending & 2u) w[1] = ll_load(pa + D);
-      if (pending & 4u) w[2] = ll_load(pa + D + 1);
-      if (pending & 8u) w[3] = ll_load(pb + db);
-      if (pending & 16u) w[4] = ll_load(pb + D);
-      if (pending & 32u) w[5] = ll_load(pb + D + 1);
-#pragma unroll
-      for (int j = 0; j < 6; ++j)
-        if ((pending & (1u << j)) && static_cast<uint32_t>(w[j] >> 32) == tag) pending &= ~(1u << j);
-      if (pending == 0u) break;
-      if (P.spin_sleep_ns) __nanosleep(P.spin_sleep_ns);
-      if ((++it & 255u) == 0u) {
-        if (c.flags()[0]) break;
-        if (ld_relaxed_u32(P.status) != 0u) { c.flags()[0] = 1; break; }
-        const unsigned long long t = now_ns();
-        if (t0 == 0) t0 = t;
-        if (t - t0 > P.timeout_ns) { raise_error(P, c, QMK_ERR_WAIT_TIMEOUT, WHERE_LL); break; }
-      }
-    }
-  }
-  float v[6];
-#pragma unroll
-  for (int j = 0; j < 6; ++j) v[j] = __uint_as_float(static_cast<uint32_t>(w[j]));
-  QMK_FINE(51);
-  float m[2], M[2], L[2], A[2];
-#pragma unroll
-  for (int q = 0; q < 2; ++q) { m[q] = (valid >> (3 * q)) & 1u ? v[3 * q + 1] : -INFINITY; M[q] = m[q]; }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-    for (int q = 0; q < 2; ++q) M[q] = fmaxf(M[q], __shfl_xor_sync(0xffffffffu, M[q], o));
-#pragma unroll
-  for (int q = 0; q < 2; ++q) {
-    const float sc = (m[q] == -INFINITY) ? 0.f : exp2f(m[q] - M[q]);
-    const bool on = (valid >> (3 * q)) & 1u;
-    L[q] = on ? v[3 * q + 2] * sc : 0.f;
-    A[q] = on ? v[3 * q] * sc : 0.f;
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-    for (int q = 0; q < 2; ++q) {
-      L[q] += __shfl_xor_sync(0xffffffffu, L[q], o);
-      A[q] += __shfl_xor_sync(0xffffffffu, A[q], o);
-    }
-  QMK_FINE(52);
-#pragma unroll
-  for (int q = 0; q < 2; ++q) {
-    const int e = e0 + c.warp + q * CONS_WARPS;
-    if (e < e1 && c.lane == 0) {
-      const float out = A[q] / L[q];
-      s_attn[e - e0] = out;
-      act16[e - e0] = split_half(out, false);
-      act16[ACT16_PITCH + e - e0] = split_half(out, true);
-    }
-  }
-  if (c.tid < 32 && c.tid >= e1 - e0) { act16[c.tid] = __float2half_rn(0.f); act16[ACT16_PITCH + c.tid] = __float2half_rn(0.f); }
-}
-
 // Split-K slice of the O (which = 0) or down (1) projection (see slice_colgemv of megakernel_fused.cuh) on the
 // tensor cores: partial[n] = sum_i act[i] * Wt[first + i][n] with the K-major rows as the A operand read through
 // ldmatrix.trans (tile = 16 outputs x 16 rows, at most two k-steps: slices of at most 32 rows), the slice's
@@ -975,11 +893,7 @@ __global__ void __launch_bounds__(THREADS, 1) qwen3_decode_megakernel_tc(const _
         QMK_STAMP(layer * 12 + 1);
         c.chunk = attention_tc(P, c, nv, layer, pos, tag);
         QMK_STAMP(layer * 12 + 2);
-#ifdef QMK_MERGE2
-        merge_slice2(P, c, S_step, tag);
-#else
         merge_slice(P, c, S_step, tag, reinterpret_cast<__half *>(c.smem + OFF_ACT16));
-#endif
         QMK_STAMP(layer * 12 + 3);
         cons_sync();
         c.chunk = slice_cols(P, c, 0);
