@@ -42,7 +42,9 @@ constexpr int stages_for(int bn, int wq = 0) {
   return wq ? (bn == 32 ? 8 : bn == 64 ? 6 : bn == 128 ? 4 : 2) : (bn == 32 ? 10 : bn == 64 ? 8 : bn == 128 ? 6 : 4);
 }
 constexpr int MAX_GROUPS = 3;   // matrices sharing one A operand that one launch can multiply (q/k/v, gate/up)
-constexpr int THREADS = 192;
+constexpr int THREADS = 192;                     // fp16 weights: producer warp, MMA warp, four epilogue warps
+constexpr int THREADS_PACKED = 320;              // packed weights: four more warps that only expand K blocks
+constexpr int threads_for(int wq) { return wq ? THREADS_PACKED : THREADS; }
 constexpr uint32_t TILE_A_BYTES = BM * BK * 2;   // 16 KB
 // Packed K block of one B row: 64 e4m3 bytes, or 32 bytes of e2m1 pairs
 constexpr uint32_t raw_row_bytes(int wq) { return wq == 1 ? 64u : wq == 2 ? 32u : 0u; }
@@ -58,7 +60,7 @@ constexpr uint32_t scale_bytes_for(int bn, int wq) {
   return wq == 0 ? 0u : static_cast<uint32_t>(bn) * 4u + (wq == 2 ? static_cast<uint32_t>(bn) * BS_PITCH : 0u);
 }
 constexpr int MAX_STAGES = 16;
-constexpr uint32_t BARRIER_BYTES = 512;   // full[16], empty[16], acc_full, raw_full[16], TMEM address, abort flag
+constexpr uint32_t BARRIER_BYTES = 640;   // full[16], empty[16], acc_full, raw_full[16], a_full[16], TMEM address, abort flag
 constexpr size_t smem_bytes_for(int bn, int wq = 0) {
   return 1024 /* alignment slack */ + static_cast<size_t>(stages_for(bn, wq)) * stage_bytes_for(bn, wq) + BARRIER_BYTES +
          scale_bytes_for(bn, wq);
@@ -185,12 +187,18 @@ struct Groups {
   int *amax_idx;
 };
 
-// e2m1 pairs of one byte -> two fp16 values.  (code & 7) << 9 read as fp16 is the e2m1 magnitude times 2^-14 - the
-// two-bit exponent lands in the low exponent bits, subnormal code 1 (0.5) included - so one multiplication by 2^14
-// finishes the conversion exactly; bit 3 is the sign.
-__device__ __forceinline__ __half2 e2m1x2_to_half2(uint32_t byte) {
-  const uint32_t bits = ((byte & 0x07u) << 9) | ((byte & 0x08u) << 12) | ((byte & 0x70u) << 21) | ((byte & 0x80u) << 24);
-  return __hmul2(*reinterpret_cast<const __half2 *>(&bits), __float2half2_rn(16384.0f));
+// Eight e2m1 values of one 32-bit word (element 2 i in the low nibble of byte i) -> four half2 registers.
+__device__ __forceinline__ void e2m1x8_to_half2x4(uint32_t word, uint32_t (&out)[4]) {
+  asm("{\n\t"
+      ".reg .b8 b0, b1, b2, b3;\n\t"
+      "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t"
+      "}"
+      : "=r"(out[0]), "=r"(out[1]), "=r"(out[2]), "=r"(out[3])
+      : "r"(word));
 }
 __device__ __forceinline__ uint32_t e4m3x2_to_half2_bits(uint32_t two_bytes) {
   const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(two_bytes & 0xFFFFu), __NV_E4M3);
@@ -201,7 +209,7 @@ __device__ __forceinline__ uint32_t e4m3x2_to_half2_bits(uint32_t two_bytes) {
 // (gate tile in TMEM columns [0, BN), up tile in [BN, 2 BN)) and its epilogue writes fp16 silu(gate) * up to
 // groups.C[0] (reinterpreted as __half [M x N]) instead of two fp32 matrices.
 template <int BN, bool FUSE = false, int WQ = 0>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(WQ ? THREADS_PACKED : THREADS, 1)
 gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
                    const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_b2,
                    const Groups groups, int M, int K, unsigned int *status, unsigned long long budget_ns,
@@ -224,11 +232,11 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   const uint32_t raw = s32(gemm_smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;                 // swizzled tiles need 1024-byte alignment
   unsigned char *aligned = gemm_smem_raw + (base - raw);
-  const uint32_t bars = base + groups.ring_bytes;               // full[16], empty[16], acc_full, raw_full[16], then scratch
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(aligned + groups.ring_bytes + 8 * (3 * MAX_STAGES + 1));
+  const uint32_t bars = base + groups.ring_bytes;               // full[16], empty[16], acc_full, raw_full[16], a_full[16], then scratch
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(aligned + groups.ring_bytes + 8 * (4 * MAX_STAGES + 1));
   float *s_rowscale = reinterpret_cast<float *>(aligned + groups.ring_bytes + BARRIER_BYTES);   // [SB] (WQ != 0)
   unsigned char *s_bs = reinterpret_cast<unsigned char *>(s_rowscale + SB);                // [SB][BS_PITCH] (WQ == 2)
-  static_assert(8 * (3 * MAX_STAGES + 1) + 8 <= BARRIER_BYTES, "barriers and scratch fit the bytes reserved behind the ring");
+  static_assert(8 * (4 * MAX_STAGES + 1) + 8 <= BARRIER_BYTES, "barriers and scratch fit the bytes reserved behind the ring");
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = tile * BN, m0 = blockIdx.y * BM;
@@ -239,12 +247,18 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   auto full = [&](int s) { return bars + 8u * s; };
   auto empty = [&](int s) { return bars + 8u * (MAX_STAGES + s); };
   const uint32_t acc_full = bars + 8u * (2 * MAX_STAGES);
-  auto raw_full = [&](int s) { return bars + 8u * (2 * MAX_STAGES + 1 + s); };   // packed K block (and A) landed
-  // what the producer's copies of one stage signal: with packed weights the expanding warps wait for them and
-  // arrive on `full` themselves (one warp per stage)
-  auto landed = [&](int s) { return WQ ? raw_full(s) : full(s); };
+  auto raw_full = [&](int s) { return bars + 8u * (2 * MAX_STAGES + 1 + s); };   // packed K block landed
+  auto a_full = [&](int s) { return bars + 8u * (3 * MAX_STAGES + 1 + s); };     // packed weights: the A tile landed
+  // What the producer's copies of one stage signal.  fp16 weights: A and B complete `full` together.  Packed weights:
+  // the packed K block completes `raw_full`, on which the expanding warps wait before they arrive on `full`
+  // themselves (one warp per stage), and the A tile completes `a_full` - on its own barrier, because B does not
+  // depend on the preceding kernel: the first ring fill of weights is requested AND expanded before that kernel has
+  // finished, and when A finally arrives the MMAs start at once.
+  auto b_landed = [&](int s) { return WQ ? raw_full(s) : full(s); };
+  auto a_landed = [&](int s) { return WQ ? a_full(s) : full(s); };
   constexpr uint32_t TILE_RAW_BYTES = BN * RAW_ROW;
-  const uint32_t stage_tx = (groups.a_box_bytes ? groups.a_box_bytes : TILE_A_BYTES) + (FUSE ? 2u : 1u) * (WQ ? TILE_RAW_BYTES : TILE_B_BYTES);
+  const uint32_t a_tx = groups.a_box_bytes ? groups.a_box_bytes : TILE_A_BYTES;
+  const uint32_t b_tx = (FUSE ? 2u : 1u) * (WQ ? TILE_RAW_BYTES : TILE_B_BYTES);
   constexpr uint32_t TILE_A = TILE_A_BYTES;   // the B tile follows the A tile in a stage
   const int kcol = WQ ? static_cast<int>(RAW_ROW) : BK;          // B-map columns (bytes for packed rows) per K block
   const uint32_t b_dst = WQ ? TILE_A + (FUSE ? 2u : 1u) * TILE_B_BYTES : TILE_A;   // where the B copies land in a stage
@@ -257,9 +271,9 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map_b)) : "memory");
     if (FUSE) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b1)) : "memory");
     for (int s = 0; s < STAGES; ++s) {
-      bar_init(full(s), 1);
+      bar_init(full(s), WQ ? 2 : 1);      // packed weights: the two warps that expand a stage arrive
       bar_init(empty(s), 1);
-      if (WQ) bar_init(raw_full(s), 1);
+      if (WQ) { bar_init(raw_full(s), 1); bar_init(a_full(s), 1); }
     }
     bar_init(acc_full, 1);
     *abort_flag = 0;
@@ -267,12 +281,12 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     // B is a weight matrix: its first tiles are requested before the wait for the preceding kernel (whose output is
     // A, requested behind the wait below), so the weight stream of this GEMM overlaps that kernel's tail
     for (int kb = 0; kb < prologue; ++kb) {
-      bar_expect_tx(landed(kb), stage_tx);
-      tma_load_2d(base + kb * STAGE_BYTES + b_dst, map_b, (kb0 + kb) * kcol, n0, landed(kb));
-      if (FUSE) tma_load_2d(base + kb * STAGE_BYTES + b_dst + b_dst_step, &map_b1, (kb0 + kb) * kcol, n0, landed(kb));
+      bar_expect_tx(b_landed(kb), WQ ? b_tx : a_tx + b_tx);
+      tma_load_2d(base + kb * STAGE_BYTES + b_dst, map_b, (kb0 + kb) * kcol, n0, b_landed(kb));
+      if (FUSE) tma_load_2d(base + kb * STAGE_BYTES + b_dst + b_dst_step, &map_b1, (kb0 + kb) * kcol, n0, b_landed(kb));
     }
   }
-  if (WQ != 0 && warp >= 2) {
+  if (WQ != 0 && warp >= 2 && warp < 6) {
     // scales of this CTA's B rows into shared memory while the first copies are in flight (the CTA-wide barrier below
     // publishes them): the fp32 row / tensor scale of every row and, for NVFP4, the block scales of the K range
     const int ct = static_cast<int>(threadIdx.x) - 64;          // 0..127
@@ -311,24 +325,28 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       // this one): a kernel that let its dependents go before its own predecessor had completed put three kernels in
       // flight at once, and the chunked prefill then produced run-to-run different cache rows - at most two overlap.
       pdl_trigger();
-      for (int kb = 0; kb < prologue; ++kb) tma_load_2d(base + kb * STAGE_BYTES, &map_a, (kb0 + kb) * BK, m0, landed(kb));
+      for (int kb = 0; kb < prologue; ++kb) {
+        if (WQ) bar_expect_tx(a_full(kb), a_tx);
+        tma_load_2d(base + kb * STAGE_BYTES, &map_a, (kb0 + kb) * BK, m0, a_landed(kb));
+      }
       int issued = prologue;
       // self test of the bounded waits: the loads are never issued, so the MMA thread's first wait runs out
       for (int kb = prologue; kb < (selftest_no_loads ? 0 : kblocks); ++kb) {
         const int s = kb % STAGES;
         if (kb >= STAGES && !bar_wait(empty(s), ((kb / STAGES) - 1) & 1, abort_flag, status, budget_ns)) break;
         if (*abort_flag) break;
-        bar_expect_tx(landed(s), stage_tx);
-        tma_load_2d(base + s * STAGE_BYTES, &map_a, (kb0 + kb) * BK, m0, landed(s));
-        tma_load_2d(base + s * STAGE_BYTES + b_dst, map_b, (kb0 + kb) * kcol, n0, landed(s));
-        if (FUSE) tma_load_2d(base + s * STAGE_BYTES + b_dst + b_dst_step, &map_b1, (kb0 + kb) * kcol, n0, landed(s));
+        bar_expect_tx(b_landed(s), WQ ? b_tx : a_tx + b_tx);
+        if (WQ) bar_expect_tx(a_full(s), a_tx);
+        tma_load_2d(base + s * STAGE_BYTES, &map_a, (kb0 + kb) * BK, m0, a_landed(s));
+        tma_load_2d(base + s * STAGE_BYTES + b_dst, map_b, (kb0 + kb) * kcol, n0, b_landed(s));
+        if (FUSE) tma_load_2d(base + s * STAGE_BYTES + b_dst + b_dst_step, &map_b1, (kb0 + kb) * kcol, n0, b_landed(s));
         issued = kb + 1;
       }
       // after an abort the copies already issued must land before the CTA can exit
       if (*abort_flag) {
         for (int kb = (issued > STAGES ? issued - STAGES : 0); kb < issued; ++kb) {
           const unsigned long long t0 = gtime();
-          while (!bar_try(landed(kb % STAGES), (kb / STAGES) & 1)) {
+          while (!(bar_try(b_landed(kb % STAGES), (kb / STAGES) & 1) && bar_try(a_landed(kb % STAGES), (kb / STAGES) & 1))) {
             if (gtime() - t0 > (budget_ns > 2000000ull ? budget_ns : 2000000ull)) break;   // landing takes microseconds
           }
         }
@@ -339,7 +357,8 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       bool ok = true;
       for (int kb = 0; kb < kblocks && ok; ++kb) {
         const int s = kb % STAGES;
-        ok = bar_wait(full(s), (kb / STAGES) & 1, abort_flag, status, budget_ns);
+        ok = bar_wait(full(s), (kb / STAGES) & 1, abort_flag, status, budget_ns) &&
+             (!WQ || bar_wait(a_full(s), (kb / STAGES) & 1, abort_flag, status, budget_ns));
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint64_t da = smem_desc_sw128(base + s * STAGE_BYTES);
@@ -354,19 +373,20 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       }
       if (ok) mma_commit(acc_full);         // accumulator complete
     }
-  } else {                                 // ---- epilogue: warps 2..5 own TMEM lanes 32 * (warp % 4) ..
+  } else {                                 // ---- warps 2..5: epilogue, each owns TMEM lanes 32 * (warp % 4) ..; packed
+                                           //      weights: first they and warps 6..9 expand the K blocks
     const int quarter = warp & 3;
     if (WQ) {
-      // ---- expansion of the packed K blocks (these warps have nothing else to do until the accumulator is done)
-      // Each of the four warps expands the K blocks of its own stages (stage mod 4 == its index): the chain wait -> load
-      // -> convert -> store -> fence -> arrive is latency, not throughput, so four chains in flight finish a K loop four
-      // times sooner than four warps sharing every block.  A warp owns STAGES, not K blocks: it then meets the uses
-      // of a stage's barrier in order - a parity wait cannot tell use u from use u - 2, so a warp that reached use
-      // u of a stage before anyone had waited for use u - 1 would run ahead on stale data.
+      // Eight warps expand: stage s belongs to the two warps whose (index mod 4) is s mod 4, each takes every other
+      // 16-value chunk of it and arrives on `full` (count 2).  The chain wait -> load -> convert -> store -> fence ->
+      // arrive is latency, so several chains run side by side; and a warp owns STAGES, not K blocks: it then meets
+      // the uses of a stage's barrier in order - a parity wait cannot tell use u from use u - 2, so a warp that
+      // reached use u of a stage before anyone had waited for use u - 1 would run ahead on stale data.
+      const int cw = warp - 2, part = cw >> 2;
       bool live = !selftest_no_loads;
       for (int kb = 0; kb < kblocks && live; ++kb) {
         const int s = kb % STAGES;
-        if ((s & 3) != quarter) continue;
+        if ((s & 3) != (cw & 3)) continue;
         live = __all_sync(0xffffffffu, bar_wait(raw_full(s), (kb / STAGES) & 1, abort_flag, status, budget_ns));
         if (!live) break;
         const uint32_t btile = base + s * STAGE_BYTES + TILE_A;
@@ -374,7 +394,7 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         // one 16-value chunk per lane and pass: chunk i = row * 4 + quarter of the 64-wide K block; the packed
         // rows are dense, so consecutive lanes read consecutive bytes
 #pragma unroll 4
-        for (int i = lane; i < SB * 4; i += 32) {
+        for (int i = lane + 32 * part; i < SB * 4; i += 64) {
           const int r = i >> 2, c = i & 3;
           uint32_t h[8];
           if (WQ == 1) {
@@ -389,10 +409,13 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(v0), "=r"(v1) : "r"(rawt + i * 8));
             const uint32_t sb2 = e4m3x2_to_half2_bits(s_bs[r * BS_PITCH + 4 * kb + c]);   // low half = the block's scale
             const __half2 sc = __half2half2(__ushort_as_half(static_cast<unsigned short>(sb2 & 0xFFFFu)));
+            uint32_t lo[4], hi[4];
+            e2m1x8_to_half2x4(v0, lo);
+            e2m1x8_to_half2x4(v1, hi);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const __half2 a = __hmul2(e2m1x2_to_half2((v0 >> (8 * j)) & 0xFFu), sc);
-              const __half2 b = __hmul2(e2m1x2_to_half2((v1 >> (8 * j)) & 0xFFu), sc);
+            for (int j = 0; j < 4; ++j) {       // e2m1 x e4m3 has six significant bits: exact in fp16
+              const __half2 a = __hmul2(*reinterpret_cast<const __half2 *>(&lo[j]), sc);
+              const __half2 b = __hmul2(*reinterpret_cast<const __half2 *>(&hi[j]), sc);
               h[j] = *reinterpret_cast<const uint32_t *>(&a);
               h[4 + j] = *reinterpret_cast<const uint32_t *>(&b);
             }
@@ -408,6 +431,7 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(full(s)) : "memory");
       }
     }
+    if (warp < 6) {
     // warp-uniform outcome: the TMEM loads below are warp-wide instructions
     const bool ok = __all_sync(0xffffffffu, bar_wait(acc_full, 0, abort_flag, status, budget_ns));
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -497,6 +521,7 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         groups.amax_idx[static_cast<size_t>(row) * gridDim.x + blockIdx.x] = best_col;
       }
     }
+    }   // warps 2..5
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();

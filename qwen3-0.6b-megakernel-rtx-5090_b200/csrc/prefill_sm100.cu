@@ -270,7 +270,7 @@ int launch_gemm_grouped(const CUtensorMap &map_a, int ngroups, const CUtensorMap
   int rows = live_rows > 0 ? live_rows : M;   // rows the epilogue stores (the rest of the tile is padding)
   if (!a_box_ok(a_box_rows, M, &rows, &gr.a_box_bytes, err)) return QMK_ERR_BAD_ARGUMENT;
   const size_t smem = set_ring(&gr, box_n, wq);
-  cudaError_t e = launch_kernel(gemm_kernel(box_n, false, wq), grid, dim3(qmk_gemm::THREADS), smem, stream,
+  cudaError_t e = launch_kernel(gemm_kernel(box_n, false, wq), grid, dim3(qmk_gemm::threads_for(wq)), smem, stream,
                                 map_a, b0, b1, b2, gr, rows, K, status, budget, 0);
   if (e != cudaSuccess) { *err = std::string("gemm launch: ") + cudaGetErrorString(e); return QMK_ERR_CUDA; }
   return QMK_OK;
@@ -301,7 +301,7 @@ int launch_gemm_swiglu(const CUtensorMap &map_a, const CUtensorMap &map_gate, co
   if (!a_box_ok(a_box_rows, M, &rows, &gr.a_box_bytes, err)) return QMK_ERR_BAD_ARGUMENT;
   const unsigned long long budget = static_cast<unsigned long long>(timeout_ms) * 1000000ull;
   const size_t smem = set_ring(&gr, 2 * box_n, wq);
-  cudaError_t e = launch_kernel(gemm_kernel(box_n, true, wq), dim3(N / box_n, M / qmk_gemm::BM), dim3(qmk_gemm::THREADS),
+  cudaError_t e = launch_kernel(gemm_kernel(box_n, true, wq), dim3(N / box_n, M / qmk_gemm::BM), dim3(qmk_gemm::threads_for(wq)),
                                 smem, stream, map_a, map_gate, map_up, map_up, gr, rows, K, status, budget, 0);
   if (e != cudaSuccess) { *err = std::string("gemm launch: ") + cudaGetErrorString(e); return QMK_ERR_CUDA; }
   return QMK_OK;
@@ -331,7 +331,7 @@ int launch_gemm_splitk(const CUtensorMap &map_a, const CUtensorMap &map_b, float
   if (!a_box_ok(a_box_rows, M, &rows, &gr.a_box_bytes, err)) return QMK_ERR_BAD_ARGUMENT;
   const unsigned long long budget = static_cast<unsigned long long>(timeout_ms) * 1000000ull;
   const size_t smem = set_ring(&gr, box_n, wq);
-  cudaError_t e = launch_kernel(gemm_kernel(box_n, false, wq), dim3(N / box_n, M / qmk_gemm::BM, splits), dim3(qmk_gemm::THREADS),
+  cudaError_t e = launch_kernel(gemm_kernel(box_n, false, wq), dim3(N / box_n, M / qmk_gemm::BM, splits), dim3(qmk_gemm::threads_for(wq)),
                                 smem, stream, map_a, map_b, map_b, map_b, gr, rows, K, status, budget, 0);
   if (e != cudaSuccess) { *err = std::string("gemm launch: ") + cudaGetErrorString(e); return QMK_ERR_CUDA; }
   return QMK_OK;
