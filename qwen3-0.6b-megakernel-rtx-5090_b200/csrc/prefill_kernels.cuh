@@ -75,27 +75,20 @@ __global__ void add_rmsnorm_rows(float *x, const float *add, int nparts, size_t 
   __shared__ float red[8];
   pdl_wait();
   pdl_trigger();
-  const int t = blockIdx.x;
+  const int t = blockIdx.x, k0 = 4 * threadIdx.x;        // four consecutive elements per thread: 16-byte accesses
   float *xr = x + static_cast<size_t>(t) * H;
-  float v[4];
-  float ss = 0.f;
   constexpr int MAX_PARTS = 4;   // all loads of a thread are issued before the first add (one L2 round trip)
-  float part[4][MAX_PARTS];
+  float4 v = *reinterpret_cast<const float4 *>(xr + k0);
+  float4 part[MAX_PARTS];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int k = threadIdx.x + j * 256;
-    v[j] = xr[k];
+  for (int p = 0; p < MAX_PARTS; ++p)
+    part[p] = (add && p < nparts) ? *reinterpret_cast<const float4 *>(add + p * part_stride + static_cast<size_t>(t) * H + k0)
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+  const uint2 wraw = *reinterpret_cast<const uint2 *>(w + k0);
 #pragma unroll
-    for (int p = 0; p < MAX_PARTS; ++p)
-      part[j][p] = (add && p < nparts) ? add[p * part_stride + static_cast<size_t>(t) * H + k] : 0.f;
-  }
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-#pragma unroll
-    for (int p = 0; p < MAX_PARTS; ++p)
-      if (add && p < nparts) v[j] += part[j][p];   // index order, as the split-K contract says
-    ss = fmaf(v[j], v[j], ss);
-  }
+  for (int p = 0; p < MAX_PARTS; ++p)
+    if (add && p < nparts) { v.x += part[p].x; v.y += part[p].y; v.z += part[p].z; v.w += part[p].w; }   // index order, as the split-K contract says
+  float ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
   ss = warp_sum(ss);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
   __syncthreads();
@@ -103,12 +96,14 @@ __global__ void add_rmsnorm_rows(float *x, const float *add, int nparts, size_t 
 #pragma unroll
   for (int i = 0; i < 8; ++i) tot += red[i];
   const float rstd = 1.0f / sqrtf(tot * (1.0f / H) + RMS_EPS);
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int k = threadIdx.x + j * 256;
-    if (add) xr[k] = v[j];
-    y[static_cast<size_t>(t) * H + k] = __float2half_rn(v[j] * rstd * __half2float(w[k]));
-  }
+  if (add) *reinterpret_cast<float4 *>(xr + k0) = v;
+  const __half2 w01 = *reinterpret_cast<const __half2 *>(&wraw.x), w23 = *reinterpret_cast<const __half2 *>(&wraw.y);
+  const __half2 y01 = __floats2half2_rn(v.x * rstd * __low2float(w01), v.y * rstd * __high2float(w01));
+  const __half2 y23 = __floats2half2_rn(v.z * rstd * __low2float(w23), v.w * rstd * __high2float(w23));
+  uint2 out;
+  out.x = *reinterpret_cast<const uint32_t *>(&y01);
+  out.y = *reinterpret_cast<const uint32_t *>(&y23);
+  *reinterpret_cast<uint2 *>(y + static_cast<size_t>(t) * H + k0) = out;
 }
 
 // Per head: RMSNorm over 128 with q_norm / k_norm, rotate-half RoPE at position pos0 + t.  Query heads stay
@@ -123,49 +118,61 @@ __global__ void qk_norm_rope_cache(const float *q, const float *k, const float *
   pdl_trigger();
   const int t = blockIdx.x, slot = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   const int pos = pos0 + t;
+  const int d0 = 4 * lane;                      // four consecutive dims per lane: 16-byte accesses
+  auto pack4 = [](float a, float b, float c, float d) {
+    const __half2 lo = __floats2half2_rn(a, b), hi = __floats2half2_rn(c, d);
+    uint2 o;
+    o.x = *reinterpret_cast<const uint32_t *>(&lo);
+    o.y = *reinterpret_cast<const uint32_t *>(&hi);
+    return o;
+  };
   if (slot >= 24) {   // V head: plain copy to the cache
     const int g = slot - 24;
-    const float *src = v + static_cast<size_t>(t) * KVS + g * D;
-    __half *dst = v_cache_layer + (static_cast<size_t>(g) * max_seq_len + pos) * D;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) dst[lane + 32 * i] = __float2half_rn(src[lane + 32 * i]);
+    const float4 x = *reinterpret_cast<const float4 *>(v + static_cast<size_t>(t) * KVS + g * D + d0);
+    *reinterpret_cast<uint2 *>(v_cache_layer + (static_cast<size_t>(g) * max_seq_len + pos) * D + d0) = pack4(x.x, x.y, x.z, x.w);
     return;
   }
   const bool is_q = slot < 16;
   const int head = is_q ? slot : slot - 16;
   const float *src = is_q ? q + static_cast<size_t>(t) * QS + head * D : k + static_cast<size_t>(t) * KVS + head * D;
   const __half *nw = is_q ? q_norm : k_norm;
-  float x[4];
-  float ss = 0.f;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    x[i] = src[lane + 32 * i];
-    ss = fmaf(x[i], x[i], ss);
-  }
-  ss = warp_sum(ss);
-  const float rstd = 1.0f / sqrtf(ss * (1.0f / D) + RMS_EPS);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) x[i] = x[i] * rstd * __half2float(nw[lane + 32 * i]);
-  // element i pairs with i + 64 and both use frequency i (i < 64): lane holds i = lane, lane + 32
-  float c0, s0, c1, s1;
+  float4 x = *reinterpret_cast<const float4 *>(src + d0);
+  const uint2 wraw = *reinterpret_cast<const uint2 *>(nw + d0);
+  // element i pairs with i + 64 and both use frequency i (i < 64): lanes 0..15 hold the low halves, lane + 16 the
+  // partners; the frequencies of this lane's dims are those of dims (d0 mod 64) ..
+  const int f0 = d0 & 63;
+  float4 cs, sn;
   if (rope) {
     const float *r = rope + static_cast<size_t>(pos) * D;
-    c0 = r[lane]; c1 = r[lane + 32]; s0 = r[64 + lane]; s1 = r[64 + lane + 32];
+    cs = *reinterpret_cast<const float4 *>(r + f0);
+    sn = *reinterpret_cast<const float4 *>(r + 64 + f0);
   } else {
-    const __half *ct = cos_table + static_cast<size_t>(pos) * D, *st = sin_table + static_cast<size_t>(pos) * D;
-    c0 = __half2float(ct[lane]); c1 = __half2float(ct[lane + 32]);
-    s0 = __half2float(st[lane]); s1 = __half2float(st[lane + 32]);
+    const uint2 c2 = *reinterpret_cast<const uint2 *>(cos_table + static_cast<size_t>(pos) * D + f0);
+    const uint2 s2 = *reinterpret_cast<const uint2 *>(sin_table + static_cast<size_t>(pos) * D + f0);
+    const __half2 c01 = *reinterpret_cast<const __half2 *>(&c2.x), c23 = *reinterpret_cast<const __half2 *>(&c2.y);
+    const __half2 s01 = *reinterpret_cast<const __half2 *>(&s2.x), s23 = *reinterpret_cast<const __half2 *>(&s2.y);
+    cs = make_float4(__low2float(c01), __high2float(c01), __low2float(c23), __high2float(c23));
+    sn = make_float4(__low2float(s01), __high2float(s01), __low2float(s23), __high2float(s23));
   }
-  const float r0 = x[0] * c0 - x[2] * s0, r2 = x[0] * s0 + x[2] * c0;
-  const float r1 = x[1] * c1 - x[3] * s1, r3 = x[1] * s1 + x[3] * c1;
-  if (is_q) {
-    float *dst = qr + (static_cast<size_t>(t) * NQ + head) * D;
-    dst[lane] = r0; dst[lane + 32] = r1; dst[lane + 64] = r2; dst[lane + 96] = r3;
-  } else {
-    __half *dst = k_cache_layer + (static_cast<size_t>(head) * max_seq_len + pos) * D;
-    dst[lane] = __float2half_rn(r0); dst[lane + 32] = __float2half_rn(r1);
-    dst[lane + 64] = __float2half_rn(r2); dst[lane + 96] = __float2half_rn(r3);
+  float ss = fmaf(x.x, x.x, fmaf(x.y, x.y, fmaf(x.z, x.z, x.w * x.w)));
+  ss = warp_sum(ss);
+  const float rstd = 1.0f / sqrtf(ss * (1.0f / D) + RMS_EPS);
+  const __half2 w01 = *reinterpret_cast<const __half2 *>(&wraw.x), w23 = *reinterpret_cast<const __half2 *>(&wraw.y);
+  x.x = x.x * rstd * __low2float(w01); x.y = x.y * rstd * __high2float(w01);
+  x.z = x.z * rstd * __low2float(w23); x.w = x.w * rstd * __high2float(w23);
+  float4 o;   // the partner's normalised values
+  o.x = __shfl_xor_sync(0xffffffffu, x.x, 16); o.y = __shfl_xor_sync(0xffffffffu, x.y, 16);
+  o.z = __shfl_xor_sync(0xffffffffu, x.z, 16); o.w = __shfl_xor_sync(0xffffffffu, x.w, 16);
+  float4 r;
+  if (lane < 16) {    // low half: lo * cos - hi * sin
+    r = make_float4(x.x * cs.x - o.x * sn.x, x.y * cs.y - o.y * sn.y, x.z * cs.z - o.z * sn.z, x.w * cs.w - o.w * sn.w);
+  } else {            // high half: lo * sin + hi * cos
+    r = make_float4(o.x * sn.x + x.x * cs.x, o.y * sn.y + x.y * cs.y, o.z * sn.z + x.z * cs.z, o.w * sn.w + x.w * cs.w);
   }
+  if (is_q)
+    *reinterpret_cast<float4 *>(qr + (static_cast<size_t>(t) * NQ + head) * D + d0) = r;
+  else
+    *reinterpret_cast<uint2 *>(k_cache_layer + (static_cast<size_t>(head) * max_seq_len + pos) * D + d0) = pack4(r.x, r.y, r.z, r.w);
 }
 
 // Causal attention of the chunk's queries over cache rows [0, pos0 + t] (the chunk's own rows are already in the
