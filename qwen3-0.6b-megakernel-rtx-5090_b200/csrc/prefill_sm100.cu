@@ -313,7 +313,7 @@ int launch_gemm_splitk(const CUtensorMap &map_a, const CUtensorMap &map_b, float
                        unsigned int *status, int timeout_ms, cudaStream_t stream, std::string *err, int box_n,
                        int live_rows, int a_box_rows, int wq, const void *raw) {
   if (M <= 0 || N <= 0 || K <= 0 || M % qmk_gemm::BM || N % 128 || K % qmk_gemm::BK || splits < 1 ||
-      (K / qmk_gemm::BK) % splits || (box_n != 32 && box_n != 64)) {
+      (K / qmk_gemm::BK) % splits || (box_n != 32 && box_n != 64 && box_n != 128)) {
     *err = "gemm: bad split-K shape";
     return QMK_ERR_BAD_ARGUMENT;
   }
@@ -417,8 +417,8 @@ int ensure_workspace(Workspace &w, int rows) {
   PF_CUDA(cudaMalloc(&w.k, sizeof(float) * C * KVS));
   PF_CUDA(cudaMalloc(&w.v, sizeof(float) * C * KVS));
   PF_CUDA(cudaMalloc(&w.qr, sizeof(float) * C * QS));
-  PF_CUDA(cudaMalloc(&w.o, sizeof(float) * C * H));
-  PF_CUDA(cudaMalloc(&w.down, sizeof(float) * C * H));
+  PF_CUDA(cudaMalloc(&w.o, sizeof(float) * 2 * C * H));      // (two split-K partial matrices of a prefill chunk)
+  PF_CUDA(cudaMalloc(&w.down, sizeof(float) * 2 * C * H));
   PF_CUDA(cudaMalloc(&w.xn, sizeof(__half) * C * H));
   PF_CUDA(cudaMalloc(&w.attn, sizeof(__half) * C * QS));
   PF_CUDA(cudaMalloc(&w.act, sizeof(__half) * C * I));
@@ -538,6 +538,16 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
     const int T = (num_tokens - c0 < CHUNK) ? num_tokens - c0 : CHUNK;
     const int M = (T + qmk_gemm::BM - 1) / qmk_gemm::BM * qmk_gemm::BM;
     const int pos0 = start_position + c0;
+    // The O and down projections have only 1024 output columns: with 128-wide tiles a long chunk gives 128 CTAs for
+    // 148 SMs (296 slots with two CTAs per SM) and a K loop of 32 / 48 blocks.  K split in two doubles the CTAs and
+    // halves the loop; the partial matrices are added by the residual + RMSNorm kernel that follows anyway.
+    const int od_splits = (M >= 1024 && wq == 0) ? 2 : 1;
+    const size_t od_stride = od_splits > 1 ? static_cast<size_t>(M) * H : 0;
+    auto gemm_od = [&](const CUtensorMap &a, int l, int j, float *c, int Mrows, int K, int live) {
+      if (od_splits == 1) return gemm(a, l, j, c, Mrows, H, K, live);
+      return qmk_tc::launch_gemm_splitk(a, wmap_for(l, j, 128), c, Mrows, H, K, od_splits, w.status, env.timeout_ms, stream, &err, 128,
+                                        live, 0, wq, wptr(l, j));
+    };
     CUtensorMap map_kc, map_vc;   // the caches up to this chunk's last position, all layers
     if (env.attn_tc) {
       rc = qmk_tc::make_map_kv(&map_kc, k_cache, static_cast<uint64_t>(pos0 + T), static_cast<uint64_t>(max_seq_len),
@@ -560,7 +570,7 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
     for (int l = 0; l < num_layers; ++l) {
       const unsigned long long *r = rec.data() + static_cast<size_t>(l) * 12;
       __half *kc = static_cast<__half *>(k_cache) + l * layer_stride, *vc = static_cast<__half *>(v_cache) + l * layer_stride;
-      PF_CUDA(qmk_tc::launch_kernel(add_rmsnorm_rows, dim3(T), dim3(256), 0, stream, w.x, l > 0 ? w.down : nullptr, 1, size_t(0),
+      PF_CUDA(qmk_tc::launch_kernel(add_rmsnorm_rows, dim3(T), dim3(256), 0, stream, w.x, l > 0 ? w.down : nullptr, od_splits, od_stride,
                                     reinterpret_cast<const __half *>(r[0]), w.xn));
       {
         const int js[3] = {0, 1, 2};
@@ -582,8 +592,8 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
       else
         PF_CUDA(qmk_tc::launch_kernel(causal_attention_mma, dim3((T + ATM_Q - 1) / ATM_Q, NKV), dim3(ATM_THREADS), ATM_SMEM_BYTES, stream,
                                       w.qr, kc, vc, w.attn, T, pos0, max_seq_len, attn_scale));
-      if ((rc = gemm(w.map_attn, l, 3, w.o, M, H, QS, T)) != QMK_OK) break;
-      PF_CUDA(qmk_tc::launch_kernel(add_rmsnorm_rows, dim3(T), dim3(256), 0, stream, w.x, w.o, 1, size_t(0),
+      if ((rc = gemm_od(w.map_attn, l, 3, w.o, M, QS, T)) != QMK_OK) break;
+      PF_CUDA(qmk_tc::launch_kernel(add_rmsnorm_rows, dim3(T), dim3(256), 0, stream, w.x, w.o, od_splits, od_stride,
                                     reinterpret_cast<const __half *>(r[7]), w.xn));
       {
         const int box_gu = qmk_tc::gemm_box_n_fused(M, I);
@@ -594,7 +604,7 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
                                              wptr(l, 5))) != QMK_OK)
           break;
       }
-      if ((rc = gemm(w.map_act, l, 6, w.down, M, H, I, T)) != QMK_OK) break;
+      if ((rc = gemm_od(w.map_act, l, 6, w.down, M, I, T)) != QMK_OK) break;
     }
     if (rc != QMK_OK) break;
     PF_CUDA(cudaGetLastError());     // (the next chunk's token copy is stream-ordered behind this chunk's kernels)
