@@ -197,6 +197,11 @@ int qmk_set_tuning2(int repl, int stream_inflight);
  * oracle either way; negative keeps. */
 int qmk_set_prefill_attention(int tensor_core);
 
+/* Batched decode (qmk_decode_batched): 1 (default) runs the per-sequence attention on mma.sync tensor-core tiles (cache
+ * rows by tiled TMA through per-sequence descriptors the call encodes), 0 on the CUDA-core kernel it replaces.  Same
+ * tolerance against the oracle either way; negative keeps. */
+int qmk_set_decode_attention(int tensor_core);
+
 /* Batched decode (qmk_decode_batched): 1 (default) launches the ~200 kernels of a decode step as programmatic
  * dependents of one another - each kernel is scheduled while its predecessor still runs, sets itself up, streams the
  * operands no kernel of the step writes (weight tiles, cache rows of earlier steps) and only then waits for the

@@ -23,7 +23,7 @@ HEADERS = [os.path.join(os.path.dirname(HERE), "include", "qwen_megakernel.h"),
            os.path.join(HERE, "csrc", "megakernel_tc.cuh"), os.path.join(HERE, "csrc", "megakernel_tc.h"), os.path.join(HERE, "csrc", "megakernel_batch.h"),
            os.path.join(HERE, "csrc", "gemm_tcgen05.cuh"), os.path.join(HERE, "csrc", "prefill_sm100.h"),
            os.path.join(HERE, "csrc", "prefill_kernels.cuh"), os.path.join(HERE, "csrc", "engine_internal.h"),
-           os.path.join(HERE, "csrc", "attention_tcgen05.cuh")]
+           os.path.join(HERE, "csrc", "attention_tcgen05.cuh"), os.path.join(HERE, "csrc", "decode_attention_mma.cuh")]
 LIB_PATH = os.path.join(HERE, "libqwen_megakernel.so")
 
 NVCC_FLAGS = [

@@ -14,6 +14,7 @@ struct PrefillEnv {
   int wfmt;               // 0 fp16 weights, 1 fp8 rows, 2 nvfp4 rows
   int rope_from_table;
   float *logits_out;      // debug dump set through qmk_set_logits_dump (may be null)
+  int attn_mma;           // 1: batched decode attention on mma.sync (decode_attention_mma), 0: the CUDA-core ring kernel
   int attn_tc;            // 1: prefill attention on tcgen05 (causal_attention_tc), 0: on mma.sync (causal_attention_mma)
   int pdl;                // 1: kernels of a decode step / prefill pass are launched as programmatic dependents of one another
 };

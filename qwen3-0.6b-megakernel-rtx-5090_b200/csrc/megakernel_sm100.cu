@@ -204,6 +204,7 @@ struct Engine {
   // fused single-sequence kernel (megakernel_fused.cuh)
   int fused = 2;             // 0: always the unfused kernel; 1: fused, CUDA-core row products; 2: fused, tensor-core row products (fp16 weights)
   int red_copies = 1;
+  int decode_attn_mma = 1;   // batched decode: attention on mma.sync (0: the CUDA-core ring kernel)
   int prefill_attn_tc = 1;   // chunked prefill: attention on tcgen05 (0: the mma.sync kernel)
   int step_overlap = 1;      // batched decode: kernels of a step launched as programmatic dependents of one another
   int fused_sleep_ns = 0;    // measured at 4096-token context: 600 ns 1224 tok/s, 200 ns 1259, 0 ns 1305 (few pollers per word)
@@ -551,6 +552,7 @@ int prefill_env(int max_seq_len, cudaStream_t stream, PrefillEnv *out) {
   out->logits_out = e->logits_out;
   out->pdl = e->step_overlap;
   out->attn_tc = e->prefill_attn_tc;
+  out->attn_mma = e->decode_attn_mma;
   return QMK_OK;
 }
 int report(int code, const std::string &msg) {
@@ -614,6 +616,14 @@ int qmk_set_prefill_attention(int tensor_core) {
   Engine *e = current_engine_unlocked();
   if (!e) return QMK_ERR_CUDA;
   if (tensor_core >= 0) e->prefill_attn_tc = tensor_core ? 1 : 0;
+  return QMK_OK;
+}
+
+int qmk_set_decode_attention(int tensor_core) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  Engine *e = current_engine_unlocked();
+  if (!e) return QMK_ERR_CUDA;
+  if (tensor_core >= 0) e->decode_attn_mma = tensor_core ? 1 : 0;
   return QMK_OK;
 }
 

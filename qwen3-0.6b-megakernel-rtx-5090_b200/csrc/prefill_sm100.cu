@@ -14,6 +14,7 @@
 #include "prefill_sm100.h"
 #include "prefill_kernels.cuh"
 #include "attention_tcgen05.cuh"
+#include "decode_attention_mma.cuh"
 #include "engine_internal.h"
 #include <vector>
 
@@ -188,6 +189,9 @@ int ensure_gemm_attrs(std::string *err) {
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(qmk_pf::decode_attention_ring, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                qmk_pf::DAR_SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(qmk_pf::decode_attention_mma, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               qmk_pf::DAM_SMEM_BYTES);
     if (e != cudaSuccess) { *err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e); return QMK_ERR_CUDA; }
     g_attr_set[dev] = true;
   }
@@ -373,6 +377,7 @@ struct Workspace {                  // per device, allocated on first use, never
   unsigned long long step_key[129][12] = {};
   unsigned long long graph_epoch = 1;    // bumped whenever tensor maps baked into the graphs are rebuilt
   __half **k_ptrs = nullptr, **v_ptrs = nullptr;
+  CUtensorMap *kv_maps = nullptr;        // [128][2]: tiled-copy descriptors of every sequence's K and V cache (decode_attention_mma)
   int **log_ptrs = nullptr;
   float *split_part = nullptr;            // partial attention states of split sequences (decode_attention_ring)
   unsigned int *split_count = nullptr;    // arrival counters, one per (sequence, kv head); zero between launches
@@ -641,6 +646,7 @@ int ensure_decode_workspace(Workspace &w, const void *lm_head, int vocab, int wq
     PF_CUDA(cudaMalloc(&w.k_ptrs, sizeof(void *) * MAX_BATCH));
     PF_CUDA(cudaMalloc(&w.v_ptrs, sizeof(void *) * MAX_BATCH));
     PF_CUDA(cudaMalloc(&w.log_ptrs, sizeof(void *) * MAX_BATCH));
+    PF_CUDA(cudaMalloc(&w.kv_maps, sizeof(CUtensorMap) * 2 * MAX_BATCH));
     PF_CUDA(cudaMalloc(&w.split_part, sizeof(float) * MAX_BATCH * qmk_pf::NKV * MAX_ATTN_SPLITS * 2 * (qmk_pf::D + 2)));
     PF_CUDA(cudaMalloc(&w.split_count, sizeof(unsigned int) * MAX_BATCH * qmk_pf::NKV));
     PF_CUDA(cudaMemset(w.split_count, 0, sizeof(unsigned int) * MAX_BATCH * qmk_pf::NKV));
@@ -729,6 +735,18 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
   PF_CUDA(cudaMemcpyAsync(w.v_ptrs, v_caches, sizeof(void *) * B, cudaMemcpyHostToDevice, stream));
   PF_CUDA(cudaMemcpyAsync(w.log_ptrs, output_logs, sizeof(void *) * B, cudaMemcpyHostToDevice, stream));
   std::string err;
+  std::vector<CUtensorMap> host_maps;
+  if (env.attn_mma) {   // per-sequence descriptors of the whole [layer][kv head][position] caches, boxes of 16 rows x 64 dims
+    host_maps.resize(2 * static_cast<size_t>(B));
+    const uint64_t cache_rows = static_cast<uint64_t>(num_layers) * NKV * static_cast<uint64_t>(max_seq_len);
+    for (int b = 0; b < B && rc == QMK_OK; ++b) {
+      rc = qmk_tc::make_map_f16(&host_maps[2 * b], k_caches[b], cache_rows, D, 16, &err);
+      if (rc == QMK_OK) rc = qmk_tc::make_map_f16(&host_maps[2 * b + 1], v_caches[b], cache_rows, D, 16, &err);
+    }
+    if (rc != QMK_OK) return qmk_internal::report(rc, err);
+    PF_CUDA(cudaMemcpyAsync(w.kv_maps, host_maps.data(), sizeof(CUtensorMap) * host_maps.size(), cudaMemcpyHostToDevice, stream));
+    PF_CUDA(cudaStreamSynchronize(stream));   // (the pageable host vector must outlive the copy)
+  }
   if ((rc = qmk_tc::ensure_gemm_attrs(&err)) != QMK_OK) return qmk_internal::report(rc, err);
   (void)qmk_tc::gemm_box_n(128, 128);   // caches the SM count before any capture
   {
@@ -783,10 +801,18 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
                                               live, a_box, wq, raws)) != QMK_OK)
           return r2;
       }
-      PF_CUDA(qmk_tc::launch_kernel(decode_attention_ring, dim3(B, NKV, attn_splits), dim3((DAR_WARPS + 1) * 32), DAR_SMEM_BYTES, s,
-                                    w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]), reinterpret_cast<const __half *>(r[5]), rope,
-                                    cosv, sinv, w.k_ptrs, w.v_ptrs, layer_off, w.positions, w.attn, max_seq_len, attn_scale, w.status,
-                                    static_cast<unsigned long long>(env.timeout_ms) * 1000000ull, w.split_part, w.split_count));
+      if (env.attn_mma)
+        PF_CUDA(qmk_tc::launch_kernel(decode_attention_mma, dim3(B, NKV, attn_splits), dim3((DAM_WARPS + 1) * 32), DAM_SMEM_BYTES, s,
+                                      w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]), reinterpret_cast<const __half *>(r[5]),
+                                      rope, cosv, sinv, w.k_ptrs, w.v_ptrs, layer_off, w.positions, w.attn, max_seq_len, attn_scale,
+                                      w.status, static_cast<unsigned long long>(env.timeout_ms) * 1000000ull, w.split_part,
+                                      w.split_count, w.kv_maps, l * NKV * max_seq_len));
+      else
+        PF_CUDA(qmk_tc::launch_kernel(decode_attention_ring, dim3(B, NKV, attn_splits), dim3((DAR_WARPS + 1) * 32), DAR_SMEM_BYTES, s,
+                                      w.q, w.k, w.v, reinterpret_cast<const __half *>(r[4]), reinterpret_cast<const __half *>(r[5]),
+                                      rope, cosv, sinv, w.k_ptrs, w.v_ptrs, layer_off, w.positions, w.attn, max_seq_len, attn_scale,
+                                      w.status, static_cast<unsigned long long>(env.timeout_ms) * 1000000ull, w.split_part,
+                                      w.split_count));
       if ((r2 = qmk_tc::launch_gemm_splitk(w.map_attn_b, wm(3), w.o, M, H, QS, O_SPLITS, w.status, env.timeout_ms, s, &err,
                                            TILE_N, live, a_box, wq, wp(3))) != QMK_OK)
         return r2;
@@ -839,7 +865,7 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
         reinterpret_cast<unsigned long long>(final_norm_weight), reinterpret_cast<unsigned long long>(lm_head_weight),
         reinterpret_cast<unsigned long long>(rope), reinterpret_cast<unsigned long long>(cos_table),
         reinterpret_cast<unsigned long long>(sin_table) ^ (static_cast<unsigned long long>(env.timeout_ms) << 48) ^
-            (static_cast<unsigned long long>(env.pdl != 0) << 63)};
+            (static_cast<unsigned long long>(env.pdl != 0) << 63) ^ (static_cast<unsigned long long>(env.attn_mma != 0) << 62)};
     if (memcmp(key, w.step_key[B], sizeof(key)) != 0) {
       if (w.step_graph[B]) { cudaGraphExecDestroy(w.step_graph[B]); w.step_graph[B] = nullptr; }
       w.step_key[B][0] = 0;

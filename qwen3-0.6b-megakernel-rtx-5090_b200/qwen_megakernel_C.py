@@ -58,6 +58,8 @@ _lib.qmk_set_profile_buffer.argtypes = [_P]
 _lib.qmk_set_profile_buffer.restype = _I
 _lib.qmk_set_prefill_attention.argtypes = [_I]
 _lib.qmk_set_prefill_attention.restype = _I
+_lib.qmk_set_decode_attention.argtypes = [_I]
+_lib.qmk_set_decode_attention.restype = _I
 _lib.qmk_set_step_overlap.argtypes = [_I]
 _lib.qmk_set_step_overlap.restype = _I
 _lib.qmk_set_fused.argtypes = [_I, _I]
@@ -114,7 +116,7 @@ _lib.qmk_selftest_gemm_wait_timeout.restype = _I
 EXPORTED_SYMBOLS = (
     "launch_ldg_decode_direct", "launch_ldg_decode_persistent", "launch_ldg_generate_nosync",
     "launch_ldg_prefill", "qmk_abi_version", "qmk_configure", "qmk_set_inv_freq", "qmk_set_logits_dump",
-    "qmk_set_weight_format", "qmk_set_tuning", "qmk_set_tuning2", "qmk_set_profile_buffer", "qmk_set_fused", "qmk_set_step_overlap", "qmk_set_prefill_attention", "qmk_invalidate_weights", "qmk_release_weights", "qmk_decode", "qmk_generate", "qmk_generate_static", "qmk_generate_batch", "qmk_gemm_f16_tn", "qmk_gemm_packed_tn", "qmk_decode_batched", "qmk_prefill_chunked", "qmk_prefill", "qmk_engine_create", "qmk_engine_destroy", "qmk_engine_apply", "qmk_engine_decode", "qmk_engine_generate", "qmk_engine_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
+    "qmk_set_weight_format", "qmk_set_tuning", "qmk_set_tuning2", "qmk_set_profile_buffer", "qmk_set_fused", "qmk_set_step_overlap", "qmk_set_prefill_attention", "qmk_set_decode_attention", "qmk_invalidate_weights", "qmk_release_weights", "qmk_decode", "qmk_generate", "qmk_generate_static", "qmk_generate_batch", "qmk_gemm_f16_tn", "qmk_gemm_packed_tn", "qmk_decode_batched", "qmk_prefill_chunked", "qmk_prefill", "qmk_engine_create", "qmk_engine_destroy", "qmk_engine_apply", "qmk_engine_decode", "qmk_engine_generate", "qmk_engine_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
     "qmk_scratch_bytes", "qmk_selftest_wait_timeout", "qmk_selftest_gemm_wait_timeout",
 )
 
@@ -366,6 +368,11 @@ def set_fused(fused=-1, red_copies=-1) -> None:
 def set_prefill_attention(tensor_core: bool) -> None:
     """Chunked prefill: causal attention on tcgen05 (default) or on the mma.sync kernel."""
     _check(_lib.qmk_set_prefill_attention(int(bool(tensor_core))) == 0, "set_prefill_attention failed")
+
+
+def set_decode_attention(tensor_core: bool) -> None:
+    """Batched decode: per-sequence attention on mma.sync tiles (default) or on the CUDA-core kernel."""
+    _check(_lib.qmk_set_decode_attention(int(bool(tensor_core))) == 0, "set_decode_attention failed")
 
 
 def set_step_overlap(enabled: bool) -> None:
