@@ -164,6 +164,32 @@ def test_step_overlap_changes_nothing_but_time(C):
     assert tok_on == want
 
 
+@pytest.mark.parametrize("mma", [1, 0])
+def test_both_decode_attention_kernels(C, mma):
+    """The per-sequence attention of a decode step on mma.sync tiles (default) and on the CUDA-core kernel it replaced:
+    contexts of 1 .. 600 rows (chunks of 16 with ragged ends, sequences split over several CTAs), against the oracle."""
+    vocab, steps, L, n = 2048, 4, 640, 7
+    w = S.make_weights(seed=27, num_layers=2, vocab_size=vocab, norm_std=0.1, max_seq_len=16)
+    lens = [1, 2, 16, 17, 33, 250, 600]
+    prompts = [S.make_prompt(Ln, seed=700 + i, vocab_size=vocab) for i, Ln in enumerate(lens)]
+    eng = _engine(w, n, L, engine="gemm")
+    dump = torch.zeros(n, steps, vocab, device="cuda")
+    C.set_decode_attention(mma)
+    C.set_logits_dump(dump)
+    try:
+        got = eng.generate_ids(prompts, steps)
+    finally:
+        C.set_logits_dump(None)
+        C.set_decode_attention(1)
+    worst = 0.0
+    for b in range(n):
+        want, logits = OracleDecoder(w, max_seq_len=L).generate_ids(prompts[b], steps, keep_logits=True)
+        worst = max(worst, float((dump[b].cpu() - logits).abs().max()))
+        assert got[b] == want, f"sequence {b} (prompt {lens[b]} tokens)"
+    print(f"decode attention mma={mma}: worst max |logit - oracle| = {worst:.3e}")
+    assert worst < LOGIT_TOL
+
+
 def test_refusals(C):
     vocab = 2048
     w = S.make_weights(seed=1, num_layers=2, vocab_size=vocab, max_seq_len=16)
