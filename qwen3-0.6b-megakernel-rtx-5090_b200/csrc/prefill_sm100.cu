@@ -831,6 +831,7 @@ extern "C" int qmk_decode_batched(int num_sequences, const int *first_token_ids,
     // rows of logits (B x 608 KB per step) are never written
     const bool fused_pick = env.logits_out == nullptr;
     if (fused_pick) qmk_tc::set_argmax_target(w.amax_val, w.amax_idx);
+    qmk_tc::RingBudgetScope lm_scope(PREFILL_RING_BYTES);   // 1187 tiles: two CTAs per SM, four waves instead of eight
     r2 = qmk_tc::launch_gemm(w.map_xn_b, w.map_lm, w.logits, M, env.vocab, H, 128, w.status, env.timeout_ms, s, &err, live, a_box,
                              wq, lm_head_weight);
     qmk_tc::set_argmax_target(nullptr, nullptr);
