@@ -592,8 +592,7 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
       if (env.attn_tc)
         PF_CUDA(qmk_tc::launch_kernel(qmk_attn::causal_attention_tc, dim3((T + qmk_attn::TQ - 1) / qmk_attn::TQ * NQ),
                                       dim3(qmk_attn::THREADS), qmk_attn::SMEM_BYTES, stream, w.qr, map_kc, map_vc, l * NKV, w.attn, T,
-                                      pos0, attn_scale, w.status, static_cast<unsigned long long>(env.timeout_ms) * 1000000ull,
-                                      qmk_tc::gemm_sm_count()));
+                                      pos0, attn_scale, w.status, static_cast<unsigned long long>(env.timeout_ms) * 1000000ull));
       else
         PF_CUDA(qmk_tc::launch_kernel(causal_attention_mma, dim3((T + ATM_Q - 1) / ATM_Q, NKV), dim3(ATM_THREADS), ATM_SMEM_BYTES, stream,
                                       w.qr, kc, vc, w.attn, T, pos0, max_seq_len, attn_scale));
