@@ -185,6 +185,9 @@ struct Groups {
   // reading the whole row of logits, which is never written.
   float *amax_val;
   int *amax_idx;
+  // Plain epilogue, no split-K: 1 = the C matrices are fp16 [M x N_g] (the pointers are reinterpreted), half the
+  // store burst of a launch whose CTAs all reach their epilogue together.
+  int out_f16;
 };
 
 // Eight e2m1 values of one 32-bit word (element 2 i in the low nibble of byte i) -> four half2 registers.
@@ -467,7 +470,9 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
               g0 *= s_rowscale[c * 16 + 2 * i]; g1 *= s_rowscale[c * 16 + 2 * i + 1];
               u0 *= s_rowscale[BN + c * 16 + 2 * i]; u1 *= s_rowscale[BN + c * 16 + 2 * i + 1];
             }
-            const __half2 h = __floats2half2_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+            // (hardware exp2 and reciprocal: a few ulp, far inside the fp16 rounding of the result; the exact forms
+            // cost about 25 instructions per value and made this epilogue as long as a third of the K loop)
+            const __half2 h = __floats2half2_rn(__fdividef(g0, 1.0f + __expf(-g0)) * u0, __fdividef(g1, 1.0f + __expf(-g1)) * u1);
             packed[i] = *reinterpret_cast<const uint32_t *>(&h);
           }
           *reinterpret_cast<uint4 *>(arow + c * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
@@ -477,7 +482,9 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     } else if (ok) {
       const int row = m0 + quarter * 32 + lane;
       float *crow = C + static_cast<size_t>(blockIdx.z) * groups.split_stride + static_cast<size_t>(row) * N + n0;
+      __half *hrow = reinterpret_cast<__half *>(C) + static_cast<size_t>(row) * N + n0;   // (out_f16)
       const bool pick = groups.amax_val != nullptr;
+      const bool f16 = groups.out_f16 != 0;
       float best = -INFINITY;
       int best_col = 0x7fffffff;
 #pragma unroll 1
@@ -495,7 +502,20 @@ gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             : "r"(taddr)
             : "memory");
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row < M) {
+        if (row < M && f16) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint32_t packed[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              float a = __uint_as_float(r[i + 2 * k]), b = __uint_as_float(r[i + 2 * k + 1]);
+              if (WQ) { a *= s_rowscale[c * 32 + i + 2 * k]; b *= s_rowscale[c * 32 + i + 2 * k + 1]; }
+              const __half2 h = __floats2half2_rn(a, b);
+              packed[k] = *reinterpret_cast<const uint32_t *>(&h);
+            }
+            *reinterpret_cast<uint4 *>(hrow + c * 32 + i) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          }
+        } else if (row < M) {
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             float4 o = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),

@@ -110,7 +110,8 @@ __global__ void add_rmsnorm_rows(float *x, const float *add, int nparts, size_t 
 // fp32 (qr[t][head][128]); K (normalised, rotated) and V go to the fp16 cache rows of this layer.
 // grid = (T, 4), block = 256 = 8 warps; warp w of block y handles head slot y * 8 + w of 32:
 // 0..15 query heads, 16..23 K heads, 24..31 V heads.
-__global__ void qk_norm_rope_cache(const float *q, const float *k, const float *v, const __half *q_norm,
+// in_f16: q / k / v hold fp16 (the projection's epilogue stored halves) instead of fp32.
+__global__ void qk_norm_rope_cache(const float *q, const float *k, const float *v, int in_f16, const __half *q_norm,
                                    const __half *k_norm, const float *rope, const __half *cos_table,
                                    const __half *sin_table, float *qr, __half *k_cache_layer, __half *v_cache_layer,
                                    int pos0, int max_seq_len) {
@@ -126,17 +127,22 @@ __global__ void qk_norm_rope_cache(const float *q, const float *k, const float *
     o.y = *reinterpret_cast<const uint32_t *>(&hi);
     return o;
   };
+  auto load4 = [&](const float *m, size_t idx) {   // four consecutive values from element idx of an fp32 or fp16 matrix
+    if (!in_f16) return *reinterpret_cast<const float4 *>(m + idx);
+    const uint2 raw = *reinterpret_cast<const uint2 *>(reinterpret_cast<const __half *>(m) + idx);
+    const __half2 a = *reinterpret_cast<const __half2 *>(&raw.x), b = *reinterpret_cast<const __half2 *>(&raw.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+  };
   if (slot >= 24) {   // V head: plain copy to the cache
     const int g = slot - 24;
-    const float4 x = *reinterpret_cast<const float4 *>(v + static_cast<size_t>(t) * KVS + g * D + d0);
+    const float4 x = load4(v, static_cast<size_t>(t) * KVS + g * D + d0);
     *reinterpret_cast<uint2 *>(v_cache_layer + (static_cast<size_t>(g) * max_seq_len + pos) * D + d0) = pack4(x.x, x.y, x.z, x.w);
     return;
   }
   const bool is_q = slot < 16;
   const int head = is_q ? slot : slot - 16;
-  const float *src = is_q ? q + static_cast<size_t>(t) * QS + head * D : k + static_cast<size_t>(t) * KVS + head * D;
   const __half *nw = is_q ? q_norm : k_norm;
-  float4 x = *reinterpret_cast<const float4 *>(src + d0);
+  float4 x = is_q ? load4(q, static_cast<size_t>(t) * QS + head * D + d0) : load4(k, static_cast<size_t>(t) * KVS + head * D + d0);
   const uint2 wraw = *reinterpret_cast<const uint2 *>(nw + d0);
   // element i pairs with i + 64 and both use frequency i (i < 64): lanes 0..15 hold the low halves, lane + 16 the
   // partners; the frequencies of this lane's dims are those of dims (d0 mod 64) ..

@@ -228,6 +228,8 @@ static size_t set_ring(qmk_gemm::Groups *gr, int sb, int wq) {
 RingBudgetScope::RingBudgetScope(unsigned int bytes) : prev_(t_ring_budget) { t_ring_budget = bytes; }
 RingBudgetScope::~RingBudgetScope() { t_ring_budget = prev_; }
 void set_argmax_target(float *val, int *idx) { t_amax_val = val; t_amax_idx = idx; }
+thread_local bool t_out_f16 = false;        // the next grouped GEMM of this thread stores fp16
+void set_out_f16(bool on) { t_out_f16 = on; }
 size_t selftest_ring(qmk_gemm::Groups *gr) { return set_ring(gr, 128, 0); }
 
 // A maps with short boxes (`a_box_rows` < 128 rows per box, a multiple of 8; decode steps with few live rows): one
@@ -260,6 +262,7 @@ int launch_gemm_grouped(const CUtensorMap &map_a, int ngroups, const CUtensorMap
   gr.kblocks_per_split = 0;
   gr.split_stride = 0;
   if (!set_packed(&gr, wq, K, ngroups, raws, err)) return QMK_ERR_BAD_ARGUMENT;
+  gr.out_f16 = t_out_f16 ? 1 : 0;
   gr.amax_val = ngroups == 1 ? t_amax_val : nullptr;   // (set around the LM-head launch of a decode step only)
   gr.amax_idx = ngroups == 1 ? t_amax_idx : nullptr;
   int tiles = 0;
@@ -300,6 +303,7 @@ int launch_gemm_swiglu(const CUtensorMap &map_a, const CUtensorMap &map_gate, co
   const void *raws[2] = {raw_gate, raw_up};
   if (!set_packed(&gr, wq, K, 2, raws, err)) return QMK_ERR_BAD_ARGUMENT;
   gr.amax_val = nullptr;
+  gr.out_f16 = 0;
   gr.amax_idx = nullptr;
   int rows = live_rows > 0 ? live_rows : M;
   if (!a_box_ok(a_box_rows, M, &rows, &gr.a_box_bytes, err)) return QMK_ERR_BAD_ARGUMENT;
@@ -330,6 +334,7 @@ int launch_gemm_splitk(const CUtensorMap &map_a, const CUtensorMap &map_b, float
   gr.split_stride = static_cast<size_t>(M) * N;
   if (!set_packed(&gr, wq, K, 1, &raw, err)) return QMK_ERR_BAD_ARGUMENT;
   gr.amax_val = nullptr;
+  gr.out_f16 = 0;
   gr.amax_idx = nullptr;
   int rows = live_rows > 0 ? live_rows : M;
   if (!a_box_ok(a_box_rows, M, &rows, &gr.a_box_bytes, err)) return QMK_ERR_BAD_ARGUMENT;
@@ -581,11 +586,16 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
         const int js[3] = {0, 1, 2};
         float *const cs[3] = {w.q, w.k, w.v};
         const int ns[3] = {QS, KVS, KVS};
-        if ((rc = gemm_group(w.map_xn, l, 3, js, cs, ns, M, H, T)) != QMK_OK) break;
+        // fp16 q / k / v: every CTA of this launch reaches its epilogue at the same time, and the burst of stores set
+        // its length (9.8 of 26 us at 2048 rows with fp32); the consumer below rounds to fp16 anyway
+        qmk_tc::set_out_f16(true);
+        rc = gemm_group(w.map_xn, l, 3, js, cs, ns, M, H, T);
+        qmk_tc::set_out_f16(false);
+        if (rc != QMK_OK) break;
       }
       // (Folding this kernel into the q/k/v GEMM's epilogue - one 128-wide N tile is one head - was built and measured
       // slower: 128 threads per CTA walking TMEM eight columns at a time lose to 2300 x 4 fully parallel CTAs.)
-      PF_CUDA(qmk_tc::launch_kernel(qk_norm_rope_cache, dim3(T, 4), dim3(256), 0, stream, w.q, w.k, w.v,
+      PF_CUDA(qmk_tc::launch_kernel(qk_norm_rope_cache, dim3(T, 4), dim3(256), 0, stream, w.q, w.k, w.v, 1,
                                     reinterpret_cast<const __half *>(r[4]), reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv,
                                     w.qr, kc, vc, pos0, max_seq_len));
       if (l == num_layers - 1) break;   // the cache is complete; nothing downstream of the last layer is kept
@@ -926,6 +936,8 @@ extern "C" int qmk_selftest_gemm_wait_timeout(int budget_us) {
     for (int g = 0; g < qmk_gemm::MAX_GROUPS; ++g) gr.braw[g] = nullptr;
     gr.raw_pitch = gr.raw_bs_off = gr.raw_scale_off = 0;
     gr.amax_val = nullptr;
+    gr.out_f16 = 0;
+  gr.out_f16 = 0;
     gr.amax_idx = nullptr;
     const size_t smem = qmk_tc::selftest_ring(&gr);
     qmk_gemm::gemm_f16_tn_kernel<128><<<dim3(1, 1), qmk_gemm::THREADS, smem>>>(

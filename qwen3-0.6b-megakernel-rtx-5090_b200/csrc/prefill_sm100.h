@@ -21,6 +21,7 @@ bool pdl_active();
 }  // namespace qmk_tc
 namespace qmk_gemm { struct Groups; }
 namespace qmk_tc {
+void set_out_f16(bool on);                     // calling thread: the next grouped GEMM stores fp16 matrices
 void set_argmax_target(float *val, int *idx);   // calling thread: the next single-matrix GEMM picks per tile instead of storing
 // While one is alive on a thread, GEMM launches of that thread size their rings to `bytes` of shared memory (0 = full depth).
 class RingBudgetScope {
