@@ -106,18 +106,69 @@ __global__ void add_rmsnorm_rows(float *x, const float *add, int nparts, size_t 
   *reinterpret_cast<uint2 *>(y + static_cast<size_t>(t) * H + k0) = out;
 }
 
-// Per head: RMSNorm over 128 with q_norm / k_norm, rotate-half RoPE at position pos0 + t.  Query heads stay
-// fp32 (qr[t][head][128]); K (normalised, rotated) and V go to the fp16 cache rows of this layer.
-// grid = (T, 4), block = 256 = 8 warps; warp w of block y handles head slot y * 8 + w of 32:
-// 0..15 query heads, 16..23 K heads, 24..31 V heads.
-// in_f16: q / k / v hold fp16 (the projection's epilogue stored halves) instead of fp32.
-__global__ void qk_norm_rope_cache(const float *q, const float *k, const float *v, int in_f16, const __half *q_norm,
-                                   const __half *k_norm, const float *rope, const __half *cos_table,
-                                   const __half *sin_table, float *qr, __half *k_cache_layer, __half *v_cache_layer,
-                                   int pos0, int max_seq_len) {
+// The same for long chunks: one WARP per row (grid = ceil(T / 8), block = 256), eight 16-byte pieces per lane, every
+// load of the lane issued before the first add.  The block-per-row form above keeps one piece per thread in flight
+// and needs two waves of blocks for 2048 rows; it spent its 7 us waiting, not copying.  (The sum of squares is added
+// in another order than above: results agree to rounding, not bit for bit.)
+__global__ void __launch_bounds__(256)
+add_rmsnorm_rows_wide(float *x, const float *add, int nparts, size_t part_stride, const __half *w, __half *y, int T) {
   pdl_wait();
   pdl_trigger();
-  const int t = blockIdx.x, slot = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= T) return;
+  constexpr int PIECES = H / 128;                // pieces of four floats per lane
+  constexpr int MAX_PARTS = 2;
+  float *xr = x + static_cast<size_t>(t) * H;
+  float4 v[PIECES], part[MAX_PARTS][PIECES];
+  uint2 wraw[PIECES];
+#pragma unroll
+  for (int i = 0; i < PIECES; ++i) v[i] = *reinterpret_cast<const float4 *>(xr + 4 * (lane + 32 * i));
+#pragma unroll
+  for (int p = 0; p < MAX_PARTS; ++p)
+#pragma unroll
+    for (int i = 0; i < PIECES; ++i)
+      part[p][i] = (add && p < nparts)
+                       ? *reinterpret_cast<const float4 *>(add + p * part_stride + static_cast<size_t>(t) * H + 4 * (lane + 32 * i))
+                       : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int i = 0; i < PIECES; ++i) wraw[i] = *reinterpret_cast<const uint2 *>(w + 4 * (lane + 32 * i));
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < PIECES; ++i) {
+#pragma unroll
+    for (int p = 0; p < MAX_PARTS; ++p)
+      if (add && p < nparts) { v[i].x += part[p][i].x; v[i].y += part[p][i].y; v[i].z += part[p][i].z; v[i].w += part[p][i].w; }   // index order
+    ss = fmaf(v[i].x, v[i].x, fmaf(v[i].y, v[i].y, fmaf(v[i].z, v[i].z, fmaf(v[i].w, v[i].w, ss))));
+  }
+  ss = warp_sum(ss);
+  const float rstd = 1.0f / sqrtf(ss * (1.0f / H) + RMS_EPS);
+#pragma unroll
+  for (int i = 0; i < PIECES; ++i) {
+    if (add) *reinterpret_cast<float4 *>(xr + 4 * (lane + 32 * i)) = v[i];
+    const __half2 w01 = *reinterpret_cast<const __half2 *>(&wraw[i].x), w23 = *reinterpret_cast<const __half2 *>(&wraw[i].y);
+    const __half2 y01 = __floats2half2_rn(v[i].x * rstd * __low2float(w01), v[i].y * rstd * __high2float(w01));
+    const __half2 y23 = __floats2half2_rn(v[i].z * rstd * __low2float(w23), v[i].w * rstd * __high2float(w23));
+    uint2 out;
+    out.x = *reinterpret_cast<const uint32_t *>(&y01);
+    out.y = *reinterpret_cast<const uint32_t *>(&y23);
+    *reinterpret_cast<uint2 *>(y + static_cast<size_t>(t) * H + 4 * (lane + 32 * i)) = out;
+  }
+}
+
+// Per head: RMSNorm over 128 with q_norm / k_norm, rotate-half RoPE at position pos0 + t.  Query heads stay
+// fp32 (qr[t][head][128]); K (normalised, rotated) and V go to the fp16 cache rows of this layer.
+// grid = T, block = 256 = 8 warps; warp w handles query heads w and w + 8, K head w and V head w, with the loads of
+// all four issued before the first is used (the kernel is a few dependent round trips per warp: with one head per warp
+// and four blocks per token it spent 13 us on seven waves of blocks at 2048 tokens).
+// in_f16: q / k / v hold fp16 (the projection's epilogue stored halves) instead of fp32.
+__global__ void __launch_bounds__(256)
+qk_norm_rope_cache(const float *q, const float *k, const float *v, int in_f16, const __half *q_norm,
+                   const __half *k_norm, const float *rope, const __half *cos_table,
+                   const __half *sin_table, float *qr, __half *k_cache_layer, __half *v_cache_layer,
+                   int pos0, int max_seq_len) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x, w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = pos0 + t;
   const int d0 = 4 * lane;                      // four consecutive dims per lane: 16-byte accesses
   auto pack4 = [](float a, float b, float c, float d) {
@@ -133,17 +184,18 @@ __global__ void qk_norm_rope_cache(const float *q, const float *k, const float *
     const __half2 a = *reinterpret_cast<const __half2 *>(&raw.x), b = *reinterpret_cast<const __half2 *>(&raw.y);
     return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
   };
-  if (slot >= 24) {   // V head: plain copy to the cache
-    const int g = slot - 24;
-    const float4 x = load4(v, static_cast<size_t>(t) * KVS + g * D + d0);
-    *reinterpret_cast<uint2 *>(v_cache_layer + (static_cast<size_t>(g) * max_seq_len + pos) * D + d0) = pack4(x.x, x.y, x.z, x.w);
-    return;
-  }
-  const bool is_q = slot < 16;
-  const int head = is_q ? slot : slot - 16;
-  const __half *nw = is_q ? q_norm : k_norm;
-  float4 x = is_q ? load4(q, static_cast<size_t>(t) * QS + head * D + d0) : load4(k, static_cast<size_t>(t) * KVS + head * D + d0);
-  const uint2 wraw = *reinterpret_cast<const uint2 *>(nw + d0);
+  auto unpack4 = [](uint2 raw) {
+    const __half2 a = *reinterpret_cast<const __half2 *>(&raw.x), b = *reinterpret_cast<const __half2 *>(&raw.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+  };
+  // ---- every load first
+  float4 x[3];                                  // query heads w and w + 8, K head w
+  x[0] = load4(q, static_cast<size_t>(t) * QS + w * D + d0);
+  x[1] = load4(q, static_cast<size_t>(t) * QS + (w + 8) * D + d0);
+  x[2] = load4(k, static_cast<size_t>(t) * KVS + w * D + d0);
+  const float4 vv = load4(v, static_cast<size_t>(t) * KVS + w * D + d0);
+  const float4 wq4 = unpack4(*reinterpret_cast<const uint2 *>(q_norm + d0));
+  const float4 wk4 = unpack4(*reinterpret_cast<const uint2 *>(k_norm + d0));
   // element i pairs with i + 64 and both use frequency i (i < 64): lanes 0..15 hold the low halves, lane + 16 the
   // partners; the frequencies of this lane's dims are those of dims (d0 mod 64) ..
   const int f0 = d0 & 63;
@@ -153,32 +205,33 @@ __global__ void qk_norm_rope_cache(const float *q, const float *k, const float *
     cs = *reinterpret_cast<const float4 *>(r + f0);
     sn = *reinterpret_cast<const float4 *>(r + 64 + f0);
   } else {
-    const uint2 c2 = *reinterpret_cast<const uint2 *>(cos_table + static_cast<size_t>(pos) * D + f0);
-    const uint2 s2 = *reinterpret_cast<const uint2 *>(sin_table + static_cast<size_t>(pos) * D + f0);
-    const __half2 c01 = *reinterpret_cast<const __half2 *>(&c2.x), c23 = *reinterpret_cast<const __half2 *>(&c2.y);
-    const __half2 s01 = *reinterpret_cast<const __half2 *>(&s2.x), s23 = *reinterpret_cast<const __half2 *>(&s2.y);
-    cs = make_float4(__low2float(c01), __high2float(c01), __low2float(c23), __high2float(c23));
-    sn = make_float4(__low2float(s01), __high2float(s01), __low2float(s23), __high2float(s23));
+    cs = unpack4(*reinterpret_cast<const uint2 *>(cos_table + static_cast<size_t>(pos) * D + f0));
+    sn = unpack4(*reinterpret_cast<const uint2 *>(sin_table + static_cast<size_t>(pos) * D + f0));
   }
-  float ss = fmaf(x.x, x.x, fmaf(x.y, x.y, fmaf(x.z, x.z, x.w * x.w)));
-  ss = warp_sum(ss);
-  const float rstd = 1.0f / sqrtf(ss * (1.0f / D) + RMS_EPS);
-  const __half2 w01 = *reinterpret_cast<const __half2 *>(&wraw.x), w23 = *reinterpret_cast<const __half2 *>(&wraw.y);
-  x.x = x.x * rstd * __low2float(w01); x.y = x.y * rstd * __high2float(w01);
-  x.z = x.z * rstd * __low2float(w23); x.w = x.w * rstd * __high2float(w23);
-  float4 o;   // the partner's normalised values
-  o.x = __shfl_xor_sync(0xffffffffu, x.x, 16); o.y = __shfl_xor_sync(0xffffffffu, x.y, 16);
-  o.z = __shfl_xor_sync(0xffffffffu, x.z, 16); o.w = __shfl_xor_sync(0xffffffffu, x.w, 16);
-  float4 r;
-  if (lane < 16) {    // low half: lo * cos - hi * sin
-    r = make_float4(x.x * cs.x - o.x * sn.x, x.y * cs.y - o.y * sn.y, x.z * cs.z - o.z * sn.z, x.w * cs.w - o.w * sn.w);
-  } else {            // high half: lo * sin + hi * cos
-    r = make_float4(o.x * sn.x + x.x * cs.x, o.y * sn.y + x.y * cs.y, o.z * sn.z + x.z * cs.z, o.w * sn.w + x.w * cs.w);
+  // ---- V head: plain copy to the cache
+  *reinterpret_cast<uint2 *>(v_cache_layer + (static_cast<size_t>(w) * max_seq_len + pos) * D + d0) = pack4(vv.x, vv.y, vv.z, vv.w);
+#pragma unroll
+  for (int h = 0; h < 3; ++h) {
+    const float4 nw = h < 2 ? wq4 : wk4;
+    float4 a = x[h];
+    float ss = fmaf(a.x, a.x, fmaf(a.y, a.y, fmaf(a.z, a.z, a.w * a.w)));
+    ss = warp_sum(ss);
+    const float rstd = 1.0f / sqrtf(ss * (1.0f / D) + RMS_EPS);
+    a.x = a.x * rstd * nw.x; a.y = a.y * rstd * nw.y; a.z = a.z * rstd * nw.z; a.w = a.w * rstd * nw.w;
+    float4 o;   // the partner's normalised values
+    o.x = __shfl_xor_sync(0xffffffffu, a.x, 16); o.y = __shfl_xor_sync(0xffffffffu, a.y, 16);
+    o.z = __shfl_xor_sync(0xffffffffu, a.z, 16); o.w = __shfl_xor_sync(0xffffffffu, a.w, 16);
+    float4 r;
+    if (lane < 16) {    // low half: lo * cos - hi * sin
+      r = make_float4(a.x * cs.x - o.x * sn.x, a.y * cs.y - o.y * sn.y, a.z * cs.z - o.z * sn.z, a.w * cs.w - o.w * sn.w);
+    } else {            // high half: lo * sin + hi * cos
+      r = make_float4(o.x * sn.x + a.x * cs.x, o.y * sn.y + a.y * cs.y, o.z * sn.z + a.z * cs.z, o.w * sn.w + a.w * cs.w);
+    }
+    if (h < 2)
+      *reinterpret_cast<float4 *>(qr + (static_cast<size_t>(t) * NQ + w + 8 * h) * D + d0) = r;
+    else
+      *reinterpret_cast<uint2 *>(k_cache_layer + (static_cast<size_t>(w) * max_seq_len + pos) * D + d0) = pack4(r.x, r.y, r.z, r.w);
   }
-  if (is_q)
-    *reinterpret_cast<float4 *>(qr + (static_cast<size_t>(t) * NQ + head) * D + d0) = r;
-  else
-    *reinterpret_cast<uint2 *>(k_cache_layer + (static_cast<size_t>(head) * max_seq_len + pos) * D + d0) = pack4(r.x, r.y, r.z, r.w);
 }
 
 // Causal attention of the chunk's queries over cache rows [0, pos0 + t] (the chunk's own rows are already in the

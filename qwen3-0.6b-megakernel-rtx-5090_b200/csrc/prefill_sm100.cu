@@ -577,11 +577,17 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
       qmk_tc::PdlScope first(false);            // (follows a copy, not a kernel)
       PF_CUDA(qmk_tc::launch_kernel(embed_rows, dim3(T), dim3(256), 0, stream, w.tokens, embed_weight, wq, w.x));
     }
+    // residual add (+ split-K partials) and RMSNorm: a warp per row for long chunks, a block per row for short ones
+    auto norm_rows = [&](const float *add, const __half *g) {
+      if (T >= 256 && od_splits <= 2)
+        return qmk_tc::launch_kernel(add_rmsnorm_rows_wide, dim3((T + 7) / 8), dim3(256), 0, stream, w.x, add, od_splits, od_stride, g,
+                                     w.xn, T);
+      return qmk_tc::launch_kernel(add_rmsnorm_rows, dim3(T), dim3(256), 0, stream, w.x, add, od_splits, od_stride, g, w.xn);
+    };
     for (int l = 0; l < num_layers; ++l) {
       const unsigned long long *r = rec.data() + static_cast<size_t>(l) * 12;
       __half *kc = static_cast<__half *>(k_cache) + l * layer_stride, *vc = static_cast<__half *>(v_cache) + l * layer_stride;
-      PF_CUDA(qmk_tc::launch_kernel(add_rmsnorm_rows, dim3(T), dim3(256), 0, stream, w.x, l > 0 ? w.down : nullptr, od_splits, od_stride,
-                                    reinterpret_cast<const __half *>(r[0]), w.xn));
+      PF_CUDA(norm_rows(l > 0 ? w.down : nullptr, reinterpret_cast<const __half *>(r[0])));
       {
         const int js[3] = {0, 1, 2};
         float *const cs[3] = {w.q, w.k, w.v};
@@ -595,7 +601,7 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
       }
       // (Folding this kernel into the q/k/v GEMM's epilogue - one 128-wide N tile is one head - was built and measured
       // slower: 128 threads per CTA walking TMEM eight columns at a time lose to 2300 x 4 fully parallel CTAs.)
-      PF_CUDA(qmk_tc::launch_kernel(qk_norm_rope_cache, dim3(T, 4), dim3(256), 0, stream, w.q, w.k, w.v, 1,
+      PF_CUDA(qmk_tc::launch_kernel(qk_norm_rope_cache, dim3(T), dim3(256), 0, stream, w.q, w.k, w.v, 1,
                                     reinterpret_cast<const __half *>(r[4]), reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv,
                                     w.qr, kc, vc, pos0, max_seq_len));
       if (l == num_layers - 1) break;   // the cache is complete; nothing downstream of the last layer is kept
@@ -607,8 +613,7 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
         PF_CUDA(qmk_tc::launch_kernel(causal_attention_mma, dim3((T + ATM_Q - 1) / ATM_Q, NKV), dim3(ATM_THREADS), ATM_SMEM_BYTES, stream,
                                       w.qr, kc, vc, w.attn, T, pos0, max_seq_len, attn_scale));
       if ((rc = gemm_od(w.map_attn, l, 3, w.o, M, QS, T)) != QMK_OK) break;
-      PF_CUDA(qmk_tc::launch_kernel(add_rmsnorm_rows, dim3(T), dim3(256), 0, stream, w.x, w.o, od_splits, od_stride,
-                                    reinterpret_cast<const __half *>(r[7]), w.xn));
+      PF_CUDA(norm_rows(w.o, reinterpret_cast<const __half *>(r[7])));
       {
         const int box_gu = qmk_tc::gemm_box_n_fused(M, I);
         // three of these CTAs per SM instead of two: their epilogue (two TMEM reads, SiLU, fp16 pack) is the long part
