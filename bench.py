@@ -526,7 +526,8 @@ def run_continuous(args):
 def run_prefill_only(args):
     """Chunked tensor-core prefill alone (the step before the decode path): N prompt tokens through
     ``Decoder(prefill_mode="tensor").prefill_ids``, timed with CUDA events; prompt tok/s and dense fp16 TFLOP/s
-    (2 x 440 M matrix weights per token, the LM head is not part of a prefill, + causal attention)."""
+    (2 x the matrix weights a token actually passes - every layer but the last in full, of the last one the q / k / v
+    projection; the LM head is not part of a prefill - + causal attention in the layers that run it)."""
     rank, world, device = init_engine_arm()
     from Model.Qwen06B_architecture import Decoder
     n = args.prefill_only
@@ -547,8 +548,12 @@ def run_prefill_only(args):
     barrier(world)
     ms = statistics.mean(a.elapsed_time(b) for a, b in ev)
     ms = max_over_ranks(ms, world, device)
+    # Work the pass executes: a prefill leaves only cache rows behind, so the last layer stops after its q / k / v
+    # projection (its K and V rows); attention, O and the MLP run in the layers before it.
     per_layer_w = sum(S.math.prod(shape) for _, shape in S.LAYER_FIELDS if len(shape) == 2)
-    flops = n * 2.0 * S.NUM_LAYERS * per_layer_w + S.NUM_LAYERS * 4.0 * 16 * 128 * n * (n + 1) / 2
+    qkv_w = sum(S.math.prod(shape) for name, shape in S.LAYER_FIELDS if name in ("q_proj", "k_proj", "v_proj"))
+    full_layers = S.NUM_LAYERS - 1
+    flops = n * 2.0 * (full_layers * per_layer_w + qkv_w) + full_layers * 4.0 * 16 * 128 * n * (n + 1) / 2
     if rank == 0:
         print(json.dumps({"metric": "chunked tensor-core prefill, prompt tok/s", "value": world * n / (ms / 1e3), "unit": UNIT,
                           "n_gpus": world, "prompt_tokens": n, "ms_per_prefill": ms, "tflops": flops / (ms / 1e3) / 1e12,
