@@ -551,7 +551,9 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
     // The O and down projections have only 1024 output columns: with 128-wide tiles a long chunk gives 128 CTAs for
     // 148 SMs (296 slots with two CTAs per SM) and a K loop of 32 / 48 blocks.  K split in two doubles the CTAs and
     // halves the loop; the partial matrices are added by the residual + RMSNorm kernel that follows anyway.
-    const int od_splits = (M >= 1024 && wq == 0) ? 2 : 1;
+    // Short chunks: four splits (M = 512: 32 tiles x 4 = 128 CTAs with K loops of 8 / 12 blocks; unsplit, the narrowest
+    // tiles gave 128 CTAs with loops of 32 / 48 blocks of N = 32 MMAs and these two products were 41 % of the pass).
+    const int od_splits = wq != 0 ? 1 : M >= 1024 ? 2 : 4;
     const size_t od_stride = od_splits > 1 ? static_cast<size_t>(M) * H : 0;
     auto gemm_od = [&](const CUtensorMap &a, int l, int j, float *c, int Mrows, int K, int live) {
       if (od_splits == 1) return gemm(a, l, j, c, Mrows, H, K, live);
