@@ -309,7 +309,7 @@ int qmk_generate_static(
     int *output_log, int num_layers, int start_position, int max_seq_len,
     float attn_scale, int eos_token_id, cudaStream_t stream);
 
-/* qmk_prefill on the tensor cores: the prompt is processed in chunks of up to 2048 tokens; per layer the
+/* qmk_prefill on the tensor cores: the prompt is processed in chunks of up to 4096 tokens; per layer the
  * seven projections run as tcgen05 GEMMs over the whole chunk (weights are read once per chunk instead
  * of once per token, megakernel_5090.cu:1324-1350), with row-wise kernels for RMSNorm, per-head QK-norm +
  * RoPE + cache write, causal attention over the cache, and SwiGLU between them.  Same arguments, cache

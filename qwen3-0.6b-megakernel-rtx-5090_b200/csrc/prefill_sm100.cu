@@ -362,7 +362,7 @@ int launch_gemm(const CUtensorMap &map_a, const CUtensorMap &map_b, float *C, in
 namespace {
 
 constexpr unsigned int PREFILL_RING_BYTES = 96 * 1024, GATE_UP_RING_BYTES = 64 * 1024;
-constexpr int CHUNK = 2048;         // prompt tokens per pass over the weights (a multiple of the GEMM's 128)
+constexpr int CHUNK = 4096;         // prompt tokens per pass over the weights (a multiple of the GEMM's 128)
 constexpr int MAX_LAYERS = 48;
 
 struct Workspace {                  // per device, allocated on first use, never freed (like the engine's scratch)

@@ -489,7 +489,7 @@ def decode_batched(first_token_ids, start_positions, num_steps, embed_weight, la
 
 def prefill_chunked(token_ids, embed_weight, layer_weights_packed, cos_table, sin_table, k_cache, v_cache,
                     num_layers, start_position, max_seq_len, attn_scale):
-    """``prefill`` on the tensor cores (chunks of up to 2048 tokens, tcgen05 GEMMs; fp16 weights only).
+    """``prefill`` on the tensor cores (chunks of up to 4096 tokens, tcgen05 GEMMs; fp16 weights only).
     ``token_ids``: CPU int32 tensor.  Blocks; raises ``RuntimeError`` on any reported error."""
     _require_cuda()
     _check((not token_ids.is_cuda) and token_ids.dtype == torch.int32 and token_ids.is_contiguous(),
