@@ -391,6 +391,14 @@ def continuous_case(device, rank, world, fp16_weights, requests, slots, prefill=
         inner(b, ids)
         prefill_s[0] += time.perf_counter() - t
     eng.prefill_slot = timed_prefill
+    if hasattr(eng, "prefill_slots"):                          # several waiting requests in one pass
+        inner_many = eng.prefill_slots
+
+        def timed_prefill_many(bs, many):
+            t = time.perf_counter()
+            inner_many(bs, many)
+            prefill_s[0] += time.perf_counter() - t
+        eng.prefill_slots = timed_prefill_many
     sch = ContinuousBatcher(eng, eos_token_id=None, quantum=32,
                             overlap_prefill=bool(overlap) and getattr(eng, "supports_overlap", False))
     sch.submit(prompts[0][:64], 8)                             # warm-up: both kernels, all buffers

@@ -323,6 +323,20 @@ int qmk_prefill_chunked(
     void *k_cache, void *v_cache, int num_layers, int start_position, int max_seq_len,
     float attn_scale, cudaStream_t stream);
 
+/* Several prompts in ONE pass of qmk_prefill_chunked (no counterpart in the reference, whose prefill is one sequence;
+ * the continuous-batching caller admits waiting requests together): sequence s has seq_lens[s] tokens - all of them
+ * concatenated in token_ids_host - and its own caches k_caches[s] / v_caches[s] (HOST arrays of device pointers, the
+ * layout of qmk_prefill), filled from position 0.  The sequences become consecutive row ranges of one chunk, each
+ * padded to whole 128-row tiles (at most 64 sequences and 4096 padded rows per call); the GEMMs and row kernels run
+ * once over all rows, the attention kernel takes (sequence, query tile, head) items and reads each sequence's cache
+ * through its own tensor map.  Needs the tcgen05 attention kernel (qmk_set_prefill_attention(1), the default).  Every
+ * cache ends up as qmk_prefill_chunked would have left it, to the rounding of a different GEMM tiling.  Blocks. */
+int qmk_prefill_packed(
+    const int *token_ids_host, int num_seqs, const int *seq_lens, const void *embed_weight,
+    const struct LDGLayerWeight *layer_weights, const void *cos_table, const void *sin_table,
+    void *const *k_caches, void *const *v_caches, int num_layers, int max_seq_len,
+    float attn_scale, cudaStream_t stream);
+
 /* Greedy decode of up to 128 sequences on the tensor-core path (the batched configurations): each step runs
  * the seven projections and the LM head as tcgen05 GEMMs over one 128-row tile of sequences, with row kernels
  * for the norms, per-head QK-norm + RoPE + cache write (each sequence at its own position in its own cache),

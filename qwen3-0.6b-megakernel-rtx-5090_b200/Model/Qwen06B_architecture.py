@@ -410,6 +410,40 @@ class BatchDecoder:
 
     _prefill_slot = prefill_slot
 
+    @property
+    def packed_prefill_rows(self) -> int:
+        """Rows one ``prefill_slots`` pass may hold (each prompt padded to a multiple of 128); 0: no packed prefill."""
+        base = self._base
+        return 4096 if base.prefill_mode == "tensor" else 0
+
+    def prefill_slots(self, slots: Sequence[int], prompts: Sequence[Sequence[int]]) -> None:
+        """Fill the caches of several slots in ONE tensor-core pass (``qmk_prefill_packed``): weights are read once for all
+        of them and a pass's ~200 launches are shared.  Empty prompts are skipped (their slot starts at position 0)."""
+        slots = [int(b) for b in slots]
+        if len(slots) != len(prompts) or len(set(slots)) != len(slots) or not all(0 <= b < self.num_sequences for b in slots):
+            raise ValueError("slots must be distinct, in range, one per prompt")
+        base = self._base
+        if base.prefill_mode != "tensor":
+            raise RuntimeError("prefill_slots needs prefill_mode='tensor'")
+        todo = [(b, list(ids)) for b, ids in zip(slots, prompts) if len(ids) > 0]
+        for _, ids in todo:
+            if len(ids) > self.max_seq_len:
+                raise ValueError("prompt exceeds max_seq_len")
+        if todo:
+            base.apply_options()
+            args = ([ids for _, ids in todo], base._embed_weight, base._layer_weights_packed, base._cos_table, base._sin_table,
+                    [self._k_caches[b] for b, _ in todo], [self._v_caches[b] for b, _ in todo], base.num_layers, self.max_seq_len,
+                    base._attn_scale)
+            op = _require_megakernel_op("prefill_packed")
+            if self._prefill_stream is not None:
+                with torch.cuda.stream(self._prefill_stream):   # the op blocks until its stream is idle
+                    op(*args)
+            else:
+                op(*args)
+        for b, ids in zip(slots, prompts):
+            self.positions[b] = len(ids)
+
+
     def decode_slots(self, slots: Sequence[int], first_tokens: Sequence[int], steps: int) -> List[List[int]]:
         """One launch: ``steps`` greedy tokens for every slot in ``slots`` (any subset, each from its own
         position and ``first_tokens`` entry).  Returns the raw token lists (no EOS cut) and advances

@@ -104,19 +104,36 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // cache rows 0 .. pos0 + t).  map_k / map_v: 3-D maps {128 dims, pos0 + T rows, layers x 8 kv heads} of the fp16
 // caches, boxes of {64, 64, 1}, 128-byte swizzle.  out: fp16 [T][2048].  grid = ceil(T / 128) * 16 CTAs in one
 // dimension, numbered from the heaviest (last) query tile down: causal tile i sees 2 (i + 1) key tiles of 64.
+//
+// Packed prompts (items != null): the rows hold several sequences, each padded to whole query tiles.  CTA i takes
+// items[i] = {sequence, first row of the query tile, its position within the sequence, head | length << 8} (sorted
+// from the heaviest down by the host) and reads that sequence's caches through maps_dev[2 seq], maps_dev[2 seq + 1]
+// in device memory; T and pos0 are then not used.
 __global__ void __launch_bounds__(THREADS, 1)
 causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                     int layer_head0, __half *out, int T, int pos0, float scale, unsigned int *status,
-                    unsigned long long budget_ns) {
+                    unsigned long long budget_ns, const int4 *items, const CUtensorMap *maps_dev) {
   using namespace qmk_gemm;
   extern __shared__ __align__(1024) unsigned char attn_smem[];
   const uint32_t base = s32(attn_smem);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total = static_cast<int>(gridDim.x), id = static_cast<int>(blockIdx.x);
-  const int head = id % NQ, g = head >> 1;
-  const int q0 = (total / NQ - 1 - id / NQ) * TQ;
+  int head = id % NQ;
+  int q0 = (total / NQ - 1 - id / NQ) * TQ;
+  int pbase = pos0 + q0;                       // position of the tile's first query in its sequence
+  const CUtensorMap *mk = &map_k, *mv = &map_v;
+  if (items != nullptr) {
+    const int4 it = items[id];
+    head = it.w & 0xff;
+    q0 = it.y;
+    pbase = it.z;
+    T = it.y - it.z + (it.w >> 8);             // the sequence's end among the rows
+    mk = maps_dev + 2 * it.x;
+    mv = mk + 1;
+  }
+  const int g = head >> 1;
   const int last_q = (q0 + TQ < T ? q0 + TQ : T) - 1;                                        // last live query of the tile
-  const int ntiles = (pos0 + last_q) / TK + 1;                                              // key tiles it can see
+  const int ntiles = (pbase + last_q - q0) / TK + 1;                                        // key tiles it can see
   const uint32_t bars = base + OFF_BARS;
   auto k_full = [&](int s) { return bars + 8u * s; };
   auto k_empty = [&](int s) { return bars + 8u * (4 + s); };
@@ -135,8 +152,10 @@ causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, 
     return;
   }
   if (threadIdx.x == 0) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
+    if (items == nullptr) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
+    }
     for (int s = 0; s < STAGES; ++s) {
       bar_init(k_full(s), 1); bar_init(k_empty(s), 1); bar_init(v_full(s), 1); bar_init(v_empty(s), 1);
     }
@@ -166,10 +185,15 @@ causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, 
     const uint32_t d0 = base + (is_v ? OFF_V + s * 2 * K_HALF_BYTES : OFF_K + s * K_HALF_BYTES);
     const uint32_t d1 = d0 + (is_v ? K_HALF_BYTES : STAGES * K_HALF_BYTES);
     bar_expect_tx(full, 2 * K_HALF_BYTES);
-    tma_load_3d(d0, is_v ? &map_v : &map_k, 0, j * TK, layer_head0 + g, full);
-    tma_load_3d(d1, is_v ? &map_v : &map_k, 64, j * TK, layer_head0 + g, full);
+    tma_load_3d(d0, is_v ? mv : mk, 0, j * TK, layer_head0 + g, full);
+    tma_load_3d(d1, is_v ? mv : mk, 64, j * TK, layer_head0 + g, full);
   };
   int k_prefilled = 0;
+  if (items != nullptr && lane == 0 && (warp == 0 || warp == 3 + 4 * CHAINS)) {
+    // descriptors written by a copy before this launch: the loading threads make them visible to their TMA unit
+    asm volatile("fence.proxy.tensormap::generic.acquire.sys [%0], 128;" ::"l"(reinterpret_cast<uint64_t>(mk)) : "memory");
+    asm volatile("fence.proxy.tensormap::generic.acquire.sys [%0], 128;" ::"l"(reinterpret_cast<uint64_t>(mv)) : "memory");
+  }
   if (threadIdx.x == 0)
     for (; k_prefilled < STAGES && k_prefilled < ntiles; ++k_prefilled) load_tile(false, k_prefilled);
   if (warp >= 2 && warp < 2 + 4 * CHAINS) {
@@ -272,7 +296,7 @@ causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, 
   } else {                                 // ---- softmax: chain = warp group, thread = query row = TMEM lane
     const int chain = (warp - 2) >> 2;
     const int quarter = warp & 3, row = quarter * 32 + lane;
-    const int qpos = pos0 + q0 + row;      // (rows past T compute on zeros and are not stored)
+    const int qpos = pbase + row;          // (rows past T compute on zeros and are not stored)
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t tmem_o = tmem_o0 + 128u * static_cast<uint32_t>(chain);
     const uint32_t p_tile = base + OFF_P + static_cast<uint32_t>(chain) * P_BYTES;
@@ -292,7 +316,7 @@ causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, 
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s_free(n & 1)) : "memory");
       const int k0 = j * TK;
-      const bool diagonal = k0 + TK - 1 > pos0 + q0;        // some key of the tile is ahead of some query of the CTA
+      const bool diagonal = k0 + TK - 1 > pbase;            // some key of the tile is ahead of some query of the CTA
       if (diagonal) {
 #pragma unroll
         for (int c = 0; c < 32; ++c) {

@@ -161,15 +161,25 @@ add_rmsnorm_rows_wide(float *x, const float *add, int nparts, size_t part_stride
 // all four issued before the first is used (the kernel is a few dependent round trips per warp: with one head per warp
 // and four blocks per token it spent 13 us on seven waves of blocks at 2048 tokens).
 // in_f16: q / k / v hold fp16 (the projection's epilogue stored halves) instead of fp32.
+// Packed prompts (row_info != null): row t belongs to sequence row_info[t].x at position row_info[t].y (negative:
+// a padding row, nothing to do), whose K / V caches start at kv_ptrs[2 seq], kv_ptrs[2 seq + 1]; the layer's rows
+// begin `layer_off` halves into each.
 __global__ void __launch_bounds__(256)
 qk_norm_rope_cache(const float *q, const float *k, const float *v, int in_f16, const __half *q_norm,
                    const __half *k_norm, const float *rope, const __half *cos_table,
                    const __half *sin_table, float *qr, __half *k_cache_layer, __half *v_cache_layer,
-                   int pos0, int max_seq_len) {
+                   int pos0, int max_seq_len, const int2 *row_info, const unsigned long long *kv_ptrs, size_t layer_off) {
   pdl_wait();
   pdl_trigger();
   const int t = blockIdx.x, w = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int pos = pos0 + t;
+  int pos = pos0 + t;
+  if (row_info != nullptr) {
+    const int2 info = row_info[t];
+    if (info.y < 0) return;
+    pos = info.y;
+    k_cache_layer = reinterpret_cast<__half *>(kv_ptrs[2 * info.x]) + layer_off;
+    v_cache_layer = reinterpret_cast<__half *>(kv_ptrs[2 * info.x + 1]) + layer_off;
+  }
   const int d0 = 4 * lane;                      // four consecutive dims per lane: 16-byte accesses
   auto pack4 = [](float a, float b, float c, float d) {
     const __half2 lo = __floats2half2_rn(a, b), hi = __floats2half2_rn(c, d);

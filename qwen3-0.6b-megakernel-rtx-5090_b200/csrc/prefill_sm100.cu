@@ -7,6 +7,7 @@
 #include <stdlib.h>
 #include <string.h>
 #include <mutex>
+#include <algorithm>
 #include <string>
 
 #include "../../include/qwen_megakernel.h"
@@ -383,6 +384,7 @@ struct Workspace {                  // per device, allocated on first use, never
   unsigned long long graph_epoch = 1;    // bumped whenever tensor maps baked into the graphs are rebuilt
   __half **k_ptrs = nullptr, **v_ptrs = nullptr;
   CUtensorMap *kv_maps = nullptr;        // [128][2]: tiled-copy descriptors of every sequence's K and V cache (decode_attention_mma)
+  unsigned char *packed = nullptr;       // tables of a packed prefill (row info, attention items, per-sequence descriptors and cache pointers)
   int **log_ptrs = nullptr;
   float *split_part = nullptr;            // partial attention states of split sequences (decode_attention_ring)
   unsigned int *split_count = nullptr;    // arrival counters, one per (sequence, kv head); zero between launches
@@ -481,22 +483,44 @@ int ensure_weight_maps(Workspace &w, const LDGLayerWeight *layers_dev, int num_l
 
 }  // namespace
 
-extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, const void *embed_weight,
-                                   const LDGLayerWeight *layer_weights, const void *cos_table, const void *sin_table,
-                                   void *k_cache, void *v_cache, int num_layers, int start_position, int max_seq_len,
-                                   float attn_scale, cudaStream_t stream) {
+namespace {
+// Several prompts in one pass: sequence s holds lens[s] tokens (concatenated in token_ids_host) and owns the caches
+// k_caches[s] / v_caches[s]; every sequence starts at position 0.
+struct PackedSeqs {
+  int num_seqs;
+  const int *lens;
+  void *const *k_caches, *const *v_caches;
+};
+constexpr int MAX_PACKED_SEQS = 64;
+constexpr size_t PK_ROWS_OFF = 0, PK_ITEMS_OFF = 32768, PK_MAPS_OFF = 49152, PK_PTRS_OFF = 65536, PK_BYTES = 66560;
+
+int prefill_impl(const int *token_ids_host, int num_tokens, const void *embed_weight, const LDGLayerWeight *layer_weights,
+                 const void *cos_table, const void *sin_table, void *k_cache, void *v_cache, int num_layers,
+                 int start_position, int max_seq_len, float attn_scale, cudaStream_t stream, const PackedSeqs *pk) {
   using namespace qmk_pf;
   if (num_tokens <= 0) return QMK_OK;
   qmk_internal::PrefillEnv env;
   int rc = qmk_internal::prefill_env(max_seq_len, stream, &env);
   if (rc != QMK_OK) return rc;
-  if (!token_ids_host || !embed_weight || !layer_weights || !k_cache || !v_cache)
+  if (!token_ids_host || !embed_weight || !layer_weights || (!pk && (!k_cache || !v_cache)))
     return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "prefill: null pointer argument");
   const int wq = env.wfmt;   // 0 fp16, 1 FP8-E4M3 rows, 2 NVFP4 rows: packed matrices are expanded inside the GEMM
   if (num_layers < 1 || num_layers > MAX_LAYERS)
     return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "num_layers must be in [1, 48]");
-  if (start_position < 0 || start_position + num_tokens > max_seq_len)
+  if (!pk && (start_position < 0 || start_position + num_tokens > max_seq_len))
     return qmk_internal::report(QMK_ERR_POSITION, "start_position + steps exceeds max_seq_len");
+  if (pk) {
+    if (pk->num_seqs < 1 || pk->num_seqs > MAX_PACKED_SEQS || !pk->lens || !pk->k_caches || !pk->v_caches || start_position != 0)
+      return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "packed prefill: 1 to 64 sequences, each from position 0");
+    int total = 0;
+    for (int s = 0; s < pk->num_seqs; ++s) {
+      if (pk->lens[s] < 1 || !pk->k_caches[s] || !pk->v_caches[s])
+        return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "packed prefill: empty sequence or null cache");
+      if (pk->lens[s] > max_seq_len) return qmk_internal::report(QMK_ERR_POSITION, "a prompt exceeds max_seq_len");
+      total += pk->lens[s];
+    }
+    if (total != num_tokens) return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "packed prefill: lengths do not add up to num_tokens");
+  }
   if (env.rope_from_table && (!cos_table || !sin_table))
     return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "rope_from_table needs cos/sin tables");
   for (int i = 0; i < num_tokens; ++i)
@@ -510,6 +534,55 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
   rc = ensure_workspace(w, CHUNK);
   if (rc == QMK_OK) rc = ensure_weight_maps(w, layer_weights, num_layers, wq, stream);
   if (rc != QMK_OK) return rc;
+  // ---- packed prompts: rows = the sequences one after the other, each padded to whole 128-row tiles
+  std::vector<int> padded_tokens;
+  std::vector<unsigned char> pk_host;
+  int pk_items = 0;
+  if (pk) {
+    if (!env.attn_tc) return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "packed prefill needs the tcgen05 attention kernel");
+    if (!w.packed) PF_CUDA(cudaMalloc(&w.packed, PK_BYTES));
+    pk_host.assign(PK_BYTES, 0);
+    int2 *rows = reinterpret_cast<int2 *>(pk_host.data() + PK_ROWS_OFF);
+    int4 *items = reinterpret_cast<int4 *>(pk_host.data() + PK_ITEMS_OFF);
+    CUtensorMap *maps = reinterpret_cast<CUtensorMap *>(pk_host.data() + PK_MAPS_OFF);
+    unsigned long long *ptrs = reinterpret_cast<unsigned long long *>(pk_host.data() + PK_PTRS_OFF);
+    int total_rows = 0;
+    for (int s = 0; s < pk->num_seqs; ++s) total_rows += (pk->lens[s] + qmk_gemm::BM - 1) / qmk_gemm::BM * qmk_gemm::BM;
+    if (total_rows > CHUNK) return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "packed prefill: more than 4096 padded rows");
+    padded_tokens.assign(total_rows, 0);
+    for (int i = 0; i < total_rows; ++i) rows[i] = make_int2(0, -1);
+    std::vector<std::pair<int, int4>> order;   // (key tiles, item)
+    std::string merr;
+    int row0 = 0, tok0 = 0;
+    for (int s = 0; s < pk->num_seqs; ++s) {
+      const int len = pk->lens[s];
+      for (int i = 0; i < len; ++i) {
+        padded_tokens[row0 + i] = token_ids_host[tok0 + i];
+        rows[row0 + i] = make_int2(s, i);
+      }
+      ptrs[2 * s] = reinterpret_cast<unsigned long long>(pk->k_caches[s]);
+      ptrs[2 * s + 1] = reinterpret_cast<unsigned long long>(pk->v_caches[s]);
+      int mrc = qmk_tc::make_map_kv(&maps[2 * s], pk->k_caches[s], static_cast<uint64_t>(len), static_cast<uint64_t>(max_seq_len),
+                                    static_cast<uint64_t>(num_layers) * NKV, &merr);
+      if (mrc == QMK_OK)
+        mrc = qmk_tc::make_map_kv(&maps[2 * s + 1], pk->v_caches[s], static_cast<uint64_t>(len), static_cast<uint64_t>(max_seq_len),
+                                  static_cast<uint64_t>(num_layers) * NKV, &merr);
+      if (mrc != QMK_OK) return qmk_internal::report(mrc, merr);
+      for (int qt = 0; qt * qmk_attn::TQ < len; ++qt) {
+        const int last = (qt + 1) * qmk_attn::TQ < len ? (qt + 1) * qmk_attn::TQ - 1 : len - 1;
+        for (int h = 0; h < NQ; ++h)
+          order.push_back({last / qmk_attn::TK + 1, make_int4(s, row0 + qt * qmk_attn::TQ, qt * qmk_attn::TQ, h | (len << 8))});
+      }
+      row0 += (len + qmk_gemm::BM - 1) / qmk_gemm::BM * qmk_gemm::BM;
+      tok0 += len;
+    }
+    std::stable_sort(order.begin(), order.end(), [](const auto &a, const auto &b) { return a.first > b.first; });   // longest job first
+    pk_items = static_cast<int>(order.size());
+    for (int i = 0; i < pk_items; ++i) items[i] = order[i].second;
+    PF_CUDA(cudaMemcpyAsync(w.packed, pk_host.data(), PK_BYTES, cudaMemcpyHostToDevice, stream));
+    token_ids_host = padded_tokens.data();
+    num_tokens = total_rows;
+  }
   std::vector<unsigned long long> rec(w.table, w.table + static_cast<size_t>(num_layers) * 12);
   const float *rope = env.rope_from_table ? nullptr : env.rope;
   const __half *cosv = static_cast<const __half *>(cos_table), *sinv = static_cast<const __half *>(sin_table);
@@ -569,7 +642,9 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
                                         live, 0, wq, wptr(l, j));
     };
     CUtensorMap map_kc, map_vc;   // the caches up to this chunk's last position, all layers
-    if (env.attn_tc) {
+    memset(&map_kc, 0, sizeof(map_kc));
+    memset(&map_vc, 0, sizeof(map_vc));
+    if (env.attn_tc && !pk) {
       rc = qmk_tc::make_map_kv(&map_kc, k_cache, static_cast<uint64_t>(pos0 + T), static_cast<uint64_t>(max_seq_len),
                                static_cast<uint64_t>(num_layers) * NKV, &err);
       if (rc == QMK_OK)
@@ -596,7 +671,8 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
     };
     for (int l = 0; l < num_layers; ++l) {
       const unsigned long long *r = rec.data() + static_cast<size_t>(l) * 12;
-      __half *kc = static_cast<__half *>(k_cache) + l * layer_stride, *vc = static_cast<__half *>(v_cache) + l * layer_stride;
+      __half *kc = pk ? nullptr : static_cast<__half *>(k_cache) + l * layer_stride;
+      __half *vc = pk ? nullptr : static_cast<__half *>(v_cache) + l * layer_stride;
       PF_CUDA(norm_rows(l > 0 ? w.down : nullptr, reinterpret_cast<const __half *>(r[0])));
       {
         const int js[3] = {0, 1, 2};
@@ -613,12 +689,17 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
       // slower: 128 threads per CTA walking TMEM eight columns at a time lose to 2300 x 4 fully parallel CTAs.)
       PF_CUDA(qmk_tc::launch_kernel(qk_norm_rope_cache, dim3(T), dim3(256), 0, stream, w.q, w.k, w.v, 1,
                                     reinterpret_cast<const __half *>(r[4]), reinterpret_cast<const __half *>(r[5]), rope, cosv, sinv,
-                                    w.qr, kc, vc, pos0, max_seq_len));
+                                    w.qr, kc, vc, pos0, max_seq_len,
+                                    pk ? reinterpret_cast<const int2 *>(w.packed + PK_ROWS_OFF) : nullptr,
+                                    pk ? reinterpret_cast<const unsigned long long *>(w.packed + PK_PTRS_OFF) : nullptr,
+                                    static_cast<size_t>(l) * layer_stride));
       if (l == num_layers - 1) break;   // the cache is complete; nothing downstream of the last layer is kept
       if (env.attn_tc)
-        PF_CUDA(qmk_tc::launch_kernel(qmk_attn::causal_attention_tc, dim3((T + qmk_attn::TQ - 1) / qmk_attn::TQ * NQ),
+        PF_CUDA(qmk_tc::launch_kernel(qmk_attn::causal_attention_tc, dim3(pk ? pk_items : (T + qmk_attn::TQ - 1) / qmk_attn::TQ * NQ),
                                       dim3(qmk_attn::THREADS), qmk_attn::SMEM_BYTES, stream, w.qr, map_kc, map_vc, l * NKV, w.attn, T,
-                                      pos0, attn_scale, w.status, static_cast<unsigned long long>(env.timeout_ms) * 1000000ull));
+                                      pos0, attn_scale, w.status, static_cast<unsigned long long>(env.timeout_ms) * 1000000ull,
+                                      pk ? reinterpret_cast<const int4 *>(w.packed + PK_ITEMS_OFF) : nullptr,
+                                      pk ? reinterpret_cast<const CUtensorMap *>(w.packed + PK_MAPS_OFF) : nullptr));
       else
         PF_CUDA(qmk_tc::launch_kernel(causal_attention_mma, dim3((T + ATM_Q - 1) / ATM_Q, NKV), dim3(ATM_THREADS), ATM_SMEM_BYTES, stream,
                                       w.qr, kc, vc, w.attn, T, pos0, max_seq_len, attn_scale));
@@ -647,6 +728,28 @@ extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, co
                                 host_status[0] == 5 ? "prefill: dynamic shared memory of the attention kernel is not 1024-byte aligned"
                                                     : "prefill: a bounded device wait ran out");
   return QMK_OK;
+}
+}  // namespace
+
+extern "C" int qmk_prefill_chunked(const int *token_ids_host, int num_tokens, const void *embed_weight,
+                                   const LDGLayerWeight *layer_weights, const void *cos_table, const void *sin_table,
+                                   void *k_cache, void *v_cache, int num_layers, int start_position, int max_seq_len,
+                                   float attn_scale, cudaStream_t stream) {
+  return prefill_impl(token_ids_host, num_tokens, embed_weight, layer_weights, cos_table, sin_table, k_cache, v_cache, num_layers,
+                      start_position, max_seq_len, attn_scale, stream, nullptr);
+}
+
+extern "C" int qmk_prefill_packed(const int *token_ids_host, int num_seqs, const int *seq_lens, const void *embed_weight,
+                                  const LDGLayerWeight *layer_weights, const void *cos_table, const void *sin_table,
+                                  void *const *k_caches, void *const *v_caches, int num_layers, int max_seq_len, float attn_scale,
+                                  cudaStream_t stream) {
+  if (num_seqs <= 0) return QMK_OK;
+  if (!seq_lens) return qmk_internal::report(QMK_ERR_BAD_ARGUMENT, "packed prefill: null lengths");
+  long total = 0;
+  for (int s = 0; s < num_seqs && s < MAX_PACKED_SEQS; ++s) total += seq_lens[s] > 0 ? seq_lens[s] : 0;
+  const PackedSeqs pk = {num_seqs, seq_lens, k_caches, v_caches};
+  return prefill_impl(token_ids_host, static_cast<int>(total), embed_weight, layer_weights, cos_table, sin_table, nullptr, nullptr,
+                      num_layers, 0, max_seq_len, attn_scale, stream, &pk);
 }
 
 // ----------------------------------------------------------------------------- batched decode on the GEMM path

@@ -81,6 +81,8 @@ _lib.qmk_decode_batched.argtypes = [_I, _P, _P, _I, *([_P] * 6), _P, _P, _P, _I,
 _lib.qmk_decode_batched.restype = _I
 _lib.qmk_prefill_chunked.argtypes = [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _P]
 _lib.qmk_prefill_chunked.restype = _I
+_lib.qmk_prefill_packed.argtypes = [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _F, _P]
+_lib.qmk_prefill_packed.restype = _I
 _lib.qmk_gemm_f16_tn.argtypes = [_P, _P, _P, _I, _I, _I, _P]
 _lib.qmk_gemm_f16_tn.restype = _I
 _lib.qmk_gemm_packed_tn.argtypes = [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]
@@ -116,7 +118,7 @@ _lib.qmk_selftest_gemm_wait_timeout.restype = _I
 EXPORTED_SYMBOLS = (
     "launch_ldg_decode_direct", "launch_ldg_decode_persistent", "launch_ldg_generate_nosync",
     "launch_ldg_prefill", "qmk_abi_version", "qmk_configure", "qmk_set_inv_freq", "qmk_set_logits_dump",
-    "qmk_set_weight_format", "qmk_set_tuning", "qmk_set_tuning2", "qmk_set_profile_buffer", "qmk_set_fused", "qmk_set_step_overlap", "qmk_set_prefill_attention", "qmk_set_decode_attention", "qmk_invalidate_weights", "qmk_release_weights", "qmk_decode", "qmk_generate", "qmk_generate_static", "qmk_generate_batch", "qmk_gemm_f16_tn", "qmk_gemm_packed_tn", "qmk_decode_batched", "qmk_prefill_chunked", "qmk_prefill", "qmk_engine_create", "qmk_engine_destroy", "qmk_engine_apply", "qmk_engine_decode", "qmk_engine_generate", "qmk_engine_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
+    "qmk_set_weight_format", "qmk_set_tuning", "qmk_set_tuning2", "qmk_set_profile_buffer", "qmk_set_fused", "qmk_set_step_overlap", "qmk_set_prefill_attention", "qmk_set_decode_attention", "qmk_invalidate_weights", "qmk_release_weights", "qmk_decode", "qmk_generate", "qmk_generate_static", "qmk_generate_batch", "qmk_gemm_f16_tn", "qmk_gemm_packed_tn", "qmk_decode_batched", "qmk_prefill_chunked", "qmk_prefill_packed", "qmk_prefill", "qmk_engine_create", "qmk_engine_destroy", "qmk_engine_apply", "qmk_engine_decode", "qmk_engine_generate", "qmk_engine_prefill", "qmk_sync_status", "qmk_last_error", "qmk_num_ctas",
     "qmk_scratch_bytes", "qmk_selftest_wait_timeout", "qmk_selftest_gemm_wait_timeout",
 )
 
@@ -501,6 +503,27 @@ def prefill_chunked(token_ids, embed_weight, layer_weights_packed, cos_table, si
         int(max_seq_len), float(attn_scale), _stream())
     if rc != 0:
         raise RuntimeError(f"prefill_chunked: {_lib.qmk_last_error().decode()} (status {rc})")
+    return None
+
+
+def prefill_packed(token_lists, embed_weight, layer_weights_packed, cos_table, sin_table, k_caches, v_caches,
+                   num_layers, max_seq_len, attn_scale):
+    """Several prompts in one tensor-core prefill pass: ``token_lists[s]`` (ints) fills ``k_caches[s]`` / ``v_caches[s]``
+    from position 0.  At most 64 sequences and 4096 rows after padding each prompt to a multiple of 128.  Blocks;
+    raises ``RuntimeError`` on any reported error."""
+    _require_cuda()
+    n = len(token_lists)
+    _check(n >= 1 and n == len(k_caches) == len(v_caches), "prefill_packed: one cache pair per prompt")
+    _check_table(layer_weights_packed, "prefill_packed")
+    flat = [int(t) for ids in token_lists for t in ids]
+    tok = (ctypes.c_int * max(len(flat), 1))(*flat)
+    lens = (ctypes.c_int * n)(*[len(ids) for ids in token_lists])
+    kp = (ctypes.c_void_p * n)(*[_ptr(c) for c in k_caches])
+    vp = (ctypes.c_void_p * n)(*[_ptr(c) for c in v_caches])
+    rc = _lib.qmk_prefill_packed(tok, n, lens, _ptr(embed_weight), _ptr(layer_weights_packed), _ptr(cos_table), _ptr(sin_table),
+                                 kp, vp, int(num_layers), int(max_seq_len), float(attn_scale), _stream())
+    if rc != 0:
+        raise RuntimeError(f"prefill_packed: {_lib.qmk_last_error().decode()} (status {rc})")
     return None
 
 

@@ -98,31 +98,56 @@ class ContinuousBatcher:
 
     # ------------------------------------------------------------------ one scheduling round
     def _admit(self) -> None:
-        """Prefills waiting requests into free slots until one of the two runs out."""
+        """Prefills waiting requests into free slots until one of the two runs out.  An engine with ``prefill_slots``
+        (several prompts in one pass, up to ``packed_prefill_rows`` rows after padding each to a multiple of 128)
+        gets every waiting request that fits at once: a pass over one ~1000-token prompt is mostly launch latency."""
+        packed = getattr(self.engine, "prefill_slots", None)
+        budget = int(getattr(self.engine, "packed_prefill_rows", 0)) if packed is not None else 0
         while True:
             with self._wake:
                 if not self._waiting or not self._free:
                     return
-                req = self._waiting.popleft()
-                slot = self._free.pop(0)
-                self._prefilling += 1
-            try:
-                self.engine.prefill_slot(slot, req.prompt_ids[:-1])
-            except Exception as exc:           # a bad prompt fails its own request only
-                with self._wake:
-                    self._free.append(slot)
-                    self._free.sort()
-                    self._prefilling -= 1
-                    self._wake.notify_all()
-                req.future.set_exception(exc)
-                continue
-            req.slot = slot
-            req.next_token = req.prompt_ids[-1]
+                group = []
+                rows = 0
+                while self._waiting and self._free and len(group) < 64:
+                    need = (max(len(self._waiting[0].prompt_ids) - 1, 1) + 127) // 128 * 128
+                    if group and (budget <= 0 or rows + need > budget):
+                        break
+                    rows += need
+                    group.append((self._waiting.popleft(), self._free.pop(0)))
+                    if budget <= 0:
+                        break
+                self._prefilling += len(group)
+            if len(group) > 1:
+                try:
+                    packed([slot for _, slot in group], [req.prompt_ids[:-1] for req, _ in group])
+                    failed = {}
+                except Exception:              # find the culprit: fall back to one pass per request
+                    failed = None
+            else:
+                failed = None
+            if failed is None:
+                failed = {}
+                for req, slot in group:
+                    try:
+                        self.engine.prefill_slot(slot, req.prompt_ids[:-1])
+                    except Exception as exc:   # a bad prompt fails its own request only
+                        failed[slot] = exc
             with self._wake:
-                self._live[slot] = req
-                self._prefilling -= 1
+                for req, slot in group:
+                    self._prefilling -= 1
+                    if slot in failed:
+                        self._free.append(slot)
+                        self._free.sort()
+                    else:
+                        req.slot = slot
+                        req.next_token = req.prompt_ids[-1]
+                        self._live[slot] = req
                 self.max_live = max(self.max_live, len(self._live))
                 self._wake.notify_all()
+            for req, slot in group:
+                if slot in failed:
+                    req.future.set_exception(failed[slot])
 
     def step(self) -> bool:
         """One round (admit, launch, retire).  Returns False when there was nothing to do."""

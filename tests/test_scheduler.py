@@ -205,6 +205,75 @@ def test_overlapped_admission_gives_the_same_answers():
     assert any(len(s) < 3 for s, _ in eng.launch_log[:5])
 
 
+def test_waiting_requests_are_prefilled_together_when_the_engine_can():
+    """An engine with ``prefill_slots`` gets every waiting request that fits its row budget in one call (prompts
+    padded to multiples of 128 rows); a failing group falls back to one pass per request."""
+    class Packing(FakeEngine):
+        packed_prefill_rows = 512
+
+        def __init__(self, **kw):
+            super().__init__(**kw)
+            self.groups = []
+
+        def prefill_slots(self, slots, prompts):
+            self.groups.append([len(p) for p in prompts])
+            if any(t < 0 for p in prompts for t in p):
+                raise RuntimeError("bad token")
+            for b, p in zip(slots, prompts):
+                self.positions[b] = len(p)
+
+    eng = Packing(num_sequences=6, max_seq_len=400)
+    sch = ContinuousBatcher(eng, eos_token_id=None, quantum=4)
+    lens = [5, 130, 100, 300, 2, 7]            # rows 128 + 256 + 128 | 384 + 128 | 128
+    reqs = [(S.make_prompt(n, seed=i, vocab_size=97), 6) for i, n in enumerate(lens)]
+    reqs[4] = ([-3, 5], 6)                      # prompt_ids[:-1] holds a bad token: its group fails as a whole
+    futs = [sch.submit(ids, n) for ids, n in reqs]
+    sch.run_until_idle()
+    sch.stop()
+    assert eng.groups[0] == [4, 129, 99] and eng.groups[1] == [299, 1]
+    for i, ((ids, n), f) in enumerate(zip(reqs, futs)):
+        if i == 4:
+            with pytest.raises(RuntimeError):
+                f.result(timeout=0)
+        else:
+            assert f.result(timeout=0).tokens == FakeEngine.reference(ids, n)[0]
+
+
+@pytest.mark.gpu
+def test_gpu_packed_prefill_matches_one_prompt_per_pass(built_library):
+    """Several prompts through one tensor-core pass (``prefill_slots``): every slot's cache rows agree with a pass of
+    its own to the rounding of a different GEMM tiling, and the tokens decoded from them are the same."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from Model.Qwen06B_architecture import BatchDecoder
+    vocab = 2048
+    w = S.weights_to(S.make_weights(seed=9, num_layers=3, vocab_size=vocab, norm_std=0.1, max_seq_len=16), "cuda")
+    tok = S.StubTokenizer(-1, vocab)
+    lens = [1, 37, 128, 129, 300, 700, 64, 1000]
+    prompts = [S.make_prompt(n + 1, seed=300 + i, vocab_size=vocab) for i, n in enumerate(lens)]
+    eng = BatchDecoder(weights=w, tokenizer=tok, num_sequences=len(lens), max_seq_len=1100, engine="gemm", prefill_mode="tensor")
+    for b, ids in enumerate(prompts):
+        eng.prefill_slot(b, ids[:-1])
+    want_k = [eng._k_caches[b].clone() for b in range(len(lens))]
+    want_v = [eng._v_caches[b].clone() for b in range(len(lens))]
+    want = eng.decode_slots(list(range(len(lens))), [ids[-1] for ids in prompts], 12)
+    for b in range(len(lens)):
+        eng._k_caches[b].zero_()
+        eng._v_caches[b].zero_()
+    eng.prefill_slots(list(range(len(lens))), [ids[:-1] for ids in prompts])   # 128 + 128 + 128 + 256 + 384 + 768 + 128 + 1024 rows
+    assert eng.positions == lens
+    for b, n in enumerate(lens):
+        got_k = eng._k_caches[b].view(3, 8, -1, 128)[:, :, :n].float()
+        ref_k = want_k[b].view(3, 8, -1, 128)[:, :, :n].float()
+        got_v = eng._v_caches[b].view(3, 8, -1, 128)[:, :, :n].float()
+        ref_v = want_v[b].view(3, 8, -1, 128)[:, :, :n].float()
+        assert (got_k - ref_k).abs().max().item() < 1e-2 and (got_v - ref_v).abs().max().item() < 1e-2   # fp16 operands, other tile shapes
+        # rows past the prompt stay untouched
+        assert eng._k_caches[b].view(3, 8, -1, 128)[:, :, n:].abs().max().item() == 0
+    got = eng.decode_slots(list(range(len(lens))), [ids[-1] for ids in prompts], 12)
+    assert got == want
+
+
 @pytest.mark.gpu
 def test_gpu_overlapped_prefill_matches_serial_scheduling(built_library, tiny_cfg):
     """Tensor-core engines, 8 slots: prefill of the next request on its own stream and thread while the live
