@@ -416,6 +416,30 @@ class BatchDecoder:
         base = self._base
         return 4096 if base.prefill_mode == "tensor" else 0
 
+    def prefill_many(self, slots: Sequence[int], prompts: Sequence[Sequence[int]]) -> None:
+        """Prefill any number of slots: in packed passes of up to ``packed_prefill_rows`` rows where the engine has
+        them, a prompt longer than that (or any prompt of an engine without packed prefill) through ``prefill_slot``."""
+        budget = self.packed_prefill_rows
+        group, rows = [], 0
+
+        def flush():
+            nonlocal group, rows
+            if len(group) == 1:
+                self.prefill_slot(*group[0])
+            elif group:
+                self.prefill_slots([b for b, _ in group], [ids for _, ids in group])
+            group, rows = [], 0
+        for b, ids in zip(slots, prompts):
+            need = (max(len(ids), 1) + 127) // 128 * 128
+            if budget <= 0 or need > budget:
+                self.prefill_slot(b, ids)
+                continue
+            if group and (rows + need > budget or len(group) == 64):
+                flush()
+            group.append((b, list(ids)))
+            rows += need
+        flush()
+
     def prefill_slots(self, slots: Sequence[int], prompts: Sequence[Sequence[int]]) -> None:
         """Fill the caches of several slots in ONE tensor-core pass (``qmk_prefill_packed``): weights are read once for all
         of them and a pass's ~200 launches are shared.  Empty prompts are skipped (their slot starts at position 0)."""
@@ -485,14 +509,16 @@ class BatchDecoder:
             raise ValueError(f"between 1 and {self.num_sequences} prompts per call")
         max_tokens = int(max_tokens)
         firsts = []
+        heads = []
         for b, ids in enumerate(prompts):
             ids = list(ids)
             if not ids:
                 raise ValueError("empty prompt")
             if len(ids) - 1 + max_tokens > self.max_seq_len:
                 raise ValueError("prompt + max_tokens exceeds max_seq_len")
-            self._prefill_slot(b, ids[:-1])
+            heads.append(ids[:-1])
             firsts.append(ids[-1])
+        self.prefill_many(list(range(n)), heads)
         if max_tokens <= 0:
             return [[] for _ in range(n)]
         base = self._base
