@@ -51,11 +51,15 @@ class Result:
 
 
 class ContinuousBatcher:
-    def __init__(self, engine, eos_token_id: Optional[int] = None, quantum: int = 16, overlap_prefill: bool = False):
+    def __init__(self, engine, eos_token_id: Optional[int] = None, quantum: int = 16, overlap_prefill: bool = False,
+                 packed_prefill: bool = True):
         if quantum < 1:
             raise ValueError("quantum must be >= 1")
         self.engine = engine
         self.overlap_prefill = bool(overlap_prefill)
+        # several waiting requests per prefill pass where the engine offers it; False: one pass per request (a
+        # request's cache then does not depend on who was admitted with it, not even in the last bits)
+        self.packed_prefill = bool(packed_prefill)
         self._prefilling = 0                          # requests taken from the queue whose prefill is running
         self._admit_thread: Optional[threading.Thread] = None
         self.eos = -1 if eos_token_id is None else int(eos_token_id)
@@ -101,7 +105,7 @@ class ContinuousBatcher:
         """Prefills waiting requests into free slots until one of the two runs out.  An engine with ``prefill_slots``
         (several prompts in one pass, up to ``packed_prefill_rows`` rows after padding each to a multiple of 128)
         gets every waiting request that fits at once: a pass over one ~1000-token prompt is mostly launch latency."""
-        packed = getattr(self.engine, "prefill_slots", None)
+        packed = getattr(self.engine, "prefill_slots", None) if self.packed_prefill else None
         budget = int(getattr(self.engine, "packed_prefill_rows", 0)) if packed is not None else 0
         while True:
             with self._wake:
