@@ -378,8 +378,11 @@ def continuous_case(device, rank, world, fp16_weights, requests, slots, prefill=
     from Model.Qwen06B_architecture import BatchDecoder
     from scheduler import ContinuousBatcher
     new_tokens = 128
-    eng = BatchDecoder(weights=fp16_weights, tokenizer=S.StubTokenizer(-1), num_sequences=slots, max_seq_len=2048 + new_tokens,
-                       device=str(device), prefill_mode=prefill)
+    # `slots` sequences decode together; half as many extra cache slots hold requests that are prefilled already, so
+    # that a seat which frees up is taken in the next round (ContinuousBatcher(live_limit=...))
+    spare = min(slots // 2, 128 - slots) if prefill == "tensor" and overlap else 0
+    eng = BatchDecoder(weights=fp16_weights, tokenizer=S.StubTokenizer(-1), num_sequences=slots + spare,
+                       max_seq_len=2048 + new_tokens, device=str(device), prefill_mode=prefill)
     gen = torch.Generator("cpu").manual_seed(rank)             # a different request stream per replica
     lens = torch.randint(64, 2049, (requests,), generator=gen).tolist()
     prompts = [S.make_prompt(L, seed=1000 * rank + i) for i, L in enumerate(lens)]
@@ -400,7 +403,7 @@ def continuous_case(device, rank, world, fp16_weights, requests, slots, prefill=
             prefill_s[0] += time.perf_counter() - t
         eng.prefill_slots = timed_prefill_many
     sch = ContinuousBatcher(eng, eos_token_id=None, quantum=32,
-                            overlap_prefill=bool(overlap) and getattr(eng, "supports_overlap", False))
+                            overlap_prefill=bool(overlap) and getattr(eng, "supports_overlap", False), live_limit=slots)
     sch.submit(prompts[0][:64], 8)                             # warm-up: both kernels, all buffers
     sch.run_until_idle()
     prefill_s[0] = 0.0
@@ -419,7 +422,7 @@ def continuous_case(device, rank, world, fp16_weights, requests, slots, prefill=
                new_tokens_per_request=new_tokens, prompt_tokens=sum(lens), prefill_s=prefill_s[0],
                decode_s=own_wall - prefill_s[0], decode_only_tok_s=n_out / max(own_wall - prefill_s[0], 1e-9),
                prompt_tok_s=sum(lens) / max(prefill_s[0], 1e-9), launches=sch.launches - launches0, prefill=prefill,
-               overlap_prefill=sch.overlap_prefill, clocks=clocks.summary())
+               overlap_prefill=sch.overlap_prefill, prefilled_ahead_slots=spare, max_live=sch.max_live, clocks=clocks.summary())
     del sch, eng
     torch.cuda.empty_cache()
     return res

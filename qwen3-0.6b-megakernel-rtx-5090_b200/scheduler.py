@@ -52,9 +52,11 @@ class Result:
 
 class ContinuousBatcher:
     def __init__(self, engine, eos_token_id: Optional[int] = None, quantum: int = 16, overlap_prefill: bool = False,
-                 packed_prefill: bool = True):
+                 packed_prefill: bool = True, live_limit: Optional[int] = None):
         if quantum < 1:
             raise ValueError("quantum must be >= 1")
+        if live_limit is not None and live_limit < 1:
+            raise ValueError("live_limit must be >= 1")
         self.engine = engine
         self.overlap_prefill = bool(overlap_prefill)
         # several waiting requests per prefill pass where the engine offers it; False: one pass per request (a
@@ -65,6 +67,11 @@ class ContinuousBatcher:
         self.eos = -1 if eos_token_id is None else int(eos_token_id)
         self.quantum = int(quantum)
         self.num_slots = int(engine.num_sequences)
+        # at most this many sequences decode together; the engine's other slots hold requests that are prefilled already
+        # and take a seat in the round after one frees up (without them a seat stays empty for a round while its next
+        # request is prefilled)
+        self.live_limit = self.num_slots if live_limit is None else min(int(live_limit), self.num_slots)
+        self._ready: Deque[Request] = deque()         # prefilled, waiting for a seat
         self._waiting: Deque[Request] = deque()
         self._live: Dict[int, Request] = {}           # slot -> request
         self._free: List[int] = list(range(self.num_slots))
@@ -146,8 +153,7 @@ class ContinuousBatcher:
                     else:
                         req.slot = slot
                         req.next_token = req.prompt_ids[-1]
-                        self._live[slot] = req
-                self.max_live = max(self.max_live, len(self._live))
+                        self._ready.append(req)
                 self._wake.notify_all()
             for req, slot in group:
                 if slot in failed:
@@ -158,11 +164,15 @@ class ContinuousBatcher:
         if self.overlap_prefill:
             self._ensure_admit_thread()
             with self._wake:                   # nothing live yet but a prefill is on its way: wait for it
-                while not self._live and (self._prefilling or (self._waiting and self._free)):
+                while not self._live and not self._ready and (self._prefilling or (self._waiting and self._free)):
                     self._wake.wait(timeout=0.05)
         else:
             self._admit()
         with self._lock:
+            while self._ready and len(self._live) < self.live_limit:
+                r = self._ready.popleft()
+                self._live[r.slot] = r
+            self.max_live = max(self.max_live, len(self._live))
             live = [self._live[s] for s in sorted(self._live)]
         if not live:
             return False
@@ -223,7 +233,7 @@ class ContinuousBatcher:
             if self.step():
                 continue
             with self._lock:
-                if not self._waiting and not self._live and not self._prefilling:
+                if not self._waiting and not self._live and not self._prefilling and not self._ready:
                     return
 
     # ------------------------------------------------------------------ background driver
@@ -254,8 +264,8 @@ class ContinuousBatcher:
                 with self._wake:
                     if self._stop:
                         return
-                    if not self._waiting and not self._live and not self._prefilling:
+                    if not self._waiting and not self._live and not self._prefilling and not self._ready:
                         self._wake.wait(timeout=0.5)
             with self._lock:
-                if self._stop and not self._waiting and not self._live and not self._prefilling:
+                if self._stop and not self._waiting and not self._live and not self._prefilling and not self._ready:
                     return

@@ -205,6 +205,24 @@ def test_overlapped_admission_gives_the_same_answers():
     assert any(len(s) < 3 for s, _ in eng.launch_log[:5])
 
 
+def test_live_limit_keeps_spare_slots_for_prefilled_requests():
+    """With ``live_limit`` below the engine's slot count no launch carries more sequences than the limit; the other
+    slots hold prefilled requests that take a seat as soon as one frees up, and every answer is still its own."""
+    eng = FakeEngine(num_sequences=6)
+    sch = ContinuousBatcher(eng, eos_token_id=None, quantum=4, live_limit=3)
+    reqs = [(S.make_prompt(2 + (i * 3) % 7, seed=i, vocab_size=97), 3 + (i * 5) % 17) for i in range(14)]
+    futs = [sch.submit(ids, n) for ids, n in reqs]
+    sch.run_until_idle()
+    sch.stop()
+    for (ids, n), f in zip(reqs, futs):
+        assert f.result(timeout=0).tokens == FakeEngine.reference(ids, n)[0]
+    assert sch.max_live == 3 and all(len(s) <= 3 for s, _ in eng.launch_log)
+    full = sum(1 for s, _ in eng.launch_log if len(s) == 3)
+    assert full >= len(eng.launch_log) - 4        # seats are refilled at once: only the last rounds run short
+    with pytest.raises(ValueError):
+        ContinuousBatcher(eng, live_limit=0)
+
+
 def test_waiting_requests_are_prefilled_together_when_the_engine_can():
     """An engine with ``prefill_slots`` gets every waiting request that fits its row budget in one call (prompts
     padded to multiples of 128 rows); a failing group falls back to one pass per request."""
