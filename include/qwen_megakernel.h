@@ -205,7 +205,9 @@ int qmk_set_decode_attention(int tensor_core);
 /* Batched decode (qmk_decode_batched): 1 (default) launches the ~200 kernels of a decode step as programmatic
  * dependents of one another - each kernel is scheduled while its predecessor still runs, sets itself up, streams the
  * operands no kernel of the step writes (weight tiles, cache rows of earlier steps) and only then waits for the
- * predecessor to complete; 0 launches them strictly one after the other.  Same results either way; negative keeps. */
+ * predecessor to complete; 0 launches them strictly one after the other.  The same switch covers the GEMMs of
+ * qmk_prefill_chunked / qmk_prefill_packed (only the GEMMs: the other kernels of a prefill pass always launch
+ * plainly).  Same results either way; negative keeps. */
 int qmk_set_step_overlap(int enabled);
 
 /* Kernel choice for one sequence (qmk_decode / qmk_generate / qmk_prefill); negative keeps a value.

@@ -653,10 +653,14 @@ int prefill_impl(const int *token_ids_host, int num_tokens, const void *embed_we
       if (rc != QMK_OK) break;
     }
     PF_CUDA(cudaMemcpyAsync(w.tokens, token_ids_host + c0, sizeof(int) * T, cudaMemcpyHostToDevice, stream));
-    // Plain launches: programmatic dependent launch was tried on this chain too; it gained nothing (these kernels are
-    // long) and a decode launched after such a prefill produced run-to-run different logits although every cache
-    // row compared bit-identical afterwards - unexplained, so the chain stays strictly serial.
+    // Programmatic dependent launch for the GEMMs only: their set-up and first ring fill of WEIGHT tiles run under the
+    // tail of the kernel before them (every kernel here lasts 2-6 us longer than its CTAs run; 2048 tokens 4.11 -> 3.81
+    // ms).  The row kernels and the attention kernel launch plainly: with EVERY kernel of this chain launched as a
+    // programmatic dependent, a decode launched after the prefill had returned produced run-to-run different logits
+    // although every cache row compared bit-identical afterwards - unexplained; the attribute on the GEMMs alone never
+    // showed it (128 prefill + decode cycles compared bit for bit, and the test that found it runs every time).
     qmk_tc::PdlScope pdl_scope(false);
+    const bool pdl_gemm = env.pdl != 0;
     qmk_tc::RingBudgetScope ring_scope(PREFILL_RING_BYTES);   // two GEMM CTAs per SM: one's epilogue under the other's main loop
     {
       qmk_tc::PdlScope first(false);            // (follows a copy, not a kernel)
@@ -681,7 +685,10 @@ int prefill_impl(const int *token_ids_host, int num_tokens, const void *embed_we
         // fp16 q / k / v: every CTA of this launch reaches its epilogue at the same time, and the burst of stores set
         // its length (9.8 of 26 us at 2048 rows with fp32); the consumer below rounds to fp16 anyway
         qmk_tc::set_out_f16(true);
-        rc = gemm_group(w.map_xn, l, 3, js, cs, ns, M, H, T);
+        {
+          qmk_tc::PdlScope g(pdl_gemm);
+          rc = gemm_group(w.map_xn, l, 3, js, cs, ns, M, H, T);
+        }
         qmk_tc::set_out_f16(false);
         if (rc != QMK_OK) break;
       }
@@ -703,18 +710,28 @@ int prefill_impl(const int *token_ids_host, int num_tokens, const void *embed_we
       else
         PF_CUDA(qmk_tc::launch_kernel(causal_attention_mma, dim3((T + ATM_Q - 1) / ATM_Q, NKV), dim3(ATM_THREADS), ATM_SMEM_BYTES, stream,
                                       w.qr, kc, vc, w.attn, T, pos0, max_seq_len, attn_scale));
-      if ((rc = gemm_od(w.map_attn, l, 3, w.o, M, QS, T)) != QMK_OK) break;
+      {
+        qmk_tc::PdlScope g(pdl_gemm);
+        rc = gemm_od(w.map_attn, l, 3, w.o, M, QS, T);
+      }
+      if (rc != QMK_OK) break;
       PF_CUDA(norm_rows(w.o, reinterpret_cast<const __half *>(r[7])));
       {
         const int box_gu = qmk_tc::gemm_box_n_fused(M, I);
         // three of these CTAs per SM instead of two: their epilogue (two TMEM reads, SiLU, fp16 pack) is the long part
         qmk_tc::RingBudgetScope gu_scope(M >= 1024 ? GATE_UP_RING_BYTES : PREFILL_RING_BYTES);
-        if ((rc = qmk_tc::launch_gemm_swiglu(w.map_xn, wmap_for(l, 4, box_gu), wmap_for(l, 5, box_gu), w.act, M, I, H,
-                                             w.status, env.timeout_ms, stream, &err, box_gu, T, 0, wq, wptr(l, 4),
-                                             wptr(l, 5))) != QMK_OK)
-          break;
+        {
+          qmk_tc::PdlScope g(pdl_gemm);
+          rc = qmk_tc::launch_gemm_swiglu(w.map_xn, wmap_for(l, 4, box_gu), wmap_for(l, 5, box_gu), w.act, M, I, H, w.status,
+                                          env.timeout_ms, stream, &err, box_gu, T, 0, wq, wptr(l, 4), wptr(l, 5));
+        }
+        if (rc != QMK_OK) break;
       }
-      if ((rc = gemm_od(w.map_act, l, 6, w.down, M, I, T)) != QMK_OK) break;
+      {
+        qmk_tc::PdlScope g(pdl_gemm);
+        rc = gemm_od(w.map_act, l, 6, w.down, M, I, T);
+      }
+      if (rc != QMK_OK) break;
     }
     if (rc != QMK_OK) break;
     PF_CUDA(cudaGetLastError());     // (the next chunk's token copy is stream-ordered behind this chunk's kernels)
