@@ -74,7 +74,8 @@ def build_prompt(tokenizer, messages: List[Message]) -> str:
 def _load_decoder(model_name: str):
     """``BATCH_SLOTS`` > 1 (up to 128; above 4 the tensor-core batched decode) loads the multi-sequence
     engine: requests are then served concurrently by the continuous-batching scheduler, with tensor-core
-    prefill, instead of one at a time."""
+    prefill (several waiting prompts per pass), instead of one at a time.  ``BATCH_LIVE`` (optional, below
+    ``BATCH_SLOTS``) caps the sequences that decode together; the remaining slots are prefilled ahead."""
     from Model.Qwen06B_architecture import BatchDecoder, Decoder, load_weights
     slots = int(os.getenv("BATCH_SLOTS", "1"))
     if os.getenv("SYNTHETIC", "0") == "1":
@@ -103,8 +104,11 @@ def create_app(decoder=None, model_name: Optional[str] = None, default_max_token
         if state["batcher"] is None and hasattr(dec, "decode_slots"):   # multi-sequence engine
             from scheduler import ContinuousBatcher
             eos = getattr(dec.tokenizer, "eos_token_id", None)
+            # BATCH_LIVE < BATCH_SLOTS: that many sequences decode together, the other slots hold prefilled requests
+            live = int(os.getenv("BATCH_LIVE", "0"))
             state["batcher"] = ContinuousBatcher(dec, eos_token_id=eos, quantum=int(os.getenv("BATCH_QUANTUM", "16")),
-                                                 overlap_prefill=getattr(dec, "supports_overlap", False))
+                                                 overlap_prefill=getattr(dec, "supports_overlap", False),
+                                                 live_limit=live if live > 0 else None)
             state["batcher"].start()
 
     @asynccontextmanager
