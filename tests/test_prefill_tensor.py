@@ -97,8 +97,8 @@ def test_appends_at_a_start_position_and_agrees_with_serial_prefill(C):
 
 @pytest.mark.parametrize("n_prompt", [150, 900])
 def test_table_rope_mode(C, n_prompt):
-    """fp16 cos / sin tables instead of the fp32 in-library table: 150 tokens take the row kernel for QK-norm + RoPE,
-    900 tokens the q/k/v GEMM's per-head epilogue (128-wide tiles)."""
+    """fp16 cos / sin tables instead of the fp32 in-library table, for a short chunk (block-per-row norm kernel, four K
+    splits) and a longer one (warp-per-row norm kernel)."""
     vocab, L = 2048, 1024
     w = S.make_weights(seed=14, num_layers=2, vocab_size=vocab, norm_std=0.1, max_seq_len=L)
     ids = S.make_prompt(n_prompt, seed=4, vocab_size=vocab)

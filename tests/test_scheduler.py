@@ -258,18 +258,31 @@ def test_waiting_requests_are_prefilled_together_when_the_engine_can():
 
 
 @pytest.mark.gpu
-def test_gpu_packed_prefill_matches_one_prompt_per_pass(built_library):
+@pytest.mark.parametrize("table_rope", [False, True])
+def test_gpu_packed_prefill_matches_one_prompt_per_pass(built_library, table_rope):
     """Several prompts through one tensor-core pass (``prefill_slots``): every slot's cache rows agree with a pass of
-    its own to the rounding of a different GEMM tiling, and the tokens decoded from them are the same."""
+    its own to the rounding of a different GEMM tiling, and the tokens decoded from them are the same.  Also with
+    the rotary angles read from the fp16 cos / sin tables."""
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
+    import qwen_megakernel_C as C
     from Model.Qwen06B_architecture import BatchDecoder
     vocab = 2048
     w = S.weights_to(S.make_weights(seed=9, num_layers=3, vocab_size=vocab, norm_std=0.1, max_seq_len=16), "cuda")
     tok = S.StubTokenizer(-1, vocab)
     lens = [1, 37, 128, 129, 300, 700, 64, 1000]
     prompts = [S.make_prompt(n + 1, seed=300 + i, vocab_size=vocab) for i, n in enumerate(lens)]
-    eng = BatchDecoder(weights=w, tokenizer=tok, num_sequences=len(lens), max_seq_len=1100, engine="gemm", prefill_mode="tensor")
+    if table_rope:
+        w = S.weights_to(S.make_weights(seed=9, num_layers=3, vocab_size=vocab, norm_std=0.1, max_seq_len=1100), "cuda")
+    eng = BatchDecoder(weights=w, tokenizer=tok, num_sequences=len(lens), max_seq_len=1100, engine="gemm", prefill_mode="tensor",
+                       rope_from_table=table_rope)
+    try:
+        _packed_against_single(eng, lens, prompts)
+    finally:
+        C.configure(rope_from_table=0)
+
+
+def _packed_against_single(eng, lens, prompts):
     for b, ids in enumerate(prompts):
         eng.prefill_slot(b, ids[:-1])
     want_k = [eng._k_caches[b].clone() for b in range(len(lens))]
