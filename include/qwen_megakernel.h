@@ -318,7 +318,7 @@ int qmk_generate_static(
  * layout, position rule and blocking behaviour as qmk_prefill; all three weight formats (packed FP8 / NVFP4 matrices
  * stay packed in HBM and are expanded to fp16 tiles inside the GEMM, see qmk_gemm_packed_tn).  GEMM operands are rounded to fp16 (the
  * decode kernel keeps fp32 activations), so cache rows agree with qmk_prefill's to fp16 rounding, not
- * bit for bit.  Scratch (about 160 MB) is allocated on the first call per device. */
+ * bit for bit.  Scratch (about 230 MB) is allocated on the first call per device. */
 int qmk_prefill_chunked(
     const int *token_ids_host, int num_tokens, const void *embed_weight,
     const struct LDGLayerWeight *layer_weights, const void *cos_table, const void *sin_table,
