@@ -22,7 +22,8 @@
 // V ring (a K slot is free again as soon as its S product is done, a V slot after its P . V), one thread issues the
 // score MMAs and one the P . V MMAs.  The scores have two buffers of 128 TMEM columns; a buffer is free again as soon
 // as both chains have read it into registers, so the scores run a pair ahead and the softmax warps only wait (for
-// "O has taken the chain's previous tile", one commit) before they overwrite P or rescale O.  One CTA per SM
+// "O has taken the chain's previous tile", one commit) before they overwrite P or rescale O.  The query tile arrives
+// by TMA as fp16 (the kernel before this one stores the rotated queries that way, pre-scaled).  One CTA per SM
 // (193 KB of shared memory, all 512 TMEM columns).  Every wait is bounded (status 4).
 #ifndef QMK_ATTENTION_TCGEN05_CUH_
 #define QMK_ATTENTION_TCGEN05_CUH_
@@ -100,7 +101,8 @@ __device__ __forceinline__ float fast_exp2(float x) {
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])                                                    \
       : "memory")
 
-// qr: fp32 [T][16 heads][128] (normalised, rotated queries of the chunk; query t sits at position pos0 + t and sees
+// map_q: 2-D map of the fp16 queries [rows][16 heads x 128] (normalised, rotated, times scale * log2 e), boxes of
+// {64, 128}, 128-byte swizzle; query t sits at position pos0 + t and sees
 // cache rows 0 .. pos0 + t).  map_k / map_v: 3-D maps {128 dims, pos0 + T rows, layers x 8 kv heads} of the fp16
 // caches, boxes of {64, 64, 1}, 128-byte swizzle.  out: fp16 [T][2048].  grid = ceil(T / 128) * 16 CTAs in one
 // dimension, numbered from the heaviest (last) query tile down: causal tile i sees 2 (i + 1) key tiles of 64.
@@ -110,7 +112,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // from the heaviest down by the host) and reads that sequence's caches through maps_dev[2 seq], maps_dev[2 seq + 1]
 // in device memory; T and pos0 are then not used.
 __global__ void __launch_bounds__(THREADS, 1)
-causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+causal_attention_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                     int layer_head0, __half *out, int T, int pos0, float scale, unsigned int *status,
                     unsigned long long budget_ns, const int4 *items, const CUtensorMap *maps_dev) {
   using namespace qmk_gemm;
@@ -143,7 +145,8 @@ causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, 
   auto s_free = [&](int b) { return bars + 8u * (18 + b); };
   auto p_ready = [&](int c) { return bars + 8u * (20 + c); };      // per chain
   auto pv_done = [&](int c) { return bars + 8u * (22 + c); };
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(attn_smem + OFF_BARS + 8 * 24);
+  const uint32_t q_full = bars + 8u * 24;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(attn_smem + OFF_BARS + 8 * 25);
   static_assert(STAGES == 4 && CHAINS == 2, "barrier layout above");
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
@@ -152,6 +155,7 @@ causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, 
     return;
   }
   if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
     if (items == nullptr) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
@@ -167,6 +171,7 @@ causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, 
       bar_init(p_ready(c), 4);      // one arrival per softmax warp of the chain
       bar_init(pv_done(c), 1);
     }
+    bar_init(q_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -177,8 +182,8 @@ causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, 
   }
   pdl_wait();   // queries and this chunk's cache rows come from the kernel launched just before
   pdl_trigger();
-  // the K ring's first fill goes out before the query tile is converted (thread 0 is the K producer and has just
-  // initialised the barriers itself); a CTA's fixed costs weigh as much as its first key tiles
+  // the query tile and the K ring's first fill go out at once (thread 0 is the K producer and has just initialised
+  // the barriers itself); a CTA's fixed costs weigh as much as its first key tiles
   auto load_tile = [&](bool is_v, int j) {
     const int s = j % STAGES;
     const uint32_t full = is_v ? v_full(s) : k_full(s);
@@ -194,32 +199,14 @@ causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, 
     asm volatile("fence.proxy.tensormap::generic.acquire.sys [%0], 128;" ::"l"(reinterpret_cast<uint64_t>(mk)) : "memory");
     asm volatile("fence.proxy.tensormap::generic.acquire.sys [%0], 128;" ::"l"(reinterpret_cast<uint64_t>(mv)) : "memory");
   }
-  if (threadIdx.x == 0)
+  if (threadIdx.x == 0) {
+    // the query tile: fp16, already times scale * log2 e (the softmax is an exp2), as two [128 x 64] boxes in the
+    // K-major 128-byte-swizzled layout the score MMAs read; rows past the live ones hold other tokens' or stale
+    // finite values and are never stored
+    bar_expect_tx(q_full, Q_BYTES);
+    tma_load_2d(base, &map_q, head * D, q0, q_full);
+    tma_load_2d(base + TQ * 128, &map_q, head * D + 64, q0, q_full);
     for (; k_prefilled < STAGES && k_prefilled < ntiles; ++k_prefilled) load_tile(false, k_prefilled);
-  if (warp >= 2 && warp < 2 + 4 * CHAINS) {
-    // Q tile: fp32 -> fp16 (times scale * log2 e, so that the softmax is an exp2), stored as two [128 x 64] tiles in
-    // the K-major 128-byte-swizzled layout: row r, 16-byte segment s of a tile at r * 128 + ((s ^ (r & 7)) << 4)
-    const float sc = scale * 1.4426950408889634f;
-    const int w = warp - 2;
-    constexpr int ROWS_PER_WARP = TQ / (4 * CHAINS);
-    float4 qv[ROWS_PER_WARP];              // every load of the warp in flight at once: one round trip, not sixteen
-#pragma unroll
-    for (int i = 0; i < ROWS_PER_WARP; ++i) {
-      const int t = q0 + w + i * 4 * CHAINS;
-      qv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (t < T) qv[i] = __ldg(reinterpret_cast<const float4 *>(qr + (static_cast<size_t>(t) * NQ + head) * D + 4 * lane));
-    }
-#pragma unroll
-    for (int i = 0; i < ROWS_PER_WARP; ++i) {
-      const int r = w + i * 4 * CHAINS;
-      const float4 v = qv[i];
-      const __half2 lo = __floats2half2_rn(v.x * sc, v.y * sc), hi = __floats2half2_rn(v.z * sc, v.w * sc);
-      const int d = 4 * lane, tile = d >> 6, seg = (d & 63) >> 3, within = (d & 7) * 2;
-      const uint32_t addr = base + tile * (TQ * 128) + r * 128 + (((seg ^ (r & 7)) << 4)) + within;
-      asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(*reinterpret_cast<const uint32_t *>(&lo)),
-                   "r"(*reinterpret_cast<const uint32_t *>(&hi)) : "memory");
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -255,7 +242,8 @@ causal_attention_tc(const float *qr, const __grid_constant__ CUtensorMap map_k, 
       for (int p = 0; p < npairs && ok; ++p) {
         const int j0 = 2 * p, s0 = j0 % STAGES;               // s0 is 0 or 2: slots s0 and s0 + 1 are adjacent
         const bool two = j0 + 1 < ntiles;                     // (an odd last tile goes alone, 64 wide)
-        ok = bar_wait(k_full(s0), (j0 / STAGES) & 1, abort_flag, status, budget_ns) &&
+        ok = (p > 0 || bar_wait(q_full, 0, abort_flag, status, budget_ns)) &&
+             bar_wait(k_full(s0), (j0 / STAGES) & 1, abort_flag, status, budget_ns) &&
              (!two || bar_wait(k_full(s0 + 1), (j0 / STAGES) & 1, abort_flag, status, budget_ns)) &&
              (p < 2 || bar_wait(s_free(p & 1), ((p >> 1) - 1) & 1, abort_flag, status, budget_ns));   // both chains have read pair p - 2
         if (!ok) break;

@@ -592,7 +592,7 @@ __device__ __noinline__ uint32_t slice_cols(const Params &P, Ctx c, int which) {
   unsigned long long *mine = P.red + (which ? RED_X2 : RED_X1) + (c.cta % P.red_copies) * H;
   const int nch = (nrows + CH_ROWS - 1) / CH_ROWS;
   const bool two = nrows > 16;
-  const int fb = which ? 30 : 20;
+  [[maybe_unused]] const int fb = which ? 30 : 20;
   QMK_FINE(fb + 0);
   bool ok = true;
   if (c.lane < nch) {

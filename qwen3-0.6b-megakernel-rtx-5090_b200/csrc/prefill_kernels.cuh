@@ -161,6 +161,7 @@ add_rmsnorm_rows_wide(float *x, const float *add, int nparts, size_t part_stride
 // all four issued before the first is used (the kernel is a few dependent round trips per warp: with one head per warp
 // and four blocks per token it spent 13 us on seven waves of blocks at 2048 tokens).
 // in_f16: q / k / v hold fp16 (the projection's epilogue stored halves) instead of fp32.
+// q_f16_scale != 0: the rotated queries are stored as fp16 times that factor (same [t][head][128] layout in halves).
 // Packed prompts (row_info != null): row t belongs to sequence row_info[t].x at position row_info[t].y (negative:
 // a padding row, nothing to do), whose K / V caches start at kv_ptrs[2 seq], kv_ptrs[2 seq + 1]; the layer's rows
 // begin `layer_off` halves into each.
@@ -168,7 +169,8 @@ __global__ void __launch_bounds__(256)
 qk_norm_rope_cache(const float *q, const float *k, const float *v, int in_f16, const __half *q_norm,
                    const __half *k_norm, const float *rope, const __half *cos_table,
                    const __half *sin_table, float *qr, __half *k_cache_layer, __half *v_cache_layer,
-                   int pos0, int max_seq_len, const int2 *row_info, const unsigned long long *kv_ptrs, size_t layer_off) {
+                   int pos0, int max_seq_len, const int2 *row_info, const unsigned long long *kv_ptrs, size_t layer_off,
+                   float q_f16_scale) {
   pdl_wait();
   pdl_trigger();
   const int t = blockIdx.x, w = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -237,7 +239,10 @@ qk_norm_rope_cache(const float *q, const float *k, const float *v, int in_f16, c
     } else {            // high half: lo * sin + hi * cos
       r = make_float4(o.x * sn.x + a.x * cs.x, o.y * sn.y + a.y * cs.y, o.z * sn.z + a.z * cs.z, o.w * sn.w + a.w * cs.w);
     }
-    if (h < 2)
+    if (h < 2 && q_f16_scale != 0.f)   // fp16 queries, pre-scaled: the tcgen05 attention kernel takes them by TMA as they are
+      *reinterpret_cast<uint2 *>(reinterpret_cast<__half *>(qr) + (static_cast<size_t>(t) * NQ + w + 8 * h) * D + d0) =
+          pack4(r.x * q_f16_scale, r.y * q_f16_scale, r.z * q_f16_scale, r.w * q_f16_scale);
+    else if (h < 2)
       *reinterpret_cast<float4 *>(qr + (static_cast<size_t>(t) * NQ + w + 8 * h) * D + d0) = r;
     else
       *reinterpret_cast<uint2 *>(k_cache_layer + (static_cast<size_t>(w) * max_seq_len + pos) * D + d0) = pack4(r.x, r.y, r.z, r.w);

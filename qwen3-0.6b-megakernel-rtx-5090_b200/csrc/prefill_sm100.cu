@@ -372,7 +372,7 @@ struct Workspace {                  // per device, allocated on first use, never
   float *x = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *qr = nullptr, *o = nullptr, *down = nullptr;
   __half *xn = nullptr, *attn = nullptr, *act = nullptr;
   unsigned int *status = nullptr;
-  CUtensorMap map_xn, map_attn, map_act;
+  CUtensorMap map_xn, map_attn, map_act, map_qh;
   // batched decode: per-sequence state and the logits of one step
   int *positions = nullptr, *start_positions = nullptr;
   cudaStream_t gstream = nullptr;        // capture needs a non-default stream
@@ -439,10 +439,13 @@ int ensure_workspace(Workspace &w, int rows) {
   PF_CUDA(cudaMemset(w.xn, 0, sizeof(__half) * C * H));
   PF_CUDA(cudaMemset(w.attn, 0, sizeof(__half) * C * QS));
   PF_CUDA(cudaMemset(w.act, 0, sizeof(__half) * C * I));
+  PF_CUDA(cudaMemset(w.qr, 0, sizeof(float) * C * QS));
   std::string err;
   int rc = qmk_tc::make_map_f16(&w.map_xn, w.xn, C, H, qmk_gemm::BM, &err);
   if (rc == QMK_OK) rc = qmk_tc::make_map_f16(&w.map_attn, w.attn, C, QS, qmk_gemm::BM, &err);
   if (rc == QMK_OK) rc = qmk_tc::make_map_f16(&w.map_act, w.act, C, I, qmk_gemm::BM, &err);
+  // the rotated queries as fp16 (the first half of the fp32 buffer), read by the attention kernel in 128-row boxes
+  if (rc == QMK_OK) rc = qmk_tc::make_map_f16(&w.map_qh, w.qr, C, QS, qmk_gemm::BM, &err);
   if (rc != QMK_OK) return qmk_internal::report(rc, err);
   w.ready = true;
   return QMK_OK;
@@ -699,11 +702,12 @@ int prefill_impl(const int *token_ids_host, int num_tokens, const void *embed_we
                                     w.qr, kc, vc, pos0, max_seq_len,
                                     pk ? reinterpret_cast<const int2 *>(w.packed + PK_ROWS_OFF) : nullptr,
                                     pk ? reinterpret_cast<const unsigned long long *>(w.packed + PK_PTRS_OFF) : nullptr,
-                                    static_cast<size_t>(l) * layer_stride));
+                                    static_cast<size_t>(l) * layer_stride,
+                                    env.attn_tc ? attn_scale * 1.4426950408889634f : 0.f));
       if (l == num_layers - 1) break;   // the cache is complete; nothing downstream of the last layer is kept
       if (env.attn_tc)
         PF_CUDA(qmk_tc::launch_kernel(qmk_attn::causal_attention_tc, dim3(pk ? pk_items : (T + qmk_attn::TQ - 1) / qmk_attn::TQ * NQ),
-                                      dim3(qmk_attn::THREADS), qmk_attn::SMEM_BYTES, stream, w.qr, map_kc, map_vc, l * NKV, w.attn, T,
+                                      dim3(qmk_attn::THREADS), qmk_attn::SMEM_BYTES, stream, w.map_qh, map_kc, map_vc, l * NKV, w.attn, T,
                                       pos0, attn_scale, w.status, static_cast<unsigned long long>(env.timeout_ms) * 1000000ull,
                                       pk ? reinterpret_cast<const int4 *>(w.packed + PK_ITEMS_OFF) : nullptr,
                                       pk ? reinterpret_cast<const CUtensorMap *>(w.packed + PK_MAPS_OFF) : nullptr));
